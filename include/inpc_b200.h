@@ -1,0 +1,223 @@
+/*
+ * inpc_b200 — C ABI of the B200-native (sm_100a) replacement for the INPC CUDA backend.
+ *
+ * Every entry point takes plain device pointers, sizes and a CUDA stream (passed as void*, i.e. a
+ * cudaStream_t; NULL is the legacy default stream).  No torch types cross this boundary.  All
+ * functions return 0 on success or a negative INPC_E_* code; inpc_last_error() returns a message
+ * for the last failure on the calling thread.  Unless stated otherwise a call only enqueues work
+ * on `stream` and returns; the few calls that must read a count back say so.
+ *
+ * Each declaration cites the interface of the reference project it replaces, as
+ * path:line below INPCCudaBackend/INPCCudaBackend/ of nerficg-project/INPC.
+ */
+#ifndef INPC_B200_H
+#define INPC_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define INPC_OK 0
+#define INPC_E_INVALID (-1)   /* bad argument (mode, tile size, null pointer, size out of range) */
+#define INPC_E_CUDA (-2)      /* a CUDA runtime call failed; message has the CUDA error string */
+#define INPC_E_ALLOC (-3)     /* the allocator callback returned NULL */
+#define INPC_E_DEVICE (-4)    /* a kernel reported a failed internal check (bounded wait ran out) */
+#define INPC_E_CAPACITY (-5)  /* size beyond a fixed capacity of the called entry point */
+
+#define INPC_MODE_BILINEAR 0
+#define INPC_MODE_GAUSSIAN 1
+
+/* Scratch allocator: returns a device pointer to at least `bytes` bytes (256-byte aligned), valid
+ * until the matching backward has run.  Replaces the three std::function<char*(size_t)> resize
+ * callbacks of rasterization/include/bilinear/forward.h:11-13 (torch_utils.h:6-11). */
+typedef void* (*inpc_alloc_fn)(void* user, size_t bytes);
+
+/* Pinhole camera and raster parameters.  `w2c` and `cam_position` stay device pointers exactly as
+ * in the reference (rows 0..2 of a row-major 4x4 float matrix; 3 floats).  Mirrors the scalar tail
+ * of rasterization/include/bilinear/forward.h:22-30 and RasterizerSettings.as_tuple()
+ * (torch_bindings/rasterization.py:20-46). */
+typedef struct inpc_view {
+    const float* w2c;           /* device, 16 floats */
+    const float* cam_position;  /* device, 3 floats */
+    int32_t width, height;
+    float fx, fy, cx, cy;
+    float near_plane, far_plane;
+} inpc_view;
+
+/* What forward hands to backward; plain data, no ownership.  Replaces the (n_instances, selector)
+ * pair plus the three blob base pointers the reference keeps on the autograd context
+ * (torch_bindings/rasterization.py:62-74). */
+typedef struct inpc_raster_state {
+    void* point_blob;     /* per-point scratch from alloc_point */
+    void* instance_blob;  /* per-instance + per-tile scratch from alloc_instance */
+    int64_t n_points;
+    int64_t n_visible;
+    int64_t n_instances;
+    int32_t tile_size;
+    int32_t mode;
+} inpc_raster_state;
+
+const char* inpc_last_error(void);
+/* Library/ABI version as major*10000 + minor*100 + patch. */
+int inpc_version(void);
+
+/* ------------------------------------------------------------------------------------------
+ * Rasterizer
+ * ---------------------------------------------------------------------------------------- */
+
+/* Training forward: cull/project/SH-evaluate, order by (tile, depth), blend front to back.
+ *   positions (n,3) f32 | features (n,36) f16, coefficient-major channel-minor | opacities (n) f32
+ *   image (4,H,W) f32 | alpha (H,W) f32 | blending_weights (n) f32 — all three fully written.
+ * tile_size is 8 (the reference's tiling; tile ranges comparable with it) or 16.
+ * Reads two counters back to the host once (n_visible, n_instances) to size the instance scratch;
+ * this is the only host synchronisation (the reference has two).
+ * Replaces inpc::rasterization::{bilinear,gaussian}::forward
+ * (rasterization/include/bilinear/forward.h:10-30, gaussian/forward.h:10-30) together with the
+ * output zero-fill of forward_wrapper (rasterization/src/rasterization_api.cu:44-46). */
+int inpc_rasterize_forward(int mode, int tile_size, const inpc_view* view, int64_t n,
+                           const float* positions, const void* features, const float* opacities,
+                           float* image, float* alpha, float* blending_weights,
+                           inpc_alloc_fn alloc_point, inpc_alloc_fn alloc_instance, void* alloc_user,
+                           inpc_raster_state* state, void* stream);
+
+/* Training backward for the forward that produced `state`.
+ *   grad_image (4,H,W), grad_alpha (H,W), image, alpha: as returned by / upstream of forward
+ *   grad_features (n,36) f16 and grad_opacities (n) f32 — fully written (zero rows for culled points)
+ *   grad_features_view (n,4) f32 — caller scratch for the per-point view-space gradient
+ * Replaces inpc::rasterization::{bilinear,gaussian}::backward
+ * (rasterization/include/bilinear/backward.h:8-26) together with the three zero-fills of
+ * backward_wrapper (rasterization/src/rasterization_api.cu:138-140). */
+int inpc_rasterize_backward(const inpc_raster_state* state, const inpc_view* view,
+                            const float* grad_image, const float* grad_alpha, const float* image,
+                            const float* alpha, const float* positions, const float* opacities,
+                            float* grad_features_view, void* grad_features, float* grad_opacities,
+                            void* stream);
+
+/* Inference from raw network output: features_raw (n,37) f16 = [opacity logit, 36 SH halves];
+ * opacity = 1 - exp(-exp(raw)).  Writes image (4,H,W), depth (H,W), alpha (H,W).
+ * sigma_world / sigma_cutoff are used by the gaussian mode only.
+ * Replaces inpc::rasterization::{bilinear,gaussian}::inference
+ * (rasterization/include/bilinear/inference.h:9-28, gaussian/inference.h:9-30). */
+int inpc_render(int mode, int tile_size, const inpc_view* view, int64_t n, const float* positions,
+                const void* features_raw, float sigma_world, float sigma_cutoff, float* image,
+                float* depth, float* alpha, inpc_alloc_fn alloc_point, inpc_alloc_fn alloc_instance,
+                void* alloc_user, void* stream);
+
+/* Inference from a pre-extracted point cloud; `scales` (n) f32 may be NULL (gaussian mode then uses
+ * sigma_world for every point).
+ * Replaces inpc::rasterization::{bilinear,gaussian}::inference_preextracted
+ * (rasterization/include/bilinear/inference_preextracted.h:9-29,
+ *  gaussian/inference_preextracted.h:9-32). */
+int inpc_render_preextracted(int mode, int tile_size, const inpc_view* view, int64_t n,
+                             const float* positions, const void* features, const float* opacities,
+                             const float* scales, float sigma_world, float sigma_cutoff, float* image,
+                             float* depth, float* alpha, inpc_alloc_fn alloc_point,
+                             inpc_alloc_fn alloc_instance, void* alloc_user, void* stream);
+
+/* Introspection for parity tests: copies one intermediate array of the forward that produced
+ * `state` into `dst` (device pointer, caller-sized).  which: 0 sorted visible point ids (n_visible
+ * u32) | 1 sorted depth keys (n_visible u32) | 2 sorted instance point ids (n_instances u32) |
+ * 3 tile ranges (2 u32 per tile) | 4 tiles touched per point (n u32) | 5 screen xy (n,2 f32) |
+ * 6 depth (n f32) | 7 view-space feature (n,4 f32) | 8 tile bounds x0,x1,y0,y1 (n,4 u16).
+ * These are the arrays the reference keeps in PerPrimitiveBuffers / PerInstanceBuffers /
+ * PerTileBuffers (rasterization/include/bilinear/buffer_utils.h:24-115). */
+int inpc_raster_debug_copy(const inpc_raster_state* state, const inpc_view* view, int which, void* dst,
+                           void* stream);
+
+/* Stable least-significant-digit radix sort of (u32 key, u32 value) pairs on bits [0, end_bit),
+ * the library's own onesweep.  keys_alt / values_alt are same-sized ping-pong buffers; `workspace`
+ * needs inpc_sort_workspace_bytes(n).  *result_in_alt tells which pair holds the result.
+ * Replaces the two cub::DeviceRadixSort::SortPairs calls of
+ * rasterization/src/bilinear/forward.cu:91-98 and :132-139. */
+size_t inpc_sort_workspace_bytes(int64_t n);
+int inpc_sort_pairs(uint32_t* keys, uint32_t* keys_alt, uint32_t* values, uint32_t* values_alt, int64_t n,
+                    int end_bit, void* workspace, int* result_in_alt, void* stream);
+
+/* ------------------------------------------------------------------------------------------
+ * Probability-field sampler
+ * ---------------------------------------------------------------------------------------- */
+
+/* Per-leaf sampling weight for one viewpoint.  centers (L,3) f32, levels (L) i32, weights (L) f32,
+ * out (L) f32.  Replaces inpc::sampling::compute_viewpoint_weights (sampling/include/sampling.h:11-26). */
+int inpc_compute_viewpoint_weights(const inpc_view* view, int64_t n_cells, const float* centers,
+                                   const int32_t* levels, const float* weights, float initial_size,
+                                   float* out, void* stream);
+
+/* Opaque sampler: a counter-based Philox4x32-10 stream keyed by `seed`; each generate_* call consumes
+ * one value of a 64-bit call counter, which is all the state there is.  Replaces
+ * struct ProbabilityFieldSampler and its host-side pcg32 (sampling/include/sampling_api.h:26-82). */
+typedef struct inpc_sampler inpc_sampler;
+inpc_sampler* inpc_sampler_create(int64_t seed);
+void inpc_sampler_destroy(inpc_sampler* s);
+/* Checkpoint / resume of the stream position (the reference's pcg32 state is not checkpointable). */
+uint64_t inpc_sampler_get_counter(const inpc_sampler* s);
+void inpc_sampler_set_counter(inpc_sampler* s, uint64_t counter);
+
+/* Bytes of device scratch the generate_* calls need for `n_cells` leaves (CDF + scan partials). */
+size_t inpc_sampler_workspace_bytes(int64_t n_cells);
+
+/* Visible training samples: positions (n,3) f32, indices (n) i64.  No host synchronisation: when
+ * the weight sum is <= 0 the kernel writes zeros / -1 as the reference does
+ * (sampling/src/sampling.cu:107-111).  Replaces inpc::sampling::create_training_samples
+ * (sampling/include/sampling.h:28-50). */
+int inpc_generate_training_samples(inpc_sampler* s, const inpc_view* view, int64_t n_cells,
+                                   const float* centers, const int32_t* levels, const float* weights,
+                                   float initial_size, int64_t n_samples, float* positions,
+                                   int64_t* indices, void* workspace, void* stream);
+
+/* Unconditional samples.  Reads the weight sum back; *n_written is n_samples, or 0 when the sum is
+ * <= 0 (the reference then returns an empty tensor, sampling/src/sampling_api.cu:154).
+ * Replaces compute_cdf + create_samples (sampling/include/sampling.h:52-66). */
+int inpc_generate_samples(inpc_sampler* s, const inpc_view* view, int64_t n_cells, const float* centers,
+                          const int32_t* levels, const float* weights, float initial_size,
+                          int64_t n_samples, float* positions, int64_t* n_written, void* workspace,
+                          void* stream);
+
+/* Expected-count samples in two steps so the caller can size the output.  _count reads one integer
+ * back: *n_created = sum over visible leaves of max(1, round(w/sum*n_samples)), 0 if sum <= 0.
+ * _fill writes n_created*n_multi positions.  Replaces compute_sample_distribution +
+ * create_expected_samples (sampling/include/sampling.h:68-83). */
+int inpc_generate_expected_samples_count(inpc_sampler* s, const inpc_view* view, int64_t n_cells,
+                                         const float* centers, const int32_t* levels,
+                                         const float* weights, float initial_size, int64_t n_samples,
+                                         int64_t* n_created, void* workspace, void* stream);
+int inpc_generate_expected_samples_fill(inpc_sampler* s, int64_t n_cells, const float* centers,
+                                        const int32_t* levels, float initial_size, int64_t n_created,
+                                        int64_t n_multi, float* positions, void* workspace, void* stream);
+
+/* Leaf look-up alone: out[i] = min(lower_bound(cdf, u[i]), n_cells-1) as int64.
+ * Replaces binary_search (sampling/include/sampling_utils.h:49-69). */
+int inpc_draw_leaves(const float* cdf, int64_t n_cells, const float* u, int64_t n, int64_t* out,
+                     void* stream);
+
+/* Normalised inclusive CDF of `weights` into `cdf` (fp32), and the plain sum into *sum_out (device,
+ * one float).  Replaces the Sum / normalize / InclusiveSum sequence of sampling/src/sampling.cu:97-125. */
+int inpc_build_cdf(const float* weights, int64_t n_cells, float* cdf, float* sum_out, void* workspace,
+                   void* stream);
+
+/* ------------------------------------------------------------------------------------------
+ * Fused misc ops (misc/include/misc.h:7-33)
+ * ---------------------------------------------------------------------------------------- */
+
+/* grads (=|+=) factor(level(index)) * weights for the fixed ten-level hash grid layout; `add` != 0
+ * accumulates.  Replaces compute_/add_normalized_weight_decay_grads (misc/include/misc.h:9-17). */
+int inpc_weight_decay_grads(const float* weights, float* grads, int64_t n, int add, void* stream);
+/* Replaces spherical_contraction (misc/include/misc.h:19-22). */
+int inpc_spherical_contraction(const float* positions, float* out, int64_t n, void* stream);
+/* Mean Cauchy loss into *loss (device, one float), reduction fused; `partials` needs
+ * inpc_cauchy_workspace_bytes(n).  Replaces cauchy_loss + the torch .sum()
+ * (misc/include/misc.h:24-28, misc/src/misc_api.cu:64). */
+size_t inpc_cauchy_workspace_bytes(int64_t n);
+int inpc_cauchy_loss(const float* input, const float* target, int64_t n, float* loss, void* partials,
+                     void* stream);
+/* grad (device, one float) is the upstream scalar.  Replaces cauchy_loss_backward (misc.h:29-33). */
+int inpc_cauchy_loss_backward(const float* grad, const float* input, const float* target, int64_t n,
+                              float* grad_input, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* INPC_B200_H */

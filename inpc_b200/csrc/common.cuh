@@ -1,0 +1,123 @@
+// Shared host/device helpers of the inpc_b200 library (sm_100a only).
+#pragma once
+
+#include <cuda_runtime.h>
+#include <cuda_fp16.h>
+#include <cstdint>
+#include <cstdio>
+#include <cstdarg>
+#include "../../include/inpc_b200.h"
+
+namespace inpc {
+
+// ---- error reporting ---------------------------------------------------------------------
+void set_error(const char* fmt, ...);
+int cuda_fail(cudaError_t e, const char* what);
+
+#define INPC_CUDA_TRY(expr)                                        \
+    do {                                                           \
+        cudaError_t _e = (expr);                                   \
+        if (_e != cudaSuccess) return ::inpc::cuda_fail(_e, #expr); \
+    } while (0)
+
+#define INPC_LAUNCH_CHECK(name)                                       \
+    do {                                                              \
+        cudaError_t _e = cudaGetLastError();                          \
+        if (_e != cudaSuccess) return ::inpc::cuda_fail(_e, name);     \
+    } while (0)
+
+// Device-visible status words in mapped pinned host memory: a kernel stores 1 into its word when a
+// bounded wait runs out (plain store, no atomics over PCIe); the host reads them without a device
+// synchronisation.
+enum : unsigned {
+    STATUS_LOOKBACK_TIMEOUT = 0,   // a radix-sort tile gave up waiting for a predecessor tile
+    STATUS_SAMPLER_EXHAUSTED = 1,  // informational: some sample slots ran out of rejection attempts
+    STATUS_WORDS = 4,
+};
+unsigned* device_status_ptr();            // device pointer to STATUS_WORDS words (allocated on first use)
+unsigned read_and_clear_status(int word);  // host-side read of one word, then reset to 0
+
+// ---- small utilities ---------------------------------------------------------------------
+template <typename T>
+__host__ __device__ constexpr T ceil_div(T a, T b) { return (a + b - 1) / b; }
+
+inline size_t align_up(size_t x, size_t a = 256) { return (x + a - 1) / a * a; }
+
+// Carves consecutive 256-byte-aligned arrays out of one blob.
+struct Carver {
+    char* base;
+    size_t off = 0;
+    explicit Carver(void* p) : base(static_cast<char*>(p)) {}
+    template <typename T>
+    T* take(size_t count) {
+        off = align_up(off);
+        T* p = reinterpret_cast<T*>(base + off);
+        off += sizeof(T) * count;
+        return p;
+    }
+    size_t used() const { return align_up(off); }
+};
+
+inline int bit_length(uint32_t v) {
+    int b = 0;
+    while (v) { ++b; v >>= 1; }
+    return b;
+}
+
+// ---- camera parameters passed by value to kernels -----------------------------------------
+struct ViewParams {
+    const float* w2c;   // device, 16 floats
+    const float* cam;   // device, 3 floats
+    int width, height;
+    float fx, fy, cx, cy, near_plane, far_plane;
+};
+
+inline ViewParams to_params(const inpc_view* v) {
+    ViewParams p;
+    p.w2c = v->w2c; p.cam = v->cam_position;
+    p.width = v->width; p.height = v->height;
+    p.fx = v->fx; p.fy = v->fy; p.cx = v->cx; p.cy = v->cy;
+    p.near_plane = v->near_plane; p.far_plane = v->far_plane;
+    return p;
+}
+
+// ---- radix sort (radix_sort.cu) ------------------------------------------------------------
+size_t sort_workspace_bytes(int64_t n);
+int sort_pairs(uint32_t* keys, uint32_t* keys_alt, uint32_t* values, uint32_t* values_alt, int64_t n,
+               int end_bit, void* workspace, int* result_in_alt, cudaStream_t stream);
+
+// ---- device helpers ------------------------------------------------------------------------
+#ifdef __CUDACC__
+__device__ __forceinline__ unsigned lane_id() { return threadIdx.x & 31u; }
+
+__device__ __forceinline__ unsigned warp_inclusive_scan(unsigned v) {
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        unsigned t = __shfl_up_sync(0xffffffffu, v, o);
+        if (lane_id() >= (unsigned)o) v += t;
+    }
+    return v;
+}
+
+// Block-wide exclusive scan of one unsigned per thread; `smem` needs (blockDim.x/32 + 1) words.
+// Returns the exclusive prefix; *total receives the block sum (same value in every thread).
+__device__ __forceinline__ unsigned block_exclusive_scan(unsigned v, unsigned* smem, unsigned* total) {
+    const unsigned lane = lane_id(), warp = threadIdx.x >> 5, nwarps = (blockDim.x + 31) >> 5;
+    const unsigned inc = warp_inclusive_scan(v);
+    if (lane == 31) smem[warp] = inc;
+    __syncthreads();
+    if (warp == 0) {
+        unsigned w = lane < nwarps ? smem[lane] : 0u;
+        unsigned winc = warp_inclusive_scan(w);
+        if (lane < nwarps) smem[lane] = winc - w;
+        if (lane == 31) smem[nwarps] = winc;
+    }
+    __syncthreads();
+    const unsigned r = smem[warp] + inc - v;
+    *total = smem[nwarps];
+    __syncthreads();
+    return r;
+}
+#endif
+
+}  // namespace inpc

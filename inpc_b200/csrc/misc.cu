@@ -1,0 +1,190 @@
+// Fused element-wise helpers of the inpc_b200 library (hash-grid weight decay, spherical
+// contraction, Cauchy loss).  Pure HBM streams: 16-byte vector accesses where the layout allows and
+// grid-stride loops sized to the SM count.  Citations are paths below
+// INPCCudaBackend/INPCCudaBackend/misc/ of the reference.
+#include "common.cuh"
+
+namespace inpc {
+
+namespace {
+
+constexpr int kThreads = 256;
+
+int grid_for(int64_t work_items) {
+    static int sms = 0;
+    if (!sms) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
+    }
+    const int64_t want = ceil_div<int64_t>(work_items, kThreads);
+    const int64_t cap = (int64_t)sms * 8;
+    return (int)(want < cap ? (want > 0 ? want : 1) : cap);
+}
+
+// Per-level factor 0.2 / len(level) of the fixed ten-level hash grid, zero below index 6144:
+// src/misc_kernels.cu:15-36.
+__device__ __forceinline__ float decay_factor(unsigned idx) {
+    constexpr float f0 = 0.1f * 2.0f / float(210917376 - 177362944);
+    constexpr float f1 = 0.1f * 2.0f / float(177362944 - 143808512);
+    constexpr float f2 = 0.1f * 2.0f / float(143808512 - 110254080);
+    constexpr float f3 = 0.1f * 2.0f / float(110254080 - 76699648);
+    constexpr float f4 = 0.1f * 2.0f / float(76699648 - 43145216);
+    constexpr float f5 = 0.1f * 2.0f / float(43145216 - 9590784);
+    constexpr float f6 = 0.1f * 2.0f / float(9590784 - 1202176);
+    constexpr float f7 = 0.1f * 2.0f / float(1202176 - 153600);
+    constexpr float f8 = 0.1f * 2.0f / float(153600 - 22528);
+    constexpr float f9 = 0.1f * 2.0f / float(22528 - 6144);
+    if (idx >= 177362944u) return f0;
+    if (idx >= 143808512u) return f1;
+    if (idx >= 110254080u) return f2;
+    if (idx >= 76699648u) return f3;
+    if (idx >= 43145216u) return f4;
+    if (idx >= 9590784u) return f5;
+    if (idx >= 1202176u) return f6;
+    if (idx >= 153600u) return f7;
+    if (idx >= 22528u) return f8;
+    if (idx >= 6144u) return f9;
+    return 0.0f;
+}
+
+// Every level boundary is a multiple of 4, so a float4 never straddles two levels.
+template <bool ADD>
+__global__ void __launch_bounds__(kThreads) weight_decay_kernel(const float* __restrict__ w, float* __restrict__ g, int64_t n,
+                                                                bool vec_ok) {
+    const int64_t stride = (int64_t)gridDim.x * kThreads;
+    const int64_t tid = (int64_t)blockIdx.x * kThreads + threadIdx.x;
+    const int64_t n4 = vec_ok ? n / 4 : 0;
+    for (int64_t v = tid; v < n4; v += stride) {
+        const float f = decay_factor((unsigned)(4 * v));
+        const float4 wv = __ldg(reinterpret_cast<const float4*>(w) + v);
+        float4 gv;
+        if (ADD) {
+            gv = reinterpret_cast<float4*>(g)[v];
+            gv.x += f * wv.x; gv.y += f * wv.y; gv.z += f * wv.z; gv.w += f * wv.w;
+        } else {
+            gv = make_float4(f * wv.x, f * wv.y, f * wv.z, f * wv.w);
+        }
+        reinterpret_cast<float4*>(g)[v] = gv;
+    }
+    for (int64_t i = 4 * n4 + tid; i < n; i += stride) {
+        const float f = decay_factor((unsigned)i);
+        if (ADD) g[i] += f * w[i];
+        else g[i] = f * w[i];
+    }
+}
+
+// src/misc_kernels.cu:49-66
+__global__ void __launch_bounds__(kThreads) contraction_kernel(const float* __restrict__ p, float* __restrict__ out, int64_t n) {
+    const int64_t stride = (int64_t)gridDim.x * kThreads;
+    for (int64_t i = (int64_t)blockIdx.x * kThreads + threadIdx.x; i < n; i += stride) {
+        const float x = __ldg(p + 3 * i), y = __ldg(p + 3 * i + 1), z = __ldg(p + 3 * i + 2);
+        const float length_sq = fmaxf(x * x + y * y + z * z, 1.0f);
+        const float scale = (sqrtf(length_sq) * 2.0f - 1.0f) / length_sq * 0.25f;
+        out[3 * i] = __saturatef(scale * x + 0.5f);
+        out[3 * i + 1] = __saturatef(scale * y + 0.5f);
+        out[3 * i + 2] = __saturatef(scale * z + 0.5f);
+    }
+}
+
+// Cauchy loss, src/misc_kernels.cu:68-79, with the mean reduction fused: per-block partial sums in a
+// fixed order, then one block adds the partials in index order.
+__global__ void __launch_bounds__(kThreads) cauchy_partial_kernel(const float* __restrict__ a, const float* __restrict__ b,
+                                                                  int64_t n, float* __restrict__ partial) {
+    __shared__ float s[kThreads / 32];
+    const int64_t stride = (int64_t)gridDim.x * kThreads;
+    const float nf = (float)(unsigned)n;
+    float acc = 0.0f;
+    for (int64_t i = (int64_t)blockIdx.x * kThreads + threadIdx.x; i < n; i += stride) {
+        const float d = __ldg(a + i) - __ldg(b + i);
+        acc += log1pf(d * d * 12.5f) / nf;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) acc += __shfl_down_sync(0xffffffffu, acc, o);
+    if (lane_id() == 0) s[threadIdx.x >> 5] = acc;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float t = 0.0f;
+        for (int w = 0; w < kThreads / 32; ++w) t += s[w];
+        partial[blockIdx.x] = t;
+    }
+}
+
+__global__ void __launch_bounds__(1024) cauchy_final_kernel(const float* __restrict__ partial, int n_partial, float* __restrict__ loss) {
+    __shared__ float s[32];
+    float acc = 0.0f;
+    for (int i = threadIdx.x; i < n_partial; i += 1024) acc += partial[i];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) acc += __shfl_down_sync(0xffffffffu, acc, o);
+    if (lane_id() == 0) s[threadIdx.x >> 5] = acc;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float t = 0.0f;
+        for (int w = 0; w < 32; ++w) t += s[w];
+        *loss = t;
+    }
+}
+
+// src/misc_kernels.cu:81-94
+__global__ void __launch_bounds__(kThreads) cauchy_backward_kernel(const float* __restrict__ grad, const float* __restrict__ a,
+                                                                   const float* __restrict__ b, int64_t n, float* __restrict__ out) {
+    const int64_t stride = (int64_t)gridDim.x * kThreads;
+    const float g = __ldg(grad);
+    const float nf = (float)(unsigned)n;
+    for (int64_t i = (int64_t)blockIdx.x * kThreads + threadIdx.x; i < n; i += stride) {
+        const float d = __ldg(a + i) - __ldg(b + i);
+        const float denominator = nf * (12.5f * d * d + 1.0f);
+        out[i] = 25.0f * d / fmaxf(denominator, 1.0e-12f) * g;
+    }
+}
+
+constexpr int kCauchyMaxBlocks = 148 * 8;
+
+}  // namespace
+
+}  // namespace inpc
+
+using namespace inpc;
+
+extern "C" int inpc_weight_decay_grads(const float* weights, float* grads, int64_t n, int add, void* stream_) {
+    if (n == 0) return INPC_OK;
+    if (n < 0 || n >= ((int64_t)1 << 32) || !weights || !grads) { set_error("inpc_weight_decay_grads: bad argument"); return INPC_E_INVALID; }
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    const bool vec_ok = ((reinterpret_cast<uintptr_t>(weights) | reinterpret_cast<uintptr_t>(grads)) & 15u) == 0;
+    const int grid = grid_for(n / 4 + 1);
+    if (add) weight_decay_kernel<true><<<grid, kThreads, 0, stream>>>(weights, grads, n, vec_ok);
+    else weight_decay_kernel<false><<<grid, kThreads, 0, stream>>>(weights, grads, n, vec_ok);
+    INPC_LAUNCH_CHECK("weight_decay_kernel");
+    return INPC_OK;
+}
+
+extern "C" int inpc_spherical_contraction(const float* positions, float* out, int64_t n, void* stream_) {
+    if (n == 0) return INPC_OK;
+    if (n < 0 || !positions || !out) { set_error("inpc_spherical_contraction: bad argument"); return INPC_E_INVALID; }
+    contraction_kernel<<<grid_for(n), kThreads, 0, static_cast<cudaStream_t>(stream_)>>>(positions, out, n);
+    INPC_LAUNCH_CHECK("contraction_kernel");
+    return INPC_OK;
+}
+
+extern "C" size_t inpc_cauchy_workspace_bytes(int64_t n) { (void)n; return sizeof(float) * kCauchyMaxBlocks; }
+
+extern "C" int inpc_cauchy_loss(const float* input, const float* target, int64_t n, float* loss, void* partials, void* stream_) {
+    if (n <= 0 || n >= ((int64_t)1 << 32) || !input || !target || !loss || !partials) { set_error("inpc_cauchy_loss: bad argument"); return INPC_E_INVALID; }
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    int grid = grid_for(n);
+    if (grid > kCauchyMaxBlocks) grid = kCauchyMaxBlocks;
+    cauchy_partial_kernel<<<grid, kThreads, 0, stream>>>(input, target, n, static_cast<float*>(partials));
+    INPC_LAUNCH_CHECK("cauchy_partial_kernel");
+    cauchy_final_kernel<<<1, 1024, 0, stream>>>(static_cast<const float*>(partials), grid, loss);
+    INPC_LAUNCH_CHECK("cauchy_final_kernel");
+    return INPC_OK;
+}
+
+extern "C" int inpc_cauchy_loss_backward(const float* grad, const float* input, const float* target, int64_t n,
+                                         float* grad_input, void* stream_) {
+    if (n == 0) return INPC_OK;
+    if (n < 0 || n >= ((int64_t)1 << 32) || !grad || !input || !target || !grad_input) { set_error("inpc_cauchy_loss_backward: bad argument"); return INPC_E_INVALID; }
+    cauchy_backward_kernel<<<grid_for(n), kThreads, 0, static_cast<cudaStream_t>(stream_)>>>(grad, input, target, n, grad_input);
+    INPC_LAUNCH_CHECK("cauchy_backward_kernel");
+    return INPC_OK;
+}

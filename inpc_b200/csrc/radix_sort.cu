@@ -1,0 +1,305 @@
+// Onesweep least-significant-digit radix sort of (u32 key, u32 value) pairs for sm_100a.
+//
+// One up-front kernel builds the digit histograms of every pass in a single read of the keys; each
+// pass is then ONE kernel that reads the pairs once and writes them once.  Inside a pass every tile
+// ranks its keys stably (per-warp match-any ranking), publishes its per-digit counts and resolves
+// its global offsets with a decoupled look-back over the tiles before it.  Tiles take their index
+// from a ticket counter, so a tile a later one waits for is always already running; every wait is
+// nevertheless bounded and reports through the status word instead of spinning for ever.
+//
+// Replaces cub::DeviceRadixSort::SortPairs as used in rasterization/src/bilinear/forward.cu:91-98
+// (32-bit depth keys) and :132-139 (tile keys) of the reference.
+#include "common.cuh"
+
+namespace inpc {
+
+namespace {
+
+constexpr int kRadixBits = 8;
+constexpr int kRadix = 1 << kRadixBits;
+constexpr int kMaxPasses = 4;
+constexpr int kThreads = 512;
+constexpr int kItems = 16;
+constexpr int kTile = kThreads * kItems;   // 8192 pairs per tile
+constexpr int kWarps = kThreads / 32;
+
+constexpr unsigned kFlagAggregate = 1u << 30;
+constexpr unsigned kFlagPrefix = 2u << 30;
+constexpr unsigned kFlagMask = 3u << 30;
+constexpr unsigned kValueMask = ~kFlagMask;
+constexpr int kSpinLimit = 1 << 22;
+
+struct PassTable {
+    int n_passes;
+    int shift[kMaxPasses];
+    int bits[kMaxPasses];
+};
+
+// ---- histogram of every pass in one read ---------------------------------------------------
+constexpr int kHistThreads = 512;
+constexpr int kHistItemsPerBlock = kHistThreads * 4 * 8;   // 8 uint4 loads per thread
+
+__global__ void __launch_bounds__(kHistThreads) radix_histogram_kernel(
+    const uint32_t* __restrict__ keys, int64_t n, PassTable pt, unsigned* __restrict__ hist) {
+    __shared__ unsigned s_hist[kMaxPasses][kRadix];
+    for (int i = threadIdx.x; i < kMaxPasses * kRadix; i += kHistThreads) (&s_hist[0][0])[i] = 0;
+    __syncthreads();
+
+    const int64_t block_base = (int64_t)blockIdx.x * kHistItemsPerBlock;
+    const int64_t block_end = min(n, block_base + (int64_t)kHistItemsPerBlock);
+    auto count = [&](uint32_t k) {
+#pragma unroll
+        for (int p = 0; p < kMaxPasses; ++p)
+            if (p < pt.n_passes) atomicAdd(&s_hist[p][(k >> pt.shift[p]) & ((1u << pt.bits[p]) - 1u)], 1u);
+    };
+    // keys is 16-byte aligned (carved at 256 bytes) and block_base is a multiple of 4
+    const uint4* keys4 = reinterpret_cast<const uint4*>(keys + block_base);
+    const int64_t n_vec = (block_end - block_base) / 4;
+    for (int64_t v = threadIdx.x; v < n_vec; v += kHistThreads) {
+        const uint4 k = __ldg(keys4 + v);
+        count(k.x); count(k.y); count(k.z); count(k.w);
+    }
+    for (int64_t i = block_base + n_vec * 4 + threadIdx.x; i < block_end; i += kHistThreads) count(keys[i]);
+    __syncthreads();
+    for (int i = threadIdx.x; i < kMaxPasses * kRadix; i += kHistThreads) {
+        const unsigned c = (&s_hist[0][0])[i];
+        if (c) atomicAdd(hist + i, c);
+    }
+}
+
+// exclusive scan of each pass's 256 counters -> global digit bases
+__global__ void __launch_bounds__(kRadix) radix_scan_histogram_kernel(const unsigned* __restrict__ hist,
+                                                                      unsigned* __restrict__ base) {
+    __shared__ unsigned s_scan[kRadix / 32 + 1];
+    const int p = blockIdx.x;
+    const unsigned c = hist[p * kRadix + threadIdx.x];
+    unsigned total;
+    const unsigned ex = block_exclusive_scan(c, s_scan, &total);
+    base[p * kRadix + threadIdx.x] = ex;
+}
+
+// ---- one pass ---------------------------------------------------------------------------------
+struct PassSmem {
+    union {
+        unsigned warp_hist[kWarps][kRadix];   // ranking phase
+        uint32_t keys[kTile];                 // reorder phase (keys), 32 KB — warp_hist is 16 KB
+    };
+    uint32_t values[kTile];
+    unsigned bin_start[kRadix];    // tile-local exclusive start of each digit
+    unsigned global_off[kRadix];   // global position of a digit's first key minus bin_start
+    unsigned scan[kWarps + 1];
+    unsigned tile_id;
+};
+
+__global__ void __launch_bounds__(kThreads) radix_onesweep_pass_kernel(
+    const uint32_t* __restrict__ keys_in, const uint32_t* __restrict__ vals_in,
+    uint32_t* __restrict__ keys_out, uint32_t* __restrict__ vals_out, int64_t n, int shift, int bits,
+    const unsigned* __restrict__ digit_base, volatile unsigned* tile_state, unsigned* ticket,
+    volatile unsigned* status) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    PassSmem& s = *reinterpret_cast<PassSmem*>(smem_raw);
+
+    const unsigned tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
+    const unsigned digit_mask = (1u << bits) - 1u;
+
+    if (tid == 0) s.tile_id = atomicAdd(ticket, 1u);
+    for (int i = tid; i < kWarps * kRadix; i += kThreads) (&s.warp_hist[0][0])[i] = 0;
+    __syncthreads();
+    const unsigned tile = s.tile_id;
+    const int64_t tile_base = (int64_t)tile * kTile;
+    const int valid = (int)min((int64_t)kTile, n - tile_base);
+
+    // warp-striped load: warp w owns [w*32*kItems, (w+1)*32*kItems) of the tile, item i of lane l
+    // is element i*32+l of that segment, so (warp, item, lane) order is the input order.
+    uint32_t key[kItems];
+    unsigned rank[kItems];
+    const int seg = warp * 32 * kItems;
+#pragma unroll
+    for (int i = 0; i < kItems; ++i) {
+        const int local = seg + i * 32 + lane;
+        key[i] = local < valid ? __ldg(keys_in + tile_base + local) : 0xFFFFFFFFu;
+    }
+
+    // stable rank within the warp's segment, per digit
+#pragma unroll
+    for (int i = 0; i < kItems; ++i) {
+        const unsigned d = (key[i] >> shift) & digit_mask;
+        const unsigned peers = __match_any_sync(0xffffffffu, d);
+        const int leader = __ffs(peers) - 1;
+        unsigned base = 0;
+        if ((int)lane == leader) {
+            base = s.warp_hist[warp][d];
+            s.warp_hist[warp][d] = base + __popc(peers);
+        }
+        base = __shfl_sync(0xffffffffu, base, leader);
+        rank[i] = base + __popc(peers & ((1u << lane) - 1u));
+        __syncwarp();
+    }
+    __syncthreads();
+
+    // per digit: exclusive scan over warps, tile total
+    unsigned total = 0;
+    if (tid < kRadix) {
+#pragma unroll
+        for (int w = 0; w < kWarps; ++w) {
+            const unsigned c = s.warp_hist[w][tid];
+            s.warp_hist[w][tid] = total;
+            total += c;
+        }
+        // publish this tile's digit count before any waiting
+        tile_state[(size_t)tile * kRadix + tid] = total | (tile == 0 ? kFlagPrefix : kFlagAggregate);
+    }
+    unsigned block_total;
+    const unsigned start = block_exclusive_scan(tid < kRadix ? total : 0u, s.scan, &block_total);
+    if (tid < kRadix) {
+        s.bin_start[tid] = start;
+        // decoupled look-back
+        unsigned exclusive = 0;
+        if (tile > 0) {
+            int64_t j = (int64_t)tile - 1;
+            bool gave_up = false;
+            while (j >= 0) {
+                unsigned v = 0;
+                int spins = 0;
+                do {
+                    v = tile_state[(size_t)j * kRadix + tid];
+                    if ((v & kFlagMask) != 0u) break;
+                    __nanosleep(20);
+                } while (++spins < kSpinLimit);
+                if ((v & kFlagMask) == 0u) { gave_up = true; break; }
+                exclusive += v & kValueMask;
+                if (v & kFlagPrefix) break;
+                --j;
+            }
+            if (gave_up) status[STATUS_LOOKBACK_TIMEOUT] = 1u;
+            tile_state[(size_t)tile * kRadix + tid] = ((exclusive + total) & kValueMask) | kFlagPrefix;
+        }
+        s.global_off[tid] = digit_base[tid] + exclusive - start;
+    }
+    __syncthreads();
+
+    // tile-local position of every key; values follow the same permutation
+    unsigned pos[kItems];
+#pragma unroll
+    for (int i = 0; i < kItems; ++i) {
+        const unsigned d = (key[i] >> shift) & digit_mask;
+        pos[i] = s.bin_start[d] + s.warp_hist[warp][d] + rank[i];
+    }
+    uint32_t val[kItems];
+#pragma unroll
+    for (int i = 0; i < kItems; ++i) {
+        const int local = seg + i * 32 + lane;
+        val[i] = local < valid ? __ldg(vals_in + tile_base + local) : 0u;
+    }
+    __syncthreads();   // warp_hist is dead from here on: its storage becomes the key staging area
+#pragma unroll
+    for (int i = 0; i < kItems; ++i) {
+        s.keys[pos[i]] = key[i];
+        s.values[pos[i]] = val[i];
+    }
+    __syncthreads();
+
+    // coalesced write-out: consecutive staged slots of one digit go to consecutive addresses.
+    // Padding keys (0xFFFFFFFF) rank behind every real key of the last tile, i.e. at slots >= valid.
+    for (int q = tid; q < valid; q += kThreads) {
+        const uint32_t k = s.keys[q];
+        const unsigned d = (k >> shift) & digit_mask;
+        const unsigned dst = s.global_off[d] + (unsigned)q;
+        keys_out[dst] = k;
+        vals_out[dst] = s.values[q];
+    }
+}
+
+struct SortWorkspace {
+    unsigned* hist;     // [kMaxPasses][kRadix]
+    unsigned* ticket;   // [kMaxPasses]
+    unsigned* base;     // [kMaxPasses][kRadix]
+    unsigned* state;    // [kMaxPasses][tiles][kRadix]
+    size_t zero_bytes;  // leading bytes that must be cleared per sort (hist + ticket)
+    size_t state_bytes;
+    size_t total;
+};
+
+SortWorkspace carve_sort_workspace(void* ws, int64_t n) {
+    SortWorkspace w;
+    const int64_t tiles = n > 0 ? ceil_div<int64_t>(n, kTile) : 1;
+    Carver c(ws);
+    w.hist = c.take<unsigned>(kMaxPasses * kRadix);
+    w.ticket = c.take<unsigned>(64);
+    w.zero_bytes = c.used();
+    w.state = c.take<unsigned>((size_t)kMaxPasses * tiles * kRadix);
+    w.state_bytes = c.used() - w.zero_bytes;
+    w.base = c.take<unsigned>(kMaxPasses * kRadix);
+    w.total = c.used();
+    return w;
+}
+
+}  // namespace
+
+size_t sort_workspace_bytes(int64_t n) { return carve_sort_workspace(nullptr, n).total; }
+
+int sort_pairs(uint32_t* keys, uint32_t* keys_alt, uint32_t* values, uint32_t* values_alt, int64_t n,
+               int end_bit, void* workspace, int* result_in_alt, cudaStream_t stream) {
+    if (result_in_alt) *result_in_alt = 0;
+    if (n < 0 || n >= (int64_t)1 << 30) { set_error("sort_pairs: n=%lld out of range [0, 2^30)", (long long)n); return INPC_E_INVALID; }
+    if (end_bit < 0 || end_bit > 32) { set_error("sort_pairs: end_bit=%d out of range", end_bit); return INPC_E_INVALID; }
+    if (n <= 1 || end_bit == 0) return INPC_OK;
+    if (!keys || !keys_alt || !values || !values_alt || !workspace) { set_error("sort_pairs: null pointer"); return INPC_E_INVALID; }
+    if ((reinterpret_cast<uintptr_t>(keys) | reinterpret_cast<uintptr_t>(keys_alt)) & 15u) {
+        set_error("sort_pairs: key buffers must be 16-byte aligned");
+        return INPC_E_INVALID;
+    }
+
+    PassTable pt;
+    pt.n_passes = ceil_div(end_bit, kRadixBits);
+    int bit = 0;
+    for (int p = 0; p < kMaxPasses; ++p) { pt.shift[p] = 0; pt.bits[p] = 0; }
+    for (int p = 0; p < pt.n_passes; ++p) {
+        // spread the bits evenly over the passes (e.g. 12 bits -> 6 + 6): fewer digits per pass
+        // means longer, better-coalesced output runs
+        const int b = (end_bit - bit + (pt.n_passes - p) - 1) / (pt.n_passes - p);
+        pt.shift[p] = bit;
+        pt.bits[p] = b;
+        bit += b;
+    }
+
+    SortWorkspace w = carve_sort_workspace(workspace, n);
+    const int64_t tiles = ceil_div<int64_t>(n, kTile);
+    // hist, tickets and the look-back state are contiguous at the front of the workspace
+    INPC_CUDA_TRY(cudaMemsetAsync(workspace, 0, w.zero_bytes + (size_t)pt.n_passes * tiles * kRadix * sizeof(unsigned), stream));
+
+    const int hist_blocks = (int)ceil_div<int64_t>(n, kHistItemsPerBlock);
+    radix_histogram_kernel<<<hist_blocks, kHistThreads, 0, stream>>>(keys, n, pt, w.hist);
+    INPC_LAUNCH_CHECK("radix_histogram_kernel");
+    radix_scan_histogram_kernel<<<pt.n_passes, kRadix, 0, stream>>>(w.hist, w.base);
+    INPC_LAUNCH_CHECK("radix_scan_histogram_kernel");
+
+    static bool attr_set = false;
+    if (!attr_set) {
+        INPC_CUDA_TRY(cudaFuncSetAttribute(radix_onesweep_pass_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(PassSmem)));
+        attr_set = true;
+    }
+    unsigned* status = device_status_ptr();
+    if (!status) return INPC_E_CUDA;
+    uint32_t *kin = keys, *kout = keys_alt, *vin = values, *vout = values_alt;
+    for (int p = 0; p < pt.n_passes; ++p) {
+        radix_onesweep_pass_kernel<<<(unsigned)tiles, kThreads, sizeof(PassSmem), stream>>>(
+            kin, vin, kout, vout, n, pt.shift[p], pt.bits[p], w.base + p * kRadix,
+            w.state + (size_t)p * tiles * kRadix, w.ticket + p, status);
+        INPC_LAUNCH_CHECK("radix_onesweep_pass_kernel");
+        uint32_t* t = kin; kin = kout; kout = t;
+        t = vin; vin = vout; vout = t;
+    }
+    if (result_in_alt) *result_in_alt = pt.n_passes & 1;
+    return INPC_OK;
+}
+
+}  // namespace inpc
+
+extern "C" size_t inpc_sort_workspace_bytes(int64_t n) { return inpc::sort_workspace_bytes(n < 0 ? 0 : n); }
+
+extern "C" int inpc_sort_pairs(uint32_t* keys, uint32_t* keys_alt, uint32_t* values, uint32_t* values_alt,
+                               int64_t n, int end_bit, void* workspace, int* result_in_alt, void* stream) {
+    return inpc::sort_pairs(keys, keys_alt, values, values_alt, n, end_bit, workspace, result_in_alt,
+                            static_cast<cudaStream_t>(stream));
+}

@@ -1,0 +1,1149 @@
+// Rasterizer of the inpc_b200 library: cull/project/SH-evaluate -> order by (tile, depth) ->
+// front-to-back blend, forward, backward and inference, bilinear and gaussian splats.
+//
+// Data layout in HBM (all carved from two caller-allocated blobs):
+//   per point   : PointRec 32 B {screen x, screen y, opacity, depth | 4 view-space feature channels}
+//                 (one 32-byte sector per gather in the blend), tile bounds 8 B, conic 16 B (gaussian)
+//   per visible : depth key + point id, ping-pong pair for the depth sort
+//   per instance: tile key + point id, ping-pong pair for the tile sort
+//   per tile    : [first, last+1) instance range
+//
+// The arithmetic follows the reference kernels expression by expression (cited per function, paths
+// below INPCCudaBackend/INPCCudaBackend/rasterization/ of the reference); the organisation of the
+// work does not: compaction is a deterministic two-pass scan instead of atomics, the sorts are the
+// library's own onesweep, and the bilinear blend walks per-pixel bit masks of the staged batch
+// instead of testing every staged point against every pixel.
+#include "common.cuh"
+
+namespace inpc {
+
+namespace {
+
+constexpr float kTransmittanceEps = 1e-4f;      // include/bilinear/config.h:16
+constexpr float kOneMinusAlphaEps = 1e-8f;      // include/bilinear/config.h:17
+constexpr float kDilation = 0.16f;              // include/gaussian/config.h:19
+constexpr float kTrainGaussThreshold = 0.01110899653f;   // src/gaussian/kernels.cu:452
+
+enum { VAR_TRAIN = 0, VAR_RAW37 = 1, VAR_PREEXTRACTED = 2 };
+
+struct __align__(16) PointRec {
+    float sx, sy, opacity, depth;
+    float f[4];
+};
+
+struct RasterParams {
+    ViewParams v;
+    int tile;       // tile edge in pixels
+    int gw, gh;     // tile grid
+    float sigma_world, sigma_cutoff;
+    const float* scales;   // optional per-point sigma (gaussian, pre-extracted)
+};
+
+struct Projection {
+    bool visible;
+    float depth, sx, sy;
+    unsigned x0, x1, y0, y1;
+    float cx, cy, cz;   // conic
+};
+
+struct W2C {
+    float r0[4], r1[4], r2[4];
+};
+
+__device__ __forceinline__ W2C load_w2c(const float* __restrict__ w2c) {
+    W2C m;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) { m.r0[k] = __ldg(w2c + k); m.r1[k] = __ldg(w2c + 4 + k); m.r2[k] = __ldg(w2c + 8 + k); }
+    return m;
+}
+
+// src/bilinear/kernels.cu:41-65 and src/gaussian/kernels.cu:41-90 (training), :145-186 (inference),
+// :243-292 (pre-extracted): depth cull, perspective divide, pixel coordinates, tile bounds.
+template <int MODE, int VARIANT>
+__device__ __forceinline__ Projection project_point(const float px, const float py, const float pz, const W2C& m,
+                                                    const RasterParams& rp, const int64_t i) {
+    Projection o;
+    o.visible = false;
+    o.x0 = o.x1 = o.y0 = o.y1 = 0;
+    o.cx = o.cy = o.cz = 0.0f;
+    const float depth = m.r2[0] * px + m.r2[1] * py + m.r2[2] * pz + m.r2[3];
+    o.depth = depth;
+    o.sx = o.sy = 0.0f;
+    if (depth < rp.v.near_plane || depth > rp.v.far_plane) return o;
+    const float x = (m.r0[0] * px + m.r0[1] * py + m.r0[2] * pz + m.r0[3]) / depth;
+    const float y = (m.r1[0] * px + m.r1[1] * py + m.r1[2] * pz + m.r1[3]) / depth;
+    const float sx = x * rp.v.fx + rp.v.cx;
+    const float sy = y * rp.v.fy + rp.v.cy;
+    float ex = 0.5f, ey = 0.5f;
+    if (MODE == INPC_MODE_GAUSSIAN) {
+        float variance_world;
+        float k = 3.0f;
+        if (VARIANT == VAR_TRAIN) {
+            constexpr float numerator = 0.3f * 0.3f * 0.5f * 0.5f;
+            variance_world = numerator / (rp.v.fx * rp.v.fy);
+        } else {
+            k = rp.sigma_cutoff;
+            if (VARIANT == VAR_PREEXTRACTED && rp.scales != nullptr) {
+                const float s = __ldg(rp.scales + i);
+                variance_world = s * s;
+            } else {
+                variance_world = rp.sigma_world * rp.sigma_world;
+            }
+        }
+        const float fx = rp.v.fx, fy = rp.v.fy, cx = rp.v.cx, cy = rp.v.cy;
+        const float J_00 = fx / depth;
+        const float J_02 = -J_00 * fminf(fmaxf(x, -1.3f * cx / fx), 1.3f * cx / fx);
+        const float J_11 = fy / depth;
+        const float J_12 = -J_11 * fminf(fmaxf(y, -1.3f * cy / fy), 1.3f * cy / fy);
+        float cov_x = variance_world * (J_00 * J_00 + J_02 * J_02);
+        const float cov_y = variance_world * (J_02 * J_12);
+        float cov_z = variance_world * (J_11 * J_11 + J_12 * J_12);
+        cov_x += kDilation;
+        cov_z += kDilation;
+        const float det = cov_x * cov_z - cov_y * cov_y;
+        if (det == 0.0f) return o;
+        const float det_rcp = 1.0f / det;
+        o.cx = cov_z * det_rcp;
+        o.cy = -cov_y * det_rcp;
+        o.cz = cov_x * det_rcp;
+        ex = k * sqrtf(cov_x) - 0.5f;
+        ey = k * sqrtf(cov_z) - 0.5f;
+    }
+    const float tf = (float)rp.tile;
+    const unsigned gw = (unsigned)rp.gw, gh = (unsigned)rp.gh;
+    o.x0 = min(gw, (unsigned)max(0, __float2int_rd((sx - ex) / tf)));
+    o.x1 = min(gw, (unsigned)max(0, __float2int_ru((sx + ex) / tf)));
+    o.y0 = min(gh, (unsigned)max(0, __float2int_rd((sy - ey) / tf)));
+    o.y1 = min(gh, (unsigned)max(0, __float2int_ru((sy + ey) / tf)));
+    o.sx = sx;
+    o.sy = sy;
+    o.visible = (o.x1 - o.x0) * (o.y1 - o.y0) != 0u;
+    return o;
+}
+
+constexpr int kPreThreads = 256;
+
+// Pass 1 of the deterministic compaction: per block, how many points survive culling and how many
+// (point, tile) instances they create.
+template <int MODE, int VARIANT>
+__global__ void __launch_bounds__(kPreThreads) visibility_count_kernel(
+    const float* __restrict__ positions, int64_t n, RasterParams rp, unsigned* __restrict__ block_visible,
+    unsigned long long* __restrict__ block_instances) {
+    __shared__ unsigned s_v[kPreThreads / 32];
+    __shared__ unsigned long long s_i[kPreThreads / 32];
+    const W2C m = load_w2c(rp.v.w2c);
+    const int64_t i = (int64_t)blockIdx.x * kPreThreads + threadIdx.x;
+    unsigned vis = 0, cnt = 0;
+    if (i < n) {
+        const Projection pr = project_point<MODE, VARIANT>(__ldg(positions + 3 * i), __ldg(positions + 3 * i + 1),
+                                                           __ldg(positions + 3 * i + 2), m, rp, i);
+        if (pr.visible) { vis = 1; cnt = (pr.x1 - pr.x0) * (pr.y1 - pr.y0); }
+    }
+    unsigned v = vis;
+    unsigned long long c = cnt;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        v += __shfl_down_sync(0xffffffffu, v, o);
+        c += __shfl_down_sync(0xffffffffu, c, o);
+    }
+    if (lane_id() == 0) { s_v[threadIdx.x >> 5] = v; s_i[threadIdx.x >> 5] = c; }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        unsigned tv = 0;
+        unsigned long long ti = 0;
+#pragma unroll
+        for (int w = 0; w < kPreThreads / 32; ++w) { tv += s_v[w]; ti += s_i[w]; }
+        block_visible[blockIdx.x] = tv;
+        block_instances[blockIdx.x] = ti;
+    }
+}
+
+// Exclusive scan of per-block counts by one block; totals land in counters[0] (visible, u64) and
+// counters[1] (instances, u64).
+constexpr int kScanThreads = 1024;
+__global__ void __launch_bounds__(kScanThreads) scan_block_counts_kernel(unsigned* __restrict__ block_visible,
+                                                                         const unsigned long long* __restrict__ block_instances,
+                                                                         int64_t n_blocks,
+                                                                         unsigned long long* __restrict__ counters) {
+    __shared__ unsigned s_scan[kScanThreads / 32 + 1];
+    __shared__ unsigned long long s_inst[kScanThreads / 32];
+    unsigned running = 0;
+    unsigned long long inst = 0;
+    for (int64_t base = 0; base < n_blocks; base += kScanThreads) {
+        const int64_t j = base + threadIdx.x;
+        const unsigned c = j < n_blocks ? block_visible[j] : 0u;
+        if (j < n_blocks) inst += block_instances[j];
+        unsigned total;
+        const unsigned ex = block_exclusive_scan(c, s_scan, &total);
+        if (j < n_blocks) block_visible[j] = running + ex;
+        running += total;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) inst += __shfl_down_sync(0xffffffffu, inst, o);
+    if (lane_id() == 0) s_inst[threadIdx.x >> 5] = inst;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        unsigned long long t = 0;
+        for (int w = 0; w < kScanThreads / 32; ++w) t += s_inst[w];
+        counters[0] = running;
+        counters[1] = t;
+    }
+}
+
+// SH degree 2 along the view ray -> 4 channels: include/sh_utils.cuh:6-23.  `h` points at 36 halves
+// (coefficient-major, channel-minor) in shared memory.
+__device__ __forceinline__ void sh_basis(const float px, const float py, const float pz, const float* __restrict__ cam,
+                                         float* b) {
+    const float vx = px - __ldg(cam), vy = py - __ldg(cam + 1), vz = pz - __ldg(cam + 2);
+    const float inv = rsqrtf(vx * vx + vy * vy + vz * vz);
+    const float x = vx * inv, y = vy * inv, z = vz * inv;
+    const float xx = x * x, yy = y * y, zz = z * z;
+    const float xy = x * y, yz = y * z, xz = x * z;
+    b[0] = 0.28209479177387814f;
+    b[1] = 0.48860251190291987f * y;
+    b[2] = 0.48860251190291987f * z;
+    b[3] = 0.48860251190291987f * x;
+    b[4] = 1.0925484305920792f * xy;
+    b[5] = 1.0925484305920792f * yz;
+    b[6] = 0.94617469575755997f * zz - 0.31539156525251999f;
+    b[7] = 1.0925484305920792f * xz;
+    b[8] = 0.54627421529603959f * xx - 0.54627421529603959f * yy;
+}
+
+__device__ __forceinline__ float sh_eval_channel(const float* b, const __half* h, int c) {
+    return b[0] * __half2float(h[c]) - b[1] * __half2float(h[4 + c]) + b[2] * __half2float(h[8 + c]) -
+           b[3] * __half2float(h[12 + c]) + b[4] * __half2float(h[16 + c]) - b[5] * __half2float(h[20 + c]) +
+           b[6] * __half2float(h[24 + c]) - b[7] * __half2float(h[28 + c]) + b[8] * __half2float(h[32 + c]);
+}
+
+// Pass 2: project again (same arithmetic, same outcome), evaluate SH, write the point record and
+// bounds, and append (depth key, point id) at the slot given by the block offset plus the rank of
+// the point among the block's survivors — index order, hence reproducible.
+// src/bilinear/kernels.cu:11-84, :106-184; src/gaussian/kernels.cu:11-111, :113-217, :219-324.
+template <int MODE, int VARIANT>
+__global__ void __launch_bounds__(kPreThreads) preprocess_kernel(
+    const float* __restrict__ positions, const __half* __restrict__ features, const float* __restrict__ opacities,
+    int64_t n, RasterParams rp, const unsigned* __restrict__ block_offset, PointRec* __restrict__ rec,
+    uint2* __restrict__ bounds, float4* __restrict__ conic, uint32_t* __restrict__ depth_keys,
+    uint32_t* __restrict__ point_ids) {
+    constexpr int kHalves = VARIANT == VAR_RAW37 ? 37 : 36;
+    constexpr int kSlabBytes = kPreThreads * kHalves * 2;   // multiple of 16 for both layouts
+    __shared__ __align__(16) unsigned char s_feat[kSlabBytes];
+    __shared__ unsigned s_scan[kPreThreads / 32 + 1];
+
+    const int64_t block_first = (int64_t)blockIdx.x * kPreThreads;
+    const int in_block = (int)min((int64_t)kPreThreads, n - block_first);
+    {
+        // coalesced 16-byte staging of the block's contiguous feature slab
+        const unsigned char* src = reinterpret_cast<const unsigned char*>(features) + block_first * (kHalves * 2);
+        const int bytes = in_block * kHalves * 2;
+        const int n16 = bytes / 16;
+        const uint4* src16 = reinterpret_cast<const uint4*>(src);
+        uint4* dst16 = reinterpret_cast<uint4*>(s_feat);
+        for (int k = threadIdx.x; k < n16; k += kPreThreads) dst16[k] = __ldg(src16 + k);
+        for (int k = n16 * 16 + 2 * threadIdx.x; k < bytes; k += 2 * kPreThreads)
+            *reinterpret_cast<unsigned short*>(s_feat + k) = __ldg(reinterpret_cast<const unsigned short*>(src + k));
+    }
+    const W2C m = load_w2c(rp.v.w2c);
+    const int64_t i = block_first + threadIdx.x;
+    Projection pr;
+    pr.visible = false;
+    float px = 0, py = 0, pz = 0;
+    if (i < n) {
+        px = __ldg(positions + 3 * i); py = __ldg(positions + 3 * i + 1); pz = __ldg(positions + 3 * i + 2);
+        pr = project_point<MODE, VARIANT>(px, py, pz, m, rp, i);
+    }
+    __syncthreads();
+    if (i < n) {
+        if (pr.visible) {
+            const __half* h = reinterpret_cast<const __half*>(s_feat) + threadIdx.x * kHalves;
+            float b[9];
+            sh_basis(px, py, pz, rp.v.cam, b);
+            PointRec r;
+            r.sx = pr.sx; r.sy = pr.sy; r.depth = pr.depth;
+            if (VARIANT == VAR_RAW37) {
+                // opacity = 1 - exp(-exp(raw)) with the fast exponential: src/bilinear/kernels.cu:144
+                r.opacity = 1.0f - __expf(-__expf(__half2float(h[0])));
+                h += 1;
+            } else {
+                r.opacity = __ldg(opacities + i);
+            }
+#pragma unroll
+            for (int c = 0; c < 4; ++c) r.f[c] = sh_eval_channel(b, h, c);
+            float4* dst = reinterpret_cast<float4*>(rec + i);
+            dst[0] = make_float4(r.sx, r.sy, r.opacity, r.depth);
+            dst[1] = make_float4(r.f[0], r.f[1], r.f[2], r.f[3]);
+            bounds[i] = make_uint2(pr.x0 | (pr.x1 << 16), pr.y0 | (pr.y1 << 16));
+            if (MODE == INPC_MODE_GAUSSIAN) conic[i] = make_float4(pr.cx, pr.cy, pr.cz, 0.0f);
+        } else {
+            bounds[i] = make_uint2(0u, 0u);
+        }
+    }
+    unsigned total;
+    const unsigned rank = block_exclusive_scan(pr.visible ? 1u : 0u, s_scan, &total);
+    if (pr.visible) {
+        const unsigned slot = block_offset[blockIdx.x] + rank;
+        depth_keys[slot] = __float_as_uint(pr.depth);
+        point_ids[slot] = (uint32_t)i;
+    }
+}
+
+__device__ __forceinline__ unsigned tiles_of(const uint2 b) {
+    return ((b.x >> 16) - (b.x & 0xffffu)) * ((b.y >> 16) - (b.y & 0xffffu));
+}
+
+// Instances per depth-sorted point, reduced per block (src/bilinear/kernels.cu:186-196 + the
+// cub::DeviceScan::ExclusiveSum of src/bilinear/forward.cu:109-115, first half).
+constexpr int kInstThreads = 256;
+__global__ void __launch_bounds__(kInstThreads) instance_count_kernel(const uint32_t* __restrict__ sorted_ids,
+                                                                      const uint2* __restrict__ bounds, int64_t n_visible,
+                                                                      unsigned* __restrict__ block_sums) {
+    __shared__ unsigned s_w[kInstThreads / 32];
+    const int64_t s = (int64_t)blockIdx.x * kInstThreads + threadIdx.x;
+    unsigned c = 0;
+    if (s < n_visible) c = tiles_of(__ldg(bounds + __ldg(sorted_ids + s)));
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) c += __shfl_down_sync(0xffffffffu, c, o);
+    if (lane_id() == 0) s_w[threadIdx.x >> 5] = c;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        unsigned t = 0;
+#pragma unroll
+        for (int w = 0; w < kInstThreads / 32; ++w) t += s_w[w];
+        block_sums[blockIdx.x] = t;
+    }
+}
+
+__global__ void __launch_bounds__(kScanThreads) scan_u32_kernel(unsigned* __restrict__ data, int64_t n) {
+    __shared__ unsigned s_scan[kScanThreads / 32 + 1];
+    unsigned running = 0;
+    for (int64_t base = 0; base < n; base += kScanThreads) {
+        const int64_t j = base + threadIdx.x;
+        const unsigned c = j < n ? data[j] : 0u;
+        unsigned total;
+        const unsigned ex = block_exclusive_scan(c, s_scan, &total);
+        if (j < n) data[j] = running + ex;
+        running += total;
+    }
+}
+
+// One (tile key, point id) pair per touched tile, row-major over the point's bounds, points in depth
+// order (src/bilinear/kernels.cu:198-220).
+__global__ void __launch_bounds__(kInstThreads) emit_instances_kernel(const uint32_t* __restrict__ sorted_ids,
+                                                                      const uint2* __restrict__ bounds, int64_t n_visible,
+                                                                      const unsigned* __restrict__ block_base, int gw,
+                                                                      uint32_t* __restrict__ inst_keys,
+                                                                      uint32_t* __restrict__ inst_ids) {
+    __shared__ unsigned s_scan[kInstThreads / 32 + 1];
+    const int64_t s = (int64_t)blockIdx.x * kInstThreads + threadIdx.x;
+    uint32_t id = 0;
+    uint2 b = make_uint2(0u, 0u);
+    if (s < n_visible) { id = __ldg(sorted_ids + s); b = __ldg(bounds + id); }
+    const unsigned c = tiles_of(b);
+    unsigned total;
+    unsigned off = block_base[blockIdx.x] + block_exclusive_scan(c, s_scan, &total);
+    const unsigned x0 = b.x & 0xffffu, x1 = b.x >> 16, y0 = b.y & 0xffffu, y1 = b.y >> 16;
+    for (unsigned ty = y0; ty < y1; ++ty)
+        for (unsigned tx = x0; tx < x1; ++tx) {
+            inst_keys[off] = ty * (unsigned)gw + tx;
+            inst_ids[off] = id;
+            ++off;
+        }
+}
+
+// Run boundaries of the sorted tile keys -> [first, last+1) per tile (src/bilinear/kernels.cu:222-239).
+__global__ void __launch_bounds__(256) tile_ranges_kernel(const uint32_t* __restrict__ keys, int64_t n_instances,
+                                                          uint2* __restrict__ ranges) {
+    const int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x;
+    if (i >= n_instances) return;
+    const uint32_t k = __ldg(keys + i);
+    if (i == 0) ranges[k].x = 0u;
+    else {
+        const uint32_t kp = __ldg(keys + i - 1);
+        if (kp != k) { ranges[kp].y = (unsigned)i; ranges[k].x = (unsigned)i; }
+    }
+    if (i == n_instances - 1) ranges[k].y = (unsigned)n_instances;
+}
+
+// ------------------------------------------------------------------------------------------------
+// Bilinear blend.  A point touches the 2x2 pixels whose centres lie within distance < 1 of it, so a
+// tile stages T*T instances at a time, every instance thread sets its bit in the masks of the (up
+// to four) pixels it reaches, and every pixel thread then walks only its own set bits, in staged
+// (= depth) order.  Per-fragment results that belong to the point (blending weight, gradients) go
+// to a private smem slot per (instance, quad corner) and are reduced by the instance thread in a
+// fixed order: no shared-memory atomics, one global vector atomic per instance.
+// Arithmetic per fragment: src/bilinear/kernels.cu:283-303 (forward), :361-415 (backward),
+// :462-475 (inference).
+// ------------------------------------------------------------------------------------------------
+enum { BLEND_TRAIN = 0, BLEND_INFER = 1 };
+
+template <int T, int KIND>
+__global__ void __launch_bounds__(T * T) blend_bilinear_forward_kernel(
+    const uint2* __restrict__ ranges, const uint32_t* __restrict__ inst_ids, const PointRec* __restrict__ rec,
+    float* __restrict__ image, float* __restrict__ depth_image, float* __restrict__ alpha_image,
+    float* __restrict__ blending_weights, int width, int height, int gw) {
+    constexpr int B = T * T;
+    constexpr int WORDS = B / 32;
+    __shared__ float4 s_a[B];
+    __shared__ float4 s_f[B];
+    __shared__ unsigned s_mask[WORDS][B];
+    __shared__ float s_slot[KIND == BLEND_TRAIN ? 4 : 1][B];
+
+    const int t = threadIdx.x;
+    const int tile = blockIdx.x;
+    const int tx = tile % gw, ty = tile / gw;
+    const int lx = t % T, ly = t / T;
+    const int px = tx * T + lx, py = ty * T + ly;
+    const bool inside = px < width && py < height;
+    const float pcx = (float)px + 0.5f, pcy = (float)py + 0.5f;
+
+    float C0 = 0.0f, C1 = 0.0f, C2 = 0.0f, C3 = 0.0f, Z = 0.0f;
+    float Tr = 1.0f;
+    bool done = !inside;
+
+    const uint2 range = __ldg(ranges + tile);
+    for (unsigned base = range.x; base < range.y; base += B) {
+        if (__syncthreads_count(done) == B) break;
+#pragma unroll
+        for (int w = 0; w < WORDS; ++w) s_mask[w][t] = 0u;
+        if (KIND == BLEND_TRAIN) {
+#pragma unroll
+            for (int q = 0; q < 4; ++q) s_slot[q][t] = 0.0f;
+        }
+        __syncthreads();
+        const int cnt = (int)min((unsigned)B, range.y - base);
+        uint32_t id = 0;
+        if (t < cnt) {
+            id = __ldg(inst_ids + base + t);
+            const float4* r = reinterpret_cast<const float4*>(rec + id);
+            const float4 a = __ldg(r);
+            s_a[t] = a;
+            s_f[t] = __ldg(r + 1);
+            // first pixel column/row whose centre is within reach; the second is the next one
+            const int qx = __float2int_rd(a.x - 0.5f) - tx * T;
+            const int qy = __float2int_rd(a.y - 0.5f) - ty * T;
+            const unsigned bit = 1u << (t & 31);
+            unsigned* mrow = s_mask[t >> 5];
+#pragma unroll
+            for (int dy = 0; dy < 2; ++dy)
+#pragma unroll
+                for (int dx = 0; dx < 2; ++dx) {
+                    const int cx = qx + dx, cy = qy + dy;
+                    if (cx >= 0 && cx < T && cy >= 0 && cy < T) atomicOr(mrow + cy * T + cx, bit);
+                }
+        }
+        __syncthreads();
+        if (!done) {
+#pragma unroll 1
+            for (int w = 0; w < WORDS && !done; ++w) {
+                unsigned mbits = s_mask[w][t];
+                while (mbits) {
+                    const int j = w * 32 + __ffs(mbits) - 1;
+                    mbits &= mbits - 1u;
+                    const float4 a = s_a[j];
+                    const float dx = fabsf(a.x - pcx), dy = fabsf(a.y - pcy);
+                    if (dx >= 1.0f || dy >= 1.0f) continue;
+                    const float wgt = __saturatef(1.0f - dx) * __saturatef(1.0f - dy);
+                    const float al = a.z * wgt;
+                    const float bw = Tr * al;
+                    if (KIND == BLEND_TRAIN) {
+                        // corner of the point's 2x2 footprint this pixel is: unique writer per slot
+                        if (bw > 0.0f) s_slot[(pcx > a.x ? 1 : 0) + (pcy > a.y ? 2 : 0)][j] = bw * wgt;
+                    }
+                    const float4 f = s_f[j];
+                    C0 += bw * f.x; C1 += bw * f.y; C2 += bw * f.z; C3 += bw * f.w;
+                    if (KIND == BLEND_INFER) Z += bw * a.w;
+                    Tr *= 1.0f - al;
+                    if (Tr < kTransmittanceEps) { done = true; break; }
+                }
+            }
+        }
+        if (KIND == BLEND_TRAIN) {
+            __syncthreads();
+            if (t < cnt) {
+                const float sum = ((s_slot[0][t] + s_slot[1][t]) + s_slot[2][t]) + s_slot[3][t];
+                if (sum > 0.0f) atomicAdd(blending_weights + id, sum);
+            }
+        }
+    }
+    if (inside) {
+        const int64_t n_px = (int64_t)width * height;
+        const int64_t pi = (int64_t)py * width + px;
+        image[pi] = C0;
+        image[n_px + pi] = C1;
+        image[2 * n_px + pi] = C2;
+        image[3 * n_px + pi] = C3;
+        if (KIND == BLEND_INFER) {
+            const float A = 1.0f - Tr;
+            depth_image[pi] = A > 0.0f ? Z / A : 0.0f;
+            alpha_image[pi] = Tr < kTransmittanceEps ? 1.0f : A;
+        } else {
+            alpha_image[pi] = Tr < kTransmittanceEps ? 1.0f : 1.0f - Tr;
+        }
+    }
+}
+
+template <int T>
+__global__ void __launch_bounds__(T * T) blend_bilinear_backward_kernel(
+    const uint2* __restrict__ ranges, const uint32_t* __restrict__ inst_ids, const PointRec* __restrict__ rec,
+    const float* __restrict__ grad_image, const float* __restrict__ grad_alpha, const float* __restrict__ image,
+    const float* __restrict__ alpha_image, float4* __restrict__ grad_feat_view, float* __restrict__ grad_opacity,
+    int width, int height, int gw) {
+    constexpr int B = T * T;
+    constexpr int WORDS = B / 32;
+    __shared__ float4 s_a[B];
+    __shared__ float4 s_f[B];
+    __shared__ unsigned s_mask[WORDS][B];
+    __shared__ float4 s_gf[4][B];    // per corner: feature gradient contribution
+    __shared__ float s_go[4][B];     // per corner: opacity gradient contribution
+
+    const int t = threadIdx.x;
+    const int tile = blockIdx.x;
+    const int tx = tile % gw, ty = tile / gw;
+    const int lx = t % T, ly = t / T;
+    const int px = tx * T + lx, py = ty * T + ly;
+    const bool inside = px < width && py < height;
+    const float pcx = (float)px + 0.5f, pcy = (float)py + 0.5f;
+
+    float4 g = make_float4(0.f, 0.f, 0.f, 0.f), Cfin = make_float4(0.f, 0.f, 0.f, 0.f);
+    float K = 0.0f;
+    if (inside) {
+        const int64_t n_px = (int64_t)width * height;
+        const int64_t pi = (int64_t)py * width + px;
+        g = make_float4(__ldg(grad_image + pi), __ldg(grad_image + n_px + pi), __ldg(grad_image + 2 * n_px + pi),
+                        __ldg(grad_image + 3 * n_px + pi));
+        Cfin = make_float4(__ldg(image + pi), __ldg(image + n_px + pi), __ldg(image + 2 * n_px + pi),
+                           __ldg(image + 3 * n_px + pi));
+        K = __ldg(grad_alpha + pi) * (1.0f - __ldg(alpha_image + pi));
+    }
+    float4 Crun = make_float4(0.f, 0.f, 0.f, 0.f);
+    float Tr = 1.0f;
+    bool done = !inside;
+
+    const uint2 range = __ldg(ranges + tile);
+    for (unsigned base = range.x; base < range.y; base += B) {
+        if (__syncthreads_count(done) == B) break;
+#pragma unroll
+        for (int w = 0; w < WORDS; ++w) s_mask[w][t] = 0u;
+#pragma unroll
+        for (int q = 0; q < 4; ++q) { s_gf[q][t] = make_float4(0.f, 0.f, 0.f, 0.f); s_go[q][t] = 0.0f; }
+        __syncthreads();
+        const int cnt = (int)min((unsigned)B, range.y - base);
+        uint32_t id = 0;
+        if (t < cnt) {
+            id = __ldg(inst_ids + base + t);
+            const float4* r = reinterpret_cast<const float4*>(rec + id);
+            const float4 a = __ldg(r);
+            s_a[t] = a;
+            s_f[t] = __ldg(r + 1);
+            const int qx = __float2int_rd(a.x - 0.5f) - tx * T;
+            const int qy = __float2int_rd(a.y - 0.5f) - ty * T;
+            const unsigned bit = 1u << (t & 31);
+            unsigned* mrow = s_mask[t >> 5];
+#pragma unroll
+            for (int dy = 0; dy < 2; ++dy)
+#pragma unroll
+                for (int dx = 0; dx < 2; ++dx) {
+                    const int cx = qx + dx, cy = qy + dy;
+                    if (cx >= 0 && cx < T && cy >= 0 && cy < T) atomicOr(mrow + cy * T + cx, bit);
+                }
+        }
+        __syncthreads();
+        if (!done) {
+#pragma unroll 1
+            for (int w = 0; w < WORDS && !done; ++w) {
+                unsigned mbits = s_mask[w][t];
+                while (mbits) {
+                    const int j = w * 32 + __ffs(mbits) - 1;
+                    mbits &= mbits - 1u;
+                    const float4 a = s_a[j];
+                    const float dx = fabsf(a.x - pcx), dy = fabsf(a.y - pcy);
+                    if (dx >= 1.0f || dy >= 1.0f) continue;
+                    const float wgt = __saturatef(1.0f - dx) * __saturatef(1.0f - dy);
+                    const float al = a.z * wgt;
+                    const float bw = Tr * al;
+                    const int q = (pcx > a.x ? 1 : 0) + (pcy > a.y ? 2 : 0);
+                    if (bw > 0.0f) s_gf[q][j] = make_float4(bw * g.x, bw * g.y, bw * g.z, bw * g.w);
+                    const float4 f = s_f[j];
+                    Crun.x += bw * f.x; Crun.y += bw * f.y; Crun.z += bw * f.z; Crun.w += bw * f.w;
+                    const float oma = 1.0f - al;
+                    const float rcp = 1.0f / fmaxf(oma, kOneMinusAlphaEps);
+                    const float from_features = (Tr * f.x + (Crun.x - Cfin.x) * rcp) * g.x +
+                                                (Tr * f.y + (Crun.y - Cfin.y) * rcp) * g.y +
+                                                (Tr * f.z + (Crun.z - Cfin.z) * rcp) * g.z +
+                                                (Tr * f.w + (Crun.w - Cfin.w) * rcp) * g.w;
+                    const float dalpha = from_features + K * rcp;
+                    const float dop = dalpha * wgt;
+                    if (dop != 0.0f) s_go[q][j] = dop;
+                    Tr *= oma;
+                    if (Tr < kTransmittanceEps) { done = true; break; }
+                }
+            }
+        }
+        __syncthreads();
+        if (t < cnt) {
+            float4 sf = s_gf[0][t];
+            float so = s_go[0][t];
+#pragma unroll
+            for (int q = 1; q < 4; ++q) {
+                const float4 v = s_gf[q][t];
+                sf.x += v.x; sf.y += v.y; sf.z += v.z; sf.w += v.w;
+                so += s_go[q][t];
+            }
+            if (sf.x != 0.0f || sf.y != 0.0f || sf.z != 0.0f || sf.w != 0.0f) atomicAdd(grad_feat_view + id, sf);
+            if (so != 0.0f) atomicAdd(grad_opacity + id, so);
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
+// Gaussian blend: footprints are not bounded by 2x2 pixels, so every pixel tests every staged point
+// (src/gaussian/kernels.cu:401-474 forward, :476-579 backward, :581-660 inference).
+// ------------------------------------------------------------------------------------------------
+template <int T, int KIND>
+__global__ void __launch_bounds__(T * T) blend_gaussian_forward_kernel(
+    const uint2* __restrict__ ranges, const uint32_t* __restrict__ inst_ids, const PointRec* __restrict__ rec,
+    const float4* __restrict__ conic, float* __restrict__ image, float* __restrict__ depth_image,
+    float* __restrict__ alpha_image, float* __restrict__ blending_weights, int width, int height, int gw,
+    float threshold) {
+    constexpr int B = T * T;
+    __shared__ float4 s_a[B];
+    __shared__ float4 s_f[B];
+    __shared__ float4 s_c[B];
+    __shared__ uint32_t s_id[B];
+    const int t = threadIdx.x;
+    const int tile = blockIdx.x;
+    const int tx = tile % gw, ty = tile / gw;
+    const int px = tx * T + t % T, py = ty * T + t / T;
+    const bool inside = px < width && py < height;
+    const float pcx = (float)px + 0.5f, pcy = (float)py + 0.5f;
+    float C0 = 0.f, C1 = 0.f, C2 = 0.f, C3 = 0.f, Z = 0.f, Tr = 1.0f;
+    bool done = !inside;
+    const uint2 range = __ldg(ranges + tile);
+    for (unsigned base = range.x; base < range.y; base += B) {
+        if (__syncthreads_count(done) == B) break;
+        const int cnt = (int)min((unsigned)B, range.y - base);
+        if (t < cnt) {
+            const uint32_t id = __ldg(inst_ids + base + t);
+            const float4* r = reinterpret_cast<const float4*>(rec + id);
+            s_a[t] = __ldg(r);
+            s_f[t] = __ldg(r + 1);
+            s_c[t] = __ldg(conic + id);
+            s_id[t] = id;
+        }
+        __syncthreads();
+        for (int j = 0; !done && j < cnt; ++j) {
+            const float4 a = s_a[j];
+            const float4 c = s_c[j];
+            const float dx = a.x - pcx, dy = a.y - pcy;
+            const float e = -0.5f * (c.x * dx * dx + c.z * dy * dy) - c.y * dx * dy;
+            if (e > 0.0f) continue;
+            const float G = KIND == BLEND_INFER ? __expf(e) : expf(e);
+            if (G < threshold) continue;
+            const float al = a.z * G;
+            const float bw = Tr * al;
+            if (KIND == BLEND_TRAIN) {
+                if (bw > 0.0f) atomicAdd(blending_weights + s_id[j], G * bw);
+            }
+            const float4 f = s_f[j];
+            C0 += bw * f.x; C1 += bw * f.y; C2 += bw * f.z; C3 += bw * f.w;
+            if (KIND == BLEND_INFER) Z += bw * a.w;
+            Tr *= 1.0f - al;
+            if (Tr < kTransmittanceEps) done = true;
+        }
+    }
+    if (inside) {
+        const int64_t n_px = (int64_t)width * height;
+        const int64_t pi = (int64_t)py * width + px;
+        image[pi] = C0;
+        image[n_px + pi] = C1;
+        image[2 * n_px + pi] = C2;
+        image[3 * n_px + pi] = C3;
+        if (KIND == BLEND_INFER) {
+            const float A = 1.0f - Tr;
+            depth_image[pi] = A > 0.0f ? Z / A : 0.0f;
+            alpha_image[pi] = Tr < kTransmittanceEps ? 1.0f : A;
+        } else {
+            alpha_image[pi] = Tr < kTransmittanceEps ? 1.0f : 1.0f - Tr;
+        }
+    }
+}
+
+template <int T>
+__global__ void __launch_bounds__(T * T) blend_gaussian_backward_kernel(
+    const uint2* __restrict__ ranges, const uint32_t* __restrict__ inst_ids, const PointRec* __restrict__ rec,
+    const float4* __restrict__ conic, const float* __restrict__ grad_image, const float* __restrict__ grad_alpha,
+    const float* __restrict__ image, const float* __restrict__ alpha_image, float4* __restrict__ grad_feat_view,
+    float* __restrict__ grad_opacity, int width, int height, int gw) {
+    constexpr int B = T * T;
+    __shared__ float4 s_a[B];
+    __shared__ float4 s_f[B];
+    __shared__ float4 s_c[B];
+    __shared__ uint32_t s_id[B];
+    const int t = threadIdx.x;
+    const int tile = blockIdx.x;
+    const int tx = tile % gw, ty = tile / gw;
+    const int px = tx * T + t % T, py = ty * T + t / T;
+    const bool inside = px < width && py < height;
+    const float pcx = (float)px + 0.5f, pcy = (float)py + 0.5f;
+    float4 g = make_float4(0.f, 0.f, 0.f, 0.f), Cfin = make_float4(0.f, 0.f, 0.f, 0.f);
+    float K = 0.0f;
+    if (inside) {
+        const int64_t n_px = (int64_t)width * height;
+        const int64_t pi = (int64_t)py * width + px;
+        g = make_float4(__ldg(grad_image + pi), __ldg(grad_image + n_px + pi), __ldg(grad_image + 2 * n_px + pi),
+                        __ldg(grad_image + 3 * n_px + pi));
+        Cfin = make_float4(__ldg(image + pi), __ldg(image + n_px + pi), __ldg(image + 2 * n_px + pi),
+                           __ldg(image + 3 * n_px + pi));
+        K = __ldg(grad_alpha + pi) * (1.0f - __ldg(alpha_image + pi));
+    }
+    float4 Crun = make_float4(0.f, 0.f, 0.f, 0.f);
+    float Tr = 1.0f;
+    bool done = !inside;
+    const uint2 range = __ldg(ranges + tile);
+    for (unsigned base = range.x; base < range.y; base += B) {
+        if (__syncthreads_count(done) == B) break;
+        const int cnt = (int)min((unsigned)B, range.y - base);
+        if (t < cnt) {
+            const uint32_t id = __ldg(inst_ids + base + t);
+            const float4* r = reinterpret_cast<const float4*>(rec + id);
+            s_a[t] = __ldg(r);
+            s_f[t] = __ldg(r + 1);
+            s_c[t] = __ldg(conic + id);
+            s_id[t] = id;
+        }
+        __syncthreads();
+        for (int j = 0; !done && j < cnt; ++j) {
+            const float4 a = s_a[j];
+            const float4 c = s_c[j];
+            const float dx = a.x - pcx, dy = a.y - pcy;
+            const float e = -0.5f * (c.x * dx * dx + c.z * dy * dy) - c.y * dx * dy;
+            if (e > 0.0f) continue;
+            const float G = expf(e);
+            if (G < kTrainGaussThreshold) continue;
+            const float al = a.z * G;
+            const float bw = Tr * al;
+            const uint32_t id = s_id[j];
+            if (bw > 0.0f) atomicAdd(grad_feat_view + id, make_float4(bw * g.x, bw * g.y, bw * g.z, bw * g.w));
+            const float4 f = s_f[j];
+            Crun.x += bw * f.x; Crun.y += bw * f.y; Crun.z += bw * f.z; Crun.w += bw * f.w;
+            const float oma = 1.0f - al;
+            const float rcp = 1.0f / fmaxf(oma, kOneMinusAlphaEps);
+            const float from_features = (Tr * f.x + (Crun.x - Cfin.x) * rcp) * g.x +
+                                        (Tr * f.y + (Crun.y - Cfin.y) * rcp) * g.y +
+                                        (Tr * f.z + (Crun.z - Cfin.z) * rcp) * g.z +
+                                        (Tr * f.w + (Crun.w - Cfin.w) * rcp) * g.w;
+            const float dalpha = from_features + K * rcp;
+            const float dop = dalpha * G;
+            if (dop != 0.0f) atomicAdd(grad_opacity + id, dop);
+            Tr *= oma;
+            if (Tr < kTransmittanceEps) done = true;
+        }
+    }
+}
+
+// SH chain rule for every point, zero rows for culled ones, written as 72 contiguous bytes per point
+// through a shared-memory slab so the stores are coalesced 16-byte vectors.
+// src/bilinear/kernels.cu:86-104 + include/sh_utils.cuh:44-62; the zero rows replace the
+// torch::zeros of src/rasterization_api.cu:139.
+__global__ void __launch_bounds__(kPreThreads) preprocess_backward_kernel(
+    const float* __restrict__ positions, const float* __restrict__ cam, const uint2* __restrict__ bounds,
+    const float4* __restrict__ grad_feat_view, __half* __restrict__ grad_features, int64_t n) {
+    __shared__ __align__(16) __half s_out[kPreThreads * 36];
+    const int64_t block_first = (int64_t)blockIdx.x * kPreThreads;
+    const int in_block = (int)min((int64_t)kPreThreads, n - block_first);
+    const int64_t i = block_first + threadIdx.x;
+    __half* o = s_out + threadIdx.x * 36;
+    bool touched = false;
+    if (i < n) touched = tiles_of(__ldg(bounds + i)) != 0u;
+    if (touched) {
+        float b[9];
+        sh_basis(__ldg(positions + 3 * i), __ldg(positions + 3 * i + 1), __ldg(positions + 3 * i + 2), cam, b);
+        b[1] = -b[1]; b[3] = -b[3]; b[5] = -b[5]; b[7] = -b[7];
+        const float4 gv = __ldg(grad_feat_view + i);
+#pragma unroll
+        for (int k = 0; k < 9; ++k) {
+            const __half2 xy = __float22half2_rn(make_float2(b[k] * gv.x, b[k] * gv.y));
+            const __half2 zw = __float22half2_rn(make_float2(b[k] * gv.z, b[k] * gv.w));
+            *reinterpret_cast<__half2*>(o + 4 * k) = xy;
+            *reinterpret_cast<__half2*>(o + 4 * k + 2) = zw;
+        }
+    } else {
+#pragma unroll
+        for (int k = 0; k < 18; ++k) *reinterpret_cast<unsigned*>(o + 2 * k) = 0u;
+    }
+    __syncthreads();
+    unsigned char* dst = reinterpret_cast<unsigned char*>(grad_features) + block_first * 72;
+    const int bytes = in_block * 72;
+    const int n16 = bytes / 16;
+    uint4* dst16 = reinterpret_cast<uint4*>(dst);
+    const uint4* src16 = reinterpret_cast<const uint4*>(s_out);
+    for (int k = threadIdx.x; k < n16; k += kPreThreads) dst16[k] = src16[k];
+    for (int k = n16 * 16 + 2 * threadIdx.x; k < bytes; k += 2 * kPreThreads)
+        *reinterpret_cast<unsigned short*>(dst + k) = *reinterpret_cast<const unsigned short*>(reinterpret_cast<const unsigned char*>(s_out) + k);
+}
+
+// ------------------------------------------------------------------------------------------------
+// Host side
+// ------------------------------------------------------------------------------------------------
+struct PointBlob {
+    PointRec* rec;
+    uint2* bounds;
+    float4* conic;
+    unsigned* block_visible;
+    unsigned long long* block_instances;
+    unsigned long long* counters;
+    size_t phase1_bytes;   // everything above; the rest needs n_visible
+    uint32_t* keys[2];
+    uint32_t* ids[2];
+    unsigned* inst_block_sums;
+    void* sort_ws;
+    size_t total;
+};
+
+PointBlob carve_point_blob(void* p, int64_t n, int64_t n_visible, int mode) {
+    PointBlob b;
+    Carver c(p);
+    const int64_t nb = ceil_div<int64_t>(n > 0 ? n : 1, kPreThreads);
+    b.rec = c.take<PointRec>(n);
+    b.bounds = c.take<uint2>(n);
+    b.conic = mode == INPC_MODE_GAUSSIAN ? c.take<float4>(n) : nullptr;
+    b.block_visible = c.take<unsigned>(nb);
+    b.block_instances = c.take<unsigned long long>(nb);
+    b.counters = c.take<unsigned long long>(4);
+    b.phase1_bytes = c.used();
+    for (int k = 0; k < 2; ++k) b.keys[k] = c.take<uint32_t>(n_visible);
+    for (int k = 0; k < 2; ++k) b.ids[k] = c.take<uint32_t>(n_visible);
+    b.inst_block_sums = c.take<unsigned>(ceil_div<int64_t>(n_visible > 0 ? n_visible : 1, kInstThreads));
+    c.off = align_up(c.off);
+    b.sort_ws = c.base + c.off;
+    c.off += sort_workspace_bytes(n_visible);
+    b.total = c.used();
+    return b;
+}
+
+struct InstanceBlob {
+    uint32_t* keys[2];
+    uint32_t* ids[2];
+    uint2* ranges;
+    void* sort_ws;
+    size_t total;
+};
+
+InstanceBlob carve_instance_blob(void* p, int64_t n_instances, int n_tiles) {
+    InstanceBlob b;
+    Carver c(p);
+    b.ranges = c.take<uint2>(n_tiles);
+    for (int k = 0; k < 2; ++k) b.keys[k] = c.take<uint32_t>(n_instances);
+    for (int k = 0; k < 2; ++k) b.ids[k] = c.take<uint32_t>(n_instances);
+    c.off = align_up(c.off);
+    b.sort_ws = c.base + c.off;
+    c.off += sort_workspace_bytes(n_instances);
+    b.total = c.used();
+    return b;
+}
+
+// The state handed back to the caller only stores blob bases and counts; which ping-pong buffer holds
+// a sorted result follows from the number of radix passes, which follows from the counts.
+int depth_result_buffer(int64_t n_visible) { return n_visible > 1 ? (ceil_div(32, 8) & 1) : 0; }
+int tile_result_buffer(int64_t n_instances, int n_tiles) {
+    const int end_bit = bit_length((uint32_t)(n_tiles - 1));
+    return (n_instances > 1 && end_bit > 0) ? (ceil_div(end_bit, 8) & 1) : 0;
+}
+
+unsigned long long* pinned_counters() {
+    static thread_local unsigned long long* p = nullptr;
+    if (!p && cudaHostAlloc(reinterpret_cast<void**>(&p), 4 * sizeof(unsigned long long), cudaHostAllocDefault) != cudaSuccess) p = nullptr;
+    return p;
+}
+
+int check_view(const inpc_view* v, int tile_size, int mode, int64_t n) {
+    if (!v || !v->w2c || !v->cam_position) { set_error("view, view.w2c and view.cam_position must be non-null"); return INPC_E_INVALID; }
+    if (mode != INPC_MODE_BILINEAR && mode != INPC_MODE_GAUSSIAN) { set_error("unsupported rasterizer mode %d", mode); return INPC_E_INVALID; }
+    if (tile_size != 8 && tile_size != 16) { set_error("tile_size must be 8 or 16, got %d", tile_size); return INPC_E_INVALID; }
+    if (v->width <= 0 || v->height <= 0 || v->width > 65535 * tile_size || v->height > 65535 * tile_size) {
+        set_error("image size %dx%d out of range", v->width, v->height);
+        return INPC_E_INVALID;
+    }
+    if (n < 0 || n >= ((int64_t)1 << 30)) { set_error("n=%lld out of range [0, 2^30)", (long long)n); return INPC_E_INVALID; }
+    return INPC_OK;
+}
+
+template <int MODE, int VARIANT>
+int run_front(const RasterParams& rp, int64_t n, const float* positions, const void* features, const float* opacities,
+              inpc_alloc_fn alloc_point, inpc_alloc_fn alloc_instance, void* user, inpc_raster_state* st,
+              PointBlob* pb_out, InstanceBlob* ib_out, cudaStream_t stream) {
+    const int n_tiles = rp.gw * rp.gh;
+    const int64_t nb = ceil_div<int64_t>(n > 0 ? n : 1, kPreThreads);
+    // phase 1 needs only n: allocate for the worst case n_visible == n so that one blob serves both phases
+    const PointBlob sizing = carve_point_blob(nullptr, n, n, MODE);
+    void* pblob = alloc_point(user, sizing.total);
+    if (!pblob) { set_error("point allocator returned NULL for %zu bytes", sizing.total); return INPC_E_ALLOC; }
+    PointBlob pb = carve_point_blob(pblob, n, n, MODE);
+
+    int64_t n_visible = 0, n_instances = 0;
+    if (n > 0) {
+        visibility_count_kernel<MODE, VARIANT><<<(unsigned)nb, kPreThreads, 0, stream>>>(positions, n, rp, pb.block_visible, pb.block_instances);
+        INPC_LAUNCH_CHECK("visibility_count_kernel");
+        scan_block_counts_kernel<<<1, kScanThreads, 0, stream>>>(pb.block_visible, pb.block_instances, nb, pb.counters);
+        INPC_LAUNCH_CHECK("scan_block_counts_kernel");
+        unsigned long long* host = pinned_counters();
+        if (!host) return cuda_fail(cudaGetLastError(), "cudaHostAlloc(counters)");
+        INPC_CUDA_TRY(cudaMemcpyAsync(host, pb.counters, 2 * sizeof(unsigned long long), cudaMemcpyDeviceToHost, stream));
+        INPC_CUDA_TRY(cudaStreamSynchronize(stream));
+        n_visible = (int64_t)host[0];
+        n_instances = (int64_t)host[1];
+        if (read_and_clear_status(STATUS_LOOKBACK_TIMEOUT)) {
+            set_error("an earlier radix-sort pass gave up waiting for a predecessor tile; results of that call are invalid");
+            return INPC_E_DEVICE;
+        }
+    }
+    if (n_instances >= ((int64_t)1 << 30)) {
+        set_error("%lld (point, tile) instances exceed the 2^30 capacity", (long long)n_instances);
+        return INPC_E_CAPACITY;
+    }
+    // re-carve with the true visible count: the leading arrays keep their place
+    pb = carve_point_blob(pblob, n, n_visible, MODE);
+
+    const InstanceBlob isz = carve_instance_blob(nullptr, n_instances, n_tiles);
+    void* iblob = alloc_instance(user, isz.total);
+    if (!iblob) { set_error("instance allocator returned NULL for %zu bytes", isz.total); return INPC_E_ALLOC; }
+    InstanceBlob ib = carve_instance_blob(iblob, n_instances, n_tiles);
+    INPC_CUDA_TRY(cudaMemsetAsync(ib.ranges, 0, sizeof(uint2) * (size_t)n_tiles, stream));
+
+    if (n > 0) {
+        preprocess_kernel<MODE, VARIANT><<<(unsigned)nb, kPreThreads, 0, stream>>>(
+            positions, static_cast<const __half*>(features), opacities, n, rp, pb.block_visible, pb.rec, pb.bounds,
+            pb.conic, pb.keys[0], pb.ids[0]);
+        INPC_LAUNCH_CHECK("preprocess_kernel");
+    }
+    int in_alt = 0;
+    int rc = sort_pairs(pb.keys[0], pb.keys[1], pb.ids[0], pb.ids[1], n_visible, 32, pb.sort_ws, &in_alt, stream);
+    if (rc != INPC_OK) return rc;
+    const uint32_t* sorted_ids = pb.ids[in_alt];
+    if (n_visible > 0 && n_instances > 0) {
+        const int64_t ibk = ceil_div<int64_t>(n_visible, kInstThreads);
+        instance_count_kernel<<<(unsigned)ibk, kInstThreads, 0, stream>>>(sorted_ids, pb.bounds, n_visible, pb.inst_block_sums);
+        INPC_LAUNCH_CHECK("instance_count_kernel");
+        scan_u32_kernel<<<1, kScanThreads, 0, stream>>>(pb.inst_block_sums, ibk);
+        INPC_LAUNCH_CHECK("scan_u32_kernel");
+        emit_instances_kernel<<<(unsigned)ibk, kInstThreads, 0, stream>>>(sorted_ids, pb.bounds, n_visible, pb.inst_block_sums, rp.gw, ib.keys[0], ib.ids[0]);
+        INPC_LAUNCH_CHECK("emit_instances_kernel");
+        int t_alt = 0;
+        rc = sort_pairs(ib.keys[0], ib.keys[1], ib.ids[0], ib.ids[1], n_instances, bit_length((uint32_t)(n_tiles - 1)), ib.sort_ws, &t_alt, stream);
+        if (rc != INPC_OK) return rc;
+        tile_ranges_kernel<<<(unsigned)ceil_div<int64_t>(n_instances, 256), 256, 0, stream>>>(ib.keys[t_alt], n_instances, ib.ranges);
+        INPC_LAUNCH_CHECK("tile_ranges_kernel");
+    }
+    st->point_blob = pblob;
+    st->instance_blob = iblob;
+    st->n_points = n;
+    st->n_visible = n_visible;
+    st->n_instances = n_instances;
+    st->tile_size = rp.tile;
+    st->mode = MODE;
+    *pb_out = pb;
+    *ib_out = ib;
+    return INPC_OK;
+}
+
+RasterParams make_params(const inpc_view* view, int tile_size, float sigma_world, float sigma_cutoff, const float* scales) {
+    RasterParams rp;
+    rp.v = to_params(view);
+    rp.tile = tile_size;
+    rp.gw = ceil_div(view->width, tile_size);
+    rp.gh = ceil_div(view->height, tile_size);
+    rp.sigma_world = sigma_world;
+    rp.sigma_cutoff = sigma_cutoff;
+    rp.scales = scales;
+    return rp;
+}
+
+template <int KIND>
+int launch_blend_forward(int mode, const RasterParams& rp, const PointBlob& pb, const InstanceBlob& ib, int64_t n_instances,
+                         float* image, float* depth, float* alpha, float* blending_weights, float threshold,
+                         cudaStream_t stream) {
+    const int n_tiles = rp.gw * rp.gh;
+    const uint32_t* ids = ib.ids[tile_result_buffer(n_instances, n_tiles)];
+    const int W = rp.v.width, H = rp.v.height;
+    if (mode == INPC_MODE_BILINEAR) {
+        if (rp.tile == 8)
+            blend_bilinear_forward_kernel<8, KIND><<<n_tiles, 64, 0, stream>>>(ib.ranges, ids, pb.rec, image, depth, alpha, blending_weights, W, H, rp.gw);
+        else
+            blend_bilinear_forward_kernel<16, KIND><<<n_tiles, 256, 0, stream>>>(ib.ranges, ids, pb.rec, image, depth, alpha, blending_weights, W, H, rp.gw);
+    } else {
+        if (rp.tile == 8)
+            blend_gaussian_forward_kernel<8, KIND><<<n_tiles, 64, 0, stream>>>(ib.ranges, ids, pb.rec, pb.conic, image, depth, alpha, blending_weights, W, H, rp.gw, threshold);
+        else
+            blend_gaussian_forward_kernel<16, KIND><<<n_tiles, 256, 0, stream>>>(ib.ranges, ids, pb.rec, pb.conic, image, depth, alpha, blending_weights, W, H, rp.gw, threshold);
+    }
+    INPC_LAUNCH_CHECK("blend_forward_kernel");
+    return INPC_OK;
+}
+
+}  // namespace
+
+}  // namespace inpc
+
+using namespace inpc;
+
+extern "C" int inpc_rasterize_forward(int mode, int tile_size, const inpc_view* view, int64_t n, const float* positions,
+                                      const void* features, const float* opacities, float* image, float* alpha,
+                                      float* blending_weights, inpc_alloc_fn alloc_point, inpc_alloc_fn alloc_instance,
+                                      void* alloc_user, inpc_raster_state* state, void* stream_) {
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    int rc = check_view(view, tile_size, mode, n);
+    if (rc != INPC_OK) return rc;
+    if (!state || !alloc_point || !alloc_instance || !image || !alpha || (n > 0 && (!positions || !features || !opacities || !blending_weights))) {
+        set_error("inpc_rasterize_forward: null argument");
+        return INPC_E_INVALID;
+    }
+    const RasterParams rp = make_params(view, tile_size, 0.0f, 3.0f, nullptr);
+    if (n > 0) INPC_CUDA_TRY(cudaMemsetAsync(blending_weights, 0, sizeof(float) * (size_t)n, stream));
+    PointBlob pb;
+    InstanceBlob ib;
+    if (mode == INPC_MODE_BILINEAR)
+        rc = run_front<INPC_MODE_BILINEAR, VAR_TRAIN>(rp, n, positions, features, opacities, alloc_point, alloc_instance, alloc_user, state, &pb, &ib, stream);
+    else
+        rc = run_front<INPC_MODE_GAUSSIAN, VAR_TRAIN>(rp, n, positions, features, opacities, alloc_point, alloc_instance, alloc_user, state, &pb, &ib, stream);
+    if (rc != INPC_OK) return rc;
+    return launch_blend_forward<BLEND_TRAIN>(mode, rp, pb, ib, state->n_instances, image, nullptr, alpha, blending_weights, kTrainGaussThreshold, stream);
+}
+
+extern "C" int inpc_rasterize_backward(const inpc_raster_state* state, const inpc_view* view, const float* grad_image,
+                                       const float* grad_alpha, const float* image, const float* alpha,
+                                       const float* positions, const float* opacities, float* grad_features_view,
+                                       void* grad_features, float* grad_opacities, void* stream_) {
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    if (!state) { set_error("inpc_rasterize_backward: null state"); return INPC_E_INVALID; }
+    int rc = check_view(view, state->tile_size, state->mode, state->n_points);
+    if (rc != INPC_OK) return rc;
+    const int64_t n = state->n_points;
+    if (!grad_image || !grad_alpha || !image || !alpha || (n > 0 && (!positions || !grad_features_view || !grad_features || !grad_opacities || !state->point_blob || !state->instance_blob))) {
+        set_error("inpc_rasterize_backward: null argument");
+        return INPC_E_INVALID;
+    }
+    (void)opacities;   // the opacity travels in the point record
+    if (n == 0) return INPC_OK;
+    const RasterParams rp = make_params(view, state->tile_size, 0.0f, 3.0f, nullptr);
+    const int n_tiles = rp.gw * rp.gh;
+    const PointBlob pb = carve_point_blob(state->point_blob, n, state->n_visible, state->mode);
+    const InstanceBlob ib = carve_instance_blob(state->instance_blob, state->n_instances, n_tiles);
+    const uint32_t* ids = ib.ids[tile_result_buffer(state->n_instances, n_tiles)];
+    INPC_CUDA_TRY(cudaMemsetAsync(grad_features_view, 0, sizeof(float4) * (size_t)n, stream));
+    INPC_CUDA_TRY(cudaMemsetAsync(grad_opacities, 0, sizeof(float) * (size_t)n, stream));
+    float4* gfv = reinterpret_cast<float4*>(grad_features_view);
+    const int W = rp.v.width, H = rp.v.height;
+    if (state->mode == INPC_MODE_BILINEAR) {
+        if (rp.tile == 8)
+            blend_bilinear_backward_kernel<8><<<n_tiles, 64, 0, stream>>>(ib.ranges, ids, pb.rec, grad_image, grad_alpha, image, alpha, gfv, grad_opacities, W, H, rp.gw);
+        else
+            blend_bilinear_backward_kernel<16><<<n_tiles, 256, 0, stream>>>(ib.ranges, ids, pb.rec, grad_image, grad_alpha, image, alpha, gfv, grad_opacities, W, H, rp.gw);
+    } else {
+        if (rp.tile == 8)
+            blend_gaussian_backward_kernel<8><<<n_tiles, 64, 0, stream>>>(ib.ranges, ids, pb.rec, pb.conic, grad_image, grad_alpha, image, alpha, gfv, grad_opacities, W, H, rp.gw);
+        else
+            blend_gaussian_backward_kernel<16><<<n_tiles, 256, 0, stream>>>(ib.ranges, ids, pb.rec, pb.conic, grad_image, grad_alpha, image, alpha, gfv, grad_opacities, W, H, rp.gw);
+    }
+    INPC_LAUNCH_CHECK("blend_backward_kernel");
+    preprocess_backward_kernel<<<(unsigned)ceil_div<int64_t>(n, kPreThreads), kPreThreads, 0, stream>>>(
+        positions, view->cam_position, pb.bounds, gfv, static_cast<__half*>(grad_features), n);
+    INPC_LAUNCH_CHECK("preprocess_backward_kernel");
+    return INPC_OK;
+}
+
+extern "C" int inpc_render(int mode, int tile_size, const inpc_view* view, int64_t n, const float* positions,
+                           const void* features_raw, float sigma_world, float sigma_cutoff, float* image, float* depth,
+                           float* alpha, inpc_alloc_fn alloc_point, inpc_alloc_fn alloc_instance, void* alloc_user,
+                           void* stream_) {
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    int rc = check_view(view, tile_size, mode, n);
+    if (rc != INPC_OK) return rc;
+    if (!alloc_point || !alloc_instance || !image || !depth || !alpha || (n > 0 && (!positions || !features_raw))) {
+        set_error("inpc_render: null argument");
+        return INPC_E_INVALID;
+    }
+    const RasterParams rp = make_params(view, tile_size, sigma_world, sigma_cutoff, nullptr);
+    inpc_raster_state st;
+    PointBlob pb;
+    InstanceBlob ib;
+    if (mode == INPC_MODE_BILINEAR)
+        rc = run_front<INPC_MODE_BILINEAR, VAR_RAW37>(rp, n, positions, features_raw, nullptr, alloc_point, alloc_instance, alloc_user, &st, &pb, &ib, stream);
+    else
+        rc = run_front<INPC_MODE_GAUSSIAN, VAR_RAW37>(rp, n, positions, features_raw, nullptr, alloc_point, alloc_instance, alloc_user, &st, &pb, &ib, stream);
+    if (rc != INPC_OK) return rc;
+    // runtime cut-off exp(-cutoff^2/2): src/gaussian/inference.cu:171
+    const float threshold = expf(-0.5f * sigma_cutoff * sigma_cutoff);
+    return launch_blend_forward<BLEND_INFER>(mode, rp, pb, ib, st.n_instances, image, depth, alpha, nullptr, threshold, stream);
+}
+
+extern "C" int inpc_render_preextracted(int mode, int tile_size, const inpc_view* view, int64_t n, const float* positions,
+                                        const void* features, const float* opacities, const float* scales,
+                                        float sigma_world, float sigma_cutoff, float* image, float* depth, float* alpha,
+                                        inpc_alloc_fn alloc_point, inpc_alloc_fn alloc_instance, void* alloc_user,
+                                        void* stream_) {
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    int rc = check_view(view, tile_size, mode, n);
+    if (rc != INPC_OK) return rc;
+    if (!alloc_point || !alloc_instance || !image || !depth || !alpha || (n > 0 && (!positions || !features || !opacities))) {
+        set_error("inpc_render_preextracted: null argument");
+        return INPC_E_INVALID;
+    }
+    const RasterParams rp = make_params(view, tile_size, sigma_world, sigma_cutoff, scales);
+    inpc_raster_state st;
+    PointBlob pb;
+    InstanceBlob ib;
+    if (mode == INPC_MODE_BILINEAR)
+        rc = run_front<INPC_MODE_BILINEAR, VAR_PREEXTRACTED>(rp, n, positions, features, opacities, alloc_point, alloc_instance, alloc_user, &st, &pb, &ib, stream);
+    else
+        rc = run_front<INPC_MODE_GAUSSIAN, VAR_PREEXTRACTED>(rp, n, positions, features, opacities, alloc_point, alloc_instance, alloc_user, &st, &pb, &ib, stream);
+    if (rc != INPC_OK) return rc;
+    const float threshold = expf(-0.5f * sigma_cutoff * sigma_cutoff);
+    return launch_blend_forward<BLEND_INFER>(mode, rp, pb, ib, st.n_instances, image, depth, alpha, nullptr, threshold, stream);
+}
+
+namespace inpc_debug {
+__global__ void unpack_points_kernel(const PointRec* __restrict__ rec, const uint2* __restrict__ bounds, int64_t n, int which,
+                                     void* __restrict__ dst) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const uint2 b = bounds[i];
+    const bool vis = tiles_of(b) != 0u;
+    const float4* r = reinterpret_cast<const float4*>(rec + i);
+    if (which == 4) static_cast<unsigned*>(dst)[i] = tiles_of(b);
+    else if (which == 5) { const float4 a = vis ? r[0] : make_float4(0, 0, 0, 0); static_cast<float2*>(dst)[i] = make_float2(a.x, a.y); }
+    else if (which == 6) static_cast<float*>(dst)[i] = vis ? r[0].w : 0.0f;
+    else if (which == 7) static_cast<float4*>(dst)[i] = vis ? r[1] : make_float4(0, 0, 0, 0);
+    else if (which == 8) {
+        unsigned short* o = static_cast<unsigned short*>(dst) + 4 * i;
+        o[0] = (unsigned short)(b.x & 0xffffu); o[1] = (unsigned short)(b.x >> 16);
+        o[2] = (unsigned short)(b.y & 0xffffu); o[3] = (unsigned short)(b.y >> 16);
+    }
+}
+}  // namespace inpc_debug
+
+extern "C" int inpc_raster_debug_copy(const inpc_raster_state* state, const inpc_view* view, int which, void* dst,
+                                      void* stream_) {
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    if (!state || !view || !dst) { set_error("inpc_raster_debug_copy: null argument"); return INPC_E_INVALID; }
+    const int gw = ceil_div(view->width, state->tile_size), gh = ceil_div(view->height, state->tile_size);
+    const int n_tiles = gw * gh;
+    const PointBlob pb = carve_point_blob(state->point_blob, state->n_points, state->n_visible, state->mode);
+    const InstanceBlob ib = carve_instance_blob(state->instance_blob, state->n_instances, n_tiles);
+    const int d = depth_result_buffer(state->n_visible);
+    const int ti = tile_result_buffer(state->n_instances, n_tiles);
+    switch (which) {
+        case 0: INPC_CUDA_TRY(cudaMemcpyAsync(dst, pb.ids[d], 4 * (size_t)state->n_visible, cudaMemcpyDeviceToDevice, stream)); break;
+        case 1: INPC_CUDA_TRY(cudaMemcpyAsync(dst, pb.keys[d], 4 * (size_t)state->n_visible, cudaMemcpyDeviceToDevice, stream)); break;
+        case 2: INPC_CUDA_TRY(cudaMemcpyAsync(dst, ib.ids[ti], 4 * (size_t)state->n_instances, cudaMemcpyDeviceToDevice, stream)); break;
+        case 3: INPC_CUDA_TRY(cudaMemcpyAsync(dst, ib.ranges, 8 * (size_t)n_tiles, cudaMemcpyDeviceToDevice, stream)); break;
+        case 4: case 5: case 6: case 7: case 8:
+            if (state->n_points > 0) {
+                inpc_debug::unpack_points_kernel<<<(unsigned)ceil_div<int64_t>(state->n_points, 256), 256, 0, stream>>>(pb.rec, pb.bounds, state->n_points, which, dst);
+                INPC_LAUNCH_CHECK("unpack_points_kernel");
+            }
+            break;
+        default: set_error("inpc_raster_debug_copy: unknown array %d", which); return INPC_E_INVALID;
+    }
+    return INPC_OK;
+}

@@ -1,0 +1,593 @@
+// Probability-field sampler of the inpc_b200 library.
+//
+// Per-view leaf weights -> normalised fp32 CDF (deterministic block scans) -> per-slot draws from a
+// counter-based Philox4x32-10 stream: one Philox block yields the CDF uniform and the three jitter
+// uniforms of a draw.  Every output slot owns its own sub-stream (seed, call, slot, attempt), so the
+// training sampler needs no atomics and is reproducible; the reference's rejection sampler hands out
+// slots with an atomic ticket and is not (sampling/src/sampling_kernels.cu:104-125).
+// Citations are paths below INPCCudaBackend/INPCCudaBackend/sampling/ of the reference.
+#include "common.cuh"
+
+namespace inpc {
+
+namespace {
+
+constexpr float kEps = 1e-8f;   // FLT_EPS of the reference's utils.h:8
+constexpr int kThreads = 256;
+constexpr int kMaxAttempts = 4096;
+
+// ---- viewpoint weights: src/sampling_kernels.cu:9-64 ----------------------------------------
+struct Rows {
+    float r0[4], r1[4], r2[4];
+};
+__device__ __forceinline__ Rows load_rows(const float* __restrict__ w2c) {
+    Rows m;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) { m.r0[k] = __ldg(w2c + k); m.r1[k] = __ldg(w2c + 4 + k); m.r2[k] = __ldg(w2c + 8 + k); }
+    return m;
+}
+
+__device__ __forceinline__ bool in_frustum(const Rows& m, const ViewParams& v, float px, float py, float pz, float* z_out) {
+    const float vx = m.r0[0] * px + m.r0[1] * py + m.r0[2] * pz + m.r0[3];
+    const float vy = m.r1[0] * px + m.r1[1] * py + m.r1[2] * pz + m.r1[3];
+    const float z = m.r2[0] * px + m.r2[1] * py + m.r2[2] * pz + m.r2[3];
+    const float inv_z = 1.0f / (z + kEps);
+    const float x = vx * inv_z * v.fx + v.cx;
+    const float y = vy * inv_z * v.fy + v.cy;
+    if (z_out) *z_out = z;
+    return (z >= v.near_plane) & (z <= v.far_plane) & (x >= 0.0f) & (x < (float)v.width) & (y >= 0.0f) & (y < (float)v.height);
+}
+
+__global__ void __launch_bounds__(kThreads) viewpoint_weights_kernel(ViewParams v, int64_t n_cells,
+                                                                     const float* __restrict__ centers,
+                                                                     const int* __restrict__ levels,
+                                                                     const float* __restrict__ weights,
+                                                                     float initial_size, float* __restrict__ out) {
+    const int64_t l = (int64_t)blockIdx.x * kThreads + threadIdx.x;
+    if (l >= n_cells) return;
+    const Rows m = load_rows(v.w2c);
+    const float cx = __ldg(centers + 3 * l), cy = __ldg(centers + 3 * l + 1), cz = __ldg(centers + 3 * l + 2);
+    const int level = __ldg(levels + l);
+    float z;
+    bool valid = in_frustum(m, v, cx, cy, cz, &z);
+    if (!valid) {
+        const float half_size = initial_size / scalbnf(1.0f, level + 1);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            const float ox = (k & 4) ? 1.0f : -1.0f, oy = (k & 2) ? 1.0f : -1.0f, oz = (k & 1) ? 1.0f : -1.0f;
+            valid |= in_frustum(m, v, cx + half_size * ox, cy + half_size * oy, cz + half_size * oz, nullptr);
+        }
+    }
+    float w = 0.0f;
+    if (valid) {
+        const float depth_scale = fmaxf(fabsf(z - v.near_plane) / v.far_plane, kEps);
+        const float size_scale = exp2f(static_cast<float>(level) * 0.5f);
+        w = 1.0f / (depth_scale * size_scale) * __ldg(weights + l);
+    }
+    out[l] = w;
+}
+
+// ---- CDF: src/sampling.cu:97-125 (Sum, multiply by 1/sum, InclusiveSum) -------------------------
+// Chunks of kCdfChunk leaves per block; all partial results are combined in index order, so the CDF
+// is reproducible bit for bit from run to run.
+constexpr int kCdfThreads = 256;
+constexpr int kCdfItems = 8;
+constexpr int kCdfChunk = kCdfThreads * kCdfItems;
+
+__device__ __forceinline__ float block_sum_ordered(float v, float* smem) {
+    // fixed-shape tree: lanes, then warps in index order
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_down_sync(0xffffffffu, v, o);
+    if (lane_id() == 0) smem[threadIdx.x >> 5] = v;
+    __syncthreads();
+    float t = 0.0f;
+    if (threadIdx.x == 0)
+        for (int w = 0; w < (int)(blockDim.x >> 5); ++w) t += smem[w];
+    __syncthreads();
+    return t;   // valid in thread 0
+}
+
+// partial[b] = sum of scale * w over chunk b (scale read from *scale_ptr when non-null, else 1)
+__global__ void __launch_bounds__(kCdfThreads) cdf_partial_sums_kernel(const float* __restrict__ w, int64_t n,
+                                                                       const float* __restrict__ sum_ptr,
+                                                                       float* __restrict__ partial) {
+    __shared__ float s[kCdfThreads / 32];
+    const float norm = sum_ptr ? 1.0f / __ldg(sum_ptr) : 1.0f;
+    const int64_t base = (int64_t)blockIdx.x * kCdfChunk + (int64_t)threadIdx.x * kCdfItems;
+    float acc = 0.0f;
+#pragma unroll
+    for (int k = 0; k < kCdfItems; ++k)
+        if (base + k < n) acc += sum_ptr ? __ldg(w + base + k) * norm : __ldg(w + base + k);
+    const float t = block_sum_ordered(acc, s);
+    if (threadIdx.x == 0) partial[blockIdx.x] = t;
+}
+
+// One block: total of the partials into *sum_out (when non-null) and their exclusive scan in place.
+__global__ void __launch_bounds__(1024) cdf_scan_partials_kernel(float* __restrict__ partial, int64_t n_chunks,
+                                                                 float* __restrict__ sum_out) {
+    __shared__ float s_warp[33];
+    __shared__ float s_running;
+    if (threadIdx.x == 0) s_running = 0.0f;
+    __syncthreads();
+    for (int64_t base = 0; base < n_chunks; base += 1024) {
+        const int64_t j = base + threadIdx.x;
+        const float v = j < n_chunks ? partial[j] : 0.0f;
+        float inc = v;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const float t = __shfl_up_sync(0xffffffffu, inc, o);
+            if (lane_id() >= (unsigned)o) inc += t;
+        }
+        if (lane_id() == 31) s_warp[threadIdx.x >> 5] = inc;
+        __syncthreads();
+        if (threadIdx.x < 32) {
+            const float wv = s_warp[threadIdx.x];
+            float winc = wv;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const float t = __shfl_up_sync(0xffffffffu, winc, o);
+                if (lane_id() >= (unsigned)o) winc += t;
+            }
+            s_warp[threadIdx.x] = winc - wv;
+            if (threadIdx.x == 31) s_warp[32] = winc;
+        }
+        __syncthreads();
+        const float running = s_running;
+        float excl = __shfl_up_sync(0xffffffffu, inc, 1);
+        if (lane_id() == 0) excl = 0.0f;
+        if (j < n_chunks) partial[j] = running + s_warp[threadIdx.x >> 5] + excl;
+        __syncthreads();
+        if (threadIdx.x == 0) s_running = running + s_warp[32];
+        __syncthreads();
+    }
+    if (threadIdx.x == 0 && sum_out) *sum_out = s_running;
+}
+
+// cdf[i] = chunk base + inclusive scan of w*norm inside the chunk
+__global__ void __launch_bounds__(kCdfThreads) cdf_finalize_kernel(const float* __restrict__ w, int64_t n,
+                                                                   const float* __restrict__ sum_ptr,
+                                                                   const float* __restrict__ chunk_base,
+                                                                   float* __restrict__ cdf) {
+    __shared__ float s_warp[kCdfThreads / 32 + 1];
+    const float norm = 1.0f / __ldg(sum_ptr);
+    const int64_t base = (int64_t)blockIdx.x * kCdfChunk + (int64_t)threadIdx.x * kCdfItems;
+    float v[kCdfItems];
+    float acc = 0.0f;
+#pragma unroll
+    for (int k = 0; k < kCdfItems; ++k) {
+        v[k] = base + k < n ? __ldg(w + base + k) * norm : 0.0f;
+        acc += v[k];
+        v[k] = acc;   // inclusive inside the thread
+    }
+    float inc = acc;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const float t = __shfl_up_sync(0xffffffffu, inc, o);
+        if (lane_id() >= (unsigned)o) inc += t;
+    }
+    if (lane_id() == 31) s_warp[threadIdx.x >> 5] = inc;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float run = 0.0f;
+        for (int wi = 0; wi < kCdfThreads / 32; ++wi) { const float t = s_warp[wi]; s_warp[wi] = run; run += t; }
+    }
+    __syncthreads();
+    float excl = __shfl_up_sync(0xffffffffu, inc, 1);
+    if (lane_id() == 0) excl = 0.0f;
+    const float before = __ldg(chunk_base + blockIdx.x) + s_warp[threadIdx.x >> 5] + excl;
+#pragma unroll
+    for (int k = 0; k < kCdfItems; ++k)
+        if (base + k < n) cdf[base + k] = before + v[k];
+}
+
+// ---- Philox4x32-10 ----------------------------------------------------------------------------
+__device__ __forceinline__ uint4 philox4x32_10(uint4 c, uint2 k) {
+#pragma unroll
+    for (int r = 0; r < 10; ++r) {
+        const unsigned hi0 = __umulhi(0xD2511F53u, c.x), lo0 = 0xD2511F53u * c.x;
+        const unsigned hi1 = __umulhi(0xCD9E8D57u, c.z), lo1 = 0xCD9E8D57u * c.z;
+        c = make_uint4(hi1 ^ c.y ^ k.x, lo1, hi0 ^ c.w ^ k.y, lo0);
+        k.x += 0x9E3779B9u;
+        k.y += 0xBB67AE85u;
+    }
+    return c;
+}
+
+// 23 random mantissa bits -> [0,1), the mapping of include/pcg32.h:105-114
+__device__ __forceinline__ float unit_float(unsigned r) { return __uint_as_float((r >> 9) | 0x3f800000u) - 1.0f; }
+
+struct Draw {
+    float u, jx, jy, jz;
+};
+// stream layout: counter = (slot, attempt, call lo, call hi), key = seed (lo, hi)
+__device__ __forceinline__ Draw philox_draw(unsigned long long seed, unsigned long long call, unsigned slot, unsigned attempt) {
+    const uint4 o = philox4x32_10(make_uint4(slot, attempt, (unsigned)call, (unsigned)(call >> 32)),
+                                  make_uint2((unsigned)seed, (unsigned)(seed >> 32)));
+    Draw d;
+    d.u = unit_float(o.x); d.jx = unit_float(o.y); d.jy = unit_float(o.z); d.jz = unit_float(o.w);
+    return d;
+}
+
+// first index with cdf[idx] >= u, clamped to n-1: include/sampling_utils.h:49-69
+__device__ __forceinline__ unsigned lower_bound_clamped(const float* __restrict__ cdf, float u, unsigned n) {
+    unsigned first = 0, count = n;
+    while (count > 0) {
+        const unsigned step = count >> 1;
+        if (__ldg(cdf + first + step) < u) { first += step + 1; count -= step + 1; }
+        else count = step;
+    }
+    return min(first, n - 1);
+}
+
+__device__ __forceinline__ float leaf_scale(int level, float initial_size) {
+    return 1.0f / scalbnf(1.0f, level) * initial_size;
+}
+
+// ---- training samples: same acceptance test as src/sampling_kernels.cu:98-113 -------------------
+__global__ void __launch_bounds__(kThreads) training_samples_kernel(
+    ViewParams v, unsigned long long seed, unsigned long long call, const float* __restrict__ cdf,
+    const float* __restrict__ sum_ptr, unsigned n_cells, const float* __restrict__ centers, const int* __restrict__ levels,
+    float initial_size, int64_t n_samples, float* __restrict__ positions, long long* __restrict__ indices,
+    volatile unsigned* status) {
+    const int64_t s = (int64_t)blockIdx.x * kThreads + threadIdx.x;
+    if (s >= n_samples) return;
+    if (!(__ldg(sum_ptr) > 0.0f)) {
+        // src/sampling.cu:107-111: zero positions, indices of -1
+        positions[3 * s] = 0.0f; positions[3 * s + 1] = 0.0f; positions[3 * s + 2] = 0.0f;
+        indices[s] = -1;
+        return;
+    }
+    const Rows m = load_rows(v.w2c);
+    unsigned leaf = 0;
+    float x = 0.0f, y = 0.0f, z = 0.0f;
+    bool ok = false;
+    for (unsigned a = 0; a < (unsigned)kMaxAttempts && !ok; ++a) {
+        const Draw d = philox_draw(seed, call, (unsigned)s, a);
+        leaf = lower_bound_clamped(cdf, d.u, n_cells);
+        const float scale = leaf_scale(__ldg(levels + leaf), initial_size);
+        x = fmaf(d.jx - 0.5f, scale, __ldg(centers + 3 * (int64_t)leaf));
+        y = fmaf(d.jy - 0.5f, scale, __ldg(centers + 3 * (int64_t)leaf + 1));
+        z = fmaf(d.jz - 0.5f, scale, __ldg(centers + 3 * (int64_t)leaf + 2));
+        const float vz = m.r2[0] * x + m.r2[1] * y + m.r2[2] * z + m.r2[3];
+        if (vz < v.near_plane || vz > v.far_plane) continue;
+        const float inv_z = 1.0f / (vz + kEps);
+        const float sx = (m.r0[0] * x + m.r0[1] * y + m.r0[2] * z + m.r0[3]) * inv_z * v.fx + v.cx;
+        if (sx < 0.0f || sx >= (float)v.width) continue;
+        const float sy = (m.r1[0] * x + m.r1[1] * y + m.r1[2] * z + m.r1[3]) * inv_z * v.fy + v.cy;
+        if (sy < 0.0f || sy >= (float)v.height) continue;
+        ok = true;
+    }
+    if (!ok) status[STATUS_SAMPLER_EXHAUSTED] = 1u;
+    positions[3 * s] = x; positions[3 * s + 1] = y; positions[3 * s + 2] = z;
+    indices[s] = (long long)leaf;
+}
+
+// ---- unconditional samples: src/sampling_kernels.cu:128-150 with the Philox stream ----------------
+__global__ void __launch_bounds__(kThreads) samples_kernel(unsigned long long seed, unsigned long long call,
+                                                           const float* __restrict__ cdf, unsigned n_cells,
+                                                           const float* __restrict__ centers, const int* __restrict__ levels,
+                                                           float initial_size, int64_t n_samples,
+                                                           float* __restrict__ positions) {
+    const int64_t s = (int64_t)blockIdx.x * kThreads + threadIdx.x;
+    if (s >= n_samples) return;
+    const Draw d = philox_draw(seed, call, (unsigned)s, 0u);
+    const unsigned leaf = lower_bound_clamped(cdf, d.u, n_cells);
+    const float scale = leaf_scale(__ldg(levels + leaf), initial_size);
+    positions[3 * s] = fmaf(d.jx - 0.5f, scale, __ldg(centers + 3 * (int64_t)leaf));
+    positions[3 * s + 1] = fmaf(d.jy - 0.5f, scale, __ldg(centers + 3 * (int64_t)leaf + 1));
+    positions[3 * s + 2] = fmaf(d.jz - 0.5f, scale, __ldg(centers + 3 * (int64_t)leaf + 2));
+}
+
+__global__ void __launch_bounds__(kThreads) draw_leaves_kernel(const float* __restrict__ cdf, unsigned n_cells,
+                                                               const float* __restrict__ u, int64_t n,
+                                                               long long* __restrict__ out) {
+    const int64_t i = (int64_t)blockIdx.x * kThreads + threadIdx.x;
+    if (i >= n) return;
+    out[i] = (long long)lower_bound_clamped(cdf, __ldg(u + i), n_cells);
+}
+
+// ---- expected samples: src/sampling_kernels.cu:152-205 ----------------------------------------
+__global__ void __launch_bounds__(kThreads) sample_counts_kernel(const float* __restrict__ vw, const float* __restrict__ sum_ptr,
+                                                                 unsigned n_samples, int64_t n_cells, unsigned* __restrict__ counts) {
+    const int64_t l = (int64_t)blockIdx.x * kThreads + threadIdx.x;
+    if (l >= n_cells) return;
+    const float w = __ldg(vw + l);
+    const float sum = __ldg(sum_ptr);
+    int c = 0;
+    if (w > 0.0f && sum > 0.0f) {
+        const float norm = 1.0f / sum;
+        c = max(__float2int_rn(w * norm * static_cast<float>(n_samples)), 1);
+    }
+    counts[l] = (unsigned)c;
+}
+
+constexpr int kIScanThreads = 1024;
+// in-place inclusive scan of per-chunk sums is not needed: the counts array is small enough for a
+// two-level scheme (chunk sums by one kernel, one block scans them, one kernel finalises).
+__global__ void __launch_bounds__(kThreads) count_chunk_sums_kernel(const unsigned* __restrict__ counts, int64_t n,
+                                                                    unsigned* __restrict__ chunk_sums) {
+    __shared__ unsigned s[kThreads / 32];
+    const int64_t i = (int64_t)blockIdx.x * kThreads + threadIdx.x;
+    unsigned c = i < n ? counts[i] : 0u;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) c += __shfl_down_sync(0xffffffffu, c, o);
+    if (lane_id() == 0) s[threadIdx.x >> 5] = c;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        unsigned t = 0;
+        for (int w = 0; w < kThreads / 32; ++w) t += s[w];
+        chunk_sums[blockIdx.x] = t;
+    }
+}
+
+__global__ void __launch_bounds__(kIScanThreads) scan_chunk_sums_kernel(unsigned* __restrict__ chunk_sums, int64_t n_chunks,
+                                                                        unsigned long long* __restrict__ total_out) {
+    __shared__ unsigned s_scan[kIScanThreads / 32 + 1];
+    unsigned long long running = 0;
+    for (int64_t base = 0; base < n_chunks; base += kIScanThreads) {
+        const int64_t j = base + threadIdx.x;
+        const unsigned c = j < n_chunks ? chunk_sums[j] : 0u;
+        unsigned total;
+        const unsigned ex = block_exclusive_scan(c, s_scan, &total);
+        if (j < n_chunks) chunk_sums[j] = (unsigned)running + ex;
+        running += total;
+    }
+    if (threadIdx.x == 0) *total_out = running;
+}
+
+// offsets[l] = inclusive prefix of counts (the reference's sample_offsets)
+__global__ void __launch_bounds__(kThreads) count_offsets_kernel(const unsigned* __restrict__ counts, int64_t n,
+                                                                 const unsigned* __restrict__ chunk_base,
+                                                                 unsigned* __restrict__ offsets) {
+    __shared__ unsigned s_scan[kThreads / 32 + 1];
+    const int64_t i = (int64_t)blockIdx.x * kThreads + threadIdx.x;
+    const unsigned c = i < n ? counts[i] : 0u;
+    unsigned total;
+    const unsigned ex = block_exclusive_scan(c, s_scan, &total);
+    if (i < n) offsets[i] = chunk_base[blockIdx.x] + ex + c;
+}
+
+// slot i jitters inside leaf upper_bound(offsets, i % n_created): the load-balanced form of the
+// reference's per-leaf fill loop + gather
+__global__ void __launch_bounds__(kThreads) expected_samples_kernel(unsigned long long seed, unsigned long long call,
+                                                                    const unsigned* __restrict__ offsets, unsigned n_cells,
+                                                                    const float* __restrict__ centers, const int* __restrict__ levels,
+                                                                    float initial_size, int64_t n_total, unsigned n_created,
+                                                                    float* __restrict__ positions) {
+    const int64_t i = (int64_t)blockIdx.x * kThreads + threadIdx.x;
+    if (i >= n_total) return;
+    const unsigned r = (unsigned)(i % n_created);
+    // first leaf whose inclusive offset exceeds r
+    unsigned first = 0, count = n_cells;
+    while (count > 0) {
+        const unsigned step = count >> 1;
+        if (__ldg(offsets + first + step) <= r) { first += step + 1; count -= step + 1; }
+        else count = step;
+    }
+    const unsigned leaf = min(first, n_cells - 1);
+    const Draw d = philox_draw(seed, call, (unsigned)i, 0u);
+    const float scale = leaf_scale(__ldg(levels + leaf), initial_size);
+    positions[3 * i] = fmaf(d.jx - 0.5f, scale, __ldg(centers + 3 * (int64_t)leaf));
+    positions[3 * i + 1] = fmaf(d.jy - 0.5f, scale, __ldg(centers + 3 * (int64_t)leaf + 1));
+    positions[3 * i + 2] = fmaf(d.jz - 0.5f, scale, __ldg(centers + 3 * (int64_t)leaf + 2));
+}
+
+struct SamplerWs {
+    float* vw;          // viewpoint weights (n_cells)
+    float* cdf;         // (n_cells)
+    float* partial;     // per-chunk sums
+    float* sum;         // 1 float (+ padding)
+    unsigned* counts;   // expected-sample counts (n_cells)
+    unsigned* offsets;  // inclusive offsets (n_cells)
+    unsigned* chunk_sums;
+    unsigned long long* total;
+    size_t bytes;
+};
+
+SamplerWs carve_sampler_ws(void* p, int64_t n_cells) {
+    SamplerWs w;
+    Carver c(p);
+    const int64_t n = n_cells > 0 ? n_cells : 1;
+    w.vw = c.take<float>(n);
+    w.cdf = c.take<float>(n);
+    w.partial = c.take<float>(ceil_div<int64_t>(n, kCdfChunk));
+    w.sum = c.take<float>(4);
+    w.counts = c.take<unsigned>(n);
+    w.offsets = c.take<unsigned>(n);
+    w.chunk_sums = c.take<unsigned>(ceil_div<int64_t>(n, kThreads));
+    w.total = c.take<unsigned long long>(2);
+    w.bytes = c.used();
+    return w;
+}
+
+int build_cdf(const float* weights, int64_t n_cells, float* cdf, float* sum_out, float* partial, cudaStream_t stream) {
+    const int64_t chunks = ceil_div<int64_t>(n_cells, kCdfChunk);
+    cdf_partial_sums_kernel<<<(unsigned)chunks, kCdfThreads, 0, stream>>>(weights, n_cells, nullptr, partial);
+    INPC_LAUNCH_CHECK("cdf_partial_sums_kernel");
+    cdf_scan_partials_kernel<<<1, 1024, 0, stream>>>(partial, chunks, sum_out);
+    INPC_LAUNCH_CHECK("cdf_scan_partials_kernel");
+    cdf_partial_sums_kernel<<<(unsigned)chunks, kCdfThreads, 0, stream>>>(weights, n_cells, sum_out, partial);
+    INPC_LAUNCH_CHECK("cdf_partial_sums_kernel(normalised)");
+    cdf_scan_partials_kernel<<<1, 1024, 0, stream>>>(partial, chunks, nullptr);
+    INPC_LAUNCH_CHECK("cdf_scan_partials_kernel(normalised)");
+    cdf_finalize_kernel<<<(unsigned)chunks, kCdfThreads, 0, stream>>>(weights, n_cells, sum_out, partial, cdf);
+    INPC_LAUNCH_CHECK("cdf_finalize_kernel");
+    return INPC_OK;
+}
+
+int check_cells(const inpc_view* view, int64_t n_cells, const void* a, const void* b, const void* c) {
+    if (!view || !view->w2c) { set_error("sampler: view and view.w2c must be non-null"); return INPC_E_INVALID; }
+    if (n_cells <= 0 || n_cells >= ((int64_t)1 << 31)) { set_error("sampler: n_cells=%lld out of range", (long long)n_cells); return INPC_E_INVALID; }
+    if (!a || !b || !c) { set_error("sampler: null leaf array"); return INPC_E_INVALID; }
+    return INPC_OK;
+}
+
+float* pinned_float() {
+    static thread_local float* p = nullptr;
+    if (!p && cudaHostAlloc(reinterpret_cast<void**>(&p), 64, cudaHostAllocDefault) != cudaSuccess) p = nullptr;
+    return p;
+}
+
+}  // namespace
+
+}  // namespace inpc
+
+using namespace inpc;
+
+struct inpc_sampler {
+    unsigned long long seed;
+    unsigned long long counter;
+};
+
+extern "C" inpc_sampler* inpc_sampler_create(int64_t seed) {
+    inpc_sampler* s = new inpc_sampler;
+    s->seed = (unsigned long long)seed;
+    s->counter = 0;
+    return s;
+}
+extern "C" void inpc_sampler_destroy(inpc_sampler* s) { delete s; }
+extern "C" uint64_t inpc_sampler_get_counter(const inpc_sampler* s) { return s ? s->counter : 0; }
+extern "C" void inpc_sampler_set_counter(inpc_sampler* s, uint64_t counter) { if (s) s->counter = counter; }
+
+extern "C" size_t inpc_sampler_workspace_bytes(int64_t n_cells) { return carve_sampler_ws(nullptr, n_cells).bytes; }
+
+extern "C" int inpc_compute_viewpoint_weights(const inpc_view* view, int64_t n_cells, const float* centers,
+                                              const int32_t* levels, const float* weights, float initial_size,
+                                              float* out, void* stream_) {
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    if (n_cells == 0) return INPC_OK;
+    int rc = check_cells(view, n_cells, centers, levels, weights);
+    if (rc != INPC_OK) return rc;
+    if (!out) { set_error("inpc_compute_viewpoint_weights: null output"); return INPC_E_INVALID; }
+    viewpoint_weights_kernel<<<(unsigned)ceil_div<int64_t>(n_cells, kThreads), kThreads, 0, stream>>>(
+        to_params(view), n_cells, centers, levels, weights, initial_size, out);
+    INPC_LAUNCH_CHECK("viewpoint_weights_kernel");
+    return INPC_OK;
+}
+
+extern "C" int inpc_build_cdf(const float* weights, int64_t n_cells, float* cdf, float* sum_out, void* workspace,
+                              void* stream_) {
+    if (n_cells <= 0 || !weights || !cdf || !sum_out || !workspace) { set_error("inpc_build_cdf: bad argument"); return INPC_E_INVALID; }
+    SamplerWs w = carve_sampler_ws(workspace, n_cells);
+    return build_cdf(weights, n_cells, cdf, sum_out, w.partial, static_cast<cudaStream_t>(stream_));
+}
+
+extern "C" int inpc_draw_leaves(const float* cdf, int64_t n_cells, const float* u, int64_t n, int64_t* out, void* stream_) {
+    if (n == 0) return INPC_OK;
+    if (n_cells <= 0 || n_cells >= ((int64_t)1 << 31) || !cdf || !u || !out || n < 0) { set_error("inpc_draw_leaves: bad argument"); return INPC_E_INVALID; }
+    draw_leaves_kernel<<<(unsigned)ceil_div<int64_t>(n, kThreads), kThreads, 0, static_cast<cudaStream_t>(stream_)>>>(
+        cdf, (unsigned)n_cells, u, n, reinterpret_cast<long long*>(out));
+    INPC_LAUNCH_CHECK("draw_leaves_kernel");
+    return INPC_OK;
+}
+
+extern "C" int inpc_generate_training_samples(inpc_sampler* s, const inpc_view* view, int64_t n_cells, const float* centers,
+                                              const int32_t* levels, const float* weights, float initial_size,
+                                              int64_t n_samples, float* positions, int64_t* indices, void* workspace,
+                                              void* stream_) {
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    if (!s) { set_error("null sampler"); return INPC_E_INVALID; }
+    if (n_samples == 0) return INPC_OK;
+    int rc = check_cells(view, n_cells, centers, levels, weights);
+    if (rc != INPC_OK) return rc;
+    if (n_samples < 0 || n_samples >= ((int64_t)1 << 32) || !positions || !indices || !workspace) { set_error("inpc_generate_training_samples: bad argument"); return INPC_E_INVALID; }
+    SamplerWs w = carve_sampler_ws(workspace, n_cells);
+    const ViewParams v = to_params(view);
+    viewpoint_weights_kernel<<<(unsigned)ceil_div<int64_t>(n_cells, kThreads), kThreads, 0, stream>>>(v, n_cells, centers, levels, weights, initial_size, w.vw);
+    INPC_LAUNCH_CHECK("viewpoint_weights_kernel");
+    rc = build_cdf(w.vw, n_cells, w.cdf, w.sum, w.partial, stream);
+    if (rc != INPC_OK) return rc;
+    unsigned* status = device_status_ptr();
+    if (!status) return INPC_E_CUDA;
+    training_samples_kernel<<<(unsigned)ceil_div<int64_t>(n_samples, kThreads), kThreads, 0, stream>>>(
+        v, s->seed, s->counter, w.cdf, w.sum, (unsigned)n_cells, centers, levels, initial_size, n_samples, positions,
+        reinterpret_cast<long long*>(indices), status);
+    INPC_LAUNCH_CHECK("training_samples_kernel");
+    s->counter += 1;
+    return INPC_OK;
+}
+
+extern "C" int inpc_generate_samples(inpc_sampler* s, const inpc_view* view, int64_t n_cells, const float* centers,
+                                     const int32_t* levels, const float* weights, float initial_size, int64_t n_samples,
+                                     float* positions, int64_t* n_written, void* workspace, void* stream_) {
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    if (!s || !n_written) { set_error("null sampler or n_written"); return INPC_E_INVALID; }
+    *n_written = 0;
+    int rc = check_cells(view, n_cells, centers, levels, weights);
+    if (rc != INPC_OK) return rc;
+    if (n_samples < 0 || n_samples >= ((int64_t)1 << 32) || !workspace || (n_samples > 0 && !positions)) { set_error("inpc_generate_samples: bad argument"); return INPC_E_INVALID; }
+    SamplerWs w = carve_sampler_ws(workspace, n_cells);
+    const ViewParams v = to_params(view);
+    viewpoint_weights_kernel<<<(unsigned)ceil_div<int64_t>(n_cells, kThreads), kThreads, 0, stream>>>(v, n_cells, centers, levels, weights, initial_size, w.vw);
+    INPC_LAUNCH_CHECK("viewpoint_weights_kernel");
+    rc = build_cdf(w.vw, n_cells, w.cdf, w.sum, w.partial, stream);
+    if (rc != INPC_OK) return rc;
+    float* host = pinned_float();
+    if (!host) return cuda_fail(cudaGetLastError(), "cudaHostAlloc");
+    INPC_CUDA_TRY(cudaMemcpyAsync(host, w.sum, sizeof(float), cudaMemcpyDeviceToHost, stream));
+    INPC_CUDA_TRY(cudaStreamSynchronize(stream));
+    if (!(host[0] > 0.0f)) return INPC_OK;   // src/sampling_api.cu:154: empty result
+    if (n_samples > 0) {
+        samples_kernel<<<(unsigned)ceil_div<int64_t>(n_samples, kThreads), kThreads, 0, stream>>>(
+            s->seed, s->counter, w.cdf, (unsigned)n_cells, centers, levels, initial_size, n_samples, positions);
+        INPC_LAUNCH_CHECK("samples_kernel");
+    }
+    s->counter += 1;
+    *n_written = n_samples;
+    return INPC_OK;
+}
+
+extern "C" int inpc_generate_expected_samples_count(inpc_sampler* s, const inpc_view* view, int64_t n_cells,
+                                                    const float* centers, const int32_t* levels, const float* weights,
+                                                    float initial_size, int64_t n_samples, int64_t* n_created,
+                                                    void* workspace, void* stream_) {
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    if (!s || !n_created) { set_error("null sampler or n_created"); return INPC_E_INVALID; }
+    *n_created = 0;
+    int rc = check_cells(view, n_cells, centers, levels, weights);
+    if (rc != INPC_OK) return rc;
+    if (n_samples < 0 || n_samples >= ((int64_t)1 << 32) || !workspace) { set_error("inpc_generate_expected_samples_count: bad argument"); return INPC_E_INVALID; }
+    SamplerWs w = carve_sampler_ws(workspace, n_cells);
+    const ViewParams v = to_params(view);
+    const unsigned blocks = (unsigned)ceil_div<int64_t>(n_cells, kThreads);
+    viewpoint_weights_kernel<<<blocks, kThreads, 0, stream>>>(v, n_cells, centers, levels, weights, initial_size, w.vw);
+    INPC_LAUNCH_CHECK("viewpoint_weights_kernel");
+    const int64_t chunks = ceil_div<int64_t>(n_cells, kCdfChunk);
+    cdf_partial_sums_kernel<<<(unsigned)chunks, kCdfThreads, 0, stream>>>(w.vw, n_cells, nullptr, w.partial);
+    INPC_LAUNCH_CHECK("cdf_partial_sums_kernel");
+    cdf_scan_partials_kernel<<<1, 1024, 0, stream>>>(w.partial, chunks, w.sum);
+    INPC_LAUNCH_CHECK("cdf_scan_partials_kernel");
+    sample_counts_kernel<<<blocks, kThreads, 0, stream>>>(w.vw, w.sum, (unsigned)n_samples, n_cells, w.counts);
+    INPC_LAUNCH_CHECK("sample_counts_kernel");
+    count_chunk_sums_kernel<<<blocks, kThreads, 0, stream>>>(w.counts, n_cells, w.chunk_sums);
+    INPC_LAUNCH_CHECK("count_chunk_sums_kernel");
+    scan_chunk_sums_kernel<<<1, kIScanThreads, 0, stream>>>(w.chunk_sums, blocks, w.total);
+    INPC_LAUNCH_CHECK("scan_chunk_sums_kernel");
+    count_offsets_kernel<<<blocks, kThreads, 0, stream>>>(w.counts, n_cells, w.chunk_sums, w.offsets);
+    INPC_LAUNCH_CHECK("count_offsets_kernel");
+    unsigned long long* host = reinterpret_cast<unsigned long long*>(pinned_float());
+    if (!host) return cuda_fail(cudaGetLastError(), "cudaHostAlloc");
+    INPC_CUDA_TRY(cudaMemcpyAsync(host, w.total, sizeof(unsigned long long), cudaMemcpyDeviceToHost, stream));
+    INPC_CUDA_TRY(cudaStreamSynchronize(stream));
+    if (host[0] >= (1ull << 32)) { set_error("expected sample count %llu exceeds 2^32", host[0]); return INPC_E_CAPACITY; }
+    *n_created = (int64_t)host[0];
+    return INPC_OK;
+}
+
+extern "C" int inpc_generate_expected_samples_fill(inpc_sampler* s, int64_t n_cells, const float* centers,
+                                                   const int32_t* levels, float initial_size, int64_t n_created,
+                                                   int64_t n_multi, float* positions, void* workspace, void* stream_) {
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    if (!s) { set_error("null sampler"); return INPC_E_INVALID; }
+    const int64_t total = n_created * n_multi;
+    if (n_cells <= 0 || n_created <= 0 || n_multi <= 0 || total >= ((int64_t)1 << 32) || !centers || !levels || !positions || !workspace) {
+        set_error("inpc_generate_expected_samples_fill: bad argument");
+        return INPC_E_INVALID;
+    }
+    SamplerWs w = carve_sampler_ws(workspace, n_cells);
+    expected_samples_kernel<<<(unsigned)ceil_div<int64_t>(total, kThreads), kThreads, 0, stream>>>(
+        s->seed, s->counter, w.offsets, (unsigned)n_cells, centers, levels, initial_size, total, (unsigned)n_created, positions);
+    INPC_LAUNCH_CHECK("expected_samples_kernel");
+    s->counter += 1;
+    return INPC_OK;
+}
