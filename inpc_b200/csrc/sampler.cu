@@ -27,13 +27,19 @@ __device__ __forceinline__ Rows load_rows(const float* __restrict__ w2c) {
     return m;
 }
 
+// All sampler arithmetic spells out its fused multiply-adds, so that the CPU restatement used by the
+// tests reproduces every value bit for bit.
+__device__ __forceinline__ float affine(const float* r, float x, float y, float z) {
+    return fmaf(r[2], z, fmaf(r[1], y, fmaf(r[0], x, r[3])));
+}
+
 __device__ __forceinline__ bool in_frustum(const Rows& m, const ViewParams& v, float px, float py, float pz, float* z_out) {
-    const float vx = m.r0[0] * px + m.r0[1] * py + m.r0[2] * pz + m.r0[3];
-    const float vy = m.r1[0] * px + m.r1[1] * py + m.r1[2] * pz + m.r1[3];
-    const float z = m.r2[0] * px + m.r2[1] * py + m.r2[2] * pz + m.r2[3];
+    const float vx = affine(m.r0, px, py, pz);
+    const float vy = affine(m.r1, px, py, pz);
+    const float z = affine(m.r2, px, py, pz);
     const float inv_z = 1.0f / (z + kEps);
-    const float x = vx * inv_z * v.fx + v.cx;
-    const float y = vy * inv_z * v.fy + v.cy;
+    const float x = fmaf(vx * inv_z, v.fx, v.cx);
+    const float y = fmaf(vy * inv_z, v.fy, v.cy);
     if (z_out) *z_out = z;
     return (z >= v.near_plane) & (z <= v.far_plane) & (x >= 0.0f) & (x < (float)v.width) & (y >= 0.0f) & (y < (float)v.height);
 }
@@ -55,129 +61,134 @@ __global__ void __launch_bounds__(kThreads) viewpoint_weights_kernel(ViewParams 
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
             const float ox = (k & 4) ? 1.0f : -1.0f, oy = (k & 2) ? 1.0f : -1.0f, oz = (k & 1) ? 1.0f : -1.0f;
-            valid |= in_frustum(m, v, cx + half_size * ox, cy + half_size * oy, cz + half_size * oz, nullptr);
+            valid |= in_frustum(m, v, fmaf(half_size, ox, cx), fmaf(half_size, oy, cy), fmaf(half_size, oz, cz), nullptr);
         }
     }
     float w = 0.0f;
     if (valid) {
         const float depth_scale = fmaxf(fabsf(z - v.near_plane) / v.far_plane, kEps);
-        const float size_scale = exp2f(static_cast<float>(level) * 0.5f);
+        // 2^(level/2), exact: the reference's exp2f(level * 0.5f) agrees to within the 2 ulp of exp2f
+        const float size_scale = scalbnf((level & 1) ? 1.41421356237309504880f : 1.0f, level >> 1);
         w = 1.0f / (depth_scale * size_scale) * __ldg(weights + l);
     }
     out[l] = w;
 }
 
 // ---- CDF: src/sampling.cu:97-125 (Sum, multiply by 1/sum, InclusiveSum) -------------------------
-// Chunks of kCdfChunk leaves per block; all partial results are combined in index order, so the CDF
-// is reproducible bit for bit from run to run.
+// The reference scans fp32 values with CUB, whose summation order is unspecified.  Here every weight
+// is first expressed as a 39-bit fixed-point fraction of the largest weight; integer prefix sums are
+// exact and associative, so the CDF is independent of how the scan is parallelised, monotone, and
+// reproducible bit for bit anywhere (the CPU restatement is a plain loop):
+//   q_i = trunc(w_i / w_max * 2^39),  P_i = q_0 + ... + q_i,  cdf_i = float(P_i / P_last),
+//   sum = float(P_last * 2^-39 * w_max).
 constexpr int kCdfThreads = 256;
 constexpr int kCdfItems = 8;
 constexpr int kCdfChunk = kCdfThreads * kCdfItems;
+constexpr float kFixedOne = 549755813888.0f;   // 2^39
+constexpr double kFixedInv = 1.0 / 549755813888.0;
 
-__device__ __forceinline__ float block_sum_ordered(float v, float* smem) {
-    // fixed-shape tree: lanes, then warps in index order
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) v += __shfl_down_sync(0xffffffffu, v, o);
-    if (lane_id() == 0) smem[threadIdx.x >> 5] = v;
-    __syncthreads();
-    float t = 0.0f;
-    if (threadIdx.x == 0)
-        for (int w = 0; w < (int)(blockDim.x >> 5); ++w) t += smem[w];
-    __syncthreads();
-    return t;   // valid in thread 0
+__device__ __forceinline__ unsigned long long to_fixed(float w, float w_max) {
+    return w > 0.0f ? (unsigned long long)((w / w_max) * kFixedOne) : 0ull;
 }
 
-// partial[b] = sum of scale * w over chunk b (scale read from *scale_ptr when non-null, else 1)
-__global__ void __launch_bounds__(kCdfThreads) cdf_partial_sums_kernel(const float* __restrict__ w, int64_t n,
-                                                                       const float* __restrict__ sum_ptr,
-                                                                       float* __restrict__ partial) {
-    __shared__ float s[kCdfThreads / 32];
-    const float norm = sum_ptr ? 1.0f / __ldg(sum_ptr) : 1.0f;
+// largest weight via atomicMax on the bit pattern (valid for non-negative floats; order-free)
+__global__ void __launch_bounds__(kCdfThreads) cdf_max_kernel(const float* __restrict__ w, int64_t n, unsigned* __restrict__ max_bits) {
     const int64_t base = (int64_t)blockIdx.x * kCdfChunk + (int64_t)threadIdx.x * kCdfItems;
-    float acc = 0.0f;
+    float m = 0.0f;
 #pragma unroll
     for (int k = 0; k < kCdfItems; ++k)
-        if (base + k < n) acc += sum_ptr ? __ldg(w + base + k) * norm : __ldg(w + base + k);
-    const float t = block_sum_ordered(acc, s);
-    if (threadIdx.x == 0) partial[blockIdx.x] = t;
+        if (base + k < n) m = fmaxf(m, __ldg(w + base + k));
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_down_sync(0xffffffffu, m, o));
+    if (lane_id() == 0 && m > 0.0f) atomicMax(max_bits, __float_as_uint(m));
 }
 
-// One block: total of the partials into *sum_out (when non-null) and their exclusive scan in place.
-__global__ void __launch_bounds__(1024) cdf_scan_partials_kernel(float* __restrict__ partial, int64_t n_chunks,
-                                                                 float* __restrict__ sum_out) {
-    __shared__ float s_warp[33];
-    __shared__ float s_running;
-    if (threadIdx.x == 0) s_running = 0.0f;
-    __syncthreads();
-    for (int64_t base = 0; base < n_chunks; base += 1024) {
-        const int64_t j = base + threadIdx.x;
-        const float v = j < n_chunks ? partial[j] : 0.0f;
-        float inc = v;
-#pragma unroll
-        for (int o = 1; o < 32; o <<= 1) {
-            const float t = __shfl_up_sync(0xffffffffu, inc, o);
-            if (lane_id() >= (unsigned)o) inc += t;
-        }
-        if (lane_id() == 31) s_warp[threadIdx.x >> 5] = inc;
-        __syncthreads();
-        if (threadIdx.x < 32) {
-            const float wv = s_warp[threadIdx.x];
-            float winc = wv;
-#pragma unroll
-            for (int o = 1; o < 32; o <<= 1) {
-                const float t = __shfl_up_sync(0xffffffffu, winc, o);
-                if (lane_id() >= (unsigned)o) winc += t;
-            }
-            s_warp[threadIdx.x] = winc - wv;
-            if (threadIdx.x == 31) s_warp[32] = winc;
-        }
-        __syncthreads();
-        const float running = s_running;
-        float excl = __shfl_up_sync(0xffffffffu, inc, 1);
-        if (lane_id() == 0) excl = 0.0f;
-        if (j < n_chunks) partial[j] = running + s_warp[threadIdx.x >> 5] + excl;
-        __syncthreads();
-        if (threadIdx.x == 0) s_running = running + s_warp[32];
-        __syncthreads();
-    }
-    if (threadIdx.x == 0 && sum_out) *sum_out = s_running;
-}
-
-// cdf[i] = chunk base + inclusive scan of w*norm inside the chunk
-__global__ void __launch_bounds__(kCdfThreads) cdf_finalize_kernel(const float* __restrict__ w, int64_t n,
-                                                                   const float* __restrict__ sum_ptr,
-                                                                   const float* __restrict__ chunk_base,
-                                                                   float* __restrict__ cdf) {
-    __shared__ float s_warp[kCdfThreads / 32 + 1];
-    const float norm = 1.0f / __ldg(sum_ptr);
-    const int64_t base = (int64_t)blockIdx.x * kCdfChunk + (int64_t)threadIdx.x * kCdfItems;
-    float v[kCdfItems];
-    float acc = 0.0f;
-#pragma unroll
-    for (int k = 0; k < kCdfItems; ++k) {
-        v[k] = base + k < n ? __ldg(w + base + k) * norm : 0.0f;
-        acc += v[k];
-        v[k] = acc;   // inclusive inside the thread
-    }
-    float inc = acc;
+__device__ __forceinline__ unsigned long long warp_inclusive_scan_u64(unsigned long long v) {
 #pragma unroll
     for (int o = 1; o < 32; o <<= 1) {
-        const float t = __shfl_up_sync(0xffffffffu, inc, o);
-        if (lane_id() >= (unsigned)o) inc += t;
+        const unsigned long long t = __shfl_up_sync(0xffffffffu, v, o);
+        if (lane_id() >= (unsigned)o) v += t;
     }
-    if (lane_id() == 31) s_warp[threadIdx.x >> 5] = inc;
+    return v;
+}
+
+// exclusive scan of one u64 per thread over the block; smem needs blockDim/32 + 1 entries
+__device__ __forceinline__ unsigned long long block_exclusive_scan_u64(unsigned long long v, unsigned long long* smem,
+                                                                     unsigned long long* total) {
+    const unsigned lane = lane_id(), warp = threadIdx.x >> 5, nwarps = (blockDim.x + 31) >> 5;
+    const unsigned long long inc = warp_inclusive_scan_u64(v);
+    if (lane == 31) smem[warp] = inc;
     __syncthreads();
-    if (threadIdx.x == 0) {
-        float run = 0.0f;
-        for (int wi = 0; wi < kCdfThreads / 32; ++wi) { const float t = s_warp[wi]; s_warp[wi] = run; run += t; }
+    if (warp == 0) {
+        const unsigned long long wv = lane < nwarps ? smem[lane] : 0ull;
+        const unsigned long long winc = warp_inclusive_scan_u64(wv);
+        if (lane < nwarps) smem[lane] = winc - wv;
+        if (lane == 31) smem[nwarps] = winc;
     }
     __syncthreads();
-    float excl = __shfl_up_sync(0xffffffffu, inc, 1);
-    if (lane_id() == 0) excl = 0.0f;
-    const float before = __ldg(chunk_base + blockIdx.x) + s_warp[threadIdx.x >> 5] + excl;
+    const unsigned long long r = smem[warp] + inc - v;
+    *total = smem[nwarps];
+    __syncthreads();
+    return r;
+}
+
+__global__ void __launch_bounds__(kCdfThreads) cdf_chunk_sums_kernel(const float* __restrict__ w, int64_t n,
+                                                                     const unsigned* __restrict__ max_bits,
+                                                                     unsigned long long* __restrict__ chunk_sums) {
+    __shared__ unsigned long long s[kCdfThreads / 32 + 1];
+    const float w_max = __uint_as_float(__ldg(max_bits));
+    const int64_t base = (int64_t)blockIdx.x * kCdfChunk + (int64_t)threadIdx.x * kCdfItems;
+    unsigned long long acc = 0;
 #pragma unroll
     for (int k = 0; k < kCdfItems; ++k)
-        if (base + k < n) cdf[base + k] = before + v[k];
+        if (base + k < n) acc += to_fixed(__ldg(w + base + k), w_max);
+    unsigned long long total;
+    block_exclusive_scan_u64(acc, s, &total);
+    if (threadIdx.x == 0) chunk_sums[blockIdx.x] = total;
+}
+
+// one block: exclusive scan of the chunk sums in place; total -> *total_out, fp32 sum -> *sum_out
+__global__ void __launch_bounds__(1024) cdf_scan_chunks_kernel(unsigned long long* __restrict__ chunk_sums, int64_t n_chunks,
+                                                               const unsigned* __restrict__ max_bits,
+                                                               unsigned long long* __restrict__ total_out,
+                                                               float* __restrict__ sum_out) {
+    __shared__ unsigned long long s[1024 / 32 + 1];
+    unsigned long long running = 0;
+    for (int64_t base = 0; base < n_chunks; base += 1024) {
+        const int64_t j = base + threadIdx.x;
+        const unsigned long long c = j < n_chunks ? chunk_sums[j] : 0ull;
+        unsigned long long total;
+        const unsigned long long ex = block_exclusive_scan_u64(c, s, &total);
+        if (j < n_chunks) chunk_sums[j] = running + ex;
+        running += total;
+    }
+    if (threadIdx.x == 0) {
+        *total_out = running;
+        *sum_out = (float)((double)running * kFixedInv * (double)__uint_as_float(*max_bits));
+    }
+}
+
+__global__ void __launch_bounds__(kCdfThreads) cdf_finalize_kernel(const float* __restrict__ w, int64_t n,
+                                                                   const unsigned* __restrict__ max_bits,
+                                                                   const unsigned long long* __restrict__ chunk_base,
+                                                                   const unsigned long long* __restrict__ total_ptr,
+                                                                   float* __restrict__ cdf) {
+    __shared__ unsigned long long s[kCdfThreads / 32 + 1];
+    const float w_max = __uint_as_float(__ldg(max_bits));
+    const double total = (double)__ldg(total_ptr);
+    const int64_t base = (int64_t)blockIdx.x * kCdfChunk + (int64_t)threadIdx.x * kCdfItems;
+    unsigned long long q[kCdfItems];
+    unsigned long long acc = 0;
+#pragma unroll
+    for (int k = 0; k < kCdfItems; ++k) {
+        acc += base + k < n ? to_fixed(__ldg(w + base + k), w_max) : 0ull;
+        q[k] = acc;
+    }
+    unsigned long long block_total;
+    const unsigned long long before = __ldg(chunk_base + blockIdx.x) + block_exclusive_scan_u64(acc, s, &block_total);
+#pragma unroll
+    for (int k = 0; k < kCdfItems; ++k)
+        if (base + k < n) cdf[base + k] = (float)((double)(before + q[k]) / total);
 }
 
 // ---- Philox4x32-10 ----------------------------------------------------------------------------
@@ -248,12 +259,12 @@ __global__ void __launch_bounds__(kThreads) training_samples_kernel(
         x = fmaf(d.jx - 0.5f, scale, __ldg(centers + 3 * (int64_t)leaf));
         y = fmaf(d.jy - 0.5f, scale, __ldg(centers + 3 * (int64_t)leaf + 1));
         z = fmaf(d.jz - 0.5f, scale, __ldg(centers + 3 * (int64_t)leaf + 2));
-        const float vz = m.r2[0] * x + m.r2[1] * y + m.r2[2] * z + m.r2[3];
+        const float vz = affine(m.r2, x, y, z);
         if (vz < v.near_plane || vz > v.far_plane) continue;
         const float inv_z = 1.0f / (vz + kEps);
-        const float sx = (m.r0[0] * x + m.r0[1] * y + m.r0[2] * z + m.r0[3]) * inv_z * v.fx + v.cx;
+        const float sx = fmaf(affine(m.r0, x, y, z) * inv_z, v.fx, v.cx);
         if (sx < 0.0f || sx >= (float)v.width) continue;
-        const float sy = (m.r1[0] * x + m.r1[1] * y + m.r1[2] * z + m.r1[3]) * inv_z * v.fy + v.cy;
+        const float sy = fmaf(affine(m.r1, x, y, z) * inv_z, v.fy, v.cy);
         if (sy < 0.0f || sy >= (float)v.height) continue;
         ok = true;
     }
@@ -375,7 +386,9 @@ __global__ void __launch_bounds__(kThreads) expected_samples_kernel(unsigned lon
 struct SamplerWs {
     float* vw;          // viewpoint weights (n_cells)
     float* cdf;         // (n_cells)
-    float* partial;     // per-chunk sums
+    unsigned long long* chunk_sums64;   // fixed-point chunk sums / bases
+    unsigned long long* total64;        // fixed-point total
+    unsigned* max_bits;                 // bit pattern of the largest weight
     float* sum;         // 1 float (+ padding)
     unsigned* counts;   // expected-sample counts (n_cells)
     unsigned* offsets;  // inclusive offsets (n_cells)
@@ -390,7 +403,9 @@ SamplerWs carve_sampler_ws(void* p, int64_t n_cells) {
     const int64_t n = n_cells > 0 ? n_cells : 1;
     w.vw = c.take<float>(n);
     w.cdf = c.take<float>(n);
-    w.partial = c.take<float>(ceil_div<int64_t>(n, kCdfChunk));
+    w.chunk_sums64 = c.take<unsigned long long>(ceil_div<int64_t>(n, kCdfChunk));
+    w.total64 = c.take<unsigned long long>(2);
+    w.max_bits = c.take<unsigned>(4);
     w.sum = c.take<float>(4);
     w.counts = c.take<unsigned>(n);
     w.offsets = c.take<unsigned>(n);
@@ -400,18 +415,20 @@ SamplerWs carve_sampler_ws(void* p, int64_t n_cells) {
     return w;
 }
 
-int build_cdf(const float* weights, int64_t n_cells, float* cdf, float* sum_out, float* partial, cudaStream_t stream) {
+// weight sum only (expected-sample mode) or sum + CDF
+int build_cdf(const float* weights, int64_t n_cells, float* cdf, float* sum_out, const SamplerWs& w, cudaStream_t stream) {
     const int64_t chunks = ceil_div<int64_t>(n_cells, kCdfChunk);
-    cdf_partial_sums_kernel<<<(unsigned)chunks, kCdfThreads, 0, stream>>>(weights, n_cells, nullptr, partial);
-    INPC_LAUNCH_CHECK("cdf_partial_sums_kernel");
-    cdf_scan_partials_kernel<<<1, 1024, 0, stream>>>(partial, chunks, sum_out);
-    INPC_LAUNCH_CHECK("cdf_scan_partials_kernel");
-    cdf_partial_sums_kernel<<<(unsigned)chunks, kCdfThreads, 0, stream>>>(weights, n_cells, sum_out, partial);
-    INPC_LAUNCH_CHECK("cdf_partial_sums_kernel(normalised)");
-    cdf_scan_partials_kernel<<<1, 1024, 0, stream>>>(partial, chunks, nullptr);
-    INPC_LAUNCH_CHECK("cdf_scan_partials_kernel(normalised)");
-    cdf_finalize_kernel<<<(unsigned)chunks, kCdfThreads, 0, stream>>>(weights, n_cells, sum_out, partial, cdf);
-    INPC_LAUNCH_CHECK("cdf_finalize_kernel");
+    INPC_CUDA_TRY(cudaMemsetAsync(w.max_bits, 0, sizeof(unsigned), stream));
+    cdf_max_kernel<<<(unsigned)chunks, kCdfThreads, 0, stream>>>(weights, n_cells, w.max_bits);
+    INPC_LAUNCH_CHECK("cdf_max_kernel");
+    cdf_chunk_sums_kernel<<<(unsigned)chunks, kCdfThreads, 0, stream>>>(weights, n_cells, w.max_bits, w.chunk_sums64);
+    INPC_LAUNCH_CHECK("cdf_chunk_sums_kernel");
+    cdf_scan_chunks_kernel<<<1, 1024, 0, stream>>>(w.chunk_sums64, chunks, w.max_bits, w.total64, sum_out);
+    INPC_LAUNCH_CHECK("cdf_scan_chunks_kernel");
+    if (cdf) {
+        cdf_finalize_kernel<<<(unsigned)chunks, kCdfThreads, 0, stream>>>(weights, n_cells, w.max_bits, w.chunk_sums64, w.total64, cdf);
+        INPC_LAUNCH_CHECK("cdf_finalize_kernel");
+    }
     return INPC_OK;
 }
 
@@ -469,7 +486,7 @@ extern "C" int inpc_build_cdf(const float* weights, int64_t n_cells, float* cdf,
                               void* stream_) {
     if (n_cells <= 0 || !weights || !cdf || !sum_out || !workspace) { set_error("inpc_build_cdf: bad argument"); return INPC_E_INVALID; }
     SamplerWs w = carve_sampler_ws(workspace, n_cells);
-    return build_cdf(weights, n_cells, cdf, sum_out, w.partial, static_cast<cudaStream_t>(stream_));
+    return build_cdf(weights, n_cells, cdf, sum_out, w, static_cast<cudaStream_t>(stream_));
 }
 
 extern "C" int inpc_draw_leaves(const float* cdf, int64_t n_cells, const float* u, int64_t n, int64_t* out, void* stream_) {
@@ -495,7 +512,7 @@ extern "C" int inpc_generate_training_samples(inpc_sampler* s, const inpc_view* 
     const ViewParams v = to_params(view);
     viewpoint_weights_kernel<<<(unsigned)ceil_div<int64_t>(n_cells, kThreads), kThreads, 0, stream>>>(v, n_cells, centers, levels, weights, initial_size, w.vw);
     INPC_LAUNCH_CHECK("viewpoint_weights_kernel");
-    rc = build_cdf(w.vw, n_cells, w.cdf, w.sum, w.partial, stream);
+    rc = build_cdf(w.vw, n_cells, w.cdf, w.sum, w, stream);
     if (rc != INPC_OK) return rc;
     unsigned* status = device_status_ptr();
     if (!status) return INPC_E_CUDA;
@@ -520,7 +537,7 @@ extern "C" int inpc_generate_samples(inpc_sampler* s, const inpc_view* view, int
     const ViewParams v = to_params(view);
     viewpoint_weights_kernel<<<(unsigned)ceil_div<int64_t>(n_cells, kThreads), kThreads, 0, stream>>>(v, n_cells, centers, levels, weights, initial_size, w.vw);
     INPC_LAUNCH_CHECK("viewpoint_weights_kernel");
-    rc = build_cdf(w.vw, n_cells, w.cdf, w.sum, w.partial, stream);
+    rc = build_cdf(w.vw, n_cells, w.cdf, w.sum, w, stream);
     if (rc != INPC_OK) return rc;
     float* host = pinned_float();
     if (!host) return cuda_fail(cudaGetLastError(), "cudaHostAlloc");
@@ -552,11 +569,8 @@ extern "C" int inpc_generate_expected_samples_count(inpc_sampler* s, const inpc_
     const unsigned blocks = (unsigned)ceil_div<int64_t>(n_cells, kThreads);
     viewpoint_weights_kernel<<<blocks, kThreads, 0, stream>>>(v, n_cells, centers, levels, weights, initial_size, w.vw);
     INPC_LAUNCH_CHECK("viewpoint_weights_kernel");
-    const int64_t chunks = ceil_div<int64_t>(n_cells, kCdfChunk);
-    cdf_partial_sums_kernel<<<(unsigned)chunks, kCdfThreads, 0, stream>>>(w.vw, n_cells, nullptr, w.partial);
-    INPC_LAUNCH_CHECK("cdf_partial_sums_kernel");
-    cdf_scan_partials_kernel<<<1, 1024, 0, stream>>>(w.partial, chunks, w.sum);
-    INPC_LAUNCH_CHECK("cdf_scan_partials_kernel");
+    rc = build_cdf(w.vw, n_cells, nullptr, w.sum, w, stream);
+    if (rc != INPC_OK) return rc;
     sample_counts_kernel<<<blocks, kThreads, 0, stream>>>(w.vw, w.sum, (unsigned)n_samples, n_cells, w.counts);
     INPC_LAUNCH_CHECK("sample_counts_kernel");
     count_chunk_sums_kernel<<<blocks, kThreads, 0, stream>>>(w.counts, n_cells, w.chunk_sums);

@@ -46,7 +46,7 @@ def adaptive_octree(n_leaves: int, seed: int, min_level: int = 6, max_level: int
     depth = max_level - min_level
     # expected leaves per start cell when half the cells split at each of `depth` levels
     per_cell = sum(0.5 * 4 ** k for k in range(depth)) + 4 ** depth
-    n_start = int(math.ceil(n_leaves / per_cell * 1.02)) + 1
+    n_start = int(math.ceil(n_leaves / per_cell * 1.01)) + 2
     r = 2 ** min_level
     n_start = min(n_start, r ** 3)
     start = torch.randperm(r ** 3, generator=g)[:n_start]
@@ -55,7 +55,8 @@ def adaptive_octree(n_leaves: int, seed: int, min_level: int = 6, max_level: int
     done_ijk, done_lv = [], []
     offs = torch.tensor([[a, b, c] for a in (0, 1) for b in (0, 1) for c in (0, 1)], dtype=torch.int64)
     for level in range(min_level, max_level):
-        split = torch.rand(ijk.shape[0], generator=g) < 0.5
+        split = torch.zeros(ijk.shape[0], dtype=torch.bool)
+        split[torch.randperm(ijk.shape[0], generator=g)[:(ijk.shape[0] + 1) // 2]] = True
         done_ijk.append(ijk[~split])
         done_lv.append(lv[~split])
         parents = ijk[split]
