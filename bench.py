@@ -1,0 +1,449 @@
+#!/usr/bin/env python
+"""Benchmark of the INPC hot path (sample -> project/bin -> sort -> blend, forward + backward).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+One *step* is one batch of 64 camera views on a radius-3 orbit, every view being the single-view
+training workload (2^18-leaf octree, 2^23 sampled points, 36 fp16 SH coefficients + fp32 opacity per
+point, 1237x822, forward and backward).  The batch is sharded by view over the ranks (one process
+per GPU, torchrun); per step the ranks exchange two fp32 buffers with NCCL all-reduce.  Rank 0
+prints ONE JSON line.
+
+  value  fwd+bwd Mpoints/s of the whole job, inputs resident in HBM, CUDA events, max over ranks
+  e2e    the same through the public Python API with, per view, the camera and the upstream image
+         gradient copied from pinned host memory and the loss read back
+  roofline      dominant kernel's algorithmic bytes / measured launch time against the measured HBM peak
+  cpu_baseline  the CPU restatement (oracle/, all host cores) on a bounded sample; reported only
+
+`--impl reference` runs the reference's own CUDA backend (oracle/_ref, compiled unmodified from the
+reference tree) on the same workload on one GPU; without that library it times the CPU restatement
+on a bounded sample instead.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+METRIC = "fwd+bwd Mpoints/s at 2^23 points per view, 1237x822"
+UNIT = "Mpoints/s"
+N_VIEWS = 64
+N_POINTS = 1 << 23
+N_LEAVES = 1 << 18
+N_APPEARANCE = 1 << 22
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=3)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--views", type=int, default=N_VIEWS)
+    ap.add_argument("--points", type=int, default=N_POINTS)
+    ap.add_argument("--tile", type=int, default=16)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    return ap.parse_args()
+
+
+# ---------------------------------------------------------------------------------------------------
+class ClockSampler:
+    """Samples SM clocks and throttle reasons of one GPU with nvidia-smi while the timed region runs."""
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.lines: list[str] = []
+        self.proc = None
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100",
+                                          "-i", str(gpu_index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._pump, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.proc = None
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for line in self.lines:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 7:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[3:7]):
+                if val.lower() == "active":
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def dist_setup(args):
+    import torch
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world > 1:
+        import torch.distributed as dist
+        torch.cuda.set_device(local)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    else:
+        torch.cuda.set_device(0)
+        local = 0
+    return rank, local, world
+
+
+def barrier(world):
+    import torch
+    if world > 1:
+        import torch.distributed as dist
+        dist.barrier()
+    torch.cuda.synchronize()
+
+
+def max_over_ranks(value: float, world: int, device) -> float:
+    import torch
+    if world == 1:
+        return value
+    import torch.distributed as dist
+    t = torch.tensor([value], dtype=torch.float64, device=device)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def build_workload(args, device):
+    import torch
+    from inpc_b200 import synthetic as syn
+    cfg = syn.config1(n_samples=args.points, n_leaves=N_LEAVES)
+    views = syn.config3_views(args.views)
+    g = torch.Generator().manual_seed(5)
+    H, W = views[0].camera.height, views[0].camera.width
+    grad_image = torch.randn((4, H, W), generator=g) * 1e-3
+    grad_alpha = torch.randn((1, H, W), generator=g) * 1e-3
+    return dict(tree=cfg["tree"].to(device), features=cfg["features"].to(device), opacities=cfg["opacities"].to(device),
+                views_host=views, views=[v.to(device) for v in views], grad_image=grad_image, grad_alpha=grad_alpha, H=H, W=W)
+
+
+# ---------------------------------------------------------------------------------------------------
+def cpu_pipeline_points_per_s(n_points: int, threads: int) -> tuple[float, str]:
+    """The CPU restatement of the whole path on a bounded sample of the workload: one view, forward and
+    backward, `n_points` samples of the same octree and camera."""
+    import numpy as np
+    import torch
+    sys.path.insert(0, str(ROOT / "oracle"))
+    import oracle as O
+    from inpc_b200 import synthetic as syn
+    os.environ["OMP_NUM_THREADS"] = str(threads)
+    cfg = syn.config1(n_samples=n_points, n_leaves=N_LEAVES)
+    tree, view = cfg["tree"], cfg["view"]
+    c = view.camera
+    cam = O.Camera(view.w2c.numpy(), view.position.numpy(), c.width, c.height, c.focal_x, c.focal_y, c.center_x, c.center_y,
+                   c.near_plane, c.far_plane)
+    g = torch.Generator().manual_seed(5)
+    gi = (torch.randn((4, c.height, c.width), generator=g) * 1e-3).numpy()
+    ga = (torch.randn((1, c.height, c.width), generator=g) * 1e-3).numpy()
+    feats, opac = cfg["features"].numpy(), cfg["opacities"].numpy()
+    centers, levels, weights = tree.centers.numpy(), tree.levels.numpy(), tree.weights.numpy()
+    O.lib()
+    t0 = time.perf_counter()
+    vw = O.viewpoint_weights(cam, centers, levels, weights, tree.initial_size)
+    cdf, _ = O.build_cdf(vw)
+    pos, idx, _ = O.training_samples(cam, 0, 0, cdf, centers, levels, tree.initial_size, n_points)
+    st = O.rasterize_forward(O.BILINEAR, cam, pos, feats, opac, tile=16)
+    O.rasterize_backward(st, gi, ga)
+    dt = time.perf_counter() - t0
+    return n_points / dt, f"1 view of the bench workload at {n_points} points (of {N_POINTS}), fwd+bwd, {dt:.1f} s"
+
+
+def cpu_baseline(args) -> dict:
+    threads = os.cpu_count() or 1
+    pps, _ = cpu_pipeline_points_per_s(1 << 17, threads)            # calibration run
+    n = int(min(max(pps * 12.0, 1 << 17), N_POINTS))                # about 12 s of CPU work, at most one full view
+    pps, sample = cpu_pipeline_points_per_s(n, threads)
+    return {"value": pps / 1e6, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample}
+
+
+# ---------------------------------------------------------------------------------------------------
+def run_ours(args):
+    import torch
+    from inpc_b200 import _cabi
+    from inpc_b200.batch import ViewShardedTrainer, partition_views
+
+    rank, local, world = dist_setup(args)
+    device = torch.device("cuda", local)
+    wl = build_workload(args, device)
+    trainer = ViewShardedTrainer(wl["tree"], wl["features"], wl["opacities"], args.points, seed=0, n_appearance=N_APPEARANCE,
+                                 tile_size=args.tile)
+    gi_dev, ga_dev = wl["grad_image"].to(device), wl["grad_alpha"].to(device)
+    my_views = partition_views(args.views, rank, world)
+
+    def step():
+        trainer.run_batch(wl["views"], (gi_dev, ga_dev), rank, world)
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    barrier(world)
+    _cabi.profile_read(reset=True)
+    _cabi.profile_enable(True)
+    launches0 = _cabi.launch_count()
+    clocks = ClockSampler(local) if rank == 0 else None
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(args.steps):
+        step()
+    stop.record()
+    barrier(world)
+    elapsed_ms = max_over_ranks(start.elapsed_time(stop), world, device)
+    clock_info = clocks.stop() if clocks else None
+    launches = _cabi.launch_count() - launches0
+    _cabi.profile_enable(False)
+    stages = _cabi.profile_read(reset=True)
+
+    # instance / visible counts of this rank's views, for the algorithmic-byte model
+    from inpc_b200 import rasterization as R
+    n_inst, n_vis = [], []
+    for vi in my_views[:4]:
+        trainer.sampler.set_rng_state(vi)
+        t = wl["tree"]
+        pos, _ = trainer.sampler.generate_training_samples(t.centers, t.levels, t.weights, wl["views"][vi], args.points, t.initial_size)
+        st = R.forward_with_state(pos, wl["features"], wl["opacities"], R.INPCRasterizer.extract_settings(wl["views"][vi], 0), args.tile)[3]
+        n_inst.append(int(st.n_instances))
+        n_vis.append(int(st.n_visible))
+    torch.cuda.synchronize()
+
+    # ---- end to end through the public API: host camera + host upstream gradient in, loss out
+    pinned_gi = wl["grad_image"].pin_memory()
+    pinned_ga = wl["grad_alpha"].pin_memory()
+    pinned_views = [(v.w2c.pin_memory(), v.position.pin_memory()) for v in wl["views_host"]]
+    loss_host = torch.zeros(1, dtype=torch.float32).pin_memory()
+    copy_stream = torch.cuda.Stream(device=device)
+    from inpc_b200.views import View
+
+    def e2e_step():
+        trainer.buffers.zero_()
+        for vi in my_views:
+            with torch.cuda.stream(copy_stream):
+                gi = pinned_gi.to(device, non_blocking=True)
+                ga = pinned_ga.to(device, non_blocking=True)
+                copied = torch.cuda.Event()
+                copied.record(copy_stream)
+            w2c, cpos = pinned_views[vi]
+            view = View(wl["views_host"][vi].camera, w2c.to(device, non_blocking=True), cpos.to(device, non_blocking=True))
+            trainer.sampler.set_rng_state(vi)
+            t = wl["tree"]
+            pos, idx = trainer.sampler.generate_training_samples(t.centers, t.levels, t.weights, view, args.points, t.initial_size)
+            feats = wl["features"].detach().requires_grad_(True)
+            opac = wl["opacities"].detach().requires_grad_(True)
+            image, alpha, bw = trainer.rasterizer(view, 0, pos, feats, opac)
+            torch.cuda.current_stream().wait_event(copied)
+            gi.record_stream(torch.cuda.current_stream())
+            ga.record_stream(torch.cuda.current_stream())
+            loss = (image * gi).sum() + (alpha * ga).sum()
+            loss.backward()
+            from inpc_b200.batch import accumulate_view
+            accumulate_view(trainer.buffers, idx, bw, feats.grad, opac.grad)
+            loss_host.copy_(loss.detach().reshape(1), non_blocking=True)
+        from inpc_b200.batch import allreduce_buffers
+        allreduce_buffers(trainer.buffers)
+        torch.cuda.synchronize()
+        return float(loss_host.item())
+
+    e2e_step()
+    barrier(world)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        e2e_step()
+    barrier(world)
+    e2e_s = max_over_ranks(time.perf_counter() - t0, world, device)
+
+    if world > 1:
+        import torch.distributed as dist
+        gathered = [None] * world
+        dist.all_gather_object(gathered, (n_inst, n_vis))
+        n_inst = [x for g in gathered for x in g[0]]
+        n_vis = [x for g in gathered for x in g[1]]
+    if rank != 0:
+        if world > 1:
+            import torch.distributed as dist
+            dist.destroy_process_group()
+        return
+
+    total_points = args.steps * args.views * args.points
+    value = total_points / (elapsed_ms * 1e-3) / 1e6
+    e2e_value = total_points / e2e_s / 1e6
+    peaks = {}
+    peaks_path = ROOT / "MEASURED_PEAKS.json"
+    if peaks_path.exists():
+        peaks = json.loads(peaks_path.read_text())
+    peak_gbs = float(peaks.get("hbm_gbs", 6650.0))
+    peak_kind = "measured" if "hbm_gbs" in peaks else "fallback"
+
+    mean_i = statistics.mean(n_inst) if n_inst else 0.0
+    mean_v = statistics.mean(n_vis) if n_vis else 0.0
+    P = wl["H"] * wl["W"]
+    c = 4
+    alg = {   # algorithmic bytes per launch
+        "blend_fwd": mean_i * (4 + 4 + 8 + 4 * c) + P * 4 * (c + 1) + mean_v * 8,
+        "blend_bwd": mean_i * (16 + 4 * c) + P * 4 * (2 * c + 2) + mean_v * 8 * (c + 1),
+        "sort_depth": mean_v * (4 + 4 * 16),
+        "preprocess": args.points * (12 + 12 + 72) + mean_v * (32 + 4 * c + 4 + 8),
+    }
+    per_stage = {k: {"ms_per_view": ms / max(n, 1), "calls": n} for k, (ms, n) in stages.items()}
+    dominant = max(alg, key=lambda k: stages[k][0])
+    dom_ms = stages[dominant][0] / max(stages[dominant][1], 1)
+    achieved = alg[dominant] / (dom_ms * 1e-3) / 1e9 if dom_ms > 0 else 0.0
+    roofline = {"bound": "hbm", "kernel": dominant, "achieved": achieved, "peak": peak_gbs, "unit": "GB/s",
+                "frac": achieved / peak_gbs if peak_gbs else None, "peak_source": peak_kind, "traffic": None,
+                "algorithmic_bytes_per_launch": alg[dominant], "launch_ms": dom_ms}
+
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+        "ms_per_step": elapsed_ms / args.steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": "f32", "data": "synthetic",
+        "config": {"workload": f"config 1 single-view training step x {args.views} orbit views (config 3 batch), sharded by view",
+                   "points_per_view": args.points, "views_per_step": args.views, "leaves": N_LEAVES, "image": [wl["W"], wl["H"]],
+                   "features": "36 x fp16 SH -> 4 channels", "tile": args.tile, "parallelism": f"view-dp{world}",
+                   "l2": "inputs (604 MB of features per view) exceed the 126 MB L2; no flush needed",
+                   "allreduce_floats": N_LEAVES + N_APPEARANCE},
+        "frames_per_s": args.steps * args.views / (elapsed_ms * 1e-3),
+        "ms_per_view": elapsed_ms / args.steps / max(len(my_views), 1),
+        "e2e": {"value": e2e_value, "unit": UNIT,
+                "h2d_bytes_per_step": args.views * (5 * P * 4 + 16 * 4 + 3 * 4), "d2h_bytes_per_step": args.views * 4},
+        "gpu_launches": launches,
+        "clocks": clock_info,
+        "roofline": roofline,
+        "stages": per_stage,
+        "instances_per_view": mean_i, "visible_per_view": mean_v,
+    }
+    if world == 1 and not args.no_cpu_baseline:
+        try:
+            line["cpu_baseline"] = cpu_baseline(args)
+        except Exception as e:   # the baseline is a side number: never lose the bench line over it
+            line["cpu_baseline"] = {"value": None, "unit": UNIT, "cores": os.cpu_count(), "kind": "port", "sample": f"failed: {e!r}"}
+    print(json.dumps(line))
+    if world > 1:
+        import torch.distributed as dist
+        dist.destroy_process_group()
+
+
+# ---------------------------------------------------------------------------------------------------
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return                                   # the reference is single-GPU: rank 0 alone runs it
+    sys.path.insert(0, str(ROOT / "oracle"))
+    import ref_backend as RB
+    config = {"workload": f"config 1 single-view training step x {args.views} orbit views (config 3 batch)",
+              "points_per_view": args.points, "views_per_step": args.views, "leaves": N_LEAVES,
+              "features": "36 x fp16 SH -> 4 channels", "tile": 8, "parallelism": "single GPU (the reference has no multi-GPU path)"}
+    base = {"impl": "reference", "metric": METRIC, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps, "warmup": max(args.warmup, 3),
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": config}
+    import torch
+    if not RB.available() or not torch.cuda.is_available():
+        # no compiled reference backend (or no GPU): time the CPU restatement on a bounded sample
+        cb = cpu_baseline(args)
+        base.update(value=cb["value"], ms_per_step=args.views * args.points / (cb["value"] * 1e6) * 1e3, cpu_baseline=cb,
+                    e2e={"value": cb["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0})
+        print(json.dumps(base))
+        return
+
+    torch.cuda.set_device(0)
+    device = torch.device("cuda", 0)
+    wl = build_workload(args, device)
+    t = wl["tree"]
+    gi_dev, ga_dev = wl["grad_image"].to(device), wl["grad_alpha"].to(device)
+    opac_flat = wl["opacities"].reshape(-1).contiguous()
+    RB.sampler_seed(0)
+
+    def view_step(view, gi, ga):
+        pos, idx, _ = RB.training_samples(view, t.centers, t.levels, t.weights, args.points, t.initial_size, sync=False)
+        img, alpha, bw = RB.forward(view, 0, pos, wl["features"], opac_flat, sync=False)
+        RB.backward(view, 0, gi, ga, img, alpha, pos, opac_flat, sync=False)
+        return img, alpha
+
+    def step():
+        for v in wl["views"]:
+            view_step(v, gi_dev, ga_dev)
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    torch.cuda.synchronize()
+    clocks = ClockSampler(0)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        step()
+    torch.cuda.synchronize()
+    elapsed = time.perf_counter() - t0
+    clock_info = clocks.stop()
+
+    pinned_gi, pinned_ga = wl["grad_image"].pin_memory(), wl["grad_alpha"].pin_memory()
+    pinned_views = [(v.w2c.pin_memory(), v.position.pin_memory()) for v in wl["views_host"]]
+    loss_host = torch.zeros(1, dtype=torch.float32).pin_memory()
+    from inpc_b200.views import View
+
+    def e2e_step():
+        for vi in range(args.views):
+            gi = pinned_gi.to(device, non_blocking=True)
+            ga = pinned_ga.to(device, non_blocking=True)
+            w2c, cpos = pinned_views[vi]
+            view = View(wl["views_host"][vi].camera, w2c.to(device, non_blocking=True), cpos.to(device, non_blocking=True))
+            img, alpha = view_step(view, gi, ga)
+            loss = (img * gi).sum() + (alpha * ga).sum()
+            loss_host.copy_(loss.reshape(1), non_blocking=True)
+        torch.cuda.synchronize()
+
+    e2e_step()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        e2e_step()
+    e2e_s = time.perf_counter() - t0
+
+    total_points = args.steps * args.views * args.points
+    P = wl["H"] * wl["W"]
+    base.update(value=total_points / elapsed / 1e6, ms_per_step=elapsed / args.steps * 1e3,
+                frames_per_s=args.steps * args.views / elapsed, ms_per_view=elapsed / args.steps / args.views * 1e3,
+                clocks=clock_info,
+                cpu_baseline={"value": total_points / elapsed / 1e6, "unit": UNIT, "cores": 0, "kind": "reference",
+                              "sample": "the reference's own CUDA backend (it has no CPU implementation of this path), "
+                                        "compiled unmodified for sm_100a, full workload on one B200"},
+                e2e={"value": total_points / e2e_s / 1e6, "unit": UNIT,
+                     "h2d_bytes_per_step": args.views * (5 * P * 4 + 16 * 4 + 3 * 4), "d2h_bytes_per_step": args.views * 4})
+    print(json.dumps(base))
+
+
+def main():
+    args = parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -64,6 +64,18 @@ const char* inpc_last_error(void);
 /* Library/ABI version as major*10000 + minor*100 + patch. */
 int inpc_version(void);
 
+/* Number of kernels this library has launched in the process so far. */
+long long inpc_launch_count(void);
+
+/* Per-stage device timing with CUDA events on the caller's stream; off by default.  Stages:
+ * 0 sample | 1 preprocess | 2 depth sort | 3 instance emission | 4 tile sort + ranges | 5 blend
+ * forward | 6 blend backward | 7 preprocess backward.  inpc_profile_read waits for the recorded
+ * events, adds them to running totals and copies min(n, 8) totals (milliseconds, number of timed
+ * scopes) out; `reset` != 0 clears the totals afterwards.  Stands in for the reference's only
+ * profiling aid, the -lineinfo switch of INPCCudaBackend/setup.py:11,32-33. */
+int inpc_profile_enable(int on);
+int inpc_profile_read(double* stage_ms, long long* stage_calls, int n, int reset);
+
 /* ------------------------------------------------------------------------------------------
  * Rasterizer
  * ---------------------------------------------------------------------------------------- */

@@ -38,6 +38,9 @@ _VP, _SP = C.POINTER(View), C.POINTER(RasterState)
 PROTOTYPES = {
     "inpc_last_error": (C.c_char_p, []),
     "inpc_version": (_I, []),
+    "inpc_launch_count": (C.c_longlong, []),
+    "inpc_profile_enable": (_I, [_I]),
+    "inpc_profile_read": (_I, [C.POINTER(C.c_double), C.POINTER(C.c_longlong), _I, _I]),
     "inpc_rasterize_forward": (_I, [_I, _I, _VP, _L, _P, _P, _P, _P, _P, _P, ALLOC_FN, ALLOC_FN, _P, _SP, _P]),
     "inpc_rasterize_backward": (_I, [_SP, _VP, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P]),
     "inpc_render": (_I, [_I, _I, _VP, _L, _P, _P, _F, _F, _P, _P, _P, ALLOC_FN, ALLOC_FN, _P, _P]),
@@ -87,3 +90,23 @@ def check(status: int) -> None:
     if status != 0:
         msg = lib().inpc_last_error()
         raise InpcError(f"inpc_b200 error {status}: {msg.decode() if msg else ''}")
+
+
+STAGES = ("sample", "preprocess", "sort_depth", "instances", "sort_tile", "blend_fwd", "blend_bwd", "preprocess_bwd")
+
+
+def launch_count() -> int:
+    """Kernels launched by the library in this process so far."""
+    return int(lib().inpc_launch_count())
+
+
+def profile_enable(on: bool) -> None:
+    check(lib().inpc_profile_enable(1 if on else 0))
+
+
+def profile_read(reset: bool = True) -> dict:
+    """Per-stage device time since the last reset: {stage: (total milliseconds, timed scopes)}."""
+    ms = (C.c_double * len(STAGES))()
+    calls = (C.c_longlong * len(STAGES))()
+    check(lib().inpc_profile_read(ms, calls, len(STAGES), 1 if reset else 0))
+    return {name: (float(ms[i]), int(calls[i])) for i, name in enumerate(STAGES)}

@@ -20,11 +20,35 @@ int cuda_fail(cudaError_t e, const char* what);
         if (_e != cudaSuccess) return ::inpc::cuda_fail(_e, #expr); \
     } while (0)
 
+// After every kernel launch: counts it (inpc_launch_count) and turns a launch error into a status.
 #define INPC_LAUNCH_CHECK(name)                                       \
     do {                                                              \
+        ::inpc::count_launch();                                       \
         cudaError_t _e = cudaGetLastError();                          \
         if (_e != cudaSuccess) return ::inpc::cuda_fail(_e, name);     \
     } while (0)
+
+void count_launch();
+
+// Optional per-stage device timing (inpc_profile_enable): a StageScope records a CUDA event pair
+// around the launches of one pipeline stage on the stream they are issued to.
+enum Stage : int {
+    STAGE_SAMPLE = 0,        // leaf weights, CDF, draws
+    STAGE_PREPROCESS = 1,    // visibility count, scan, project + SH
+    STAGE_SORT_DEPTH = 2,
+    STAGE_INSTANCES = 3,     // per-point tile counts, scan, emission
+    STAGE_SORT_TILE = 4,     // tile sort + ranges
+    STAGE_BLEND_FWD = 5,
+    STAGE_BLEND_BWD = 6,
+    STAGE_PREPROCESS_BWD = 7,
+    STAGE_COUNT = 8,
+};
+struct StageScope {
+    int slot;
+    cudaStream_t stream;
+    StageScope(Stage stage, cudaStream_t s);
+    ~StageScope();
+};
 
 // Device-visible status words in mapped pinned host memory: a kernel stores 1 into its word when a
 // bounded wait runs out (plain store, no atomics over PCIe); the host reads them without a device

@@ -883,6 +883,7 @@ int run_front(const RasterParams& rp, int64_t n, const float* positions, const v
 
     int64_t n_visible = 0, n_instances = 0;
     if (n > 0) {
+        StageScope scope(STAGE_PREPROCESS, stream);
         visibility_count_kernel<MODE, VARIANT><<<(unsigned)nb, kPreThreads, 0, stream>>>(positions, n, rp, pb.block_visible, pb.block_instances);
         INPC_LAUNCH_CHECK("visibility_count_kernel");
         scan_block_counts_kernel<<<1, kScanThreads, 0, stream>>>(pb.block_visible, pb.block_instances, nb, pb.counters);
@@ -912,23 +913,32 @@ int run_front(const RasterParams& rp, int64_t n, const float* positions, const v
     INPC_CUDA_TRY(cudaMemsetAsync(ib.ranges, 0, sizeof(uint2) * (size_t)n_tiles, stream));
 
     if (n > 0) {
+        StageScope scope(STAGE_PREPROCESS, stream);
         preprocess_kernel<MODE, VARIANT><<<(unsigned)nb, kPreThreads, 0, stream>>>(
             positions, static_cast<const __half*>(features), opacities, n, rp, pb.block_visible, pb.rec, pb.bounds,
             pb.conic, pb.keys[0], pb.ids[0]);
         INPC_LAUNCH_CHECK("preprocess_kernel");
     }
     int in_alt = 0;
-    int rc = sort_pairs(pb.keys[0], pb.keys[1], pb.ids[0], pb.ids[1], n_visible, 32, pb.sort_ws, &in_alt, stream);
+    int rc;
+    {
+        StageScope scope(STAGE_SORT_DEPTH, stream);
+        rc = sort_pairs(pb.keys[0], pb.keys[1], pb.ids[0], pb.ids[1], n_visible, 32, pb.sort_ws, &in_alt, stream);
+    }
     if (rc != INPC_OK) return rc;
     const uint32_t* sorted_ids = pb.ids[in_alt];
     if (n_visible > 0 && n_instances > 0) {
         const int64_t ibk = ceil_div<int64_t>(n_visible, kInstThreads);
-        instance_count_kernel<<<(unsigned)ibk, kInstThreads, 0, stream>>>(sorted_ids, pb.bounds, n_visible, pb.inst_block_sums);
-        INPC_LAUNCH_CHECK("instance_count_kernel");
-        scan_u32_kernel<<<1, kScanThreads, 0, stream>>>(pb.inst_block_sums, ibk);
-        INPC_LAUNCH_CHECK("scan_u32_kernel");
-        emit_instances_kernel<<<(unsigned)ibk, kInstThreads, 0, stream>>>(sorted_ids, pb.bounds, n_visible, pb.inst_block_sums, rp.gw, ib.keys[0], ib.ids[0]);
-        INPC_LAUNCH_CHECK("emit_instances_kernel");
+        {
+            StageScope scope(STAGE_INSTANCES, stream);
+            instance_count_kernel<<<(unsigned)ibk, kInstThreads, 0, stream>>>(sorted_ids, pb.bounds, n_visible, pb.inst_block_sums);
+            INPC_LAUNCH_CHECK("instance_count_kernel");
+            scan_u32_kernel<<<1, kScanThreads, 0, stream>>>(pb.inst_block_sums, ibk);
+            INPC_LAUNCH_CHECK("scan_u32_kernel");
+            emit_instances_kernel<<<(unsigned)ibk, kInstThreads, 0, stream>>>(sorted_ids, pb.bounds, n_visible, pb.inst_block_sums, rp.gw, ib.keys[0], ib.ids[0]);
+            INPC_LAUNCH_CHECK("emit_instances_kernel");
+        }
+        StageScope scope(STAGE_SORT_TILE, stream);
         int t_alt = 0;
         rc = sort_pairs(ib.keys[0], ib.keys[1], ib.ids[0], ib.ids[1], n_instances, bit_length((uint32_t)(n_tiles - 1)), ib.sort_ws, &t_alt, stream);
         if (rc != INPC_OK) return rc;
@@ -966,6 +976,7 @@ int launch_blend_forward(int mode, const RasterParams& rp, const PointBlob& pb, 
     const int n_tiles = rp.gw * rp.gh;
     const uint32_t* ids = ib.ids[tile_result_buffer(n_instances, n_tiles)];
     const int W = rp.v.width, H = rp.v.height;
+    StageScope scope(STAGE_BLEND_FWD, stream);
     if (mode == INPC_MODE_BILINEAR) {
         if (rp.tile == 8)
             blend_bilinear_forward_kernel<8, KIND><<<n_tiles, 64, 0, stream>>>(ib.ranges, ids, pb.rec, image, depth, alpha, blending_weights, W, H, rp.gw);
@@ -1034,18 +1045,22 @@ extern "C" int inpc_rasterize_backward(const inpc_raster_state* state, const inp
     INPC_CUDA_TRY(cudaMemsetAsync(grad_opacities, 0, sizeof(float) * (size_t)n, stream));
     float4* gfv = reinterpret_cast<float4*>(grad_features_view);
     const int W = rp.v.width, H = rp.v.height;
-    if (state->mode == INPC_MODE_BILINEAR) {
-        if (rp.tile == 8)
-            blend_bilinear_backward_kernel<8><<<n_tiles, 64, 0, stream>>>(ib.ranges, ids, pb.rec, grad_image, grad_alpha, image, alpha, gfv, grad_opacities, W, H, rp.gw);
-        else
-            blend_bilinear_backward_kernel<16><<<n_tiles, 256, 0, stream>>>(ib.ranges, ids, pb.rec, grad_image, grad_alpha, image, alpha, gfv, grad_opacities, W, H, rp.gw);
-    } else {
-        if (rp.tile == 8)
-            blend_gaussian_backward_kernel<8><<<n_tiles, 64, 0, stream>>>(ib.ranges, ids, pb.rec, pb.conic, grad_image, grad_alpha, image, alpha, gfv, grad_opacities, W, H, rp.gw);
-        else
-            blend_gaussian_backward_kernel<16><<<n_tiles, 256, 0, stream>>>(ib.ranges, ids, pb.rec, pb.conic, grad_image, grad_alpha, image, alpha, gfv, grad_opacities, W, H, rp.gw);
+    {
+        StageScope scope(STAGE_BLEND_BWD, stream);
+        if (state->mode == INPC_MODE_BILINEAR) {
+            if (rp.tile == 8)
+                blend_bilinear_backward_kernel<8><<<n_tiles, 64, 0, stream>>>(ib.ranges, ids, pb.rec, grad_image, grad_alpha, image, alpha, gfv, grad_opacities, W, H, rp.gw);
+            else
+                blend_bilinear_backward_kernel<16><<<n_tiles, 256, 0, stream>>>(ib.ranges, ids, pb.rec, grad_image, grad_alpha, image, alpha, gfv, grad_opacities, W, H, rp.gw);
+        } else {
+            if (rp.tile == 8)
+                blend_gaussian_backward_kernel<8><<<n_tiles, 64, 0, stream>>>(ib.ranges, ids, pb.rec, pb.conic, grad_image, grad_alpha, image, alpha, gfv, grad_opacities, W, H, rp.gw);
+            else
+                blend_gaussian_backward_kernel<16><<<n_tiles, 256, 0, stream>>>(ib.ranges, ids, pb.rec, pb.conic, grad_image, grad_alpha, image, alpha, gfv, grad_opacities, W, H, rp.gw);
+        }
+        INPC_LAUNCH_CHECK("blend_backward_kernel");
     }
-    INPC_LAUNCH_CHECK("blend_backward_kernel");
+    StageScope scope(STAGE_PREPROCESS_BWD, stream);
     preprocess_backward_kernel<<<(unsigned)ceil_div<int64_t>(n, kPreThreads), kPreThreads, 0, stream>>>(
         positions, view->cam_position, pb.bounds, gfv, static_cast<__half*>(grad_features), n);
     INPC_LAUNCH_CHECK("preprocess_backward_kernel");

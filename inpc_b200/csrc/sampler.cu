@@ -510,6 +510,7 @@ extern "C" int inpc_generate_training_samples(inpc_sampler* s, const inpc_view* 
     if (n_samples < 0 || n_samples >= ((int64_t)1 << 32) || !positions || !indices || !workspace) { set_error("inpc_generate_training_samples: bad argument"); return INPC_E_INVALID; }
     SamplerWs w = carve_sampler_ws(workspace, n_cells);
     const ViewParams v = to_params(view);
+    StageScope scope(STAGE_SAMPLE, stream);
     viewpoint_weights_kernel<<<(unsigned)ceil_div<int64_t>(n_cells, kThreads), kThreads, 0, stream>>>(v, n_cells, centers, levels, weights, initial_size, w.vw);
     INPC_LAUNCH_CHECK("viewpoint_weights_kernel");
     rc = build_cdf(w.vw, n_cells, w.cdf, w.sum, w, stream);
