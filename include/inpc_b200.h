@@ -148,6 +148,25 @@ size_t inpc_sort_workspace_bytes(int64_t n);
 int inpc_sort_pairs(uint32_t* keys, uint32_t* keys_alt, uint32_t* values, uint32_t* values_alt, int64_t n,
                     int end_bit, void* workspace, int* result_in_alt, void* stream);
 
+/* The same sort for callers that cannot allocate device memory: hosts that run inside someone
+ * else's memory budget — an engine plugin handed a fixed arena, a real-time loop where cudaMalloc's
+ * implicit synchronisation is not acceptable, a process whose allocator is owned by another
+ * framework and must not see foreign allocations.  It takes no workspace argument: its scratch is a
+ * fixed array inside the library's device image (about 520 KB, held by every GPU that loads the
+ * library until the process exits), and it makes no cudaMalloc / cudaFree / allocating call of any
+ * kind, torch's included.  Inputs and outputs are still the caller's.
+ *   - Capacity: n <= 1,048,576 pairs; larger n returns INPC_E_CAPACITY with a message.
+ *   - The first call on a device resolves the array's device address (once per device, with that
+ *     device current); make that first call before starting any stream capture.
+ *   - All calls on a device share the one array, which still holds the previous call's histograms
+ *     and flags; each call clears what it reads, on `stream`.  Two calls whose work overlaps on the
+ *     GPU (different streams, no ordering) race on it: serialise them.
+ *   - A look-back wait that runs out is recorded only inside the array, not reported to the host
+ *     (reporting needs pinned memory, which would be an allocation); the wait stays bounded.
+ * This entry point has no counterpart in the reference. */
+int inpc_sort_pairs_static(uint32_t* keys, uint32_t* keys_alt, uint32_t* values, uint32_t* values_alt, int64_t n,
+                           int end_bit, int* result_in_alt, void* stream);
+
 /* ------------------------------------------------------------------------------------------
  * Probability-field sampler
  * ---------------------------------------------------------------------------------------- */

@@ -48,6 +48,7 @@ PROTOTYPES = {
     "inpc_raster_debug_copy": (_I, [_SP, _VP, _I, _P, _P]),
     "inpc_sort_workspace_bytes": (_Z, [_L]),
     "inpc_sort_pairs": (_I, [_P, _P, _P, _P, _L, _I, _P, C.POINTER(C.c_int), _P]),
+    "inpc_sort_pairs_static": (_I, [_P, _P, _P, _P, _L, _I, C.POINTER(C.c_int), _P]),
     "inpc_compute_viewpoint_weights": (_I, [_VP, _L, _P, _P, _P, _F, _P, _P]),
     "inpc_sampler_create": (_P, [_L]),
     "inpc_sampler_destroy": (None, [_P]),

@@ -10,6 +10,7 @@
 // Replaces cub::DeviceRadixSort::SortPairs as used in rasterization/src/bilinear/forward.cu:91-98
 // (32-bit depth keys) and :132-139 (tile keys) of the reference.
 #include "common.cuh"
+#include <mutex>
 
 namespace inpc {
 
@@ -295,6 +296,101 @@ int sort_pairs(uint32_t* keys, uint32_t* keys_alt, uint32_t* values, uint32_t* v
 }
 
 }  // namespace inpc
+
+// ---- sorting without any allocation -------------------------------------------------------------
+// Scratch for inpc_sort_pairs_static lives in this fixed device array: every GPU that loads the library
+// holds it (about 520 KB) until the process exits.  Layout = the ordinary sort workspace for
+// kStaticMaxPairs pairs, followed by one 256-byte status area.
+namespace inpc {
+namespace {
+constexpr int64_t kStaticMaxPairs = 1 << 20;
+constexpr size_t kStaticTiles = (kStaticMaxPairs + kTile - 1) / kTile;
+constexpr size_t kStaticWorkspaceBytes = (kMaxPasses * kRadix * 4 + 256)            // histograms + tickets
+                                         + kMaxPasses * kStaticTiles * kRadix * 4   // look-back state
+                                         + kMaxPasses * kRadix * 4;                 // digit bases
+constexpr size_t kStaticScratchBytes = kStaticWorkspaceBytes + 256;
+static_assert(kStaticWorkspaceBytes % 256 == 0, "status area must stay 256-byte aligned");
+
+static __device__ __align__(256) unsigned char g_static_sort_scratch[kStaticScratchBytes];
+
+constexpr int kMaxDevices = 64;
+std::mutex g_static_mutex;
+void* g_static_scratch_ptr[kMaxDevices] = {nullptr};   // device address of the array, per device
+
+// Once per device, with that device current: resolve the array's device address.  In host code the
+// array's name is only a handle for the runtime, not an address a kernel could use.
+int static_scratch_for_current_device(void** out) {
+    int dev = -1;
+    INPC_CUDA_TRY(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= kMaxDevices) { set_error("device index %d outside the supported range", dev); return INPC_E_INVALID; }
+    std::lock_guard<std::mutex> lock(g_static_mutex);
+    if (!g_static_scratch_ptr[dev]) {
+        void* p = nullptr;
+        INPC_CUDA_TRY(cudaGetSymbolAddress(&p, g_static_sort_scratch));
+        INPC_CUDA_TRY(cudaFuncSetAttribute(radix_onesweep_pass_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(PassSmem)));
+        g_static_scratch_ptr[dev] = p;
+    }
+    *out = g_static_scratch_ptr[dev];
+    return INPC_OK;
+}
+}  // namespace
+}  // namespace inpc
+
+extern "C" int inpc_sort_pairs_static(uint32_t* keys, uint32_t* keys_alt, uint32_t* values, uint32_t* values_alt,
+                                      int64_t n, int end_bit, int* result_in_alt, void* stream_) {
+    using namespace inpc;
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    if (result_in_alt) *result_in_alt = 0;
+    if (n < 0) { set_error("inpc_sort_pairs_static: n=%lld is negative", (long long)n); return INPC_E_INVALID; }
+    if (n > kStaticMaxPairs) {
+        set_error("inpc_sort_pairs_static: n=%lld exceeds the fixed capacity of %lld pairs; use inpc_sort_pairs with a caller workspace",
+                  (long long)n, (long long)kStaticMaxPairs);
+        return INPC_E_CAPACITY;
+    }
+    if (end_bit < 0 || end_bit > 32) { set_error("inpc_sort_pairs_static: end_bit=%d out of range", end_bit); return INPC_E_INVALID; }
+    if (n <= 1 || end_bit == 0) return INPC_OK;
+    if (!keys || !keys_alt || !values || !values_alt) { set_error("inpc_sort_pairs_static: null pointer"); return INPC_E_INVALID; }
+    if ((reinterpret_cast<uintptr_t>(keys) | reinterpret_cast<uintptr_t>(keys_alt)) & 15u) {
+        set_error("inpc_sort_pairs_static: key buffers must be 16-byte aligned");
+        return INPC_E_INVALID;
+    }
+    void* scratch = nullptr;
+    int rc = static_scratch_for_current_device(&scratch);
+    if (rc != INPC_OK) return rc;
+
+    PassTable pt;
+    pt.n_passes = ceil_div(end_bit, kRadixBits);
+    int bit = 0;
+    for (int p = 0; p < kMaxPasses; ++p) { pt.shift[p] = 0; pt.bits[p] = 0; }
+    for (int p = 0; p < pt.n_passes; ++p) {
+        const int b = (end_bit - bit + (pt.n_passes - p) - 1) / (pt.n_passes - p);
+        pt.shift[p] = bit;
+        pt.bits[p] = b;
+        bit += b;
+    }
+    SortWorkspace w = carve_sort_workspace(scratch, n);
+    const int64_t tiles = ceil_div<int64_t>(n, kTile);
+    // the array keeps the previous call's histograms, tickets and look-back flags: clear what this call reads
+    INPC_CUDA_TRY(cudaMemsetAsync(scratch, 0, w.zero_bytes + (size_t)pt.n_passes * tiles * kRadix * sizeof(unsigned), stream));
+    volatile unsigned* status = reinterpret_cast<unsigned*>(static_cast<unsigned char*>(scratch) + kStaticWorkspaceBytes);
+
+    const int hist_blocks = (int)ceil_div<int64_t>(n, kHistItemsPerBlock);
+    radix_histogram_kernel<<<hist_blocks, kHistThreads, 0, stream>>>(keys, n, pt, w.hist);
+    INPC_LAUNCH_CHECK("radix_histogram_kernel");
+    radix_scan_histogram_kernel<<<pt.n_passes, kRadix, 0, stream>>>(w.hist, w.base);
+    INPC_LAUNCH_CHECK("radix_scan_histogram_kernel");
+    uint32_t *kin = keys, *kout = keys_alt, *vin = values, *vout = values_alt;
+    for (int p = 0; p < pt.n_passes; ++p) {
+        radix_onesweep_pass_kernel<<<(unsigned)tiles, kThreads, sizeof(PassSmem), stream>>>(
+            kin, vin, kout, vout, n, pt.shift[p], pt.bits[p], w.base + p * kRadix,
+            w.state + (size_t)p * tiles * kRadix, w.ticket + p, status);
+        INPC_LAUNCH_CHECK("radix_onesweep_pass_kernel");
+        uint32_t* t = kin; kin = kout; kout = t;
+        t = vin; vin = vout; vout = t;
+    }
+    if (result_in_alt) *result_in_alt = pt.n_passes & 1;
+    return INPC_OK;
+}
 
 extern "C" size_t inpc_sort_workspace_bytes(int64_t n) { return inpc::sort_workspace_bytes(n < 0 ? 0 : n); }
 

@@ -1,0 +1,54 @@
+"""GPU test of inpc_sort_pairs_static, the sort variant for callers that must not allocate device
+memory (its scratch is a fixed array inside the library).  Called through the C ABI and compared bit
+for bit with the ordinary entry point, on two calls in a row so that the second one meets the first
+one's leftovers in the shared array.  Lives in a file pytest collects last."""
+import ctypes as C
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def _run(fn_name, keys, vals, end_bit):
+    from inpc_b200 import _cabi
+    L = _cabi.lib()
+    n = keys.numel()
+    k, v = keys.clone(), vals.clone()
+    ka, va = torch.empty_like(k), torch.empty_like(v)
+    alt = C.c_int(0)
+    stream = torch.cuda.current_stream().cuda_stream
+    if fn_name == "static":
+        before = torch.cuda.memory_allocated()
+        _cabi.check(L.inpc_sort_pairs_static(k.data_ptr(), ka.data_ptr(), v.data_ptr(), va.data_ptr(), n, end_bit, C.byref(alt), stream))
+        assert torch.cuda.memory_allocated() == before          # nothing went through torch's allocator either
+    else:
+        ws = torch.empty(max(int(L.inpc_sort_workspace_bytes(n)), 256), dtype=torch.uint8, device=DEV)
+        _cabi.check(L.inpc_sort_pairs(k.data_ptr(), ka.data_ptr(), v.data_ptr(), va.data_ptr(), n, end_bit, ws.data_ptr(),
+                                      C.byref(alt), stream))
+    torch.cuda.synchronize()
+    return (ka, va) if alt.value else (k, v)
+
+
+def test_static_sort_matches_workspace_sort_on_consecutive_calls():
+    g = torch.Generator(device=DEV).manual_seed(77)
+    cases = [(1 << 20, 32), (300_001, 14), (8193, 32), (1 << 20, 12)]      # the last reuses the array after a full-size call
+    for n, end_bit in cases:
+        keys = torch.randint(0, 1 << 32, (n,), generator=g, device=DEV, dtype=torch.int64).to(torch.int32)
+        vals = torch.arange(n, device=DEV, dtype=torch.int32)
+        sk, sv = _run("static", keys, vals, end_bit)
+        wk, wv = _run("workspace", keys, vals, end_bit)
+        assert torch.equal(sk, wk) and torch.equal(sv, wv)                  # integer work: bit-exact
+        order = torch.sort(keys.to(torch.int64) & ((1 << end_bit) - 1), stable=True).indices
+        assert torch.equal(sv.to(torch.int64), order)
+
+
+def test_static_sort_rejects_sizes_beyond_its_capacity():
+    from inpc_b200 import _cabi
+    L = _cabi.lib()
+    rc = L.inpc_sort_pairs_static(None, None, None, None, (1 << 20) + 1, 32, None, None)
+    assert rc == -5
+    msg = L.inpc_last_error().decode()
+    assert "capacity" in msg and "1048576" in msg
+    assert L.inpc_sort_pairs_static(None, None, None, None, 0, 32, None, None) == 0
