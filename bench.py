@@ -313,9 +313,10 @@ def run_ours(args):
         "sort_depth": mean_v * (4 + 4 * 16),
         "preprocess": args.points * (12 + 12 + 72) + mean_v * (32 + 4 * c + 4 + 8),
     }
-    per_stage = {k: {"ms_per_view": ms / max(n, 1), "calls": n} for k, (ms, n) in stages.items()}
+    views_timed = max(args.steps * len(my_views), 1)
+    per_stage = {k: {"ms_per_view": ms / views_timed, "scopes": n} for k, (ms, n) in stages.items()}
     dominant = max(alg, key=lambda k: stages[k][0])
-    dom_ms = stages[dominant][0] / max(stages[dominant][1], 1)
+    dom_ms = stages[dominant][0] / views_timed
     achieved = alg[dominant] / (dom_ms * 1e-3) / 1e9 if dom_ms > 0 else 0.0
     roofline = {"bound": "hbm", "kernel": dominant, "achieved": achieved, "peak": peak_gbs, "unit": "GB/s",
                 "frac": achieved / peak_gbs if peak_gbs else None, "peak_source": peak_kind, "traffic": None,

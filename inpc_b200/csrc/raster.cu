@@ -165,17 +165,28 @@ __global__ void __launch_bounds__(kScanThreads) scan_block_counts_kernel(unsigne
                                                                          const unsigned long long* __restrict__ block_instances,
                                                                          int64_t n_blocks,
                                                                          unsigned long long* __restrict__ counters) {
+    constexpr int kItems = 8;
     __shared__ unsigned s_scan[kScanThreads / 32 + 1];
     __shared__ unsigned long long s_inst[kScanThreads / 32];
     unsigned running = 0;
     unsigned long long inst = 0;
-    for (int64_t base = 0; base < n_blocks; base += kScanThreads) {
-        const int64_t j = base + threadIdx.x;
-        const unsigned c = j < n_blocks ? block_visible[j] : 0u;
-        if (j < n_blocks) inst += block_instances[j];
+    for (int64_t base = 0; base < n_blocks; base += (int64_t)kScanThreads * kItems) {
+        const int64_t j0 = base + (int64_t)threadIdx.x * kItems;
+        unsigned v[kItems];
+        unsigned sum = 0;
+#pragma unroll
+        for (int k = 0; k < kItems; ++k) {
+            v[k] = j0 + k < n_blocks ? block_visible[j0 + k] : 0u;
+            sum += v[k];
+            if (j0 + k < n_blocks) inst += block_instances[j0 + k];
+        }
         unsigned total;
-        const unsigned ex = block_exclusive_scan(c, s_scan, &total);
-        if (j < n_blocks) block_visible[j] = running + ex;
+        unsigned ex = running + block_exclusive_scan(sum, s_scan, &total);
+#pragma unroll
+        for (int k = 0; k < kItems; ++k) {
+            if (j0 + k < n_blocks) block_visible[j0 + k] = ex;
+            ex += v[k];
+        }
         running += total;
     }
 #pragma unroll
@@ -314,15 +325,26 @@ __global__ void __launch_bounds__(kInstThreads) instance_count_kernel(const uint
     }
 }
 
+constexpr int kScanItems = 8;
 __global__ void __launch_bounds__(kScanThreads) scan_u32_kernel(unsigned* __restrict__ data, int64_t n) {
     __shared__ unsigned s_scan[kScanThreads / 32 + 1];
     unsigned running = 0;
-    for (int64_t base = 0; base < n; base += kScanThreads) {
-        const int64_t j = base + threadIdx.x;
-        const unsigned c = j < n ? data[j] : 0u;
+    for (int64_t base = 0; base < n; base += (int64_t)kScanThreads * kScanItems) {
+        const int64_t j0 = base + (int64_t)threadIdx.x * kScanItems;
+        unsigned v[kScanItems];
+        unsigned sum = 0;
+#pragma unroll
+        for (int k = 0; k < kScanItems; ++k) {
+            v[k] = j0 + k < n ? data[j0 + k] : 0u;
+            sum += v[k];
+        }
         unsigned total;
-        const unsigned ex = block_exclusive_scan(c, s_scan, &total);
-        if (j < n) data[j] = running + ex;
+        unsigned ex = running + block_exclusive_scan(sum, s_scan, &total);
+#pragma unroll
+        for (int k = 0; k < kScanItems; ++k) {
+            if (j0 + k < n) data[j0 + k] = ex;
+            ex += v[k];
+        }
         running += total;
     }
 }
@@ -366,147 +388,371 @@ __global__ void __launch_bounds__(256) tile_ranges_kernel(const uint32_t* __rest
 }
 
 // ------------------------------------------------------------------------------------------------
-// Bilinear blend.  A point touches the 2x2 pixels whose centres lie within distance < 1 of it, so a
-// tile stages T*T instances at a time, every instance thread sets its bit in the masks of the (up
-// to four) pixels it reaches, and every pixel thread then walks only its own set bits, in staged
-// (= depth) order.  Per-fragment results that belong to the point (blending weight, gradients) go
-// to a private smem slot per (instance, quad corner) and are reduced by the instance thread in a
-// fixed order: no shared-memory atomics, one global vector atomic per instance.
+// Bilinear blend.
+//
+// (1) Per-pixel bit masks.  A point reaches only the 2x2 pixels whose centres lie within distance
+// < 1 of it, so a block stages T*T instances at a time, every instance thread sets its bit in the
+// masks of the (up to four) pixels it reaches, and every pixel thread then walks only its own set
+// bits, in staged (= depth) order.  Per-fragment results that belong to the point (blending weight,
+// gradients) go to a private shared-memory slot per (instance, footprint corner) and are reduced by
+// the instance thread in a fixed order: no shared-memory atomics, one global (vector) atomic per
+// instance.  Two block barriers per batch.
+//
+// (2) Segments.  Front-to-back compositing is associative: (C, T) o (C', T') = (C + T C', T T').  A
+// tile's instance list is cut into segments of at least 16 batches (at most 64 segments per tile) and
+// every (tile, segment) pair is one block, so a tile that carries 100x the average load no longer
+// sets the kernel's critical path.  For tiles with more than one segment a first pass computes each
+// segment's per-pixel transmittance product, a per-tile prefix turns these into the transmittance at
+// the start of every segment, and the main pass starts from that value (keeping the reference's
+// early-termination rule); partial colours are added up per tile in segment order.  The backward
+// pass starts every segment from the stored transmittance and colour prefix.
+//
 // Arithmetic per fragment: src/bilinear/kernels.cu:283-303 (forward), :361-415 (backward),
 // :462-475 (inference).
 // ------------------------------------------------------------------------------------------------
 enum { BLEND_TRAIN = 0, BLEND_INFER = 1 };
 
+struct __align__(16) Segment {
+    uint32_t tile;
+    uint32_t begin, end;   // instance range of this segment
+    uint32_t info;         // index of the segment within its tile | number of segments of the tile << 16
+};
+constexpr int kMaxSegmentsPerTile = 64;
+constexpr int kMinBatchesPerSegment = 16;
+
+// One block: per tile the number of segments, their exclusive scan, and the segment records.
+__global__ void __launch_bounds__(kScanThreads) build_segments_kernel(const uint2* __restrict__ ranges, int n_tiles, int batch,
+                                                                      Segment* __restrict__ segs, uint32_t* __restrict__ tile_first,
+                                                                      uint32_t* __restrict__ n_segments) {
+    __shared__ unsigned s_scan[kScanThreads / 32 + 1];
+    unsigned running = 0;
+    const unsigned s_min = (unsigned)(batch * kMinBatchesPerSegment);
+    for (int base = 0; base < n_tiles; base += kScanThreads) {
+        const int t = base + threadIdx.x;
+        unsigned seg_len = s_min, n = 0;
+        uint2 r = make_uint2(0u, 0u);
+        if (t < n_tiles) {
+            r = ranges[t];
+            const unsigned len = r.y - r.x;
+            const unsigned want = ceil_div(len, (unsigned)kMaxSegmentsPerTile);
+            seg_len = max(s_min, ceil_div(want, (unsigned)batch) * (unsigned)batch);
+            n = max(1u, ceil_div(len, seg_len));
+        }
+        unsigned total;
+        const unsigned ex = block_exclusive_scan(n, s_scan, &total);
+        if (t < n_tiles) {
+            const unsigned first = running + ex;
+            tile_first[t] = first;
+            for (unsigned s = 0; s < n; ++s) {
+                Segment g;
+                g.tile = (uint32_t)t;
+                g.begin = r.x + s * seg_len;
+                g.end = min(r.y, g.begin + seg_len);
+                g.info = s | (n << 16);
+                segs[first + s] = g;
+            }
+        }
+        running += total;
+    }
+    if (threadIdx.x == 0) *n_segments = running;
+}
+
+// Stages instance `t` of the batch starting at `base`: record into shared memory, bit into the masks of
+// the pixels it reaches.  Returns the point id.
+template <int T, bool NEED_F>
+__device__ __forceinline__ uint32_t stage_instance(int t, int cnt, unsigned base, const uint32_t* __restrict__ inst_ids,
+                                                   const PointRec* __restrict__ rec, int tile_x, int tile_y, float4* s_a,
+                                                   float4* s_f, unsigned (*s_mask)[T * T]) {
+    uint32_t id = 0;
+    if (t < cnt) {
+        id = __ldg(inst_ids + base + t);
+        const float4* r = reinterpret_cast<const float4*>(rec + id);
+        const float4 a = __ldg(r);
+        s_a[t] = a;
+        if (NEED_F) s_f[t] = __ldg(r + 1);
+        // first pixel column / row whose centre is within reach; the second is the next one
+        const int qx = __float2int_rd(a.x - 0.5f) - tile_x * T;
+        const int qy = __float2int_rd(a.y - 0.5f) - tile_y * T;
+        const unsigned bit = 1u << (t & 31);
+        unsigned* mrow = s_mask[t >> 5];
+#pragma unroll
+        for (int dy = 0; dy < 2; ++dy)
+#pragma unroll
+            for (int dx = 0; dx < 2; ++dx) {
+                const int cx = qx + dx, cy = qy + dy;
+                if (cx >= 0 && cx < T && cy >= 0 && cy < T) atomicOr(mrow + cy * T + cx, bit);
+            }
+    }
+    return id;
+}
+
+// Pass 1 (tiles with several segments only): per-pixel product of (1 - alpha) over one segment.
+template <int T>
+__global__ void __launch_bounds__(T * T) blend_bilinear_transmittance_kernel(
+    const Segment* __restrict__ segs, const uint32_t* __restrict__ n_segments, const uint32_t* __restrict__ inst_ids,
+    const PointRec* __restrict__ rec, float* __restrict__ seg_T, int width, int height, int gw) {
+    constexpr int B = T * T;
+    constexpr int WORDS = B / 32;
+    if (blockIdx.x >= *n_segments) return;
+    const Segment sg = segs[blockIdx.x];
+    const unsigned seg_idx = sg.info & 0xffffu, n_seg = sg.info >> 16;
+    if (n_seg == 1u || seg_idx == n_seg - 1u) return;   // the last segment's product is never needed
+
+    __shared__ float4 s_a[B];
+    __shared__ unsigned s_mask[WORDS][B];
+    const int t = threadIdx.x;
+    const int tx = (int)(sg.tile % (unsigned)gw), ty = (int)(sg.tile / (unsigned)gw);
+    const int px = tx * T + t % T, py = ty * T + t / T;
+    const bool inside = px < width && py < height;
+    const float pcx = (float)px + 0.5f, pcy = (float)py + 0.5f;
+#pragma unroll
+    for (int w = 0; w < WORDS; ++w) s_mask[w][t] = 0u;
+    __syncthreads();
+    float Tr = 1.0f;
+    bool done = !inside;
+    for (unsigned base = sg.begin; base < sg.end; base += B) {
+        const int cnt = (int)min((unsigned)B, sg.end - base);
+        stage_instance<T, false>(t, cnt, base, inst_ids, rec, tx, ty, s_a, nullptr, s_mask);
+        __syncthreads();
+#pragma unroll 1
+        for (int w = 0; w < WORDS; ++w) {
+            unsigned mbits = s_mask[w][t];
+            if (mbits) s_mask[w][t] = 0u;
+            while (mbits && !done) {
+                const int j = w * 32 + __ffs(mbits) - 1;
+                mbits &= mbits - 1u;
+                const float4 a = s_a[j];
+                const float dx = fabsf(a.x - pcx), dy = fabsf(a.y - pcy);
+                if (dx >= 1.0f || dy >= 1.0f) continue;
+                const float wgt = __saturatef(1.0f - dx) * __saturatef(1.0f - dy);
+                Tr *= 1.0f - a.z * wgt;
+                if (Tr < kTransmittanceEps) done = true;
+            }
+        }
+        if (__syncthreads_count(done) == B) break;
+    }
+    seg_T[(size_t)blockIdx.x * B + t] = Tr;
+}
+
+// Per tile with several segments: products of the segments before -> transmittance at segment start.
+template <int T>
+__global__ void __launch_bounds__(T * T) blend_prefix_kernel(const Segment* __restrict__ segs, const uint32_t* __restrict__ tile_first,
+                                                             float* __restrict__ seg_T) {
+    constexpr int B = T * T;
+    const unsigned first = tile_first[blockIdx.x];
+    const unsigned n_seg = segs[first].info >> 16;
+    if (n_seg == 1u) return;
+    const int t = threadIdx.x;
+    float run = 1.0f;
+    for (unsigned s0 = 0; s0 < n_seg; s0 += 8) {
+        float loc[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            const unsigned s = s0 + k;
+            loc[k] = s + 1u < n_seg ? seg_T[(size_t)(first + s) * B + t] : 1.0f;
+        }
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            const unsigned s = s0 + k;
+            if (s < n_seg) seg_T[(size_t)(first + s) * B + t] = run;
+            run *= loc[k];
+        }
+    }
+}
+
 template <int T, int KIND>
 __global__ void __launch_bounds__(T * T) blend_bilinear_forward_kernel(
-    const uint2* __restrict__ ranges, const uint32_t* __restrict__ inst_ids, const PointRec* __restrict__ rec,
+    const Segment* __restrict__ segs, const uint32_t* __restrict__ n_segments, const uint32_t* __restrict__ inst_ids,
+    const PointRec* __restrict__ rec, float* __restrict__ seg_T, float4* __restrict__ seg_C, float* __restrict__ seg_Z,
     float* __restrict__ image, float* __restrict__ depth_image, float* __restrict__ alpha_image,
     float* __restrict__ blending_weights, int width, int height, int gw) {
     constexpr int B = T * T;
     constexpr int WORDS = B / 32;
+    if (blockIdx.x >= *n_segments) return;
+    const Segment sg = segs[blockIdx.x];
+    const unsigned seg_idx = sg.info & 0xffffu, n_seg = sg.info >> 16;
+
     __shared__ float4 s_a[B];
     __shared__ float4 s_f[B];
     __shared__ unsigned s_mask[WORDS][B];
     __shared__ float s_slot[KIND == BLEND_TRAIN ? 4 : 1][B];
 
     const int t = threadIdx.x;
-    const int tile = blockIdx.x;
-    const int tx = tile % gw, ty = tile / gw;
-    const int lx = t % T, ly = t / T;
-    const int px = tx * T + lx, py = ty * T + ly;
+    const int tx = (int)(sg.tile % (unsigned)gw), ty = (int)(sg.tile / (unsigned)gw);
+    const int px = tx * T + t % T, py = ty * T + t / T;
     const bool inside = px < width && py < height;
     const float pcx = (float)px + 0.5f, pcy = (float)py + 0.5f;
+    const size_t state_idx = (size_t)blockIdx.x * B + t;
 
+#pragma unroll
+    for (int w = 0; w < WORDS; ++w) s_mask[w][t] = 0u;
+    if (KIND == BLEND_TRAIN) {
+#pragma unroll
+        for (int q = 0; q < 4; ++q) s_slot[q][t] = 0.0f;
+    }
     float C0 = 0.0f, C1 = 0.0f, C2 = 0.0f, C3 = 0.0f, Z = 0.0f;
     float Tr = 1.0f;
-    bool done = !inside;
+    if (seg_idx > 0u && inside) Tr = seg_T[state_idx];
+    bool done = !inside || Tr < kTransmittanceEps;
+    __syncthreads();
 
-    const uint2 range = __ldg(ranges + tile);
-    for (unsigned base = range.x; base < range.y; base += B) {
-        if (__syncthreads_count(done) == B) break;
-#pragma unroll
-        for (int w = 0; w < WORDS; ++w) s_mask[w][t] = 0u;
-        if (KIND == BLEND_TRAIN) {
-#pragma unroll
-            for (int q = 0; q < 4; ++q) s_slot[q][t] = 0.0f;
-        }
-        __syncthreads();
-        const int cnt = (int)min((unsigned)B, range.y - base);
-        uint32_t id = 0;
+    uint32_t id = 0;
+    int cnt = 0;
+    auto flush_weights = [&]() {
+        // blending weight of the instance staged last by this thread: its (up to) four fragments in
+        // fixed order; the slots are cleared for the next batch
         if (t < cnt) {
-            id = __ldg(inst_ids + base + t);
-            const float4* r = reinterpret_cast<const float4*>(rec + id);
-            const float4 a = __ldg(r);
-            s_a[t] = a;
-            s_f[t] = __ldg(r + 1);
-            // first pixel column/row whose centre is within reach; the second is the next one
-            const int qx = __float2int_rd(a.x - 0.5f) - tx * T;
-            const int qy = __float2int_rd(a.y - 0.5f) - ty * T;
-            const unsigned bit = 1u << (t & 31);
-            unsigned* mrow = s_mask[t >> 5];
-#pragma unroll
-            for (int dy = 0; dy < 2; ++dy)
-#pragma unroll
-                for (int dx = 0; dx < 2; ++dx) {
-                    const int cx = qx + dx, cy = qy + dy;
-                    if (cx >= 0 && cx < T && cy >= 0 && cy < T) atomicOr(mrow + cy * T + cx, bit);
-                }
+            const float sum = ((s_slot[0][t] + s_slot[1][t]) + s_slot[2][t]) + s_slot[3][t];
+            if (sum > 0.0f) atomicAdd(blending_weights + id, sum);
+            s_slot[0][t] = 0.0f; s_slot[1][t] = 0.0f; s_slot[2][t] = 0.0f; s_slot[3][t] = 0.0f;
         }
+    };
+    for (unsigned base = sg.begin; base < sg.end; base += B) {
+        if (KIND == BLEND_TRAIN) flush_weights();
+        cnt = (int)min((unsigned)B, sg.end - base);
+        id = stage_instance<T, true>(t, cnt, base, inst_ids, rec, tx, ty, s_a, s_f, s_mask);
         __syncthreads();
-        if (!done) {
 #pragma unroll 1
-            for (int w = 0; w < WORDS && !done; ++w) {
-                unsigned mbits = s_mask[w][t];
-                while (mbits) {
-                    const int j = w * 32 + __ffs(mbits) - 1;
-                    mbits &= mbits - 1u;
-                    const float4 a = s_a[j];
-                    const float dx = fabsf(a.x - pcx), dy = fabsf(a.y - pcy);
-                    if (dx >= 1.0f || dy >= 1.0f) continue;
-                    const float wgt = __saturatef(1.0f - dx) * __saturatef(1.0f - dy);
-                    const float al = a.z * wgt;
-                    const float bw = Tr * al;
-                    if (KIND == BLEND_TRAIN) {
-                        // corner of the point's 2x2 footprint this pixel is: unique writer per slot
-                        if (bw > 0.0f) s_slot[(pcx > a.x ? 1 : 0) + (pcy > a.y ? 2 : 0)][j] = bw * wgt;
-                    }
-                    const float4 f = s_f[j];
-                    C0 += bw * f.x; C1 += bw * f.y; C2 += bw * f.z; C3 += bw * f.w;
-                    if (KIND == BLEND_INFER) Z += bw * a.w;
-                    Tr *= 1.0f - al;
-                    if (Tr < kTransmittanceEps) { done = true; break; }
+        for (int w = 0; w < WORDS; ++w) {
+            unsigned mbits = s_mask[w][t];
+            if (mbits) s_mask[w][t] = 0u;
+            while (mbits && !done) {
+                const int j = w * 32 + __ffs(mbits) - 1;
+                mbits &= mbits - 1u;
+                const float4 a = s_a[j];
+                const float dx = fabsf(a.x - pcx), dy = fabsf(a.y - pcy);
+                if (dx >= 1.0f || dy >= 1.0f) continue;
+                const float wgt = __saturatef(1.0f - dx) * __saturatef(1.0f - dy);
+                const float al = a.z * wgt;
+                const float bw = Tr * al;
+                if (KIND == BLEND_TRAIN) {
+                    // corner of the point's 2x2 footprint this pixel is: exactly one writer per slot
+                    if (bw > 0.0f) s_slot[(pcx > a.x ? 1 : 0) + (pcy > a.y ? 2 : 0)][j] = bw * wgt;
                 }
+                const float4 f = s_f[j];
+                C0 += bw * f.x; C1 += bw * f.y; C2 += bw * f.z; C3 += bw * f.w;
+                if (KIND == BLEND_INFER) Z += bw * a.w;
+                Tr *= 1.0f - al;
+                if (Tr < kTransmittanceEps) done = true;
             }
         }
-        if (KIND == BLEND_TRAIN) {
-            __syncthreads();
-            if (t < cnt) {
-                const float sum = ((s_slot[0][t] + s_slot[1][t]) + s_slot[2][t]) + s_slot[3][t];
-                if (sum > 0.0f) atomicAdd(blending_weights + id, sum);
+        if (__syncthreads_count(done) == B) break;
+    }
+    if (KIND == BLEND_TRAIN) flush_weights();
+
+    if (n_seg == 1u) {
+        if (inside) {
+            const int64_t n_px = (int64_t)width * height;
+            const int64_t pi = (int64_t)py * width + px;
+            image[pi] = C0;
+            image[n_px + pi] = C1;
+            image[2 * n_px + pi] = C2;
+            image[3 * n_px + pi] = C3;
+            if (KIND == BLEND_INFER) {
+                const float A = 1.0f - Tr;
+                depth_image[pi] = A > 0.0f ? Z / A : 0.0f;
+                alpha_image[pi] = Tr < kTransmittanceEps ? 1.0f : A;
+            } else {
+                alpha_image[pi] = Tr < kTransmittanceEps ? 1.0f : 1.0f - Tr;
             }
+        }
+    } else {
+        // partial colour of this segment; the per-tile combine adds the segments up in order
+        seg_C[state_idx] = make_float4(C0, C1, C2, C3);
+        if (KIND == BLEND_INFER) {
+            seg_Z[state_idx] = Z;
+            seg_T[state_idx] = Tr;
+        } else if (seg_idx == n_seg - 1u && inside) {
+            alpha_image[(int64_t)py * width + px] = Tr < kTransmittanceEps ? 1.0f : 1.0f - Tr;
         }
     }
-    if (inside) {
+}
+
+// Per tile with several segments: image = sum of the segment colours in order.  For training the
+// running sum before each segment is written back (the backward pass starts from it).
+template <int T, int KIND>
+__global__ void __launch_bounds__(T * T) blend_combine_kernel(const Segment* __restrict__ segs, const uint32_t* __restrict__ tile_first,
+                                                              float4* __restrict__ seg_C, const float* __restrict__ seg_Z,
+                                                              const float* __restrict__ seg_T, float* __restrict__ image,
+                                                              float* __restrict__ depth_image, float* __restrict__ alpha_image,
+                                                              int width, int height, int gw) {
+    constexpr int B = T * T;
+    const unsigned first = tile_first[blockIdx.x];
+    const unsigned n_seg = segs[first].info >> 16;
+    if (n_seg == 1u) return;
+    const int t = threadIdx.x;
+    const int tx = (int)(blockIdx.x % (unsigned)gw), ty = (int)(blockIdx.x / (unsigned)gw);
+    const int px = tx * T + t % T, py = ty * T + t / T;
+    float4 run = make_float4(0.f, 0.f, 0.f, 0.f);
+    float z = 0.0f;
+    for (unsigned s0 = 0; s0 < n_seg; s0 += 4) {
+        float4 c[4];
+        float zz[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const unsigned s = s0 + k;
+            c[k] = s < n_seg ? seg_C[(size_t)(first + s) * B + t] : make_float4(0.f, 0.f, 0.f, 0.f);
+            zz[k] = (KIND == BLEND_INFER && s < n_seg) ? seg_Z[(size_t)(first + s) * B + t] : 0.0f;
+        }
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const unsigned s = s0 + k;
+            if (KIND == BLEND_TRAIN && s < n_seg) seg_C[(size_t)(first + s) * B + t] = run;
+            run.x += c[k].x; run.y += c[k].y; run.z += c[k].z; run.w += c[k].w;
+            z += zz[k];
+        }
+    }
+    if (px < width && py < height) {
         const int64_t n_px = (int64_t)width * height;
         const int64_t pi = (int64_t)py * width + px;
-        image[pi] = C0;
-        image[n_px + pi] = C1;
-        image[2 * n_px + pi] = C2;
-        image[3 * n_px + pi] = C3;
+        image[pi] = run.x;
+        image[n_px + pi] = run.y;
+        image[2 * n_px + pi] = run.z;
+        image[3 * n_px + pi] = run.w;
         if (KIND == BLEND_INFER) {
+            const float Tr = seg_T[(size_t)(first + n_seg - 1u) * B + t];
             const float A = 1.0f - Tr;
-            depth_image[pi] = A > 0.0f ? Z / A : 0.0f;
+            depth_image[pi] = A > 0.0f ? z / A : 0.0f;
             alpha_image[pi] = Tr < kTransmittanceEps ? 1.0f : A;
-        } else {
-            alpha_image[pi] = Tr < kTransmittanceEps ? 1.0f : 1.0f - Tr;
         }
     }
 }
 
 template <int T>
 __global__ void __launch_bounds__(T * T) blend_bilinear_backward_kernel(
-    const uint2* __restrict__ ranges, const uint32_t* __restrict__ inst_ids, const PointRec* __restrict__ rec,
+    const Segment* __restrict__ segs, const uint32_t* __restrict__ n_segments, const uint32_t* __restrict__ inst_ids,
+    const PointRec* __restrict__ rec, const float* __restrict__ seg_T, const float4* __restrict__ seg_C,
     const float* __restrict__ grad_image, const float* __restrict__ grad_alpha, const float* __restrict__ image,
     const float* __restrict__ alpha_image, float4* __restrict__ grad_feat_view, float* __restrict__ grad_opacity,
     int width, int height, int gw) {
     constexpr int B = T * T;
     constexpr int WORDS = B / 32;
+    if (blockIdx.x >= *n_segments) return;
+    const Segment sg = segs[blockIdx.x];
+    const unsigned seg_idx = sg.info & 0xffffu;
+    if (sg.begin == sg.end) return;
+
     __shared__ float4 s_a[B];
     __shared__ float4 s_f[B];
     __shared__ unsigned s_mask[WORDS][B];
-    __shared__ float4 s_gf[4][B];    // per corner: feature gradient contribution
-    __shared__ float s_go[4][B];     // per corner: opacity gradient contribution
+    __shared__ float4 s_gf[4][B];    // per footprint corner: feature gradient contribution
+    __shared__ float s_go[4][B];     // per footprint corner: opacity gradient contribution
 
     const int t = threadIdx.x;
-    const int tile = blockIdx.x;
-    const int tx = tile % gw, ty = tile / gw;
-    const int lx = t % T, ly = t / T;
-    const int px = tx * T + lx, py = ty * T + ly;
+    const int tx = (int)(sg.tile % (unsigned)gw), ty = (int)(sg.tile / (unsigned)gw);
+    const int px = tx * T + t % T, py = ty * T + t / T;
     const bool inside = px < width && py < height;
     const float pcx = (float)px + 0.5f, pcy = (float)py + 0.5f;
+    const size_t state_idx = (size_t)blockIdx.x * B + t;
+
+#pragma unroll
+    for (int w = 0; w < WORDS; ++w) s_mask[w][t] = 0u;
+#pragma unroll
+    for (int q = 0; q < 4; ++q) { s_gf[q][t] = make_float4(0.f, 0.f, 0.f, 0.f); s_go[q][t] = 0.0f; }
 
     float4 g = make_float4(0.f, 0.f, 0.f, 0.f), Cfin = make_float4(0.f, 0.f, 0.f, 0.f);
-    float K = 0.0f;
+    float4 Crun = make_float4(0.f, 0.f, 0.f, 0.f);
+    float K = 0.0f, Tr = 1.0f;
     if (inside) {
         const int64_t n_px = (int64_t)width * height;
         const int64_t pi = (int64_t)py * width + px;
@@ -515,72 +761,14 @@ __global__ void __launch_bounds__(T * T) blend_bilinear_backward_kernel(
         Cfin = make_float4(__ldg(image + pi), __ldg(image + n_px + pi), __ldg(image + 2 * n_px + pi),
                            __ldg(image + 3 * n_px + pi));
         K = __ldg(grad_alpha + pi) * (1.0f - __ldg(alpha_image + pi));
+        if (seg_idx > 0u) { Tr = seg_T[state_idx]; Crun = seg_C[state_idx]; }
     }
-    float4 Crun = make_float4(0.f, 0.f, 0.f, 0.f);
-    float Tr = 1.0f;
-    bool done = !inside;
+    bool done = !inside || Tr < kTransmittanceEps;
+    __syncthreads();
 
-    const uint2 range = __ldg(ranges + tile);
-    for (unsigned base = range.x; base < range.y; base += B) {
-        if (__syncthreads_count(done) == B) break;
-#pragma unroll
-        for (int w = 0; w < WORDS; ++w) s_mask[w][t] = 0u;
-#pragma unroll
-        for (int q = 0; q < 4; ++q) { s_gf[q][t] = make_float4(0.f, 0.f, 0.f, 0.f); s_go[q][t] = 0.0f; }
-        __syncthreads();
-        const int cnt = (int)min((unsigned)B, range.y - base);
-        uint32_t id = 0;
-        if (t < cnt) {
-            id = __ldg(inst_ids + base + t);
-            const float4* r = reinterpret_cast<const float4*>(rec + id);
-            const float4 a = __ldg(r);
-            s_a[t] = a;
-            s_f[t] = __ldg(r + 1);
-            const int qx = __float2int_rd(a.x - 0.5f) - tx * T;
-            const int qy = __float2int_rd(a.y - 0.5f) - ty * T;
-            const unsigned bit = 1u << (t & 31);
-            unsigned* mrow = s_mask[t >> 5];
-#pragma unroll
-            for (int dy = 0; dy < 2; ++dy)
-#pragma unroll
-                for (int dx = 0; dx < 2; ++dx) {
-                    const int cx = qx + dx, cy = qy + dy;
-                    if (cx >= 0 && cx < T && cy >= 0 && cy < T) atomicOr(mrow + cy * T + cx, bit);
-                }
-        }
-        __syncthreads();
-        if (!done) {
-#pragma unroll 1
-            for (int w = 0; w < WORDS && !done; ++w) {
-                unsigned mbits = s_mask[w][t];
-                while (mbits) {
-                    const int j = w * 32 + __ffs(mbits) - 1;
-                    mbits &= mbits - 1u;
-                    const float4 a = s_a[j];
-                    const float dx = fabsf(a.x - pcx), dy = fabsf(a.y - pcy);
-                    if (dx >= 1.0f || dy >= 1.0f) continue;
-                    const float wgt = __saturatef(1.0f - dx) * __saturatef(1.0f - dy);
-                    const float al = a.z * wgt;
-                    const float bw = Tr * al;
-                    const int q = (pcx > a.x ? 1 : 0) + (pcy > a.y ? 2 : 0);
-                    if (bw > 0.0f) s_gf[q][j] = make_float4(bw * g.x, bw * g.y, bw * g.z, bw * g.w);
-                    const float4 f = s_f[j];
-                    Crun.x += bw * f.x; Crun.y += bw * f.y; Crun.z += bw * f.z; Crun.w += bw * f.w;
-                    const float oma = 1.0f - al;
-                    const float rcp = 1.0f / fmaxf(oma, kOneMinusAlphaEps);
-                    const float from_features = (Tr * f.x + (Crun.x - Cfin.x) * rcp) * g.x +
-                                                (Tr * f.y + (Crun.y - Cfin.y) * rcp) * g.y +
-                                                (Tr * f.z + (Crun.z - Cfin.z) * rcp) * g.z +
-                                                (Tr * f.w + (Crun.w - Cfin.w) * rcp) * g.w;
-                    const float dalpha = from_features + K * rcp;
-                    const float dop = dalpha * wgt;
-                    if (dop != 0.0f) s_go[q][j] = dop;
-                    Tr *= oma;
-                    if (Tr < kTransmittanceEps) { done = true; break; }
-                }
-            }
-        }
-        __syncthreads();
+    uint32_t id = 0;
+    int cnt = 0;
+    auto flush_gradients = [&]() {
         if (t < cnt) {
             float4 sf = s_gf[0][t];
             float so = s_go[0][t];
@@ -592,8 +780,48 @@ __global__ void __launch_bounds__(T * T) blend_bilinear_backward_kernel(
             }
             if (sf.x != 0.0f || sf.y != 0.0f || sf.z != 0.0f || sf.w != 0.0f) atomicAdd(grad_feat_view + id, sf);
             if (so != 0.0f) atomicAdd(grad_opacity + id, so);
+#pragma unroll
+            for (int q = 0; q < 4; ++q) { s_gf[q][t] = make_float4(0.f, 0.f, 0.f, 0.f); s_go[q][t] = 0.0f; }
         }
+    };
+    for (unsigned base = sg.begin; base < sg.end; base += B) {
+        flush_gradients();
+        cnt = (int)min((unsigned)B, sg.end - base);
+        id = stage_instance<T, true>(t, cnt, base, inst_ids, rec, tx, ty, s_a, s_f, s_mask);
+        __syncthreads();
+#pragma unroll 1
+        for (int w = 0; w < WORDS; ++w) {
+            unsigned mbits = s_mask[w][t];
+            if (mbits) s_mask[w][t] = 0u;
+            while (mbits && !done) {
+                const int j = w * 32 + __ffs(mbits) - 1;
+                mbits &= mbits - 1u;
+                const float4 a = s_a[j];
+                const float dx = fabsf(a.x - pcx), dy = fabsf(a.y - pcy);
+                if (dx >= 1.0f || dy >= 1.0f) continue;
+                const float wgt = __saturatef(1.0f - dx) * __saturatef(1.0f - dy);
+                const float al = a.z * wgt;
+                const float bw = Tr * al;
+                const int q = (pcx > a.x ? 1 : 0) + (pcy > a.y ? 2 : 0);
+                if (bw > 0.0f) s_gf[q][j] = make_float4(bw * g.x, bw * g.y, bw * g.z, bw * g.w);
+                const float4 f = s_f[j];
+                Crun.x += bw * f.x; Crun.y += bw * f.y; Crun.z += bw * f.z; Crun.w += bw * f.w;
+                const float oma = 1.0f - al;
+                const float rcp = 1.0f / fmaxf(oma, kOneMinusAlphaEps);
+                const float from_features = (Tr * f.x + (Crun.x - Cfin.x) * rcp) * g.x +
+                                            (Tr * f.y + (Crun.y - Cfin.y) * rcp) * g.y +
+                                            (Tr * f.z + (Crun.z - Cfin.z) * rcp) * g.z +
+                                            (Tr * f.w + (Crun.w - Cfin.w) * rcp) * g.w;
+                const float dalpha = from_features + K * rcp;
+                const float dop = dalpha * wgt;
+                if (dop != 0.0f) s_go[q][j] = dop;
+                Tr *= oma;
+                if (Tr < kTransmittanceEps) done = true;
+            }
+        }
+        if (__syncthreads_count(done) == B) break;
     }
+    flush_gradients();
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -826,16 +1054,36 @@ struct InstanceBlob {
     uint32_t* keys[2];
     uint32_t* ids[2];
     uint2* ranges;
+    Segment* segs;
+    uint32_t* tile_first;
+    uint32_t* n_segments;
+    float* seg_T;
+    float4* seg_C;
+    float* seg_Z;
+    int64_t max_segments;
     void* sort_ws;
     size_t total;
 };
 
-InstanceBlob carve_instance_blob(void* p, int64_t n_instances, int n_tiles) {
+// Upper bound on the number of (tile, segment) work items, known from the instance count alone.
+int64_t max_segments(int64_t n_instances, int n_tiles, int tile) {
+    return (int64_t)n_tiles + ceil_div<int64_t>(n_instances, (int64_t)tile * tile * kMinBatchesPerSegment);
+}
+
+InstanceBlob carve_instance_blob(void* p, int64_t n_instances, int n_tiles, int tile, int mode, bool with_depth) {
     InstanceBlob b;
     Carver c(p);
     b.ranges = c.take<uint2>(n_tiles);
     for (int k = 0; k < 2; ++k) b.keys[k] = c.take<uint32_t>(n_instances);
     for (int k = 0; k < 2; ++k) b.ids[k] = c.take<uint32_t>(n_instances);
+    b.max_segments = mode == INPC_MODE_BILINEAR ? max_segments(n_instances, n_tiles, tile) : 0;
+    const size_t px = (size_t)b.max_segments * tile * tile;
+    b.segs = c.take<Segment>(b.max_segments);
+    b.tile_first = c.take<uint32_t>(n_tiles);
+    b.n_segments = c.take<uint32_t>(4);
+    b.seg_T = c.take<float>(px);
+    b.seg_C = c.take<float4>(px);
+    b.seg_Z = c.take<float>(with_depth ? px : 0);
     c.off = align_up(c.off);
     b.sort_ws = c.base + c.off;
     c.off += sort_workspace_bytes(n_instances);
@@ -872,7 +1120,7 @@ int check_view(const inpc_view* v, int tile_size, int mode, int64_t n) {
 template <int MODE, int VARIANT>
 int run_front(const RasterParams& rp, int64_t n, const float* positions, const void* features, const float* opacities,
               inpc_alloc_fn alloc_point, inpc_alloc_fn alloc_instance, void* user, inpc_raster_state* st,
-              PointBlob* pb_out, InstanceBlob* ib_out, cudaStream_t stream) {
+              bool with_depth, PointBlob* pb_out, InstanceBlob* ib_out, cudaStream_t stream) {
     const int n_tiles = rp.gw * rp.gh;
     const int64_t nb = ceil_div<int64_t>(n > 0 ? n : 1, kPreThreads);
     // phase 1 needs only n: allocate for the worst case n_visible == n so that one blob serves both phases
@@ -906,10 +1154,10 @@ int run_front(const RasterParams& rp, int64_t n, const float* positions, const v
     // re-carve with the true visible count: the leading arrays keep their place
     pb = carve_point_blob(pblob, n, n_visible, MODE);
 
-    const InstanceBlob isz = carve_instance_blob(nullptr, n_instances, n_tiles);
+    const InstanceBlob isz = carve_instance_blob(nullptr, n_instances, n_tiles, rp.tile, MODE, with_depth);
     void* iblob = alloc_instance(user, isz.total);
     if (!iblob) { set_error("instance allocator returned NULL for %zu bytes", isz.total); return INPC_E_ALLOC; }
-    InstanceBlob ib = carve_instance_blob(iblob, n_instances, n_tiles);
+    InstanceBlob ib = carve_instance_blob(iblob, n_instances, n_tiles, rp.tile, MODE, with_depth);
     INPC_CUDA_TRY(cudaMemsetAsync(ib.ranges, 0, sizeof(uint2) * (size_t)n_tiles, stream));
 
     if (n > 0) {
@@ -945,6 +1193,11 @@ int run_front(const RasterParams& rp, int64_t n, const float* positions, const v
         tile_ranges_kernel<<<(unsigned)ceil_div<int64_t>(n_instances, 256), 256, 0, stream>>>(ib.keys[t_alt], n_instances, ib.ranges);
         INPC_LAUNCH_CHECK("tile_ranges_kernel");
     }
+    if (MODE == INPC_MODE_BILINEAR) {
+        StageScope scope(STAGE_SORT_TILE, stream);
+        build_segments_kernel<<<1, kScanThreads, 0, stream>>>(ib.ranges, n_tiles, rp.tile * rp.tile, ib.segs, ib.tile_first, ib.n_segments);
+        INPC_LAUNCH_CHECK("build_segments_kernel");
+    }
     st->point_blob = pblob;
     st->instance_blob = iblob;
     st->n_points = n;
@@ -969,6 +1222,25 @@ RasterParams make_params(const inpc_view* view, int tile_size, float sigma_world
     return rp;
 }
 
+template <int T, int KIND>
+int launch_bilinear_forward(const RasterParams& rp, const PointBlob& pb, const InstanceBlob& ib, const uint32_t* ids, float* image,
+                            float* depth, float* alpha, float* blending_weights, cudaStream_t stream) {
+    const int n_tiles = rp.gw * rp.gh;
+    const int W = rp.v.width, H = rp.v.height;
+    const unsigned grid = (unsigned)ib.max_segments;
+    blend_bilinear_transmittance_kernel<T><<<grid, T * T, 0, stream>>>(ib.segs, ib.n_segments, ids, pb.rec, ib.seg_T, W, H, rp.gw);
+    INPC_LAUNCH_CHECK("blend_bilinear_transmittance_kernel");
+    blend_prefix_kernel<T><<<n_tiles, T * T, 0, stream>>>(ib.segs, ib.tile_first, ib.seg_T);
+    INPC_LAUNCH_CHECK("blend_prefix_kernel");
+    blend_bilinear_forward_kernel<T, KIND><<<grid, T * T, 0, stream>>>(ib.segs, ib.n_segments, ids, pb.rec, ib.seg_T, ib.seg_C, ib.seg_Z,
+                                                                      image, depth, alpha, blending_weights, W, H, rp.gw);
+    INPC_LAUNCH_CHECK("blend_bilinear_forward_kernel");
+    blend_combine_kernel<T, KIND><<<n_tiles, T * T, 0, stream>>>(ib.segs, ib.tile_first, ib.seg_C, ib.seg_Z, ib.seg_T, image, depth, alpha,
+                                                                W, H, rp.gw);
+    INPC_LAUNCH_CHECK("blend_combine_kernel");
+    return INPC_OK;
+}
+
 template <int KIND>
 int launch_blend_forward(int mode, const RasterParams& rp, const PointBlob& pb, const InstanceBlob& ib, int64_t n_instances,
                          float* image, float* depth, float* alpha, float* blending_weights, float threshold,
@@ -978,16 +1250,13 @@ int launch_blend_forward(int mode, const RasterParams& rp, const PointBlob& pb, 
     const int W = rp.v.width, H = rp.v.height;
     StageScope scope(STAGE_BLEND_FWD, stream);
     if (mode == INPC_MODE_BILINEAR) {
-        if (rp.tile == 8)
-            blend_bilinear_forward_kernel<8, KIND><<<n_tiles, 64, 0, stream>>>(ib.ranges, ids, pb.rec, image, depth, alpha, blending_weights, W, H, rp.gw);
-        else
-            blend_bilinear_forward_kernel<16, KIND><<<n_tiles, 256, 0, stream>>>(ib.ranges, ids, pb.rec, image, depth, alpha, blending_weights, W, H, rp.gw);
-    } else {
-        if (rp.tile == 8)
-            blend_gaussian_forward_kernel<8, KIND><<<n_tiles, 64, 0, stream>>>(ib.ranges, ids, pb.rec, pb.conic, image, depth, alpha, blending_weights, W, H, rp.gw, threshold);
-        else
-            blend_gaussian_forward_kernel<16, KIND><<<n_tiles, 256, 0, stream>>>(ib.ranges, ids, pb.rec, pb.conic, image, depth, alpha, blending_weights, W, H, rp.gw, threshold);
+        if (rp.tile == 8) return launch_bilinear_forward<8, KIND>(rp, pb, ib, ids, image, depth, alpha, blending_weights, stream);
+        return launch_bilinear_forward<16, KIND>(rp, pb, ib, ids, image, depth, alpha, blending_weights, stream);
     }
+    if (rp.tile == 8)
+        blend_gaussian_forward_kernel<8, KIND><<<n_tiles, 64, 0, stream>>>(ib.ranges, ids, pb.rec, pb.conic, image, depth, alpha, blending_weights, W, H, rp.gw, threshold);
+    else
+        blend_gaussian_forward_kernel<16, KIND><<<n_tiles, 256, 0, stream>>>(ib.ranges, ids, pb.rec, pb.conic, image, depth, alpha, blending_weights, W, H, rp.gw, threshold);
     INPC_LAUNCH_CHECK("blend_forward_kernel");
     return INPC_OK;
 }
@@ -1014,9 +1283,9 @@ extern "C" int inpc_rasterize_forward(int mode, int tile_size, const inpc_view* 
     PointBlob pb;
     InstanceBlob ib;
     if (mode == INPC_MODE_BILINEAR)
-        rc = run_front<INPC_MODE_BILINEAR, VAR_TRAIN>(rp, n, positions, features, opacities, alloc_point, alloc_instance, alloc_user, state, &pb, &ib, stream);
+        rc = run_front<INPC_MODE_BILINEAR, VAR_TRAIN>(rp, n, positions, features, opacities, alloc_point, alloc_instance, alloc_user, state, false, &pb, &ib, stream);
     else
-        rc = run_front<INPC_MODE_GAUSSIAN, VAR_TRAIN>(rp, n, positions, features, opacities, alloc_point, alloc_instance, alloc_user, state, &pb, &ib, stream);
+        rc = run_front<INPC_MODE_GAUSSIAN, VAR_TRAIN>(rp, n, positions, features, opacities, alloc_point, alloc_instance, alloc_user, state, false, &pb, &ib, stream);
     if (rc != INPC_OK) return rc;
     return launch_blend_forward<BLEND_TRAIN>(mode, rp, pb, ib, state->n_instances, image, nullptr, alpha, blending_weights, kTrainGaussThreshold, stream);
 }
@@ -1039,7 +1308,7 @@ extern "C" int inpc_rasterize_backward(const inpc_raster_state* state, const inp
     const RasterParams rp = make_params(view, state->tile_size, 0.0f, 3.0f, nullptr);
     const int n_tiles = rp.gw * rp.gh;
     const PointBlob pb = carve_point_blob(state->point_blob, n, state->n_visible, state->mode);
-    const InstanceBlob ib = carve_instance_blob(state->instance_blob, state->n_instances, n_tiles);
+    const InstanceBlob ib = carve_instance_blob(state->instance_blob, state->n_instances, n_tiles, state->tile_size, state->mode, false);
     const uint32_t* ids = ib.ids[tile_result_buffer(state->n_instances, n_tiles)];
     INPC_CUDA_TRY(cudaMemsetAsync(grad_features_view, 0, sizeof(float4) * (size_t)n, stream));
     INPC_CUDA_TRY(cudaMemsetAsync(grad_opacities, 0, sizeof(float) * (size_t)n, stream));
@@ -1049,9 +1318,9 @@ extern "C" int inpc_rasterize_backward(const inpc_raster_state* state, const inp
         StageScope scope(STAGE_BLEND_BWD, stream);
         if (state->mode == INPC_MODE_BILINEAR) {
             if (rp.tile == 8)
-                blend_bilinear_backward_kernel<8><<<n_tiles, 64, 0, stream>>>(ib.ranges, ids, pb.rec, grad_image, grad_alpha, image, alpha, gfv, grad_opacities, W, H, rp.gw);
+                blend_bilinear_backward_kernel<8><<<(unsigned)ib.max_segments, 64, 0, stream>>>(ib.segs, ib.n_segments, ids, pb.rec, ib.seg_T, ib.seg_C, grad_image, grad_alpha, image, alpha, gfv, grad_opacities, W, H, rp.gw);
             else
-                blend_bilinear_backward_kernel<16><<<n_tiles, 256, 0, stream>>>(ib.ranges, ids, pb.rec, grad_image, grad_alpha, image, alpha, gfv, grad_opacities, W, H, rp.gw);
+                blend_bilinear_backward_kernel<16><<<(unsigned)ib.max_segments, 256, 0, stream>>>(ib.segs, ib.n_segments, ids, pb.rec, ib.seg_T, ib.seg_C, grad_image, grad_alpha, image, alpha, gfv, grad_opacities, W, H, rp.gw);
         } else {
             if (rp.tile == 8)
                 blend_gaussian_backward_kernel<8><<<n_tiles, 64, 0, stream>>>(ib.ranges, ids, pb.rec, pb.conic, grad_image, grad_alpha, image, alpha, gfv, grad_opacities, W, H, rp.gw);
@@ -1083,9 +1352,9 @@ extern "C" int inpc_render(int mode, int tile_size, const inpc_view* view, int64
     PointBlob pb;
     InstanceBlob ib;
     if (mode == INPC_MODE_BILINEAR)
-        rc = run_front<INPC_MODE_BILINEAR, VAR_RAW37>(rp, n, positions, features_raw, nullptr, alloc_point, alloc_instance, alloc_user, &st, &pb, &ib, stream);
+        rc = run_front<INPC_MODE_BILINEAR, VAR_RAW37>(rp, n, positions, features_raw, nullptr, alloc_point, alloc_instance, alloc_user, &st, true, &pb, &ib, stream);
     else
-        rc = run_front<INPC_MODE_GAUSSIAN, VAR_RAW37>(rp, n, positions, features_raw, nullptr, alloc_point, alloc_instance, alloc_user, &st, &pb, &ib, stream);
+        rc = run_front<INPC_MODE_GAUSSIAN, VAR_RAW37>(rp, n, positions, features_raw, nullptr, alloc_point, alloc_instance, alloc_user, &st, true, &pb, &ib, stream);
     if (rc != INPC_OK) return rc;
     // runtime cut-off exp(-cutoff^2/2): src/gaussian/inference.cu:171
     const float threshold = expf(-0.5f * sigma_cutoff * sigma_cutoff);
@@ -1109,9 +1378,9 @@ extern "C" int inpc_render_preextracted(int mode, int tile_size, const inpc_view
     PointBlob pb;
     InstanceBlob ib;
     if (mode == INPC_MODE_BILINEAR)
-        rc = run_front<INPC_MODE_BILINEAR, VAR_PREEXTRACTED>(rp, n, positions, features, opacities, alloc_point, alloc_instance, alloc_user, &st, &pb, &ib, stream);
+        rc = run_front<INPC_MODE_BILINEAR, VAR_PREEXTRACTED>(rp, n, positions, features, opacities, alloc_point, alloc_instance, alloc_user, &st, true, &pb, &ib, stream);
     else
-        rc = run_front<INPC_MODE_GAUSSIAN, VAR_PREEXTRACTED>(rp, n, positions, features, opacities, alloc_point, alloc_instance, alloc_user, &st, &pb, &ib, stream);
+        rc = run_front<INPC_MODE_GAUSSIAN, VAR_PREEXTRACTED>(rp, n, positions, features, opacities, alloc_point, alloc_instance, alloc_user, &st, true, &pb, &ib, stream);
     if (rc != INPC_OK) return rc;
     const float threshold = expf(-0.5f * sigma_cutoff * sigma_cutoff);
     return launch_blend_forward<BLEND_INFER>(mode, rp, pb, ib, st.n_instances, image, depth, alpha, nullptr, threshold, stream);
@@ -1144,7 +1413,7 @@ extern "C" int inpc_raster_debug_copy(const inpc_raster_state* state, const inpc
     const int gw = ceil_div(view->width, state->tile_size), gh = ceil_div(view->height, state->tile_size);
     const int n_tiles = gw * gh;
     const PointBlob pb = carve_point_blob(state->point_blob, state->n_points, state->n_visible, state->mode);
-    const InstanceBlob ib = carve_instance_blob(state->instance_blob, state->n_instances, n_tiles);
+    const InstanceBlob ib = carve_instance_blob(state->instance_blob, state->n_instances, n_tiles, state->tile_size, state->mode, false);
     const int d = depth_result_buffer(state->n_visible);
     const int ti = tile_result_buffer(state->n_instances, n_tiles);
     switch (which) {

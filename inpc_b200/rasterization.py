@@ -116,6 +116,10 @@ class _Blobs:
 
 
 def _check(status: int, blobs: _Blobs | None = None) -> None:
+    if blobs is not None:
+        # the ctypes callbacks hold bound methods of `blobs`: drop them, or the reference cycle keeps
+        # the scratch tensors alive until the cyclic garbage collector runs
+        blobs.cb_point = blobs.cb_instance = None
     if status != 0 and blobs is not None and blobs.error is not None:
         raise blobs.error
     _cabi.check(status)

@@ -350,7 +350,8 @@ def test_full_size_properties():
         out[tile] = (image, alpha, bw)
         again = R.forward_with_state(pos, feats, opac, settings, tile)
         assert torch.equal(again[0], image) and torch.equal(again[1], alpha)
-    assert torch.equal(out[8][0], out[16][0]) and torch.equal(out[8][1], out[16][1])
-    assert torch.allclose(out[8][2], out[16][2], rtol=1e-5, atol=1e-7)
+    # the image does not depend on the tiling, up to the summation order of per-segment partial colours
+    assert torch.allclose(out[8][0], out[16][0], rtol=1e-5, atol=1e-6) and torch.allclose(out[8][1], out[16][1], rtol=1e-5, atol=1e-6)
+    assert torch.allclose(out[8][2], out[16][2], rtol=1e-5, atol=1e-6)
     covered = out[8][1] > 0
     assert 0.2 < covered.float().mean().item() <= 1.0
