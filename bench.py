@@ -50,7 +50,7 @@ def parse_args():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--views", type=int, default=N_VIEWS)
     ap.add_argument("--points", type=int, default=N_POINTS)
-    ap.add_argument("--tile", type=int, default=16)
+    ap.add_argument("--tile", type=int, default=8)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     return ap.parse_args()
 

@@ -6,10 +6,12 @@ no fallback: if the library is missing or a call fails, an exception is raised.
 from __future__ import annotations
 
 import ctypes as C
+import os
 from pathlib import Path
 
 _PKG = Path(__file__).resolve().parent
-LIB_PATH = _PKG / "libinpc_b200.so"
+# INPC_B200_LIB selects another build of the same library (e.g. one compiled with different tuning macros)
+LIB_PATH = Path(os.environ.get("INPC_B200_LIB", _PKG / "libinpc_b200.so"))
 
 ALLOC_FN = C.CFUNCTYPE(C.c_void_p, C.c_void_p, C.c_size_t)
 

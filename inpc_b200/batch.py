@@ -67,7 +67,7 @@ class ViewShardedTrainer:
     """Runs sample -> rasterize -> backward for this rank's share of a batch of views."""
 
     def __init__(self, tree, features: torch.Tensor, opacities: torch.Tensor, n_samples: int, seed: int,
-                 n_appearance: int = 1 << 22, tile_size: int = 16, mode: int = 0):
+                 n_appearance: int = 1 << 22, tile_size: int = 8, mode: int = 0):
         from .rasterization import INPCRasterizer
         from .sampling import ProbabilityFieldSampler
         self.tree = tree

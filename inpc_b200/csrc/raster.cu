@@ -15,6 +15,10 @@
 // instead of testing every staged point against every pixel.
 #include "common.cuh"
 
+#ifndef INPC_MIN_BATCHES
+#define INPC_MIN_BATCHES 16
+#endif
+
 namespace inpc {
 
 namespace {
@@ -418,7 +422,13 @@ struct __align__(16) Segment {
     uint32_t info;         // index of the segment within its tile | number of segments of the tile << 16
 };
 constexpr int kMaxSegmentsPerTile = 64;
-constexpr int kMinBatchesPerSegment = 16;
+constexpr int kMinBatchesPerSegment = INPC_MIN_BATCHES;
+#ifndef INPC_IPT8
+#define INPC_IPT8 1
+#endif
+#ifndef INPC_IPT16
+#define INPC_IPT16 1
+#endif
 
 // One block: per tile the number of segments, their exclusive scan, and the segment records.
 __global__ void __launch_bounds__(kScanThreads) build_segments_kernel(const uint2* __restrict__ ranges, int n_tiles, int batch,
@@ -457,24 +467,24 @@ __global__ void __launch_bounds__(kScanThreads) build_segments_kernel(const uint
     if (threadIdx.x == 0) *n_segments = running;
 }
 
-// Stages instance `t` of the batch starting at `base`: record into shared memory, bit into the masks of
+// Stages instance `j` of the batch starting at `base`: record into shared memory, bit into the masks of
 // the pixels it reaches.  Returns the point id.
-template <int T, bool NEED_F>
-__device__ __forceinline__ uint32_t stage_instance(int t, int cnt, unsigned base, const uint32_t* __restrict__ inst_ids,
+template <int T, int B, bool NEED_F>
+__device__ __forceinline__ uint32_t stage_instance(int j, int cnt, unsigned base, const uint32_t* __restrict__ inst_ids,
                                                    const PointRec* __restrict__ rec, int tile_x, int tile_y, float4* s_a,
                                                    float4* s_f, unsigned (*s_mask)[T * T]) {
     uint32_t id = 0;
-    if (t < cnt) {
-        id = __ldg(inst_ids + base + t);
+    if (j < cnt) {
+        id = __ldg(inst_ids + base + j);
         const float4* r = reinterpret_cast<const float4*>(rec + id);
         const float4 a = __ldg(r);
-        s_a[t] = a;
-        if (NEED_F) s_f[t] = __ldg(r + 1);
+        s_a[j] = a;
+        if (NEED_F) s_f[j] = __ldg(r + 1);
         // first pixel column / row whose centre is within reach; the second is the next one
         const int qx = __float2int_rd(a.x - 0.5f) - tile_x * T;
         const int qy = __float2int_rd(a.y - 0.5f) - tile_y * T;
-        const unsigned bit = 1u << (t & 31);
-        unsigned* mrow = s_mask[t >> 5];
+        const unsigned bit = 1u << (j & 31);
+        unsigned* mrow = s_mask[j >> 5];
 #pragma unroll
         for (int dy = 0; dy < 2; ++dy)
 #pragma unroll
@@ -487,11 +497,13 @@ __device__ __forceinline__ uint32_t stage_instance(int t, int cnt, unsigned base
 }
 
 // Pass 1 (tiles with several segments only): per-pixel product of (1 - alpha) over one segment.
-template <int T>
+// A block is one (tile, segment): T*T threads = pixels, batches of B = T*T*IPT instances.
+template <int T, int IPT>
 __global__ void __launch_bounds__(T * T) blend_bilinear_transmittance_kernel(
     const Segment* __restrict__ segs, const uint32_t* __restrict__ n_segments, const uint32_t* __restrict__ inst_ids,
     const PointRec* __restrict__ rec, float* __restrict__ seg_T, int width, int height, int gw) {
-    constexpr int B = T * T;
+    constexpr int P = T * T;
+    constexpr int B = P * IPT;
     constexpr int WORDS = B / 32;
     if (blockIdx.x >= *n_segments) return;
     const Segment sg = segs[blockIdx.x];
@@ -499,7 +511,7 @@ __global__ void __launch_bounds__(T * T) blend_bilinear_transmittance_kernel(
     if (n_seg == 1u || seg_idx == n_seg - 1u) return;   // the last segment's product is never needed
 
     __shared__ float4 s_a[B];
-    __shared__ unsigned s_mask[WORDS][B];
+    __shared__ unsigned s_mask[WORDS][P];
     const int t = threadIdx.x;
     const int tx = (int)(sg.tile % (unsigned)gw), ty = (int)(sg.tile / (unsigned)gw);
     const int px = tx * T + t % T, py = ty * T + t / T;
@@ -512,7 +524,8 @@ __global__ void __launch_bounds__(T * T) blend_bilinear_transmittance_kernel(
     bool done = !inside;
     for (unsigned base = sg.begin; base < sg.end; base += B) {
         const int cnt = (int)min((unsigned)B, sg.end - base);
-        stage_instance<T, false>(t, cnt, base, inst_ids, rec, tx, ty, s_a, nullptr, s_mask);
+#pragma unroll
+        for (int k = 0; k < IPT; ++k) stage_instance<T, B, false>(t + k * P, cnt, base, inst_ids, rec, tx, ty, s_a, nullptr, s_mask);
         __syncthreads();
 #pragma unroll 1
         for (int w = 0; w < WORDS; ++w) {
@@ -529,16 +542,16 @@ __global__ void __launch_bounds__(T * T) blend_bilinear_transmittance_kernel(
                 if (Tr < kTransmittanceEps) done = true;
             }
         }
-        if (__syncthreads_count(done) == B) break;
+        if (__syncthreads_count(done) == P) break;
     }
-    seg_T[(size_t)blockIdx.x * B + t] = Tr;
+    seg_T[(size_t)blockIdx.x * P + t] = Tr;
 }
 
 // Per tile with several segments: products of the segments before -> transmittance at segment start.
 template <int T>
 __global__ void __launch_bounds__(T * T) blend_prefix_kernel(const Segment* __restrict__ segs, const uint32_t* __restrict__ tile_first,
                                                              float* __restrict__ seg_T) {
-    constexpr int B = T * T;
+    constexpr int P = T * T;
     const unsigned first = tile_first[blockIdx.x];
     const unsigned n_seg = segs[first].info >> 16;
     if (n_seg == 1u) return;
@@ -549,24 +562,25 @@ __global__ void __launch_bounds__(T * T) blend_prefix_kernel(const Segment* __re
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
             const unsigned s = s0 + k;
-            loc[k] = s + 1u < n_seg ? seg_T[(size_t)(first + s) * B + t] : 1.0f;
+            loc[k] = s + 1u < n_seg ? seg_T[(size_t)(first + s) * P + t] : 1.0f;
         }
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
             const unsigned s = s0 + k;
-            if (s < n_seg) seg_T[(size_t)(first + s) * B + t] = run;
+            if (s < n_seg) seg_T[(size_t)(first + s) * P + t] = run;
             run *= loc[k];
         }
     }
 }
 
-template <int T, int KIND>
+template <int T, int IPT, int KIND>
 __global__ void __launch_bounds__(T * T) blend_bilinear_forward_kernel(
     const Segment* __restrict__ segs, const uint32_t* __restrict__ n_segments, const uint32_t* __restrict__ inst_ids,
     const PointRec* __restrict__ rec, float* __restrict__ seg_T, float4* __restrict__ seg_C, float* __restrict__ seg_Z,
     float* __restrict__ image, float* __restrict__ depth_image, float* __restrict__ alpha_image,
     float* __restrict__ blending_weights, int width, int height, int gw) {
-    constexpr int B = T * T;
+    constexpr int P = T * T;
+    constexpr int B = P * IPT;
     constexpr int WORDS = B / 32;
     if (blockIdx.x >= *n_segments) return;
     const Segment sg = segs[blockIdx.x];
@@ -574,21 +588,23 @@ __global__ void __launch_bounds__(T * T) blend_bilinear_forward_kernel(
 
     __shared__ float4 s_a[B];
     __shared__ float4 s_f[B];
-    __shared__ unsigned s_mask[WORDS][B];
-    __shared__ float s_slot[KIND == BLEND_TRAIN ? 4 : 1][B];
+    __shared__ unsigned s_mask[WORDS][P];
+    __shared__ float s_slot[KIND == BLEND_TRAIN ? 4 : 1][KIND == BLEND_TRAIN ? B : 1];
 
     const int t = threadIdx.x;
     const int tx = (int)(sg.tile % (unsigned)gw), ty = (int)(sg.tile / (unsigned)gw);
     const int px = tx * T + t % T, py = ty * T + t / T;
     const bool inside = px < width && py < height;
     const float pcx = (float)px + 0.5f, pcy = (float)py + 0.5f;
-    const size_t state_idx = (size_t)blockIdx.x * B + t;
+    const size_t state_idx = (size_t)blockIdx.x * P + t;
 
 #pragma unroll
     for (int w = 0; w < WORDS; ++w) s_mask[w][t] = 0u;
     if (KIND == BLEND_TRAIN) {
 #pragma unroll
-        for (int q = 0; q < 4; ++q) s_slot[q][t] = 0.0f;
+        for (int k = 0; k < IPT; ++k)
+#pragma unroll
+            for (int q = 0; q < 4; ++q) s_slot[q][t + k * P] = 0.0f;
     }
     float C0 = 0.0f, C1 = 0.0f, C2 = 0.0f, C3 = 0.0f, Z = 0.0f;
     float Tr = 1.0f;
@@ -596,21 +612,26 @@ __global__ void __launch_bounds__(T * T) blend_bilinear_forward_kernel(
     bool done = !inside || Tr < kTransmittanceEps;
     __syncthreads();
 
-    uint32_t id = 0;
+    uint32_t id[IPT];
     int cnt = 0;
     auto flush_weights = [&]() {
-        // blending weight of the instance staged last by this thread: its (up to) four fragments in
-        // fixed order; the slots are cleared for the next batch
-        if (t < cnt) {
-            const float sum = ((s_slot[0][t] + s_slot[1][t]) + s_slot[2][t]) + s_slot[3][t];
-            if (sum > 0.0f) atomicAdd(blending_weights + id, sum);
-            s_slot[0][t] = 0.0f; s_slot[1][t] = 0.0f; s_slot[2][t] = 0.0f; s_slot[3][t] = 0.0f;
+        // blending weights of the instances this thread staged last: the (up to) four fragments of each
+        // in fixed order; the slots are cleared for the next batch
+#pragma unroll
+        for (int k = 0; k < IPT; ++k) {
+            const int j = t + k * P;
+            if (j < cnt) {
+                const float sum = ((s_slot[0][j] + s_slot[1][j]) + s_slot[2][j]) + s_slot[3][j];
+                if (sum > 0.0f) atomicAdd(blending_weights + id[k], sum);
+                s_slot[0][j] = 0.0f; s_slot[1][j] = 0.0f; s_slot[2][j] = 0.0f; s_slot[3][j] = 0.0f;
+            }
         }
     };
     for (unsigned base = sg.begin; base < sg.end; base += B) {
         if (KIND == BLEND_TRAIN) flush_weights();
         cnt = (int)min((unsigned)B, sg.end - base);
-        id = stage_instance<T, true>(t, cnt, base, inst_ids, rec, tx, ty, s_a, s_f, s_mask);
+#pragma unroll
+        for (int k = 0; k < IPT; ++k) id[k] = stage_instance<T, B, true>(t + k * P, cnt, base, inst_ids, rec, tx, ty, s_a, s_f, s_mask);
         __syncthreads();
 #pragma unroll 1
         for (int w = 0; w < WORDS; ++w) {
@@ -636,7 +657,7 @@ __global__ void __launch_bounds__(T * T) blend_bilinear_forward_kernel(
                 if (Tr < kTransmittanceEps) done = true;
             }
         }
-        if (__syncthreads_count(done) == B) break;
+        if (__syncthreads_count(done) == P) break;
     }
     if (KIND == BLEND_TRAIN) flush_weights();
 
@@ -676,7 +697,7 @@ __global__ void __launch_bounds__(T * T) blend_combine_kernel(const Segment* __r
                                                               const float* __restrict__ seg_T, float* __restrict__ image,
                                                               float* __restrict__ depth_image, float* __restrict__ alpha_image,
                                                               int width, int height, int gw) {
-    constexpr int B = T * T;
+    constexpr int P = T * T;
     const unsigned first = tile_first[blockIdx.x];
     const unsigned n_seg = segs[first].info >> 16;
     if (n_seg == 1u) return;
@@ -691,13 +712,13 @@ __global__ void __launch_bounds__(T * T) blend_combine_kernel(const Segment* __r
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
             const unsigned s = s0 + k;
-            c[k] = s < n_seg ? seg_C[(size_t)(first + s) * B + t] : make_float4(0.f, 0.f, 0.f, 0.f);
-            zz[k] = (KIND == BLEND_INFER && s < n_seg) ? seg_Z[(size_t)(first + s) * B + t] : 0.0f;
+            c[k] = s < n_seg ? seg_C[(size_t)(first + s) * P + t] : make_float4(0.f, 0.f, 0.f, 0.f);
+            zz[k] = (KIND == BLEND_INFER && s < n_seg) ? seg_Z[(size_t)(first + s) * P + t] : 0.0f;
         }
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
             const unsigned s = s0 + k;
-            if (KIND == BLEND_TRAIN && s < n_seg) seg_C[(size_t)(first + s) * B + t] = run;
+            if (KIND == BLEND_TRAIN && s < n_seg) seg_C[(size_t)(first + s) * P + t] = run;
             run.x += c[k].x; run.y += c[k].y; run.z += c[k].z; run.w += c[k].w;
             z += zz[k];
         }
@@ -710,7 +731,7 @@ __global__ void __launch_bounds__(T * T) blend_combine_kernel(const Segment* __r
         image[2 * n_px + pi] = run.z;
         image[3 * n_px + pi] = run.w;
         if (KIND == BLEND_INFER) {
-            const float Tr = seg_T[(size_t)(first + n_seg - 1u) * B + t];
+            const float Tr = seg_T[(size_t)(first + n_seg - 1u) * P + t];
             const float A = 1.0f - Tr;
             depth_image[pi] = A > 0.0f ? z / A : 0.0f;
             alpha_image[pi] = Tr < kTransmittanceEps ? 1.0f : A;
@@ -718,37 +739,41 @@ __global__ void __launch_bounds__(T * T) blend_combine_kernel(const Segment* __r
     }
 }
 
-template <int T>
+template <int T, int IPT>
 __global__ void __launch_bounds__(T * T) blend_bilinear_backward_kernel(
     const Segment* __restrict__ segs, const uint32_t* __restrict__ n_segments, const uint32_t* __restrict__ inst_ids,
     const PointRec* __restrict__ rec, const float* __restrict__ seg_T, const float4* __restrict__ seg_C,
     const float* __restrict__ grad_image, const float* __restrict__ grad_alpha, const float* __restrict__ image,
     const float* __restrict__ alpha_image, float4* __restrict__ grad_feat_view, float* __restrict__ grad_opacity,
     int width, int height, int gw) {
-    constexpr int B = T * T;
+    constexpr int P = T * T;
+    constexpr int B = P * IPT;
     constexpr int WORDS = B / 32;
     if (blockIdx.x >= *n_segments) return;
     const Segment sg = segs[blockIdx.x];
     const unsigned seg_idx = sg.info & 0xffffu;
     if (sg.begin == sg.end) return;
 
-    __shared__ float4 s_a[B];
-    __shared__ float4 s_f[B];
-    __shared__ unsigned s_mask[WORDS][B];
-    __shared__ float4 s_gf[4][B];    // per footprint corner: feature gradient contribution
-    __shared__ float s_go[4][B];     // per footprint corner: opacity gradient contribution
+    extern __shared__ __align__(16) unsigned char blend_smem[];
+    float4* s_a = reinterpret_cast<float4*>(blend_smem);            // [B]
+    float4* s_f = s_a + B;                                          // [B]
+    float4* s_gf = s_f + B;                                         // [4][B] per footprint corner: feature gradient
+    float* s_go = reinterpret_cast<float*>(s_gf + 4 * B);           // [4][B] per footprint corner: opacity gradient
+    unsigned (*s_mask)[P] = reinterpret_cast<unsigned (*)[P]>(s_go + 4 * B);   // [WORDS][P]
 
     const int t = threadIdx.x;
     const int tx = (int)(sg.tile % (unsigned)gw), ty = (int)(sg.tile / (unsigned)gw);
     const int px = tx * T + t % T, py = ty * T + t / T;
     const bool inside = px < width && py < height;
     const float pcx = (float)px + 0.5f, pcy = (float)py + 0.5f;
-    const size_t state_idx = (size_t)blockIdx.x * B + t;
+    const size_t state_idx = (size_t)blockIdx.x * P + t;
 
 #pragma unroll
     for (int w = 0; w < WORDS; ++w) s_mask[w][t] = 0u;
 #pragma unroll
-    for (int q = 0; q < 4; ++q) { s_gf[q][t] = make_float4(0.f, 0.f, 0.f, 0.f); s_go[q][t] = 0.0f; }
+    for (int k = 0; k < IPT; ++k)
+#pragma unroll
+        for (int q = 0; q < 4; ++q) { s_gf[q * B + t + k * P] = make_float4(0.f, 0.f, 0.f, 0.f); s_go[q * B + t + k * P] = 0.0f; }
 
     float4 g = make_float4(0.f, 0.f, 0.f, 0.f), Cfin = make_float4(0.f, 0.f, 0.f, 0.f);
     float4 Crun = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -766,28 +791,33 @@ __global__ void __launch_bounds__(T * T) blend_bilinear_backward_kernel(
     bool done = !inside || Tr < kTransmittanceEps;
     __syncthreads();
 
-    uint32_t id = 0;
+    uint32_t id[IPT];
     int cnt = 0;
     auto flush_gradients = [&]() {
-        if (t < cnt) {
-            float4 sf = s_gf[0][t];
-            float so = s_go[0][t];
 #pragma unroll
-            for (int q = 1; q < 4; ++q) {
-                const float4 v = s_gf[q][t];
-                sf.x += v.x; sf.y += v.y; sf.z += v.z; sf.w += v.w;
-                so += s_go[q][t];
+        for (int k = 0; k < IPT; ++k) {
+            const int j = t + k * P;
+            if (j < cnt) {
+                float4 sf = s_gf[j];
+                float so = s_go[j];
+#pragma unroll
+                for (int q = 1; q < 4; ++q) {
+                    const float4 v = s_gf[q * B + j];
+                    sf.x += v.x; sf.y += v.y; sf.z += v.z; sf.w += v.w;
+                    so += s_go[q * B + j];
+                }
+                if (sf.x != 0.0f || sf.y != 0.0f || sf.z != 0.0f || sf.w != 0.0f) atomicAdd(grad_feat_view + id[k], sf);
+                if (so != 0.0f) atomicAdd(grad_opacity + id[k], so);
+#pragma unroll
+                for (int q = 0; q < 4; ++q) { s_gf[q * B + j] = make_float4(0.f, 0.f, 0.f, 0.f); s_go[q * B + j] = 0.0f; }
             }
-            if (sf.x != 0.0f || sf.y != 0.0f || sf.z != 0.0f || sf.w != 0.0f) atomicAdd(grad_feat_view + id, sf);
-            if (so != 0.0f) atomicAdd(grad_opacity + id, so);
-#pragma unroll
-            for (int q = 0; q < 4; ++q) { s_gf[q][t] = make_float4(0.f, 0.f, 0.f, 0.f); s_go[q][t] = 0.0f; }
         }
     };
     for (unsigned base = sg.begin; base < sg.end; base += B) {
         flush_gradients();
         cnt = (int)min((unsigned)B, sg.end - base);
-        id = stage_instance<T, true>(t, cnt, base, inst_ids, rec, tx, ty, s_a, s_f, s_mask);
+#pragma unroll
+        for (int k = 0; k < IPT; ++k) id[k] = stage_instance<T, B, true>(t + k * P, cnt, base, inst_ids, rec, tx, ty, s_a, s_f, s_mask);
         __syncthreads();
 #pragma unroll 1
         for (int w = 0; w < WORDS; ++w) {
@@ -803,7 +833,7 @@ __global__ void __launch_bounds__(T * T) blend_bilinear_backward_kernel(
                 const float al = a.z * wgt;
                 const float bw = Tr * al;
                 const int q = (pcx > a.x ? 1 : 0) + (pcy > a.y ? 2 : 0);
-                if (bw > 0.0f) s_gf[q][j] = make_float4(bw * g.x, bw * g.y, bw * g.z, bw * g.w);
+                if (bw > 0.0f) s_gf[q * B + j] = make_float4(bw * g.x, bw * g.y, bw * g.z, bw * g.w);
                 const float4 f = s_f[j];
                 Crun.x += bw * f.x; Crun.y += bw * f.y; Crun.z += bw * f.z; Crun.w += bw * f.w;
                 const float oma = 1.0f - al;
@@ -814,14 +844,19 @@ __global__ void __launch_bounds__(T * T) blend_bilinear_backward_kernel(
                                             (Tr * f.w + (Crun.w - Cfin.w) * rcp) * g.w;
                 const float dalpha = from_features + K * rcp;
                 const float dop = dalpha * wgt;
-                if (dop != 0.0f) s_go[q][j] = dop;
+                if (dop != 0.0f) s_go[q * B + j] = dop;
                 Tr *= oma;
                 if (Tr < kTransmittanceEps) done = true;
             }
         }
-        if (__syncthreads_count(done) == B) break;
+        if (__syncthreads_count(done) == P) break;
     }
     flush_gradients();
+}
+
+template <int T, int IPT>
+constexpr size_t backward_smem_bytes() {
+    return (size_t)T * T * IPT * (16 + 16 + 4 * 16 + 4 * 4) + (size_t)(T * T * IPT / 32) * T * T * 4;
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -1066,8 +1101,9 @@ struct InstanceBlob {
 };
 
 // Upper bound on the number of (tile, segment) work items, known from the instance count alone.
+int blend_batch(int tile);
 int64_t max_segments(int64_t n_instances, int n_tiles, int tile) {
-    return (int64_t)n_tiles + ceil_div<int64_t>(n_instances, (int64_t)tile * tile * kMinBatchesPerSegment);
+    return (int64_t)n_tiles + ceil_div<int64_t>(n_instances, (int64_t)blend_batch(tile) * kMinBatchesPerSegment);
 }
 
 InstanceBlob carve_instance_blob(void* p, int64_t n_instances, int n_tiles, int tile, int mode, bool with_depth) {
@@ -1195,7 +1231,7 @@ int run_front(const RasterParams& rp, int64_t n, const float* positions, const v
     }
     if (MODE == INPC_MODE_BILINEAR) {
         StageScope scope(STAGE_SORT_TILE, stream);
-        build_segments_kernel<<<1, kScanThreads, 0, stream>>>(ib.ranges, n_tiles, rp.tile * rp.tile, ib.segs, ib.tile_first, ib.n_segments);
+        build_segments_kernel<<<1, kScanThreads, 0, stream>>>(ib.ranges, n_tiles, blend_batch(rp.tile), ib.segs, ib.tile_first, ib.n_segments);
         INPC_LAUNCH_CHECK("build_segments_kernel");
     }
     st->point_blob = pblob;
@@ -1222,22 +1258,50 @@ RasterParams make_params(const inpc_view* view, int tile_size, float sigma_world
     return rp;
 }
 
+// Instances staged per pixel thread and batch.  Measured on B200 (2^23 points, clustered and uniform
+// scenes): one per thread is fastest for both tile sizes; deeper batches lose more to mask traffic
+// and same-word atomicOr contention than they gain from fewer barriers.
+template <int T> struct BlendConfig;
+template <> struct BlendConfig<8> { static constexpr int kIpt = INPC_IPT8; };
+template <> struct BlendConfig<16> { static constexpr int kIpt = INPC_IPT16; };
+
+int blend_batch(int tile) { return tile == 8 ? 64 * BlendConfig<8>::kIpt : 256 * BlendConfig<16>::kIpt; }
+
 template <int T, int KIND>
 int launch_bilinear_forward(const RasterParams& rp, const PointBlob& pb, const InstanceBlob& ib, const uint32_t* ids, float* image,
                             float* depth, float* alpha, float* blending_weights, cudaStream_t stream) {
+    constexpr int IPT = BlendConfig<T>::kIpt;
     const int n_tiles = rp.gw * rp.gh;
     const int W = rp.v.width, H = rp.v.height;
     const unsigned grid = (unsigned)ib.max_segments;
-    blend_bilinear_transmittance_kernel<T><<<grid, T * T, 0, stream>>>(ib.segs, ib.n_segments, ids, pb.rec, ib.seg_T, W, H, rp.gw);
+    blend_bilinear_transmittance_kernel<T, IPT><<<grid, T * T, 0, stream>>>(ib.segs, ib.n_segments, ids, pb.rec, ib.seg_T, W, H, rp.gw);
     INPC_LAUNCH_CHECK("blend_bilinear_transmittance_kernel");
     blend_prefix_kernel<T><<<n_tiles, T * T, 0, stream>>>(ib.segs, ib.tile_first, ib.seg_T);
     INPC_LAUNCH_CHECK("blend_prefix_kernel");
-    blend_bilinear_forward_kernel<T, KIND><<<grid, T * T, 0, stream>>>(ib.segs, ib.n_segments, ids, pb.rec, ib.seg_T, ib.seg_C, ib.seg_Z,
-                                                                      image, depth, alpha, blending_weights, W, H, rp.gw);
+    blend_bilinear_forward_kernel<T, IPT, KIND><<<grid, T * T, 0, stream>>>(ib.segs, ib.n_segments, ids, pb.rec, ib.seg_T, ib.seg_C, ib.seg_Z,
+                                                                           image, depth, alpha, blending_weights, W, H, rp.gw);
     INPC_LAUNCH_CHECK("blend_bilinear_forward_kernel");
     blend_combine_kernel<T, KIND><<<n_tiles, T * T, 0, stream>>>(ib.segs, ib.tile_first, ib.seg_C, ib.seg_Z, ib.seg_T, image, depth, alpha,
                                                                 W, H, rp.gw);
     INPC_LAUNCH_CHECK("blend_combine_kernel");
+    return INPC_OK;
+}
+
+template <int T>
+int launch_bilinear_backward(const RasterParams& rp, const PointBlob& pb, const InstanceBlob& ib, const uint32_t* ids,
+                             const float* grad_image, const float* grad_alpha, const float* image, const float* alpha, float4* gfv,
+                             float* grad_opacities, cudaStream_t stream) {
+    constexpr int IPT = BlendConfig<T>::kIpt;
+    constexpr size_t smem = backward_smem_bytes<T, IPT>();
+    static bool attr_set = false;
+    if (!attr_set) {
+        INPC_CUDA_TRY(cudaFuncSetAttribute(blend_bilinear_backward_kernel<T, IPT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        attr_set = true;
+    }
+    blend_bilinear_backward_kernel<T, IPT><<<(unsigned)ib.max_segments, T * T, smem, stream>>>(
+        ib.segs, ib.n_segments, ids, pb.rec, ib.seg_T, ib.seg_C, grad_image, grad_alpha, image, alpha, gfv, grad_opacities,
+        rp.v.width, rp.v.height, rp.gw);
+    INPC_LAUNCH_CHECK("blend_bilinear_backward_kernel");
     return INPC_OK;
 }
 
@@ -1317,10 +1381,9 @@ extern "C" int inpc_rasterize_backward(const inpc_raster_state* state, const inp
     {
         StageScope scope(STAGE_BLEND_BWD, stream);
         if (state->mode == INPC_MODE_BILINEAR) {
-            if (rp.tile == 8)
-                blend_bilinear_backward_kernel<8><<<(unsigned)ib.max_segments, 64, 0, stream>>>(ib.segs, ib.n_segments, ids, pb.rec, ib.seg_T, ib.seg_C, grad_image, grad_alpha, image, alpha, gfv, grad_opacities, W, H, rp.gw);
-            else
-                blend_bilinear_backward_kernel<16><<<(unsigned)ib.max_segments, 256, 0, stream>>>(ib.segs, ib.n_segments, ids, pb.rec, ib.seg_T, ib.seg_C, grad_image, grad_alpha, image, alpha, gfv, grad_opacities, W, H, rp.gw);
+            rc = rp.tile == 8 ? launch_bilinear_backward<8>(rp, pb, ib, ids, grad_image, grad_alpha, image, alpha, gfv, grad_opacities, stream)
+                              : launch_bilinear_backward<16>(rp, pb, ib, ids, grad_image, grad_alpha, image, alpha, gfv, grad_opacities, stream);
+            if (rc != INPC_OK) return rc;
         } else {
             if (rp.tile == 8)
                 blend_gaussian_backward_kernel<8><<<n_tiles, 64, 0, stream>>>(ib.ranges, ids, pb.rec, pb.conic, grad_image, grad_alpha, image, alpha, gfv, grad_opacities, W, H, rp.gw);

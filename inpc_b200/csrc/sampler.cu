@@ -209,6 +209,7 @@ __device__ __forceinline__ float unit_float(unsigned r) { return __uint_as_float
 
 struct Draw {
     float u, jx, jy, jz;
+    unsigned raw_u;   // the 32 bits u was made of
 };
 // stream layout: counter = (slot, attempt, call lo, call hi), key = seed (lo, hi)
 __device__ __forceinline__ Draw philox_draw(unsigned long long seed, unsigned long long call, unsigned slot, unsigned attempt) {
@@ -216,12 +217,45 @@ __device__ __forceinline__ Draw philox_draw(unsigned long long seed, unsigned lo
                                   make_uint2((unsigned)seed, (unsigned)(seed >> 32)));
     Draw d;
     d.u = unit_float(o.x); d.jx = unit_float(o.y); d.jy = unit_float(o.z); d.jz = unit_float(o.w);
+    d.raw_u = o.x;
     return d;
 }
 
 // first index with cdf[idx] >= u, clamped to n-1: include/sampling_utils.h:49-69
 __device__ __forceinline__ unsigned lower_bound_clamped(const float* __restrict__ cdf, float u, unsigned n) {
     unsigned first = 0, count = n;
+    while (count > 0) {
+        const unsigned step = count >> 1;
+        if (__ldg(cdf + first + step) < u) { first += step + 1; count -= step + 1; }
+        else count = step;
+    }
+    return min(first, n - 1);
+}
+
+// Guide table: guide[b] = lower_bound(cdf, b / 2^k) for b = 0 .. 2^k.  The CDF is monotone (integer
+// prefix sums), so the look-up for a uniform in bucket b only has to search [guide[b], guide[b+1]):
+// about L / 2^k entries instead of log2(L) dependent loads, with bit-identical results.
+__global__ void __launch_bounds__(kThreads) guide_table_kernel(const float* __restrict__ cdf, unsigned n_cells, int k,
+                                                               unsigned* __restrict__ guide) {
+    const unsigned b = blockIdx.x * kThreads + threadIdx.x;
+    if (b > (1u << k)) return;
+    // bucket edge as a float: (b << (23 - k)) * 2^-23, exact
+    const float edge = (float)(b << (23 - k)) * 1.1920928955078125e-07f;
+    unsigned first = 0, count = n_cells;
+    while (count > 0) {
+        const unsigned step = count >> 1;
+        if (__ldg(cdf + first + step) < edge) { first += step + 1; count -= step + 1; }
+        else count = step;
+    }
+    guide[b] = first;
+}
+
+// r: the raw 32 random bits the uniform is made of (u = (r >> 9) * 2^-23)
+__device__ __forceinline__ unsigned guided_lower_bound(const float* __restrict__ cdf, const unsigned* __restrict__ guide, int k,
+                                                       unsigned r, float u, unsigned n) {
+    const unsigned b = (r >> 9) >> (23 - k);
+    const uint2 g = make_uint2(__ldg(guide + b), __ldg(guide + b + 1));
+    unsigned first = g.x, count = g.y - g.x;
     while (count > 0) {
         const unsigned step = count >> 1;
         if (__ldg(cdf + first + step) < u) { first += step + 1; count -= step + 1; }
@@ -237,7 +271,7 @@ __device__ __forceinline__ float leaf_scale(int level, float initial_size) {
 // ---- training samples: same acceptance test as src/sampling_kernels.cu:98-113 -------------------
 __global__ void __launch_bounds__(kThreads) training_samples_kernel(
     ViewParams v, unsigned long long seed, unsigned long long call, const float* __restrict__ cdf,
-    const float* __restrict__ sum_ptr, unsigned n_cells, const float* __restrict__ centers, const int* __restrict__ levels,
+    const unsigned* __restrict__ guide, int guide_bits, const float* __restrict__ sum_ptr, unsigned n_cells, const float* __restrict__ centers, const int* __restrict__ levels,
     float initial_size, int64_t n_samples, float* __restrict__ positions, long long* __restrict__ indices,
     volatile unsigned* status) {
     const int64_t s = (int64_t)blockIdx.x * kThreads + threadIdx.x;
@@ -254,7 +288,7 @@ __global__ void __launch_bounds__(kThreads) training_samples_kernel(
     bool ok = false;
     for (unsigned a = 0; a < (unsigned)kMaxAttempts && !ok; ++a) {
         const Draw d = philox_draw(seed, call, (unsigned)s, a);
-        leaf = lower_bound_clamped(cdf, d.u, n_cells);
+        leaf = guided_lower_bound(cdf, guide, guide_bits, d.raw_u, d.u, n_cells);
         const float scale = leaf_scale(__ldg(levels + leaf), initial_size);
         x = fmaf(d.jx - 0.5f, scale, __ldg(centers + 3 * (int64_t)leaf));
         y = fmaf(d.jy - 0.5f, scale, __ldg(centers + 3 * (int64_t)leaf + 1));
@@ -275,14 +309,15 @@ __global__ void __launch_bounds__(kThreads) training_samples_kernel(
 
 // ---- unconditional samples: src/sampling_kernels.cu:128-150 with the Philox stream ----------------
 __global__ void __launch_bounds__(kThreads) samples_kernel(unsigned long long seed, unsigned long long call,
-                                                           const float* __restrict__ cdf, unsigned n_cells,
+                                                           const float* __restrict__ cdf, const unsigned* __restrict__ guide,
+                                                           int guide_bits, unsigned n_cells,
                                                            const float* __restrict__ centers, const int* __restrict__ levels,
                                                            float initial_size, int64_t n_samples,
                                                            float* __restrict__ positions) {
     const int64_t s = (int64_t)blockIdx.x * kThreads + threadIdx.x;
     if (s >= n_samples) return;
     const Draw d = philox_draw(seed, call, (unsigned)s, 0u);
-    const unsigned leaf = lower_bound_clamped(cdf, d.u, n_cells);
+    const unsigned leaf = guided_lower_bound(cdf, guide, guide_bits, d.raw_u, d.u, n_cells);
     const float scale = leaf_scale(__ldg(levels + leaf), initial_size);
     positions[3 * s] = fmaf(d.jx - 0.5f, scale, __ldg(centers + 3 * (int64_t)leaf));
     positions[3 * s + 1] = fmaf(d.jy - 0.5f, scale, __ldg(centers + 3 * (int64_t)leaf + 1));
@@ -394,8 +429,16 @@ struct SamplerWs {
     unsigned* offsets;  // inclusive offsets (n_cells)
     unsigned* chunk_sums;
     unsigned long long* total;
+    unsigned* guide;    // 2^guide_bits + 1 entries
+    int guide_bits;
     size_t bytes;
 };
+
+int guide_bits_for(int64_t n_cells) {
+    int k = 8;
+    while (k < 20 && ((int64_t)1 << k) < n_cells) ++k;
+    return k;
+}
 
 SamplerWs carve_sampler_ws(void* p, int64_t n_cells) {
     SamplerWs w;
@@ -411,6 +454,8 @@ SamplerWs carve_sampler_ws(void* p, int64_t n_cells) {
     w.offsets = c.take<unsigned>(n);
     w.chunk_sums = c.take<unsigned>(ceil_div<int64_t>(n, kThreads));
     w.total = c.take<unsigned long long>(2);
+    w.guide_bits = guide_bits_for(n);
+    w.guide = c.take<unsigned>(((size_t)1 << w.guide_bits) + 2);
     w.bytes = c.used();
     return w;
 }
@@ -428,6 +473,11 @@ int build_cdf(const float* weights, int64_t n_cells, float* cdf, float* sum_out,
     if (cdf) {
         cdf_finalize_kernel<<<(unsigned)chunks, kCdfThreads, 0, stream>>>(weights, n_cells, w.max_bits, w.chunk_sums64, w.total64, cdf);
         INPC_LAUNCH_CHECK("cdf_finalize_kernel");
+        if (cdf == w.cdf) {
+            guide_table_kernel<<<(unsigned)ceil_div<int64_t>(((int64_t)1 << w.guide_bits) + 1, kThreads), kThreads, 0, stream>>>(
+                cdf, (unsigned)n_cells, w.guide_bits, w.guide);
+            INPC_LAUNCH_CHECK("guide_table_kernel");
+        }
     }
     return INPC_OK;
 }
@@ -518,7 +568,7 @@ extern "C" int inpc_generate_training_samples(inpc_sampler* s, const inpc_view* 
     unsigned* status = device_status_ptr();
     if (!status) return INPC_E_CUDA;
     training_samples_kernel<<<(unsigned)ceil_div<int64_t>(n_samples, kThreads), kThreads, 0, stream>>>(
-        v, s->seed, s->counter, w.cdf, w.sum, (unsigned)n_cells, centers, levels, initial_size, n_samples, positions,
+        v, s->seed, s->counter, w.cdf, w.guide, w.guide_bits, w.sum, (unsigned)n_cells, centers, levels, initial_size, n_samples, positions,
         reinterpret_cast<long long*>(indices), status);
     INPC_LAUNCH_CHECK("training_samples_kernel");
     s->counter += 1;
@@ -547,7 +597,7 @@ extern "C" int inpc_generate_samples(inpc_sampler* s, const inpc_view* view, int
     if (!(host[0] > 0.0f)) return INPC_OK;   // src/sampling_api.cu:154: empty result
     if (n_samples > 0) {
         samples_kernel<<<(unsigned)ceil_div<int64_t>(n_samples, kThreads), kThreads, 0, stream>>>(
-            s->seed, s->counter, w.cdf, (unsigned)n_cells, centers, levels, initial_size, n_samples, positions);
+            s->seed, s->counter, w.cdf, w.guide, w.guide_bits, (unsigned)n_cells, centers, levels, initial_size, n_samples, positions);
         INPC_LAUNCH_CHECK("samples_kernel");
     }
     s->counter += 1;
