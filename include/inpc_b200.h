@@ -58,6 +58,8 @@ typedef struct inpc_raster_state {
     int64_t n_instances;
     int32_t tile_size;
     int32_t mode;
+    uint32_t depth_key_base;  /* smallest depth bit pattern among the visible points (sort keys are offsets from it) */
+    int32_t depth_key_bits;   /* significant bits of the largest offset */
 } inpc_raster_state;
 
 const char* inpc_last_error(void);
@@ -152,7 +154,7 @@ int inpc_sort_pairs(uint32_t* keys, uint32_t* keys_alt, uint32_t* values, uint32
  * else's memory budget — an engine plugin handed a fixed arena, a real-time loop where cudaMalloc's
  * implicit synchronisation is not acceptable, a process whose allocator is owned by another
  * framework and must not see foreign allocations.  It takes no workspace argument: its scratch is a
- * fixed array inside the library's device image (about 520 KB, held by every GPU that loads the
+ * fixed array inside the library's device image (about 1 MB, held by every GPU that loads the
  * library until the process exits), and it makes no cudaMalloc / cudaFree / allocating call of any
  * kind, torch's included.  Inputs and outputs are still the caller's.
  *   - Capacity: n <= 1,048,576 pairs; larger n returns INPC_E_CAPACITY with a message.

@@ -30,7 +30,8 @@ class View(C.Structure):
 class RasterState(C.Structure):
     """struct inpc_raster_state."""
     _fields_ = [("point_blob", C.c_void_p), ("instance_blob", C.c_void_p), ("n_points", C.c_int64),
-                ("n_visible", C.c_int64), ("n_instances", C.c_int64), ("tile_size", C.c_int32), ("mode", C.c_int32)]
+                ("n_visible", C.c_int64), ("n_instances", C.c_int64), ("tile_size", C.c_int32), ("mode", C.c_int32),
+                ("depth_key_base", C.c_uint32), ("depth_key_bits", C.c_int32)]
 
 
 _P, _I, _L, _F, _Z = C.c_void_p, C.c_int, C.c_int64, C.c_float, C.c_size_t

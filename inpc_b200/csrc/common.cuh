@@ -107,6 +107,7 @@ inline ViewParams to_params(const inpc_view* v) {
 
 // ---- radix sort (radix_sort.cu) ------------------------------------------------------------
 size_t sort_workspace_bytes(int64_t n);
+int sort_pass_count(int end_bit);   // passes sort_pairs makes; the result is in the alternate buffers iff odd (and n > 1)
 int sort_pairs(uint32_t* keys, uint32_t* keys_alt, uint32_t* values, uint32_t* values_alt, int64_t n,
                int end_bit, void* workspace, int* result_in_alt, cudaStream_t stream);
 

@@ -16,8 +16,8 @@ namespace inpc {
 
 namespace {
 
-constexpr int kRadixBits = 8;
-constexpr int kRadix = 1 << kRadixBits;
+constexpr int kRadixBits = 9;            // widest digit of a pass: 27 key bits sort in 3 passes, 32 in 4 x 8
+constexpr int kRadix = 1 << kRadixBits;  // capacity of every per-digit array
 constexpr int kMaxPasses = 4;
 constexpr int kThreads = 512;
 constexpr int kItems = 16;
@@ -83,7 +83,7 @@ __global__ void __launch_bounds__(kRadix) radix_scan_histogram_kernel(const unsi
 struct PassSmem {
     union {
         unsigned warp_hist[kWarps][kRadix];   // ranking phase
-        uint32_t keys[kTile];                 // reorder phase (keys), 32 KB — warp_hist is 16 KB
+        uint32_t keys[kTile];                 // reorder phase (keys), 32 KB, as large as warp_hist
     };
     uint32_t values[kTile];
     unsigned bin_start[kRadix];    // tile-local exclusive start of each digit
@@ -139,8 +139,9 @@ __global__ void __launch_bounds__(kThreads) radix_onesweep_pass_kernel(
     __syncthreads();
 
     // per digit: exclusive scan over warps, tile total
+    const unsigned radix = 1u << bits;
     unsigned total = 0;
-    if (tid < kRadix) {
+    if (tid < radix) {
 #pragma unroll
         for (int w = 0; w < kWarps; ++w) {
             const unsigned c = s.warp_hist[w][tid];
@@ -151,8 +152,8 @@ __global__ void __launch_bounds__(kThreads) radix_onesweep_pass_kernel(
         tile_state[(size_t)tile * kRadix + tid] = total | (tile == 0 ? kFlagPrefix : kFlagAggregate);
     }
     unsigned block_total;
-    const unsigned start = block_exclusive_scan(tid < kRadix ? total : 0u, s.scan, &block_total);
-    if (tid < kRadix) {
+    const unsigned start = block_exclusive_scan(tid < radix ? total : 0u, s.scan, &block_total);
+    if (tid < radix) {
         s.bin_start[tid] = start;
         // decoupled look-back
         unsigned exclusive = 0;
@@ -239,6 +240,8 @@ SortWorkspace carve_sort_workspace(void* ws, int64_t n) {
 
 size_t sort_workspace_bytes(int64_t n) { return carve_sort_workspace(nullptr, n).total; }
 
+int sort_pass_count(int end_bit) { return end_bit > 0 ? ceil_div(end_bit, kRadixBits) : 0; }
+
 int sort_pairs(uint32_t* keys, uint32_t* keys_alt, uint32_t* values, uint32_t* values_alt, int64_t n,
                int end_bit, void* workspace, int* result_in_alt, cudaStream_t stream) {
     if (result_in_alt) *result_in_alt = 0;
@@ -299,12 +302,13 @@ int sort_pairs(uint32_t* keys, uint32_t* keys_alt, uint32_t* values, uint32_t* v
 
 // ---- sorting without any allocation -------------------------------------------------------------
 // Scratch for inpc_sort_pairs_static lives in this fixed device array: every GPU that loads the library
-// holds it (about 520 KB) until the process exits.  Layout = the ordinary sort workspace for
+// holds it (about 1 MB) until the process exits.  Layout = the ordinary sort workspace for
 // kStaticMaxPairs pairs, followed by one 256-byte status area.
 namespace inpc {
 namespace {
 constexpr int64_t kStaticMaxPairs = 1 << 20;
 constexpr size_t kStaticTiles = (kStaticMaxPairs + kTile - 1) / kTile;
+static_assert(kThreads >= kRadix, "one thread per digit");
 constexpr size_t kStaticWorkspaceBytes = (kMaxPasses * kRadix * 4 + 256)            // histograms + tickets
                                          + kMaxPasses * kStaticTiles * kRadix * 4   // look-back state
                                          + kMaxPasses * kRadix * 4;                 // digit bases

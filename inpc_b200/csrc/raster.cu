@@ -132,16 +132,20 @@ constexpr int kPreThreads = 256;
 template <int MODE, int VARIANT>
 __global__ void __launch_bounds__(kPreThreads) visibility_count_kernel(
     const float* __restrict__ positions, int64_t n, RasterParams rp, unsigned* __restrict__ block_visible,
-    unsigned long long* __restrict__ block_instances) {
-    __shared__ unsigned s_v[kPreThreads / 32];
+    unsigned long long* __restrict__ block_instances, unsigned* __restrict__ depth_min, unsigned* __restrict__ depth_max) {
+    __shared__ unsigned s_v[kPreThreads / 32], s_lo[kPreThreads / 32], s_hi[kPreThreads / 32];
     __shared__ unsigned long long s_i[kPreThreads / 32];
     const W2C m = load_w2c(rp.v.w2c);
     const int64_t i = (int64_t)blockIdx.x * kPreThreads + threadIdx.x;
-    unsigned vis = 0, cnt = 0;
+    unsigned vis = 0, cnt = 0, lo = 0xFFFFFFFFu, hi = 0u;
     if (i < n) {
         const Projection pr = project_point<MODE, VARIANT>(__ldg(positions + 3 * i), __ldg(positions + 3 * i + 1),
                                                            __ldg(positions + 3 * i + 2), m, rp, i);
-        if (pr.visible) { vis = 1; cnt = (pr.x1 - pr.x0) * (pr.y1 - pr.y0); }
+        if (pr.visible) {
+            vis = 1;
+            cnt = (pr.x1 - pr.x0) * (pr.y1 - pr.y0);
+            lo = hi = __float_as_uint(pr.depth);   // visible depths are positive: bit patterns order like the values
+        }
     }
     unsigned v = vis;
     unsigned long long c = cnt;
@@ -149,16 +153,19 @@ __global__ void __launch_bounds__(kPreThreads) visibility_count_kernel(
     for (int o = 16; o > 0; o >>= 1) {
         v += __shfl_down_sync(0xffffffffu, v, o);
         c += __shfl_down_sync(0xffffffffu, c, o);
+        lo = min(lo, __shfl_down_sync(0xffffffffu, lo, o));
+        hi = max(hi, __shfl_down_sync(0xffffffffu, hi, o));
     }
-    if (lane_id() == 0) { s_v[threadIdx.x >> 5] = v; s_i[threadIdx.x >> 5] = c; }
+    if (lane_id() == 0) { s_v[threadIdx.x >> 5] = v; s_i[threadIdx.x >> 5] = c; s_lo[threadIdx.x >> 5] = lo; s_hi[threadIdx.x >> 5] = hi; }
     __syncthreads();
     if (threadIdx.x == 0) {
-        unsigned tv = 0;
+        unsigned tv = 0, tlo = 0xFFFFFFFFu, thi = 0u;
         unsigned long long ti = 0;
 #pragma unroll
-        for (int w = 0; w < kPreThreads / 32; ++w) { tv += s_v[w]; ti += s_i[w]; }
+        for (int w = 0; w < kPreThreads / 32; ++w) { tv += s_v[w]; ti += s_i[w]; tlo = min(tlo, s_lo[w]); thi = max(thi, s_hi[w]); }
         block_visible[blockIdx.x] = tv;
         block_instances[blockIdx.x] = ti;
+        if (tv) { atomicMin(depth_min, tlo); atomicMax(depth_max, thi); }
     }
 }
 
@@ -168,6 +175,8 @@ constexpr int kScanThreads = 1024;
 __global__ void __launch_bounds__(kScanThreads) scan_block_counts_kernel(unsigned* __restrict__ block_visible,
                                                                          const unsigned long long* __restrict__ block_instances,
                                                                          int64_t n_blocks,
+                                                                         const unsigned* __restrict__ depth_min,
+                                                                         const unsigned* __restrict__ depth_max,
                                                                          unsigned long long* __restrict__ counters) {
     constexpr int kItems = 8;
     __shared__ unsigned s_scan[kScanThreads / 32 + 1];
@@ -202,6 +211,8 @@ __global__ void __launch_bounds__(kScanThreads) scan_block_counts_kernel(unsigne
         for (int w = 0; w < kScanThreads / 32; ++w) t += s_inst[w];
         counters[0] = running;
         counters[1] = t;
+        counters[2] = *depth_min;
+        counters[3] = *depth_max;
     }
 }
 
@@ -238,8 +249,8 @@ __device__ __forceinline__ float sh_eval_channel(const float* b, const __half* h
 template <int MODE, int VARIANT>
 __global__ void __launch_bounds__(kPreThreads) preprocess_kernel(
     const float* __restrict__ positions, const __half* __restrict__ features, const float* __restrict__ opacities,
-    int64_t n, RasterParams rp, const unsigned* __restrict__ block_offset, PointRec* __restrict__ rec,
-    uint2* __restrict__ bounds, float4* __restrict__ conic, uint32_t* __restrict__ depth_keys,
+    int64_t n, RasterParams rp, const unsigned* __restrict__ block_offset, const unsigned* __restrict__ depth_min,
+    PointRec* __restrict__ rec, uint2* __restrict__ bounds, float4* __restrict__ conic, uint32_t* __restrict__ depth_keys,
     uint32_t* __restrict__ point_ids) {
     constexpr int kHalves = VARIANT == VAR_RAW37 ? 37 : 36;
     constexpr int kSlabBytes = kPreThreads * kHalves * 2;   // multiple of 16 for both layouts
@@ -298,7 +309,8 @@ __global__ void __launch_bounds__(kPreThreads) preprocess_kernel(
     const unsigned rank = block_exclusive_scan(pr.visible ? 1u : 0u, s_scan, &total);
     if (pr.visible) {
         const unsigned slot = block_offset[blockIdx.x] + rank;
-        depth_keys[slot] = __float_as_uint(pr.depth);
+        // sort key: offset of the depth's bit pattern from the smallest visible one (fewer radix passes)
+        depth_keys[slot] = __float_as_uint(pr.depth) - __ldg(depth_min);
         point_ids[slot] = (uint32_t)i;
     }
 }
@@ -1055,8 +1067,9 @@ struct PointBlob {
     float4* conic;
     unsigned* block_visible;
     unsigned long long* block_instances;
-    unsigned long long* counters;
-    size_t phase1_bytes;   // everything above; the rest needs n_visible
+    unsigned long long* counters;   // visible, instances, smallest / largest depth bit pattern
+    unsigned* depth_min;
+    unsigned* depth_max;
     uint32_t* keys[2];
     uint32_t* ids[2];
     unsigned* inst_block_sums;
@@ -1064,7 +1077,9 @@ struct PointBlob {
     size_t total;
 };
 
-PointBlob carve_point_blob(void* p, int64_t n, int64_t n_visible, int mode) {
+// Sized by the number of input points alone (every per-visible array gets room for all of them), so
+// that the layout is known before the visible count has been read back.
+PointBlob carve_point_blob(void* p, int64_t n, int mode) {
     PointBlob b;
     Carver c(p);
     const int64_t nb = ceil_div<int64_t>(n > 0 ? n : 1, kPreThreads);
@@ -1074,13 +1089,14 @@ PointBlob carve_point_blob(void* p, int64_t n, int64_t n_visible, int mode) {
     b.block_visible = c.take<unsigned>(nb);
     b.block_instances = c.take<unsigned long long>(nb);
     b.counters = c.take<unsigned long long>(4);
-    b.phase1_bytes = c.used();
-    for (int k = 0; k < 2; ++k) b.keys[k] = c.take<uint32_t>(n_visible);
-    for (int k = 0; k < 2; ++k) b.ids[k] = c.take<uint32_t>(n_visible);
-    b.inst_block_sums = c.take<unsigned>(ceil_div<int64_t>(n_visible > 0 ? n_visible : 1, kInstThreads));
+    b.depth_min = c.take<unsigned>(1);
+    b.depth_max = c.take<unsigned>(1);
+    for (int k = 0; k < 2; ++k) b.keys[k] = c.take<uint32_t>(n);
+    for (int k = 0; k < 2; ++k) b.ids[k] = c.take<uint32_t>(n);
+    b.inst_block_sums = c.take<unsigned>(ceil_div<int64_t>(n > 0 ? n : 1, kInstThreads));
     c.off = align_up(c.off);
     b.sort_ws = c.base + c.off;
-    c.off += sort_workspace_bytes(n_visible);
+    c.off += sort_workspace_bytes(n);
     b.total = c.used();
     return b;
 }
@@ -1129,10 +1145,16 @@ InstanceBlob carve_instance_blob(void* p, int64_t n_instances, int n_tiles, int 
 
 // The state handed back to the caller only stores blob bases and counts; which ping-pong buffer holds
 // a sorted result follows from the number of radix passes, which follows from the counts.
-int depth_result_buffer(int64_t n_visible) { return n_visible > 1 ? (ceil_div(32, 8) & 1) : 0; }
+int depth_result_buffer(int64_t n_visible, int depth_key_bits) { return n_visible > 1 ? (sort_pass_count(depth_key_bits) & 1) : 0; }
 int tile_result_buffer(int64_t n_instances, int n_tiles) {
     const int end_bit = bit_length((uint32_t)(n_tiles - 1));
-    return (n_instances > 1 && end_bit > 0) ? (ceil_div(end_bit, 8) & 1) : 0;
+    return n_instances > 1 ? (sort_pass_count(end_bit) & 1) : 0;
+}
+
+cudaEvent_t counters_event() {
+    static thread_local cudaEvent_t e = nullptr;
+    if (!e && cudaEventCreateWithFlags(&e, cudaEventDisableTiming) != cudaSuccess) e = nullptr;
+    return e;
 }
 
 unsigned long long* pinned_counters() {
@@ -1159,25 +1181,42 @@ int run_front(const RasterParams& rp, int64_t n, const float* positions, const v
               bool with_depth, PointBlob* pb_out, InstanceBlob* ib_out, cudaStream_t stream) {
     const int n_tiles = rp.gw * rp.gh;
     const int64_t nb = ceil_div<int64_t>(n > 0 ? n : 1, kPreThreads);
-    // phase 1 needs only n: allocate for the worst case n_visible == n so that one blob serves both phases
-    const PointBlob sizing = carve_point_blob(nullptr, n, n, MODE);
+    const PointBlob sizing = carve_point_blob(nullptr, n, MODE);
     void* pblob = alloc_point(user, sizing.total);
     if (!pblob) { set_error("point allocator returned NULL for %zu bytes", sizing.total); return INPC_E_ALLOC; }
-    PointBlob pb = carve_point_blob(pblob, n, n, MODE);
+    const PointBlob pb = carve_point_blob(pblob, n, MODE);
 
     int64_t n_visible = 0, n_instances = 0;
+    uint32_t key_base = 0;
+    int key_bits = 0;
     if (n > 0) {
-        StageScope scope(STAGE_PREPROCESS, stream);
-        visibility_count_kernel<MODE, VARIANT><<<(unsigned)nb, kPreThreads, 0, stream>>>(positions, n, rp, pb.block_visible, pb.block_instances);
-        INPC_LAUNCH_CHECK("visibility_count_kernel");
-        scan_block_counts_kernel<<<1, kScanThreads, 0, stream>>>(pb.block_visible, pb.block_instances, nb, pb.counters);
-        INPC_LAUNCH_CHECK("scan_block_counts_kernel");
         unsigned long long* host = pinned_counters();
-        if (!host) return cuda_fail(cudaGetLastError(), "cudaHostAlloc(counters)");
-        INPC_CUDA_TRY(cudaMemcpyAsync(host, pb.counters, 2 * sizeof(unsigned long long), cudaMemcpyDeviceToHost, stream));
-        INPC_CUDA_TRY(cudaStreamSynchronize(stream));
+        cudaEvent_t ready = counters_event();
+        if (!host || !ready) return cuda_fail(cudaGetLastError(), "cudaHostAlloc / cudaEventCreate (counters)");
+        {
+            StageScope scope(STAGE_PREPROCESS, stream);
+            INPC_CUDA_TRY(cudaMemsetAsync(pb.depth_min, 0xFF, sizeof(unsigned), stream));
+            INPC_CUDA_TRY(cudaMemsetAsync(pb.depth_max, 0, sizeof(unsigned), stream));
+            visibility_count_kernel<MODE, VARIANT><<<(unsigned)nb, kPreThreads, 0, stream>>>(positions, n, rp, pb.block_visible, pb.block_instances,
+                                                                                          pb.depth_min, pb.depth_max);
+            INPC_LAUNCH_CHECK("visibility_count_kernel");
+            scan_block_counts_kernel<<<1, kScanThreads, 0, stream>>>(pb.block_visible, pb.block_instances, nb, pb.depth_min, pb.depth_max, pb.counters);
+            INPC_LAUNCH_CHECK("scan_block_counts_kernel");
+            INPC_CUDA_TRY(cudaMemcpyAsync(host, pb.counters, 4 * sizeof(unsigned long long), cudaMemcpyDeviceToHost, stream));
+            INPC_CUDA_TRY(cudaEventRecord(ready, stream));
+            // the projection pass needs nothing from the host: it runs while the host waits for the counters
+            preprocess_kernel<MODE, VARIANT><<<(unsigned)nb, kPreThreads, 0, stream>>>(
+                positions, static_cast<const __half*>(features), opacities, n, rp, pb.block_visible, pb.depth_min, pb.rec, pb.bounds,
+                pb.conic, pb.keys[0], pb.ids[0]);
+            INPC_LAUNCH_CHECK("preprocess_kernel");
+        }
+        INPC_CUDA_TRY(cudaEventSynchronize(ready));
         n_visible = (int64_t)host[0];
         n_instances = (int64_t)host[1];
+        if (n_visible > 0) {
+            key_base = (uint32_t)host[2];
+            key_bits = bit_length((uint32_t)host[3] - key_base);
+        }
         if (read_and_clear_status(STATUS_LOOKBACK_TIMEOUT)) {
             set_error("an earlier radix-sort pass gave up waiting for a predecessor tile; results of that call are invalid");
             return INPC_E_DEVICE;
@@ -1187,8 +1226,6 @@ int run_front(const RasterParams& rp, int64_t n, const float* positions, const v
         set_error("%lld (point, tile) instances exceed the 2^30 capacity", (long long)n_instances);
         return INPC_E_CAPACITY;
     }
-    // re-carve with the true visible count: the leading arrays keep their place
-    pb = carve_point_blob(pblob, n, n_visible, MODE);
 
     const InstanceBlob isz = carve_instance_blob(nullptr, n_instances, n_tiles, rp.tile, MODE, with_depth);
     void* iblob = alloc_instance(user, isz.total);
@@ -1196,18 +1233,11 @@ int run_front(const RasterParams& rp, int64_t n, const float* positions, const v
     InstanceBlob ib = carve_instance_blob(iblob, n_instances, n_tiles, rp.tile, MODE, with_depth);
     INPC_CUDA_TRY(cudaMemsetAsync(ib.ranges, 0, sizeof(uint2) * (size_t)n_tiles, stream));
 
-    if (n > 0) {
-        StageScope scope(STAGE_PREPROCESS, stream);
-        preprocess_kernel<MODE, VARIANT><<<(unsigned)nb, kPreThreads, 0, stream>>>(
-            positions, static_cast<const __half*>(features), opacities, n, rp, pb.block_visible, pb.rec, pb.bounds,
-            pb.conic, pb.keys[0], pb.ids[0]);
-        INPC_LAUNCH_CHECK("preprocess_kernel");
-    }
     int in_alt = 0;
     int rc;
     {
         StageScope scope(STAGE_SORT_DEPTH, stream);
-        rc = sort_pairs(pb.keys[0], pb.keys[1], pb.ids[0], pb.ids[1], n_visible, 32, pb.sort_ws, &in_alt, stream);
+        rc = sort_pairs(pb.keys[0], pb.keys[1], pb.ids[0], pb.ids[1], n_visible, key_bits, pb.sort_ws, &in_alt, stream);
     }
     if (rc != INPC_OK) return rc;
     const uint32_t* sorted_ids = pb.ids[in_alt];
@@ -1241,6 +1271,8 @@ int run_front(const RasterParams& rp, int64_t n, const float* positions, const v
     st->n_instances = n_instances;
     st->tile_size = rp.tile;
     st->mode = MODE;
+    st->depth_key_base = key_base;
+    st->depth_key_bits = key_bits;
     *pb_out = pb;
     *ib_out = ib;
     return INPC_OK;
@@ -1371,7 +1403,7 @@ extern "C" int inpc_rasterize_backward(const inpc_raster_state* state, const inp
     if (n == 0) return INPC_OK;
     const RasterParams rp = make_params(view, state->tile_size, 0.0f, 3.0f, nullptr);
     const int n_tiles = rp.gw * rp.gh;
-    const PointBlob pb = carve_point_blob(state->point_blob, n, state->n_visible, state->mode);
+    const PointBlob pb = carve_point_blob(state->point_blob, n, state->mode);
     const InstanceBlob ib = carve_instance_blob(state->instance_blob, state->n_instances, n_tiles, state->tile_size, state->mode, false);
     const uint32_t* ids = ib.ids[tile_result_buffer(state->n_instances, n_tiles)];
     INPC_CUDA_TRY(cudaMemsetAsync(grad_features_view, 0, sizeof(float4) * (size_t)n, stream));
@@ -1450,6 +1482,11 @@ extern "C" int inpc_render_preextracted(int mode, int tile_size, const inpc_view
 }
 
 namespace inpc_debug {
+__global__ void add_base_kernel(const uint32_t* __restrict__ src, int64_t n, uint32_t base, uint32_t* __restrict__ dst) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) dst[i] = src[i] + base;
+}
+
 __global__ void unpack_points_kernel(const PointRec* __restrict__ rec, const uint2* __restrict__ bounds, int64_t n, int which,
                                      void* __restrict__ dst) {
     const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -1475,13 +1512,19 @@ extern "C" int inpc_raster_debug_copy(const inpc_raster_state* state, const inpc
     if (!state || !view || !dst) { set_error("inpc_raster_debug_copy: null argument"); return INPC_E_INVALID; }
     const int gw = ceil_div(view->width, state->tile_size), gh = ceil_div(view->height, state->tile_size);
     const int n_tiles = gw * gh;
-    const PointBlob pb = carve_point_blob(state->point_blob, state->n_points, state->n_visible, state->mode);
+    const PointBlob pb = carve_point_blob(state->point_blob, state->n_points, state->mode);
     const InstanceBlob ib = carve_instance_blob(state->instance_blob, state->n_instances, n_tiles, state->tile_size, state->mode, false);
-    const int d = depth_result_buffer(state->n_visible);
+    const int d = depth_result_buffer(state->n_visible, state->depth_key_bits);
     const int ti = tile_result_buffer(state->n_instances, n_tiles);
     switch (which) {
         case 0: INPC_CUDA_TRY(cudaMemcpyAsync(dst, pb.ids[d], 4 * (size_t)state->n_visible, cudaMemcpyDeviceToDevice, stream)); break;
-        case 1: INPC_CUDA_TRY(cudaMemcpyAsync(dst, pb.keys[d], 4 * (size_t)state->n_visible, cudaMemcpyDeviceToDevice, stream)); break;
+        case 1:   // the sort works on offsets from the smallest depth key: add the base back
+            if (state->n_visible > 0) {
+                inpc_debug::add_base_kernel<<<(unsigned)ceil_div<int64_t>(state->n_visible, 256), 256, 0, stream>>>(
+                    pb.keys[d], state->n_visible, state->depth_key_base, static_cast<uint32_t*>(dst));
+                INPC_LAUNCH_CHECK("add_base_kernel");
+            }
+            break;
         case 2: INPC_CUDA_TRY(cudaMemcpyAsync(dst, ib.ids[ti], 4 * (size_t)state->n_instances, cudaMemcpyDeviceToDevice, stream)); break;
         case 3: INPC_CUDA_TRY(cudaMemcpyAsync(dst, ib.ranges, 8 * (size_t)n_tiles, cudaMemcpyDeviceToDevice, stream)); break;
         case 4: case 5: case 6: case 7: case 8:
