@@ -121,19 +121,36 @@ __global__ void __launch_bounds__(kThreads) radix_onesweep_pass_kernel(
         key[i] = local < valid ? __ldg(keys_in + tile_base + local) : 0xFFFFFFFFu;
     }
 
-    // stable rank within the warp's segment, per digit
+    // stable rank within the warp's segment, per digit.  The lanes holding the same digit are found
+    // with one ballot per digit bit (independent across items, so they pipeline); only the update of
+    // the warp's digit counter is a serial chain.
+    unsigned peers[kItems];
 #pragma unroll
     for (int i = 0; i < kItems; ++i) {
         const unsigned d = (key[i] >> shift) & digit_mask;
-        const unsigned peers = __match_any_sync(0xffffffffu, d);
-        const int leader = __ffs(peers) - 1;
+#ifdef INPC_SORT_MATCH_ANY
+        peers[i] = __match_any_sync(0xffffffffu, d);
+#else
+        unsigned p = 0xffffffffu;
+        for (int b = 0; b < bits; ++b) {
+            const bool one = (d >> b) & 1u;
+            const unsigned m = __ballot_sync(0xffffffffu, one);
+            p &= one ? m : ~m;
+        }
+        peers[i] = p;
+#endif
+    }
+#pragma unroll
+    for (int i = 0; i < kItems; ++i) {
+        const unsigned d = (key[i] >> shift) & digit_mask;
+        const int leader = __ffs(peers[i]) - 1;
         unsigned base = 0;
         if ((int)lane == leader) {
             base = s.warp_hist[warp][d];
-            s.warp_hist[warp][d] = base + __popc(peers);
+            s.warp_hist[warp][d] = base + __popc(peers[i]);
         }
         base = __shfl_sync(0xffffffffu, base, leader);
-        rank[i] = base + __popc(peers & ((1u << lane) - 1u));
+        rank[i] = base + __popc(peers[i] & ((1u << lane) - 1u));
         __syncwarp();
     }
     __syncthreads();
@@ -155,23 +172,35 @@ __global__ void __launch_bounds__(kThreads) radix_onesweep_pass_kernel(
     const unsigned start = block_exclusive_scan(tid < radix ? total : 0u, s.scan, &block_total);
     if (tid < radix) {
         s.bin_start[tid] = start;
-        // decoupled look-back
+        // decoupled look-back, a window of predecessors per round trip: the loads of a window are
+        // independent, so their latencies overlap; entries are then consumed nearest-first
         unsigned exclusive = 0;
         if (tile > 0) {
+            constexpr int kWindow = 8;
             int64_t j = (int64_t)tile - 1;
-            bool gave_up = false;
-            while (j >= 0) {
-                unsigned v = 0;
-                int spins = 0;
-                do {
-                    v = tile_state[(size_t)j * kRadix + tid];
-                    if ((v & kFlagMask) != 0u) break;
-                    __nanosleep(20);
-                } while (++spins < kSpinLimit);
-                if ((v & kFlagMask) == 0u) { gave_up = true; break; }
-                exclusive += v & kValueMask;
-                if (v & kFlagPrefix) break;
-                --j;
+            bool gave_up = false, finished = false;
+            while (j >= 0 && !finished && !gave_up) {
+                unsigned v[kWindow];
+#pragma unroll
+                for (int k = 0; k < kWindow; ++k) {
+                    v[k] = 2u << 30;   // beyond tile 0: an empty inclusive prefix
+                    if (j - k >= 0) v[k] = tile_state[(size_t)(j - k) * kRadix + tid];
+                }
+#pragma unroll
+                for (int k = 0; k < kWindow; ++k) {
+                    if (finished || gave_up) break;
+                    unsigned x = v[k];
+                    int spins = 0;
+                    while ((x & kFlagMask) == 0u && spins < kSpinLimit) {   // not published yet: poll this one
+                        __nanosleep(20);
+                        x = tile_state[(size_t)(j - k) * kRadix + tid];
+                        ++spins;
+                    }
+                    if ((x & kFlagMask) == 0u) { gave_up = true; break; }
+                    exclusive += x & kValueMask;
+                    if (x & kFlagPrefix) finished = true;
+                }
+                j -= kWindow;
             }
             if (gave_up) status[STATUS_LOOKBACK_TIMEOUT] = 1u;
             tile_state[(size_t)tile * kRadix + tid] = ((exclusive + total) & kValueMask) | kFlagPrefix;
