@@ -126,6 +126,7 @@ __device__ __forceinline__ Projection project_point(const float px, const float 
 }
 
 constexpr int kPreThreads = 256;
+constexpr unsigned kCountShift = 30;   // bilinear: (tiles touched - 1) in key bits 30..31 when the depth offsets fit below
 
 // Pass 1 of the deterministic compaction: per block, how many points survive culling and how many
 // (point, tile) instances they create.
@@ -133,22 +134,43 @@ template <int MODE, int VARIANT>
 __global__ void __launch_bounds__(kPreThreads) visibility_count_kernel(
     const float* __restrict__ positions, int64_t n, RasterParams rp, unsigned* __restrict__ block_visible,
     unsigned long long* __restrict__ block_instances, unsigned* __restrict__ depth_min, unsigned* __restrict__ depth_max) {
-    __shared__ unsigned s_v[kPreThreads / 32], s_lo[kPreThreads / 32], s_hi[kPreThreads / 32];
+    // Every thread takes 4 consecutive points (three 16-byte loads when the array is aligned), so a
+    // block covers 4 chunks of kPreThreads points; counts are kept per chunk because the projection
+    // pass works on chunks of kPreThreads points.
+    constexpr int kPerThread = 4;
+    constexpr int kWarpsPerChunk = kPreThreads / kPerThread / 32;   // 2
+    __shared__ unsigned s_v[kPreThreads / 32];
     __shared__ unsigned long long s_i[kPreThreads / 32];
+    __shared__ unsigned s_lo[kPreThreads / 32], s_hi[kPreThreads / 32];
     const W2C m = load_w2c(rp.v.w2c);
-    const int64_t i = (int64_t)blockIdx.x * kPreThreads + threadIdx.x;
-    unsigned vis = 0, cnt = 0, lo = 0xFFFFFFFFu, hi = 0u;
-    if (i < n) {
-        const Projection pr = project_point<MODE, VARIANT>(__ldg(positions + 3 * i), __ldg(positions + 3 * i + 1),
-                                                           __ldg(positions + 3 * i + 2), m, rp, i);
-        if (pr.visible) {
-            vis = 1;
-            cnt = (pr.x1 - pr.x0) * (pr.y1 - pr.y0);
-            lo = hi = __float_as_uint(pr.depth);   // visible depths are positive: bit patterns order like the values
+    const int64_t first = ((int64_t)blockIdx.x * kPreThreads + threadIdx.x) * kPerThread;
+    float p[3 * kPerThread];
+    if (first + kPerThread <= n && (reinterpret_cast<uintptr_t>(positions) & 15u) == 0) {
+        const float4* src = reinterpret_cast<const float4*>(positions + 3 * first);
+#pragma unroll
+        for (int k = 0; k < 3; ++k) {
+            const float4 v = __ldg(src + k);
+            p[4 * k] = v.x; p[4 * k + 1] = v.y; p[4 * k + 2] = v.z; p[4 * k + 3] = v.w;
+        }
+    } else {
+#pragma unroll
+        for (int k = 0; k < 3 * kPerThread; ++k) p[k] = first * 3 + k < 3 * n ? __ldg(positions + 3 * first + k) : 0.0f;
+    }
+    unsigned v = 0, lo = 0xFFFFFFFFu, hi = 0u;
+    unsigned long long c = 0;
+#pragma unroll
+    for (int k = 0; k < kPerThread; ++k) {
+        if (first + k < n) {
+            const Projection pr = project_point<MODE, VARIANT>(p[3 * k], p[3 * k + 1], p[3 * k + 2], m, rp, first + k);
+            if (pr.visible) {
+                v += 1u;
+                c += (pr.x1 - pr.x0) * (pr.y1 - pr.y0);
+                const unsigned bits = __float_as_uint(pr.depth);   // visible depths are positive: bit patterns order like the values
+                lo = min(lo, bits);
+                hi = max(hi, bits);
+            }
         }
     }
-    unsigned v = vis;
-    unsigned long long c = cnt;
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
         v += __shfl_down_sync(0xffffffffu, v, o);
@@ -156,16 +178,26 @@ __global__ void __launch_bounds__(kPreThreads) visibility_count_kernel(
         lo = min(lo, __shfl_down_sync(0xffffffffu, lo, o));
         hi = max(hi, __shfl_down_sync(0xffffffffu, hi, o));
     }
-    if (lane_id() == 0) { s_v[threadIdx.x >> 5] = v; s_i[threadIdx.x >> 5] = c; s_lo[threadIdx.x >> 5] = lo; s_hi[threadIdx.x >> 5] = hi; }
+    const int warp = threadIdx.x >> 5;
+    if (lane_id() == 0) { s_v[warp] = v; s_i[warp] = c; s_lo[warp] = lo; s_hi[warp] = hi; }
     __syncthreads();
-    if (threadIdx.x == 0) {
-        unsigned tv = 0, tlo = 0xFFFFFFFFu, thi = 0u;
-        unsigned long long ti = 0;
+    if (threadIdx.x < kPerThread) {
+        // chunk `threadIdx.x` of this block
+        const int64_t chunk = (int64_t)blockIdx.x * kPerThread + threadIdx.x;
+        if (chunk * kPreThreads < n) {
+            unsigned tv = 0;
+            unsigned long long ti = 0;
 #pragma unroll
-        for (int w = 0; w < kPreThreads / 32; ++w) { tv += s_v[w]; ti += s_i[w]; tlo = min(tlo, s_lo[w]); thi = max(thi, s_hi[w]); }
-        block_visible[blockIdx.x] = tv;
-        block_instances[blockIdx.x] = ti;
-        if (tv) { atomicMin(depth_min, tlo); atomicMax(depth_max, thi); }
+            for (int w = 0; w < kWarpsPerChunk; ++w) { tv += s_v[threadIdx.x * kWarpsPerChunk + w]; ti += s_i[threadIdx.x * kWarpsPerChunk + w]; }
+            block_visible[chunk] = tv;
+            block_instances[chunk] = ti;
+        }
+    }
+    if (threadIdx.x == 0) {
+        unsigned tlo = 0xFFFFFFFFu, thi = 0u;
+#pragma unroll
+        for (int w = 0; w < kPreThreads / 32; ++w) { tlo = min(tlo, s_lo[w]); thi = max(thi, s_hi[w]); }
+        if (tlo <= thi) { atomicMin(depth_min, tlo); atomicMax(depth_max, thi); }
     }
 }
 
@@ -250,7 +282,7 @@ template <int MODE, int VARIANT>
 __global__ void __launch_bounds__(kPreThreads) preprocess_kernel(
     const float* __restrict__ positions, const __half* __restrict__ features, const float* __restrict__ opacities,
     int64_t n, RasterParams rp, const unsigned* __restrict__ block_offset, const unsigned* __restrict__ depth_min,
-    PointRec* __restrict__ rec, uint2* __restrict__ bounds, float4* __restrict__ conic, uint32_t* __restrict__ depth_keys,
+    const unsigned* __restrict__ depth_max, PointRec* __restrict__ rec, uint2* __restrict__ bounds, float4* __restrict__ conic, uint32_t* __restrict__ depth_keys,
     uint32_t* __restrict__ point_ids) {
     constexpr int kHalves = VARIANT == VAR_RAW37 ? 37 : 36;
     constexpr int kSlabBytes = kPreThreads * kHalves * 2;   // multiple of 16 for both layouts
@@ -309,8 +341,15 @@ __global__ void __launch_bounds__(kPreThreads) preprocess_kernel(
     const unsigned rank = block_exclusive_scan(pr.visible ? 1u : 0u, s_scan, &total);
     if (pr.visible) {
         const unsigned slot = block_offset[blockIdx.x] + rank;
-        // sort key: offset of the depth's bit pattern from the smallest visible one (fewer radix passes)
-        depth_keys[slot] = __float_as_uint(pr.depth) - __ldg(depth_min);
+        // sort key: offset of the depth's bit pattern from the smallest visible one (fewer radix passes).
+        // A bilinear splat touches 1, 2 or 4 tiles; when the offsets leave the two top bits free that
+        // count rides there (the sort ignores bits above its range and carries them along), which
+        // saves the instance pass a gather.
+        const unsigned lo = __ldg(depth_min);
+        unsigned key = __float_as_uint(pr.depth) - lo;
+        if (MODE == INPC_MODE_BILINEAR && __ldg(depth_max) - lo < (1u << kCountShift))
+            key |= ((pr.x1 - pr.x0) * (pr.y1 - pr.y0) - 1u) << kCountShift;
+        depth_keys[slot] = key;
         point_ids[slot] = (uint32_t)i;
     }
 }
@@ -322,13 +361,15 @@ __device__ __forceinline__ unsigned tiles_of(const uint2 b) {
 // Instances per depth-sorted point, reduced per block (src/bilinear/kernels.cu:186-196 + the
 // cub::DeviceScan::ExclusiveSum of src/bilinear/forward.cu:109-115, first half).
 constexpr int kInstThreads = 256;
-__global__ void __launch_bounds__(kInstThreads) instance_count_kernel(const uint32_t* __restrict__ sorted_ids,
+template <bool PACKED>
+__global__ void __launch_bounds__(kInstThreads) instance_count_kernel(const uint32_t* __restrict__ sorted_keys,
+                                                                      const uint32_t* __restrict__ sorted_ids,
                                                                       const uint2* __restrict__ bounds, int64_t n_visible,
                                                                       unsigned* __restrict__ block_sums) {
     __shared__ unsigned s_w[kInstThreads / 32];
     const int64_t s = (int64_t)blockIdx.x * kInstThreads + threadIdx.x;
     unsigned c = 0;
-    if (s < n_visible) c = tiles_of(__ldg(bounds + __ldg(sorted_ids + s)));
+    if (s < n_visible) c = PACKED ? (__ldg(sorted_keys + s) >> kCountShift) + 1u : tiles_of(__ldg(bounds + __ldg(sorted_ids + s)));
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) c += __shfl_down_sync(0xffffffffu, c, o);
     if (lane_id() == 0) s_w[threadIdx.x >> 5] = c;
@@ -1197,7 +1238,7 @@ int run_front(const RasterParams& rp, int64_t n, const float* positions, const v
             StageScope scope(STAGE_PREPROCESS, stream);
             INPC_CUDA_TRY(cudaMemsetAsync(pb.depth_min, 0xFF, sizeof(unsigned), stream));
             INPC_CUDA_TRY(cudaMemsetAsync(pb.depth_max, 0, sizeof(unsigned), stream));
-            visibility_count_kernel<MODE, VARIANT><<<(unsigned)nb, kPreThreads, 0, stream>>>(positions, n, rp, pb.block_visible, pb.block_instances,
+            visibility_count_kernel<MODE, VARIANT><<<(unsigned)ceil_div<int64_t>(nb, 4), kPreThreads, 0, stream>>>(positions, n, rp, pb.block_visible, pb.block_instances,
                                                                                           pb.depth_min, pb.depth_max);
             INPC_LAUNCH_CHECK("visibility_count_kernel");
             scan_block_counts_kernel<<<1, kScanThreads, 0, stream>>>(pb.block_visible, pb.block_instances, nb, pb.depth_min, pb.depth_max, pb.counters);
@@ -1206,7 +1247,7 @@ int run_front(const RasterParams& rp, int64_t n, const float* positions, const v
             INPC_CUDA_TRY(cudaEventRecord(ready, stream));
             // the projection pass needs nothing from the host: it runs while the host waits for the counters
             preprocess_kernel<MODE, VARIANT><<<(unsigned)nb, kPreThreads, 0, stream>>>(
-                positions, static_cast<const __half*>(features), opacities, n, rp, pb.block_visible, pb.depth_min, pb.rec, pb.bounds,
+                positions, static_cast<const __half*>(features), opacities, n, rp, pb.block_visible, pb.depth_min, pb.depth_max, pb.rec, pb.bounds,
                 pb.conic, pb.keys[0], pb.ids[0]);
             INPC_LAUNCH_CHECK("preprocess_kernel");
         }
@@ -1245,7 +1286,11 @@ int run_front(const RasterParams& rp, int64_t n, const float* positions, const v
         const int64_t ibk = ceil_div<int64_t>(n_visible, kInstThreads);
         {
             StageScope scope(STAGE_INSTANCES, stream);
-            instance_count_kernel<<<(unsigned)ibk, kInstThreads, 0, stream>>>(sorted_ids, pb.bounds, n_visible, pb.inst_block_sums);
+            // the count of touched tiles rides in the top key bits when the depth offsets left them free
+            if (MODE == INPC_MODE_BILINEAR && key_bits <= (int)kCountShift)
+                instance_count_kernel<true><<<(unsigned)ibk, kInstThreads, 0, stream>>>(pb.keys[in_alt], sorted_ids, pb.bounds, n_visible, pb.inst_block_sums);
+            else
+                instance_count_kernel<false><<<(unsigned)ibk, kInstThreads, 0, stream>>>(pb.keys[in_alt], sorted_ids, pb.bounds, n_visible, pb.inst_block_sums);
             INPC_LAUNCH_CHECK("instance_count_kernel");
             scan_u32_kernel<<<1, kScanThreads, 0, stream>>>(pb.inst_block_sums, ibk);
             INPC_LAUNCH_CHECK("scan_u32_kernel");
@@ -1482,9 +1527,9 @@ extern "C" int inpc_render_preextracted(int mode, int tile_size, const inpc_view
 }
 
 namespace inpc_debug {
-__global__ void add_base_kernel(const uint32_t* __restrict__ src, int64_t n, uint32_t base, uint32_t* __restrict__ dst) {
+__global__ void add_base_kernel(const uint32_t* __restrict__ src, int64_t n, uint32_t base, uint32_t mask, uint32_t* __restrict__ dst) {
     const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (i < n) dst[i] = src[i] + base;
+    if (i < n) dst[i] = (src[i] & mask) + base;
 }
 
 __global__ void unpack_points_kernel(const PointRec* __restrict__ rec, const uint2* __restrict__ bounds, int64_t n, int which,
@@ -1521,7 +1566,8 @@ extern "C" int inpc_raster_debug_copy(const inpc_raster_state* state, const inpc
         case 1:   // the sort works on offsets from the smallest depth key: add the base back
             if (state->n_visible > 0) {
                 inpc_debug::add_base_kernel<<<(unsigned)ceil_div<int64_t>(state->n_visible, 256), 256, 0, stream>>>(
-                    pb.keys[d], state->n_visible, state->depth_key_base, static_cast<uint32_t*>(dst));
+                    pb.keys[d], state->n_visible, state->depth_key_base,
+                    state->depth_key_bits <= 30 ? 0x3FFFFFFFu : 0xFFFFFFFFu, static_cast<uint32_t*>(dst));
                 INPC_LAUNCH_CHECK("add_base_kernel");
             }
             break;

@@ -48,7 +48,8 @@ __global__ void __launch_bounds__(kThreads) viewpoint_weights_kernel(ViewParams 
                                                                      const float* __restrict__ centers,
                                                                      const int* __restrict__ levels,
                                                                      const float* __restrict__ weights,
-                                                                     float initial_size, float* __restrict__ out) {
+                                                                     float initial_size, float* __restrict__ out,
+                                                                     float4* __restrict__ leaf_pack) {
     const int64_t l = (int64_t)blockIdx.x * kThreads + threadIdx.x;
     if (l >= n_cells) return;
     const Rows m = load_rows(v.w2c);
@@ -72,6 +73,8 @@ __global__ void __launch_bounds__(kThreads) viewpoint_weights_kernel(ViewParams 
         w = 1.0f / (depth_scale * size_scale) * __ldg(weights + l);
     }
     out[l] = w;
+    // centre and edge length in one 16-byte record: a draw then needs one load per leaf instead of four
+    if (leaf_pack) leaf_pack[l] = make_float4(cx, cy, cz, 1.0f / scalbnf(1.0f, level) * initial_size);
 }
 
 // ---- CDF: src/sampling.cu:97-125 (Sum, multiply by 1/sum, InclusiveSum) -------------------------
@@ -271,8 +274,8 @@ __device__ __forceinline__ float leaf_scale(int level, float initial_size) {
 // ---- training samples: same acceptance test as src/sampling_kernels.cu:98-113 -------------------
 __global__ void __launch_bounds__(kThreads) training_samples_kernel(
     ViewParams v, unsigned long long seed, unsigned long long call, const float* __restrict__ cdf,
-    const unsigned* __restrict__ guide, int guide_bits, const float* __restrict__ sum_ptr, unsigned n_cells, const float* __restrict__ centers, const int* __restrict__ levels,
-    float initial_size, int64_t n_samples, float* __restrict__ positions, long long* __restrict__ indices,
+    const unsigned* __restrict__ guide, int guide_bits, const float* __restrict__ sum_ptr, unsigned n_cells,
+    const float4* __restrict__ leaf_pack, int64_t n_samples, float* __restrict__ positions, long long* __restrict__ indices,
     volatile unsigned* status) {
     const int64_t s = (int64_t)blockIdx.x * kThreads + threadIdx.x;
     if (s >= n_samples) return;
@@ -289,10 +292,10 @@ __global__ void __launch_bounds__(kThreads) training_samples_kernel(
     for (unsigned a = 0; a < (unsigned)kMaxAttempts && !ok; ++a) {
         const Draw d = philox_draw(seed, call, (unsigned)s, a);
         leaf = guided_lower_bound(cdf, guide, guide_bits, d.raw_u, d.u, n_cells);
-        const float scale = leaf_scale(__ldg(levels + leaf), initial_size);
-        x = fmaf(d.jx - 0.5f, scale, __ldg(centers + 3 * (int64_t)leaf));
-        y = fmaf(d.jy - 0.5f, scale, __ldg(centers + 3 * (int64_t)leaf + 1));
-        z = fmaf(d.jz - 0.5f, scale, __ldg(centers + 3 * (int64_t)leaf + 2));
+        const float4 lp = __ldg(leaf_pack + leaf);
+        x = fmaf(d.jx - 0.5f, lp.w, lp.x);
+        y = fmaf(d.jy - 0.5f, lp.w, lp.y);
+        z = fmaf(d.jz - 0.5f, lp.w, lp.z);
         const float vz = affine(m.r2, x, y, z);
         if (vz < v.near_plane || vz > v.far_plane) continue;
         const float inv_z = 1.0f / (vz + kEps);
@@ -311,17 +314,16 @@ __global__ void __launch_bounds__(kThreads) training_samples_kernel(
 __global__ void __launch_bounds__(kThreads) samples_kernel(unsigned long long seed, unsigned long long call,
                                                            const float* __restrict__ cdf, const unsigned* __restrict__ guide,
                                                            int guide_bits, unsigned n_cells,
-                                                           const float* __restrict__ centers, const int* __restrict__ levels,
-                                                           float initial_size, int64_t n_samples,
+                                                           const float4* __restrict__ leaf_pack, int64_t n_samples,
                                                            float* __restrict__ positions) {
     const int64_t s = (int64_t)blockIdx.x * kThreads + threadIdx.x;
     if (s >= n_samples) return;
     const Draw d = philox_draw(seed, call, (unsigned)s, 0u);
     const unsigned leaf = guided_lower_bound(cdf, guide, guide_bits, d.raw_u, d.u, n_cells);
-    const float scale = leaf_scale(__ldg(levels + leaf), initial_size);
-    positions[3 * s] = fmaf(d.jx - 0.5f, scale, __ldg(centers + 3 * (int64_t)leaf));
-    positions[3 * s + 1] = fmaf(d.jy - 0.5f, scale, __ldg(centers + 3 * (int64_t)leaf + 1));
-    positions[3 * s + 2] = fmaf(d.jz - 0.5f, scale, __ldg(centers + 3 * (int64_t)leaf + 2));
+    const float4 lp = __ldg(leaf_pack + leaf);
+    positions[3 * s] = fmaf(d.jx - 0.5f, lp.w, lp.x);
+    positions[3 * s + 1] = fmaf(d.jy - 0.5f, lp.w, lp.y);
+    positions[3 * s + 2] = fmaf(d.jz - 0.5f, lp.w, lp.z);
 }
 
 __global__ void __launch_bounds__(kThreads) draw_leaves_kernel(const float* __restrict__ cdf, unsigned n_cells,
@@ -431,6 +433,7 @@ struct SamplerWs {
     unsigned long long* total;
     unsigned* guide;    // 2^guide_bits + 1 entries
     int guide_bits;
+    float4* leaf_pack;  // (n_cells) centre + edge length
     size_t bytes;
 };
 
@@ -456,6 +459,7 @@ SamplerWs carve_sampler_ws(void* p, int64_t n_cells) {
     w.total = c.take<unsigned long long>(2);
     w.guide_bits = guide_bits_for(n);
     w.guide = c.take<unsigned>(((size_t)1 << w.guide_bits) + 2);
+    w.leaf_pack = c.take<float4>(n);
     w.bytes = c.used();
     return w;
 }
@@ -527,7 +531,7 @@ extern "C" int inpc_compute_viewpoint_weights(const inpc_view* view, int64_t n_c
     if (rc != INPC_OK) return rc;
     if (!out) { set_error("inpc_compute_viewpoint_weights: null output"); return INPC_E_INVALID; }
     viewpoint_weights_kernel<<<(unsigned)ceil_div<int64_t>(n_cells, kThreads), kThreads, 0, stream>>>(
-        to_params(view), n_cells, centers, levels, weights, initial_size, out);
+        to_params(view), n_cells, centers, levels, weights, initial_size, out, nullptr);
     INPC_LAUNCH_CHECK("viewpoint_weights_kernel");
     return INPC_OK;
 }
@@ -561,14 +565,14 @@ extern "C" int inpc_generate_training_samples(inpc_sampler* s, const inpc_view* 
     SamplerWs w = carve_sampler_ws(workspace, n_cells);
     const ViewParams v = to_params(view);
     StageScope scope(STAGE_SAMPLE, stream);
-    viewpoint_weights_kernel<<<(unsigned)ceil_div<int64_t>(n_cells, kThreads), kThreads, 0, stream>>>(v, n_cells, centers, levels, weights, initial_size, w.vw);
+    viewpoint_weights_kernel<<<(unsigned)ceil_div<int64_t>(n_cells, kThreads), kThreads, 0, stream>>>(v, n_cells, centers, levels, weights, initial_size, w.vw, w.leaf_pack);
     INPC_LAUNCH_CHECK("viewpoint_weights_kernel");
     rc = build_cdf(w.vw, n_cells, w.cdf, w.sum, w, stream);
     if (rc != INPC_OK) return rc;
     unsigned* status = device_status_ptr();
     if (!status) return INPC_E_CUDA;
     training_samples_kernel<<<(unsigned)ceil_div<int64_t>(n_samples, kThreads), kThreads, 0, stream>>>(
-        v, s->seed, s->counter, w.cdf, w.guide, w.guide_bits, w.sum, (unsigned)n_cells, centers, levels, initial_size, n_samples, positions,
+        v, s->seed, s->counter, w.cdf, w.guide, w.guide_bits, w.sum, (unsigned)n_cells, w.leaf_pack, n_samples, positions,
         reinterpret_cast<long long*>(indices), status);
     INPC_LAUNCH_CHECK("training_samples_kernel");
     s->counter += 1;
@@ -586,7 +590,7 @@ extern "C" int inpc_generate_samples(inpc_sampler* s, const inpc_view* view, int
     if (n_samples < 0 || n_samples >= ((int64_t)1 << 32) || !workspace || (n_samples > 0 && !positions)) { set_error("inpc_generate_samples: bad argument"); return INPC_E_INVALID; }
     SamplerWs w = carve_sampler_ws(workspace, n_cells);
     const ViewParams v = to_params(view);
-    viewpoint_weights_kernel<<<(unsigned)ceil_div<int64_t>(n_cells, kThreads), kThreads, 0, stream>>>(v, n_cells, centers, levels, weights, initial_size, w.vw);
+    viewpoint_weights_kernel<<<(unsigned)ceil_div<int64_t>(n_cells, kThreads), kThreads, 0, stream>>>(v, n_cells, centers, levels, weights, initial_size, w.vw, w.leaf_pack);
     INPC_LAUNCH_CHECK("viewpoint_weights_kernel");
     rc = build_cdf(w.vw, n_cells, w.cdf, w.sum, w, stream);
     if (rc != INPC_OK) return rc;
@@ -597,7 +601,7 @@ extern "C" int inpc_generate_samples(inpc_sampler* s, const inpc_view* view, int
     if (!(host[0] > 0.0f)) return INPC_OK;   // src/sampling_api.cu:154: empty result
     if (n_samples > 0) {
         samples_kernel<<<(unsigned)ceil_div<int64_t>(n_samples, kThreads), kThreads, 0, stream>>>(
-            s->seed, s->counter, w.cdf, w.guide, w.guide_bits, (unsigned)n_cells, centers, levels, initial_size, n_samples, positions);
+            s->seed, s->counter, w.cdf, w.guide, w.guide_bits, (unsigned)n_cells, w.leaf_pack, n_samples, positions);
         INPC_LAUNCH_CHECK("samples_kernel");
     }
     s->counter += 1;
@@ -618,7 +622,7 @@ extern "C" int inpc_generate_expected_samples_count(inpc_sampler* s, const inpc_
     SamplerWs w = carve_sampler_ws(workspace, n_cells);
     const ViewParams v = to_params(view);
     const unsigned blocks = (unsigned)ceil_div<int64_t>(n_cells, kThreads);
-    viewpoint_weights_kernel<<<blocks, kThreads, 0, stream>>>(v, n_cells, centers, levels, weights, initial_size, w.vw);
+    viewpoint_weights_kernel<<<blocks, kThreads, 0, stream>>>(v, n_cells, centers, levels, weights, initial_size, w.vw, nullptr);
     INPC_LAUNCH_CHECK("viewpoint_weights_kernel");
     rc = build_cdf(w.vw, n_cells, nullptr, w.sum, w, stream);
     if (rc != INPC_OK) return rc;
