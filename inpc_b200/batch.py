@@ -2,20 +2,17 @@
 
 A batch of camera views is split across ranks (rank r takes views r, r+G, r+2G, ...); each view's
 sample -> rasterize -> backward chain is independent and runs on the rank's own GPU.  Per batch the
-ranks exchange two fp32 buffers with ONE NCCL all-reduce each (over NVLink / NVSwitch; in-switch
-reduction when NCCL picks NVLS): a per-leaf statistic of the probability field and the gradient
-buffer of the appearance field.  The reference has no multi-GPU code (one view per optimizer step
+ranks exchange three buffers with one NCCL all-reduce each (over NVLink / NVSwitch; in-switch
+reduction when NCCL picks NVLS): the per-leaf max and min of the blending weights (MAX / MIN) that the
+probability-field update consumes, and the gradient buffer of the appearance field (SUM).  The reference has no multi-GPU code (one view per optimizer step
 on one GPU); correctness here means: the reduced buffers equal what one GPU accumulates over the
 same views.
 
 The appearance network itself (tiny-cuda-nn in the reference) is outside this library, so its
-gradient buffer is stood in for by a fixed scatter of the per-point gradients into `n_appearance`
-slots; the per-leaf statistic is the sum of blending weights per leaf (the quantity the
-reference's `ProbabilityField.update` reduces with max/min).
+gradient buffer is stood in for by a fixed fold of the per-point opacity gradients into
+`n_appearance` slots.
 """
 from __future__ import annotations
-
-from dataclasses import dataclass
 
 import torch
 
@@ -27,26 +24,59 @@ def partition_views(n_views: int, rank: int, world_size: int) -> list[int]:
     return list(range(rank, n_views, world_size))
 
 
-@dataclass
 class BatchBuffers:
-    leaf: torch.Tensor         # (n_leaves,) fp32
-    appearance: torch.Tensor   # (n_appearance,) fp32
+    """What a batch exchanges: per-leaf max / min of the blending weights (reduced with MAX / MIN,
+    exactly what the reference's `ProbabilityField.update` needs) and the appearance gradient buffer
+    (reduced with SUM)."""
+
+    def __init__(self, n_leaves: int, n_appearance: int, device) -> None:
+        self.appearance = torch.zeros(n_appearance, dtype=torch.float32, device=device)
+        self.device = torch.device(device)
+        if self.device.type == "cuda":
+            from .probability_field import LeafStatistics
+            self.leaf = LeafStatistics(n_leaves, device)
+        else:   # host-side tests of the exchange logic: same buffers, filled by the caller
+            self.leaf = _HostLeafStatistics(n_leaves)
 
     def zero_(self) -> None:
-        self.leaf.zero_()
+        self.leaf.reset()
         self.appearance.zero_()
+
+
+class _HostLeafStatistics:
+    NO_SAMPLE = 0x7F7F7F7F
+
+    def __init__(self, n_leaves: int) -> None:
+        self.max_sampled = torch.zeros(n_leaves, dtype=torch.float32)
+        self.min_sampled = torch.full((n_leaves,), self.NO_SAMPLE, dtype=torch.int32).view(torch.float32)
+
+    def reset(self) -> None:
+        self.max_sampled.zero_()
+        self.min_sampled.view(torch.int32).fill_(self.NO_SAMPLE)
+
+    def accumulate(self, indices: torch.Tensor, weights: torch.Tensor) -> None:
+        valid = indices >= 0
+        idx, w = indices[valid], weights.reshape(-1)[valid].clamp_min(0)
+        self.max_sampled.scatter_reduce_(0, idx, w, reduce="amax", include_self=True)
+        bits = self.min_sampled.view(torch.int32)
+        bits.scatter_reduce_(0, idx, w.view(torch.int32), reduce="amin", include_self=True)
+
+    def all_reduce(self, group=None) -> None:
+        import torch.distributed as dist
+        if not (dist.is_available() and dist.is_initialized()) or dist.get_world_size(group) == 1:
+            return
+        dist.all_reduce(self.max_sampled.view(torch.int32), op=dist.ReduceOp.MAX, group=group)
+        dist.all_reduce(self.min_sampled.view(torch.int32), op=dist.ReduceOp.MIN, group=group)
 
 
 def accumulate_view(buffers: BatchBuffers, leaf_indices: torch.Tensor, blending_weights: torch.Tensor,
                     grad_features: torch.Tensor, grad_opacities: torch.Tensor) -> None:
-    """Adds one view's contribution to the two buffers (device-side, no synchronisation).  The
-    appearance stand-in folds the per-point opacity gradient and the DC feature gradient of the
-    first channel into `n_appearance` slots."""
-    valid = leaf_indices >= 0
-    buffers.leaf.index_add_(0, leaf_indices.clamp_min(0), blending_weights * valid)
+    """Adds one view's contribution to the buffers (device-side, no synchronisation).  The appearance
+    stand-in folds the per-point opacity gradient into `n_appearance` slots."""
+    buffers.leaf.accumulate(leaf_indices, blending_weights)
     n_app = buffers.appearance.numel()
-    n = grad_opacities.numel()
-    per_point = grad_opacities.reshape(-1) + grad_features[:, 0].float()
+    per_point = grad_opacities.reshape(-1)
+    n = per_point.numel()
     if n % n_app == 0:
         buffers.appearance.add_(per_point.view(n // n_app, n_app).sum(dim=0))
     else:
@@ -55,11 +85,11 @@ def accumulate_view(buffers: BatchBuffers, leaf_indices: torch.Tensor, blending_
 
 
 def allreduce_buffers(buffers: BatchBuffers, group=None) -> None:
-    """SUM all-reduce of both buffers across the ranks of `group` (no-op without a process group)."""
+    """The one exchange step of a batch: MAX / MIN of the leaf statistics, SUM of the appearance buffer."""
     import torch.distributed as dist
     if not (dist.is_available() and dist.is_initialized()) or dist.get_world_size(group) == 1:
         return
-    dist.all_reduce(buffers.leaf, op=dist.ReduceOp.SUM, group=group)
+    buffers.leaf.all_reduce(group)
     dist.all_reduce(buffers.appearance, op=dist.ReduceOp.SUM, group=group)
 
 
@@ -77,9 +107,7 @@ class ViewShardedTrainer:
         self.mode = mode
         self.sampler = ProbabilityFieldSampler(seed)
         self.rasterizer = INPCRasterizer(tile_size=tile_size)
-        dev = features.device
-        self.buffers = BatchBuffers(torch.zeros(tree.centers.shape[0], dtype=torch.float32, device=dev),
-                                    torch.zeros(n_appearance, dtype=torch.float32, device=dev))
+        self.buffers = BatchBuffers(tree.centers.shape[0], n_appearance, features.device)
 
     def run_view(self, view, grad_image: torch.Tensor, grad_alpha: torch.Tensor, view_index: int | None = None):
         """One view, forward and backward.  `view_index` pins the random stream to the view, so the

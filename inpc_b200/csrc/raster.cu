@@ -133,7 +133,8 @@ constexpr unsigned kCountShift = 30;   // bilinear: (tiles touched - 1) in key b
 template <int MODE, int VARIANT>
 __global__ void __launch_bounds__(kPreThreads) visibility_count_kernel(
     const float* __restrict__ positions, int64_t n, RasterParams rp, unsigned* __restrict__ block_visible,
-    unsigned long long* __restrict__ block_instances, unsigned* __restrict__ depth_min, unsigned* __restrict__ depth_max) {
+    unsigned* __restrict__ group_visible, unsigned long long* __restrict__ group_instances, unsigned* __restrict__ depth_min,
+    unsigned* __restrict__ depth_max) {
     // Every thread takes 4 consecutive points (three 16-byte loads when the array is aligned), so a
     // block covers 4 chunks of kPreThreads points; counts are kept per chunk because the projection
     // pass works on chunks of kPreThreads points.
@@ -190,19 +191,23 @@ __global__ void __launch_bounds__(kPreThreads) visibility_count_kernel(
 #pragma unroll
             for (int w = 0; w < kWarpsPerChunk; ++w) { tv += s_v[threadIdx.x * kWarpsPerChunk + w]; ti += s_i[threadIdx.x * kWarpsPerChunk + w]; }
             block_visible[chunk] = tv;
-            block_instances[chunk] = ti;
+            (void)ti;
         }
     }
     if (threadIdx.x == 0) {
-        unsigned tlo = 0xFFFFFFFFu, thi = 0u;
+        unsigned tlo = 0xFFFFFFFFu, thi = 0u, tv = 0;
+        unsigned long long ti = 0;
 #pragma unroll
-        for (int w = 0; w < kPreThreads / 32; ++w) { tlo = min(tlo, s_lo[w]); thi = max(thi, s_hi[w]); }
+        for (int w = 0; w < kPreThreads / 32; ++w) { tlo = min(tlo, s_lo[w]); thi = max(thi, s_hi[w]); tv += s_v[w]; ti += s_i[w]; }
+        // totals of this group of 4 chunks: the one-block scan runs over groups, four times fewer entries
+        group_visible[blockIdx.x] = tv;
+        group_instances[blockIdx.x] = ti;
         if (tlo <= thi) { atomicMin(depth_min, tlo); atomicMax(depth_max, thi); }
     }
 }
 
-// Exclusive scan of per-block counts by one block; totals land in counters[0] (visible, u64) and
-// counters[1] (instances, u64).
+// Exclusive scan of the per-group counts (groups of 4 chunks) by one block; totals land in counters[0]
+// (visible) and counters[1] (instances), the depth range in counters[2..3].
 constexpr int kScanThreads = 1024;
 __global__ void __launch_bounds__(kScanThreads) scan_block_counts_kernel(unsigned* __restrict__ block_visible,
                                                                          const unsigned long long* __restrict__ block_instances,
@@ -281,7 +286,8 @@ __device__ __forceinline__ float sh_eval_channel(const float* b, const __half* h
 template <int MODE, int VARIANT>
 __global__ void __launch_bounds__(kPreThreads) preprocess_kernel(
     const float* __restrict__ positions, const __half* __restrict__ features, const float* __restrict__ opacities,
-    int64_t n, RasterParams rp, const unsigned* __restrict__ block_offset, const unsigned* __restrict__ depth_min,
+    int64_t n, RasterParams rp, const unsigned* __restrict__ block_visible, const unsigned* __restrict__ group_offset,
+    const unsigned* __restrict__ depth_min,
     const unsigned* __restrict__ depth_max, PointRec* __restrict__ rec, uint2* __restrict__ bounds, float4* __restrict__ conic, uint32_t* __restrict__ depth_keys,
     uint32_t* __restrict__ point_ids) {
     constexpr int kHalves = VARIANT == VAR_RAW37 ? 37 : 36;
@@ -340,7 +346,9 @@ __global__ void __launch_bounds__(kPreThreads) preprocess_kernel(
     unsigned total;
     const unsigned rank = block_exclusive_scan(pr.visible ? 1u : 0u, s_scan, &total);
     if (pr.visible) {
-        const unsigned slot = block_offset[blockIdx.x] + rank;
+        // slot = survivors of all groups before + of the earlier chunks of this group + rank in this chunk
+        unsigned slot = __ldg(group_offset + (blockIdx.x >> 2)) + rank;
+        for (unsigned c = blockIdx.x & ~3u; c < blockIdx.x; ++c) slot += __ldg(block_visible + c);
         // sort key: offset of the depth's bit pattern from the smallest visible one (fewer radix passes).
         // A bilinear splat touches 1, 2 or 4 tiles; when the offsets leave the two top bits free that
         // count rides there (the sort ignores bits above its range and carries them along), which
@@ -360,7 +368,7 @@ __device__ __forceinline__ unsigned tiles_of(const uint2 b) {
 
 // Instances per depth-sorted point, reduced per block (src/bilinear/kernels.cu:186-196 + the
 // cub::DeviceScan::ExclusiveSum of src/bilinear/forward.cu:109-115, first half).
-constexpr int kInstThreads = 256;
+constexpr int kInstThreads = 1024;   // block sums over 1024 points keep the one-block scan short
 template <bool PACKED>
 __global__ void __launch_bounds__(kInstThreads) instance_count_kernel(const uint32_t* __restrict__ sorted_keys,
                                                                       const uint32_t* __restrict__ sorted_ids,
@@ -433,15 +441,20 @@ __global__ void __launch_bounds__(kInstThreads) emit_instances_kernel(const uint
 // Run boundaries of the sorted tile keys -> [first, last+1) per tile (src/bilinear/kernels.cu:222-239).
 __global__ void __launch_bounds__(256) tile_ranges_kernel(const uint32_t* __restrict__ keys, int64_t n_instances,
                                                           uint2* __restrict__ ranges) {
-    const int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x;
-    if (i >= n_instances) return;
-    const uint32_t k = __ldg(keys + i);
-    if (i == 0) ranges[k].x = 0u;
-    else {
-        const uint32_t kp = __ldg(keys + i - 1);
-        if (kp != k) { ranges[kp].y = (unsigned)i; ranges[k].x = (unsigned)i; }
+    constexpr int kPer = 8;
+    const int64_t first = ((int64_t)blockIdx.x * 256 + threadIdx.x) * kPer;
+    if (first >= n_instances) return;
+    uint32_t prev = first > 0 ? __ldg(keys + first - 1) : 0u;
+#pragma unroll
+    for (int k = 0; k < kPer; ++k) {
+        const int64_t i = first + k;
+        if (i >= n_instances) break;
+        const uint32_t key = __ldg(keys + i);
+        if (i == 0) ranges[key].x = 0u;
+        else if (key != prev) { ranges[prev].y = (unsigned)i; ranges[key].x = (unsigned)i; }
+        if (i == n_instances - 1) ranges[key].y = (unsigned)n_instances;
+        prev = key;
     }
-    if (i == n_instances - 1) ranges[k].y = (unsigned)n_instances;
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -483,41 +496,63 @@ constexpr int kMinBatchesPerSegment = INPC_MIN_BATCHES;
 #define INPC_IPT16 1
 #endif
 
-// One block: per tile the number of segments, their exclusive scan, and the segment records.
-__global__ void __launch_bounds__(kScanThreads) build_segments_kernel(const uint2* __restrict__ ranges, int n_tiles, int batch,
-                                                                      Segment* __restrict__ segs, uint32_t* __restrict__ tile_first,
+__device__ __forceinline__ unsigned segment_length(unsigned len, unsigned batch) {
+    const unsigned s_min = batch * (unsigned)kMinBatchesPerSegment;
+    const unsigned want = ceil_div(len, (unsigned)kMaxSegmentsPerTile);
+    return max(s_min, ceil_div(want, batch) * batch);
+}
+
+// One block: number of segments per tile and their exclusive scan (tile_first), total in *n_segments.
+__global__ void __launch_bounds__(kScanThreads) count_segments_kernel(const uint2* __restrict__ ranges, int n_tiles, int batch,
+                                                                      uint32_t* __restrict__ tile_first,
                                                                       uint32_t* __restrict__ n_segments) {
+    constexpr int kItems = 16;
     __shared__ unsigned s_scan[kScanThreads / 32 + 1];
     unsigned running = 0;
-    const unsigned s_min = (unsigned)(batch * kMinBatchesPerSegment);
-    for (int base = 0; base < n_tiles; base += kScanThreads) {
-        const int t = base + threadIdx.x;
-        unsigned seg_len = s_min, n = 0;
-        uint2 r = make_uint2(0u, 0u);
-        if (t < n_tiles) {
-            r = ranges[t];
-            const unsigned len = r.y - r.x;
-            const unsigned want = ceil_div(len, (unsigned)kMaxSegmentsPerTile);
-            seg_len = max(s_min, ceil_div(want, (unsigned)batch) * (unsigned)batch);
-            n = max(1u, ceil_div(len, seg_len));
+    for (int base = 0; base < n_tiles; base += kScanThreads * kItems) {
+        const int t0 = base + threadIdx.x * kItems;
+        unsigned v[kItems];
+        unsigned sum = 0;
+#pragma unroll
+        for (int k = 0; k < kItems; ++k) {
+            v[k] = 0u;
+            if (t0 + k < n_tiles) {
+                const uint2 r = ranges[t0 + k];
+                const unsigned len = r.y - r.x;
+                v[k] = max(1u, ceil_div(len, segment_length(len, (unsigned)batch)));
+            }
+            sum += v[k];
         }
         unsigned total;
-        const unsigned ex = block_exclusive_scan(n, s_scan, &total);
-        if (t < n_tiles) {
-            const unsigned first = running + ex;
-            tile_first[t] = first;
-            for (unsigned s = 0; s < n; ++s) {
-                Segment g;
-                g.tile = (uint32_t)t;
-                g.begin = r.x + s * seg_len;
-                g.end = min(r.y, g.begin + seg_len);
-                g.info = s | (n << 16);
-                segs[first + s] = g;
-            }
+        unsigned ex = running + block_exclusive_scan(sum, s_scan, &total);
+#pragma unroll
+        for (int k = 0; k < kItems; ++k) {
+            if (t0 + k < n_tiles) tile_first[t0 + k] = ex;
+            ex += v[k];
         }
         running += total;
     }
     if (threadIdx.x == 0) *n_segments = running;
+}
+
+// One thread per tile writes the tile's segment records.
+__global__ void __launch_bounds__(256) emit_segments_kernel(const uint2* __restrict__ ranges, int n_tiles, int batch,
+                                                            const uint32_t* __restrict__ tile_first, Segment* __restrict__ segs) {
+    const int t = blockIdx.x * 256 + threadIdx.x;
+    if (t >= n_tiles) return;
+    const uint2 r = ranges[t];
+    const unsigned len = r.y - r.x;
+    const unsigned seg_len = segment_length(len, (unsigned)batch);
+    const unsigned n = max(1u, ceil_div(len, seg_len));
+    const unsigned first = tile_first[t];
+    for (unsigned s = 0; s < n; ++s) {
+        Segment g;
+        g.tile = (uint32_t)t;
+        g.begin = r.x + s * seg_len;
+        g.end = min(r.y, g.begin + seg_len);
+        g.info = s | (n << 16);
+        segs[first + s] = g;
+    }
 }
 
 // Stages instance `j` of the batch starting at `base`: record into shared memory, bit into the masks of
@@ -1106,8 +1141,9 @@ struct PointBlob {
     PointRec* rec;
     uint2* bounds;
     float4* conic;
-    unsigned* block_visible;
-    unsigned long long* block_instances;
+    unsigned* block_visible;              // survivors per chunk of kPreThreads points
+    unsigned* group_visible;              // per group of 4 chunks; scanned in place
+    unsigned long long* group_instances;
     unsigned long long* counters;   // visible, instances, smallest / largest depth bit pattern
     unsigned* depth_min;
     unsigned* depth_max;
@@ -1128,7 +1164,8 @@ PointBlob carve_point_blob(void* p, int64_t n, int mode) {
     b.bounds = c.take<uint2>(n);
     b.conic = mode == INPC_MODE_GAUSSIAN ? c.take<float4>(n) : nullptr;
     b.block_visible = c.take<unsigned>(nb);
-    b.block_instances = c.take<unsigned long long>(nb);
+    b.group_visible = c.take<unsigned>(ceil_div<int64_t>(nb, 4));
+    b.group_instances = c.take<unsigned long long>(ceil_div<int64_t>(nb, 4));
     b.counters = c.take<unsigned long long>(4);
     b.depth_min = c.take<unsigned>(1);
     b.depth_max = c.take<unsigned>(1);
@@ -1238,16 +1275,18 @@ int run_front(const RasterParams& rp, int64_t n, const float* positions, const v
             StageScope scope(STAGE_PREPROCESS, stream);
             INPC_CUDA_TRY(cudaMemsetAsync(pb.depth_min, 0xFF, sizeof(unsigned), stream));
             INPC_CUDA_TRY(cudaMemsetAsync(pb.depth_max, 0, sizeof(unsigned), stream));
-            visibility_count_kernel<MODE, VARIANT><<<(unsigned)ceil_div<int64_t>(nb, 4), kPreThreads, 0, stream>>>(positions, n, rp, pb.block_visible, pb.block_instances,
-                                                                                          pb.depth_min, pb.depth_max);
+            const int64_t groups = ceil_div<int64_t>(nb, 4);
+            visibility_count_kernel<MODE, VARIANT><<<(unsigned)groups, kPreThreads, 0, stream>>>(positions, n, rp, pb.block_visible, pb.group_visible,
+                                                                                             pb.group_instances, pb.depth_min, pb.depth_max);
             INPC_LAUNCH_CHECK("visibility_count_kernel");
-            scan_block_counts_kernel<<<1, kScanThreads, 0, stream>>>(pb.block_visible, pb.block_instances, nb, pb.depth_min, pb.depth_max, pb.counters);
+            scan_block_counts_kernel<<<1, kScanThreads, 0, stream>>>(pb.group_visible, pb.group_instances, groups, pb.depth_min, pb.depth_max, pb.counters);
             INPC_LAUNCH_CHECK("scan_block_counts_kernel");
             INPC_CUDA_TRY(cudaMemcpyAsync(host, pb.counters, 4 * sizeof(unsigned long long), cudaMemcpyDeviceToHost, stream));
             INPC_CUDA_TRY(cudaEventRecord(ready, stream));
             // the projection pass needs nothing from the host: it runs while the host waits for the counters
             preprocess_kernel<MODE, VARIANT><<<(unsigned)nb, kPreThreads, 0, stream>>>(
-                positions, static_cast<const __half*>(features), opacities, n, rp, pb.block_visible, pb.depth_min, pb.depth_max, pb.rec, pb.bounds,
+                positions, static_cast<const __half*>(features), opacities, n, rp, pb.block_visible, pb.group_visible, pb.depth_min, pb.depth_max,
+                pb.rec, pb.bounds,
                 pb.conic, pb.keys[0], pb.ids[0]);
             INPC_LAUNCH_CHECK("preprocess_kernel");
         }
@@ -1301,13 +1340,15 @@ int run_front(const RasterParams& rp, int64_t n, const float* positions, const v
         int t_alt = 0;
         rc = sort_pairs(ib.keys[0], ib.keys[1], ib.ids[0], ib.ids[1], n_instances, bit_length((uint32_t)(n_tiles - 1)), ib.sort_ws, &t_alt, stream);
         if (rc != INPC_OK) return rc;
-        tile_ranges_kernel<<<(unsigned)ceil_div<int64_t>(n_instances, 256), 256, 0, stream>>>(ib.keys[t_alt], n_instances, ib.ranges);
+        tile_ranges_kernel<<<(unsigned)ceil_div<int64_t>(n_instances, 256 * 8), 256, 0, stream>>>(ib.keys[t_alt], n_instances, ib.ranges);
         INPC_LAUNCH_CHECK("tile_ranges_kernel");
     }
     if (MODE == INPC_MODE_BILINEAR) {
         StageScope scope(STAGE_SORT_TILE, stream);
-        build_segments_kernel<<<1, kScanThreads, 0, stream>>>(ib.ranges, n_tiles, blend_batch(rp.tile), ib.segs, ib.tile_first, ib.n_segments);
-        INPC_LAUNCH_CHECK("build_segments_kernel");
+        count_segments_kernel<<<1, kScanThreads, 0, stream>>>(ib.ranges, n_tiles, blend_batch(rp.tile), ib.tile_first, ib.n_segments);
+        INPC_LAUNCH_CHECK("count_segments_kernel");
+        emit_segments_kernel<<<ceil_div(n_tiles, 256), 256, 0, stream>>>(ib.ranges, n_tiles, blend_batch(rp.tile), ib.tile_first, ib.segs);
+        INPC_LAUNCH_CHECK("emit_segments_kernel");
     }
     st->point_blob = pblob;
     st->instance_blob = iblob;

@@ -1,0 +1,67 @@
+"""Fused update of the octree probability field from one step's samples: the consumer of the
+rasterizer's `blending_weights` (reference: Modules/ProbabilityField.py:146-157, called from
+Trainer.py:167-168).  The reference does it with two `scatter_reduce_` calls and four element-wise
+ops; here it is two kernels of libinpc_b200, and the per-leaf statistics can be accumulated over
+several views and reduced across ranks before they are applied."""
+from __future__ import annotations
+
+import torch
+
+from . import _cabi
+from .rasterization import _cuda_f32, _ptr, _stream
+
+DECAY = 0.9968
+
+
+class LeafStatistics:
+    """Running per-leaf max / min of blending weights.  The two buffers hold the bit patterns of
+    non-negative floats, so `MAX` / `MIN` all-reduces of their int32 views reduce them exactly."""
+
+    def __init__(self, n_leaves: int, device) -> None:
+        self.max_sampled = torch.empty(n_leaves, dtype=torch.float32, device=device)
+        self.min_sampled = torch.empty(n_leaves, dtype=torch.float32, device=device)
+        self.reset()
+
+    def reset(self) -> None:
+        with torch.cuda.device(self.max_sampled.device):
+            _cabi.check(_cabi.lib().inpc_leaf_stats_reset(_ptr(self.max_sampled), _ptr(self.min_sampled),
+                                                          self.max_sampled.numel(), _stream()))
+
+    def accumulate(self, indices: torch.Tensor, weights: torch.Tensor) -> None:
+        if not indices.is_cuda or indices.dtype != torch.int64:
+            raise TypeError("indices must be a CUDA int64 tensor")
+        weights = _cuda_f32(weights.reshape(-1), "weights")
+        indices = indices.contiguous()
+        if indices.numel() != weights.numel():
+            raise ValueError("indices and weights must have the same number of elements")
+        with torch.cuda.device(self.max_sampled.device):
+            _cabi.check(_cabi.lib().inpc_leaf_stats_accumulate(_ptr(indices), _ptr(weights), indices.numel(),
+                                                               _ptr(self.max_sampled), _ptr(self.min_sampled),
+                                                               self.max_sampled.numel(), _stream()))
+
+    def all_reduce(self, group=None) -> None:
+        import torch.distributed as dist
+        if not (dist.is_available() and dist.is_initialized()) or dist.get_world_size(group) == 1:
+            return
+        # bit patterns of non-negative floats order like int32; the "no sample" marker is the largest
+        dist.all_reduce(self.max_sampled.view(torch.int32), op=dist.ReduceOp.MAX, group=group)
+        dist.all_reduce(self.min_sampled.view(torch.int32), op=dist.ReduceOp.MIN, group=group)
+
+
+def update(leaf_weights: torch.Tensor, leaf_subdivision_scores: torch.Tensor, stats: LeafStatistics,
+           decay: float = DECAY) -> None:
+    """In-place `ProbabilityField.update` from accumulated statistics."""
+    for t, name in ((leaf_weights, "leaf_weights"), (leaf_subdivision_scores, "leaf_subdivision_scores")):
+        if not t.is_cuda or t.dtype != torch.float32 or not t.is_contiguous():
+            raise TypeError(f"{name} must be a contiguous CUDA float32 tensor")
+    with torch.cuda.device(leaf_weights.device):
+        _cabi.check(_cabi.lib().inpc_leaf_update(_ptr(leaf_weights), _ptr(leaf_subdivision_scores), _ptr(stats.max_sampled),
+                                                 _ptr(stats.min_sampled), leaf_weights.numel(), float(decay), _stream()))
+
+
+def update_from_samples(leaf_weights: torch.Tensor, leaf_subdivision_scores: torch.Tensor, indices: torch.Tensor,
+                        weights: torch.Tensor, decay: float = DECAY) -> None:
+    """Drop-in for `ProbabilityField.update(indices, weights)` on the module's two leaf buffers."""
+    stats = LeafStatistics(leaf_weights.numel(), leaf_weights.device)
+    stats.accumulate(indices, weights)
+    update(leaf_weights, leaf_subdivision_scores, stats, decay)

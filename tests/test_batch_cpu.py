@@ -31,31 +31,42 @@ def _view_contribution(view_index, n_leaves, n_points, n_app):
 
 
 def _accumulate(views, n_leaves=50, n_points=96, n_app=32):
-    buf = BatchBuffers(torch.zeros(n_leaves), torch.zeros(n_app))
+    buf = BatchBuffers(n_leaves, n_app, "cpu")
     for v in views:
         accumulate_view(buf, *_view_contribution(v, n_leaves, n_points, n_app))
     return buf
 
 
-def test_accumulate_matches_explicit_sums():
-    buf = _accumulate([0])
-    idx, bw, gf, go = _view_contribution(0, 50, 96, 32)
-    leaf = torch.zeros(50)
-    for i, w in zip(idx.tolist(), bw.tolist()):
-        if i >= 0:
-            leaf[i] += w
-    assert torch.allclose(buf.leaf, leaf, atol=1e-6)
-    per_point = go.reshape(-1) + gf[:, 0].float()
+def _finished(buf):
+    """(max, min) with the "no sample" marker read as 0, as the update kernel does."""
+    mn = buf.leaf.min_sampled.clone()
+    mn[buf.leaf.min_sampled.view(torch.int32) == 0x7F7F7F7F] = 0.0
+    return buf.leaf.max_sampled.clone(), mn
+
+
+def test_accumulate_matches_explicit_reductions():
+    buf = _accumulate([0, 1])
+    mx, mn = torch.zeros(50), torch.full((50,), float("inf"))
     app = torch.zeros(32)
-    for k, v in enumerate(per_point.tolist()):
-        app[k % 32] += v
+    for v in (0, 1):
+        idx, bw, gf, go = _view_contribution(v, 50, 96, 32)
+        for i, w in zip(idx.tolist(), bw.tolist()):
+            if i >= 0:
+                mx[i] = max(mx[i], w)
+                mn[i] = min(mn[i], w)
+        for k, g in enumerate(go.reshape(-1).tolist()):
+            app[k % 32] += g
+    mn[torch.isinf(mn)] = 0.0
+    got_mx, got_mn = _finished(buf)
+    assert torch.equal(got_mx, mx) and torch.equal(got_mn, mn)
     assert torch.allclose(buf.appearance, app, atol=1e-6)
     # ragged point count takes the index_add path
-    buf2 = BatchBuffers(torch.zeros(50), torch.zeros(32))
+    buf2 = BatchBuffers(50, 32, "cpu")
+    idx, bw, gf, go = _view_contribution(0, 50, 96, 32)
     accumulate_view(buf2, idx[:90], bw[:90], gf[:90], go[:90])
     app2 = torch.zeros(32)
-    for k, v in enumerate(per_point[:90].tolist()):
-        app2[k % 32] += v
+    for k, g in enumerate(go.reshape(-1)[:90].tolist()):
+        app2[k % 32] += g
     assert torch.allclose(buf2.appearance, app2, atol=1e-6)
 
 
@@ -74,7 +85,7 @@ def _worker(rank, world, port, n_views, fail_rank, out):
             raise RuntimeError("injected host-side failure before the exchange step")
         buf = _accumulate(partition_views(n_views, rank, world))
         allreduce_buffers(buf)
-        out[rank] = (buf.leaf.clone(), buf.appearance.clone())
+        out[rank] = (*_finished(buf), buf.appearance.clone())
     except Exception as e:  # a failed peer surfaces as an exception, never as a hang
         out[rank] = repr(e)
     finally:
@@ -101,9 +112,10 @@ def test_two_rank_allreduce_equals_single_rank_sum():
     n_views = 5
     single = _accumulate(range(n_views))
     out = _run_world(2, n_views)
+    smx, smn = _finished(single)
     for r in range(2):
-        leaf, app = out[r]
-        assert torch.allclose(leaf, single.leaf, atol=1e-5)
+        mx, mn, app = out[r]
+        assert torch.equal(mx, smx) and torch.equal(mn, smn)            # MAX / MIN are exact in any order
         assert torch.allclose(app, single.appearance, atol=1e-5)
 
 

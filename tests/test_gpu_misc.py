@@ -60,3 +60,40 @@ def test_weight_decay_grads():
     assert torch.equal(out2, out)
     if RB.available():
         assert torch.equal(out, RB.weight_decay(w.to(DEV)))
+
+
+def test_probability_field_update_matches_reference_formula():
+    """`ProbabilityField.update` (Modules/ProbabilityField.py:146-157) as fused kernels, against the
+    reference's own torch formulation, including leaves without samples and slots without a leaf."""
+    from inpc_b200 import probability_field as PF
+    g = torch.Generator().manual_seed(4)
+    n_leaves, n = 5000, 200_000
+    leaf_w = torch.rand(n_leaves, generator=g)
+    scores = torch.rand(n_leaves, generator=g) * 0.1
+    idx = torch.randint(0, n_leaves // 2, (n,), generator=g)           # the upper half of the leaves gets no sample
+    idx[::97] = -1
+    w = torch.rand(n, generator=g) ** 4
+    # the reference, on the CPU
+    rw, rs = leaf_w.clone(), scores.clone()
+    valid = idx >= 0
+    rw.mul_(0.9968)
+    rs.mul_(0.9968)
+    mx, mn = torch.zeros_like(rw), torch.zeros_like(rw)
+    mx.scatter_reduce_(0, idx[valid], w[valid], reduce="amax", include_self=False)
+    mn.scatter_reduce_(0, idx[valid], w[valid], reduce="amin", include_self=False)
+    torch.maximum(rw, mx, out=rw)
+    torch.maximum(rs, (mx - mn).clamp_(0.0, 1.0), out=rs)
+    # the kernels, in two accumulation steps as a multi-view batch does
+    lw, sc = leaf_w.to(DEV), scores.to(DEV)
+    stats = PF.LeafStatistics(n_leaves, DEV)
+    half = n // 2
+    stats.accumulate(idx[:half].to(DEV), w[:half].to(DEV))
+    stats.accumulate(idx[half:].to(DEV), w[half:].to(DEV))
+    PF.update(lw, sc, stats)
+    assert torch.equal(lw.cpu(), rw) and torch.equal(sc.cpu(), rs)
+    # one-call form
+    lw2, sc2 = leaf_w.to(DEV), scores.to(DEV)
+    PF.update_from_samples(lw2, sc2, idx.to(DEV), w.to(DEV))
+    assert torch.equal(lw2, lw) and torch.equal(sc2, sc)
+    with pytest.raises(TypeError):
+        stats.accumulate(idx.int().to(DEV), w.to(DEV))
