@@ -19,10 +19,17 @@ namespace {
 constexpr int kRadixBits = 9;            // widest digit of a pass: 27 key bits sort in 3 passes, 32 in 4 x 8
 constexpr int kRadix = 1 << kRadixBits;  // capacity of every per-digit array
 constexpr int kMaxPasses = 4;
-constexpr int kThreads = 512;
-constexpr int kItems = 16;
+#ifndef INPC_SORT_THREADS
+#define INPC_SORT_THREADS 512
+#endif
+#ifndef INPC_SORT_ITEMS
+#define INPC_SORT_ITEMS 16
+#endif
+constexpr int kThreads = INPC_SORT_THREADS;
+constexpr int kItems = INPC_SORT_ITEMS;
 constexpr int kTile = kThreads * kItems;   // 8192 pairs per tile
 constexpr int kWarps = kThreads / 32;
+constexpr int kDigitsPerThread = (kRadix + kThreads - 1) / kThreads;   // digits a thread owns in the scan / look-back phase
 
 constexpr unsigned kFlagAggregate = 1u << 30;
 constexpr unsigned kFlagPrefix = 2u << 30;
@@ -83,7 +90,7 @@ __global__ void __launch_bounds__(kRadix) radix_scan_histogram_kernel(const unsi
 struct PassSmem {
     union {
         unsigned warp_hist[kWarps][kRadix];   // ranking phase
-        uint32_t keys[kTile];                 // reorder phase (keys), 32 KB, as large as warp_hist
+        uint32_t keys[kTile];                 // reorder phase (keys); the two never live at the same time
     };
     uint32_t values[kTile];
     unsigned bin_start[kRadix];    // tile-local exclusive start of each digit
@@ -155,23 +162,33 @@ __global__ void __launch_bounds__(kThreads) radix_onesweep_pass_kernel(
     }
     __syncthreads();
 
-    // per digit: exclusive scan over warps, tile total
+    // per digit: exclusive scan over warps, tile total.  Thread t owns digits t*kDigitsPerThread ...
     const unsigned radix = 1u << bits;
-    unsigned total = 0;
-    if (tid < radix) {
+    unsigned total[kDigitsPerThread];
+    unsigned thread_sum = 0;
 #pragma unroll
-        for (int w = 0; w < kWarps; ++w) {
-            const unsigned c = s.warp_hist[w][tid];
-            s.warp_hist[w][tid] = total;
-            total += c;
+    for (int q = 0; q < kDigitsPerThread; ++q) {
+        const unsigned d = tid * kDigitsPerThread + q;
+        total[q] = 0;
+        if (d < radix) {
+#pragma unroll
+            for (int w = 0; w < kWarps; ++w) {
+                const unsigned c = s.warp_hist[w][d];
+                s.warp_hist[w][d] = total[q];
+                total[q] += c;
+            }
+            // publish this tile's digit count before any waiting
+            tile_state[(size_t)tile * kRadix + d] = total[q] | (tile == 0 ? kFlagPrefix : kFlagAggregate);
         }
-        // publish this tile's digit count before any waiting
-        tile_state[(size_t)tile * kRadix + tid] = total | (tile == 0 ? kFlagPrefix : kFlagAggregate);
+        thread_sum += total[q];
     }
     unsigned block_total;
-    const unsigned start = block_exclusive_scan(tid < radix ? total : 0u, s.scan, &block_total);
-    if (tid < radix) {
-        s.bin_start[tid] = start;
+    unsigned start = block_exclusive_scan(thread_sum, s.scan, &block_total);
+#pragma unroll
+    for (int q = 0; q < kDigitsPerThread; ++q) {
+        const unsigned d = tid * kDigitsPerThread + q;
+        if (d >= radix) break;
+        s.bin_start[d] = start;
         // decoupled look-back, a window of predecessors per round trip: the loads of a window are
         // independent, so their latencies overlap; entries are then consumed nearest-first
         unsigned exclusive = 0;
@@ -184,7 +201,7 @@ __global__ void __launch_bounds__(kThreads) radix_onesweep_pass_kernel(
 #pragma unroll
                 for (int k = 0; k < kWindow; ++k) {
                     v[k] = 2u << 30;   // beyond tile 0: an empty inclusive prefix
-                    if (j - k >= 0) v[k] = tile_state[(size_t)(j - k) * kRadix + tid];
+                    if (j - k >= 0) v[k] = tile_state[(size_t)(j - k) * kRadix + d];
                 }
 #pragma unroll
                 for (int k = 0; k < kWindow; ++k) {
@@ -193,7 +210,7 @@ __global__ void __launch_bounds__(kThreads) radix_onesweep_pass_kernel(
                     int spins = 0;
                     while ((x & kFlagMask) == 0u && spins < kSpinLimit) {   // not published yet: poll this one
                         __nanosleep(20);
-                        x = tile_state[(size_t)(j - k) * kRadix + tid];
+                        x = tile_state[(size_t)(j - k) * kRadix + d];
                         ++spins;
                     }
                     if ((x & kFlagMask) == 0u) { gave_up = true; break; }
@@ -203,9 +220,10 @@ __global__ void __launch_bounds__(kThreads) radix_onesweep_pass_kernel(
                 j -= kWindow;
             }
             if (gave_up) status[STATUS_LOOKBACK_TIMEOUT] = 1u;
-            tile_state[(size_t)tile * kRadix + tid] = ((exclusive + total) & kValueMask) | kFlagPrefix;
+            tile_state[(size_t)tile * kRadix + d] = ((exclusive + total[q]) & kValueMask) | kFlagPrefix;
         }
-        s.global_off[tid] = digit_base[tid] + exclusive - start;
+        s.global_off[d] = digit_base[d] + exclusive - start;
+        start += total[q];
     }
     __syncthreads();
 
@@ -337,7 +355,6 @@ namespace inpc {
 namespace {
 constexpr int64_t kStaticMaxPairs = 1 << 20;
 constexpr size_t kStaticTiles = (kStaticMaxPairs + kTile - 1) / kTile;
-static_assert(kThreads >= kRadix, "one thread per digit");
 constexpr size_t kStaticWorkspaceBytes = (kMaxPasses * kRadix * 4 + 256)            // histograms + tickets
                                          + kMaxPasses * kStaticTiles * kRadix * 4   // look-back state
                                          + kMaxPasses * kRadix * 4;                 // digit bases

@@ -794,14 +794,19 @@ __global__ void __launch_bounds__(T * T) blend_combine_kernel(const Segment* __r
     const int px = tx * T + t % T, py = ty * T + t / T;
     float4 run = make_float4(0.f, 0.f, 0.f, 0.f);
     float z = 0.0f;
+    // transmittance where the pixel stopped: the end value of the first segment that fell below the
+    // threshold (later segments start below it and only carry the product of everything skipped)
+    float t_final = 1.0f;
+    bool stopped = false;
     for (unsigned s0 = 0; s0 < n_seg; s0 += 4) {
         float4 c[4];
-        float zz[4];
+        float zz[4], tt[4];
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
             const unsigned s = s0 + k;
             c[k] = s < n_seg ? seg_C[(size_t)(first + s) * P + t] : make_float4(0.f, 0.f, 0.f, 0.f);
             zz[k] = (KIND == BLEND_INFER && s < n_seg) ? seg_Z[(size_t)(first + s) * P + t] : 0.0f;
+            tt[k] = (KIND == BLEND_INFER && s < n_seg) ? seg_T[(size_t)(first + s) * P + t] : 1.0f;
         }
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
@@ -809,6 +814,10 @@ __global__ void __launch_bounds__(T * T) blend_combine_kernel(const Segment* __r
             if (KIND == BLEND_TRAIN && s < n_seg) seg_C[(size_t)(first + s) * P + t] = run;
             run.x += c[k].x; run.y += c[k].y; run.z += c[k].z; run.w += c[k].w;
             z += zz[k];
+            if (KIND == BLEND_INFER && s < n_seg && !stopped) {
+                t_final = tt[k];
+                stopped = t_final < kTransmittanceEps;
+            }
         }
     }
     if (px < width && py < height) {
@@ -819,7 +828,7 @@ __global__ void __launch_bounds__(T * T) blend_combine_kernel(const Segment* __r
         image[2 * n_px + pi] = run.z;
         image[3 * n_px + pi] = run.w;
         if (KIND == BLEND_INFER) {
-            const float Tr = seg_T[(size_t)(first + n_seg - 1u) * P + t];
+            const float Tr = t_final;
             const float A = 1.0f - Tr;
             depth_image[pi] = A > 0.0f ? z / A : 0.0f;
             alpha_image[pi] = Tr < kTransmittanceEps ? 1.0f : A;

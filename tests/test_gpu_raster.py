@@ -287,6 +287,31 @@ def test_single_hot_tile_and_deep_pixel_lists():
         assert_close(bw.detach().cpu().numpy(), st.blending_weights, what="hot-tile blending weights")
 
 
+def test_inference_on_deep_tiles_stops_where_the_reference_stops():
+    """Tiles whose lists are cut into many segments: pixels that saturate in the middle of the list
+    must report the transmittance of the fragment that stopped them (expected depth = Z / (1 - T))."""
+    import inpc_b200
+    from inpc_b200.views import look_at_view
+    view = look_at_view((0.0, 0.0, 3.0), (0.0, 0.0, 0.0), 64, 48, 60.0, 60.0)
+    g = torch.Generator().manual_seed(18)
+    n = 40000
+    pos = torch.cat([torch.randn((n, 2), generator=g) * 0.15, torch.rand((n, 1), generator=g) - 0.5], dim=1).contiguous()
+    feats = (torch.randn((n, 36), generator=g) * 0.5).to(torch.float16)
+    opac = torch.rand((n, 1), generator=g) * 0.3 + 0.05
+    v = view.to(DEV)
+    _, _, _, _, dbg0 = _fwd(v, 0, pos.to(DEV), feats.to(DEV), opac.to(DEV), 8)
+    opac_d = silence_depth_ties(dbg0["depth"], dbg0["n_touched"] > 0, opac.to(DEV))
+    for tile in (8, 16):
+        img, dep, alp = inpc_b200.INPCRasterizer(tile_size=tile).render_preextracted(
+            v, 0, pos.to(DEV), feats.to(DEV), opac_d, None, sigma_world_scale=1.0, sigma_cutoff=3.0)
+        oi, od, oa, _ = O.render_preextracted(0, oracle_camera(view), pos.numpy(), feats.numpy(), opac_d.cpu().numpy(), None,
+                                              1.0 * 0.05 / view.camera.focal_y, 3.0, tile=tile)
+        assert (oa == 1.0).sum() > 50 and ((oa > 0) & (oa < 1)).sum() > 50
+        assert_close(img.detach().cpu().numpy(), oi, what="deep-tile image")
+        assert_close(dep.detach().cpu().numpy(), od, what="deep-tile depth")
+        assert_close(alp.detach().cpu().numpy(), oa, what="deep-tile alpha")
+
+
 def test_argument_errors_raise():
     import inpc_b200
     from inpc_b200 import _cabi
