@@ -60,6 +60,8 @@ typedef struct inpc_raster_state {
     int32_t mode;
     uint32_t depth_key_base;  /* smallest depth bit pattern among the visible points (sort keys are offsets from it) */
     int32_t depth_key_bits;   /* significant bits of the largest offset */
+    int32_t channels;         /* blended channels: 4 for the spherical-harmonics layout, else the feature-row width */
+    int32_t reserved;
 } inpc_raster_state;
 
 const char* inpc_last_error(void);
@@ -130,6 +132,36 @@ int inpc_render_preextracted(int mode, int tile_size, const inpc_view* view, int
                              const float* scales, float sigma_world, float sigma_cutoff, float* image,
                              float* depth, float* alpha, inpc_alloc_fn alloc_point,
                              inpc_alloc_fn alloc_instance, void* alloc_user, void* stream);
+
+/* Feature-row layout (bilinear splats): every point carries `channels` fp32 values (4, 16 or 32;
+ * features (n, channels), 16-byte aligned) that are blended as they are, without spherical
+ * harmonics, into image (channels,H,W).  alpha (H,W), blending_weights (n), the scratch callbacks
+ * and `state` are as in inpc_rasterize_forward.
+ * No counterpart in the reference, whose backend only blends the four channels it evaluates from 36
+ * SH halves (rasterization/src/rasterization_api.cu:23-107): the ordering is that of
+ * rasterization/src/bilinear/forward.cu:59-170 and the per-fragment arithmetic that of
+ * rasterization/src/bilinear/kernels.cu:241-313 with the channel count as a parameter, so that a
+ * channels/4-fold run of the reference on DC-only coefficients gives the same image. */
+int inpc_rasterize_rows_forward(int tile_size, const inpc_view* view, int64_t n, const float* positions,
+                                const float* features, int channels, const float* opacities, float* image,
+                                float* alpha, float* blending_weights, inpc_alloc_fn alloc_point,
+                                inpc_alloc_fn alloc_instance, void* alloc_user, inpc_raster_state* state,
+                                void* stream);
+
+/* Backward of inpc_rasterize_rows_forward: grad_image (channels,H,W), grad_alpha (H,W);
+ * grad_features (n, channels) f32 and grad_opacities (n) f32 are fully written (zero rows for
+ * culled points).  Arithmetic of rasterization/src/bilinear/kernels.cu:315-420 per channel. */
+int inpc_rasterize_rows_backward(const inpc_raster_state* state, const inpc_view* view,
+                                 const float* grad_image, const float* grad_alpha, const float* image,
+                                 const float* alpha, const float* features, float* grad_features,
+                                 float* grad_opacities, void* stream);
+
+/* Inference over feature rows: image (channels,H,W), expected depth (H,W), alpha (H,W)
+ * (rasterization/src/bilinear/kernels.cu:422-495 with the channel count as a parameter). */
+int inpc_render_rows(int tile_size, const inpc_view* view, int64_t n, const float* positions,
+                     const float* features, int channels, const float* opacities, float* image, float* depth,
+                     float* alpha, inpc_alloc_fn alloc_point, inpc_alloc_fn alloc_instance, void* alloc_user,
+                     void* stream);
 
 /* Introspection for parity tests: copies one intermediate array of the forward that produced
  * `state` into `dst` (device pointer, caller-sized).  which: 0 sorted visible point ids (n_visible

@@ -15,6 +15,8 @@
 // instead of testing every staged point against every pixel.
 #include "common.cuh"
 
+#include <type_traits>
+
 #ifndef INPC_MIN_BATCHES
 #define INPC_MIN_BATCHES 16
 #endif
@@ -28,7 +30,7 @@ constexpr float kOneMinusAlphaEps = 1e-8f;      // include/bilinear/config.h:17
 constexpr float kDilation = 0.16f;              // include/gaussian/config.h:19
 constexpr float kTrainGaussThreshold = 0.01110899653f;   // src/gaussian/kernels.cu:452
 
-enum { VAR_TRAIN = 0, VAR_RAW37 = 1, VAR_PREEXTRACTED = 2 };
+enum { VAR_TRAIN = 0, VAR_RAW37 = 1, VAR_PREEXTRACTED = 2, VAR_ROWS = 3 };   // VAR_ROWS: features stay in the caller's (n, C) fp32 array
 
 struct __align__(16) PointRec {
     float sx, sy, opacity, depth;
@@ -291,13 +293,13 @@ __global__ void __launch_bounds__(kPreThreads) preprocess_kernel(
     const unsigned* __restrict__ depth_max, PointRec* __restrict__ rec, uint2* __restrict__ bounds, float4* __restrict__ conic, uint32_t* __restrict__ depth_keys,
     uint32_t* __restrict__ point_ids) {
     constexpr int kHalves = VARIANT == VAR_RAW37 ? 37 : 36;
-    constexpr int kSlabBytes = kPreThreads * kHalves * 2;   // multiple of 16 for both layouts
+    constexpr int kSlabBytes = VARIANT == VAR_ROWS ? 16 : kPreThreads * kHalves * 2;   // multiple of 16 for both layouts
     __shared__ __align__(16) unsigned char s_feat[kSlabBytes];
     __shared__ unsigned s_scan[kPreThreads / 32 + 1];
 
     const int64_t block_first = (int64_t)blockIdx.x * kPreThreads;
     const int in_block = (int)min((int64_t)kPreThreads, n - block_first);
-    {
+    if (VARIANT != VAR_ROWS) {
         // coalesced 16-byte staging of the block's contiguous feature slab
         const unsigned char* src = reinterpret_cast<const unsigned char*>(features) + block_first * (kHalves * 2);
         const int bytes = in_block * kHalves * 2;
@@ -319,7 +321,11 @@ __global__ void __launch_bounds__(kPreThreads) preprocess_kernel(
     }
     __syncthreads();
     if (i < n) {
-        if (pr.visible) {
+        if (pr.visible && VARIANT == VAR_ROWS) {
+            // feature rows are gathered by the blend itself: the record carries the geometry only
+            *reinterpret_cast<float4*>(rec + i) = make_float4(pr.sx, pr.sy, __ldg(opacities + i), pr.depth);
+            bounds[i] = make_uint2(pr.x0 | (pr.x1 << 16), pr.y0 | (pr.y1 << 16));
+        } else if (pr.visible) {
             const __half* h = reinterpret_cast<const __half*>(s_feat) + threadIdx.x * kHalves;
             float b[9];
             sh_basis(px, py, pz, rp.v.cam, b);
@@ -957,6 +963,345 @@ constexpr size_t backward_smem_bytes() {
 }
 
 // ------------------------------------------------------------------------------------------------
+// Bilinear blend over feature rows: every point carries C = 4 * C4 fp32 channels in the caller's
+// (n, C) array and they are blended as they are, into a (C, H, W) image.  The walk, the stopping
+// rule and the segment composition are those of the kernels above (src/bilinear/kernels.cu:241-420
+// with the channel count as a parameter); the reference itself only has the 36-half -> 4-channel
+// layout.  The transmittance pre-pass and the per-tile prefix do not look at features and are
+// shared.  One instance per pixel thread and batch.
+// ------------------------------------------------------------------------------------------------
+template <int T, int C4>
+constexpr size_t rows_forward_smem_bytes() {
+    return (size_t)T * T * (16 + 16 * C4 + 4 * 4) + (size_t)(T * T / 32) * T * T * 4;
+}
+
+template <int T, int C4, int KIND>
+__global__ void __launch_bounds__(T * T) blend_rows_forward_kernel(
+    const Segment* __restrict__ segs, const uint32_t* __restrict__ n_segments, const uint32_t* __restrict__ inst_ids,
+    const PointRec* __restrict__ rec, const float4* __restrict__ features, float* __restrict__ seg_T,
+    float4* __restrict__ seg_C, float* __restrict__ seg_Z, float* __restrict__ image, float* __restrict__ depth_image,
+    float* __restrict__ alpha_image, float* __restrict__ blending_weights, int width, int height, int gw) {
+    constexpr int P = T * T;
+    constexpr int WORDS = P / 32;
+    if (blockIdx.x >= *n_segments) return;
+    const Segment sg = segs[blockIdx.x];
+    const unsigned seg_idx = sg.info & 0xffffu, n_seg = sg.info >> 16;
+
+    extern __shared__ __align__(16) unsigned char blend_smem[];
+    float4* s_a = reinterpret_cast<float4*>(blend_smem);                        // [P]
+    float4* s_f = s_a + P;                                                      // [C4][P]
+    float* s_slot = reinterpret_cast<float*>(s_f + C4 * P);                     // [4][P] blending weight per footprint corner
+    unsigned (*s_mask)[P] = reinterpret_cast<unsigned (*)[P]>(s_slot + 4 * P);  // [WORDS][P]
+
+    const int t = threadIdx.x;
+    const int tx = (int)(sg.tile % (unsigned)gw), ty = (int)(sg.tile / (unsigned)gw);
+    const int px = tx * T + t % T, py = ty * T + t / T;
+    const bool inside = px < width && py < height;
+    const float pcx = (float)px + 0.5f, pcy = (float)py + 0.5f;
+    const size_t state_idx = (size_t)blockIdx.x * P + t;
+
+#pragma unroll
+    for (int w = 0; w < WORDS; ++w) s_mask[w][t] = 0u;
+#pragma unroll
+    for (int q = 0; q < 4; ++q) s_slot[q * P + t] = 0.0f;
+    float4 acc[C4];
+#pragma unroll
+    for (int c = 0; c < C4; ++c) acc[c] = make_float4(0.f, 0.f, 0.f, 0.f);
+    float Z = 0.0f, Tr = 1.0f;
+    if (seg_idx > 0u && inside) Tr = seg_T[state_idx];
+    bool done = !inside || Tr < kTransmittanceEps;
+    __syncthreads();
+
+    uint32_t id = 0;
+    int cnt = 0;
+    auto flush_weights = [&]() {
+        if (t < cnt) {
+            const float sum = ((s_slot[t] + s_slot[P + t]) + s_slot[2 * P + t]) + s_slot[3 * P + t];
+            if (sum > 0.0f) atomicAdd(blending_weights + id, sum);
+            s_slot[t] = 0.0f; s_slot[P + t] = 0.0f; s_slot[2 * P + t] = 0.0f; s_slot[3 * P + t] = 0.0f;
+        }
+    };
+    for (unsigned base = sg.begin; base < sg.end; base += P) {
+        if (KIND == BLEND_TRAIN) flush_weights();
+        cnt = (int)min((unsigned)P, sg.end - base);
+        id = stage_instance<T, P, false>(t, cnt, base, inst_ids, rec, tx, ty, s_a, nullptr, s_mask);
+        if (t < cnt) {
+            const float4* row = features + (size_t)id * C4;
+#pragma unroll
+            for (int c = 0; c < C4; ++c) s_f[c * P + t] = __ldg(row + c);
+        }
+        __syncthreads();
+#pragma unroll 1
+        for (int w = 0; w < WORDS; ++w) {
+            unsigned mbits = s_mask[w][t];
+            if (mbits) s_mask[w][t] = 0u;
+            while (mbits && !done) {
+                const int j = w * 32 + __ffs(mbits) - 1;
+                mbits &= mbits - 1u;
+                const float4 a = s_a[j];
+                const float dx = fabsf(a.x - pcx), dy = fabsf(a.y - pcy);
+                if (dx >= 1.0f || dy >= 1.0f) continue;
+                const float wgt = __saturatef(1.0f - dx) * __saturatef(1.0f - dy);
+                const float al = a.z * wgt;
+                const float bw = Tr * al;
+                if (KIND == BLEND_TRAIN) {
+                    if (bw > 0.0f) s_slot[((pcx > a.x ? 1 : 0) + (pcy > a.y ? 2 : 0)) * P + j] = bw * wgt;
+                }
+#pragma unroll
+                for (int c = 0; c < C4; ++c) {
+                    const float4 f = s_f[c * P + j];
+                    acc[c].x += bw * f.x; acc[c].y += bw * f.y; acc[c].z += bw * f.z; acc[c].w += bw * f.w;
+                }
+                if (KIND == BLEND_INFER) Z += bw * a.w;
+                Tr *= 1.0f - al;
+                if (Tr < kTransmittanceEps) done = true;
+            }
+        }
+        if (__syncthreads_count(done) == P) break;
+    }
+    if (KIND == BLEND_TRAIN) flush_weights();
+
+    if (n_seg == 1u) {
+        if (inside) {
+            const int64_t n_px = (int64_t)width * height;
+            const int64_t pi = (int64_t)py * width + px;
+#pragma unroll
+            for (int c = 0; c < C4; ++c) {
+                image[(4 * c) * n_px + pi] = acc[c].x;
+                image[(4 * c + 1) * n_px + pi] = acc[c].y;
+                image[(4 * c + 2) * n_px + pi] = acc[c].z;
+                image[(4 * c + 3) * n_px + pi] = acc[c].w;
+            }
+            if (KIND == BLEND_INFER) {
+                const float A = 1.0f - Tr;
+                depth_image[pi] = A > 0.0f ? Z / A : 0.0f;
+                alpha_image[pi] = Tr < kTransmittanceEps ? 1.0f : A;
+            } else {
+                alpha_image[pi] = Tr < kTransmittanceEps ? 1.0f : 1.0f - Tr;
+            }
+        }
+    } else {
+#pragma unroll
+        for (int c = 0; c < C4; ++c) seg_C[((size_t)blockIdx.x * C4 + c) * P + t] = acc[c];
+        if (KIND == BLEND_INFER) {
+            seg_Z[state_idx] = Z;
+            seg_T[state_idx] = Tr;
+        } else if (seg_idx == n_seg - 1u && inside) {
+            alpha_image[(int64_t)py * width + px] = Tr < kTransmittanceEps ? 1.0f : 1.0f - Tr;
+        }
+    }
+}
+
+// Per tile with several segments, feature-row layout: image = sum of the segment colours in order;
+// for training the running sum before each segment replaces the segment's own colour.
+template <int T, int C4, int KIND>
+__global__ void __launch_bounds__(T * T) blend_rows_combine_kernel(const Segment* __restrict__ segs, const uint32_t* __restrict__ tile_first,
+                                                                   float4* __restrict__ seg_C, const float* __restrict__ seg_Z,
+                                                                   const float* __restrict__ seg_T, float* __restrict__ image,
+                                                                   float* __restrict__ depth_image, float* __restrict__ alpha_image,
+                                                                   int width, int height, int gw) {
+    constexpr int P = T * T;
+    const unsigned first = tile_first[blockIdx.x];
+    const unsigned n_seg = segs[first].info >> 16;
+    if (n_seg == 1u) return;
+    const int t = threadIdx.x;
+    const int tx = (int)(blockIdx.x % (unsigned)gw), ty = (int)(blockIdx.x / (unsigned)gw);
+    const int px = tx * T + t % T, py = ty * T + t / T;
+    const bool inside = px < width && py < height;
+    const int64_t n_px = (int64_t)width * height;
+    const int64_t pi = (int64_t)py * width + px;
+#pragma unroll 1
+    for (int c = 0; c < C4; ++c) {
+        float4 run = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (unsigned s = 0; s < n_seg; ++s) {
+            float4* slot = seg_C + ((size_t)(first + s) * C4 + c) * P + t;
+            const float4 v = *slot;
+            if (KIND == BLEND_TRAIN) *slot = run;
+            run.x += v.x; run.y += v.y; run.z += v.z; run.w += v.w;
+        }
+        if (inside) {
+            image[(4 * c) * n_px + pi] = run.x;
+            image[(4 * c + 1) * n_px + pi] = run.y;
+            image[(4 * c + 2) * n_px + pi] = run.z;
+            image[(4 * c + 3) * n_px + pi] = run.w;
+        }
+    }
+    if (KIND == BLEND_INFER) {
+        float z = 0.0f, t_final = 1.0f;
+        bool stopped = false;
+        for (unsigned s = 0; s < n_seg; ++s) {
+            z += seg_Z[(size_t)(first + s) * P + t];
+            if (!stopped) {
+                t_final = seg_T[(size_t)(first + s) * P + t];
+                stopped = t_final < kTransmittanceEps;
+            }
+        }
+        if (inside) {
+            const float A = 1.0f - t_final;
+            depth_image[pi] = A > 0.0f ? z / A : 0.0f;
+            alpha_image[pi] = t_final < kTransmittanceEps ? 1.0f : A;
+        }
+    }
+}
+
+template <int T, int C4>
+constexpr size_t rows_backward_smem_bytes() {
+    return (size_t)T * T * (16 + 16 * C4 + 16 * C4 + 4 * 4 + 4 * 4) + (size_t)(T * T / 32) * T * T * 4;
+}
+
+// Backward over feature rows.  Per fragment only scalars are kept: with G = <g, .> over the channels,
+// dL/dalpha = Tr * G(f) + (G(C_run) - G(C_final)) / (1 - alpha) + K / (1 - alpha), and G(C_run) is a
+// running scalar.  The blending weight of each (instance, footprint corner) goes to a shared-memory
+// slot; the thread that staged the instance then forms sum_corner bw * g(pixel of that corner) from
+// the tile's pixel gradients in shared memory and issues one vector atomic per four channels.
+template <int T, int C4>
+__global__ void __launch_bounds__(T * T) blend_rows_backward_kernel(
+    const Segment* __restrict__ segs, const uint32_t* __restrict__ n_segments, const uint32_t* __restrict__ inst_ids,
+    const PointRec* __restrict__ rec, const float4* __restrict__ features, const float* __restrict__ seg_T,
+    const float4* __restrict__ seg_C, const float* __restrict__ grad_image, const float* __restrict__ grad_alpha,
+    const float* __restrict__ image, const float* __restrict__ alpha_image, float4* __restrict__ grad_features,
+    float* __restrict__ grad_opacity, int width, int height, int gw) {
+    constexpr int P = T * T;
+    constexpr int WORDS = P / 32;
+    if (blockIdx.x >= *n_segments) return;
+    const Segment sg = segs[blockIdx.x];
+    const unsigned seg_idx = sg.info & 0xffffu;
+    if (sg.begin == sg.end) return;
+
+    extern __shared__ __align__(16) unsigned char blend_smem[];
+    float4* s_a = reinterpret_cast<float4*>(blend_smem);                      // [P]
+    float4* s_f = s_a + P;                                                    // [C4][P] staged feature rows
+    float4* s_g = s_f + C4 * P;                                               // [C4][P] image gradient of the tile's pixels
+    float* s_bw = reinterpret_cast<float*>(s_g + C4 * P);                     // [4][P]
+    float* s_go = s_bw + 4 * P;                                               // [4][P]
+    unsigned (*s_mask)[P] = reinterpret_cast<unsigned (*)[P]>(s_go + 4 * P);  // [WORDS][P]
+
+    const int t = threadIdx.x;
+    const int tx = (int)(sg.tile % (unsigned)gw), ty = (int)(sg.tile / (unsigned)gw);
+    const int px = tx * T + t % T, py = ty * T + t / T;
+    const bool inside = px < width && py < height;
+    const float pcx = (float)px + 0.5f, pcy = (float)py + 0.5f;
+    const size_t state_idx = (size_t)blockIdx.x * P + t;
+
+#pragma unroll
+    for (int w = 0; w < WORDS; ++w) s_mask[w][t] = 0u;
+#pragma unroll
+    for (int q = 0; q < 4; ++q) { s_bw[q * P + t] = 0.0f; s_go[q * P + t] = 0.0f; }
+
+    float4 g[C4];
+    float G_final = 0.0f, G_run = 0.0f, K = 0.0f, Tr = 1.0f;
+#pragma unroll
+    for (int c = 0; c < C4; ++c) g[c] = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (inside) {
+        const int64_t n_px = (int64_t)width * height;
+        const int64_t pi = (int64_t)py * width + px;
+#pragma unroll
+        for (int c = 0; c < C4; ++c) {
+            g[c] = make_float4(__ldg(grad_image + (4 * c) * n_px + pi), __ldg(grad_image + (4 * c + 1) * n_px + pi),
+                               __ldg(grad_image + (4 * c + 2) * n_px + pi), __ldg(grad_image + (4 * c + 3) * n_px + pi));
+            G_final += __ldg(image + (4 * c) * n_px + pi) * g[c].x + __ldg(image + (4 * c + 1) * n_px + pi) * g[c].y +
+                       __ldg(image + (4 * c + 2) * n_px + pi) * g[c].z + __ldg(image + (4 * c + 3) * n_px + pi) * g[c].w;
+        }
+        K = __ldg(grad_alpha + pi) * (1.0f - __ldg(alpha_image + pi));
+        if (seg_idx > 0u) {
+            Tr = seg_T[state_idx];
+#pragma unroll
+            for (int c = 0; c < C4; ++c) {
+                const float4 v = seg_C[((size_t)blockIdx.x * C4 + c) * P + t];
+                G_run += v.x * g[c].x + v.y * g[c].y + v.z * g[c].z + v.w * g[c].w;
+            }
+        }
+    }
+#pragma unroll
+    for (int c = 0; c < C4; ++c) s_g[c * P + t] = g[c];
+    bool done = !inside || Tr < kTransmittanceEps;
+    __syncthreads();
+
+    uint32_t id = 0;
+    int cnt = 0;
+    auto flush_gradients = [&]() {
+        if (t < cnt) {
+            const float4 a = s_a[t];
+            const int qx = __float2int_rd(a.x - 0.5f) - tx * T;
+            const int qy = __float2int_rd(a.y - 0.5f) - ty * T;
+            float bw[4];
+            float so = 0.0f;
+            bool any = false;
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                bw[q] = s_bw[q * P + t];
+                so += s_go[q * P + t];
+                any = any || bw[q] != 0.0f;
+                s_bw[q * P + t] = 0.0f;
+                s_go[q * P + t] = 0.0f;
+            }
+            if (any) {
+                // a corner slot is only ever written by the pixel thread of that corner, so a filled
+                // slot names a pixel of this tile
+                float4* dst = grad_features + (size_t)id * C4;
+#pragma unroll
+                for (int c = 0; c < C4; ++c) {
+                    float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        if (bw[q] != 0.0f) {
+                            const float4 v = s_g[c * P + (qy + (q >> 1)) * T + qx + (q & 1)];
+                            sum.x += bw[q] * v.x; sum.y += bw[q] * v.y; sum.z += bw[q] * v.z; sum.w += bw[q] * v.w;
+                        }
+                    }
+                    if (sum.x != 0.0f || sum.y != 0.0f || sum.z != 0.0f || sum.w != 0.0f) atomicAdd(dst + c, sum);
+                }
+            }
+            if (so != 0.0f) atomicAdd(grad_opacity + id, so);
+        }
+    };
+    for (unsigned base = sg.begin; base < sg.end; base += P) {
+        flush_gradients();
+        cnt = (int)min((unsigned)P, sg.end - base);
+        id = stage_instance<T, P, false>(t, cnt, base, inst_ids, rec, tx, ty, s_a, nullptr, s_mask);
+        if (t < cnt) {
+            const float4* row = features + (size_t)id * C4;
+#pragma unroll
+            for (int c = 0; c < C4; ++c) s_f[c * P + t] = __ldg(row + c);
+        }
+        __syncthreads();
+#pragma unroll 1
+        for (int w = 0; w < WORDS; ++w) {
+            unsigned mbits = s_mask[w][t];
+            if (mbits) s_mask[w][t] = 0u;
+            while (mbits && !done) {
+                const int j = w * 32 + __ffs(mbits) - 1;
+                mbits &= mbits - 1u;
+                const float4 a = s_a[j];
+                const float dx = fabsf(a.x - pcx), dy = fabsf(a.y - pcy);
+                if (dx >= 1.0f || dy >= 1.0f) continue;
+                const float wgt = __saturatef(1.0f - dx) * __saturatef(1.0f - dy);
+                const float al = a.z * wgt;
+                const float bw = Tr * al;
+                const int q = (pcx > a.x ? 1 : 0) + (pcy > a.y ? 2 : 0);
+                if (bw > 0.0f) s_bw[q * P + j] = bw;
+                float fg = 0.0f;
+#pragma unroll
+                for (int c = 0; c < C4; ++c) {
+                    const float4 f = s_f[c * P + j];
+                    fg += f.x * g[c].x + f.y * g[c].y + f.z * g[c].z + f.w * g[c].w;
+                }
+                G_run += bw * fg;
+                const float oma = 1.0f - al;
+                const float rcp = 1.0f / fmaxf(oma, kOneMinusAlphaEps);
+                const float dalpha = Tr * fg + (G_run - G_final) * rcp + K * rcp;
+                const float dop = dalpha * wgt;
+                if (dop != 0.0f) s_go[q * P + j] = dop;
+                Tr *= oma;
+                if (Tr < kTransmittanceEps) done = true;
+            }
+        }
+        if (__syncthreads_count(done) == P) break;
+    }
+    flush_gradients();
+}
+
+// ------------------------------------------------------------------------------------------------
 // Gaussian blend: footprints are not bounded by 2x2 pixels, so every pixel tests every staged point
 // (src/gaussian/kernels.cu:401-474 forward, :476-579 backward, :581-660 inference).
 // ------------------------------------------------------------------------------------------------
@@ -1209,7 +1554,7 @@ int64_t max_segments(int64_t n_instances, int n_tiles, int tile) {
     return (int64_t)n_tiles + ceil_div<int64_t>(n_instances, (int64_t)blend_batch(tile) * kMinBatchesPerSegment);
 }
 
-InstanceBlob carve_instance_blob(void* p, int64_t n_instances, int n_tiles, int tile, int mode, bool with_depth) {
+InstanceBlob carve_instance_blob(void* p, int64_t n_instances, int n_tiles, int tile, int mode, bool with_depth, int c4 = 1) {
     InstanceBlob b;
     Carver c(p);
     b.ranges = c.take<uint2>(n_tiles);
@@ -1221,7 +1566,7 @@ InstanceBlob carve_instance_blob(void* p, int64_t n_instances, int n_tiles, int 
     b.tile_first = c.take<uint32_t>(n_tiles);
     b.n_segments = c.take<uint32_t>(4);
     b.seg_T = c.take<float>(px);
-    b.seg_C = c.take<float4>(px);
+    b.seg_C = c.take<float4>(px * (size_t)c4);
     b.seg_Z = c.take<float>(with_depth ? px : 0);
     c.off = align_up(c.off);
     b.sort_ws = c.base + c.off;
@@ -1265,7 +1610,7 @@ int check_view(const inpc_view* v, int tile_size, int mode, int64_t n) {
 template <int MODE, int VARIANT>
 int run_front(const RasterParams& rp, int64_t n, const float* positions, const void* features, const float* opacities,
               inpc_alloc_fn alloc_point, inpc_alloc_fn alloc_instance, void* user, inpc_raster_state* st,
-              bool with_depth, PointBlob* pb_out, InstanceBlob* ib_out, cudaStream_t stream) {
+              bool with_depth, PointBlob* pb_out, InstanceBlob* ib_out, cudaStream_t stream, int c4 = 1) {
     const int n_tiles = rp.gw * rp.gh;
     const int64_t nb = ceil_div<int64_t>(n > 0 ? n : 1, kPreThreads);
     const PointBlob sizing = carve_point_blob(nullptr, n, MODE);
@@ -1316,10 +1661,10 @@ int run_front(const RasterParams& rp, int64_t n, const float* positions, const v
         return INPC_E_CAPACITY;
     }
 
-    const InstanceBlob isz = carve_instance_blob(nullptr, n_instances, n_tiles, rp.tile, MODE, with_depth);
+    const InstanceBlob isz = carve_instance_blob(nullptr, n_instances, n_tiles, rp.tile, MODE, with_depth, c4);
     void* iblob = alloc_instance(user, isz.total);
     if (!iblob) { set_error("instance allocator returned NULL for %zu bytes", isz.total); return INPC_E_ALLOC; }
-    InstanceBlob ib = carve_instance_blob(iblob, n_instances, n_tiles, rp.tile, MODE, with_depth);
+    InstanceBlob ib = carve_instance_blob(iblob, n_instances, n_tiles, rp.tile, MODE, with_depth, c4);
     INPC_CUDA_TRY(cudaMemsetAsync(ib.ranges, 0, sizeof(uint2) * (size_t)n_tiles, stream));
 
     int in_alt = 0;
@@ -1368,6 +1713,8 @@ int run_front(const RasterParams& rp, int64_t n, const float* positions, const v
     st->mode = MODE;
     st->depth_key_base = key_base;
     st->depth_key_bits = key_bits;
+    st->channels = VARIANT == VAR_ROWS ? 4 * c4 : 4;
+    st->reserved = 0;
     *pb_out = pb;
     *ib_out = ib;
     return INPC_OK;
@@ -1450,6 +1797,81 @@ int launch_blend_forward(int mode, const RasterParams& rp, const PointBlob& pb, 
         blend_gaussian_forward_kernel<16, KIND><<<n_tiles, 256, 0, stream>>>(ib.ranges, ids, pb.rec, pb.conic, image, depth, alpha, blending_weights, W, H, rp.gw, threshold);
     INPC_LAUNCH_CHECK("blend_forward_kernel");
     return INPC_OK;
+}
+
+template <int T, int C4, int KIND>
+int launch_rows_forward(const RasterParams& rp, const PointBlob& pb, const InstanceBlob& ib, const uint32_t* ids, const float* features,
+                        float* image, float* depth, float* alpha, float* blending_weights, cudaStream_t stream) {
+    constexpr size_t smem = rows_forward_smem_bytes<T, C4>();
+    static bool attr_set = false;
+    if (!attr_set) {
+        INPC_CUDA_TRY(cudaFuncSetAttribute(blend_rows_forward_kernel<T, C4, KIND>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        attr_set = true;
+    }
+    const int n_tiles = rp.gw * rp.gh;
+    const int W = rp.v.width, H = rp.v.height;
+    const unsigned grid = (unsigned)ib.max_segments;
+    blend_bilinear_transmittance_kernel<T, 1><<<grid, T * T, 0, stream>>>(ib.segs, ib.n_segments, ids, pb.rec, ib.seg_T, W, H, rp.gw);
+    INPC_LAUNCH_CHECK("blend_bilinear_transmittance_kernel");
+    blend_prefix_kernel<T><<<n_tiles, T * T, 0, stream>>>(ib.segs, ib.tile_first, ib.seg_T);
+    INPC_LAUNCH_CHECK("blend_prefix_kernel");
+    blend_rows_forward_kernel<T, C4, KIND><<<grid, T * T, smem, stream>>>(ib.segs, ib.n_segments, ids, pb.rec, reinterpret_cast<const float4*>(features),
+                                                                         ib.seg_T, ib.seg_C, ib.seg_Z, image, depth, alpha, blending_weights, W, H, rp.gw);
+    INPC_LAUNCH_CHECK("blend_rows_forward_kernel");
+    blend_rows_combine_kernel<T, C4, KIND><<<n_tiles, T * T, 0, stream>>>(ib.segs, ib.tile_first, ib.seg_C, ib.seg_Z, ib.seg_T, image, depth, alpha,
+                                                                         W, H, rp.gw);
+    INPC_LAUNCH_CHECK("blend_rows_combine_kernel");
+    return INPC_OK;
+}
+
+template <int T, int C4>
+int launch_rows_backward(const RasterParams& rp, const PointBlob& pb, const InstanceBlob& ib, const uint32_t* ids, const float* features,
+                         const float* grad_image, const float* grad_alpha, const float* image, const float* alpha,
+                         float* grad_features, float* grad_opacities, cudaStream_t stream) {
+    constexpr size_t smem = rows_backward_smem_bytes<T, C4>();
+    static bool attr_set = false;
+    if (!attr_set) {
+        INPC_CUDA_TRY(cudaFuncSetAttribute(blend_rows_backward_kernel<T, C4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        attr_set = true;
+    }
+    blend_rows_backward_kernel<T, C4><<<(unsigned)ib.max_segments, T * T, smem, stream>>>(
+        ib.segs, ib.n_segments, ids, pb.rec, reinterpret_cast<const float4*>(features), ib.seg_T, ib.seg_C, grad_image, grad_alpha, image, alpha,
+        reinterpret_cast<float4*>(grad_features), grad_opacities, rp.v.width, rp.v.height, rp.gw);
+    INPC_LAUNCH_CHECK("blend_rows_backward_kernel");
+    return INPC_OK;
+}
+
+// Tile edge and channel count are template parameters of the kernels: one switch for all of them.
+template <typename F>
+int dispatch_rows(int tile, int channels, F&& f) {
+    if (tile == 8) {
+        if (channels == 4) return f(std::integral_constant<int, 8>(), std::integral_constant<int, 1>());
+        if (channels == 16) return f(std::integral_constant<int, 8>(), std::integral_constant<int, 4>());
+        if (channels == 32) return f(std::integral_constant<int, 8>(), std::integral_constant<int, 8>());
+    } else if (tile == 16) {
+        if (channels == 4) return f(std::integral_constant<int, 16>(), std::integral_constant<int, 1>());
+        if (channels == 16) return f(std::integral_constant<int, 16>(), std::integral_constant<int, 4>());
+        if (channels == 32) return f(std::integral_constant<int, 16>(), std::integral_constant<int, 8>());
+    }
+    set_error("feature rows: channels must be 4, 16 or 32 (got %d) and tile_size 8 or 16 (got %d)", channels, tile);
+    return INPC_E_INVALID;
+}
+
+template <int KIND>
+int rows_forward(int tile_size, const inpc_view* view, int64_t n, const float* positions, const float* features, int channels,
+                 const float* opacities, float* image, float* depth, float* alpha, float* blending_weights,
+                 inpc_alloc_fn alloc_point, inpc_alloc_fn alloc_instance, void* alloc_user, inpc_raster_state* state, cudaStream_t stream) {
+    const RasterParams rp = make_params(view, tile_size, 0.0f, 3.0f, nullptr);
+    PointBlob pb;
+    InstanceBlob ib;
+    int rc = run_front<INPC_MODE_BILINEAR, VAR_ROWS>(rp, n, positions, nullptr, opacities, alloc_point, alloc_instance, alloc_user, state,
+                                                     KIND == BLEND_INFER, &pb, &ib, stream, channels / 4);
+    if (rc != INPC_OK) return rc;
+    const uint32_t* ids = ib.ids[tile_result_buffer(state->n_instances, rp.gw * rp.gh)];
+    StageScope scope(STAGE_BLEND_FWD, stream);
+    return dispatch_rows(tile_size, channels, [&](auto t, auto c4) {
+        return launch_rows_forward<decltype(t)::value, decltype(c4)::value, KIND>(rp, pb, ib, ids, features, image, depth, alpha, blending_weights, stream);
+    });
 }
 
 }  // namespace
@@ -1574,6 +1996,81 @@ extern "C" int inpc_render_preextracted(int mode, int tile_size, const inpc_view
     if (rc != INPC_OK) return rc;
     const float threshold = expf(-0.5f * sigma_cutoff * sigma_cutoff);
     return launch_blend_forward<BLEND_INFER>(mode, rp, pb, ib, st.n_instances, image, depth, alpha, nullptr, threshold, stream);
+}
+
+namespace {
+int check_rows(const inpc_view* view, int tile_size, int64_t n, int channels) {
+    const int rc = check_view(view, tile_size, INPC_MODE_BILINEAR, n);
+    if (rc != INPC_OK) return rc;
+    if (channels != 4 && channels != 16 && channels != 32) { set_error("feature rows: channels must be 4, 16 or 32, got %d", channels); return INPC_E_INVALID; }
+    return INPC_OK;
+}
+}  // namespace
+
+extern "C" int inpc_rasterize_rows_forward(int tile_size, const inpc_view* view, int64_t n, const float* positions,
+                                           const float* features, int channels, const float* opacities, float* image,
+                                           float* alpha, float* blending_weights, inpc_alloc_fn alloc_point,
+                                           inpc_alloc_fn alloc_instance, void* alloc_user, inpc_raster_state* state, void* stream_) {
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    int rc = check_rows(view, tile_size, n, channels);
+    if (rc != INPC_OK) return rc;
+    if (!state || !alloc_point || !alloc_instance || !image || !alpha || (n > 0 && (!positions || !features || !opacities || !blending_weights))) {
+        set_error("inpc_rasterize_rows_forward: null argument");
+        return INPC_E_INVALID;
+    }
+    if (reinterpret_cast<uintptr_t>(features) & 15u) { set_error("inpc_rasterize_rows_forward: features must be 16-byte aligned"); return INPC_E_INVALID; }
+    if (n > 0) INPC_CUDA_TRY(cudaMemsetAsync(blending_weights, 0, sizeof(float) * (size_t)n, stream));
+    return rows_forward<BLEND_TRAIN>(tile_size, view, n, positions, features, channels, opacities, image, nullptr, alpha, blending_weights,
+                                     alloc_point, alloc_instance, alloc_user, state, stream);
+}
+
+extern "C" int inpc_render_rows(int tile_size, const inpc_view* view, int64_t n, const float* positions, const float* features,
+                                int channels, const float* opacities, float* image, float* depth, float* alpha,
+                                inpc_alloc_fn alloc_point, inpc_alloc_fn alloc_instance, void* alloc_user, void* stream_) {
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    int rc = check_rows(view, tile_size, n, channels);
+    if (rc != INPC_OK) return rc;
+    if (!alloc_point || !alloc_instance || !image || !depth || !alpha || (n > 0 && (!positions || !features || !opacities))) {
+        set_error("inpc_render_rows: null argument");
+        return INPC_E_INVALID;
+    }
+    if (reinterpret_cast<uintptr_t>(features) & 15u) { set_error("inpc_render_rows: features must be 16-byte aligned"); return INPC_E_INVALID; }
+    inpc_raster_state st;
+    return rows_forward<BLEND_INFER>(tile_size, view, n, positions, features, channels, opacities, image, depth, alpha, nullptr,
+                                     alloc_point, alloc_instance, alloc_user, &st, stream);
+}
+
+extern "C" int inpc_rasterize_rows_backward(const inpc_raster_state* state, const inpc_view* view, const float* grad_image,
+                                            const float* grad_alpha, const float* image, const float* alpha, const float* features,
+                                            float* grad_features, float* grad_opacities, void* stream_) {
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    if (!state) { set_error("inpc_rasterize_rows_backward: null state"); return INPC_E_INVALID; }
+    int rc = check_rows(view, state->tile_size, state->n_points, state->channels);
+    if (rc != INPC_OK) return rc;
+    if (state->mode != INPC_MODE_BILINEAR) { set_error("inpc_rasterize_rows_backward: state is not from inpc_rasterize_rows_forward"); return INPC_E_INVALID; }
+    const int64_t n = state->n_points;
+    const int channels = state->channels;
+    if (!grad_image || !grad_alpha || !image || !alpha || (n > 0 && (!features || !grad_features || !grad_opacities || !state->point_blob || !state->instance_blob))) {
+        set_error("inpc_rasterize_rows_backward: null argument");
+        return INPC_E_INVALID;
+    }
+    if ((reinterpret_cast<uintptr_t>(features) | reinterpret_cast<uintptr_t>(grad_features)) & 15u) {
+        set_error("inpc_rasterize_rows_backward: features and grad_features must be 16-byte aligned");
+        return INPC_E_INVALID;
+    }
+    if (n == 0) return INPC_OK;
+    const RasterParams rp = make_params(view, state->tile_size, 0.0f, 3.0f, nullptr);
+    const int n_tiles = rp.gw * rp.gh;
+    const PointBlob pb = carve_point_blob(state->point_blob, n, state->mode);
+    const InstanceBlob ib = carve_instance_blob(state->instance_blob, state->n_instances, n_tiles, state->tile_size, state->mode, false, channels / 4);
+    const uint32_t* ids = ib.ids[tile_result_buffer(state->n_instances, n_tiles)];
+    INPC_CUDA_TRY(cudaMemsetAsync(grad_features, 0, sizeof(float) * (size_t)n * channels, stream));
+    INPC_CUDA_TRY(cudaMemsetAsync(grad_opacities, 0, sizeof(float) * (size_t)n, stream));
+    StageScope scope(STAGE_BLEND_BWD, stream);
+    return dispatch_rows(state->tile_size, channels, [&](auto t, auto c4) {
+        return launch_rows_backward<decltype(t)::value, decltype(c4)::value>(rp, pb, ib, ids, features, grad_image, grad_alpha, image, alpha,
+                                                                            grad_features, grad_opacities, stream);
+    });
 }
 
 namespace inpc_debug {

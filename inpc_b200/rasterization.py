@@ -191,6 +191,66 @@ class _Rasterize(torch.autograd.Function):
         return None, grad_features, grad_opacities, None, None
 
 
+def _check_rows(positions, features, opacities):
+    positions = _cuda_f32(positions, "positions")
+    features = _cuda_f32(features, "features")
+    opacities = _cuda_f32(opacities, "opacities")
+    n = positions.shape[0]
+    if positions.dim() != 2 or positions.shape[1] != 3:
+        raise ValueError(f"positions must be (N,3), got {tuple(positions.shape)}")
+    if features.dim() != 2 or features.shape[0] != n or features.shape[1] not in (4, 16, 32):
+        raise ValueError(f"features must be (N,C) with C in (4, 16, 32), got {tuple(features.shape)}")
+    if opacities.numel() != n:
+        raise ValueError(f"opacities must hold N={n} values, got {tuple(opacities.shape)}")
+    return positions, features, opacities
+
+
+class _RasterizeRows(torch.autograd.Function):
+    """Bilinear training rasterisation of (N,C) fp32 feature rows into a (C,H,W) image."""
+
+    @staticmethod
+    def forward(ctx: Any, positions: torch.Tensor, features: torch.Tensor, opacities: torch.Tensor,
+                rasterizer_settings: RasterizerSettings, tile_size: int = DEFAULT_TILE_SIZE):
+        positions, features, opacities = _check_rows(positions, features, opacities)
+        n, channels = features.shape
+        dev = positions.device
+        s = rasterizer_settings
+        with torch.cuda.device(dev):
+            view = _ViewArg(s, dev)
+            image = torch.empty((channels, s.height, s.width), dtype=torch.float32, device=dev)
+            alpha = torch.empty((1, s.height, s.width), dtype=torch.float32, device=dev)
+            blending_weights = torch.empty((n,), dtype=torch.float32, device=dev)
+            blobs = _Blobs(dev)
+            state = _cabi.RasterState()
+            _check(_cabi.lib().inpc_rasterize_rows_forward(
+                int(tile_size), C.byref(view.c), n, _ptr(positions), _ptr(features), int(channels), _ptr(opacities),
+                _ptr(image), _ptr(alpha), _ptr(blending_weights), blobs.cb_point, blobs.cb_instance, None,
+                C.byref(state), _stream()), blobs)
+        ctx.save_for_backward(image, alpha, features, blobs.point, blobs.instance)
+        ctx.rasterizer_settings = rasterizer_settings
+        ctx.raster_state = state
+        ctx.mark_non_differentiable(blending_weights)
+        ctx.set_materialize_grads(False)
+        return image, alpha, blending_weights
+
+    @staticmethod
+    @once_differentiable
+    def backward(ctx: Any, grad_image: torch.Tensor, grad_alpha: torch.Tensor, _):
+        image, alpha, features, point_blob, instance_blob = ctx.saved_tensors
+        s = ctx.rasterizer_settings
+        dev = features.device
+        grad_image = torch.zeros_like(image) if grad_image is None else _cuda_f32(grad_image, "grad_image")
+        grad_alpha = torch.zeros_like(alpha) if grad_alpha is None else _cuda_f32(grad_alpha, "grad_alpha")
+        with torch.cuda.device(dev):
+            view = _ViewArg(s, dev)
+            grad_features = torch.empty_like(features)
+            grad_opacities = torch.empty((features.shape[0], 1), dtype=torch.float32, device=dev)
+            _check(_cabi.lib().inpc_rasterize_rows_backward(
+                C.byref(ctx.raster_state), C.byref(view.c), _ptr(grad_image), _ptr(grad_alpha), _ptr(image),
+                _ptr(alpha), _ptr(features), _ptr(grad_features), _ptr(grad_opacities), _stream()))
+        return None, grad_features, grad_opacities, None, None
+
+
 class INPCRasterizer(torch.nn.Module):
     """Drop-in for the reference's INPCRasterizer (torch_bindings/rasterization.py:104-189)."""
 
@@ -288,6 +348,34 @@ class INPCRasterizer(torch.nn.Module):
                 _ptr(scales), float(sigma_world_scale * self.extract_base_sigma_world(view.camera)),
                 float(sigma_cutoff), _ptr(image), _ptr(depth), _ptr(alpha), blobs.cb_point, blobs.cb_instance, None,
                 _stream()), blobs)
+            for b in (blobs.point, blobs.instance):
+                if b is not None:
+                    b.record_stream(torch.cuda.current_stream())
+        return image, depth, alpha
+
+
+    def forward_rows(self, view, positions: torch.Tensor, features: torch.Tensor, opacities: torch.Tensor):
+        """Bilinear training forward over (N,C) fp32 feature rows, C in (4, 16, 32): the features are
+        blended as they are into a (C,H,W) image (differentiable w.r.t. features and opacities).  The
+        reference has no such layout; its only one is 36 SH halves -> 4 channels (`forward`)."""
+        return _RasterizeRows.apply(positions, features, opacities, self.extract_settings(view, 0), self.tile_size)
+
+    @torch.no_grad()
+    def render_rows(self, view, positions: torch.Tensor, features: torch.Tensor, opacities: torch.Tensor):
+        """Bilinear inference over (N,C) fp32 feature rows: image (C,H,W), expected depth, alpha."""
+        s = self.extract_settings(view, 0)
+        positions, features, opacities = _check_rows(positions, features, opacities)
+        n, channels = features.shape
+        dev = positions.device
+        with torch.cuda.device(dev):
+            varg = _ViewArg(s, dev)
+            image = torch.empty((channels, s.height, s.width), dtype=torch.float32, device=dev)
+            depth = torch.empty((1, s.height, s.width), dtype=torch.float32, device=dev)
+            alpha = torch.empty((1, s.height, s.width), dtype=torch.float32, device=dev)
+            blobs = _Blobs(dev)
+            _check(_cabi.lib().inpc_render_rows(
+                self.tile_size, C.byref(varg.c), n, _ptr(positions), _ptr(features), int(channels), _ptr(opacities),
+                _ptr(image), _ptr(depth), _ptr(alpha), blobs.cb_point, blobs.cb_instance, None, _stream()), blobs)
             for b in (blobs.point, blobs.instance):
                 if b is not None:
                     b.record_stream(torch.cuda.current_stream())

@@ -220,6 +220,84 @@ def render_preextracted(mode, cam: Camera, positions, features, opacities, scale
     return _inference(st, sigma_cutoff) + (st,)
 
 
+# ----------------------------------------------------------------------------- feature rows
+# (n, C) fp32 features blended as they are.  The blend treats channels independently, so C channels
+# are C/4 runs of the four-channel restatement over the same ordering: exactly the "C/4 reference
+# passes" by which the reference itself can be run on such input.
+
+def _rows_state(cam: Camera, positions, opacities, tile) -> ForwardState:
+    n = np.asarray(positions).reshape(-1, 3).shape[0]
+    return preprocess_and_order(BILINEAR, TRAIN, cam, positions, np.zeros((n, 36), np.float16), opacities, tile=tile)
+
+
+def rasterize_rows_forward(cam: Camera, positions, features, opacities, tile=8) -> ForwardState:
+    feats = _f32(features)
+    n, ch = feats.shape
+    assert ch % 4 == 0
+    st = _rows_state(cam, positions, opacities, tile)
+    L = lib()
+    H, W = cam.height, cam.width
+    st.image = np.zeros((ch, H, W), np.float32)
+    st.alpha = np.zeros((1, H, W), np.float32)
+    st.blending_weights = np.zeros(n, np.float32)
+    st.extra["features"] = feats
+    cc = cam.c()
+    for g in range(ch // 4):
+        fv = np.ascontiguousarray(feats[:, 4 * g:4 * g + 4])
+        img = np.zeros((4, H, W), np.float32)
+        L.orc_blend_forward(C.c_int(BILINEAR), C.byref(cc), C.c_int(tile), C.c_int64(n), _p(st.ranges), _p(st.inst_point),
+                            _p(st.screen), _p(fv), _p(st.opacity), None, _p(img), _p(st.alpha), _p(st.blending_weights))
+        st.image[4 * g:4 * g + 4] = img
+    return st
+
+
+def rasterize_rows_backward(st: ForwardState, grad_image, grad_alpha):
+    """grad_features (n,C) float32 and grad_opacities (n,1) float32.  The opacity gradient is linear in
+    (grad_image, grad_alpha): channel group g contributes through its own four gradient planes, the
+    alpha term is added once (with group 0)."""
+    L = lib()
+    feats = st.extra["features"]
+    n, ch = feats.shape
+    H, W = st.cam.height, st.cam.width
+    gi = _f32(grad_image).reshape(ch, H, W)
+    ga = _f32(grad_alpha).reshape(1, H, W)
+    gf = np.zeros((n, ch), np.float32)
+    go = np.zeros((n, 1), np.float64)
+    cc = st.cam.c()
+    for g in range(ch // 4):
+        fv = np.ascontiguousarray(feats[:, 4 * g:4 * g + 4])
+        gfv = np.zeros((n, 4), np.float32)
+        gop = np.zeros((n, 1), np.float32)
+        gig = np.ascontiguousarray(gi[4 * g:4 * g + 4])
+        gag = ga if g == 0 else np.zeros_like(ga)
+        img = np.ascontiguousarray(st.image[4 * g:4 * g + 4])
+        L.orc_blend_backward(C.c_int(BILINEAR), C.byref(cc), C.c_int(st.tile), C.c_int64(n), _p(st.ranges),
+                             _p(st.inst_point), _p(st.screen), _p(fv), _p(st.opacity), None, _p(gig), _p(gag), _p(img),
+                             _p(st.alpha), _p(gfv), _p(gop))
+        gf[:, 4 * g:4 * g + 4] = gfv
+        go += gop
+    return gf, go.astype(np.float32)
+
+
+def render_rows(cam: Camera, positions, features, opacities, tile=8):
+    feats = _f32(features)
+    n, ch = feats.shape
+    st = _rows_state(cam, positions, opacities, tile)
+    L = lib()
+    H, W = cam.height, cam.width
+    image = np.zeros((ch, H, W), np.float32)
+    depth = np.zeros((1, H, W), np.float32)
+    alpha = np.zeros((1, H, W), np.float32)
+    cc = cam.c()
+    for g in range(ch // 4):
+        fv = np.ascontiguousarray(feats[:, 4 * g:4 * g + 4])
+        img = np.zeros((4, H, W), np.float32)
+        L.orc_blend_inference(C.c_int(BILINEAR), C.byref(cc), C.c_int(tile), _p(st.ranges), _p(st.inst_point), _p(st.screen),
+                              _p(fv), _p(st.opacity), _p(st.depth), None, C.c_float(0.0), _p(img), _p(depth), _p(alpha))
+        image[4 * g:4 * g + 4] = img
+    return image, depth, alpha, st
+
+
 # ----------------------------------------------------------------------------- sampler
 
 def viewpoint_weights(cam: Camera, centers, levels, weights, initial_size):

@@ -56,6 +56,12 @@ def test_sort_skewed_and_constant_keys():
     _check(depth_like, 32)
 
 
+def test_sort_full_size_depth_keys():
+    """The bench's size: 2^23 pairs with 27 significant bits (three passes), keys larger than L2."""
+    g = torch.Generator(device=DEV).manual_seed(23)
+    _check(torch.randint(0, 1 << 27, (1 << 23,), generator=g, device=DEV, dtype=torch.int64), 27)
+
+
 def test_sort_rejects_bad_arguments():
     from inpc_b200 import _cabi
     rc = _cabi.lib().inpc_sort_pairs(None, None, None, None, 10, 40, None, None, None)

@@ -314,3 +314,32 @@ def test_misc_against_torch_formulas():
     fac = np.array([O.weight_decay_factor(i) for i in range(0, 30000, 997)])
     assert np.allclose(O.weight_decay(w)[::997], fac * w[::997], rtol=1e-6)
     assert np.allclose(O.weight_decay(w, g0)[::997], g0[::997] + fac * w[::997], rtol=1e-5, atol=1e-7)
+
+
+def test_feature_rows_equal_sh_path_with_dc_only_coefficients():
+    """The C/4-pass restatement of the feature-row layout against the four-channel SH restatement:
+    rows = 0.2820948 * DC coefficient, every other coefficient zero -> same image, alpha, weights and
+    opacity gradient; feature gradient = coefficient gradient / 0.2820948 (the latter rounded to fp16)."""
+    rng = np.random.default_rng(11)
+    cam = O.Camera(np.eye(4, dtype=np.float32), np.zeros(3, np.float32), 48, 40, 50.0, 50.0, 24.0, 20.0)
+    n = 3000
+    pos = np.stack([rng.uniform(-1, 1, n), rng.uniform(-1, 1, n), rng.uniform(1.5, 3.0, n)], axis=1).astype(np.float32)
+    opac = rng.uniform(0.05, 0.9, (n, 1)).astype(np.float32)
+    dc = rng.normal(0, 0.5, (n, 8)).astype(np.float16)
+    rows = (np.float32(0.28209479177387814) * dc.astype(np.float32)).astype(np.float32)
+    st = O.rasterize_rows_forward(cam, pos, rows, opac, tile=8)
+    gi = rng.normal(0, 1e-3, (8, 40, 48)).astype(np.float32)
+    ga = rng.normal(0, 1e-3, (1, 40, 48)).astype(np.float32)
+    gf, go = O.rasterize_rows_backward(st, gi, ga)
+    go_sh = np.zeros((n, 1), np.float64)
+    for g in range(2):
+        sh = np.zeros((n, 36), np.float16)
+        sh[:, :4] = dc[:, 4 * g:4 * g + 4]
+        s4 = O.rasterize_forward(O.BILINEAR, cam, pos, sh, opac, tile=8)
+        np.testing.assert_allclose(st.image[4 * g:4 * g + 4], s4.image, rtol=1e-6, atol=1e-7)
+        np.testing.assert_array_equal(st.alpha, s4.alpha)
+        np.testing.assert_array_equal(st.blending_weights, s4.blending_weights)
+        gsh, gop, gfv = O.rasterize_backward(s4, gi[4 * g:4 * g + 4], ga if g == 0 else np.zeros_like(ga))
+        np.testing.assert_allclose(gf[:, 4 * g:4 * g + 4], gfv, rtol=1e-6, atol=1e-12)
+        go_sh += gop
+    np.testing.assert_allclose(go, go_sh, rtol=1e-5, atol=1e-10)
