@@ -301,6 +301,30 @@ int inpc_leaf_stats_accumulate(const int64_t* indices, const float* weights, int
 int inpc_leaf_update(float* leaf_weights, float* leaf_subdivision_scores, const float* max_sampled,
                      const float* min_sampled, int64_t n_leaves, float decay, void* stream);
 
+/* Structural updates of the octree probability field (the reference does them in torch:
+ * Modules/ProbabilityField.py:159-165 prune, :217-257 subdivide).  Both are two calls: *_count
+ * selects and scans (kind 0 = prune: values are the leaf weights, a leaf is KEPT when weight >
+ * threshold; kind 1 = subdivide: values are the subdivision scores, a leaf is SPLIT when score >
+ * threshold and level < max_level) and returns the number of selected leaves to the host (it
+ * synchronises the stream); the caller sizes the outputs and calls the matching *_fill with the same
+ * arguments and workspace (inpc_leaf_select_workspace_bytes(n) bytes).
+ *   prune output:     n_selected leaves, old order kept.
+ *   subdivide output: n - n_selected unsplit leaves in their old order, then 8 children per split
+ *                     leaf in leaf order; child k sits at centre +- initial_size / 2^(level + 2) per
+ *                     axis with (x, y, z) signs from bits (k&1, k&2, k&4), has level + 1, the parent's
+ *                     weight and score 0.  The reference's cap on the leaf count (16,777,216,
+ *                     ProbabilityField.py:222-224) is the caller's check between the two calls. */
+size_t inpc_leaf_select_workspace_bytes(int64_t n_leaves);
+int inpc_leaf_select_count(int kind, const float* values, const int32_t* levels, int64_t n, float threshold,
+                           int max_level, void* workspace, int64_t* n_selected, void* stream);
+int inpc_leaf_prune_fill(const float* centers, const int32_t* levels, const float* weights, const float* scores,
+                         int64_t n, float threshold, const void* workspace, float* out_centers,
+                         int32_t* out_levels, float* out_weights, float* out_scores, void* stream);
+int inpc_leaf_subdivide_fill(const float* centers, const int32_t* levels, const float* weights,
+                             const float* scores, int64_t n, float threshold, int max_level, float initial_size,
+                             int64_t n_selected, const void* workspace, float* out_centers, int32_t* out_levels,
+                             float* out_weights, float* out_scores, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

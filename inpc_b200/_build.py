@@ -16,7 +16,7 @@ PKG = Path(__file__).resolve().parent
 CSRC = PKG / "csrc"
 LIB = PKG / "libinpc_b200.so"
 OBJ = PKG / "csrc" / "_obj"
-SOURCES = ["api.cu", "radix_sort.cu", "raster.cu", "sampler.cu", "misc.cu"]
+SOURCES = ["api.cu", "radix_sort.cu", "raster.cu", "sampler.cu", "misc.cu", "octree.cu"]
 HEADERS = [CSRC / "common.cuh", PKG.parent / "include" / "inpc_b200.h"]
 NVCC_FLAGS = ["-std=c++17", "-O3", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo",
               "-Xcompiler", "-fPIC"]

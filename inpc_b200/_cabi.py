@@ -76,6 +76,10 @@ PROTOTYPES = {
     "inpc_leaf_stats_reset": (_I, [_P, _P, _L, _P]),
     "inpc_leaf_stats_accumulate": (_I, [_P, _P, _L, _P, _P, _L, _P]),
     "inpc_leaf_update": (_I, [_P, _P, _P, _P, _L, _F, _P]),
+    "inpc_leaf_select_workspace_bytes": (_Z, [_L]),
+    "inpc_leaf_select_count": (_I, [_I, _P, _P, _L, _F, _I, _P, C.POINTER(_L), _P]),
+    "inpc_leaf_prune_fill": (_I, [_P, _P, _P, _P, _L, _F, _P, _P, _P, _P, _P, _P]),
+    "inpc_leaf_subdivide_fill": (_I, [_P, _P, _P, _P, _L, _F, _I, _F, _L, _P, _P, _P, _P, _P, _P]),
 }
 
 _lib = None

@@ -5,6 +5,8 @@ ops; here it is two kernels of libinpc_b200, and the per-leaf statistics can be 
 several views and reduced across ranks before they are applied."""
 from __future__ import annotations
 
+import ctypes as C
+
 import torch
 
 from . import _cabi
@@ -65,3 +67,68 @@ def update_from_samples(leaf_weights: torch.Tensor, leaf_subdivision_scores: tor
     stats = LeafStatistics(leaf_weights.numel(), leaf_weights.device)
     stats.accumulate(indices, weights)
     update(leaf_weights, leaf_subdivision_scores, stats, decay)
+
+
+MAX_LEVEL = 6                 # ProbabilityField.py:220
+MAX_LEAVES = 16_777_216       # 256^3, ProbabilityField.py:222-224
+
+
+def _leaf_arrays(centers, levels, weights, scores):
+    n = weights.numel()
+    for t, name, dt in ((centers, "leaf_centers", torch.float32), (levels, "leaf_levels", torch.int32),
+                        (weights, "leaf_weights", torch.float32), (scores, "leaf_subdivision_scores", torch.float32)):
+        if not isinstance(t, torch.Tensor) or not t.is_cuda:
+            raise ValueError(f"{name} must be a CUDA tensor")
+        if t.dtype != dt:
+            raise TypeError(f"{name} must be {dt}, got {t.dtype}")
+    if centers.shape != (n, 3) or levels.numel() != n or scores.numel() != n:
+        raise ValueError("leaf arrays must describe the same number of leaves: centers (L,3), levels / weights / scores (L)")
+    return centers.contiguous(), levels.contiguous(), weights.contiguous(), scores.contiguous(), n
+
+
+def _select(kind, values, levels, n, threshold, max_level, device):
+    lib = _cabi.lib()
+    ws = torch.empty(int(lib.inpc_leaf_select_workspace_bytes(n)), dtype=torch.uint8, device=device)
+    count = C.c_int64(0)
+    _cabi.check(lib.inpc_leaf_select_count(kind, _ptr(values), _ptr(levels), n, float(threshold), int(max_level), _ptr(ws),
+                                           C.byref(count), _stream()))
+    return ws, int(count.value)
+
+
+def prune(leaf_centers, leaf_levels, leaf_weights, leaf_subdivision_scores, threshold: float):
+    """`ProbabilityField.prune` (Modules/ProbabilityField.py:159-165): the leaves with weight > threshold,
+    in their old order, as four new tensors (centers, levels, weights, scores)."""
+    centers, levels, weights, scores, n = _leaf_arrays(leaf_centers, leaf_levels, leaf_weights, leaf_subdivision_scores)
+    dev = weights.device
+    with torch.cuda.device(dev):
+        ws, kept = _select(0, weights, levels, n, threshold, 0, dev)
+        out = (torch.empty((kept, 3), dtype=torch.float32, device=dev), torch.empty(kept, dtype=torch.int32, device=dev),
+               torch.empty(kept, dtype=torch.float32, device=dev), torch.empty(kept, dtype=torch.float32, device=dev))
+        if kept:
+            _cabi.check(_cabi.lib().inpc_leaf_prune_fill(_ptr(centers), _ptr(levels), _ptr(weights), _ptr(scores), n,
+                                                         float(threshold), _ptr(ws), *[_ptr(o) for o in out], _stream()))
+            ws.record_stream(torch.cuda.current_stream())
+    return out
+
+
+def subdivide(leaf_centers, leaf_levels, leaf_weights, leaf_subdivision_scores, threshold: float, initial_size: float,
+              max_level: int = MAX_LEVEL, max_leaves: int = MAX_LEAVES):
+    """`ProbabilityField.subdivide` (Modules/ProbabilityField.py:217-257): leaves with score > threshold
+    and level < max_level are replaced by their eight children, appended after the unsplit leaves.
+    Returns the four new tensors, or None when the octree would exceed `max_leaves` (the reference
+    then leaves the octree as it is)."""
+    centers, levels, weights, scores, n = _leaf_arrays(leaf_centers, leaf_levels, leaf_weights, leaf_subdivision_scores)
+    dev = weights.device
+    with torch.cuda.device(dev):
+        ws, split = _select(1, scores, levels, n, threshold, max_level, dev)
+        total = n + 7 * split
+        if total > max_leaves:
+            return None
+        out = (torch.empty((total, 3), dtype=torch.float32, device=dev), torch.empty(total, dtype=torch.int32, device=dev),
+               torch.empty(total, dtype=torch.float32, device=dev), torch.empty(total, dtype=torch.float32, device=dev))
+        if n:
+            _cabi.check(_cabi.lib().inpc_leaf_subdivide_fill(_ptr(centers), _ptr(levels), _ptr(weights), _ptr(scores), n,
+                                                             float(threshold), int(max_level), float(initial_size), split,
+                                                             _ptr(ws), *[_ptr(o) for o in out], _stream()))
+            ws.record_stream(torch.cuda.current_stream())
+    return out

@@ -441,3 +441,55 @@ def weight_decay(weights, grads=None, offset_check=None):
 
 def weight_decay_factor(idx: int) -> float:
     return float(lib().orc_weight_decay_factor(C.c_uint32(idx)))
+
+
+# ----------------------------------------------------------------------------- octree structure
+# numpy restatements of the reference's torch code (no native kernel exists for these in the reference)
+
+def leaf_update(leaf_weights, leaf_scores, indices, weights, decay=np.float32(0.9968)):
+    """ProbabilityField.update (Modules/ProbabilityField.py:146-157)."""
+    lw = _f32(leaf_weights) * np.float32(decay)
+    ls = _f32(leaf_scores) * np.float32(decay)
+    w = _f32(weights).reshape(-1)
+    idx = np.asarray(indices, dtype=np.int64).reshape(-1)
+    mx = np.zeros_like(lw)
+    mn = np.full_like(lw, np.inf)
+    np.maximum.at(mx, idx, w)
+    np.minimum.at(mn, idx, w)
+    mn[np.isinf(mn)] = 0.0
+    return np.maximum(lw, mx), np.maximum(ls, np.clip(mx - mn, 0.0, 1.0))
+
+
+def leaf_prune(centers, levels, weights, scores, threshold):
+    """ProbabilityField.prune (Modules/ProbabilityField.py:159-165)."""
+    mask = _f32(weights) > np.float32(threshold)
+    return (_f32(centers).reshape(-1, 3)[mask], np.asarray(levels, np.int32)[mask], _f32(weights)[mask], _f32(scores)[mask])
+
+
+def leaf_subdivide(centers, levels, weights, scores, threshold, initial_size, max_level=6, max_leaves=16_777_216):
+    """ProbabilityField.subdivide (Modules/ProbabilityField.py:217-257); None when the cap would be exceeded."""
+    centers = _f32(centers).reshape(-1, 3)
+    levels = np.asarray(levels, np.int32)
+    weights, scores = _f32(weights), _f32(scores)
+    valid = (scores > np.float32(threshold)) & (levels < max_level)
+    nv = int(valid.sum())
+    if nv * 8 + (centers.shape[0] - nv) > max_leaves:
+        return None
+    new_centers = np.repeat(centers[valid], 8, axis=0)
+    new_levels = np.repeat(levels[valid] + 1, 8)
+    new_weights = np.repeat(weights[valid], 8)
+    offset = (np.float32(initial_size) / (2 ** (new_levels.astype(np.int64) + 1)).astype(np.float32)).astype(np.float32)
+    new_centers[0::2, 0] -= offset[0::2]
+    new_centers[1::2, 0] += offset[1::2]
+    for k in range(4):
+        if k < 2:
+            new_centers[k::4, 1] -= offset[k::4]
+        else:
+            new_centers[k::4, 1] += offset[k::4]
+    for k in range(8):
+        if k < 4:
+            new_centers[k::8, 2] -= offset[k::8]
+        else:
+            new_centers[k::8, 2] += offset[k::8]
+    return (np.concatenate([centers[~valid], new_centers]), np.concatenate([levels[~valid], new_levels]),
+            np.concatenate([weights[~valid], new_weights]), np.concatenate([scores[~valid], np.zeros_like(new_weights)]))
