@@ -325,6 +325,30 @@ int inpc_leaf_subdivide_fill(const float* centers, const int32_t* levels, const 
                              int64_t n_selected, const void* workspace, float* out_centers, int32_t* out_levels,
                              float* out_weights, float* out_scores, void* stream);
 
+/* Image composition directly after the blend; images are (channels, H, W) planar fp32, alpha and
+ * depth (H, W); n_pixels = H*W.  The reference does these with chains of torch element-wise ops.
+ *   compose_background          out = image + (1 - alpha) * background            (Renderer.py:80)
+ *   compose_background_backward grad_alpha = -sum_c g_c * background_c, grad_background = (1 - alpha) * g;
+ *                               either output may be NULL; grad_image is grad_out itself
+ *   multisample_accumulate      acc (+)= one multisample's image / depth / alpha; with `unpremultiply`
+ *                               the features are divided by the sample's alpha first (0 where alpha
+ *                               is 0)                                             (Renderer.py:108-117)
+ *   multisample_resolve         after the last sample: image, depth, alpha *= 1/n; alpha_sum =
+ *                               clamp(sum, 0, 1); with `remultiply` image *= alpha; with a background
+ *                               image += (1 - alpha) * background                 (Renderer.py:118-125)
+ * Each product and sum is rounded separately, so results equal the torch chain bit for bit. */
+int inpc_compose_background(const float* image, const float* alpha, const float* background, int channels,
+                            int64_t n_pixels, float* out, void* stream);
+int inpc_compose_background_backward(const float* grad_out, const float* alpha, const float* background,
+                                     int channels, int64_t n_pixels, float* grad_alpha, float* grad_background,
+                                     void* stream);
+int inpc_multisample_accumulate(float* acc_image, float* acc_depth, float* acc_alpha, const float* image,
+                                const float* depth, const float* alpha, int channels, int64_t n_pixels, int first,
+                                int unpremultiply, void* stream);
+int inpc_multisample_resolve(float* acc_image, float* acc_depth, float* acc_alpha, float* alpha_sum,
+                             const float* background, int channels, int64_t n_pixels, int n_multisamples,
+                             int remultiply, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

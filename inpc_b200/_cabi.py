@@ -76,6 +76,10 @@ PROTOTYPES = {
     "inpc_leaf_stats_reset": (_I, [_P, _P, _L, _P]),
     "inpc_leaf_stats_accumulate": (_I, [_P, _P, _L, _P, _P, _L, _P]),
     "inpc_leaf_update": (_I, [_P, _P, _P, _P, _L, _F, _P]),
+    "inpc_compose_background": (_I, [_P, _P, _P, _I, _L, _P, _P]),
+    "inpc_compose_background_backward": (_I, [_P, _P, _P, _I, _L, _P, _P, _P]),
+    "inpc_multisample_accumulate": (_I, [_P, _P, _P, _P, _P, _P, _I, _L, _I, _I, _P]),
+    "inpc_multisample_resolve": (_I, [_P, _P, _P, _P, _P, _I, _L, _I, _I, _P]),
     "inpc_leaf_select_workspace_bytes": (_Z, [_L]),
     "inpc_leaf_select_count": (_I, [_I, _P, _P, _L, _F, _I, _P, C.POINTER(_L), _P]),
     "inpc_leaf_prune_fill": (_I, [_P, _P, _P, _P, _L, _F, _P, _P, _P, _P, _P, _P]),

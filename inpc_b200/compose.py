@@ -1,0 +1,108 @@
+"""Image composition directly after the blend: background compose for training and multisample
+accumulation for inference (reference: Renderer.py:80 and :105-125, chains of torch element-wise ops;
+here one kernel of libinpc_b200 each, bit-identical results)."""
+from __future__ import annotations
+
+from typing import Any
+
+import torch
+from torch.autograd.function import once_differentiable
+
+from . import _cabi
+from .rasterization import _cuda_f32, _ptr, _stream
+
+
+def _planes(image, alpha, name="image"):
+    image = _cuda_f32(image, name)
+    alpha = _cuda_f32(alpha, "alpha")
+    if image.dim() != 3 or alpha.numel() != image.shape[1] * image.shape[2]:
+        raise ValueError(f"{name} must be (C,H,W) and alpha (1,H,W) or (H,W); got {tuple(image.shape)} and {tuple(alpha.shape)}")
+    return image, alpha
+
+
+class _ComposeBackground(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx: Any, image: torch.Tensor, alpha: torch.Tensor, background: torch.Tensor):
+        image, alpha = _planes(image, alpha)
+        background = _cuda_f32(background, "background")
+        if background.shape != image.shape:
+            raise ValueError(f"background must have the image's shape {tuple(image.shape)}, got {tuple(background.shape)}")
+        out = torch.empty_like(image)
+        with torch.cuda.device(image.device):
+            _cabi.check(_cabi.lib().inpc_compose_background(_ptr(image), _ptr(alpha), _ptr(background), image.shape[0],
+                                                            image.shape[1] * image.shape[2], _ptr(out), _stream()))
+        ctx.save_for_backward(alpha, background)
+        return out
+
+    @staticmethod
+    @once_differentiable
+    def backward(ctx: Any, grad_out: torch.Tensor):
+        alpha, background = ctx.saved_tensors
+        grad_out = _cuda_f32(grad_out, "grad_out")
+        need_alpha, need_bg = ctx.needs_input_grad[1], ctx.needs_input_grad[2]
+        grad_alpha = torch.empty_like(alpha) if need_alpha else None
+        grad_bg = torch.empty_like(background) if need_bg else None
+        if need_alpha or need_bg:
+            with torch.cuda.device(grad_out.device):
+                _cabi.check(_cabi.lib().inpc_compose_background_backward(
+                    _ptr(grad_out), _ptr(alpha), _ptr(background), grad_out.shape[0], grad_out.shape[1] * grad_out.shape[2],
+                    _ptr(grad_alpha), _ptr(grad_bg), _stream()))
+        return grad_out, grad_alpha, grad_bg
+
+
+def compose_background(image: torch.Tensor, alpha: torch.Tensor, background: torch.Tensor) -> torch.Tensor:
+    """`image + (1 - alpha) * background` (Renderer.py:80), differentiable in all three arguments."""
+    return _ComposeBackground.apply(image, alpha, background)
+
+
+class MultisampleAccumulator:
+    """Running sums over the multisamples of one frame and their resolve (Renderer.py:105-125).
+
+        acc = MultisampleAccumulator(n_multisamples, average_with_premultiplied_alpha=True)
+        for ...: acc.add(*rasterizer.render(...))
+        feature_image, depth, alpha, alpha_sum = acc.resolve(background)
+    """
+
+    def __init__(self, n_multisamples: int, average_with_premultiplied_alpha: bool = True) -> None:
+        self.n = max(1, int(n_multisamples))
+        self.unpremultiply = (not average_with_premultiplied_alpha) and self.n > 1
+        self.count = 0
+        self.image = self.depth = self.alpha = None
+
+    @torch.no_grad()
+    def add(self, image: torch.Tensor, depth: torch.Tensor, alpha: torch.Tensor) -> None:
+        image, alpha = _planes(image, alpha)
+        depth = _cuda_f32(depth, "depth")
+        if depth.numel() != alpha.numel():
+            raise ValueError("depth and alpha must have the same number of pixels")
+        if self.count >= self.n:
+            raise RuntimeError(f"already holds {self.n} multisamples")
+        first = self.count == 0
+        if first:
+            self.image, self.depth, self.alpha = torch.empty_like(image), torch.empty_like(depth), torch.empty_like(alpha)
+        elif image.shape != self.image.shape:
+            raise ValueError("all multisamples must have the same shape")
+        with torch.cuda.device(image.device):
+            _cabi.check(_cabi.lib().inpc_multisample_accumulate(
+                _ptr(self.image), _ptr(self.depth), _ptr(self.alpha), _ptr(image), _ptr(depth), _ptr(alpha), image.shape[0],
+                alpha.numel(), int(first), int(self.unpremultiply), _stream()))
+        self.count += 1
+
+    @torch.no_grad()
+    def resolve(self, background: torch.Tensor | None = None):
+        """Returns (feature_image, depth, alpha, alpha_sum); the accumulator is empty afterwards."""
+        if self.count != self.n:
+            raise RuntimeError(f"{self.count} of {self.n} multisamples were added")
+        if background is not None:
+            background = _cuda_f32(background, "background")
+            if background.shape != self.image.shape:
+                raise ValueError("background must have the image's shape")
+        alpha_sum = torch.empty_like(self.alpha)
+        with torch.cuda.device(self.image.device):
+            _cabi.check(_cabi.lib().inpc_multisample_resolve(
+                _ptr(self.image), _ptr(self.depth), _ptr(self.alpha), _ptr(alpha_sum), _ptr(background), self.image.shape[0],
+                self.alpha.numel(), self.n, int(self.unpremultiply), _stream()))
+        out = (self.image, self.depth, self.alpha, alpha_sum)
+        self.image = self.depth = self.alpha = None
+        self.count = 0
+        return out

@@ -111,6 +111,20 @@ int sort_pass_count(int end_bit);   // passes sort_pairs makes; the result is in
 int sort_pairs(uint32_t* keys, uint32_t* keys_alt, uint32_t* values, uint32_t* values_alt, int64_t n,
                int end_bit, void* workspace, int* result_in_alt, cudaStream_t stream);
 
+// More than 48 KB of dynamic shared memory is an opt-in per kernel AND per device: `done` is the
+// caller's per-kernel table of devices already set up.
+constexpr int kMaxDevices = 64;
+template <typename Kernel>
+int opt_in_dynamic_smem(Kernel kernel, size_t bytes, bool (&done)[kMaxDevices]) {
+    int dev = 0;
+    INPC_CUDA_TRY(cudaGetDevice(&dev));
+    const bool tracked = dev >= 0 && dev < kMaxDevices;
+    if (tracked && done[dev]) return INPC_OK;
+    INPC_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes));
+    if (tracked) done[dev] = true;
+    return INPC_OK;
+}
+
 // ---- device helpers ------------------------------------------------------------------------
 #ifdef __CUDACC__
 __device__ __forceinline__ unsigned lane_id() { return threadIdx.x & 31u; }

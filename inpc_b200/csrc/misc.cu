@@ -173,6 +173,87 @@ __global__ void __launch_bounds__(kThreads) leaf_update_kernel(float* __restrict
     }
 }
 
+// ---- image composition after the blend (Renderer.py:80 training, :105-122 inference) -------------
+// Every product and sum is rounded on its own (__fmul_rn / __fadd_rn / __fdiv_rn keep the compiler
+// from contracting them), as the chain of separate torch element-wise kernels it replaces does.
+
+// out[c] = image[c] + (1 - alpha) * background[c]
+__global__ void __launch_bounds__(kThreads) compose_background_kernel(const float* __restrict__ image, const float* __restrict__ alpha,
+                                                                      const float* __restrict__ background, int channels, int64_t n_px,
+                                                                      float* __restrict__ out) {
+    const int64_t stride = (int64_t)gridDim.x * kThreads;
+    for (int64_t p = (int64_t)blockIdx.x * kThreads + threadIdx.x; p < n_px; p += stride) {
+        const float t = __fsub_rn(1.0f, __ldg(alpha + p));
+        for (int c = 0; c < channels; ++c) {
+            const int64_t i = (int64_t)c * n_px + p;
+            out[i] = __fadd_rn(__ldg(image + i), __fmul_rn(t, __ldg(background + i)));
+        }
+    }
+}
+
+// grad_alpha = -sum_c g[c] * background[c];  grad_background[c] = (1 - alpha) * g[c]   (grad_image = g)
+__global__ void __launch_bounds__(kThreads) compose_background_backward_kernel(const float* __restrict__ grad_out, const float* __restrict__ alpha,
+                                                                               const float* __restrict__ background, int channels,
+                                                                               int64_t n_px, float* __restrict__ grad_alpha,
+                                                                               float* __restrict__ grad_background) {
+    const int64_t stride = (int64_t)gridDim.x * kThreads;
+    for (int64_t p = (int64_t)blockIdx.x * kThreads + threadIdx.x; p < n_px; p += stride) {
+        const float t = 1.0f - __ldg(alpha + p);
+        float dot = 0.0f;
+        for (int c = 0; c < channels; ++c) {
+            const int64_t i = (int64_t)c * n_px + p;
+            const float g = __ldg(grad_out + i);
+            if (grad_alpha) dot += g * __ldg(background + i);
+            if (grad_background) grad_background[i] = t * g;
+        }
+        if (grad_alpha) grad_alpha[p] = -dot;
+    }
+}
+
+// One multisample: acc (+)= sample, the features optionally divided by the sample's alpha first
+// (Renderer.py:108-117).
+__global__ void __launch_bounds__(kThreads) multisample_accumulate_kernel(float* __restrict__ acc_image, float* __restrict__ acc_depth,
+                                                                          float* __restrict__ acc_alpha, const float* __restrict__ image,
+                                                                          const float* __restrict__ depth, const float* __restrict__ alpha,
+                                                                          int channels, int64_t n_px, bool first, bool unpremultiply) {
+    const int64_t stride = (int64_t)gridDim.x * kThreads;
+    for (int64_t p = (int64_t)blockIdx.x * kThreads + threadIdx.x; p < n_px; p += stride) {
+        const float a = __ldg(alpha + p);
+        for (int c = 0; c < channels; ++c) {
+            const int64_t i = (int64_t)c * n_px + p;
+            float f = __ldg(image + i);
+            if (unpremultiply) f = a > 0.0f ? __fdiv_rn(f, a) : 0.0f;
+            acc_image[i] = first ? f : __fadd_rn(acc_image[i], f);
+        }
+        acc_depth[p] = first ? __ldg(depth + p) : __fadd_rn(acc_depth[p], __ldg(depth + p));
+        acc_alpha[p] = first ? a : __fadd_rn(acc_alpha[p], a);
+    }
+}
+
+// After the last multisample (Renderer.py:118-125): scale by 1/n, alpha_sum = clamp(sum of alphas),
+// re-multiply by the mean alpha when the features were accumulated un-premultiplied, add the background.
+__global__ void __launch_bounds__(kThreads) multisample_resolve_kernel(float* __restrict__ acc_image, float* __restrict__ acc_depth,
+                                                                       float* __restrict__ acc_alpha, float* __restrict__ alpha_sum,
+                                                                       const float* __restrict__ background, int channels, int64_t n_px,
+                                                                       float factor, bool remultiply) {
+    const int64_t stride = (int64_t)gridDim.x * kThreads;
+    for (int64_t p = (int64_t)blockIdx.x * kThreads + threadIdx.x; p < n_px; p += stride) {
+        const float a_sum = acc_alpha[p];
+        const float a = __fmul_rn(a_sum, factor);
+        alpha_sum[p] = fminf(fmaxf(a_sum, 0.0f), 1.0f);
+        acc_alpha[p] = a;
+        acc_depth[p] = __fmul_rn(acc_depth[p], factor);
+        const float t = __fsub_rn(1.0f, a);
+        for (int c = 0; c < channels; ++c) {
+            const int64_t i = (int64_t)c * n_px + p;
+            float f = __fmul_rn(acc_image[i], factor);
+            if (remultiply) f = __fmul_rn(f, a);
+            if (background) f = __fadd_rn(f, __fmul_rn(t, __ldg(background + i)));
+            acc_image[i] = f;
+        }
+    }
+}
+
 }  // namespace
 
 }  // namespace inpc
@@ -250,5 +331,46 @@ extern "C" int inpc_leaf_update(float* leaf_weights, float* leaf_subdivision_sco
         leaf_weights, leaf_subdivision_scores, reinterpret_cast<const unsigned*>(max_sampled),
         reinterpret_cast<const unsigned*>(min_sampled), n_leaves, decay);
     INPC_LAUNCH_CHECK("leaf_update_kernel");
+    return INPC_OK;
+}
+
+extern "C" int inpc_compose_background(const float* image, const float* alpha, const float* background, int channels, int64_t n_pixels,
+                                       float* out, void* stream_) {
+    if (n_pixels == 0 || channels == 0) return INPC_OK;
+    if (n_pixels < 0 || channels < 0 || !image || !alpha || !background || !out) { set_error("inpc_compose_background: bad argument"); return INPC_E_INVALID; }
+    compose_background_kernel<<<grid_for(n_pixels), kThreads, 0, static_cast<cudaStream_t>(stream_)>>>(image, alpha, background, channels, n_pixels, out);
+    INPC_LAUNCH_CHECK("compose_background_kernel");
+    return INPC_OK;
+}
+
+extern "C" int inpc_compose_background_backward(const float* grad_out, const float* alpha, const float* background, int channels,
+                                                int64_t n_pixels, float* grad_alpha, float* grad_background, void* stream_) {
+    if (n_pixels == 0 || channels == 0 || (!grad_alpha && !grad_background)) return INPC_OK;
+    if (n_pixels < 0 || channels < 0 || !grad_out || !alpha || (grad_alpha && !background)) { set_error("inpc_compose_background_backward: bad argument"); return INPC_E_INVALID; }
+    compose_background_backward_kernel<<<grid_for(n_pixels), kThreads, 0, static_cast<cudaStream_t>(stream_)>>>(grad_out, alpha, background, channels,
+                                                                                                             n_pixels, grad_alpha, grad_background);
+    INPC_LAUNCH_CHECK("compose_background_backward_kernel");
+    return INPC_OK;
+}
+
+extern "C" int inpc_multisample_accumulate(float* acc_image, float* acc_depth, float* acc_alpha, const float* image, const float* depth,
+                                           const float* alpha, int channels, int64_t n_pixels, int first, int unpremultiply, void* stream_) {
+    if (n_pixels == 0) return INPC_OK;
+    if (n_pixels < 0 || channels < 0 || !acc_image || !acc_depth || !acc_alpha || !image || !depth || !alpha) { set_error("inpc_multisample_accumulate: bad argument"); return INPC_E_INVALID; }
+    multisample_accumulate_kernel<<<grid_for(n_pixels), kThreads, 0, static_cast<cudaStream_t>(stream_)>>>(acc_image, acc_depth, acc_alpha, image, depth, alpha,
+                                                                                                        channels, n_pixels, first != 0, unpremultiply != 0);
+    INPC_LAUNCH_CHECK("multisample_accumulate_kernel");
+    return INPC_OK;
+}
+
+extern "C" int inpc_multisample_resolve(float* acc_image, float* acc_depth, float* acc_alpha, float* alpha_sum, const float* background,
+                                        int channels, int64_t n_pixels, int n_multisamples, int remultiply, void* stream_) {
+    if (n_pixels == 0) return INPC_OK;
+    if (n_pixels < 0 || channels < 0 || n_multisamples < 1 || !acc_image || !acc_depth || !acc_alpha || !alpha_sum) { set_error("inpc_multisample_resolve: bad argument"); return INPC_E_INVALID; }
+    // the factor is the double-precision 1/n rounded to float once, as a python float times an fp32 tensor is
+    const float factor = (float)(1.0 / (double)n_multisamples);
+    multisample_resolve_kernel<<<grid_for(n_pixels), kThreads, 0, static_cast<cudaStream_t>(stream_)>>>(acc_image, acc_depth, acc_alpha, alpha_sum, background,
+                                                                                                     channels, n_pixels, factor, remultiply != 0);
+    INPC_LAUNCH_CHECK("multisample_resolve_kernel");
     return INPC_OK;
 }

@@ -99,15 +99,19 @@ struct PassSmem {
     unsigned tile_id;
 };
 
+// BITS > 0 fixes the digit width at compile time (the ballot loop of the ranking unrolls); BITS == 0
+// takes it from `bits_arg`.
+template <int BITS>
 __global__ void __launch_bounds__(kThreads) radix_onesweep_pass_kernel(
     const uint32_t* __restrict__ keys_in, const uint32_t* __restrict__ vals_in,
-    uint32_t* __restrict__ keys_out, uint32_t* __restrict__ vals_out, int64_t n, int shift, int bits,
+    uint32_t* __restrict__ keys_out, uint32_t* __restrict__ vals_out, int64_t n, int shift, int bits_arg,
     const unsigned* __restrict__ digit_base, volatile unsigned* tile_state, unsigned* ticket,
     volatile unsigned* status) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     PassSmem& s = *reinterpret_cast<PassSmem*>(smem_raw);
 
     const unsigned tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
+    const int bits = BITS > 0 ? BITS : bits_arg;
     const unsigned digit_mask = (1u << bits) - 1u;
 
     if (tid == 0) s.tile_id = atomicAdd(ticket, 1u);
@@ -139,10 +143,19 @@ __global__ void __launch_bounds__(kThreads) radix_onesweep_pass_kernel(
         peers[i] = __match_any_sync(0xffffffffu, d);
 #else
         unsigned p = 0xffffffffu;
-        for (int b = 0; b < bits; ++b) {
-            const bool one = (d >> b) & 1u;
-            const unsigned m = __ballot_sync(0xffffffffu, one);
-            p &= one ? m : ~m;
+        if (BITS > 0) {
+#pragma unroll
+            for (int b = 0; b < BITS; ++b) {
+                const bool one = (d >> b) & 1u;
+                const unsigned m = __ballot_sync(0xffffffffu, one);
+                p &= one ? m : ~m;
+            }
+        } else {
+            for (int b = 0; b < bits; ++b) {
+                const bool one = (d >> b) & 1u;
+                const unsigned m = __ballot_sync(0xffffffffu, one);
+                p &= one ? m : ~m;
+            }
         }
         peers[i] = p;
 #endif
@@ -283,6 +296,26 @@ SortWorkspace carve_sort_workspace(void* ws, int64_t n) {
     return w;
 }
 
+
+int launch_onesweep_pass(int64_t tiles, const uint32_t* kin, const uint32_t* vin, uint32_t* kout, uint32_t* vout, int64_t n, int shift, int bits,
+                         const unsigned* base, unsigned* state, unsigned* ticket, unsigned* status, cudaStream_t stream) {
+    static bool attr_set[4][kMaxDevices] = {{false}};
+    int rc = opt_in_dynamic_smem(radix_onesweep_pass_kernel<0>, sizeof(PassSmem), attr_set[0]);
+    if (rc == INPC_OK) rc = opt_in_dynamic_smem(radix_onesweep_pass_kernel<7>, sizeof(PassSmem), attr_set[1]);
+    if (rc == INPC_OK) rc = opt_in_dynamic_smem(radix_onesweep_pass_kernel<8>, sizeof(PassSmem), attr_set[2]);
+    if (rc == INPC_OK) rc = opt_in_dynamic_smem(radix_onesweep_pass_kernel<9>, sizeof(PassSmem), attr_set[3]);
+    if (rc != INPC_OK) return rc;
+    // the digit widths the rasterizer's sorts use (depth keys 9/8, tile keys 7) get unrolled kernels
+    switch (bits) {
+        case 7: radix_onesweep_pass_kernel<7><<<(unsigned)tiles, kThreads, sizeof(PassSmem), stream>>>(kin, vin, kout, vout, n, shift, bits, base, state, ticket, status); break;
+        case 8: radix_onesweep_pass_kernel<8><<<(unsigned)tiles, kThreads, sizeof(PassSmem), stream>>>(kin, vin, kout, vout, n, shift, bits, base, state, ticket, status); break;
+        case 9: radix_onesweep_pass_kernel<9><<<(unsigned)tiles, kThreads, sizeof(PassSmem), stream>>>(kin, vin, kout, vout, n, shift, bits, base, state, ticket, status); break;
+        default: radix_onesweep_pass_kernel<0><<<(unsigned)tiles, kThreads, sizeof(PassSmem), stream>>>(kin, vin, kout, vout, n, shift, bits, base, state, ticket, status); break;
+    }
+    INPC_LAUNCH_CHECK("radix_onesweep_pass_kernel");
+    return INPC_OK;
+}
+
 }  // namespace
 
 size_t sort_workspace_bytes(int64_t n) { return carve_sort_workspace(nullptr, n).total; }
@@ -325,19 +358,13 @@ int sort_pairs(uint32_t* keys, uint32_t* keys_alt, uint32_t* values, uint32_t* v
     radix_scan_histogram_kernel<<<pt.n_passes, kRadix, 0, stream>>>(w.hist, w.base);
     INPC_LAUNCH_CHECK("radix_scan_histogram_kernel");
 
-    static bool attr_set = false;
-    if (!attr_set) {
-        INPC_CUDA_TRY(cudaFuncSetAttribute(radix_onesweep_pass_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(PassSmem)));
-        attr_set = true;
-    }
     unsigned* status = device_status_ptr();
     if (!status) return INPC_E_CUDA;
     uint32_t *kin = keys, *kout = keys_alt, *vin = values, *vout = values_alt;
     for (int p = 0; p < pt.n_passes; ++p) {
-        radix_onesweep_pass_kernel<<<(unsigned)tiles, kThreads, sizeof(PassSmem), stream>>>(
-            kin, vin, kout, vout, n, pt.shift[p], pt.bits[p], w.base + p * kRadix,
-            w.state + (size_t)p * tiles * kRadix, w.ticket + p, status);
-        INPC_LAUNCH_CHECK("radix_onesweep_pass_kernel");
+        const int rc = launch_onesweep_pass(tiles, kin, vin, kout, vout, n, pt.shift[p], pt.bits[p], w.base + p * kRadix,
+                                            w.state + (size_t)p * tiles * kRadix, w.ticket + p, status, stream);
+        if (rc != INPC_OK) return rc;
         uint32_t* t = kin; kin = kout; kout = t;
         t = vin; vin = vout; vout = t;
     }
@@ -363,7 +390,6 @@ static_assert(kStaticWorkspaceBytes % 256 == 0, "status area must stay 256-byte 
 
 static __device__ __align__(256) unsigned char g_static_sort_scratch[kStaticScratchBytes];
 
-constexpr int kMaxDevices = 64;
 std::mutex g_static_mutex;
 void* g_static_scratch_ptr[kMaxDevices] = {nullptr};   // device address of the array, per device
 
@@ -377,7 +403,6 @@ int static_scratch_for_current_device(void** out) {
     if (!g_static_scratch_ptr[dev]) {
         void* p = nullptr;
         INPC_CUDA_TRY(cudaGetSymbolAddress(&p, g_static_sort_scratch));
-        INPC_CUDA_TRY(cudaFuncSetAttribute(radix_onesweep_pass_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(PassSmem)));
         g_static_scratch_ptr[dev] = p;
     }
     *out = g_static_scratch_ptr[dev];
@@ -422,7 +447,7 @@ extern "C" int inpc_sort_pairs_static(uint32_t* keys, uint32_t* keys_alt, uint32
     const int64_t tiles = ceil_div<int64_t>(n, kTile);
     // the array keeps the previous call's histograms, tickets and look-back flags: clear what this call reads
     INPC_CUDA_TRY(cudaMemsetAsync(scratch, 0, w.zero_bytes + (size_t)pt.n_passes * tiles * kRadix * sizeof(unsigned), stream));
-    volatile unsigned* status = reinterpret_cast<unsigned*>(static_cast<unsigned char*>(scratch) + kStaticWorkspaceBytes);
+    unsigned* status = reinterpret_cast<unsigned*>(static_cast<unsigned char*>(scratch) + kStaticWorkspaceBytes);
 
     const int hist_blocks = (int)ceil_div<int64_t>(n, kHistItemsPerBlock);
     radix_histogram_kernel<<<hist_blocks, kHistThreads, 0, stream>>>(keys, n, pt, w.hist);
@@ -431,10 +456,9 @@ extern "C" int inpc_sort_pairs_static(uint32_t* keys, uint32_t* keys_alt, uint32
     INPC_LAUNCH_CHECK("radix_scan_histogram_kernel");
     uint32_t *kin = keys, *kout = keys_alt, *vin = values, *vout = values_alt;
     for (int p = 0; p < pt.n_passes; ++p) {
-        radix_onesweep_pass_kernel<<<(unsigned)tiles, kThreads, sizeof(PassSmem), stream>>>(
-            kin, vin, kout, vout, n, pt.shift[p], pt.bits[p], w.base + p * kRadix,
-            w.state + (size_t)p * tiles * kRadix, w.ticket + p, status);
-        INPC_LAUNCH_CHECK("radix_onesweep_pass_kernel");
+        rc = launch_onesweep_pass(tiles, kin, vin, kout, vout, n, pt.shift[p], pt.bits[p], w.base + p * kRadix,
+                                  w.state + (size_t)p * tiles * kRadix, w.ticket + p, status, stream);
+        if (rc != INPC_OK) return rc;
         uint32_t* t = kin; kin = kout; kout = t;
         t = vin; vin = vout; vout = t;
     }

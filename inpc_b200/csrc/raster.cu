@@ -1767,10 +1767,10 @@ int launch_bilinear_backward(const RasterParams& rp, const PointBlob& pb, const 
                              float* grad_opacities, cudaStream_t stream) {
     constexpr int IPT = BlendConfig<T>::kIpt;
     constexpr size_t smem = backward_smem_bytes<T, IPT>();
-    static bool attr_set = false;
-    if (!attr_set) {
-        INPC_CUDA_TRY(cudaFuncSetAttribute(blend_bilinear_backward_kernel<T, IPT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        attr_set = true;
+    static bool attr_set[kMaxDevices] = {false};
+    {
+        const int rc_attr = opt_in_dynamic_smem(blend_bilinear_backward_kernel<T, IPT>, smem, attr_set);
+        if (rc_attr != INPC_OK) return rc_attr;
     }
     blend_bilinear_backward_kernel<T, IPT><<<(unsigned)ib.max_segments, T * T, smem, stream>>>(
         ib.segs, ib.n_segments, ids, pb.rec, ib.seg_T, ib.seg_C, grad_image, grad_alpha, image, alpha, gfv, grad_opacities,
@@ -1803,10 +1803,10 @@ template <int T, int C4, int KIND>
 int launch_rows_forward(const RasterParams& rp, const PointBlob& pb, const InstanceBlob& ib, const uint32_t* ids, const float* features,
                         float* image, float* depth, float* alpha, float* blending_weights, cudaStream_t stream) {
     constexpr size_t smem = rows_forward_smem_bytes<T, C4>();
-    static bool attr_set = false;
-    if (!attr_set) {
-        INPC_CUDA_TRY(cudaFuncSetAttribute(blend_rows_forward_kernel<T, C4, KIND>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        attr_set = true;
+    static bool attr_set[kMaxDevices] = {false};
+    {
+        const int rc_attr = opt_in_dynamic_smem(blend_rows_forward_kernel<T, C4, KIND>, smem, attr_set);
+        if (rc_attr != INPC_OK) return rc_attr;
     }
     const int n_tiles = rp.gw * rp.gh;
     const int W = rp.v.width, H = rp.v.height;
@@ -1829,10 +1829,10 @@ int launch_rows_backward(const RasterParams& rp, const PointBlob& pb, const Inst
                          const float* grad_image, const float* grad_alpha, const float* image, const float* alpha,
                          float* grad_features, float* grad_opacities, cudaStream_t stream) {
     constexpr size_t smem = rows_backward_smem_bytes<T, C4>();
-    static bool attr_set = false;
-    if (!attr_set) {
-        INPC_CUDA_TRY(cudaFuncSetAttribute(blend_rows_backward_kernel<T, C4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        attr_set = true;
+    static bool attr_set[kMaxDevices] = {false};
+    {
+        const int rc_attr = opt_in_dynamic_smem(blend_rows_backward_kernel<T, C4>, smem, attr_set);
+        if (rc_attr != INPC_OK) return rc_attr;
     }
     blend_rows_backward_kernel<T, C4><<<(unsigned)ib.max_segments, T * T, smem, stream>>>(
         ib.segs, ib.n_segments, ids, pb.rec, reinterpret_cast<const float4*>(features), ib.seg_T, ib.seg_C, grad_image, grad_alpha, image, alpha,

@@ -493,3 +493,40 @@ def leaf_subdivide(centers, levels, weights, scores, threshold, initial_size, ma
             new_centers[k::8, 2] += offset[k::8]
     return (np.concatenate([centers[~valid], new_centers]), np.concatenate([levels[~valid], new_levels]),
             np.concatenate([weights[~valid], new_weights]), np.concatenate([scores[~valid], np.zeros_like(new_weights)]))
+
+
+# ----------------------------------------------------------------------------- image composition
+# numpy restatements of the reference renderer's torch element-wise chains (one rounding per op)
+
+def compose_background(image, alpha, background):
+    """Renderer.py:80: feature_image + (1 - alpha_image) * background."""
+    image, alpha, background = _f32(image), _f32(alpha), _f32(background)
+    return image + (np.float32(1.0) - alpha.reshape(1, *image.shape[1:])) * background
+
+
+def multisample_resolve(samples, background, premultiplied=True):
+    """Renderer.py:105-125 for a list of (feature_image, depth_image, alpha_image) multisamples.
+    Returns feature_image, depth, alpha, alpha_sum."""
+    n = max(1, len(samples))
+    fi = di = ai = None
+    for k, (f, d, a) in enumerate(samples):
+        f, d, a = _f32(f).copy(), _f32(d).copy(), _f32(a).copy()
+        if not premultiplied and n > 1:
+            with np.errstate(divide="ignore", invalid="ignore"):
+                f = np.where(a > 0.0, f / a, np.float32(0.0)).astype(np.float32)
+        if k == 0:
+            fi, di, ai = f, d, a
+        else:
+            fi += f
+            di += d
+            ai += a
+    factor = np.float32(1.0 / n)
+    fi *= factor
+    di *= factor
+    alpha_sum = np.clip(ai, 0.0, 1.0)
+    ai = ai * factor
+    if not premultiplied and n > 1:
+        fi *= ai
+    if background is not None:
+        fi += (np.float32(1.0) - ai) * _f32(background)
+    return fi, di, ai, alpha_sum
