@@ -40,6 +40,10 @@ N_VIEWS = 64
 N_POINTS = 1 << 23
 N_LEAVES = 1 << 18
 N_APPEARANCE = 1 << 22
+# DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) per (point, tile) instance of the kernels of a
+# stage, from the ncu capture summarised in profiles/blend_bilinear_tile8_config1_small.md (2^22 points,
+# 5,274,412 instances, 8x8 tiles); the traffic of these kernels grows in proportion to the instances.
+TRAFFIC_BYTES_PER_INSTANCE = {"blend_fwd": 796.9e6 / 5274412, "blend_bwd": 689.4e6 / 5274412}
 
 
 def parse_args():
@@ -52,6 +56,8 @@ def parse_args():
     ap.add_argument("--points", type=int, default=N_POINTS)
     ap.add_argument("--tile", type=int, default=8)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--workload", default="config1", choices=["config1", "config2", "config4", "rows16", "rows32"],
+                    help="config1 is the headline (default); the others are single-GPU side measurements, one JSON line each")
     return ap.parse_args()
 
 
@@ -150,9 +156,9 @@ def build_workload(args, device):
 
 
 # ---------------------------------------------------------------------------------------------------
-def cpu_pipeline_points_per_s(n_points: int, threads: int) -> tuple[float, str]:
-    """The CPU restatement of the whole path on a bounded sample of the workload: one view, forward and
-    backward, `n_points` samples of the same octree and camera."""
+def cpu_pipeline_points_per_s(n_points: int, threads: int, n_views: int = 1) -> tuple[float, str]:
+    """The CPU restatement of the whole path on a bounded sample of the workload: `n_views` orbit views,
+    forward and backward, `n_points` samples per view of the same octree."""
     import numpy as np
     import torch
     sys.path.insert(0, str(ROOT / "oracle"))
@@ -160,10 +166,9 @@ def cpu_pipeline_points_per_s(n_points: int, threads: int) -> tuple[float, str]:
     from inpc_b200 import synthetic as syn
     os.environ["OMP_NUM_THREADS"] = str(threads)
     cfg = syn.config1(n_samples=n_points, n_leaves=N_LEAVES)
-    tree, view = cfg["tree"], cfg["view"]
-    c = view.camera
-    cam = O.Camera(view.w2c.numpy(), view.position.numpy(), c.width, c.height, c.focal_x, c.focal_y, c.center_x, c.center_y,
-                   c.near_plane, c.far_plane)
+    tree = cfg["tree"]
+    views = syn.config3_views(max(n_views, 1))
+    c = views[0].camera
     g = torch.Generator().manual_seed(5)
     gi = (torch.randn((4, c.height, c.width), generator=g) * 1e-3).numpy()
     ga = (torch.randn((1, c.height, c.width), generator=g) * 1e-3).numpy()
@@ -171,20 +176,26 @@ def cpu_pipeline_points_per_s(n_points: int, threads: int) -> tuple[float, str]:
     centers, levels, weights = tree.centers.numpy(), tree.levels.numpy(), tree.weights.numpy()
     O.lib()
     t0 = time.perf_counter()
-    vw = O.viewpoint_weights(cam, centers, levels, weights, tree.initial_size)
-    cdf, _ = O.build_cdf(vw)
-    pos, idx, _ = O.training_samples(cam, 0, 0, cdf, centers, levels, tree.initial_size, n_points)
-    st = O.rasterize_forward(O.BILINEAR, cam, pos, feats, opac, tile=16)
-    O.rasterize_backward(st, gi, ga)
+    for vi, view in enumerate(views[:max(n_views, 1)]):
+        cam = O.Camera(view.w2c.numpy(), view.position.numpy(), c.width, c.height, c.focal_x, c.focal_y, c.center_x, c.center_y,
+                       c.near_plane, c.far_plane)
+        vw = O.viewpoint_weights(cam, centers, levels, weights, tree.initial_size)
+        cdf, _ = O.build_cdf(vw)
+        pos, idx, _ = O.training_samples(cam, 0, vi, cdf, centers, levels, tree.initial_size, n_points)
+        st = O.rasterize_forward(O.BILINEAR, cam, pos, feats, opac, tile=16)
+        O.rasterize_backward(st, gi, ga)
     dt = time.perf_counter() - t0
-    return n_points / dt, f"1 view of the bench workload at {n_points} points (of {N_POINTS}), fwd+bwd, {dt:.1f} s"
+    return n_views * n_points / dt, f"{n_views} view(s) of the bench workload at {n_points} points per view (of {N_POINTS}), fwd+bwd, {dt:.1f} s"
 
 
 def cpu_baseline(args) -> dict:
     threads = os.cpu_count() or 1
     pps, _ = cpu_pipeline_points_per_s(1 << 17, threads)            # calibration run
-    n = int(min(max(pps * 12.0, 1 << 17), N_POINTS))                # about 12 s of CPU work, at most one full view
-    pps, sample = cpu_pipeline_points_per_s(n, threads)
+    budget_points = pps * 15.0                                      # about 15 s of CPU work
+    if budget_points >= 1.5 * N_POINTS:
+        pps, sample = cpu_pipeline_points_per_s(N_POINTS, threads, n_views=int(min(8, max(1, round(budget_points / N_POINTS)))))
+    else:
+        pps, sample = cpu_pipeline_points_per_s(int(min(max(budget_points, 1 << 17), N_POINTS)), threads)
     return {"value": pps / 1e6, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample}
 
 
@@ -319,7 +330,9 @@ def run_ours(args):
     dom_ms = stages[dominant][0] / views_timed
     achieved = alg[dominant] / (dom_ms * 1e-3) / 1e9 if dom_ms > 0 else 0.0
     roofline = {"bound": "hbm", "kernel": dominant, "achieved": achieved, "peak": peak_gbs, "unit": "GB/s",
-                "frac": achieved / peak_gbs if peak_gbs else None, "peak_source": peak_kind, "traffic": None,
+                "frac": achieved / peak_gbs if peak_gbs else None, "peak_source": peak_kind,
+                "traffic": TRAFFIC_BYTES_PER_INSTANCE[dominant] * mean_i if dominant in TRAFFIC_BYTES_PER_INSTANCE and args.tile == 8 else None,
+                "traffic_source": "ncu capture at 2^22 points scaled by the instance count",
                 "algorithmic_bytes_per_launch": alg[dominant], "launch_ms": dom_ms}
 
     line = {
@@ -438,8 +451,90 @@ def run_reference(args):
     print(json.dumps(base))
 
 
+# ---------------------------------------------------------------------------------------------------
+def run_side_workload(args):
+    """Single-GPU side measurements on the other synthetic configurations (device-timed, inputs resident):
+    config2  pre-extracted inference, 2^25 points, 1920x1080            -> frames/s
+    config4  skewed stress case, 2^24 points, 3840x2160, fwd+bwd        -> Mpoints/s
+    rows16 / rows32  config 1 with (N,C) fp32 feature rows, fwd+bwd incl. sampling -> Mpoints/s"""
+    import torch
+    import inpc_b200
+    from inpc_b200 import _cabi, synthetic as syn
+    from inpc_b200.sampling import ProbabilityFieldSampler
+    if int(os.environ.get("RANK", "0")) != 0:
+        return
+    device = torch.device("cuda", 0)
+    torch.cuda.set_device(device)
+    rast = inpc_b200.INPCRasterizer(tile_size=args.tile)
+    g = torch.Generator().manual_seed(5)
+    if args.workload == "config2":
+        c = syn.config2()
+        view, pos, feats, opac = c["view"].to(device), c["positions"].to(device), c["features"].to(device), c["opacities"].to(device)
+        n_points, unit, metric = pos.shape[0], "frames/s", "render_preextracted frames/s at 2^25 points, 1920x1080"
+
+        def step():
+            rast.render_preextracted(view, 0, pos, feats, opac)
+    elif args.workload == "config4":
+        c = syn.config4()
+        view, pos, feats, opac = c["view"].to(device), c["positions"].to(device), c["features"].to(device), c["opacities"].to(device)
+        H, W = view.camera.height, view.camera.width
+        gi, ga = (torch.randn((4, H, W), generator=g) * 1e-3).to(device), (torch.randn((1, H, W), generator=g) * 1e-3).to(device)
+        n_points, unit, metric = pos.shape[0], UNIT, "fwd+bwd Mpoints/s at 2^24 skewed points, 3840x2160"
+
+        def step():
+            f, o = feats.detach().requires_grad_(True), opac.detach().requires_grad_(True)
+            im, al, _ = rast(view, 0, pos, f, o)
+            torch.autograd.backward([im, al], [gi, ga])
+    else:
+        channels = 16 if args.workload == "rows16" else 32
+        c = syn.config1(n_samples=args.points, n_leaves=N_LEAVES)
+        view, tree, opac = c["view"].to(device), c["tree"].to(device), c["opacities"].to(device)
+        feats = (torch.randn((args.points, channels), generator=g) * 0.5).to(device)
+        H, W = view.camera.height, view.camera.width
+        gi, ga = (torch.randn((channels, H, W), generator=g) * 1e-3).to(device), (torch.randn((1, H, W), generator=g) * 1e-3).to(device)
+        sampler = ProbabilityFieldSampler(0)
+        n_points, unit, metric = args.points, UNIT, f"fwd+bwd Mpoints/s at 2^23 points per view, 1237x822, {channels} fp32 channels"
+
+        def step():
+            pos, _ = sampler.generate_training_samples(tree.centers, tree.levels, tree.weights, view, args.points, tree.initial_size)
+            f, o = feats.detach().requires_grad_(True), opac.detach().requires_grad_(True)
+            im, al, _ = rast.forward_rows(view, pos, f, o)
+            torch.autograd.backward([im, al], [gi, ga])
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    torch.cuda.synchronize()
+    _cabi.profile_read(reset=True)
+    _cabi.profile_enable(True)
+    launches0 = _cabi.launch_count()
+    clocks = ClockSampler(0)
+    reps = max(args.steps, 1) * 8
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(reps):
+        step()
+    stop.record()
+    torch.cuda.synchronize()
+    ms = start.elapsed_time(stop) / reps
+    clock_info = clocks.stop()
+    _cabi.profile_enable(False)
+    stages = {k: {"ms": v[0] / reps} for k, v in _cabi.profile_read(reset=True).items() if v[0] > 0}
+    value = 1e3 / ms if unit == "frames/s" else n_points / (ms * 1e-3) / 1e6
+    print(json.dumps({"metric": metric, "value": value, "unit": unit, "n_gpus": 1, "steps": reps, "warmup": max(args.warmup, 3), "ms_per_step": ms,
+                      "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+                      "config": {"workload": args.workload, "points": n_points, "tile": args.tile,
+                                 "l2": "inputs exceed the 126 MB L2; no flush needed"},
+                      "gpu_launches": _cabi.launch_count() - launches0, "clocks": clock_info, "stages": stages}))
+
+
 def main():
     args = parse_args()
+    if args.workload != "config1":
+        if args.impl == "reference":
+            print(json.dumps({"impl": "reference", "unavailable": "side workloads are measured for this build only"}))
+            return
+        run_side_workload(args)
+        return
     if args.impl == "reference":
         run_reference(args)
     else:

@@ -287,19 +287,21 @@ int inpc_cauchy_loss_backward(const float* grad, const float* input, const float
  * ---------------------------------------------------------------------------------------- */
 
 /* Per-leaf maximum and minimum of the blending weights of the samples drawn from each leaf, over any
- * number of views / ranks: reset once, accumulate per view, all-reduce max_sampled with MAX and
- * min_sampled with MIN across ranks (as int32: the buffers hold bit patterns of non-negative floats,
- * 0x7F7F7F7F in min_sampled meaning "no sample"), then apply inpc_leaf_update.  indices < 0 are skipped.
+ * number of views / ranks.  `stats` holds two uint32 per leaf, 8-byte aligned: {bit pattern of the
+ * maximum, 0x7FFFFFFF - bit pattern of the minimum}; weights are non-negative, so both words only grow
+ * and one MAX all-reduce of the int32 view of the whole buffer reduces it across ranks; all-zero means
+ * "no sample".  Reset once, accumulate per view, all-reduce, then apply inpc_leaf_update.
+ * indices < 0 are skipped.
  * Replaces the two scatter_reduce_ calls (amax / amin, include_self=False) of
  * Modules/ProbabilityField.py:152-155. */
-int inpc_leaf_stats_reset(float* max_sampled, float* min_sampled, int64_t n_leaves, void* stream);
-int inpc_leaf_stats_accumulate(const int64_t* indices, const float* weights, int64_t n, float* max_sampled,
-                               float* min_sampled, int64_t n_leaves, void* stream);
+int inpc_leaf_stats_reset(uint32_t* stats, int64_t n_leaves, void* stream);
+int inpc_leaf_stats_accumulate(const int64_t* indices, const float* weights, int64_t n, uint32_t* stats,
+                               int64_t n_leaves, void* stream);
 /* leaf_weights = max(leaf_weights * decay, max_sampled);
  * scores = max(scores * decay, clamp(max_sampled - min_sampled, 0, 1)); decay is 0.9968 in the reference.
  * Replaces Modules/ProbabilityField.py:148-149 and :156-157. */
-int inpc_leaf_update(float* leaf_weights, float* leaf_subdivision_scores, const float* max_sampled,
-                     const float* min_sampled, int64_t n_leaves, float decay, void* stream);
+int inpc_leaf_update(float* leaf_weights, float* leaf_subdivision_scores, const uint32_t* stats,
+                     int64_t n_leaves, float decay, void* stream);
 
 /* Structural updates of the octree probability field (the reference does them in torch:
  * Modules/ProbabilityField.py:159-165 prune, :217-257 subdivide).  Both are two calls: *_count

@@ -73,9 +73,9 @@ PROTOTYPES = {
     "inpc_cauchy_workspace_bytes": (_Z, [_L]),
     "inpc_cauchy_loss": (_I, [_P, _P, _L, _P, _P, _P]),
     "inpc_cauchy_loss_backward": (_I, [_P, _P, _P, _L, _P, _P]),
-    "inpc_leaf_stats_reset": (_I, [_P, _P, _L, _P]),
-    "inpc_leaf_stats_accumulate": (_I, [_P, _P, _L, _P, _P, _L, _P]),
-    "inpc_leaf_update": (_I, [_P, _P, _P, _P, _L, _F, _P]),
+    "inpc_leaf_stats_reset": (_I, [_P, _L, _P]),
+    "inpc_leaf_stats_accumulate": (_I, [_P, _P, _L, _P, _L, _P]),
+    "inpc_leaf_update": (_I, [_P, _P, _P, _L, _F, _P]),
     "inpc_compose_background": (_I, [_P, _P, _P, _I, _L, _P, _P]),
     "inpc_compose_background_backward": (_I, [_P, _P, _P, _I, _L, _P, _P, _P]),
     "inpc_multisample_accumulate": (_I, [_P, _P, _P, _P, _P, _P, _I, _L, _I, _I, _P]),

@@ -2,8 +2,8 @@
 
 A batch of camera views is split across ranks (rank r takes views r, r+G, r+2G, ...); each view's
 sample -> rasterize -> backward chain is independent and runs on the rank's own GPU.  Per batch the
-ranks exchange three buffers with one NCCL all-reduce each (over NVLink / NVSwitch; in-switch
-reduction when NCCL picks NVLS): the per-leaf max and min of the blending weights (MAX / MIN) that the
+ranks exchange two buffers with one NCCL all-reduce each (over NVLink / NVSwitch; in-switch
+reduction when NCCL picks NVLS): the packed per-leaf max / min of the blending weights (MAX) that the
 probability-field update consumes, and the gradient buffer of the appearance field (SUM).  The reference has no multi-GPU code (one view per optimizer step
 on one GPU); correctness here means: the reduced buffers equal what one GPU accumulates over the
 same views.
@@ -25,7 +25,7 @@ def partition_views(n_views: int, rank: int, world_size: int) -> list[int]:
 
 
 class BatchBuffers:
-    """What a batch exchanges: per-leaf max / min of the blending weights (reduced with MAX / MIN,
+    """What a batch exchanges: packed per-leaf max / min of the blending weights (reduced with MAX,
     exactly what the reference's `ProbabilityField.update` needs) and the appearance gradient buffer
     (reduced with SUM)."""
 
@@ -44,29 +44,40 @@ class BatchBuffers:
 
 
 class _HostLeafStatistics:
-    NO_SAMPLE = 0x7F7F7F7F
+    """CPU mirror of `probability_field.LeafStatistics` (same packed buffer) for the host-side tests of
+    the exchange logic."""
+    MIN_FLIP = 0x7FFFFFFF
 
     def __init__(self, n_leaves: int) -> None:
-        self.max_sampled = torch.zeros(n_leaves, dtype=torch.float32)
-        self.min_sampled = torch.full((n_leaves,), self.NO_SAMPLE, dtype=torch.int32).view(torch.float32)
+        self.stats = torch.zeros((n_leaves, 2), dtype=torch.int32)
+
+    @property
+    def max_sampled(self) -> torch.Tensor:
+        from .probability_field import decode_statistics
+        return decode_statistics(self.stats)[0]
+
+    @property
+    def min_sampled(self) -> torch.Tensor:
+        from .probability_field import decode_statistics
+        return decode_statistics(self.stats)[1]
 
     def reset(self) -> None:
-        self.max_sampled.zero_()
-        self.min_sampled.view(torch.int32).fill_(self.NO_SAMPLE)
+        self.stats.zero_()
 
     def accumulate(self, indices: torch.Tensor, weights: torch.Tensor) -> None:
         valid = indices >= 0
-        idx, w = indices[valid], weights.reshape(-1)[valid].clamp_min(0)
-        self.max_sampled.scatter_reduce_(0, idx, w, reduce="amax", include_self=True)
-        bits = self.min_sampled.view(torch.int32)
-        bits.scatter_reduce_(0, idx, w.view(torch.int32), reduce="amin", include_self=True)
+        idx = indices[valid]
+        bits = weights.reshape(-1)[valid].clamp_min(0).contiguous().view(torch.int32)
+        mx, flipped = self.stats[:, 0].clone(), self.stats[:, 1].clone()
+        mx.scatter_reduce_(0, idx, bits, reduce="amax", include_self=True)
+        flipped.scatter_reduce_(0, idx, self.MIN_FLIP - bits, reduce="amax", include_self=True)
+        self.stats[:, 0], self.stats[:, 1] = mx, flipped
 
     def all_reduce(self, group=None) -> None:
         import torch.distributed as dist
         if not (dist.is_available() and dist.is_initialized()) or dist.get_world_size(group) == 1:
             return
-        dist.all_reduce(self.max_sampled.view(torch.int32), op=dist.ReduceOp.MAX, group=group)
-        dist.all_reduce(self.min_sampled.view(torch.int32), op=dist.ReduceOp.MIN, group=group)
+        dist.all_reduce(self.stats, op=dist.ReduceOp.MAX, group=group)
 
 
 def accumulate_view(buffers: BatchBuffers, leaf_indices: torch.Tensor, blending_weights: torch.Tensor,
@@ -85,7 +96,7 @@ def accumulate_view(buffers: BatchBuffers, leaf_indices: torch.Tensor, blending_
 
 
 def allreduce_buffers(buffers: BatchBuffers, group=None) -> None:
-    """The one exchange step of a batch: MAX / MIN of the leaf statistics, SUM of the appearance buffer."""
+    """The one exchange step of a batch: MAX of the packed leaf statistics, SUM of the appearance buffer."""
     import torch.distributed as dist
     if not (dist.is_available() and dist.is_initialized()) or dist.get_world_size(group) == 1:
         return

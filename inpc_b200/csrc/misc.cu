@@ -142,32 +142,36 @@ constexpr int kCauchyMaxBlocks = 148 * 8;
 
 // ---- per-leaf statistics of one step and the occupancy update (Modules/ProbabilityField.py:146-157) ----
 // Blending weights are non-negative, so their bit patterns order like the values and integer atomic
-// max / min reduce them exactly and in any order.  An untouched leaf keeps max = 0 and min = the
-// "no sample" marker 0xFFFFFFFF, which the update reads as 0 (scatter_reduce with include_self=False
-// on a zero tensor).
-constexpr unsigned kNoSample = 0xFFFFFFFFu;
+// max reduces them exactly and in any order.  One 8-byte word per leaf {x: bits of the maximum,
+// y: 0x7FFFFFFF - bits of the minimum}: both halves only ever grow, both reduce with MAX (also
+// across ranks, as int32), one 8-byte read fetches both, and all-zero means "no sample", which the
+// update reads as max = min = 0 (scatter_reduce with include_self=False on a zero tensor).
+constexpr unsigned kMinFlip = 0x7FFFFFFFu;
 
 __global__ void __launch_bounds__(kThreads) leaf_stats_kernel(const long long* __restrict__ indices, const float* __restrict__ weights,
-                                                              int64_t n, int64_t n_leaves, unsigned* __restrict__ max_bits,
-                                                              unsigned* __restrict__ min_bits) {
+                                                              int64_t n, int64_t n_leaves, uint2* __restrict__ stats) {
     const int64_t stride = (int64_t)gridDim.x * kThreads;
     for (int64_t i = (int64_t)blockIdx.x * kThreads + threadIdx.x; i < n; i += stride) {
         const long long leaf = __ldg(indices + i);
         if (leaf < 0 || leaf >= n_leaves) continue;
         const unsigned bits = __float_as_uint(fmaxf(__ldg(weights + i), 0.0f));
-        atomicMax(max_bits + leaf, bits);
-        atomicMin(min_bits + leaf, bits);
+        const unsigned flipped = kMinFlip - bits;
+        // Both halves only grow, so a value that does not beat what a plain (possibly stale) read
+        // returns cannot beat the current one either: most samples of a leaf that has already seen a
+        // few skip both atomics.
+        const uint2 cur = __ldcg(stats + leaf);
+        if (bits > cur.x) atomicMax(&stats[leaf].x, bits);
+        if (flipped > cur.y) atomicMax(&stats[leaf].y, flipped);
     }
 }
 
 __global__ void __launch_bounds__(kThreads) leaf_update_kernel(float* __restrict__ leaf_weights, float* __restrict__ scores,
-                                                               const unsigned* __restrict__ max_bits, const unsigned* __restrict__ min_bits,
-                                                               int64_t n_leaves, float decay) {
+                                                               const uint2* __restrict__ stats, int64_t n_leaves, float decay) {
     const int64_t stride = (int64_t)gridDim.x * kThreads;
     for (int64_t l = (int64_t)blockIdx.x * kThreads + threadIdx.x; l < n_leaves; l += stride) {
-        const float mx = __uint_as_float(__ldg(max_bits + l));
-        const unsigned mn_bits = __ldg(min_bits + l);
-        const float mn = mn_bits == kNoSample ? 0.0f : __uint_as_float(mn_bits);
+        const uint2 st = __ldg(stats + l);
+        const float mx = __uint_as_float(st.x);
+        const float mn = st.y == 0u ? 0.0f : __uint_as_float(kMinFlip - st.y);
         leaf_weights[l] = fmaxf(leaf_weights[l] * decay, mx);
         scores[l] = fmaxf(scores[l] * decay, __saturatef(mx - mn));
     }
@@ -303,33 +307,35 @@ extern "C" int inpc_cauchy_loss_backward(const float* grad, const float* input, 
     return INPC_OK;
 }
 
-extern "C" int inpc_leaf_stats_reset(float* max_sampled, float* min_sampled, int64_t n_leaves, void* stream_) {
+extern "C" int inpc_leaf_stats_reset(uint32_t* stats, int64_t n_leaves, void* stream_) {
     if (n_leaves == 0) return INPC_OK;
-    if (n_leaves < 0 || !max_sampled || !min_sampled) { set_error("inpc_leaf_stats_reset: bad argument"); return INPC_E_INVALID; }
-    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
-    INPC_CUDA_TRY(cudaMemsetAsync(max_sampled, 0, sizeof(float) * (size_t)n_leaves, stream));
-    INPC_CUDA_TRY(cudaMemsetAsync(min_sampled, 0x7F, sizeof(float) * (size_t)n_leaves, stream));
+    if (n_leaves < 0 || !stats) { set_error("inpc_leaf_stats_reset: bad argument"); return INPC_E_INVALID; }
+    INPC_CUDA_TRY(cudaMemsetAsync(stats, 0, 2 * sizeof(uint32_t) * (size_t)n_leaves, static_cast<cudaStream_t>(stream_)));
     return INPC_OK;
 }
 
-extern "C" int inpc_leaf_stats_accumulate(const int64_t* indices, const float* weights, int64_t n, float* max_sampled,
-                                          float* min_sampled, int64_t n_leaves, void* stream_) {
+extern "C" int inpc_leaf_stats_accumulate(const int64_t* indices, const float* weights, int64_t n, uint32_t* stats, int64_t n_leaves,
+                                          void* stream_) {
     if (n == 0) return INPC_OK;
-    if (n < 0 || n_leaves <= 0 || !indices || !weights || !max_sampled || !min_sampled) { set_error("inpc_leaf_stats_accumulate: bad argument"); return INPC_E_INVALID; }
-    leaf_stats_kernel<<<grid_for(n), kThreads, 0, static_cast<cudaStream_t>(stream_)>>>(
-        reinterpret_cast<const long long*>(indices), weights, n, n_leaves, reinterpret_cast<unsigned*>(max_sampled),
-        reinterpret_cast<unsigned*>(min_sampled));
+    if (n < 0 || n_leaves <= 0 || !indices || !weights || !stats || (reinterpret_cast<uintptr_t>(stats) & 7u)) {
+        set_error("inpc_leaf_stats_accumulate: bad argument");
+        return INPC_E_INVALID;
+    }
+    leaf_stats_kernel<<<grid_for(n), kThreads, 0, static_cast<cudaStream_t>(stream_)>>>(reinterpret_cast<const long long*>(indices), weights, n, n_leaves,
+                                                                                     reinterpret_cast<uint2*>(stats));
     INPC_LAUNCH_CHECK("leaf_stats_kernel");
     return INPC_OK;
 }
 
-extern "C" int inpc_leaf_update(float* leaf_weights, float* leaf_subdivision_scores, const float* max_sampled,
-                                const float* min_sampled, int64_t n_leaves, float decay, void* stream_) {
+extern "C" int inpc_leaf_update(float* leaf_weights, float* leaf_subdivision_scores, const uint32_t* stats, int64_t n_leaves, float decay,
+                                void* stream_) {
     if (n_leaves == 0) return INPC_OK;
-    if (n_leaves < 0 || !leaf_weights || !leaf_subdivision_scores || !max_sampled || !min_sampled) { set_error("inpc_leaf_update: bad argument"); return INPC_E_INVALID; }
-    leaf_update_kernel<<<grid_for(n_leaves), kThreads, 0, static_cast<cudaStream_t>(stream_)>>>(
-        leaf_weights, leaf_subdivision_scores, reinterpret_cast<const unsigned*>(max_sampled),
-        reinterpret_cast<const unsigned*>(min_sampled), n_leaves, decay);
+    if (n_leaves < 0 || !leaf_weights || !leaf_subdivision_scores || !stats || (reinterpret_cast<uintptr_t>(stats) & 7u)) {
+        set_error("inpc_leaf_update: bad argument");
+        return INPC_E_INVALID;
+    }
+    leaf_update_kernel<<<grid_for(n_leaves), kThreads, 0, static_cast<cudaStream_t>(stream_)>>>(leaf_weights, leaf_subdivision_scores,
+                                                                                             reinterpret_cast<const uint2*>(stats), n_leaves, decay);
     INPC_LAUNCH_CHECK("leaf_update_kernel");
     return INPC_OK;
 }

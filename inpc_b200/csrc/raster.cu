@@ -590,6 +590,51 @@ __device__ __forceinline__ uint32_t stage_instance(int j, int cnt, unsigned base
     return id;
 }
 
+// The same staging split in two, so that a batch's loads can be in flight while the batch before it is
+// walked: `fetch` only issues the loads (instance id, then the record it names: two dependent trips to
+// memory), `commit` writes the values to shared memory and sets the mask bits.
+template <bool NEED_F>
+struct Fetched {
+    uint32_t id;
+    float4 a, f;
+};
+
+template <bool NEED_F>
+__device__ __forceinline__ Fetched<NEED_F> fetch_instance(int j, int cnt, unsigned base, const uint32_t* __restrict__ inst_ids,
+                                                          const PointRec* __restrict__ rec) {
+    Fetched<NEED_F> r;
+    r.id = 0;
+    r.a = make_float4(0.f, 0.f, 0.f, 0.f);
+    r.f = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (j < cnt) {
+        r.id = __ldg(inst_ids + base + j);
+        const float4* p = reinterpret_cast<const float4*>(rec + r.id);
+        r.a = __ldg(p);
+        if (NEED_F) r.f = __ldg(p + 1);
+    }
+    return r;
+}
+
+template <int T, bool NEED_F>
+__device__ __forceinline__ void commit_instance(int j, int cnt, const Fetched<NEED_F>& r, int tile_x, int tile_y, float4* s_a, float4* s_f,
+                                                unsigned (*s_mask)[T * T]) {
+    if (j < cnt) {
+        s_a[j] = r.a;
+        if (NEED_F) s_f[j] = r.f;
+        const int qx = __float2int_rd(r.a.x - 0.5f) - tile_x * T;
+        const int qy = __float2int_rd(r.a.y - 0.5f) - tile_y * T;
+        const unsigned bit = 1u << (j & 31);
+        unsigned* mrow = s_mask[j >> 5];
+#pragma unroll
+        for (int dy = 0; dy < 2; ++dy)
+#pragma unroll
+            for (int dx = 0; dx < 2; ++dx) {
+                const int cx = qx + dx, cy = qy + dy;
+                if (cx >= 0 && cx < T && cy >= 0 && cy < T) atomicOr(mrow + cy * T + cx, bit);
+            }
+    }
+}
+
 // Pass 1 (tiles with several segments only): per-pixel product of (1 - alpha) over one segment.
 // A block is one (tile, segment): T*T threads = pixels, batches of B = T*T*IPT instances.
 template <int T, int IPT>
@@ -616,10 +661,29 @@ __global__ void __launch_bounds__(T * T) blend_bilinear_transmittance_kernel(
     __syncthreads();
     float Tr = 1.0f;
     bool done = !inside;
-    for (unsigned base = sg.begin; base < sg.end; base += B) {
-        const int cnt = (int)min((unsigned)B, sg.end - base);
+    // With 8x8 tiles the next batch's loads are issued before the current batch is walked (measured 3 %
+    // faster); with 16x16 tiles the extra registers cost more than the overlap gains.
+    constexpr bool kPrefetch = T == 8;
+    Fetched<false> next[IPT];
+    int cnt_next = (int)min((unsigned)B, sg.end - sg.begin);
+    if (kPrefetch) {
 #pragma unroll
-        for (int k = 0; k < IPT; ++k) stage_instance<T, B, false>(t + k * P, cnt, base, inst_ids, rec, tx, ty, s_a, nullptr, s_mask);
+        for (int k = 0; k < IPT; ++k) next[k] = fetch_instance<false>(t + k * P, cnt_next, sg.begin, inst_ids, rec);
+    }
+    for (unsigned base = sg.begin; base < sg.end; base += B) {
+        if (!kPrefetch) {
+            cnt_next = (int)min((unsigned)B, sg.end - base);
+#pragma unroll
+            for (int k = 0; k < IPT; ++k) next[k] = fetch_instance<false>(t + k * P, cnt_next, base, inst_ids, rec);
+        }
+        const int cnt = cnt_next;
+#pragma unroll
+        for (int k = 0; k < IPT; ++k) commit_instance<T, false>(t + k * P, cnt, next[k], tx, ty, s_a, nullptr, s_mask);
+        if (kPrefetch) {
+            cnt_next = base + B < sg.end ? (int)min((unsigned)B, sg.end - (base + B)) : 0;
+#pragma unroll
+            for (int k = 0; k < IPT; ++k) next[k] = fetch_instance<false>(t + k * P, cnt_next, base + B, inst_ids, rec);
+        }
         __syncthreads();
 #pragma unroll 1
         for (int w = 0; w < WORDS; ++w) {
@@ -721,11 +785,33 @@ __global__ void __launch_bounds__(T * T) blend_bilinear_forward_kernel(
             }
         }
     };
+    // With 8x8 tiles the next batch's loads are issued before the current batch is walked (measured 3 %
+    // faster); with 16x16 tiles the extra registers cost more than the overlap gains.
+    constexpr bool kPrefetch = T == 8;
+    Fetched<true> next[IPT];
+    int cnt_next = (int)min((unsigned)B, sg.end - sg.begin);
+    if (kPrefetch) {
+#pragma unroll
+        for (int k = 0; k < IPT; ++k) next[k] = fetch_instance<true>(t + k * P, cnt_next, sg.begin, inst_ids, rec);
+    }
     for (unsigned base = sg.begin; base < sg.end; base += B) {
         if (KIND == BLEND_TRAIN) flush_weights();
-        cnt = (int)min((unsigned)B, sg.end - base);
+        if (!kPrefetch) {
+            cnt_next = (int)min((unsigned)B, sg.end - base);
 #pragma unroll
-        for (int k = 0; k < IPT; ++k) id[k] = stage_instance<T, B, true>(t + k * P, cnt, base, inst_ids, rec, tx, ty, s_a, s_f, s_mask);
+            for (int k = 0; k < IPT; ++k) next[k] = fetch_instance<true>(t + k * P, cnt_next, base, inst_ids, rec);
+        }
+        cnt = cnt_next;
+#pragma unroll
+        for (int k = 0; k < IPT; ++k) {
+            id[k] = next[k].id;
+            commit_instance<T, true>(t + k * P, cnt, next[k], tx, ty, s_a, s_f, s_mask);
+        }
+        if (kPrefetch) {
+            cnt_next = base + B < sg.end ? (int)min((unsigned)B, sg.end - (base + B)) : 0;
+#pragma unroll
+            for (int k = 0; k < IPT; ++k) next[k] = fetch_instance<true>(t + k * P, cnt_next, base + B, inst_ids, rec);
+        }
         __syncthreads();
 #pragma unroll 1
         for (int w = 0; w < WORDS; ++w) {
@@ -916,11 +1002,33 @@ __global__ void __launch_bounds__(T * T) blend_bilinear_backward_kernel(
             }
         }
     };
+    // With 8x8 tiles the next batch's loads are issued before the current batch is walked (measured 3 %
+    // faster); with 16x16 tiles the extra registers cost more than the overlap gains.
+    constexpr bool kPrefetch = T == 8;
+    Fetched<true> next[IPT];
+    int cnt_next = (int)min((unsigned)B, sg.end - sg.begin);
+    if (kPrefetch) {
+#pragma unroll
+        for (int k = 0; k < IPT; ++k) next[k] = fetch_instance<true>(t + k * P, cnt_next, sg.begin, inst_ids, rec);
+    }
     for (unsigned base = sg.begin; base < sg.end; base += B) {
         flush_gradients();
-        cnt = (int)min((unsigned)B, sg.end - base);
+        if (!kPrefetch) {
+            cnt_next = (int)min((unsigned)B, sg.end - base);
 #pragma unroll
-        for (int k = 0; k < IPT; ++k) id[k] = stage_instance<T, B, true>(t + k * P, cnt, base, inst_ids, rec, tx, ty, s_a, s_f, s_mask);
+            for (int k = 0; k < IPT; ++k) next[k] = fetch_instance<true>(t + k * P, cnt_next, base, inst_ids, rec);
+        }
+        cnt = cnt_next;
+#pragma unroll
+        for (int k = 0; k < IPT; ++k) {
+            id[k] = next[k].id;
+            commit_instance<T, true>(t + k * P, cnt, next[k], tx, ty, s_a, s_f, s_mask);
+        }
+        if (kPrefetch) {
+            cnt_next = base + B < sg.end ? (int)min((unsigned)B, sg.end - (base + B)) : 0;
+#pragma unroll
+            for (int k = 0; k < IPT; ++k) next[k] = fetch_instance<true>(t + k * P, cnt_next, base + B, inst_ids, rec);
+        }
         __syncthreads();
 #pragma unroll 1
         for (int w = 0; w < WORDS; ++w) {

@@ -15,19 +15,38 @@ from .rasterization import _cuda_f32, _ptr, _stream
 DECAY = 0.9968
 
 
+MIN_FLIP = 0x7FFFFFFF
+
+
+def decode_statistics(stats: torch.Tensor):
+    """(max_sampled, min_sampled) as float tensors from a packed (L,2) int32 statistics buffer; leaves
+    without a sample read 0 / 0, as the update treats them."""
+    mx = stats[:, 0].contiguous().view(torch.float32)
+    flipped = stats[:, 1]
+    mn = (MIN_FLIP - flipped).to(torch.int32).contiguous().view(torch.float32)
+    return mx, torch.where(flipped == 0, torch.zeros_like(mn), mn)
+
+
 class LeafStatistics:
-    """Running per-leaf max / min of blending weights.  The two buffers hold the bit patterns of
-    non-negative floats, so `MAX` / `MIN` all-reduces of their int32 views reduce them exactly."""
+    """Running per-leaf max / min of blending weights.  One (L,2) int32 buffer: {bit pattern of the
+    maximum, 0x7FFFFFFF - bit pattern of the minimum}.  Weights are non-negative, so both columns only
+    grow and a single `MAX` all-reduce reduces the buffer across ranks exactly; zero = no sample."""
 
     def __init__(self, n_leaves: int, device) -> None:
-        self.max_sampled = torch.empty(n_leaves, dtype=torch.float32, device=device)
-        self.min_sampled = torch.empty(n_leaves, dtype=torch.float32, device=device)
+        self.stats = torch.empty((n_leaves, 2), dtype=torch.int32, device=device)
         self.reset()
 
+    @property
+    def max_sampled(self) -> torch.Tensor:
+        return decode_statistics(self.stats)[0]
+
+    @property
+    def min_sampled(self) -> torch.Tensor:
+        return decode_statistics(self.stats)[1]
+
     def reset(self) -> None:
-        with torch.cuda.device(self.max_sampled.device):
-            _cabi.check(_cabi.lib().inpc_leaf_stats_reset(_ptr(self.max_sampled), _ptr(self.min_sampled),
-                                                          self.max_sampled.numel(), _stream()))
+        with torch.cuda.device(self.stats.device):
+            _cabi.check(_cabi.lib().inpc_leaf_stats_reset(_ptr(self.stats), self.stats.shape[0], _stream()))
 
     def accumulate(self, indices: torch.Tensor, weights: torch.Tensor) -> None:
         if not indices.is_cuda or indices.dtype != torch.int64:
@@ -36,18 +55,15 @@ class LeafStatistics:
         indices = indices.contiguous()
         if indices.numel() != weights.numel():
             raise ValueError("indices and weights must have the same number of elements")
-        with torch.cuda.device(self.max_sampled.device):
-            _cabi.check(_cabi.lib().inpc_leaf_stats_accumulate(_ptr(indices), _ptr(weights), indices.numel(),
-                                                               _ptr(self.max_sampled), _ptr(self.min_sampled),
-                                                               self.max_sampled.numel(), _stream()))
+        with torch.cuda.device(self.stats.device):
+            _cabi.check(_cabi.lib().inpc_leaf_stats_accumulate(_ptr(indices), _ptr(weights), indices.numel(), _ptr(self.stats),
+                                                               self.stats.shape[0], _stream()))
 
     def all_reduce(self, group=None) -> None:
         import torch.distributed as dist
         if not (dist.is_available() and dist.is_initialized()) or dist.get_world_size(group) == 1:
             return
-        # bit patterns of non-negative floats order like int32; the "no sample" marker is the largest
-        dist.all_reduce(self.max_sampled.view(torch.int32), op=dist.ReduceOp.MAX, group=group)
-        dist.all_reduce(self.min_sampled.view(torch.int32), op=dist.ReduceOp.MIN, group=group)
+        dist.all_reduce(self.stats, op=dist.ReduceOp.MAX, group=group)
 
 
 def update(leaf_weights: torch.Tensor, leaf_subdivision_scores: torch.Tensor, stats: LeafStatistics,
@@ -57,8 +73,8 @@ def update(leaf_weights: torch.Tensor, leaf_subdivision_scores: torch.Tensor, st
         if not t.is_cuda or t.dtype != torch.float32 or not t.is_contiguous():
             raise TypeError(f"{name} must be a contiguous CUDA float32 tensor")
     with torch.cuda.device(leaf_weights.device):
-        _cabi.check(_cabi.lib().inpc_leaf_update(_ptr(leaf_weights), _ptr(leaf_subdivision_scores), _ptr(stats.max_sampled),
-                                                 _ptr(stats.min_sampled), leaf_weights.numel(), float(decay), _stream()))
+        _cabi.check(_cabi.lib().inpc_leaf_update(_ptr(leaf_weights), _ptr(leaf_subdivision_scores), _ptr(stats.stats),
+                                                 leaf_weights.numel(), float(decay), _stream()))
 
 
 def update_from_samples(leaf_weights: torch.Tensor, leaf_subdivision_scores: torch.Tensor, indices: torch.Tensor,
