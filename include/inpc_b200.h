@@ -351,6 +351,31 @@ int inpc_multisample_resolve(float* acc_image, float* acc_depth, float* acc_alph
                              const float* background, int channels, int64_t n_pixels, int n_multisamples,
                              int remultiply, void* stream);
 
+/* Global point cloud extraction (Modules/ProbabilityField.py:121-144, utils.py:36-64).
+ *   inpc_draw_leaf_counts  counts[leaf] = how many of n_samples multinomial draws (with replacement,
+ *                          probability proportional to weights) fell into the leaf; replaces
+ *                          torch.multinomial + torch.bincount (ProbabilityField.py:129-130) with the
+ *                          sampler's Philox stream.  Synchronises the stream once (zero-sum check).
+ *   inpc_halton_samples    n_total = sum(counts) positions, leaf by leaf: the h-th sample of a leaf is
+ *                          centre - cell/2 + halton(h + 1; bases 2, 3, 5) * cell, a leaf with one
+ *                          sample puts it at its centre; bit-identical to compute_halton_coords +
+ *                          ProbabilityField.py:131-140 (the Halton elements are formed in double
+ *                          precision and stored as float32 as there).
+ *   inpc_morton_order      out = positions sorted by a 30-bit Morton code (10 bits per axis) inside
+ *                          the cube [box_lo, box_lo + box_extent]^3 (box_lo: 3 HOST floats); stable.
+ *                          Stands in for NeRFICG's CudaUtils.MortonEncoding.morton_encode + argsort
+ *                          (ProbabilityField.py:141-143), which is not part of the reference tree:
+ *                          the code width and the box are this library's choice.
+ * `workspace`: inpc_sampler_workspace_bytes(n_cells) for the first two, inpc_morton_workspace_bytes(n)
+ * for the third. */
+int inpc_draw_leaf_counts(inpc_sampler* s, int64_t n_cells, const float* weights, int64_t n_samples,
+                          uint32_t* counts, void* workspace, void* stream);
+int inpc_halton_samples(const uint32_t* counts, int64_t n_cells, const float* centers, const int32_t* levels,
+                        float initial_size, int64_t n_total, float* positions, void* workspace, void* stream);
+size_t inpc_morton_workspace_bytes(int64_t n);
+int inpc_morton_order(const float* positions, int64_t n, const float* box_lo, float box_extent, float* out,
+                      void* workspace, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

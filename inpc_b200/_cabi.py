@@ -76,6 +76,10 @@ PROTOTYPES = {
     "inpc_leaf_stats_reset": (_I, [_P, _L, _P]),
     "inpc_leaf_stats_accumulate": (_I, [_P, _P, _L, _P, _L, _P]),
     "inpc_leaf_update": (_I, [_P, _P, _P, _L, _F, _P]),
+    "inpc_draw_leaf_counts": (_I, [_P, _L, _P, _L, _P, _P, _P]),
+    "inpc_halton_samples": (_I, [_P, _L, _P, _P, _F, _L, _P, _P, _P]),
+    "inpc_morton_workspace_bytes": (_Z, [_L]),
+    "inpc_morton_order": (_I, [_P, _L, C.POINTER(C.c_float), _F, _P, _P, _P]),
     "inpc_compose_background": (_I, [_P, _P, _P, _I, _L, _P, _P]),
     "inpc_compose_background_backward": (_I, [_P, _P, _P, _I, _L, _P, _P, _P]),
     "inpc_multisample_accumulate": (_I, [_P, _P, _P, _P, _P, _P, _I, _L, _I, _I, _P]),

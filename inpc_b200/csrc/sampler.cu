@@ -420,6 +420,100 @@ __global__ void __launch_bounds__(kThreads) expected_samples_kernel(unsigned lon
     positions[3 * i + 2] = fmaf(d.jz - 0.5f, scale, __ldg(centers + 3 * (int64_t)leaf + 2));
 }
 
+// ---- global point cloud: Modules/ProbabilityField.py:121-144 + utils.py:36-64 -----------------------
+// counts[leaf] = number of the n multinomial draws that fell into the leaf (torch.multinomial +
+// bincount in the reference; here the library's own Philox stream, one draw per slot)
+__global__ void __launch_bounds__(kThreads) leaf_histogram_kernel(unsigned long long seed, unsigned long long call,
+                                                                  const float* __restrict__ cdf, const unsigned* __restrict__ guide,
+                                                                  int guide_bits, unsigned n_cells, int64_t n_samples,
+                                                                  unsigned* __restrict__ counts) {
+    const int64_t s = (int64_t)blockIdx.x * kThreads + threadIdx.x;
+    if (s >= n_samples) return;
+    const Draw d = philox_draw(seed, call, (unsigned)s, 0u);
+    atomicAdd(counts + guided_lower_bound(cdf, guide, guide_bits, d.raw_u, d.u, n_cells), 1u);
+}
+
+// Element `index` (1-based) of the Halton sequence in `base`, with the reference's arithmetic
+// (utils.py:36-46): double precision, one rounding per product, sum and division; the value is then
+// stored as float32 (utils.py:52-55).
+__device__ __forceinline__ float halton_element(unsigned index, unsigned base) {
+    double result = 0.0;
+    double f = __ddiv_rn(1.0, (double)base);
+    unsigned i = index;
+    while (i > 0u) {
+        result = __dadd_rn(result, __dmul_rn(f, (double)(i % base)));
+        i /= base;
+        f = __ddiv_rn(f, (double)base);
+    }
+    return __double2float_rn(result);
+}
+
+// Sample i lies in leaf upper_bound(offsets, i) and is that leaf's h-th sample, h = i - first sample
+// of the leaf: Halton point h+1 in bases (2, 3, 5) scaled into the cell; a leaf with a single sample
+// puts it at its centre (ProbabilityField.py:131-140).
+__global__ void __launch_bounds__(kThreads) halton_samples_kernel(const unsigned* __restrict__ counts, const unsigned* __restrict__ offsets,
+                                                                  unsigned n_cells, const float* __restrict__ centers,
+                                                                  const int* __restrict__ levels, float initial_size, int64_t n_total,
+                                                                  float* __restrict__ positions) {
+    const int64_t i = (int64_t)blockIdx.x * kThreads + threadIdx.x;
+    if (i >= n_total) return;
+    unsigned first = 0, count = n_cells;
+    while (count > 0) {
+        const unsigned step = count >> 1;
+        if (__ldg(offsets + first + step) <= (unsigned)i) { first += step + 1; count -= step + 1; }
+        else count = step;
+    }
+    const unsigned leaf = min(first, n_cells - 1);
+    const unsigned c = __ldg(counts + leaf);
+    const unsigned h = (unsigned)i - (__ldg(offsets + leaf) - c);
+    const float cx = __ldg(centers + 3 * (int64_t)leaf), cy = __ldg(centers + 3 * (int64_t)leaf + 1), cz = __ldg(centers + 3 * (int64_t)leaf + 2);
+    if (c == 1u) {
+        positions[3 * i] = cx; positions[3 * i + 1] = cy; positions[3 * i + 2] = cz;
+        return;
+    }
+    // cell edge = initial_size / 2^level, exact in fp32 for the levels an octree has; every further
+    // operation rounds on its own like the torch expression  centre - cell/2 + halton * cell
+    const float cell = __fdiv_rn(initial_size, (float)(1u << __ldg(levels + leaf)));
+    const float half = __fmul_rn(cell, 0.5f);
+    positions[3 * i] = __fadd_rn(__fsub_rn(cx, half), __fmul_rn(halton_element(h + 1u, 2u), cell));
+    positions[3 * i + 1] = __fadd_rn(__fsub_rn(cy, half), __fmul_rn(halton_element(h + 1u, 3u), cell));
+    positions[3 * i + 2] = __fadd_rn(__fsub_rn(cz, half), __fmul_rn(halton_element(h + 1u, 5u), cell));
+}
+
+// 30-bit Morton code (10 bits per axis, x lowest) of a position inside the box [lo, lo + extent]^3
+__device__ __forceinline__ unsigned spread_bits_10(unsigned v) {
+    v &= 0x3FFu;
+    v = (v | (v << 16)) & 0x030000FFu;
+    v = (v | (v << 8)) & 0x0300F00Fu;
+    v = (v | (v << 4)) & 0x030C30C3u;
+    v = (v | (v << 2)) & 0x09249249u;
+    return v;
+}
+
+__global__ void __launch_bounds__(kThreads) morton_codes_kernel(const float* __restrict__ positions, int64_t n, float lo_x, float lo_y,
+                                                                float lo_z, float inv_extent, unsigned* __restrict__ codes,
+                                                                unsigned* __restrict__ order) {
+    const int64_t i = (int64_t)blockIdx.x * kThreads + threadIdx.x;
+    if (i >= n) return;
+    const float qx = (__ldg(positions + 3 * i) - lo_x) * inv_extent * 1024.0f;
+    const float qy = (__ldg(positions + 3 * i + 1) - lo_y) * inv_extent * 1024.0f;
+    const float qz = (__ldg(positions + 3 * i + 2) - lo_z) * inv_extent * 1024.0f;
+    const unsigned x = (unsigned)fminf(fmaxf(qx, 0.0f), 1023.0f), y = (unsigned)fminf(fmaxf(qy, 0.0f), 1023.0f),
+                   z = (unsigned)fminf(fmaxf(qz, 0.0f), 1023.0f);
+    codes[i] = spread_bits_10(x) | (spread_bits_10(y) << 1) | (spread_bits_10(z) << 2);
+    order[i] = (unsigned)i;
+}
+
+__global__ void __launch_bounds__(kThreads) gather_positions_kernel(const float* __restrict__ positions, const unsigned* __restrict__ order,
+                                                                    int64_t n, float* __restrict__ out) {
+    const int64_t i = (int64_t)blockIdx.x * kThreads + threadIdx.x;
+    if (i >= n) return;
+    const int64_t j = __ldg(order + i);
+    out[3 * i] = __ldg(positions + 3 * j);
+    out[3 * i + 1] = __ldg(positions + 3 * j + 1);
+    out[3 * i + 2] = __ldg(positions + 3 * j + 2);
+}
+
 struct SamplerWs {
     float* vw;          // viewpoint weights (n_cells)
     float* cdf;         // (n_cells)
@@ -658,5 +752,91 @@ extern "C" int inpc_generate_expected_samples_fill(inpc_sampler* s, int64_t n_ce
         s->seed, s->counter, w.offsets, (unsigned)n_cells, centers, levels, initial_size, total, (unsigned)n_created, positions);
     INPC_LAUNCH_CHECK("expected_samples_kernel");
     s->counter += 1;
+    return INPC_OK;
+}
+
+namespace {
+// inclusive offsets of w.counts into w.offsets
+int scan_counts(const SamplerWs& w, int64_t n_cells, cudaStream_t stream) {
+    const unsigned blocks = (unsigned)ceil_div<int64_t>(n_cells, kThreads);
+    count_chunk_sums_kernel<<<blocks, kThreads, 0, stream>>>(w.counts, n_cells, w.chunk_sums);
+    INPC_LAUNCH_CHECK("count_chunk_sums_kernel");
+    scan_chunk_sums_kernel<<<1, kIScanThreads, 0, stream>>>(w.chunk_sums, blocks, w.total);
+    INPC_LAUNCH_CHECK("scan_chunk_sums_kernel");
+    count_offsets_kernel<<<blocks, kThreads, 0, stream>>>(w.counts, n_cells, w.chunk_sums, w.offsets);
+    INPC_LAUNCH_CHECK("count_offsets_kernel");
+    return INPC_OK;
+}
+}  // namespace
+
+extern "C" int inpc_draw_leaf_counts(inpc_sampler* s, int64_t n_cells, const float* weights, int64_t n_samples, uint32_t* counts,
+                                     void* workspace, void* stream_) {
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    if (!s || n_cells <= 0 || n_cells >= ((int64_t)1 << 31) || n_samples < 0 || n_samples >= ((int64_t)1 << 32) || !weights || !counts || !workspace) {
+        set_error("inpc_draw_leaf_counts: bad argument");
+        return INPC_E_INVALID;
+    }
+    SamplerWs w = carve_sampler_ws(workspace, n_cells);
+    int rc = build_cdf(weights, n_cells, w.cdf, w.sum, w, stream);
+    if (rc != INPC_OK) return rc;
+    INPC_CUDA_TRY(cudaMemsetAsync(counts, 0, sizeof(uint32_t) * (size_t)n_cells, stream));
+    float* host = pinned_float();
+    if (!host) return cuda_fail(cudaGetLastError(), "cudaHostAlloc");
+    INPC_CUDA_TRY(cudaMemcpyAsync(host, w.sum, sizeof(float), cudaMemcpyDeviceToHost, stream));
+    INPC_CUDA_TRY(cudaStreamSynchronize(stream));
+    if (!(host[0] > 0.0f)) { set_error("inpc_draw_leaf_counts: the weights sum to zero"); return INPC_E_INVALID; }
+    if (n_samples > 0) {
+        leaf_histogram_kernel<<<(unsigned)ceil_div<int64_t>(n_samples, kThreads), kThreads, 0, stream>>>(
+            s->seed, s->counter, w.cdf, w.guide, w.guide_bits, (unsigned)n_cells, n_samples, counts);
+        INPC_LAUNCH_CHECK("leaf_histogram_kernel");
+    }
+    s->counter += 1;
+    return INPC_OK;
+}
+
+extern "C" int inpc_halton_samples(const uint32_t* counts, int64_t n_cells, const float* centers, const int32_t* levels, float initial_size,
+                                   int64_t n_total, float* positions, void* workspace, void* stream_) {
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    if (n_total == 0) return INPC_OK;
+    if (n_cells <= 0 || n_cells >= ((int64_t)1 << 31) || n_total < 0 || n_total >= ((int64_t)1 << 32) || !counts || !centers || !levels || !positions || !workspace) {
+        set_error("inpc_halton_samples: bad argument");
+        return INPC_E_INVALID;
+    }
+    SamplerWs w = carve_sampler_ws(workspace, n_cells);
+    INPC_CUDA_TRY(cudaMemcpyAsync(w.counts, counts, sizeof(uint32_t) * (size_t)n_cells, cudaMemcpyDeviceToDevice, stream));
+    const int rc = scan_counts(w, n_cells, stream);
+    if (rc != INPC_OK) return rc;
+    halton_samples_kernel<<<(unsigned)ceil_div<int64_t>(n_total, kThreads), kThreads, 0, stream>>>(w.counts, w.offsets, (unsigned)n_cells, centers, levels,
+                                                                                                 initial_size, n_total, positions);
+    INPC_LAUNCH_CHECK("halton_samples_kernel");
+    return INPC_OK;
+}
+
+extern "C" size_t inpc_morton_workspace_bytes(int64_t n) {
+    const size_t arr = align_up(sizeof(uint32_t) * (size_t)(n > 0 ? n : 1));
+    return 4 * arr + sort_workspace_bytes(n) + 256;
+}
+
+extern "C" int inpc_morton_order(const float* positions, int64_t n, const float* box_lo, float box_extent, float* out, void* workspace,
+                                 void* stream_) {
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    if (n == 0) return INPC_OK;
+    if (n < 0 || n >= ((int64_t)1 << 30) || !positions || !box_lo || !(box_extent > 0.0f) || !out || !workspace || out == positions) {
+        set_error("inpc_morton_order: bad argument");
+        return INPC_E_INVALID;
+    }
+    Carver c(workspace);
+    uint32_t* codes[2] = {c.take<uint32_t>(n), c.take<uint32_t>(n)};
+    uint32_t* order[2] = {c.take<uint32_t>(n), c.take<uint32_t>(n)};
+    c.off = align_up(c.off);
+    void* sort_ws = c.base + c.off;
+    morton_codes_kernel<<<(unsigned)ceil_div<int64_t>(n, kThreads), kThreads, 0, stream>>>(positions, n, box_lo[0], box_lo[1], box_lo[2],
+                                                                                       1.0f / box_extent, codes[0], order[0]);
+    INPC_LAUNCH_CHECK("morton_codes_kernel");
+    int in_alt = 0;
+    const int rc = sort_pairs(codes[0], codes[1], order[0], order[1], n, 30, sort_ws, &in_alt, stream);
+    if (rc != INPC_OK) return rc;
+    gather_positions_kernel<<<(unsigned)ceil_div<int64_t>(n, kThreads), kThreads, 0, stream>>>(positions, order[in_alt], n, out);
+    INPC_LAUNCH_CHECK("gather_positions_kernel");
     return INPC_OK;
 }

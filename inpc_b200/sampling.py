@@ -99,6 +99,21 @@ class ProbabilityFieldSampler(torch.nn.Module):
         nbytes = int(_cabi.lib().inpc_sampler_workspace_bytes(n_cells))
         return torch.empty(nbytes, dtype=torch.uint8, device=dev)
 
+    def draw_leaf_counts(self, weights: torch.Tensor, n_samples: int) -> torch.Tensor:
+        """Number of draws per leaf of `n_samples` multinomial draws with probabilities proportional to
+        `weights` (torch.multinomial + bincount of Modules/ProbabilityField.py:129-130), int32 (L)."""
+        if not weights.is_cuda or weights.dtype != torch.float32:
+            raise TypeError("weights must be a CUDA float32 tensor")
+        weights = weights.contiguous()
+        n, dev = weights.numel(), weights.device
+        with torch.cuda.device(dev):
+            counts = torch.empty(n, dtype=torch.int32, device=dev)
+            ws = self._workspace(n, dev)
+            _cabi.check(_cabi.lib().inpc_draw_leaf_counts(self._handle, n, _ptr(weights), int(n_samples), _ptr(counts), _ptr(ws),
+                                                          _stream()))
+            ws.record_stream(torch.cuda.current_stream())
+        return counts
+
     def generate_training_samples(self, centers: torch.Tensor, levels: torch.Tensor, weights: torch.Tensor, view,
                                   n_samples: int, initial_size: float) -> tuple[torch.Tensor, torch.Tensor]:
         _check_view(view)
@@ -153,6 +168,65 @@ class ProbabilityFieldSampler(torch.nn.Module):
                 _ptr(positions), _ptr(ws), _stream()))
             ws.record_stream(torch.cuda.current_stream())
         return positions
+
+
+def halton_samples(counts: torch.Tensor, centers: torch.Tensor, levels: torch.Tensor, initial_size: float) -> torch.Tensor:
+    """Quasi-random positions, `counts[l]` per leaf, leaf by leaf: the Halton placement of
+    `ProbabilityField.extract_global` (Modules/ProbabilityField.py:131-140 with utils.py:36-64)."""
+    if not counts.is_cuda or counts.dtype != torch.int32:
+        raise TypeError("counts must be a CUDA int32 tensor")
+    centers, levels, _, n = _leaf_args(centers, levels, torch.empty(centers.shape[0], dtype=torch.float32, device=centers.device))
+    if counts.numel() != n:
+        raise ValueError(f"counts must hold one entry per leaf ({n}), got {counts.numel()}")
+    counts = counts.contiguous()
+    total = int(counts.sum().item())
+    dev = centers.device
+    with torch.cuda.device(dev):
+        positions = torch.empty((total, 3), dtype=torch.float32, device=dev)
+        ws = torch.empty(int(_cabi.lib().inpc_sampler_workspace_bytes(n)), dtype=torch.uint8, device=dev)
+        _cabi.check(_cabi.lib().inpc_halton_samples(_ptr(counts), n, _ptr(centers), _ptr(levels), float(initial_size), total,
+                                                    _ptr(positions), _ptr(ws), _stream()))
+        ws.record_stream(torch.cuda.current_stream())
+    return positions
+
+
+def morton_order(positions: torch.Tensor) -> torch.Tensor:
+    """`positions` (N,3) reordered along a 30-bit Morton curve through their bounding cube (the role of
+    morton_encode + argsort in Modules/ProbabilityField.py:141-143)."""
+    positions = positions.contiguous()
+    if not positions.is_cuda or positions.dtype != torch.float32 or positions.dim() != 2 or positions.shape[1] != 3:
+        raise TypeError("positions must be a CUDA float32 (N,3) tensor")
+    n = positions.shape[0]
+    if n == 0:
+        return positions.clone()
+    lo = positions.amin(dim=0)
+    extent = float((positions.amax(dim=0) - lo).max().item())
+    extent = extent * (1.0 + 1e-6) if extent > 0 else 1.0
+    box_lo = (C.c_float * 3)(*[float(v) for v in lo.tolist()])
+    dev = positions.device
+    with torch.cuda.device(dev):
+        out = torch.empty_like(positions)
+        ws = torch.empty(int(_cabi.lib().inpc_morton_workspace_bytes(n)), dtype=torch.uint8, device=dev)
+        _cabi.check(_cabi.lib().inpc_morton_order(_ptr(positions), n, box_lo, extent, _ptr(out), _ptr(ws), _stream()))
+        ws.record_stream(torch.cuda.current_stream())
+    return out
+
+
+def extract_global(sampler: "ProbabilityFieldSampler", centers: torch.Tensor, levels: torch.Tensor, weights: torch.Tensor, views,
+                   n_samples: int, initial_size: float, use_morton_order: bool = True) -> torch.Tensor:
+    """`ProbabilityField.extract_global` (Modules/ProbabilityField.py:121-144): leaf weights = maximum of
+    the viewpoint weights over `views` (the level-weighted occupancy when `views` is empty), multinomial
+    sample counts per leaf, Halton placement inside every leaf, optional Morton order."""
+    centers, levels, weights, n = _leaf_args(centers, levels, weights)
+    if views:
+        global_weights = torch.zeros_like(weights)
+        for view in views:
+            torch.maximum(compute_viewpoint_weights(centers, levels, weights, view, initial_size), global_weights, out=global_weights)
+    else:
+        global_weights = weights * torch.exp2(-levels * 0.5)             # ProbabilityField.get_current_weights(None)
+    counts = sampler.draw_leaf_counts(global_weights, n_samples)
+    positions = halton_samples(counts, centers, levels, initial_size)
+    return morton_order(positions) if use_morton_order else positions
 
 
 def build_cdf(weights: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:

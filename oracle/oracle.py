@@ -530,3 +530,36 @@ def multisample_resolve(samples, background, premultiplied=True):
     if background is not None:
         fi += (np.float32(1.0) - ai) * _f32(background)
     return fi, di, ai, alpha_sum
+
+
+# ----------------------------------------------------------------------------- global point cloud
+
+def halton_element(index: int, base: int) -> float:
+    """utils.py:36-46 (double precision, as Python floats)."""
+    result, f, i = 0.0, 1.0 / base, index
+    while i > 0:
+        result += f * (i % base)
+        i //= base
+        f /= base
+    return result
+
+
+def halton_samples(counts, centers, levels, initial_size):
+    """ProbabilityField.py:131-140 with utils.py:49-64: `counts[l]` quasi-random positions per leaf."""
+    counts = np.asarray(counts, dtype=np.int64)
+    centers = _f32(centers).reshape(-1, 3)
+    levels = np.asarray(levels, dtype=np.int64)
+    cell = np.repeat(np.arange(counts.shape[0]), counts)
+    offsets = np.cumsum(counts) - counts
+    h = np.arange(int(counts.sum())) - offsets[cell]
+    table = np.zeros((int(h.max()) + 1 if h.size else 0, 3), np.float32)
+    for i in range(table.shape[0]):
+        for j, base in enumerate((2, 3, 5)):
+            table[i, j] = halton_element(i + 1, base)
+    coords = table[h]
+    cell_size = (np.float32(initial_size) / (2 ** levels[cell]).astype(np.float32)).astype(np.float32)[:, None]
+    initial = centers[cell]
+    samples = initial - (cell_size / np.float32(2)) + coords * cell_size
+    single = np.repeat(counts == 1, counts)
+    samples[single] = initial[single]
+    return samples.astype(np.float32)
