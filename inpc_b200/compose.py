@@ -106,3 +106,54 @@ class MultisampleAccumulator:
         self.image = self.depth = self.alpha = None
         self.count = 0
         return out
+
+
+class MultisamplingRingBuffer:
+    """Sample sets of the last `size` frames (utils.py:145-174): every frame appends one new set and
+    re-rasterises all cached ones, so a frame costs one sampling / shading pass instead of `size`.
+    Same behaviour as the reference class, including its start-up rule (a slot that has not been
+    filled yet yields the first set)."""
+
+    def __init__(self) -> None:
+        self.size = 0
+        self.positions: list | None = None
+        self.features: list | None = None
+        self.current_idx = 0
+        self.read_idx = 0
+
+    def append(self, positions: torch.Tensor, features: torch.Tensor, new_size: int) -> None:
+        if self.size != new_size:
+            self.current_idx = 0
+            self.size = new_size
+            self.positions = [None] * new_size
+            self.features = [None] * new_size
+        self.positions[self.current_idx] = positions
+        self.features[self.current_idx] = features
+        self.current_idx = (self.current_idx + 1) % self.size
+        self.read_idx = 0
+
+    def get_next(self):
+        if self.positions[self.read_idx] is None:
+            return self.positions[0], self.features[0]
+        positions, features = self.positions[self.read_idx], self.features[self.read_idx]
+        self.read_idx += 1
+        return positions, features
+
+
+@torch.no_grad()
+def render_multisampled(rasterizer, view, mode: int, sample_sets, background: torch.Tensor | None = None,
+                        sigma_world_scale: float = 1.0, sigma_cutoff: float = 3.0,
+                        average_with_premultiplied_alpha: bool = True):
+    """Inference over several sample sets of one view (Renderer.py:99-125 and :139-166): every set
+    `(positions, features_raw)` is rasterised with `rasterizer.render`, the results are averaged and
+    composed over `background`.  `sample_sets` is a list of pairs or a filled `MultisamplingRingBuffer`.
+    Returns (feature_image, depth, alpha, alpha_sum)."""
+    if isinstance(sample_sets, MultisamplingRingBuffer):
+        ring = sample_sets
+        sets = [ring.get_next() for _ in range(ring.size)]
+    else:
+        sets = list(sample_sets)
+    acc = MultisampleAccumulator(len(sets), average_with_premultiplied_alpha)
+    for positions, features_raw in sets:
+        acc.add(*rasterizer.render(view, mode, positions, features_raw, sigma_world_scale, sigma_cutoff))
+    return acc.resolve(background)

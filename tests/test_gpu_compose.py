@@ -87,3 +87,38 @@ def test_compose_argument_errors():
     acc.add(img, torch.zeros((1, 8, 8), device=DEV), torch.zeros((1, 8, 8), device=DEV))
     with pytest.raises(RuntimeError):
         acc.resolve()
+
+
+def test_ring_buffer_and_multisampled_render():
+    """The ring buffer hands out the same sets as the reference class would (start-up rule included), and a
+    multisampled render equals rasterising every set and composing with the restatement."""
+    import inpc_b200
+    from helpers import small_scene
+    from inpc_b200.compose import MultisamplingRingBuffer, render_multisampled
+    view, pos, feats, _ = small_scene(n=8000, width=96, height=72, focal=90.0)
+    v = view.to(DEV)
+    gen = torch.Generator().manual_seed(12)
+    sets = []
+    for k in range(3):
+        p = (pos + torch.randn(pos.shape, generator=gen) * 0.01).to(DEV)
+        raw = torch.cat([torch.randn((pos.shape[0], 1), generator=gen).to(torch.float16), feats], dim=1).contiguous().to(DEV)
+        sets.append((p, raw))
+    ring = MultisamplingRingBuffer()
+    ring.append(*sets[0], 3)
+    got = [ring.get_next() for _ in range(3)]
+    assert got[0][0] is sets[0][0] and got[1][0] is sets[0][0] and got[2][0] is sets[0][0]      # unfilled slots yield set 0
+    ring.append(*sets[1], 3)
+    ring.append(*sets[2], 3)
+    assert [ring.get_next()[0] is s[0] for s in sets] == [True, True, True]
+    ring.append(*sets[0], 3)                                                                      # wraps around
+    rast = inpc_b200.INPCRasterizer()
+    bg = torch.randn((4, 72, 96), generator=gen).to(DEV)
+    for premult in (True, False):
+        ring.read_idx = 0
+        f, d, a, s = render_multisampled(rast, v, 0, ring, bg, 1.0, 3.0, premult)
+        singles = [tuple(x.cpu().numpy() for x in rast.render(v, 0, p, raw, 1.0, 3.0)) for p, raw in sets]
+        rf, rd, ra, rs = O.multisample_resolve(singles, bg.cpu().numpy(), premult)
+        np.testing.assert_array_equal(f.cpu().numpy(), rf)
+        np.testing.assert_array_equal(d.cpu().numpy(), rd)
+        np.testing.assert_array_equal(a.cpu().numpy(), ra)
+        np.testing.assert_array_equal(s.cpu().numpy(), rs)
