@@ -43,7 +43,7 @@ N_APPEARANCE = 1 << 22
 # DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) per (point, tile) instance of the kernels of a
 # stage, from the ncu capture summarised in profiles/blend_bilinear_tile8_config1_small.md (2^22 points,
 # 5,274,412 instances, 8x8 tiles); the traffic of these kernels grows in proportion to the instances.
-TRAFFIC_BYTES_PER_INSTANCE = {"blend_fwd": 796.9e6 / 5274412, "blend_bwd": 689.4e6 / 5274412}
+TRAFFIC_BYTES_PER_INSTANCE = {"blend_fwd": 785.9e6 / 5274412, "blend_bwd": 678.7e6 / 5274412}
 
 
 def parse_args():
