@@ -56,6 +56,7 @@ struct StageScope {
 enum : unsigned {
     STATUS_LOOKBACK_TIMEOUT = 0,   // a radix-sort tile gave up waiting for a predecessor tile
     STATUS_SAMPLER_EXHAUSTED = 1,  // informational: some sample slots ran out of rejection attempts
+    STATUS_BULK_COPY_TIMEOUT = 2,  // a block gave up waiting for its bulk copy into shared memory
     STATUS_WORDS = 4,
 };
 unsigned* device_status_ptr();            // device pointer to STATUS_WORDS words (allocated on first use)
@@ -136,6 +137,53 @@ __device__ __forceinline__ unsigned warp_inclusive_scan(unsigned v) {
         if (lane_id() >= (unsigned)o) v += t;
     }
     return v;
+}
+
+// ---- bulk asynchronous copies (the copy engine behind TMA, untiled form) ------------------------------
+// global -> shared: one thread arms an mbarrier with the byte count and issues the copy; every thread
+// that will read the data waits on the barrier's phase.  Source, destination and size must be
+// multiples of 16 bytes.  The wait is bounded: a block that gives up reports it and the caller skips
+// its work, the next entry point of the library then returns an error.
+__device__ __forceinline__ unsigned shared_address(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbarrier_init(unsigned long long* bar, unsigned arrivals) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(shared_address(bar)), "r"(arrivals) : "memory");
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+
+__device__ __forceinline__ void bulk_load_to_shared(void* dst_shared, const void* src_global, unsigned bytes, unsigned long long* bar) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(shared_address(bar)), "r"(bytes) : "memory");
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(shared_address(dst_shared)),
+                 "l"(src_global), "r"(bytes), "r"(shared_address(bar))
+                 : "memory");
+}
+
+__device__ __forceinline__ bool mbarrier_wait_bounded(unsigned long long* bar, unsigned parity) {
+    const unsigned addr = shared_address(bar);
+    for (int spin = 0; spin < (1 << 20); ++spin) {
+        unsigned done;
+        asm volatile(
+            "{\n"
+            ".reg .pred p;\n"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+            "selp.u32 %0, 1, 0, p;\n"
+            "}\n"
+            : "=r"(done)
+            : "r"(addr), "r"(parity)
+            : "memory");
+        if (done) return true;
+    }
+    return false;
+}
+
+// shared -> global: the writers of the shared data call `fence_shared_for_bulk()` before the block
+// barrier, then one thread issues the store and waits until the source has been read.
+__device__ __forceinline__ void fence_shared_for_bulk() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+__device__ __forceinline__ void bulk_store_from_shared(void* dst_global, const void* src_shared, unsigned bytes) {
+    asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst_global), "r"(shared_address(src_shared)), "r"(bytes) : "memory");
+    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+    asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
 }
 
 // Block-wide exclusive scan of one unsigned per thread; `smem` needs (blockDim.x/32 + 1) words.

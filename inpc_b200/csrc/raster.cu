@@ -291,7 +291,7 @@ __global__ void __launch_bounds__(kPreThreads) preprocess_kernel(
     int64_t n, RasterParams rp, const unsigned* __restrict__ block_visible, const unsigned* __restrict__ group_offset,
     const unsigned* __restrict__ depth_min,
     const unsigned* __restrict__ depth_max, PointRec* __restrict__ rec, uint2* __restrict__ bounds, float4* __restrict__ conic, uint32_t* __restrict__ depth_keys,
-    uint32_t* __restrict__ point_ids) {
+    uint32_t* __restrict__ point_ids, bool bulk_ok, volatile unsigned* status) {
     constexpr int kHalves = VARIANT == VAR_RAW37 ? 37 : 36;
     constexpr int kSlabBytes = VARIANT == VAR_ROWS ? 16 : kPreThreads * kHalves * 2;   // multiple of 16 for both layouts
     __shared__ __align__(16) unsigned char s_feat[kSlabBytes];
@@ -299,7 +299,18 @@ __global__ void __launch_bounds__(kPreThreads) preprocess_kernel(
 
     const int64_t block_first = (int64_t)blockIdx.x * kPreThreads;
     const int in_block = (int)min((int64_t)kPreThreads, n - block_first);
-    if (VARIANT != VAR_ROWS) {
+    __shared__ __align__(8) unsigned long long s_bar;
+    // The block's feature slab is contiguous in global memory.  When base and size allow (multiples of
+    // 16 bytes) one bulk asynchronous copy brings it in while the threads project their points;
+    // otherwise (odd tail block, unaligned caller view) 16-byte loads through registers do.
+    const bool bulk = VARIANT != VAR_ROWS && bulk_ok && ((in_block * kHalves * 2) & 15) == 0;
+    if (bulk) {
+        if (threadIdx.x == 0) mbarrier_init(&s_bar, 1);
+        __syncthreads();
+        if (threadIdx.x == 0)
+            bulk_load_to_shared(s_feat, reinterpret_cast<const unsigned char*>(features) + block_first * (kHalves * 2),
+                                (unsigned)(in_block * kHalves * 2), &s_bar);
+    } else if (VARIANT != VAR_ROWS) {
         // coalesced 16-byte staging of the block's contiguous feature slab
         const unsigned char* src = reinterpret_cast<const unsigned char*>(features) + block_first * (kHalves * 2);
         const int bytes = in_block * kHalves * 2;
@@ -319,8 +330,11 @@ __global__ void __launch_bounds__(kPreThreads) preprocess_kernel(
         px = __ldg(positions + 3 * i); py = __ldg(positions + 3 * i + 1); pz = __ldg(positions + 3 * i + 2);
         pr = project_point<MODE, VARIANT>(px, py, pz, m, rp, i);
     }
+    bool slab_ready = true;
+    if (bulk) slab_ready = mbarrier_wait_bounded(&s_bar, 0u);
+    if (!slab_ready && status) status[STATUS_BULK_COPY_TIMEOUT] = 1u;
     __syncthreads();
-    if (i < n) {
+    if (i < n && slab_ready) {
         if (pr.visible && VARIANT == VAR_ROWS) {
             // feature rows are gathered by the blend itself: the record carries the geometry only
             *reinterpret_cast<float4*>(rec + i) = make_float4(pr.sx, pr.sy, __ldg(opacities + i), pr.depth);
@@ -1561,7 +1575,7 @@ __global__ void __launch_bounds__(T * T) blend_gaussian_backward_kernel(
 // torch::zeros of src/rasterization_api.cu:139.
 __global__ void __launch_bounds__(kPreThreads) preprocess_backward_kernel(
     const float* __restrict__ positions, const float* __restrict__ cam, const uint2* __restrict__ bounds,
-    const float4* __restrict__ grad_feat_view, __half* __restrict__ grad_features, int64_t n) {
+    const float4* __restrict__ grad_feat_view, __half* __restrict__ grad_features, int64_t n, bool bulk_ok) {
     __shared__ __align__(16) __half s_out[kPreThreads * 36];
     const int64_t block_first = (int64_t)blockIdx.x * kPreThreads;
     const int in_block = (int)min((int64_t)kPreThreads, n - block_first);
@@ -1585,9 +1599,17 @@ __global__ void __launch_bounds__(kPreThreads) preprocess_backward_kernel(
 #pragma unroll
         for (int k = 0; k < 18; ++k) *reinterpret_cast<unsigned*>(o + 2 * k) = 0u;
     }
-    __syncthreads();
     unsigned char* dst = reinterpret_cast<unsigned char*>(grad_features) + block_first * 72;
     const int bytes = in_block * 72;
+    // one bulk asynchronous store of the block's contiguous 72-byte rows when base and size are multiples
+    // of 16 bytes; 16-byte stores through registers otherwise
+    const bool bulk = bulk_ok && (bytes & 15) == 0;
+    if (bulk) fence_shared_for_bulk();
+    __syncthreads();
+    if (bulk) {
+        if (threadIdx.x == 0) bulk_store_from_shared(dst, s_out, (unsigned)bytes);
+        return;
+    }
     const int n16 = bytes / 16;
     uint4* dst16 = reinterpret_cast<uint4*>(dst);
     const uint4* src16 = reinterpret_cast<const uint4*>(s_out);
@@ -1749,7 +1771,7 @@ int run_front(const RasterParams& rp, int64_t n, const float* positions, const v
             preprocess_kernel<MODE, VARIANT><<<(unsigned)nb, kPreThreads, 0, stream>>>(
                 positions, static_cast<const __half*>(features), opacities, n, rp, pb.block_visible, pb.group_visible, pb.depth_min, pb.depth_max,
                 pb.rec, pb.bounds,
-                pb.conic, pb.keys[0], pb.ids[0]);
+                pb.conic, pb.keys[0], pb.ids[0], (reinterpret_cast<uintptr_t>(features) & 15u) == 0, device_status_ptr());
             INPC_LAUNCH_CHECK("preprocess_kernel");
         }
         INPC_CUDA_TRY(cudaEventSynchronize(ready));
@@ -1761,6 +1783,10 @@ int run_front(const RasterParams& rp, int64_t n, const float* positions, const v
         }
         if (read_and_clear_status(STATUS_LOOKBACK_TIMEOUT)) {
             set_error("an earlier radix-sort pass gave up waiting for a predecessor tile; results of that call are invalid");
+            return INPC_E_DEVICE;
+        }
+        if (read_and_clear_status(STATUS_BULK_COPY_TIMEOUT)) {
+            set_error("an earlier projection pass gave up waiting for a bulk copy into shared memory; results of that call are invalid");
             return INPC_E_DEVICE;
         }
     }
@@ -2051,7 +2077,7 @@ extern "C" int inpc_rasterize_backward(const inpc_raster_state* state, const inp
     }
     StageScope scope(STAGE_PREPROCESS_BWD, stream);
     preprocess_backward_kernel<<<(unsigned)ceil_div<int64_t>(n, kPreThreads), kPreThreads, 0, stream>>>(
-        positions, view->cam_position, pb.bounds, gfv, static_cast<__half*>(grad_features), n);
+        positions, view->cam_position, pb.bounds, gfv, static_cast<__half*>(grad_features), n, (reinterpret_cast<uintptr_t>(grad_features) & 15u) == 0);
     INPC_LAUNCH_CHECK("preprocess_backward_kernel");
     return INPC_OK;
 }
