@@ -101,12 +101,16 @@ struct PassSmem {
 
 // BITS > 0 fixes the digit width at compile time (the ballot loop of the ranking unrolls); BITS == 0
 // takes it from `bits_arg`.
-template <int BITS>
+// AUX: the pass also writes aux_out[destination] = aux_in[value] (8-byte records indexed by the sorted
+// values).  The pass is bound by instruction issue with the memory system mostly idle, so this gather
+// rides along almost for free; a consumer that walks the sorted order then reads its per-item data
+// sequentially instead of gathering it.
+template <int BITS, bool AUX>
 __global__ void __launch_bounds__(kThreads) radix_onesweep_pass_kernel(
     const uint32_t* __restrict__ keys_in, const uint32_t* __restrict__ vals_in,
     uint32_t* __restrict__ keys_out, uint32_t* __restrict__ vals_out, int64_t n, int shift, int bits_arg,
     const unsigned* __restrict__ digit_base, volatile unsigned* tile_state, unsigned* ticket,
-    volatile unsigned* status) {
+    volatile unsigned* status, const uint2* __restrict__ aux_in, uint2* __restrict__ aux_out) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     PassSmem& s = *reinterpret_cast<PassSmem*>(smem_raw);
 
@@ -268,7 +272,9 @@ __global__ void __launch_bounds__(kThreads) radix_onesweep_pass_kernel(
         const unsigned d = (k >> shift) & digit_mask;
         const unsigned dst = s.global_off[d] + (unsigned)q;
         keys_out[dst] = k;
-        vals_out[dst] = s.values[q];
+        const uint32_t v = s.values[q];
+        vals_out[dst] = v;
+        if (AUX) aux_out[dst] = __ldg(aux_in + v);
     }
 }
 
@@ -297,23 +303,30 @@ SortWorkspace carve_sort_workspace(void* ws, int64_t n) {
 }
 
 
-int launch_onesweep_pass(int64_t tiles, const uint32_t* kin, const uint32_t* vin, uint32_t* kout, uint32_t* vout, int64_t n, int shift, int bits,
-                         const unsigned* base, unsigned* state, unsigned* ticket, unsigned* status, cudaStream_t stream) {
-    static bool attr_set[4][kMaxDevices] = {{false}};
-    int rc = opt_in_dynamic_smem(radix_onesweep_pass_kernel<0>, sizeof(PassSmem), attr_set[0]);
-    if (rc == INPC_OK) rc = opt_in_dynamic_smem(radix_onesweep_pass_kernel<7>, sizeof(PassSmem), attr_set[1]);
-    if (rc == INPC_OK) rc = opt_in_dynamic_smem(radix_onesweep_pass_kernel<8>, sizeof(PassSmem), attr_set[2]);
-    if (rc == INPC_OK) rc = opt_in_dynamic_smem(radix_onesweep_pass_kernel<9>, sizeof(PassSmem), attr_set[3]);
+template <int BITS, bool AUX>
+int launch_onesweep_instance(int64_t tiles, const uint32_t* kin, const uint32_t* vin, uint32_t* kout, uint32_t* vout, int64_t n, int shift, int bits,
+                             const unsigned* base, unsigned* state, unsigned* ticket, unsigned* status, const uint2* aux_in, uint2* aux_out,
+                             cudaStream_t stream) {
+    static bool attr_set[kMaxDevices] = {false};
+    const int rc = opt_in_dynamic_smem(radix_onesweep_pass_kernel<BITS, AUX>, sizeof(PassSmem), attr_set);
     if (rc != INPC_OK) return rc;
-    // the digit widths the rasterizer's sorts use (depth keys 9/8, tile keys 7) get unrolled kernels
-    switch (bits) {
-        case 7: radix_onesweep_pass_kernel<7><<<(unsigned)tiles, kThreads, sizeof(PassSmem), stream>>>(kin, vin, kout, vout, n, shift, bits, base, state, ticket, status); break;
-        case 8: radix_onesweep_pass_kernel<8><<<(unsigned)tiles, kThreads, sizeof(PassSmem), stream>>>(kin, vin, kout, vout, n, shift, bits, base, state, ticket, status); break;
-        case 9: radix_onesweep_pass_kernel<9><<<(unsigned)tiles, kThreads, sizeof(PassSmem), stream>>>(kin, vin, kout, vout, n, shift, bits, base, state, ticket, status); break;
-        default: radix_onesweep_pass_kernel<0><<<(unsigned)tiles, kThreads, sizeof(PassSmem), stream>>>(kin, vin, kout, vout, n, shift, bits, base, state, ticket, status); break;
-    }
+    radix_onesweep_pass_kernel<BITS, AUX><<<(unsigned)tiles, kThreads, sizeof(PassSmem), stream>>>(kin, vin, kout, vout, n, shift, bits, base, state, ticket,
+                                                                                              status, aux_in, aux_out);
     INPC_LAUNCH_CHECK("radix_onesweep_pass_kernel");
     return INPC_OK;
+}
+
+// the digit widths the rasterizer's sorts use (depth keys 9/8, tile keys 7) get unrolled kernels
+template <bool AUX>
+int launch_onesweep_pass(int64_t tiles, const uint32_t* kin, const uint32_t* vin, uint32_t* kout, uint32_t* vout, int64_t n, int shift, int bits,
+                         const unsigned* base, unsigned* state, unsigned* ticket, unsigned* status, const uint2* aux_in, uint2* aux_out,
+                         cudaStream_t stream) {
+    switch (bits) {
+        case 7: return launch_onesweep_instance<7, AUX>(tiles, kin, vin, kout, vout, n, shift, bits, base, state, ticket, status, aux_in, aux_out, stream);
+        case 8: return launch_onesweep_instance<8, AUX>(tiles, kin, vin, kout, vout, n, shift, bits, base, state, ticket, status, aux_in, aux_out, stream);
+        case 9: return launch_onesweep_instance<9, AUX>(tiles, kin, vin, kout, vout, n, shift, bits, base, state, ticket, status, aux_in, aux_out, stream);
+        default: return launch_onesweep_instance<0, AUX>(tiles, kin, vin, kout, vout, n, shift, bits, base, state, ticket, status, aux_in, aux_out, stream);
+    }
 }
 
 }  // namespace
@@ -323,7 +336,7 @@ size_t sort_workspace_bytes(int64_t n) { return carve_sort_workspace(nullptr, n)
 int sort_pass_count(int end_bit) { return end_bit > 0 ? ceil_div(end_bit, kRadixBits) : 0; }
 
 int sort_pairs(uint32_t* keys, uint32_t* keys_alt, uint32_t* values, uint32_t* values_alt, int64_t n,
-               int end_bit, void* workspace, int* result_in_alt, cudaStream_t stream) {
+               int end_bit, void* workspace, int* result_in_alt, cudaStream_t stream, const uint2* aux_in, uint2* aux_out) {
     if (result_in_alt) *result_in_alt = 0;
     if (n < 0 || n >= (int64_t)1 << 30) { set_error("sort_pairs: n=%lld out of range [0, 2^30)", (long long)n); return INPC_E_INVALID; }
     if (end_bit < 0 || end_bit > 32) { set_error("sort_pairs: end_bit=%d out of range", end_bit); return INPC_E_INVALID; }
@@ -362,8 +375,12 @@ int sort_pairs(uint32_t* keys, uint32_t* keys_alt, uint32_t* values, uint32_t* v
     if (!status) return INPC_E_CUDA;
     uint32_t *kin = keys, *kout = keys_alt, *vin = values, *vout = values_alt;
     for (int p = 0; p < pt.n_passes; ++p) {
-        const int rc = launch_onesweep_pass(tiles, kin, vin, kout, vout, n, pt.shift[p], pt.bits[p], w.base + p * kRadix,
-                                            w.state + (size_t)p * tiles * kRadix, w.ticket + p, status, stream);
+        // the last pass knows every pair's final position: it carries the optional gather
+        const bool aux = aux_in && aux_out && p == pt.n_passes - 1;
+        const int rc = aux ? launch_onesweep_pass<true>(tiles, kin, vin, kout, vout, n, pt.shift[p], pt.bits[p], w.base + p * kRadix,
+                                                        w.state + (size_t)p * tiles * kRadix, w.ticket + p, status, aux_in, aux_out, stream)
+                           : launch_onesweep_pass<false>(tiles, kin, vin, kout, vout, n, pt.shift[p], pt.bits[p], w.base + p * kRadix,
+                                                         w.state + (size_t)p * tiles * kRadix, w.ticket + p, status, nullptr, nullptr, stream);
         if (rc != INPC_OK) return rc;
         uint32_t* t = kin; kin = kout; kout = t;
         t = vin; vin = vout; vout = t;
@@ -456,8 +473,8 @@ extern "C" int inpc_sort_pairs_static(uint32_t* keys, uint32_t* keys_alt, uint32
     INPC_LAUNCH_CHECK("radix_scan_histogram_kernel");
     uint32_t *kin = keys, *kout = keys_alt, *vin = values, *vout = values_alt;
     for (int p = 0; p < pt.n_passes; ++p) {
-        rc = launch_onesweep_pass(tiles, kin, vin, kout, vout, n, pt.shift[p], pt.bits[p], w.base + p * kRadix,
-                                  w.state + (size_t)p * tiles * kRadix, w.ticket + p, status, stream);
+        rc = launch_onesweep_pass<false>(tiles, kin, vin, kout, vout, n, pt.shift[p], pt.bits[p], w.base + p * kRadix,
+                                         w.state + (size_t)p * tiles * kRadix, w.ticket + p, status, nullptr, nullptr, stream);
         if (rc != INPC_OK) return rc;
         uint32_t* t = kin; kin = kout; kout = t;
         t = vin; vin = vout; vout = t;

@@ -39,7 +39,8 @@ struct __align__(16) PointRec {
 
 struct RasterParams {
     ViewParams v;
-    int tile;       // tile edge in pixels
+    int tile;       // tile edge in pixels (8 or 16)
+    float inv_tile; // its reciprocal: the edge is a power of two, so x * inv_tile == x / tile bit for bit
     int gw, gh;     // tile grid
     float sigma_world, sigma_cutoff;
     const float* scales;   // optional per-point sigma (gaussian, pre-extracted)
@@ -115,12 +116,12 @@ __device__ __forceinline__ Projection project_point(const float px, const float 
         ex = k * sqrtf(cov_x) - 0.5f;
         ey = k * sqrtf(cov_z) - 0.5f;
     }
-    const float tf = (float)rp.tile;
+    const float itf = rp.inv_tile;
     const unsigned gw = (unsigned)rp.gw, gh = (unsigned)rp.gh;
-    o.x0 = min(gw, (unsigned)max(0, __float2int_rd((sx - ex) / tf)));
-    o.x1 = min(gw, (unsigned)max(0, __float2int_ru((sx + ex) / tf)));
-    o.y0 = min(gh, (unsigned)max(0, __float2int_rd((sy - ey) / tf)));
-    o.y1 = min(gh, (unsigned)max(0, __float2int_ru((sy + ey) / tf)));
+    o.x0 = min(gw, (unsigned)max(0, __float2int_rd((sx - ex) * itf)));
+    o.x1 = min(gw, (unsigned)max(0, __float2int_ru((sx + ex) * itf)));
+    o.y0 = min(gh, (unsigned)max(0, __float2int_rd((sy - ey) * itf)));
+    o.y1 = min(gh, (unsigned)max(0, __float2int_ru((sy + ey) * itf)));
     o.sx = sx;
     o.sy = sy;
     o.visible = (o.x1 - o.x0) * (o.y1 - o.y0) != 0u;
@@ -390,14 +391,25 @@ __device__ __forceinline__ unsigned tiles_of(const uint2 b) {
 // cub::DeviceScan::ExclusiveSum of src/bilinear/forward.cu:109-115, first half).
 constexpr int kInstThreads = 1024;   // block sums over 1024 points keep the one-block scan short
 template <bool PACKED>
-__global__ void __launch_bounds__(kInstThreads) instance_count_kernel(const uint32_t* __restrict__ sorted_keys,
-                                                                      const uint32_t* __restrict__ sorted_ids,
-                                                                      const uint2* __restrict__ bounds, int64_t n_visible,
-                                                                      unsigned* __restrict__ block_sums) {
-    __shared__ unsigned s_w[kInstThreads / 32];
-    const int64_t s = (int64_t)blockIdx.x * kInstThreads + threadIdx.x;
+__global__ void __launch_bounds__(kInstThreads / 4) instance_count_kernel(const uint32_t* __restrict__ sorted_keys,
+                                                                          const uint32_t* __restrict__ sorted_ids,
+                                                                          const uint2* __restrict__ bounds, int64_t n_visible,
+                                                                          unsigned* __restrict__ block_sums) {
+    // a block of kInstThreads / 4 threads covers kInstThreads points, four consecutive ones per thread
+    // (one 16-byte load when the keys carry the count)
+    __shared__ unsigned s_w[kInstThreads / 4 / 32];
+    const int64_t first = (int64_t)blockIdx.x * kInstThreads + 4 * (int64_t)threadIdx.x;
     unsigned c = 0;
-    if (s < n_visible) c = PACKED ? (__ldg(sorted_keys + s) >> kCountShift) + 1u : tiles_of(__ldg(bounds + __ldg(sorted_ids + s)));
+    if (PACKED && first + 4 <= n_visible) {
+        const uint4 k = __ldg(reinterpret_cast<const uint4*>(sorted_keys + first));   // the key buffers are 16-byte aligned
+        c = (k.x >> kCountShift) + (k.y >> kCountShift) + (k.z >> kCountShift) + (k.w >> kCountShift) + 4u;
+    } else {
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            const int64_t s = first + q;
+            if (s < n_visible) c += PACKED ? (__ldg(sorted_keys + s) >> kCountShift) + 1u : tiles_of(__ldg(bounds + __ldg(sorted_ids + s)));
+        }
+    }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) c += __shfl_down_sync(0xffffffffu, c, o);
     if (lane_id() == 0) s_w[threadIdx.x >> 5] = c;
@@ -405,7 +417,7 @@ __global__ void __launch_bounds__(kInstThreads) instance_count_kernel(const uint
     if (threadIdx.x == 0) {
         unsigned t = 0;
 #pragma unroll
-        for (int w = 0; w < kInstThreads / 32; ++w) t += s_w[w];
+        for (int w = 0; w < kInstThreads / 4 / 32; ++w) t += s_w[w];
         block_sums[blockIdx.x] = t;
     }
 }
@@ -436,6 +448,8 @@ __global__ void __launch_bounds__(kScanThreads) scan_u32_kernel(unsigned* __rest
 
 // One (tile key, point id) pair per touched tile, row-major over the point's bounds, points in depth
 // order (src/bilinear/kernels.cu:198-220).
+// `bounds` is in depth order (bounds[s], SORTED) or in point order (bounds[id]).
+template <bool SORTED>
 __global__ void __launch_bounds__(kInstThreads) emit_instances_kernel(const uint32_t* __restrict__ sorted_ids,
                                                                       const uint2* __restrict__ bounds, int64_t n_visible,
                                                                       const unsigned* __restrict__ block_base, int gw,
@@ -445,7 +459,7 @@ __global__ void __launch_bounds__(kInstThreads) emit_instances_kernel(const uint
     const int64_t s = (int64_t)blockIdx.x * kInstThreads + threadIdx.x;
     uint32_t id = 0;
     uint2 b = make_uint2(0u, 0u);
-    if (s < n_visible) { id = __ldg(sorted_ids + s); b = __ldg(bounds + id); }
+    if (s < n_visible) { id = __ldg(sorted_ids + s); b = __ldg(bounds + (SORTED ? s : (int64_t)id)); }
     const unsigned c = tiles_of(b);
     unsigned total;
     unsigned off = block_base[blockIdx.x] + block_exclusive_scan(c, s_scan, &total);
@@ -526,7 +540,8 @@ __device__ __forceinline__ unsigned segment_length(unsigned len, unsigned batch)
 __global__ void __launch_bounds__(kScanThreads) count_segments_kernel(const uint2* __restrict__ ranges, int n_tiles, int batch,
                                                                       uint32_t* __restrict__ tile_first,
                                                                       uint32_t* __restrict__ n_segments) {
-    constexpr int kItems = 16;
+    // four consecutive tiles per thread: short serial chains, two 16-byte loads
+    constexpr int kItems = 4;
     __shared__ unsigned s_scan[kScanThreads / 32 + 1];
     unsigned running = 0;
     for (int base = 0; base < n_tiles; base += kScanThreads * kItems) {
@@ -537,7 +552,7 @@ __global__ void __launch_bounds__(kScanThreads) count_segments_kernel(const uint
         for (int k = 0; k < kItems; ++k) {
             v[k] = 0u;
             if (t0 + k < n_tiles) {
-                const uint2 r = ranges[t0 + k];
+                const uint2 r = __ldg(ranges + t0 + k);
                 const unsigned len = r.y - r.x;
                 v[k] = max(1u, ceil_div(len, segment_length(len, (unsigned)batch)));
             }
@@ -1624,6 +1639,7 @@ __global__ void __launch_bounds__(kPreThreads) preprocess_backward_kernel(
 struct PointBlob {
     PointRec* rec;
     uint2* bounds;
+    uint2* bounds_sorted;                 // tile bounds in depth order, written by the last pass of the depth sort
     float4* conic;
     unsigned* block_visible;              // survivors per chunk of kPreThreads points
     unsigned* group_visible;              // per group of 4 chunks; scanned in place
@@ -1646,6 +1662,7 @@ PointBlob carve_point_blob(void* p, int64_t n, int mode) {
     const int64_t nb = ceil_div<int64_t>(n > 0 ? n : 1, kPreThreads);
     b.rec = c.take<PointRec>(n);
     b.bounds = c.take<uint2>(n);
+    b.bounds_sorted = c.take<uint2>(n);
     b.conic = mode == INPC_MODE_GAUSSIAN ? c.take<float4>(n) : nullptr;
     b.block_visible = c.take<unsigned>(nb);
     b.group_visible = c.take<unsigned>(ceil_div<int64_t>(nb, 4));
@@ -1805,7 +1822,7 @@ int run_front(const RasterParams& rp, int64_t n, const float* positions, const v
     int rc;
     {
         StageScope scope(STAGE_SORT_DEPTH, stream);
-        rc = sort_pairs(pb.keys[0], pb.keys[1], pb.ids[0], pb.ids[1], n_visible, key_bits, pb.sort_ws, &in_alt, stream);
+        rc = sort_pairs(pb.keys[0], pb.keys[1], pb.ids[0], pb.ids[1], n_visible, key_bits, pb.sort_ws, &in_alt, stream, pb.bounds, pb.bounds_sorted);
     }
     if (rc != INPC_OK) return rc;
     const uint32_t* sorted_ids = pb.ids[in_alt];
@@ -1815,13 +1832,17 @@ int run_front(const RasterParams& rp, int64_t n, const float* positions, const v
             StageScope scope(STAGE_INSTANCES, stream);
             // the count of touched tiles rides in the top key bits when the depth offsets left them free
             if (MODE == INPC_MODE_BILINEAR && key_bits <= (int)kCountShift)
-                instance_count_kernel<true><<<(unsigned)ibk, kInstThreads, 0, stream>>>(pb.keys[in_alt], sorted_ids, pb.bounds, n_visible, pb.inst_block_sums);
+                instance_count_kernel<true><<<(unsigned)ibk, kInstThreads / 4, 0, stream>>>(pb.keys[in_alt], sorted_ids, pb.bounds, n_visible, pb.inst_block_sums);
             else
-                instance_count_kernel<false><<<(unsigned)ibk, kInstThreads, 0, stream>>>(pb.keys[in_alt], sorted_ids, pb.bounds, n_visible, pb.inst_block_sums);
+                instance_count_kernel<false><<<(unsigned)ibk, kInstThreads / 4, 0, stream>>>(pb.keys[in_alt], sorted_ids, pb.bounds, n_visible, pb.inst_block_sums);
             INPC_LAUNCH_CHECK("instance_count_kernel");
             scan_u32_kernel<<<1, kScanThreads, 0, stream>>>(pb.inst_block_sums, ibk);
             INPC_LAUNCH_CHECK("scan_u32_kernel");
-            emit_instances_kernel<<<(unsigned)ibk, kInstThreads, 0, stream>>>(sorted_ids, pb.bounds, n_visible, pb.inst_block_sums, rp.gw, ib.keys[0], ib.ids[0]);
+            // the depth sort's last pass left the bounds in depth order, unless it had nothing to do
+            if (n_visible > 1 && key_bits > 0)
+                emit_instances_kernel<true><<<(unsigned)ibk, kInstThreads, 0, stream>>>(sorted_ids, pb.bounds_sorted, n_visible, pb.inst_block_sums, rp.gw, ib.keys[0], ib.ids[0]);
+            else
+                emit_instances_kernel<false><<<(unsigned)ibk, kInstThreads, 0, stream>>>(sorted_ids, pb.bounds, n_visible, pb.inst_block_sums, rp.gw, ib.keys[0], ib.ids[0]);
             INPC_LAUNCH_CHECK("emit_instances_kernel");
         }
         StageScope scope(STAGE_SORT_TILE, stream);
@@ -1858,6 +1879,7 @@ RasterParams make_params(const inpc_view* view, int tile_size, float sigma_world
     RasterParams rp;
     rp.v = to_params(view);
     rp.tile = tile_size;
+    rp.inv_tile = 1.0f / (float)tile_size;
     rp.gw = ceil_div(view->width, tile_size);
     rp.gh = ceil_div(view->height, tile_size);
     rp.sigma_world = sigma_world;
