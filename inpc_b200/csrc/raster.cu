@@ -17,6 +17,13 @@
 
 #include <type_traits>
 
+// 1: the last pass of the depth sort also writes the tile bounds in depth order, so that the instance
+// emission reads them sequentially.  Measured on B200 (2^23 points): the emission gets 50 us faster but
+// the pass 90 us slower (the gather's latency is not hidden after all), so it is off.
+#ifndef INPC_SORT_CARRIES_BOUNDS
+#define INPC_SORT_CARRIES_BOUNDS 0
+#endif
+
 #ifndef INPC_MIN_BATCHES
 #define INPC_MIN_BATCHES 16
 #endif
@@ -1822,7 +1829,11 @@ int run_front(const RasterParams& rp, int64_t n, const float* positions, const v
     int rc;
     {
         StageScope scope(STAGE_SORT_DEPTH, stream);
+#if INPC_SORT_CARRIES_BOUNDS
         rc = sort_pairs(pb.keys[0], pb.keys[1], pb.ids[0], pb.ids[1], n_visible, key_bits, pb.sort_ws, &in_alt, stream, pb.bounds, pb.bounds_sorted);
+#else
+        rc = sort_pairs(pb.keys[0], pb.keys[1], pb.ids[0], pb.ids[1], n_visible, key_bits, pb.sort_ws, &in_alt, stream);
+#endif
     }
     if (rc != INPC_OK) return rc;
     const uint32_t* sorted_ids = pb.ids[in_alt];
@@ -1839,7 +1850,7 @@ int run_front(const RasterParams& rp, int64_t n, const float* positions, const v
             scan_u32_kernel<<<1, kScanThreads, 0, stream>>>(pb.inst_block_sums, ibk);
             INPC_LAUNCH_CHECK("scan_u32_kernel");
             // the depth sort's last pass left the bounds in depth order, unless it had nothing to do
-            if (n_visible > 1 && key_bits > 0)
+            if (INPC_SORT_CARRIES_BOUNDS && n_visible > 1 && key_bits > 0)
                 emit_instances_kernel<true><<<(unsigned)ibk, kInstThreads, 0, stream>>>(sorted_ids, pb.bounds_sorted, n_visible, pb.inst_block_sums, rp.gw, ib.keys[0], ib.ids[0]);
             else
                 emit_instances_kernel<false><<<(unsigned)ibk, kInstThreads, 0, stream>>>(sorted_ids, pb.bounds, n_visible, pb.inst_block_sums, rp.gw, ib.keys[0], ib.ids[0]);
