@@ -56,7 +56,7 @@ def parse_args():
     ap.add_argument("--points", type=int, default=N_POINTS)
     ap.add_argument("--tile", type=int, default=8)
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--streams", type=int, default=3, help="CUDA streams a rank pipelines its views over (1 = one view at a time)")
+    ap.add_argument("--streams", type=int, default=4, help="CUDA streams a rank pipelines its views over (1 = one view at a time)")
     ap.add_argument("--workload", default="config1", choices=["config1", "config2", "config4", "rows16", "rows32"],
                     help="config1 is the headline (default); the others are single-GPU side measurements, one JSON line each")
     return ap.parse_args()

@@ -113,10 +113,11 @@ class ViewShardedTrainer:
     The views of a shard are independent, and most kernels of the chain are bound by latency rather than
     by bandwidth, so the shard is software-pipelined over `n_streams` CUDA streams: view k runs on stream
     k mod n_streams and overlaps with its neighbours (measured on B200, 2^23 samples per view: 2.24 ms
-    per view on one stream, 1.95 on two, 1.89 on three)."""
+    per view on one stream, 1.95 on two, 1.89 on three, 1.88 on four; four also divides the 8 or 16
+    views a rank gets from a 64-view batch on 8 or 4 GPUs evenly)."""
 
     def __init__(self, tree, features: torch.Tensor, opacities: torch.Tensor, n_samples: int, seed: int,
-                 n_appearance: int = 1 << 22, tile_size: int = 8, mode: int = 0, n_streams: int = 3):
+                 n_appearance: int = 1 << 22, tile_size: int = 8, mode: int = 0, n_streams: int = 4):
         from .rasterization import INPCRasterizer
         from .sampling import ProbabilityFieldSampler
         self.tree = tree

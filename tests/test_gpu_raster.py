@@ -380,3 +380,43 @@ def test_full_size_properties():
     assert torch.allclose(out[8][2], out[16][2], rtol=1e-5, atol=1e-6)
     covered = out[8][1] > 0
     assert 0.2 < covered.float().mean().item() <= 1.0
+
+
+@needs_ref
+def test_full_size_training_step_matches_reference_backend():
+    """The bench workload itself (2^23 samples of the 2^18-leaf octree, 1237x822, forward and backward)
+    against the reference's CUDA backend on the same points, both tilings.  Depth ties (about a third of
+    the clustered samples share their depth's bit pattern with another one) are silenced first."""
+    import inpc_b200
+    from inpc_b200 import rasterization as R, sampling as S, synthetic as syn
+    cfg = syn.config1()
+    view, tree = cfg["view"].to(DEV), cfg["tree"].to(DEV)
+    feats, opac = cfg["features"].to(DEV), cfg["opacities"].to(DEV)
+    n = cfg["n_samples"]
+    pos, _ = S.ProbabilityFieldSampler(0).generate_training_samples(tree.centers, tree.levels, tree.weights, view, n, tree.initial_size)
+    settings = R.INPCRasterizer.extract_settings(view, 0)
+    _, _, _, state, blobs, _ = R.forward_with_state(pos, feats, opac, settings, 8)
+    dbg = R.debug_arrays(state, settings, blobs.point, blobs.instance)
+    opac_s = silence_depth_ties(dbg["depth"].cpu().numpy(), dbg["n_touched"].cpu().numpy() > 0, opac)
+    del dbg, blobs
+    H, W = view.camera.height, view.camera.width
+    g = torch.Generator().manual_seed(5)
+    gi = (torch.randn((4, H, W), generator=g) * 1e-3).to(DEV)
+    ga = (torch.randn((1, H, W), generator=g) * 1e-3).to(DEV)
+    rimg, ralpha, rbw = RB.forward(view, 0, pos, feats, opac_s.reshape(-1))
+    rgf, rgo, _ = RB.backward(view, 0, gi, ga, rimg, ralpha, pos, opac_s.reshape(-1))
+    for tile in (8, 16):
+        f = feats.clone().requires_grad_(True)
+        o = opac_s.clone().requires_grad_(True)
+        im, al, bw = inpc_b200.INPCRasterizer(tile_size=tile)(view, 0, pos, f, o)
+        torch.autograd.backward([im, al], [gi, ga])
+        assert_close(im.detach().cpu().numpy(), rimg.cpu().numpy(), what=f"full-size image (tile {tile})")
+        assert_close(al.detach().cpu().numpy(), ralpha.cpu().numpy(), what=f"full-size alpha (tile {tile})")
+        assert_close(bw.detach().cpu().numpy(), rbw.cpu().numpy(), what=f"full-size blending weights (tile {tile})")
+        assert_close(f.grad.float().cpu().numpy(), rgf.float().cpu().numpy(), rtol=RTOL_H, atol=ATOL_H, max_bad=36,
+                     what=f"full-size grad_features (tile {tile})")
+        # the reference sums the per-fragment terms with float atomics in arbitrary order; near-opaque
+        # fragments carry 1/max(1-alpha, 1e-8) and cancel, so a few of its own 8.4 M values move between runs
+        assert_close(o.grad.reshape(-1).cpu().numpy(), rgo.reshape(-1).cpu().numpy(), rtol=1e-4, atol=1e-9, max_bad=800,
+                     what=f"full-size grad_opacities (tile {tile})")
+        del f, o, im, al, bw
