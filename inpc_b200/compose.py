@@ -140,13 +140,27 @@ class MultisamplingRingBuffer:
         return positions, features
 
 
+_SIDE_STREAMS: dict = {}
+
+
+def _side_streams(device: torch.device, n: int) -> list:
+    """`n` persistent side streams of `device`.  They are created once: torch's caching allocator keeps a
+    pool of blocks per stream, so fresh streams on every call would allocate from the driver every time."""
+    pool = _SIDE_STREAMS.setdefault((device.type, device.index), [])
+    while len(pool) < n:
+        pool.append(torch.cuda.Stream(device=device))
+    return pool[:n]
+
+
 @torch.no_grad()
 def render_multisampled(rasterizer, view, mode: int, sample_sets, background: torch.Tensor | None = None,
                         sigma_world_scale: float = 1.0, sigma_cutoff: float = 3.0,
-                        average_with_premultiplied_alpha: bool = True):
+                        average_with_premultiplied_alpha: bool = True, n_streams: int = 1):
     """Inference over several sample sets of one view (Renderer.py:99-125 and :139-166): every set
     `(positions, features_raw)` is rasterised with `rasterizer.render`, the results are averaged and
     composed over `background`.  `sample_sets` is a list of pairs or a filled `MultisamplingRingBuffer`.
+    With `n_streams > 1` the sets are rasterised concurrently on that many CUDA streams (they are
+    independent; the accumulation order, and hence the result, stays that of the list).
     Returns (feature_image, depth, alpha, alpha_sum)."""
     if isinstance(sample_sets, MultisamplingRingBuffer):
         ring = sample_sets
@@ -154,6 +168,22 @@ def render_multisampled(rasterizer, view, mode: int, sample_sets, background: to
     else:
         sets = list(sample_sets)
     acc = MultisampleAccumulator(len(sets), average_with_premultiplied_alpha)
-    for positions, features_raw in sets:
-        acc.add(*rasterizer.render(view, mode, positions, features_raw, sigma_world_scale, sigma_cutoff))
+    if n_streams <= 1 or len(sets) < 2:
+        for positions, features_raw in sets:
+            acc.add(*rasterizer.render(view, mode, positions, features_raw, sigma_world_scale, sigma_cutoff))
+        return acc.resolve(background)
+    main = torch.cuda.current_stream()
+    streams = _side_streams(sets[0][0].device, min(n_streams, len(sets)))
+    for s in streams:
+        s.wait_stream(main)
+    rendered = []
+    for k, (positions, features_raw) in enumerate(sets):
+        with torch.cuda.stream(streams[k % len(streams)]):
+            rendered.append(rasterizer.render(view, mode, positions, features_raw, sigma_world_scale, sigma_cutoff))
+    for s in streams:
+        main.wait_stream(s)
+    for images in rendered:
+        for t in images:
+            t.record_stream(main)
+        acc.add(*images)
     return acc.resolve(background)

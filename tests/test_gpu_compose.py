@@ -122,3 +122,7 @@ def test_ring_buffer_and_multisampled_render():
         np.testing.assert_array_equal(d.cpu().numpy(), rd)
         np.testing.assert_array_equal(a.cpu().numpy(), ra)
         np.testing.assert_array_equal(s.cpu().numpy(), rs)
+        # rasterising the sets concurrently on several streams changes nothing
+        ring.read_idx = 0
+        f2, d2, a2, s2 = render_multisampled(rast, v, 0, ring, bg, 1.0, 3.0, premult, n_streams=3)
+        assert torch.equal(f2, f) and torch.equal(d2, d) and torch.equal(a2, a) and torch.equal(s2, s)
