@@ -24,6 +24,14 @@
 #define INPC_SORT_CARRIES_BOUNDS 0
 #endif
 
+// Resident blocks per SM the 8x8 blend kernels are compiled for (caps their registers).
+#ifndef INPC_FWD_MIN_BLOCKS
+#define INPC_FWD_MIN_BLOCKS 1
+#endif
+#ifndef INPC_BWD_MIN_BLOCKS
+#define INPC_BWD_MIN_BLOCKS 1
+#endif
+
 #ifndef INPC_MIN_BATCHES
 #define INPC_MIN_BATCHES 16
 #endif
@@ -768,7 +776,7 @@ __global__ void __launch_bounds__(T * T) blend_prefix_kernel(const Segment* __re
 }
 
 template <int T, int IPT, int KIND>
-__global__ void __launch_bounds__(T * T) blend_bilinear_forward_kernel(
+__global__ void __launch_bounds__(T * T, T == 8 ? INPC_FWD_MIN_BLOCKS : 1) blend_bilinear_forward_kernel(
     const Segment* __restrict__ segs, const uint32_t* __restrict__ n_segments, const uint32_t* __restrict__ inst_ids,
     const PointRec* __restrict__ rec, float* __restrict__ seg_T, float4* __restrict__ seg_C, float* __restrict__ seg_Z,
     float* __restrict__ image, float* __restrict__ depth_image, float* __restrict__ alpha_image,
@@ -965,7 +973,7 @@ __global__ void __launch_bounds__(T * T) blend_combine_kernel(const Segment* __r
 }
 
 template <int T, int IPT>
-__global__ void __launch_bounds__(T * T) blend_bilinear_backward_kernel(
+__global__ void __launch_bounds__(T * T, T == 8 ? INPC_BWD_MIN_BLOCKS : 1) blend_bilinear_backward_kernel(
     const Segment* __restrict__ segs, const uint32_t* __restrict__ n_segments, const uint32_t* __restrict__ inst_ids,
     const PointRec* __restrict__ rec, const float* __restrict__ seg_T, const float4* __restrict__ seg_C,
     const float* __restrict__ grad_image, const float* __restrict__ grad_alpha, const float* __restrict__ image,
