@@ -536,7 +536,10 @@ struct __align__(16) Segment {
     uint32_t begin, end;   // instance range of this segment
     uint32_t info;         // index of the segment within its tile | number of segments of the tile << 16
 };
-constexpr int kMaxSegmentsPerTile = 64;
+#ifndef INPC_MAX_SEGMENTS
+#define INPC_MAX_SEGMENTS 64
+#endif
+constexpr int kMaxSegmentsPerTile = INPC_MAX_SEGMENTS;
 constexpr int kMinBatchesPerSegment = INPC_MIN_BATCHES;
 #ifndef INPC_IPT8
 #define INPC_IPT8 1
