@@ -19,6 +19,9 @@ namespace {
 constexpr int kRadixBits = 9;            // widest digit of a pass: 27 key bits sort in 3 passes, 32 in 4 x 8
 constexpr int kRadix = 1 << kRadixBits;  // capacity of every per-digit array
 constexpr int kMaxPasses = 4;
+#ifndef INPC_SORT_SMEM_PAD
+#define INPC_SORT_SMEM_PAD 0
+#endif
 #ifndef INPC_SORT_THREADS
 #define INPC_SORT_THREADS 512
 #endif
@@ -308,9 +311,12 @@ int launch_onesweep_instance(int64_t tiles, const uint32_t* kin, const uint32_t*
                              const unsigned* base, unsigned* state, unsigned* ticket, unsigned* status, const uint2* aux_in, uint2* aux_out,
                              cudaStream_t stream) {
     static bool attr_set[kMaxDevices] = {false};
-    const int rc = opt_in_dynamic_smem(radix_onesweep_pass_kernel<BITS, AUX>, sizeof(PassSmem), attr_set);
+    // INPC_SORT_SMEM_PAD bytes of unused shared memory per block lower the number of resident blocks
+    // per SM (a tuning knob: fewer sort blocks leave room for kernels of other streams)
+    constexpr size_t kSmemBytes = sizeof(PassSmem) + INPC_SORT_SMEM_PAD;
+    const int rc = opt_in_dynamic_smem(radix_onesweep_pass_kernel<BITS, AUX>, kSmemBytes, attr_set);
     if (rc != INPC_OK) return rc;
-    radix_onesweep_pass_kernel<BITS, AUX><<<(unsigned)tiles, kThreads, sizeof(PassSmem), stream>>>(kin, vin, kout, vout, n, shift, bits, base, state, ticket,
+    radix_onesweep_pass_kernel<BITS, AUX><<<(unsigned)tiles, kThreads, kSmemBytes, stream>>>(kin, vin, kout, vout, n, shift, bits, base, state, ticket,
                                                                                               status, aux_in, aux_out);
     INPC_LAUNCH_CHECK("radix_onesweep_pass_kernel");
     return INPC_OK;
