@@ -133,7 +133,7 @@ int inpc_render_preextracted(int mode, int tile_size, const inpc_view* view, int
                              float* depth, float* alpha, inpc_alloc_fn alloc_point,
                              inpc_alloc_fn alloc_instance, void* alloc_user, void* stream);
 
-/* Feature-row layout (bilinear splats): every point carries `channels` fp32 values (4, 16 or 32;
+/* Feature-row layout (bilinear splats): every point carries `channels` fp32 values (4, 8, 16 or 32;
  * features (n, channels), 16-byte aligned) that are blended as they are, without spherical
  * harmonics, into image (channels,H,W).  alpha (H,W), blending_weights (n), the scratch callbacks
  * and `state` are as in inpc_rasterize_forward.

@@ -2024,14 +2024,16 @@ template <typename F>
 int dispatch_rows(int tile, int channels, F&& f) {
     if (tile == 8) {
         if (channels == 4) return f(std::integral_constant<int, 8>(), std::integral_constant<int, 1>());
+        if (channels == 8) return f(std::integral_constant<int, 8>(), std::integral_constant<int, 2>());
         if (channels == 16) return f(std::integral_constant<int, 8>(), std::integral_constant<int, 4>());
         if (channels == 32) return f(std::integral_constant<int, 8>(), std::integral_constant<int, 8>());
     } else if (tile == 16) {
         if (channels == 4) return f(std::integral_constant<int, 16>(), std::integral_constant<int, 1>());
+        if (channels == 8) return f(std::integral_constant<int, 16>(), std::integral_constant<int, 2>());
         if (channels == 16) return f(std::integral_constant<int, 16>(), std::integral_constant<int, 4>());
         if (channels == 32) return f(std::integral_constant<int, 16>(), std::integral_constant<int, 8>());
     }
-    set_error("feature rows: channels must be 4, 16 or 32 (got %d) and tile_size 8 or 16 (got %d)", channels, tile);
+    set_error("feature rows: channels must be 4, 8, 16 or 32 (got %d) and tile_size 8 or 16 (got %d)", channels, tile);
     return INPC_E_INVALID;
 }
 
@@ -2180,7 +2182,7 @@ namespace {
 int check_rows(const inpc_view* view, int tile_size, int64_t n, int channels) {
     const int rc = check_view(view, tile_size, INPC_MODE_BILINEAR, n);
     if (rc != INPC_OK) return rc;
-    if (channels != 4 && channels != 16 && channels != 32) { set_error("feature rows: channels must be 4, 16 or 32, got %d", channels); return INPC_E_INVALID; }
+    if (channels != 4 && channels != 8 && channels != 16 && channels != 32) { set_error("feature rows: channels must be 4, 8, 16 or 32, got %d", channels); return INPC_E_INVALID; }
     return INPC_OK;
 }
 }  // namespace

@@ -198,8 +198,8 @@ def _check_rows(positions, features, opacities):
     n = positions.shape[0]
     if positions.dim() != 2 or positions.shape[1] != 3:
         raise ValueError(f"positions must be (N,3), got {tuple(positions.shape)}")
-    if features.dim() != 2 or features.shape[0] != n or features.shape[1] not in (4, 16, 32):
-        raise ValueError(f"features must be (N,C) with C in (4, 16, 32), got {tuple(features.shape)}")
+    if features.dim() != 2 or features.shape[0] != n or features.shape[1] not in (4, 8, 16, 32):
+        raise ValueError(f"features must be (N,C) with C in (4, 8, 16, 32), got {tuple(features.shape)}")
     if opacities.numel() != n:
         raise ValueError(f"opacities must hold N={n} values, got {tuple(opacities.shape)}")
     return positions, features, opacities
@@ -355,7 +355,7 @@ class INPCRasterizer(torch.nn.Module):
 
 
     def forward_rows(self, view, positions: torch.Tensor, features: torch.Tensor, opacities: torch.Tensor):
-        """Bilinear training forward over (N,C) fp32 feature rows, C in (4, 16, 32): the features are
+        """Bilinear training forward over (N,C) fp32 feature rows, C in (4, 8, 16, 32): the features are
         blended as they are into a (C,H,W) image (differentiable w.r.t. features and opacities).  The
         reference has no such layout; its only one is 36 SH halves -> 4 channels (`forward`)."""
         return _RasterizeRows.apply(positions, features, opacities, self.extract_settings(view, 0), self.tile_size)

@@ -72,3 +72,28 @@ def test_random_scene_matches_oracle(seed):
         assert_close(img.cpu().numpy(), oi, what=f"seed {seed} tile {tile} inference image")
         assert_close(dep.cpu().numpy(), od, rtol=1e-5, atol=1e-5, what=f"seed {seed} tile {tile} inference depth")
         assert_close(alp.cpu().numpy(), oa, what=f"seed {seed} tile {tile} inference alpha")
+
+
+@pytest.mark.parametrize("seed", [100, 101, 102, 103])
+def test_random_scene_gaussian_mode_matches_oracle(seed):
+    """Gaussian splats (fast exponentials on the device, libm in the oracle: looser tolerances)."""
+    import inpc_b200
+    view, pos, feats, opac, g = _scene(seed)
+    pos, feats, opac = pos[:600], feats[:600], opac[:600]
+    cam = oracle_camera(view)
+    v = view.to(DEV)
+    H, W = view.camera.height, view.camera.width
+    gi = torch.randn((4, H, W), generator=g) * 1e-3
+    ga = torch.randn((1, H, W), generator=g) * 1e-3
+    for tile in (8, 16):
+        f = feats.to(DEV).requires_grad_(True)
+        o = opac.to(DEV).requires_grad_(True)
+        image, alpha, bw = inpc_b200.INPCRasterizer(tile_size=tile)(v, 1, pos.to(DEV), f, o)
+        st = O.rasterize_forward(O.GAUSSIAN, cam, pos.numpy(), feats.numpy(), opac.numpy(), tile=tile)
+        assert_close(image.detach().cpu().numpy(), st.image, rtol=1e-4, atol=1e-5, max_bad=4, what=f"seed {seed} tile {tile} gaussian image")
+        assert_close(alpha.detach().cpu().numpy(), st.alpha, rtol=1e-4, atol=1e-5, max_bad=4, what=f"seed {seed} tile {tile} gaussian alpha")
+        torch.autograd.backward([image, alpha], [gi.to(DEV), ga.to(DEV)])
+        gf, go, _ = O.rasterize_backward(st, gi.numpy(), ga.numpy())
+        assert_close(o.grad.detach().cpu().numpy(), go, rtol=1e-3, atol=1e-8, max_bad=8, what=f"seed {seed} tile {tile} gaussian grad_opacities")
+        assert_close(f.grad.float().detach().cpu().numpy(), gf.astype(np.float32), rtol=4e-3, atol=2e-7, max_bad=36 * 8,
+                     what=f"seed {seed} tile {tile} gaussian grad_features")

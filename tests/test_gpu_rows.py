@@ -1,4 +1,4 @@
-"""GPU parity tests of the feature-row layout ((N,C) fp32 features blended as they are, C = 4, 16, 32)
+"""GPU parity tests of the feature-row layout ((N,C) fp32 features blended as they are, C = 4, 8, 16, 32)
 through the Python mirror and hence the C ABI: against the CPU oracle run as C/4 four-channel passes
 and, where oracle/_ref is built, against C/4 runs of the reference's own CUDA backend on DC-only
 spherical-harmonics coefficients.
@@ -35,7 +35,7 @@ def _silenced(view, pos, opac):
 
 
 @pytest.mark.parametrize("tile", [8, 16])
-@pytest.mark.parametrize("channels", [4, 16, 32])
+@pytest.mark.parametrize("channels", [4, 8, 16, 32])
 def test_rows_forward_backward_match_oracle(channels, tile):
     import inpc_b200
     view, pos, _, opac = small_scene(n=12000, width=136, height=104, focal=120.0)
