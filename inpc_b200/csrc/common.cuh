@@ -57,6 +57,7 @@ enum : unsigned {
     STATUS_LOOKBACK_TIMEOUT = 0,   // a radix-sort tile gave up waiting for a predecessor tile
     STATUS_SAMPLER_EXHAUSTED = 1,  // informational: some sample slots ran out of rejection attempts
     STATUS_BULK_COPY_TIMEOUT = 2,  // a block gave up waiting for its bulk copy into shared memory
+    STATUS_INDEX_OUT_OF_RANGE = 3, // checked build only: a gather index was outside its array (the access was skipped)
     STATUS_WORDS = 4,
 };
 unsigned* device_status_ptr();            // device pointer to STATUS_WORDS words (allocated on first use)

@@ -45,6 +45,24 @@ constexpr float kOneMinusAlphaEps = 1e-8f;      // include/bilinear/config.h:17
 constexpr float kDilation = 0.16f;              // include/gaussian/config.h:19
 constexpr float kTrainGaussThreshold = 0.01110899653f;   // src/gaussian/kernels.cu:452
 
+// Checked build (-DINPC_CHECK_INDICES, `python -m inpc_b200._build --checked`): every point index read
+// from a sorted list is range-checked before it is used for a gather; a bad one is counted, reported
+// through a status word and replaced by 0, so the access itself never leaves its array.  The limit
+// lives in a device variable the entry points set before they launch anything.
+#ifdef INPC_CHECK_INDICES
+__device__ unsigned long long g_check_n_points;
+__device__ unsigned g_check_failures;
+__device__ __forceinline__ uint32_t checked_point(uint32_t id) {
+    if ((unsigned long long)id >= g_check_n_points) {
+        atomicAdd(&g_check_failures, 1u);
+        return 0u;
+    }
+    return id;
+}
+#else
+__device__ __forceinline__ uint32_t checked_point(uint32_t id) { return id; }
+#endif
+
 enum { VAR_TRAIN = 0, VAR_RAW37 = 1, VAR_PREEXTRACTED = 2, VAR_ROWS = 3 };   // VAR_ROWS: features stay in the caller's (n, C) fp32 array
 
 struct __align__(16) PointRec {
@@ -422,7 +440,7 @@ __global__ void __launch_bounds__(kInstThreads / 4) instance_count_kernel(const 
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
             const int64_t s = first + q;
-            if (s < n_visible) c += PACKED ? (__ldg(sorted_keys + s) >> kCountShift) + 1u : tiles_of(__ldg(bounds + __ldg(sorted_ids + s)));
+            if (s < n_visible) c += PACKED ? (__ldg(sorted_keys + s) >> kCountShift) + 1u : tiles_of(__ldg(bounds + checked_point(__ldg(sorted_ids + s))));
         }
     }
 #pragma unroll
@@ -474,7 +492,7 @@ __global__ void __launch_bounds__(kInstThreads) emit_instances_kernel(const uint
     const int64_t s = (int64_t)blockIdx.x * kInstThreads + threadIdx.x;
     uint32_t id = 0;
     uint2 b = make_uint2(0u, 0u);
-    if (s < n_visible) { id = __ldg(sorted_ids + s); b = __ldg(bounds + (SORTED ? s : (int64_t)id)); }
+    if (s < n_visible) { id = checked_point(__ldg(sorted_ids + s)); b = __ldg(bounds + (SORTED ? s : (int64_t)id)); }
     const unsigned c = tiles_of(b);
     unsigned total;
     unsigned off = block_base[blockIdx.x] + block_exclusive_scan(c, s_scan, &total);
@@ -616,7 +634,7 @@ __device__ __forceinline__ uint32_t stage_instance(int j, int cnt, unsigned base
                                                    float4* s_f, unsigned (*s_mask)[T * T]) {
     uint32_t id = 0;
     if (j < cnt) {
-        id = __ldg(inst_ids + base + j);
+        id = checked_point(__ldg(inst_ids + base + j));
         const float4* r = reinterpret_cast<const float4*>(rec + id);
         const float4 a = __ldg(r);
         s_a[j] = a;
@@ -654,7 +672,7 @@ __device__ __forceinline__ Fetched<NEED_F> fetch_instance(int j, int cnt, unsign
     r.a = make_float4(0.f, 0.f, 0.f, 0.f);
     r.f = make_float4(0.f, 0.f, 0.f, 0.f);
     if (j < cnt) {
-        r.id = __ldg(inst_ids + base + j);
+        r.id = checked_point(__ldg(inst_ids + base + j));
         const float4* p = reinterpret_cast<const float4*>(rec + r.id);
         r.a = __ldg(p);
         if (NEED_F) r.f = __ldg(p + 1);
@@ -1484,7 +1502,7 @@ __global__ void __launch_bounds__(T * T) blend_gaussian_forward_kernel(
         if (__syncthreads_count(done) == B) break;
         const int cnt = (int)min((unsigned)B, range.y - base);
         if (t < cnt) {
-            const uint32_t id = __ldg(inst_ids + base + t);
+            const uint32_t id = checked_point(__ldg(inst_ids + base + t));
             const float4* r = reinterpret_cast<const float4*>(rec + id);
             s_a[t] = __ldg(r);
             s_f[t] = __ldg(r + 1);
@@ -1565,7 +1583,7 @@ __global__ void __launch_bounds__(T * T) blend_gaussian_backward_kernel(
         if (__syncthreads_count(done) == B) break;
         const int cnt = (int)min((unsigned)B, range.y - base);
         if (t < cnt) {
-            const uint32_t id = __ldg(inst_ids + base + t);
+            const uint32_t id = checked_point(__ldg(inst_ids + base + t));
             const float4* r = reinterpret_cast<const float4*>(rec + id);
             s_a[t] = __ldg(r);
             s_f[t] = __ldg(r + 1);
@@ -1772,6 +1790,34 @@ int check_view(const inpc_view* v, int tile_size, int mode, int64_t n) {
     return INPC_OK;
 }
 
+// Checked build: publish the index limit before a call's kernels / collect the failure count after them.
+int begin_index_checks(int64_t n_points, cudaStream_t stream) {
+#ifdef INPC_CHECK_INDICES
+    const unsigned long long limit = (unsigned long long)n_points;
+    const unsigned zero = 0;
+    INPC_CUDA_TRY(cudaMemcpyToSymbolAsync(g_check_n_points, &limit, sizeof(limit), 0, cudaMemcpyHostToDevice, stream));
+    INPC_CUDA_TRY(cudaMemcpyToSymbolAsync(g_check_failures, &zero, sizeof(zero), 0, cudaMemcpyHostToDevice, stream));
+#else
+    (void)n_points; (void)stream;
+#endif
+    return INPC_OK;
+}
+
+int end_index_checks(cudaStream_t stream) {
+#ifdef INPC_CHECK_INDICES
+    unsigned failures = 0;
+    INPC_CUDA_TRY(cudaMemcpyFromSymbolAsync(&failures, g_check_failures, sizeof(failures), 0, cudaMemcpyDeviceToHost, stream));
+    INPC_CUDA_TRY(cudaStreamSynchronize(stream));
+    if (failures) {
+        set_error("checked build: %u point indices read from the sorted lists were out of range (accesses skipped)", failures);
+        return INPC_E_DEVICE;
+    }
+#else
+    (void)stream;
+#endif
+    return INPC_OK;
+}
+
 template <int MODE, int VARIANT>
 int run_front(const RasterParams& rp, int64_t n, const float* positions, const void* features, const float* opacities,
               inpc_alloc_fn alloc_point, inpc_alloc_fn alloc_instance, void* user, inpc_raster_state* st,
@@ -1782,6 +1828,10 @@ int run_front(const RasterParams& rp, int64_t n, const float* positions, const v
     void* pblob = alloc_point(user, sizing.total);
     if (!pblob) { set_error("point allocator returned NULL for %zu bytes", sizing.total); return INPC_E_ALLOC; }
     const PointBlob pb = carve_point_blob(pblob, n, MODE);
+    {
+        const int rc_check = begin_index_checks(n, stream);
+        if (rc_check != INPC_OK) return rc_check;
+    }
 
     int64_t n_visible = 0, n_instances = 0;
     uint32_t key_base = 0;
@@ -1812,6 +1862,13 @@ int run_front(const RasterParams& rp, int64_t n, const float* positions, const v
         INPC_CUDA_TRY(cudaEventSynchronize(ready));
         n_visible = (int64_t)host[0];
         n_instances = (int64_t)host[1];
+        // counts that cannot be: more survivors than points, or (bilinear: at most 2x2 tiles per splat)
+        // more instances than four per survivor, or instances without survivors
+        if (n_visible > n || (n_visible == 0 && n_instances != 0) || (MODE == INPC_MODE_BILINEAR && n_instances > 4 * n_visible)) {
+            set_error("inconsistent counts from the visibility pass: %lld visible of %lld points, %lld instances", (long long)n_visible,
+                      (long long)n, (long long)n_instances);
+            return INPC_E_DEVICE;
+        }
         if (n_visible > 0) {
             key_base = (uint32_t)host[2];
             key_bits = bit_length((uint32_t)host[3] - key_base);
@@ -2048,10 +2105,13 @@ int rows_forward(int tile_size, const inpc_view* view, int64_t n, const float* p
                                                      KIND == BLEND_INFER, &pb, &ib, stream, channels / 4);
     if (rc != INPC_OK) return rc;
     const uint32_t* ids = ib.ids[tile_result_buffer(state->n_instances, rp.gw * rp.gh)];
-    StageScope scope(STAGE_BLEND_FWD, stream);
-    return dispatch_rows(tile_size, channels, [&](auto t, auto c4) {
-        return launch_rows_forward<decltype(t)::value, decltype(c4)::value, KIND>(rp, pb, ib, ids, features, image, depth, alpha, blending_weights, stream);
-    });
+    {
+        StageScope scope(STAGE_BLEND_FWD, stream);
+        rc = dispatch_rows(tile_size, channels, [&](auto t, auto c4) {
+            return launch_rows_forward<decltype(t)::value, decltype(c4)::value, KIND>(rp, pb, ib, ids, features, image, depth, alpha, blending_weights, stream);
+        });
+    }
+    return rc != INPC_OK ? rc : end_index_checks(stream);
 }
 
 }  // namespace
@@ -2080,7 +2140,8 @@ extern "C" int inpc_rasterize_forward(int mode, int tile_size, const inpc_view* 
     else
         rc = run_front<INPC_MODE_GAUSSIAN, VAR_TRAIN>(rp, n, positions, features, opacities, alloc_point, alloc_instance, alloc_user, state, false, &pb, &ib, stream);
     if (rc != INPC_OK) return rc;
-    return launch_blend_forward<BLEND_TRAIN>(mode, rp, pb, ib, state->n_instances, image, nullptr, alpha, blending_weights, kTrainGaussThreshold, stream);
+    rc = launch_blend_forward<BLEND_TRAIN>(mode, rp, pb, ib, state->n_instances, image, nullptr, alpha, blending_weights, kTrainGaussThreshold, stream);
+    return rc != INPC_OK ? rc : end_index_checks(stream);
 }
 
 extern "C" int inpc_rasterize_backward(const inpc_raster_state* state, const inpc_view* view, const float* grad_image,
@@ -2098,6 +2159,8 @@ extern "C" int inpc_rasterize_backward(const inpc_raster_state* state, const inp
     }
     (void)opacities;   // the opacity travels in the point record
     if (n == 0) return INPC_OK;
+    rc = begin_index_checks(n, stream);
+    if (rc != INPC_OK) return rc;
     const RasterParams rp = make_params(view, state->tile_size, 0.0f, 3.0f, nullptr);
     const int n_tiles = rp.gw * rp.gh;
     const PointBlob pb = carve_point_blob(state->point_blob, n, state->mode);
@@ -2125,7 +2188,7 @@ extern "C" int inpc_rasterize_backward(const inpc_raster_state* state, const inp
     preprocess_backward_kernel<<<(unsigned)ceil_div<int64_t>(n, kPreThreads), kPreThreads, 0, stream>>>(
         positions, view->cam_position, pb.bounds, gfv, static_cast<__half*>(grad_features), n, (reinterpret_cast<uintptr_t>(grad_features) & 15u) == 0);
     INPC_LAUNCH_CHECK("preprocess_backward_kernel");
-    return INPC_OK;
+    return end_index_checks(stream);
 }
 
 extern "C" int inpc_render(int mode, int tile_size, const inpc_view* view, int64_t n, const float* positions,
@@ -2150,7 +2213,8 @@ extern "C" int inpc_render(int mode, int tile_size, const inpc_view* view, int64
     if (rc != INPC_OK) return rc;
     // runtime cut-off exp(-cutoff^2/2): src/gaussian/inference.cu:171
     const float threshold = expf(-0.5f * sigma_cutoff * sigma_cutoff);
-    return launch_blend_forward<BLEND_INFER>(mode, rp, pb, ib, st.n_instances, image, depth, alpha, nullptr, threshold, stream);
+    rc = launch_blend_forward<BLEND_INFER>(mode, rp, pb, ib, st.n_instances, image, depth, alpha, nullptr, threshold, stream);
+    return rc != INPC_OK ? rc : end_index_checks(stream);
 }
 
 extern "C" int inpc_render_preextracted(int mode, int tile_size, const inpc_view* view, int64_t n, const float* positions,
@@ -2175,7 +2239,8 @@ extern "C" int inpc_render_preextracted(int mode, int tile_size, const inpc_view
         rc = run_front<INPC_MODE_GAUSSIAN, VAR_PREEXTRACTED>(rp, n, positions, features, opacities, alloc_point, alloc_instance, alloc_user, &st, true, &pb, &ib, stream);
     if (rc != INPC_OK) return rc;
     const float threshold = expf(-0.5f * sigma_cutoff * sigma_cutoff);
-    return launch_blend_forward<BLEND_INFER>(mode, rp, pb, ib, st.n_instances, image, depth, alpha, nullptr, threshold, stream);
+    rc = launch_blend_forward<BLEND_INFER>(mode, rp, pb, ib, st.n_instances, image, depth, alpha, nullptr, threshold, stream);
+    return rc != INPC_OK ? rc : end_index_checks(stream);
 }
 
 namespace {
@@ -2246,11 +2311,16 @@ extern "C" int inpc_rasterize_rows_backward(const inpc_raster_state* state, cons
     const uint32_t* ids = ib.ids[tile_result_buffer(state->n_instances, n_tiles)];
     INPC_CUDA_TRY(cudaMemsetAsync(grad_features, 0, sizeof(float) * (size_t)n * channels, stream));
     INPC_CUDA_TRY(cudaMemsetAsync(grad_opacities, 0, sizeof(float) * (size_t)n, stream));
-    StageScope scope(STAGE_BLEND_BWD, stream);
-    return dispatch_rows(state->tile_size, channels, [&](auto t, auto c4) {
-        return launch_rows_backward<decltype(t)::value, decltype(c4)::value>(rp, pb, ib, ids, features, grad_image, grad_alpha, image, alpha,
-                                                                            grad_features, grad_opacities, stream);
-    });
+    rc = begin_index_checks(n, stream);
+    if (rc != INPC_OK) return rc;
+    {
+        StageScope scope(STAGE_BLEND_BWD, stream);
+        rc = dispatch_rows(state->tile_size, channels, [&](auto t, auto c4) {
+            return launch_rows_backward<decltype(t)::value, decltype(c4)::value>(rp, pb, ib, ids, features, grad_image, grad_alpha, image, alpha,
+                                                                                grad_features, grad_opacities, stream);
+        });
+    }
+    return rc != INPC_OK ? rc : end_index_checks(stream);
 }
 
 namespace inpc_debug {
