@@ -1475,95 +1475,238 @@ __global__ void __launch_bounds__(T * T) blend_rows_backward_kernel(
 }
 
 // ------------------------------------------------------------------------------------------------
-// Gaussian blend: footprints are not bounded by 2x2 pixels, so every pixel tests every staged point
-// (src/gaussian/kernels.cu:401-474 forward, :476-579 backward, :581-660 inference).
+// Gaussian blend (src/gaussian/kernels.cu:401-474 forward, :476-579 backward, :581-660 inference).
+// A footprint is an ellipse of a few pixels, not a fixed 2x2: the staging thread sets its instance's bit
+// for the pixels of the ellipse's bounding box inside the tile (slightly widened, so a superset of the
+// pixels that pass the reference's tests), and every pixel thread walks only its set bits and applies
+// the reference's tests and arithmetic unchanged.  Per-point sums (blending weight, gradients) are
+// accumulated with shared-memory atomics per staged instance and leave with one global atomic per
+// instance (the reference issues global atomics per fragment).
 // ------------------------------------------------------------------------------------------------
+template <int T>
+__device__ __forceinline__ void gaussian_mask_bits(int j, const float4& a, const float4& c, float neg_log_threshold, int tile_x, int tile_y,
+                                                   unsigned (*s_mask)[T * T]) {
+    // points with  -0.5 d^T Conic d >= -L  lie within |dx| <= sqrt(2 L cov_xx), |dy| <= sqrt(2 L cov_yy),
+    // cov = Conic^-1
+    const float det = c.x * c.z - c.y * c.y;
+    int x0 = 0, x1 = T - 1, y0 = 0, y1 = T - 1;
+    if (det > 0.0f) {
+        const float s = 2.0f * neg_log_threshold / det;
+        const float rx = sqrtf(fmaxf(s * c.z, 0.0f)) * 1.001f + 0.01f;
+        const float ry = sqrtf(fmaxf(s * c.x, 0.0f)) * 1.001f + 0.01f;
+        x0 = max(0, __float2int_ru(a.x - rx - 0.5f) - tile_x * T);
+        x1 = min(T - 1, __float2int_rd(a.x + rx - 0.5f) - tile_x * T);
+        y0 = max(0, __float2int_ru(a.y - ry - 0.5f) - tile_y * T);
+        y1 = min(T - 1, __float2int_rd(a.y + ry - 0.5f) - tile_y * T);
+    }
+    const unsigned bit = 1u << (j & 31);
+    unsigned* mrow = s_mask[j >> 5];
+    for (int y = y0; y <= y1; ++y)
+        for (int x = x0; x <= x1; ++x) atomicOr(mrow + y * T + x, bit);
+}
+
+// Pass 1 of the segmented gaussian blend (tiles with several segments only): per-pixel product of
+// (1 - alpha) over one segment; FAST selects the exponential of the inference kernels.
+template <int T, bool FAST>
+__global__ void __launch_bounds__(T * T) blend_gaussian_transmittance_kernel(
+    const Segment* __restrict__ segs, const uint32_t* __restrict__ n_segments, const uint32_t* __restrict__ inst_ids,
+    const PointRec* __restrict__ rec, const float4* __restrict__ conic, float* __restrict__ seg_T, int width, int height, int gw,
+    float threshold, float neg_log_threshold) {
+    constexpr int B = T * T;
+    constexpr int WORDS = B / 32;
+    if (blockIdx.x >= *n_segments) return;
+    const Segment sg = segs[blockIdx.x];
+    const unsigned seg_idx = sg.info & 0xffffu, n_seg = sg.info >> 16;
+    if (n_seg == 1u || seg_idx == n_seg - 1u) return;
+    __shared__ float4 s_a[B];
+    __shared__ float4 s_c[B];
+    __shared__ unsigned s_mask[WORDS][B];
+    const int t = threadIdx.x;
+    const int tx = (int)(sg.tile % (unsigned)gw), ty = (int)(sg.tile / (unsigned)gw);
+    const int px = tx * T + t % T, py = ty * T + t / T;
+    const float pcx = (float)px + 0.5f, pcy = (float)py + 0.5f;
+#pragma unroll
+    for (int w = 0; w < WORDS; ++w) s_mask[w][t] = 0u;
+    float Tr = 1.0f;
+    bool done = !(px < width && py < height);
+    for (unsigned base = sg.begin; base < sg.end; base += B) {
+        if (__syncthreads_count(done) == B) break;
+        const int cnt = (int)min((unsigned)B, sg.end - base);
+        if (t < cnt) {
+            const uint32_t id = checked_point(__ldg(inst_ids + base + t));
+            const float4 a = __ldg(reinterpret_cast<const float4*>(rec + id));
+            const float4 c = __ldg(conic + id);
+            s_a[t] = a;
+            s_c[t] = c;
+            gaussian_mask_bits<T>(t, a, c, neg_log_threshold, tx, ty, s_mask);
+        }
+        __syncthreads();
+#pragma unroll 1
+        for (int w = 0; w < WORDS; ++w) {
+            unsigned mbits = s_mask[w][t];
+            if (mbits) s_mask[w][t] = 0u;
+            while (mbits && !done) {
+                const int j = w * 32 + __ffs(mbits) - 1;
+                mbits &= mbits - 1u;
+                const float4 a = s_a[j];
+                const float4 c = s_c[j];
+                const float dx = a.x - pcx, dy = a.y - pcy;
+                const float e = -0.5f * (c.x * dx * dx + c.z * dy * dy) - c.y * dx * dy;
+                if (e > 0.0f) continue;
+                const float G = FAST ? __expf(e) : expf(e);
+                if (G < threshold) continue;
+                Tr *= 1.0f - a.z * G;
+                if (Tr < kTransmittanceEps) done = true;
+            }
+        }
+    }
+    seg_T[(size_t)blockIdx.x * B + t] = Tr;
+}
+
+// Main pass: one block per (tile, segment), starting from the segment's incoming transmittance.
 template <int T, int KIND>
 __global__ void __launch_bounds__(T * T) blend_gaussian_forward_kernel(
-    const uint2* __restrict__ ranges, const uint32_t* __restrict__ inst_ids, const PointRec* __restrict__ rec,
-    const float4* __restrict__ conic, float* __restrict__ image, float* __restrict__ depth_image,
+    const Segment* __restrict__ segs, const uint32_t* __restrict__ n_segments, const uint32_t* __restrict__ inst_ids,
+    const PointRec* __restrict__ rec, const float4* __restrict__ conic, float* __restrict__ seg_T, float4* __restrict__ seg_C,
+    float* __restrict__ seg_Z, float* __restrict__ image, float* __restrict__ depth_image,
     float* __restrict__ alpha_image, float* __restrict__ blending_weights, int width, int height, int gw,
-    float threshold) {
+    float threshold, float neg_log_threshold) {
     constexpr int B = T * T;
+    constexpr int WORDS = B / 32;
+    if (blockIdx.x >= *n_segments) return;
+    const Segment sg = segs[blockIdx.x];
+    const unsigned seg_idx = sg.info & 0xffffu, n_seg = sg.info >> 16;
     __shared__ float4 s_a[B];
     __shared__ float4 s_f[B];
     __shared__ float4 s_c[B];
     __shared__ uint32_t s_id[B];
+    __shared__ unsigned s_mask[WORDS][B];
+    __shared__ float s_bw[KIND == BLEND_TRAIN ? B : 1];
     const int t = threadIdx.x;
-    const int tile = blockIdx.x;
-    const int tx = tile % gw, ty = tile / gw;
+    const int tx = (int)(sg.tile % (unsigned)gw), ty = (int)(sg.tile / (unsigned)gw);
     const int px = tx * T + t % T, py = ty * T + t / T;
     const bool inside = px < width && py < height;
     const float pcx = (float)px + 0.5f, pcy = (float)py + 0.5f;
+    const size_t state_idx = (size_t)blockIdx.x * B + t;
+#pragma unroll
+    for (int w = 0; w < WORDS; ++w) s_mask[w][t] = 0u;
+    if (KIND == BLEND_TRAIN) s_bw[t] = 0.0f;
     float C0 = 0.f, C1 = 0.f, C2 = 0.f, C3 = 0.f, Z = 0.f, Tr = 1.0f;
-    bool done = !inside;
-    const uint2 range = __ldg(ranges + tile);
-    for (unsigned base = range.x; base < range.y; base += B) {
-        if (__syncthreads_count(done) == B) break;
-        const int cnt = (int)min((unsigned)B, range.y - base);
+    if (seg_idx > 0u && inside) Tr = seg_T[state_idx];
+    bool done = !inside || Tr < kTransmittanceEps;
+    int cnt = 0;
+    auto flush_weights = [&]() {
+        if (t < cnt) {
+            const float sum = s_bw[t];
+            if (sum > 0.0f) atomicAdd(blending_weights + s_id[t], sum);
+            s_bw[t] = 0.0f;
+        }
+    };
+    for (unsigned base = sg.begin; base < sg.end; base += B) {
+        if (__syncthreads_count(done) == B) break;     // also: every thread has finished the batch before
+        if (KIND == BLEND_TRAIN) flush_weights();
+        cnt = (int)min((unsigned)B, sg.end - base);
         if (t < cnt) {
             const uint32_t id = checked_point(__ldg(inst_ids + base + t));
             const float4* r = reinterpret_cast<const float4*>(rec + id);
-            s_a[t] = __ldg(r);
+            const float4 a = __ldg(r);
+            const float4 c = __ldg(conic + id);
+            s_a[t] = a;
             s_f[t] = __ldg(r + 1);
-            s_c[t] = __ldg(conic + id);
+            s_c[t] = c;
             s_id[t] = id;
+            gaussian_mask_bits<T>(t, a, c, neg_log_threshold, tx, ty, s_mask);
         }
         __syncthreads();
-        for (int j = 0; !done && j < cnt; ++j) {
-            const float4 a = s_a[j];
-            const float4 c = s_c[j];
-            const float dx = a.x - pcx, dy = a.y - pcy;
-            const float e = -0.5f * (c.x * dx * dx + c.z * dy * dy) - c.y * dx * dy;
-            if (e > 0.0f) continue;
-            const float G = KIND == BLEND_INFER ? __expf(e) : expf(e);
-            if (G < threshold) continue;
-            const float al = a.z * G;
-            const float bw = Tr * al;
-            if (KIND == BLEND_TRAIN) {
-                if (bw > 0.0f) atomicAdd(blending_weights + s_id[j], G * bw);
+#pragma unroll 1
+        for (int w = 0; w < WORDS; ++w) {
+            unsigned mbits = s_mask[w][t];
+            if (mbits) s_mask[w][t] = 0u;
+            while (mbits && !done) {
+                const int j = w * 32 + __ffs(mbits) - 1;
+                mbits &= mbits - 1u;
+                const float4 a = s_a[j];
+                const float4 c = s_c[j];
+                const float dx = a.x - pcx, dy = a.y - pcy;
+                const float e = -0.5f * (c.x * dx * dx + c.z * dy * dy) - c.y * dx * dy;
+                if (e > 0.0f) continue;
+                const float G = KIND == BLEND_INFER ? __expf(e) : expf(e);
+                if (G < threshold) continue;
+                const float al = a.z * G;
+                const float bw = Tr * al;
+                if (KIND == BLEND_TRAIN) {
+                    if (bw > 0.0f) atomicAdd(&s_bw[j], G * bw);
+                }
+                const float4 f = s_f[j];
+                C0 += bw * f.x; C1 += bw * f.y; C2 += bw * f.z; C3 += bw * f.w;
+                if (KIND == BLEND_INFER) Z += bw * a.w;
+                Tr *= 1.0f - al;
+                if (Tr < kTransmittanceEps) done = true;
             }
-            const float4 f = s_f[j];
-            C0 += bw * f.x; C1 += bw * f.y; C2 += bw * f.z; C3 += bw * f.w;
-            if (KIND == BLEND_INFER) Z += bw * a.w;
-            Tr *= 1.0f - al;
-            if (Tr < kTransmittanceEps) done = true;
         }
     }
-    if (inside) {
-        const int64_t n_px = (int64_t)width * height;
-        const int64_t pi = (int64_t)py * width + px;
-        image[pi] = C0;
-        image[n_px + pi] = C1;
-        image[2 * n_px + pi] = C2;
-        image[3 * n_px + pi] = C3;
+    if (KIND == BLEND_TRAIN) {
+        __syncthreads();
+        flush_weights();
+    }
+    if (n_seg == 1u) {
+        if (inside) {
+            const int64_t n_px = (int64_t)width * height;
+            const int64_t pi = (int64_t)py * width + px;
+            image[pi] = C0;
+            image[n_px + pi] = C1;
+            image[2 * n_px + pi] = C2;
+            image[3 * n_px + pi] = C3;
+            if (KIND == BLEND_INFER) {
+                const float A = 1.0f - Tr;
+                depth_image[pi] = A > 0.0f ? Z / A : 0.0f;
+                alpha_image[pi] = Tr < kTransmittanceEps ? 1.0f : A;
+            } else {
+                alpha_image[pi] = Tr < kTransmittanceEps ? 1.0f : 1.0f - Tr;
+            }
+        }
+    } else {
+        seg_C[state_idx] = make_float4(C0, C1, C2, C3);
         if (KIND == BLEND_INFER) {
-            const float A = 1.0f - Tr;
-            depth_image[pi] = A > 0.0f ? Z / A : 0.0f;
-            alpha_image[pi] = Tr < kTransmittanceEps ? 1.0f : A;
-        } else {
-            alpha_image[pi] = Tr < kTransmittanceEps ? 1.0f : 1.0f - Tr;
+            seg_Z[state_idx] = Z;
+            seg_T[state_idx] = Tr;
+        } else if (seg_idx == n_seg - 1u && inside) {
+            alpha_image[(int64_t)py * width + px] = Tr < kTransmittanceEps ? 1.0f : 1.0f - Tr;
         }
     }
 }
 
 template <int T>
 __global__ void __launch_bounds__(T * T) blend_gaussian_backward_kernel(
-    const uint2* __restrict__ ranges, const uint32_t* __restrict__ inst_ids, const PointRec* __restrict__ rec,
-    const float4* __restrict__ conic, const float* __restrict__ grad_image, const float* __restrict__ grad_alpha,
+    const Segment* __restrict__ segs, const uint32_t* __restrict__ n_segments, const uint32_t* __restrict__ inst_ids,
+    const PointRec* __restrict__ rec, const float4* __restrict__ conic, const float* __restrict__ seg_T,
+    const float4* __restrict__ seg_C, const float* __restrict__ grad_image, const float* __restrict__ grad_alpha,
     const float* __restrict__ image, const float* __restrict__ alpha_image, float4* __restrict__ grad_feat_view,
     float* __restrict__ grad_opacity, int width, int height, int gw) {
     constexpr int B = T * T;
+    constexpr int WORDS = B / 32;
+    if (blockIdx.x >= *n_segments) return;
+    const Segment sg = segs[blockIdx.x];
+    const unsigned seg_idx = sg.info & 0xffffu;
+    if (sg.begin == sg.end) return;
     __shared__ float4 s_a[B];
     __shared__ float4 s_f[B];
     __shared__ float4 s_c[B];
     __shared__ uint32_t s_id[B];
+    __shared__ unsigned s_mask[WORDS][B];
+    __shared__ float s_gf[4][B];   // per staged instance: view-space feature gradient ...
+    __shared__ float s_go[B];      // ... and opacity gradient, summed with shared-memory atomics
     const int t = threadIdx.x;
-    const int tile = blockIdx.x;
-    const int tx = tile % gw, ty = tile / gw;
+    const int tx = (int)(sg.tile % (unsigned)gw), ty = (int)(sg.tile / (unsigned)gw);
+    const size_t state_idx = (size_t)blockIdx.x * B + t;
     const int px = tx * T + t % T, py = ty * T + t / T;
     const bool inside = px < width && py < height;
     const float pcx = (float)px + 0.5f, pcy = (float)py + 0.5f;
+#pragma unroll
+    for (int w = 0; w < WORDS; ++w) s_mask[w][t] = 0u;
+#pragma unroll
+    for (int q = 0; q < 4; ++q) s_gf[q][t] = 0.0f;
+    s_go[t] = 0.0f;
     float4 g = make_float4(0.f, 0.f, 0.f, 0.f), Cfin = make_float4(0.f, 0.f, 0.f, 0.f);
     float K = 0.0f;
     if (inside) {
@@ -1577,47 +1720,75 @@ __global__ void __launch_bounds__(T * T) blend_gaussian_backward_kernel(
     }
     float4 Crun = make_float4(0.f, 0.f, 0.f, 0.f);
     float Tr = 1.0f;
-    bool done = !inside;
-    const uint2 range = __ldg(ranges + tile);
-    for (unsigned base = range.x; base < range.y; base += B) {
+    if (inside && seg_idx > 0u) { Tr = seg_T[state_idx]; Crun = seg_C[state_idx]; }
+    bool done = !inside || Tr < kTransmittanceEps;
+    int cnt = 0;
+    auto flush_gradients = [&]() {
+        if (t < cnt) {
+            const float4 sf = make_float4(s_gf[0][t], s_gf[1][t], s_gf[2][t], s_gf[3][t]);
+            const float so = s_go[t];
+            const uint32_t id = s_id[t];
+            if (sf.x != 0.0f || sf.y != 0.0f || sf.z != 0.0f || sf.w != 0.0f) atomicAdd(grad_feat_view + id, sf);
+            if (so != 0.0f) atomicAdd(grad_opacity + id, so);
+            s_gf[0][t] = 0.0f; s_gf[1][t] = 0.0f; s_gf[2][t] = 0.0f; s_gf[3][t] = 0.0f;
+            s_go[t] = 0.0f;
+        }
+    };
+    constexpr float kNegLogThreshold = 4.5f;   // -ln(kTrainGaussThreshold)
+    for (unsigned base = sg.begin; base < sg.end; base += B) {
         if (__syncthreads_count(done) == B) break;
-        const int cnt = (int)min((unsigned)B, range.y - base);
+        flush_gradients();
+        cnt = (int)min((unsigned)B, sg.end - base);
         if (t < cnt) {
             const uint32_t id = checked_point(__ldg(inst_ids + base + t));
             const float4* r = reinterpret_cast<const float4*>(rec + id);
-            s_a[t] = __ldg(r);
+            const float4 a = __ldg(r);
+            const float4 c = __ldg(conic + id);
+            s_a[t] = a;
             s_f[t] = __ldg(r + 1);
-            s_c[t] = __ldg(conic + id);
+            s_c[t] = c;
             s_id[t] = id;
+            gaussian_mask_bits<T>(t, a, c, kNegLogThreshold, tx, ty, s_mask);
         }
         __syncthreads();
-        for (int j = 0; !done && j < cnt; ++j) {
-            const float4 a = s_a[j];
-            const float4 c = s_c[j];
-            const float dx = a.x - pcx, dy = a.y - pcy;
-            const float e = -0.5f * (c.x * dx * dx + c.z * dy * dy) - c.y * dx * dy;
-            if (e > 0.0f) continue;
-            const float G = expf(e);
-            if (G < kTrainGaussThreshold) continue;
-            const float al = a.z * G;
-            const float bw = Tr * al;
-            const uint32_t id = s_id[j];
-            if (bw > 0.0f) atomicAdd(grad_feat_view + id, make_float4(bw * g.x, bw * g.y, bw * g.z, bw * g.w));
-            const float4 f = s_f[j];
-            Crun.x += bw * f.x; Crun.y += bw * f.y; Crun.z += bw * f.z; Crun.w += bw * f.w;
-            const float oma = 1.0f - al;
-            const float rcp = 1.0f / fmaxf(oma, kOneMinusAlphaEps);
-            const float from_features = (Tr * f.x + (Crun.x - Cfin.x) * rcp) * g.x +
-                                        (Tr * f.y + (Crun.y - Cfin.y) * rcp) * g.y +
-                                        (Tr * f.z + (Crun.z - Cfin.z) * rcp) * g.z +
-                                        (Tr * f.w + (Crun.w - Cfin.w) * rcp) * g.w;
-            const float dalpha = from_features + K * rcp;
-            const float dop = dalpha * G;
-            if (dop != 0.0f) atomicAdd(grad_opacity + id, dop);
-            Tr *= oma;
-            if (Tr < kTransmittanceEps) done = true;
+#pragma unroll 1
+        for (int w = 0; w < WORDS; ++w) {
+            unsigned mbits = s_mask[w][t];
+            if (mbits) s_mask[w][t] = 0u;
+            while (mbits && !done) {
+                const int j = w * 32 + __ffs(mbits) - 1;
+                mbits &= mbits - 1u;
+                const float4 a = s_a[j];
+                const float4 c = s_c[j];
+                const float dx = a.x - pcx, dy = a.y - pcy;
+                const float e = -0.5f * (c.x * dx * dx + c.z * dy * dy) - c.y * dx * dy;
+                if (e > 0.0f) continue;
+                const float G = expf(e);
+                if (G < kTrainGaussThreshold) continue;
+                const float al = a.z * G;
+                const float bw = Tr * al;
+                if (bw > 0.0f) {
+                    atomicAdd(&s_gf[0][j], bw * g.x); atomicAdd(&s_gf[1][j], bw * g.y);
+                    atomicAdd(&s_gf[2][j], bw * g.z); atomicAdd(&s_gf[3][j], bw * g.w);
+                }
+                const float4 f = s_f[j];
+                Crun.x += bw * f.x; Crun.y += bw * f.y; Crun.z += bw * f.z; Crun.w += bw * f.w;
+                const float oma = 1.0f - al;
+                const float rcp = 1.0f / fmaxf(oma, kOneMinusAlphaEps);
+                const float from_features = (Tr * f.x + (Crun.x - Cfin.x) * rcp) * g.x +
+                                            (Tr * f.y + (Crun.y - Cfin.y) * rcp) * g.y +
+                                            (Tr * f.z + (Crun.z - Cfin.z) * rcp) * g.z +
+                                            (Tr * f.w + (Crun.w - Cfin.w) * rcp) * g.w;
+                const float dalpha = from_features + K * rcp;
+                const float dop = dalpha * G;
+                if (dop != 0.0f) atomicAdd(&s_go[j], dop);
+                Tr *= oma;
+                if (Tr < kTransmittanceEps) done = true;
+            }
         }
     }
+    __syncthreads();
+    flush_gradients();
 }
 
 // SH chain rule for every point, zero rows for culled ones, written as 72 contiguous bytes per point
@@ -1743,7 +1914,7 @@ InstanceBlob carve_instance_blob(void* p, int64_t n_instances, int n_tiles, int 
     b.ranges = c.take<uint2>(n_tiles);
     for (int k = 0; k < 2; ++k) b.keys[k] = c.take<uint32_t>(n_instances);
     for (int k = 0; k < 2; ++k) b.ids[k] = c.take<uint32_t>(n_instances);
-    b.max_segments = mode == INPC_MODE_BILINEAR ? max_segments(n_instances, n_tiles, tile) : 0;
+    b.max_segments = max_segments(n_instances, n_tiles, tile);
     const size_t px = (size_t)b.max_segments * tile * tile;
     b.segs = c.take<Segment>(b.max_segments);
     b.tile_first = c.take<uint32_t>(n_tiles);
@@ -1931,7 +2102,7 @@ int run_front(const RasterParams& rp, int64_t n, const float* positions, const v
         tile_ranges_kernel<<<(unsigned)ceil_div<int64_t>(n_instances, 256 * 8), 256, 0, stream>>>(ib.keys[t_alt], n_instances, ib.ranges);
         INPC_LAUNCH_CHECK("tile_ranges_kernel");
     }
-    if (MODE == INPC_MODE_BILINEAR) {
+    {
         StageScope scope(STAGE_SORT_TILE, stream);
         count_segments_kernel<<<1, kScanThreads, 0, stream>>>(ib.ranges, n_tiles, blend_batch(rp.tile), ib.tile_first, ib.n_segments);
         INPC_LAUNCH_CHECK("count_segments_kernel");
@@ -2014,24 +2185,39 @@ int launch_bilinear_backward(const RasterParams& rp, const PointBlob& pb, const 
     return INPC_OK;
 }
 
+template <int T, int KIND>
+int launch_gaussian_forward(const RasterParams& rp, const PointBlob& pb, const InstanceBlob& ib, const uint32_t* ids, float* image,
+                            float* depth, float* alpha, float* blending_weights, float threshold, cudaStream_t stream) {
+    const int n_tiles = rp.gw * rp.gh;
+    const int W = rp.v.width, H = rp.v.height;
+    const unsigned grid = (unsigned)ib.max_segments;
+    const float neg_log_threshold = -logf(threshold);
+    blend_gaussian_transmittance_kernel<T, KIND == BLEND_INFER><<<grid, T * T, 0, stream>>>(ib.segs, ib.n_segments, ids, pb.rec, pb.conic, ib.seg_T, W, H,
+                                                                                          rp.gw, threshold, neg_log_threshold);
+    INPC_LAUNCH_CHECK("blend_gaussian_transmittance_kernel");
+    blend_prefix_kernel<T><<<n_tiles, T * T, 0, stream>>>(ib.segs, ib.tile_first, ib.seg_T);
+    INPC_LAUNCH_CHECK("blend_prefix_kernel");
+    blend_gaussian_forward_kernel<T, KIND><<<grid, T * T, 0, stream>>>(ib.segs, ib.n_segments, ids, pb.rec, pb.conic, ib.seg_T, ib.seg_C, ib.seg_Z, image,
+                                                                      depth, alpha, blending_weights, W, H, rp.gw, threshold, neg_log_threshold);
+    INPC_LAUNCH_CHECK("blend_gaussian_forward_kernel");
+    blend_combine_kernel<T, KIND><<<n_tiles, T * T, 0, stream>>>(ib.segs, ib.tile_first, ib.seg_C, ib.seg_Z, ib.seg_T, image, depth, alpha, W, H, rp.gw);
+    INPC_LAUNCH_CHECK("blend_combine_kernel");
+    return INPC_OK;
+}
+
 template <int KIND>
 int launch_blend_forward(int mode, const RasterParams& rp, const PointBlob& pb, const InstanceBlob& ib, int64_t n_instances,
                          float* image, float* depth, float* alpha, float* blending_weights, float threshold,
                          cudaStream_t stream) {
     const int n_tiles = rp.gw * rp.gh;
     const uint32_t* ids = ib.ids[tile_result_buffer(n_instances, n_tiles)];
-    const int W = rp.v.width, H = rp.v.height;
     StageScope scope(STAGE_BLEND_FWD, stream);
     if (mode == INPC_MODE_BILINEAR) {
         if (rp.tile == 8) return launch_bilinear_forward<8, KIND>(rp, pb, ib, ids, image, depth, alpha, blending_weights, stream);
         return launch_bilinear_forward<16, KIND>(rp, pb, ib, ids, image, depth, alpha, blending_weights, stream);
     }
-    if (rp.tile == 8)
-        blend_gaussian_forward_kernel<8, KIND><<<n_tiles, 64, 0, stream>>>(ib.ranges, ids, pb.rec, pb.conic, image, depth, alpha, blending_weights, W, H, rp.gw, threshold);
-    else
-        blend_gaussian_forward_kernel<16, KIND><<<n_tiles, 256, 0, stream>>>(ib.ranges, ids, pb.rec, pb.conic, image, depth, alpha, blending_weights, W, H, rp.gw, threshold);
-    INPC_LAUNCH_CHECK("blend_forward_kernel");
-    return INPC_OK;
+    if (rp.tile == 8) return launch_gaussian_forward<8, KIND>(rp, pb, ib, ids, image, depth, alpha, blending_weights, threshold, stream);
+    return launch_gaussian_forward<16, KIND>(rp, pb, ib, ids, image, depth, alpha, blending_weights, threshold, stream);
 }
 
 template <int T, int C4, int KIND>
@@ -2177,10 +2363,11 @@ extern "C" int inpc_rasterize_backward(const inpc_raster_state* state, const inp
                               : launch_bilinear_backward<16>(rp, pb, ib, ids, grad_image, grad_alpha, image, alpha, gfv, grad_opacities, stream);
             if (rc != INPC_OK) return rc;
         } else {
+            const unsigned grid = (unsigned)ib.max_segments;
             if (rp.tile == 8)
-                blend_gaussian_backward_kernel<8><<<n_tiles, 64, 0, stream>>>(ib.ranges, ids, pb.rec, pb.conic, grad_image, grad_alpha, image, alpha, gfv, grad_opacities, W, H, rp.gw);
+                blend_gaussian_backward_kernel<8><<<grid, 64, 0, stream>>>(ib.segs, ib.n_segments, ids, pb.rec, pb.conic, ib.seg_T, ib.seg_C, grad_image, grad_alpha, image, alpha, gfv, grad_opacities, W, H, rp.gw);
             else
-                blend_gaussian_backward_kernel<16><<<n_tiles, 256, 0, stream>>>(ib.ranges, ids, pb.rec, pb.conic, grad_image, grad_alpha, image, alpha, gfv, grad_opacities, W, H, rp.gw);
+                blend_gaussian_backward_kernel<16><<<grid, 256, 0, stream>>>(ib.segs, ib.n_segments, ids, pb.rec, pb.conic, ib.seg_T, ib.seg_C, grad_image, grad_alpha, image, alpha, gfv, grad_opacities, W, H, rp.gw);
         }
         INPC_LAUNCH_CHECK("blend_backward_kernel");
     }

@@ -420,3 +420,40 @@ def test_full_size_training_step_matches_reference_backend():
         assert_close(o.grad.reshape(-1).cpu().numpy(), rgo.reshape(-1).cpu().numpy(), rtol=1e-4, atol=1e-9, max_bad=800,
                      what=f"full-size grad_opacities (tile {tile})")
         del f, o, im, al, bw
+
+
+@pytest.mark.parametrize("tile", [8, 16])
+def test_gaussian_deep_tiles_training_and_inference(tile):
+    """Gaussian splats on tiles whose lists are cut into several segments: forward, backward and inference
+    against the oracle (fast exponentials on the device: looser tolerances)."""
+    import inpc_b200
+    from inpc_b200.views import look_at_view
+    view = look_at_view((0.0, 0.0, 3.0), (0.0, 0.0, 0.0), 64, 48, 60.0, 60.0)
+    g = torch.Generator().manual_seed(19)
+    n = 30000
+    pos = torch.cat([torch.randn((n, 2), generator=g) * 0.15, torch.rand((n, 1), generator=g) - 0.5], dim=1).contiguous()
+    feats = (torch.randn((n, 36), generator=g) * 0.5).to(torch.float16)
+    opac = torch.rand((n, 1), generator=g) * 0.1 + 0.01
+    v = view.to(DEV)
+    cam = oracle_camera(view)
+    H, W = view.camera.height, view.camera.width
+    gi = torch.randn((4, H, W), generator=g) * 1e-3
+    ga = torch.randn((1, H, W), generator=g) * 1e-3
+    rast = inpc_b200.INPCRasterizer(tile_size=tile)
+    f = feats.to(DEV).requires_grad_(True)
+    o = opac.to(DEV).requires_grad_(True)
+    image, alpha, bw = rast(v, 1, pos.to(DEV), f, o)
+    st = O.rasterize_forward(O.GAUSSIAN, cam, pos.numpy(), feats.numpy(), opac.numpy(), tile=tile)
+    assert (st.alpha == 1.0).sum() > 20 and (st.ranges[:, 1] - st.ranges[:, 0]).max() > 16 * tile * tile
+    assert_close(image.detach().cpu().numpy(), st.image, rtol=1e-4, atol=1e-5, max_bad=4, what="gaussian deep image")
+    assert_close(alpha.detach().cpu().numpy(), st.alpha, rtol=1e-4, atol=1e-5, max_bad=4, what="gaussian deep alpha")
+    assert_close(bw.detach().cpu().numpy(), st.blending_weights, rtol=1e-4, atol=1e-6, max_bad=8, what="gaussian deep blending weights")
+    torch.autograd.backward([image, alpha], [gi.to(DEV), ga.to(DEV)])
+    gf, go, _ = O.rasterize_backward(st, gi.numpy(), ga.numpy())
+    assert_close(o.grad.detach().cpu().numpy(), go, rtol=1e-3, atol=1e-8, max_bad=16, what="gaussian deep grad_opacities")
+    assert_close(f.grad.float().detach().cpu().numpy(), gf.astype(np.float32), rtol=4e-3, atol=2e-7, max_bad=36 * 16, what="gaussian deep grad_features")
+    img, dep, alp = rast.render_preextracted(v, 1, pos.to(DEV), feats.to(DEV), opac.to(DEV), None, sigma_world_scale=1.0, sigma_cutoff=3.0)
+    oi, od, oa, _ = O.render_preextracted(1, cam, pos.numpy(), feats.numpy(), opac.numpy(), None, 0.05 / view.camera.focal_y, 3.0, tile=tile)
+    assert_close(img.cpu().numpy(), oi, rtol=2e-4, atol=2e-5, max_bad=12, what="gaussian deep inference image")
+    assert_close(dep.cpu().numpy(), od, rtol=2e-4, atol=2e-5, max_bad=12, what="gaussian deep inference depth")
+    assert_close(alp.cpu().numpy(), oa, rtol=2e-4, atol=2e-5, max_bad=12, what="gaussian deep inference alpha")
