@@ -268,6 +268,7 @@ def run_ours(args):
     from inpc_b200.batch import accumulate_view, allreduce_buffers
     from inpc_b200.views import View
     e2e_streams = [torch.cuda.Stream(device=device) for _ in range(max(args.streams, 1))]
+    copy_stream = torch.cuda.Stream(device=device)
     e2e_parts = [torch.zeros_like(trainer.buffers.appearance) for _ in e2e_streams]
 
     def e2e_step():
@@ -277,15 +278,23 @@ def run_ours(args):
             part.zero_()
         for s_ in e2e_streams:
             s_.wait_stream(main)
+        copy_stream.wait_stream(main)
         for k, vi in enumerate(my_views):
             slot = k % len(e2e_streams)
-            with torch.cuda.stream(e2e_streams[slot]):
-                # this view's inputs come from pinned host memory on the view's own stream: the copies of
-                # one view overlap with the kernels of the views on the other streams
+            # this view's inputs come from pinned host memory on a copy stream of their own, so that the
+            # copies run ahead of, and under, the kernels of the views in flight
+            with torch.cuda.stream(copy_stream):
                 gi = pinned_gi.to(device, non_blocking=True)
                 ga = pinned_ga.to(device, non_blocking=True)
                 w2c, cpos = pinned_views[vi]
-                view = View(wl["views_host"][vi].camera, w2c.to(device, non_blocking=True), cpos.to(device, non_blocking=True))
+                w2c_d, cpos_d = w2c.to(device, non_blocking=True), cpos.to(device, non_blocking=True)
+                copied = torch.cuda.Event()
+                copied.record(copy_stream)
+            with torch.cuda.stream(e2e_streams[slot]):
+                e2e_streams[slot].wait_event(copied)
+                for tensor in (gi, ga, w2c_d, cpos_d):
+                    tensor.record_stream(e2e_streams[slot])
+                view = View(wl["views_host"][vi].camera, w2c_d, cpos_d)
                 trainer.sampler.set_rng_state(vi)
                 t = wl["tree"]
                 pos, idx = trainer.sampler.generate_training_samples(t.centers, t.levels, t.weights, view, args.points, t.initial_size)
