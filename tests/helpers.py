@@ -6,7 +6,7 @@ import torch
 
 import oracle as O
 
-# north-star tolerances for fp32 images / weights / opacity gradients
+# tolerances for fp32 images / weights / opacity gradients: 1e-5 relative, 1e-6 absolute
 RTOL, ATOL = 1e-5, 1e-6
 # grad_features is rounded to fp16 per coefficient (sh_utils.cuh:53-61): half-precision tolerance
 RTOL_H, ATOL_H = 2e-3, 1e-7

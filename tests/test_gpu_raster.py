@@ -139,7 +139,7 @@ needs_ref = pytest.mark.skipif(not RB.available(), reason="oracle/_ref/libinpc_r
 @needs_ref
 def test_bilinear_matches_reference_backend():
     """Tile ranges, per-tile lists and depth keys bit-exact at the reference's 8x8 tiling; images,
-    weights and gradients within the north-star tolerance.  Depth ties are silenced first."""
+    weights and gradients within rtol 1e-5 / atol 1e-6.  Depth ties are silenced first."""
     import inpc_b200
     view, pos, feats, opac = small_scene(n=60000, width=320, height=200, focal=260.0)
     v = view.to(DEV)
@@ -345,7 +345,7 @@ def test_argument_errors_raise():
 
 
 def test_full_size_properties():
-    """BASELINE sizes (2^23 points, 1237x822): properties that need no oracle — sorted keys, ranges
+    """Full benchmark sizes (2^23 points, 1237x822): properties that need no oracle — sorted keys, ranges
     partition the instance list, tile-size independence of the image, run-to-run determinism."""
     from inpc_b200 import rasterization as R, synthetic as syn
     n = 1 << 23
