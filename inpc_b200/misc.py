@@ -2,8 +2,6 @@
 (INPCCudaBackend/INPCCudaBackend/torch_bindings/misc.py) on top of libinpc_b200."""
 from __future__ import annotations
 
-from typing import Any
-
 import torch
 from torch.autograd.function import once_differentiable
 
@@ -40,28 +38,30 @@ def spherical_contraction(positions: torch.Tensor) -> torch.Tensor:
     return out
 
 
-class _CauchyLoss(torch.autograd.Function):
+class _FusedCauchy(torch.autograd.Function):
+    """Mean Cauchy loss: forward = two kernels (partial sums, final sum), backward = one."""
+
     @staticmethod
-    def forward(ctx: Any, input: torch.Tensor, target: torch.Tensor) -> torch.Tensor:
-        input = _cuda_f32(input, "input")
+    def forward(ctx, prediction, target):
+        input = _cuda_f32(prediction, "input")
         target = _cuda_f32(target, "target")
-        n = input.numel()
-        dev = input.device
+        n, dev = input.numel(), input.device
         with torch.cuda.device(dev):
             loss = torch.empty((), dtype=torch.float32, device=dev)
             ws = torch.empty(int(_cabi.lib().inpc_cauchy_workspace_bytes(n)), dtype=torch.uint8, device=dev)
             _cabi.check(_cabi.lib().inpc_cauchy_loss(_ptr(input), _ptr(target), n, _ptr(loss), _ptr(ws), _stream()))
             ws.record_stream(torch.cuda.current_stream())
+        ctx.set_materialize_grads(False)     # an unused loss arrives as None in backward
         ctx.save_for_backward(input, target)
-        ctx.set_materialize_grads(False)
         return loss
 
     @staticmethod
     @once_differentiable
-    def backward(ctx: Any, grad: torch.Tensor):
-        input, target = ctx.saved_tensors
-        if grad is None:
+    def backward(ctx, upstream):
+        if upstream is None:
             return None, None
+        input, target = ctx.saved_tensors
+        grad = upstream
         grad = _cuda_f32(grad, "grad").reshape(1)
         with torch.cuda.device(input.device):
             grad_input = torch.empty_like(input)
@@ -74,4 +74,4 @@ def fused_cauchy_loss(input: torch.Tensor, target: torch.Tensor) -> torch.Tensor
     """Cauchy loss between input and target with mean reduction."""
     if input.shape != target.shape:
         raise ValueError(f"input and target shapes must match ({input.shape} vs. {target.shape})")
-    return _CauchyLoss.apply(input, target)
+    return _FusedCauchy.apply(input, target)
