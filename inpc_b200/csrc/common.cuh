@@ -110,11 +110,8 @@ inline ViewParams to_params(const inpc_view* v) {
 // ---- radix sort (radix_sort.cu) ------------------------------------------------------------
 size_t sort_workspace_bytes(int64_t n);
 int sort_pass_count(int end_bit);   // passes sort_pairs makes; the result is in the alternate buffers iff odd (and n > 1)
-// aux_in / aux_out (both or neither): the last pass also writes aux_out[i] = aux_in[value of sorted pair i];
-// nothing is written when the sort makes no pass (n <= 1 or end_bit == 0).
 int sort_pairs(uint32_t* keys, uint32_t* keys_alt, uint32_t* values, uint32_t* values_alt, int64_t n,
-               int end_bit, void* workspace, int* result_in_alt, cudaStream_t stream, const uint2* aux_in = nullptr,
-               uint2* aux_out = nullptr);
+               int end_bit, void* workspace, int* result_in_alt, cudaStream_t stream);
 
 // More than 48 KB of dynamic shared memory is an opt-in per kernel AND per device: `done` is the
 // caller's per-kernel table of devices already set up.

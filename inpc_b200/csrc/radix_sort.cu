@@ -19,17 +19,8 @@ namespace {
 constexpr int kRadixBits = 9;            // widest digit of a pass: 27 key bits sort in 3 passes, 32 in 4 x 8
 constexpr int kRadix = 1 << kRadixBits;  // capacity of every per-digit array
 constexpr int kMaxPasses = 4;
-#ifndef INPC_SORT_SMEM_PAD
-#define INPC_SORT_SMEM_PAD 0
-#endif
-#ifndef INPC_SORT_THREADS
-#define INPC_SORT_THREADS 512
-#endif
-#ifndef INPC_SORT_ITEMS
-#define INPC_SORT_ITEMS 16
-#endif
-constexpr int kThreads = INPC_SORT_THREADS;
-constexpr int kItems = INPC_SORT_ITEMS;
+constexpr int kThreads = 512;
+constexpr int kItems = 16;
 constexpr int kTile = kThreads * kItems;   // 8192 pairs per tile
 constexpr int kWarps = kThreads / 32;
 constexpr int kDigitsPerThread = (kRadix + kThreads - 1) / kThreads;   // digits a thread owns in the scan / look-back phase
@@ -104,16 +95,12 @@ struct PassSmem {
 
 // BITS > 0 fixes the digit width at compile time (the ballot loop of the ranking unrolls); BITS == 0
 // takes it from `bits_arg`.
-// AUX: the pass also writes aux_out[destination] = aux_in[value] (8-byte records indexed by the sorted
-// values).  The pass is bound by instruction issue with the memory system mostly idle, so this gather
-// rides along almost for free; a consumer that walks the sorted order then reads its per-item data
-// sequentially instead of gathering it.
-template <int BITS, bool AUX>
+template <int BITS>
 __global__ void __launch_bounds__(kThreads) radix_onesweep_pass_kernel(
     const uint32_t* __restrict__ keys_in, const uint32_t* __restrict__ vals_in,
     uint32_t* __restrict__ keys_out, uint32_t* __restrict__ vals_out, int64_t n, int shift, int bits_arg,
     const unsigned* __restrict__ digit_base, volatile unsigned* tile_state, unsigned* ticket,
-    volatile unsigned* status, const uint2* __restrict__ aux_in, uint2* __restrict__ aux_out) {
+    volatile unsigned* status) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     PassSmem& s = *reinterpret_cast<PassSmem*>(smem_raw);
 
@@ -146,9 +133,6 @@ __global__ void __launch_bounds__(kThreads) radix_onesweep_pass_kernel(
 #pragma unroll
     for (int i = 0; i < kItems; ++i) {
         const unsigned d = (key[i] >> shift) & digit_mask;
-#ifdef INPC_SORT_MATCH_ANY
-        peers[i] = __match_any_sync(0xffffffffu, d);
-#else
         unsigned p = 0xffffffffu;
         if (BITS > 0) {
 #pragma unroll
@@ -165,7 +149,6 @@ __global__ void __launch_bounds__(kThreads) radix_onesweep_pass_kernel(
             }
         }
         peers[i] = p;
-#endif
     }
 #pragma unroll
     for (int i = 0; i < kItems; ++i) {
@@ -277,7 +260,6 @@ __global__ void __launch_bounds__(kThreads) radix_onesweep_pass_kernel(
         keys_out[dst] = k;
         const uint32_t v = s.values[q];
         vals_out[dst] = v;
-        if (AUX) aux_out[dst] = __ldg(aux_in + v);
     }
 }
 
@@ -306,32 +288,39 @@ SortWorkspace carve_sort_workspace(void* ws, int64_t n) {
 }
 
 
-template <int BITS, bool AUX>
-int launch_onesweep_instance(int64_t tiles, const uint32_t* kin, const uint32_t* vin, uint32_t* kout, uint32_t* vout, int64_t n, int shift, int bits,
-                             const unsigned* base, unsigned* state, unsigned* ticket, unsigned* status, const uint2* aux_in, uint2* aux_out,
-                             cudaStream_t stream) {
+struct PassArgs {
+    int64_t tiles;
+    const uint32_t *kin, *vin;
+    uint32_t *kout, *vout;
+    int64_t n;
+    int shift, bits;
+    const unsigned* base;
+    unsigned *state, *ticket, *status;
+};
+
+template <int BITS>
+int launch_onesweep_instance(const PassArgs& a, cudaStream_t stream) {
     static bool attr_set[kMaxDevices] = {false};
-    // INPC_SORT_SMEM_PAD bytes of unused shared memory per block lower the number of resident blocks
-    // per SM (a tuning knob: fewer sort blocks leave room for kernels of other streams)
-    constexpr size_t kSmemBytes = sizeof(PassSmem) + INPC_SORT_SMEM_PAD;
-    const int rc = opt_in_dynamic_smem(radix_onesweep_pass_kernel<BITS, AUX>, kSmemBytes, attr_set);
-    if (rc != INPC_OK) return rc;
-    radix_onesweep_pass_kernel<BITS, AUX><<<(unsigned)tiles, kThreads, kSmemBytes, stream>>>(kin, vin, kout, vout, n, shift, bits, base, state, ticket,
-                                                                                              status, aux_in, aux_out);
+    static std::mutex attr_mutex;
+    constexpr size_t kSmemBytes = sizeof(PassSmem);
+    {
+        std::lock_guard<std::mutex> lock(attr_mutex);
+        const int rc = opt_in_dynamic_smem(radix_onesweep_pass_kernel<BITS>, kSmemBytes, attr_set);
+        if (rc != INPC_OK) return rc;
+    }
+    radix_onesweep_pass_kernel<BITS><<<(unsigned)a.tiles, kThreads, kSmemBytes, stream>>>(a.kin, a.vin, a.kout, a.vout, a.n, a.shift, a.bits, a.base,
+                                                                                         a.state, a.ticket, a.status);
     INPC_LAUNCH_CHECK("radix_onesweep_pass_kernel");
     return INPC_OK;
 }
 
 // the digit widths the rasterizer's sorts use (depth keys 9/8, tile keys 7) get unrolled kernels
-template <bool AUX>
-int launch_onesweep_pass(int64_t tiles, const uint32_t* kin, const uint32_t* vin, uint32_t* kout, uint32_t* vout, int64_t n, int shift, int bits,
-                         const unsigned* base, unsigned* state, unsigned* ticket, unsigned* status, const uint2* aux_in, uint2* aux_out,
-                         cudaStream_t stream) {
-    switch (bits) {
-        case 7: return launch_onesweep_instance<7, AUX>(tiles, kin, vin, kout, vout, n, shift, bits, base, state, ticket, status, aux_in, aux_out, stream);
-        case 8: return launch_onesweep_instance<8, AUX>(tiles, kin, vin, kout, vout, n, shift, bits, base, state, ticket, status, aux_in, aux_out, stream);
-        case 9: return launch_onesweep_instance<9, AUX>(tiles, kin, vin, kout, vout, n, shift, bits, base, state, ticket, status, aux_in, aux_out, stream);
-        default: return launch_onesweep_instance<0, AUX>(tiles, kin, vin, kout, vout, n, shift, bits, base, state, ticket, status, aux_in, aux_out, stream);
+int launch_onesweep_pass(const PassArgs& a, cudaStream_t stream) {
+    switch (a.bits) {
+        case 7: return launch_onesweep_instance<7>(a, stream);
+        case 8: return launch_onesweep_instance<8>(a, stream);
+        case 9: return launch_onesweep_instance<9>(a, stream);
+        default: return launch_onesweep_instance<0>(a, stream);
     }
 }
 
@@ -341,17 +330,27 @@ size_t sort_workspace_bytes(int64_t n) { return carve_sort_workspace(nullptr, n)
 
 int sort_pass_count(int end_bit) { return end_bit > 0 ? ceil_div(end_bit, kRadixBits) : 0; }
 
-int sort_pairs(uint32_t* keys, uint32_t* keys_alt, uint32_t* values, uint32_t* values_alt, int64_t n,
-               int end_bit, void* workspace, int* result_in_alt, cudaStream_t stream, const uint2* aux_in, uint2* aux_out) {
-    if (result_in_alt) *result_in_alt = 0;
-    if (n < 0 || n >= (int64_t)1 << 30) { set_error("sort_pairs: n=%lld out of range [0, 2^30)", (long long)n); return INPC_E_INVALID; }
-    if (end_bit < 0 || end_bit > 32) { set_error("sort_pairs: end_bit=%d out of range", end_bit); return INPC_E_INVALID; }
-    if (n <= 1 || end_bit == 0) return INPC_OK;
-    if (!keys || !keys_alt || !values || !values_alt || !workspace) { set_error("sort_pairs: null pointer"); return INPC_E_INVALID; }
+// The sort proper: `workspace` holds sort_workspace_bytes(n) bytes, `status` is the device address of the
+// status words a tile that gives up its look-back writes to.  Both public entry points end up here.
+// Argument checks shared by the entry points; *nothing_to_do is set when the call is valid but makes no pass.
+static int check_sort_args(const char* who, const uint32_t* keys, const uint32_t* keys_alt, const uint32_t* values, const uint32_t* values_alt,
+                           int64_t n, int end_bit, bool* nothing_to_do) {
+    *nothing_to_do = false;
+    if (n < 0 || n >= (int64_t)1 << 30) { set_error("%s: n=%lld out of range [0, 2^30)", who, (long long)n); return INPC_E_INVALID; }
+    if (end_bit < 0 || end_bit > 32) { set_error("%s: end_bit=%d out of range", who, end_bit); return INPC_E_INVALID; }
+    if (n <= 1 || end_bit == 0) { *nothing_to_do = true; return INPC_OK; }
+    if (!keys || !keys_alt || !values || !values_alt) { set_error("%s: null pointer", who); return INPC_E_INVALID; }
     if ((reinterpret_cast<uintptr_t>(keys) | reinterpret_cast<uintptr_t>(keys_alt)) & 15u) {
-        set_error("sort_pairs: key buffers must be 16-byte aligned");
+        set_error("%s: key buffers must be 16-byte aligned", who);
         return INPC_E_INVALID;
     }
+    return INPC_OK;
+}
+
+static int sort_pairs_with(const char* who, uint32_t* keys, uint32_t* keys_alt, uint32_t* values, uint32_t* values_alt, int64_t n, int end_bit,
+                           void* workspace, unsigned* status, int* result_in_alt, cudaStream_t stream) {
+    if (result_in_alt) *result_in_alt = 0;
+    if (!workspace || !status) { set_error("%s: null workspace", who); return INPC_E_INVALID; }
 
     PassTable pt;
     pt.n_passes = ceil_div(end_bit, kRadixBits);
@@ -368,7 +367,8 @@ int sort_pairs(uint32_t* keys, uint32_t* keys_alt, uint32_t* values, uint32_t* v
 
     SortWorkspace w = carve_sort_workspace(workspace, n);
     const int64_t tiles = ceil_div<int64_t>(n, kTile);
-    // hist, tickets and the look-back state are contiguous at the front of the workspace
+    // hist, tickets and the look-back state are contiguous at the front of the workspace; a workspace that
+    // is reused keeps the previous call's contents, so everything this call reads is cleared first
     INPC_CUDA_TRY(cudaMemsetAsync(workspace, 0, w.zero_bytes + (size_t)pt.n_passes * tiles * kRadix * sizeof(unsigned), stream));
 
     const int hist_blocks = (int)ceil_div<int64_t>(n, kHistItemsPerBlock);
@@ -377,22 +377,33 @@ int sort_pairs(uint32_t* keys, uint32_t* keys_alt, uint32_t* values, uint32_t* v
     radix_scan_histogram_kernel<<<pt.n_passes, kRadix, 0, stream>>>(w.hist, w.base);
     INPC_LAUNCH_CHECK("radix_scan_histogram_kernel");
 
-    unsigned* status = device_status_ptr();
-    if (!status) return INPC_E_CUDA;
-    uint32_t *kin = keys, *kout = keys_alt, *vin = values, *vout = values_alt;
+    PassArgs a;
+    a.tiles = tiles; a.n = n; a.status = status;
+    a.kin = keys; a.kout = keys_alt; a.vin = values; a.vout = values_alt;
     for (int p = 0; p < pt.n_passes; ++p) {
-        // the last pass knows every pair's final position: it carries the optional gather
-        const bool aux = aux_in && aux_out && p == pt.n_passes - 1;
-        const int rc = aux ? launch_onesweep_pass<true>(tiles, kin, vin, kout, vout, n, pt.shift[p], pt.bits[p], w.base + p * kRadix,
-                                                        w.state + (size_t)p * tiles * kRadix, w.ticket + p, status, aux_in, aux_out, stream)
-                           : launch_onesweep_pass<false>(tiles, kin, vin, kout, vout, n, pt.shift[p], pt.bits[p], w.base + p * kRadix,
-                                                         w.state + (size_t)p * tiles * kRadix, w.ticket + p, status, nullptr, nullptr, stream);
+        a.shift = pt.shift[p]; a.bits = pt.bits[p];
+        a.base = w.base + p * kRadix;
+        a.state = w.state + (size_t)p * tiles * kRadix;
+        a.ticket = w.ticket + p;
+        const int rc = launch_onesweep_pass(a, stream);
         if (rc != INPC_OK) return rc;
-        uint32_t* t = kin; kin = kout; kout = t;
-        t = vin; vin = vout; vout = t;
+        const uint32_t* t = a.kin; a.kin = a.kout; a.kout = const_cast<uint32_t*>(t);
+        t = a.vin; a.vin = a.vout; a.vout = const_cast<uint32_t*>(t);
     }
     if (result_in_alt) *result_in_alt = pt.n_passes & 1;
     return INPC_OK;
+}
+
+int sort_pairs(uint32_t* keys, uint32_t* keys_alt, uint32_t* values, uint32_t* values_alt, int64_t n,
+               int end_bit, void* workspace, int* result_in_alt, cudaStream_t stream) {
+    if (result_in_alt) *result_in_alt = 0;
+    bool nothing = false;
+    const int rc = check_sort_args("sort_pairs", keys, keys_alt, values, values_alt, n, end_bit, &nothing);
+    if (rc != INPC_OK || nothing) return rc;
+    if (!workspace) { set_error("sort_pairs: null workspace"); return INPC_E_INVALID; }
+    unsigned* status = device_status_ptr();
+    if (!status) return INPC_E_CUDA;
+    return sort_pairs_with("sort_pairs", keys, keys_alt, values, values_alt, n, end_bit, workspace, status, result_in_alt, stream);
 }
 
 }  // namespace inpc
@@ -439,54 +450,26 @@ extern "C" int inpc_sort_pairs_static(uint32_t* keys, uint32_t* keys_alt, uint32
     using namespace inpc;
     cudaStream_t stream = static_cast<cudaStream_t>(stream_);
     if (result_in_alt) *result_in_alt = 0;
-    if (n < 0) { set_error("inpc_sort_pairs_static: n=%lld is negative", (long long)n); return INPC_E_INVALID; }
     if (n > kStaticMaxPairs) {
         set_error("inpc_sort_pairs_static: n=%lld exceeds the fixed capacity of %lld pairs; use inpc_sort_pairs with a caller workspace",
                   (long long)n, (long long)kStaticMaxPairs);
         return INPC_E_CAPACITY;
     }
-    if (end_bit < 0 || end_bit > 32) { set_error("inpc_sort_pairs_static: end_bit=%d out of range", end_bit); return INPC_E_INVALID; }
-    if (n <= 1 || end_bit == 0) return INPC_OK;
-    if (!keys || !keys_alt || !values || !values_alt) { set_error("inpc_sort_pairs_static: null pointer"); return INPC_E_INVALID; }
-    if ((reinterpret_cast<uintptr_t>(keys) | reinterpret_cast<uintptr_t>(keys_alt)) & 15u) {
-        set_error("inpc_sort_pairs_static: key buffers must be 16-byte aligned");
+    // the hand-written size of the fixed array must be what the ordinary workspace layout needs at capacity
+    if (sort_workspace_bytes(kStaticMaxPairs) != kStaticWorkspaceBytes) {
+        set_error("inpc_sort_pairs_static: fixed scratch of %zu bytes does not match the workspace layout (%zu bytes)",
+                  kStaticWorkspaceBytes, sort_workspace_bytes(kStaticMaxPairs));
         return INPC_E_INVALID;
     }
+    bool nothing = false;
+    int rc = check_sort_args("inpc_sort_pairs_static", keys, keys_alt, values, values_alt, n, end_bit, &nothing);
+    if (rc != INPC_OK || nothing) return rc;
     void* scratch = nullptr;
-    int rc = static_scratch_for_current_device(&scratch);
+    rc = static_scratch_for_current_device(&scratch);
     if (rc != INPC_OK) return rc;
-
-    PassTable pt;
-    pt.n_passes = ceil_div(end_bit, kRadixBits);
-    int bit = 0;
-    for (int p = 0; p < kMaxPasses; ++p) { pt.shift[p] = 0; pt.bits[p] = 0; }
-    for (int p = 0; p < pt.n_passes; ++p) {
-        const int b = (end_bit - bit + (pt.n_passes - p) - 1) / (pt.n_passes - p);
-        pt.shift[p] = bit;
-        pt.bits[p] = b;
-        bit += b;
-    }
-    SortWorkspace w = carve_sort_workspace(scratch, n);
-    const int64_t tiles = ceil_div<int64_t>(n, kTile);
-    // the array keeps the previous call's histograms, tickets and look-back flags: clear what this call reads
-    INPC_CUDA_TRY(cudaMemsetAsync(scratch, 0, w.zero_bytes + (size_t)pt.n_passes * tiles * kRadix * sizeof(unsigned), stream));
+    // the status words of this entry point live behind the workspace, inside the same fixed array
     unsigned* status = reinterpret_cast<unsigned*>(static_cast<unsigned char*>(scratch) + kStaticWorkspaceBytes);
-
-    const int hist_blocks = (int)ceil_div<int64_t>(n, kHistItemsPerBlock);
-    radix_histogram_kernel<<<hist_blocks, kHistThreads, 0, stream>>>(keys, n, pt, w.hist);
-    INPC_LAUNCH_CHECK("radix_histogram_kernel");
-    radix_scan_histogram_kernel<<<pt.n_passes, kRadix, 0, stream>>>(w.hist, w.base);
-    INPC_LAUNCH_CHECK("radix_scan_histogram_kernel");
-    uint32_t *kin = keys, *kout = keys_alt, *vin = values, *vout = values_alt;
-    for (int p = 0; p < pt.n_passes; ++p) {
-        rc = launch_onesweep_pass<false>(tiles, kin, vin, kout, vout, n, pt.shift[p], pt.bits[p], w.base + p * kRadix,
-                                         w.state + (size_t)p * tiles * kRadix, w.ticket + p, status, nullptr, nullptr, stream);
-        if (rc != INPC_OK) return rc;
-        uint32_t* t = kin; kin = kout; kout = t;
-        t = vin; vin = vout; vout = t;
-    }
-    if (result_in_alt) *result_in_alt = pt.n_passes & 1;
-    return INPC_OK;
+    return sort_pairs_with("inpc_sort_pairs_static", keys, keys_alt, values, values_alt, n, end_bit, scratch, status, result_in_alt, stream);
 }
 
 extern "C" size_t inpc_sort_workspace_bytes(int64_t n) { return inpc::sort_workspace_bytes(n < 0 ? 0 : n); }

@@ -17,25 +17,6 @@
 
 #include <type_traits>
 
-// 1: the last pass of the depth sort also writes the tile bounds in depth order, so that the instance
-// emission reads them sequentially.  Measured on B200 (2^23 points): the emission gets 50 us faster but
-// the pass 90 us slower (the gather's latency is not hidden after all), so it is off.
-#ifndef INPC_SORT_CARRIES_BOUNDS
-#define INPC_SORT_CARRIES_BOUNDS 0
-#endif
-
-// Resident blocks per SM the 8x8 blend kernels are compiled for (caps their registers).
-#ifndef INPC_FWD_MIN_BLOCKS
-#define INPC_FWD_MIN_BLOCKS 1
-#endif
-#ifndef INPC_BWD_MIN_BLOCKS
-#define INPC_BWD_MIN_BLOCKS 1
-#endif
-
-#ifndef INPC_MIN_BATCHES
-#define INPC_MIN_BATCHES 16
-#endif
-
 namespace inpc {
 
 namespace {
@@ -44,6 +25,7 @@ constexpr float kTransmittanceEps = 1e-4f;      // include/bilinear/config.h:16
 constexpr float kOneMinusAlphaEps = 1e-8f;      // include/bilinear/config.h:17
 constexpr float kDilation = 0.16f;              // include/gaussian/config.h:19
 constexpr float kTrainGaussThreshold = 0.01110899653f;   // src/gaussian/kernels.cu:452
+
 
 // Checked build (-DINPC_CHECK_INDICES, `python -m inpc_b200._build --checked`): every point index read
 // from a sorted list is range-checked before it is used for a gather; a bad one is counted, reported
@@ -479,27 +461,57 @@ __global__ void __launch_bounds__(kScanThreads) scan_u32_kernel(unsigned* __rest
     }
 }
 
+// Instance key: the tile index in the low 24 bits, the only bits the tile sort looks at (it carries the
+// bits above its range along).  For bilinear splats on 8x8 tiles the 8 bits above hold where the 2x2
+// pixel footprint sits in the tile: column of its left pixel relative to the tile plus one (0..8) in
+// bits 24..27, row of its upper pixel plus one in bits 28..31.  The blend then knows which pixels an
+// instance can reach from the key alone, without fetching the point record.
+constexpr unsigned kTileKeyBits = 24;
+constexpr uint32_t kTileKeyMask = (1u << kTileKeyBits) - 1u;
+
 // One (tile key, point id) pair per touched tile, row-major over the point's bounds, points in depth
-// order (src/bilinear/kernels.cu:198-220).
-// `bounds` is in depth order (bounds[s], SORTED) or in point order (bounds[id]).
-template <bool SORTED>
+// order (src/bilinear/kernels.cu:198-220).  CODED (bilinear, 8x8 tiles): bounds and footprint origin are
+// recomputed from the record's screen position with the expressions of the projection pass (same
+// inputs, same operations, hence the same bounds), so that one 8-byte gather serves both.
+template <bool CODED>
 __global__ void __launch_bounds__(kInstThreads) emit_instances_kernel(const uint32_t* __restrict__ sorted_ids,
-                                                                      const uint2* __restrict__ bounds, int64_t n_visible,
-                                                                      const unsigned* __restrict__ block_base, int gw,
+                                                                      const uint2* __restrict__ bounds, const PointRec* __restrict__ rec,
+                                                                      int64_t n_visible, const unsigned* __restrict__ block_base, int gw, int gh,
                                                                       uint32_t* __restrict__ inst_keys,
                                                                       uint32_t* __restrict__ inst_ids) {
     __shared__ unsigned s_scan[kInstThreads / 32 + 1];
     const int64_t s = (int64_t)blockIdx.x * kInstThreads + threadIdx.x;
     uint32_t id = 0;
-    uint2 b = make_uint2(0u, 0u);
-    if (s < n_visible) { id = checked_point(__ldg(sorted_ids + s)); b = __ldg(bounds + (SORTED ? s : (int64_t)id)); }
-    const unsigned c = tiles_of(b);
+    unsigned x0 = 0, x1 = 0, y0 = 0, y1 = 0;
+    int qx = 0, qy = 0;
+    if (s < n_visible) {
+        id = checked_point(__ldg(sorted_ids + s));
+        if (CODED) {
+            const float2 a = __ldg(reinterpret_cast<const float2*>(rec + id));
+            constexpr float itf = 0.125f;
+            x0 = min((unsigned)gw, (unsigned)max(0, __float2int_rd((a.x - 0.5f) * itf)));
+            x1 = min((unsigned)gw, (unsigned)max(0, __float2int_ru((a.x + 0.5f) * itf)));
+            y0 = min((unsigned)gh, (unsigned)max(0, __float2int_rd((a.y - 0.5f) * itf)));
+            y1 = min((unsigned)gh, (unsigned)max(0, __float2int_ru((a.y + 0.5f) * itf)));
+            qx = __float2int_rd(a.x - 0.5f);
+            qy = __float2int_rd(a.y - 0.5f);
+        } else {
+            const uint2 b = __ldg(bounds + id);
+            x0 = b.x & 0xffffu; x1 = b.x >> 16; y0 = b.y & 0xffffu; y1 = b.y >> 16;
+        }
+    }
+    const unsigned c = (x1 - x0) * (y1 - y0);
     unsigned total;
     unsigned off = block_base[blockIdx.x] + block_exclusive_scan(c, s_scan, &total);
-    const unsigned x0 = b.x & 0xffffu, x1 = b.x >> 16, y0 = b.y & 0xffffu, y1 = b.y >> 16;
     for (unsigned ty = y0; ty < y1; ++ty)
         for (unsigned tx = x0; tx < x1; ++tx) {
-            inst_keys[off] = ty * (unsigned)gw + tx;
+            uint32_t key = ty * (unsigned)gw + tx;
+            if (CODED) {
+                const unsigned cx = (unsigned)min(max(qx - (int)tx * 8 + 1, 0), 8);
+                const unsigned cy = (unsigned)min(max(qy - (int)ty * 8 + 1, 0), 8);
+                key |= (cx << kTileKeyBits) | (cy << (kTileKeyBits + 4));
+            }
+            inst_keys[off] = key;
             inst_ids[off] = id;
             ++off;
         }
@@ -511,12 +523,12 @@ __global__ void __launch_bounds__(256) tile_ranges_kernel(const uint32_t* __rest
     constexpr int kPer = 8;
     const int64_t first = ((int64_t)blockIdx.x * 256 + threadIdx.x) * kPer;
     if (first >= n_instances) return;
-    uint32_t prev = first > 0 ? __ldg(keys + first - 1) : 0u;
+    uint32_t prev = first > 0 ? __ldg(keys + first - 1) & kTileKeyMask : 0u;
 #pragma unroll
     for (int k = 0; k < kPer; ++k) {
         const int64_t i = first + k;
         if (i >= n_instances) break;
-        const uint32_t key = __ldg(keys + i);
+        const uint32_t key = __ldg(keys + i) & kTileKeyMask;
         if (i == 0) ranges[key].x = 0u;
         else if (key != prev) { ranges[prev].y = (unsigned)i; ranges[key].x = (unsigned)i; }
         if (i == n_instances - 1) ranges[key].y = (unsigned)n_instances;
@@ -532,8 +544,8 @@ __global__ void __launch_bounds__(256) tile_ranges_kernel(const uint32_t* __rest
 // masks of the (up to four) pixels it reaches, and every pixel thread then walks only its own set
 // bits, in staged (= depth) order.  Per-fragment results that belong to the point (blending weight,
 // gradients) go to a private shared-memory slot per (instance, footprint corner) and are reduced by
-// the instance thread in a fixed order: no shared-memory atomics, one global (vector) atomic per
-// instance.  Two block barriers per batch.
+// the instance thread in a fixed order (the only shared-memory atomics are the ORs that build the masks),
+// one global (vector) atomic per instance.  Two block barriers per batch.
 //
 // (2) Segments.  Front-to-back compositing is associative: (C, T) o (C', T') = (C + T C', T T').  A
 // tile's instance list is cut into segments of at least 16 batches (at most 64 segments per tile) and
@@ -554,17 +566,8 @@ struct __align__(16) Segment {
     uint32_t begin, end;   // instance range of this segment
     uint32_t info;         // index of the segment within its tile | number of segments of the tile << 16
 };
-#ifndef INPC_MAX_SEGMENTS
-#define INPC_MAX_SEGMENTS 64
-#endif
-constexpr int kMaxSegmentsPerTile = INPC_MAX_SEGMENTS;
-constexpr int kMinBatchesPerSegment = INPC_MIN_BATCHES;
-#ifndef INPC_IPT8
-#define INPC_IPT8 1
-#endif
-#ifndef INPC_IPT16
-#define INPC_IPT16 1
-#endif
+constexpr int kMaxSegmentsPerTile = 64;
+constexpr int kMinBatchesPerSegment = 16;
 
 __device__ __forceinline__ unsigned segment_length(unsigned len, unsigned batch) {
     const unsigned s_min = batch * (unsigned)kMinBatchesPerSegment;
@@ -797,7 +800,7 @@ __global__ void __launch_bounds__(T * T) blend_prefix_kernel(const Segment* __re
 }
 
 template <int T, int IPT, int KIND>
-__global__ void __launch_bounds__(T * T, T == 8 ? INPC_FWD_MIN_BLOCKS : 1) blend_bilinear_forward_kernel(
+__global__ void __launch_bounds__(T * T) blend_bilinear_forward_kernel(
     const Segment* __restrict__ segs, const uint32_t* __restrict__ n_segments, const uint32_t* __restrict__ inst_ids,
     const PointRec* __restrict__ rec, float* __restrict__ seg_T, float4* __restrict__ seg_C, float* __restrict__ seg_Z,
     float* __restrict__ image, float* __restrict__ depth_image, float* __restrict__ alpha_image,
@@ -994,7 +997,7 @@ __global__ void __launch_bounds__(T * T) blend_combine_kernel(const Segment* __r
 }
 
 template <int T, int IPT>
-__global__ void __launch_bounds__(T * T, T == 8 ? INPC_BWD_MIN_BLOCKS : 1) blend_bilinear_backward_kernel(
+__global__ void __launch_bounds__(T * T) blend_bilinear_backward_kernel(
     const Segment* __restrict__ segs, const uint32_t* __restrict__ n_segments, const uint32_t* __restrict__ inst_ids,
     const PointRec* __restrict__ rec, const float* __restrict__ seg_T, const float4* __restrict__ seg_C,
     const float* __restrict__ grad_image, const float* __restrict__ grad_alpha, const float* __restrict__ image,
@@ -1133,6 +1136,640 @@ __global__ void __launch_bounds__(T * T, T == 8 ? INPC_BWD_MIN_BLOCKS : 1) blend
 template <int T, int IPT>
 constexpr size_t backward_smem_bytes() {
     return (size_t)T * T * IPT * (16 + 16 + 4 * 16 + 4 * 4) + (size_t)(T * T * IPT / 32) * T * T * 4;
+}
+
+// ------------------------------------------------------------------------------------------------
+// Bilinear blend on 8x8 tiles, one warp per work item (the default path).
+//
+// (1) Dead instances.  A pixel stops taking fragments once its transmittance has fallen below the
+// threshold, and in a dense scene most instances of a tile's list lie behind pixels that have already
+// stopped.  Such an instance has no effect whatsoever, so it is discarded from its sort key alone --
+// the key says which pixels of the tile it reaches (see kTileKeyBits), a mask of stopped pixels lives
+// in registers -- and its 32-byte record is never fetched.  A warp streams the keys of its item (128
+// per step, loaded one step ahead), pushes the point ids of the instances that may still contribute
+// into a ring in shared memory and blends them in batches of 32, the records of the next batch being
+// in flight while the current one is blended.  The mask used by the filter lags the blend by a batch;
+// that only lets a few extra instances through, whose fragments are then dropped.
+//
+// (2) A batch.  The geometry of a fragment (bilinear weight, alpha) depends on nothing that came
+// before it, the blend itself is a serial chain per pixel.  So lane j first evaluates the (up to) four
+// fragments of staged instance j, then the fragments are brought into per-pixel order in shared
+// memory (bit masks per pixel give every fragment its rank, a scan of the counts gives every pixel
+// its offset), and only then does every lane run down the short list of its own pixel: load alpha
+// and features, accumulate, update the transmittance.  What a fragment saw (its transmittance) goes
+// back to the instance lane, which forms the per-point sums in fixed corner order.  The arithmetic
+// and its order are those of a plain front-to-back loop per pixel.
+//
+// (3) Segments.  Front-to-back compositing is associative: (C, T) o (C', T') = (C + T C', T T').  A
+// tile's list is cut into segments of kSegmentLength instances and every (tile half, segment) is one
+// item, so a tile with 100x the average load does not set the critical path.  Pass FIRST blends
+// segment 0 of every tile exactly; the pixels that dense clusters hit stop there.  Pass PRODUCT
+// computes, for the later segments, the per-pixel product of (1 - alpha) over the segment, starting
+// from (and filtering by) the state segment 0 left, so the work it repeats is small; a per-tile
+// prefix turns the products into the transmittance at segment start; pass REST blends the later
+// segments from that state; a per-tile combine adds the segment colours in order (and leaves the
+// colour prefix for the backward pass, whose items are then independent).
+//
+// An item covers the upper or lower 8x4 half of a tile, one pixel per lane; both halves stream the same
+// list and each keeps what reaches its own pixels.
+//
+// The forward passes write the compacted lists they blended (point ids in depth order, per item) for
+// the backward pass, which therefore neither filters nor reads keys.
+//
+// Arithmetic per fragment: src/bilinear/kernels.cu:283-303 (forward), :361-415 (backward),
+// :462-475 (inference).
+// ------------------------------------------------------------------------------------------------
+constexpr int kWarpBlendWarps = 8;        // warps per block; every warp works on items of its own
+constexpr int kQueueCap = 256;            // ring of candidate point ids per warp: >= 31 left over + 128 of one filter step
+constexpr int kFilterKeys = 4;            // keys per lane and filter step
+constexpr unsigned kSegmentLength = 1024;   // instances per segment (512, 2048 and 4096 measured within 5 % of it)
+constexpr int kBatchFragments = 128;      // 32 instances x 4 fragments
+enum { PASS_FIRST = 0, PASS_PRODUCT = 1, PASS_REST = 2 };
+
+// Pixels of the tile (bit = row * 8 + column) that the instance with this key reaches.
+__device__ __forceinline__ unsigned long long key_pixels(unsigned code) {
+    const unsigned cx = code & 15u, cy = code >> 4;
+    const unsigned m = ((3u << cx) >> 1) & 0xFFu;                        // columns cx - 1 and cx, clipped to the tile
+    const unsigned long long two = (unsigned long long)(m | (m << 8));   // the same columns in two consecutive rows
+    if (cx > 8u || cy > 8u) return 0ull;
+    return cy == 0u ? two >> 8 : two << (8u * (cy - 1u));                // rows cy - 1 and cy, clipped likewise
+}
+
+__device__ __forceinline__ unsigned warp_segments(unsigned len) { return max(1u, ceil_div(len, kSegmentLength)); }
+
+// Work lists of the warp blend, step 1 (one block): tile_first[t] = number of segments of the tiles before t
+// (empty tiles have none), tile_rank[t] = number of non-empty tiles before t, counts[0] = non-empty tiles,
+// counts[1] = segments behind a tile's first.
+__global__ void __launch_bounds__(kScanThreads) warp_items_scan_kernel(const uint2* __restrict__ ranges, int n_tiles,
+                                                                      uint32_t* __restrict__ tile_first, uint32_t* __restrict__ tile_rank,
+                                                                      uint32_t* __restrict__ counts) {
+    constexpr int kItems = 4;
+    __shared__ unsigned s_scan[kScanThreads / 32 + 1];
+    unsigned run_seg = 0, run_tiles = 0;
+    for (int base = 0; base < n_tiles; base += kScanThreads * kItems) {
+        const int t0 = base + threadIdx.x * kItems;
+        unsigned ns[kItems];
+        unsigned sum_seg = 0, sum_tiles = 0;
+#pragma unroll
+        for (int k = 0; k < kItems; ++k) {
+            ns[k] = 0u;
+            if (t0 + k < n_tiles) {
+                const uint2 r = __ldg(ranges + t0 + k);
+                ns[k] = r.y > r.x ? warp_segments(r.y - r.x) : 0u;
+            }
+            sum_seg += ns[k];
+            sum_tiles += ns[k] ? 1u : 0u;
+        }
+        // both scans in one: segments in the low 20 bits would overflow, so two calls
+        unsigned total_seg, total_tiles;
+        unsigned ex_seg = run_seg + block_exclusive_scan(sum_seg, s_scan, &total_seg);
+        unsigned ex_tiles = run_tiles + block_exclusive_scan(sum_tiles, s_scan, &total_tiles);
+#pragma unroll
+        for (int k = 0; k < kItems; ++k) {
+            if (t0 + k < n_tiles) {
+                tile_first[t0 + k] = ex_seg;
+                tile_rank[t0 + k] = ex_tiles;
+                ex_seg += ns[k];
+                ex_tiles += ns[k] ? 1u : 0u;
+            }
+        }
+        run_seg += total_seg;
+        run_tiles += total_tiles;
+    }
+    if (threadIdx.x == 0) { counts[0] = run_tiles; counts[1] = run_seg - run_tiles; }
+}
+
+// Step 2 (one thread per tile): list0 = the non-empty tiles (their segment 0), list1 = (tile, segment) of every
+// later segment.
+__global__ void __launch_bounds__(256) warp_items_fill_kernel(const uint2* __restrict__ ranges, int n_tiles,
+                                                             const uint32_t* __restrict__ tile_first, const uint32_t* __restrict__ tile_rank,
+                                                             uint32_t* __restrict__ list0, uint2* __restrict__ list1) {
+    const int t = blockIdx.x * 256 + threadIdx.x;
+    if (t >= n_tiles) return;
+    const uint2 r = __ldg(ranges + t);
+    if (r.y <= r.x) return;
+    const unsigned ns = warp_segments(r.y - r.x);
+    const unsigned rank = tile_rank[t], first = tile_first[t];
+    list0[rank] = (uint32_t)t;
+    // later segments: position = segments before this tile minus tiles before it
+    for (unsigned s = 1; s < ns; ++s) list1[first - rank + s - 1u] = make_uint2((uint32_t)t, s);
+}
+
+// Shared memory of one warp of the forward passes.
+template <bool BLEND, bool WEIGHTS, bool DEPTH>
+struct WarpForwardSmem {
+    unsigned mask[32];                               // per pixel: staged instances with a fragment there
+    unsigned off[32];                                // per pixel: first slot of its fragment list
+    float frag_alpha[kBatchFragments];               // fragments in per-pixel order
+    float4 frag_feat[BLEND ? kBatchFragments : 1];
+    float frag_depth[DEPTH ? kBatchFragments : 1];
+    float frag_seen[WEIGHTS ? kBatchFragments : 1];  // transmittance the fragment met (0: it was dropped)
+    uint32_t queue[kQueueCap];
+};
+
+template <int PASS, int KIND>
+__global__ void __launch_bounds__(kWarpBlendWarps * 32) blend_bilinear_warp_forward_kernel(
+    const uint32_t* __restrict__ list0, const uint2* __restrict__ list1, const uint32_t* __restrict__ counts, unsigned* __restrict__ ticket,
+    const uint2* __restrict__ ranges, const uint32_t* __restrict__ tile_first, const uint32_t* __restrict__ inst_keys,
+    const uint32_t* __restrict__ inst_ids, const PointRec* __restrict__ rec, float* __restrict__ seg_T, float4* __restrict__ seg_C,
+    float* __restrict__ seg_Z, float* __restrict__ seg_E, float* __restrict__ image, float* __restrict__ depth_image,
+    float* __restrict__ alpha_image, float* __restrict__ blending_weights, uint32_t* __restrict__ kept0, uint32_t* __restrict__ kept1,
+    uint32_t* __restrict__ n_kept, int width, int height, int gw) {
+    constexpr unsigned kFull = 0xffffffffu;
+    constexpr bool kBlend = PASS != PASS_PRODUCT;               // colours, weights, lists; PRODUCT only multiplies
+    constexpr bool kWeights = kBlend && KIND == BLEND_TRAIN;
+    constexpr bool kDepth = kBlend && KIND == BLEND_INFER;
+    using Smem = WarpForwardSmem<kBlend, kWeights, kDepth>;
+    __shared__ Smem s_all[kWarpBlendWarps];
+    __shared__ unsigned long long s_reach[256];     // key code -> pixels reached
+    const unsigned lane = lane_id();
+    const unsigned lt_mask = (1u << lane) - 1u;
+    Smem& sm = s_all[threadIdx.x >> 5];
+    s_reach[threadIdx.x] = key_pixels(threadIdx.x);
+    sm.mask[lane] = 0u;   // the masks start at zero and every batch leaves them at zero again
+    __syncthreads();
+    const unsigned n_items = __ldg(counts + (PASS == PASS_FIRST ? 0 : 1)) * 2u;
+
+    for (;;) {
+        unsigned item = 0;
+        if (lane == 0) item = atomicAdd(ticket, 1u);
+        item = __shfl_sync(kFull, item, 0);
+        if (item >= n_items) break;
+        unsigned tile, seg;
+        if (PASS == PASS_FIRST) { tile = __ldg(list0 + (item >> 1)); seg = 0u; }
+        else { const uint2 d = __ldg(list1 + (item >> 1)); tile = d.x; seg = d.y; }
+        const int half = (int)(item & 1u);
+        const uint2 rg_tile = __ldg(ranges + tile);
+        const unsigned n_seg = warp_segments(rg_tile.y - rg_tile.x);
+        if (PASS == PASS_PRODUCT && seg + 1u == n_seg) continue;   // the last segment's product is never needed
+        const unsigned first = __ldg(tile_first + tile);
+        const size_t sidx = (size_t)(first + seg) * 2u + half;      // this item's slot in the per-segment arrays
+        const size_t sidx0 = (size_t)first * 2u + half;             // segment 0 of the same tile half
+        uint2 rg;
+        rg.x = rg_tile.x + seg * kSegmentLength;
+        rg.y = min(rg_tile.y, rg.x + kSegmentLength);
+        const int tx = (int)(tile % (unsigned)gw), ty = (int)(tile / (unsigned)gw);
+        const int px0 = tx * 8, py0 = ty * 8 + 4 * half;            // first pixel of this half
+        const int px = px0 + (int)(lane & 7u), py = py0 + (int)(lane >> 3);
+        const bool inside = px < width && py < height;
+
+        float Tr = 1.0f, T0 = 1.0f, Z = 0.0f, C0 = 0.0f, C1 = 0.0f, C2 = 0.0f, C3 = 0.0f;
+        bool done = !inside;
+        if (PASS == PASS_PRODUCT) {
+            // the state segment 0 left: a pixel that has stopped there stays stopped; for the others the
+            // product is taken until T0 * product falls below the threshold (the true transmittance at
+            // that point is smaller still, so everything behind is dead whatever the product says)
+            T0 = seg_T[sidx0 * 32 + lane];
+            done = done || T0 < kTransmittanceEps;
+        } else if (PASS == PASS_REST) {
+            Tr = seg_T[sidx * 32 + lane];
+            done = done || Tr < kTransmittanceEps;
+        }
+        unsigned done_w = __ballot_sync(kFull, done);   // bit l = pixel of lane l has stopped (warp-uniform)
+
+        // ---- filter: keys are loaded one step ahead of their use
+        unsigned pos = rg.x;           // next key to load
+        unsigned step_pos = rg.x;      // first key of the loaded step
+        bool loaded = false;
+        uint32_t kq[kFilterKeys], iq[kFilterKeys];
+        auto load_step = [&]() {
+            step_pos = pos;
+#pragma unroll
+            for (int k = 0; k < kFilterKeys; ++k) {
+                const unsigned idx = pos + 32u * k + lane;
+                const bool ok = idx < rg.y;
+                kq[k] = ok ? __ldg(inst_keys + idx) : 0xFFFFFFFFu;   // code 0xFF reaches nothing
+                iq[k] = ok ? __ldg(inst_ids + idx) : 0u;
+            }
+            pos = min(pos + 32u * kFilterKeys, rg.y);
+            loaded = true;
+        };
+        if (pos < rg.y) load_step();
+        unsigned q_head = 0, q_tail = 0;
+        auto fill = [&]() {
+            while (q_tail - q_head < 32u && loaded) {
+                uint32_t ck[kFilterKeys], ci[kFilterKeys];
+#pragma unroll
+                for (int k = 0; k < kFilterKeys; ++k) { ck[k] = kq[k]; ci[k] = iq[k]; }
+                loaded = false;
+                if (pos < rg.y) load_step();
+#pragma unroll
+                for (int k = 0; k < kFilterKeys; ++k) {
+                    const unsigned long long reach = s_reach[ck[k] >> kTileKeyBits];
+                    const bool keep = ((unsigned)(reach >> (32 * half)) & ~done_w) != 0u;
+                    const unsigned b = __ballot_sync(kFull, keep);
+                    if (keep) sm.queue[(q_tail + __popc(b & lt_mask)) & (kQueueCap - 1)] = ci[k];
+                    q_tail += __popc(b);
+                }
+            }
+            __syncwarp();
+        };
+        int n_cur = 0, n_nxt = 0;
+        uint32_t id_cur = 0, id_nxt = 0;
+        float4 a_cur, f_cur, a_nxt, f_nxt;
+        a_cur = f_cur = a_nxt = f_nxt = make_float4(0.f, 0.f, 0.f, 0.f);
+        auto gather_next = [&]() {
+            n_nxt = (int)min(32u, q_tail - q_head);
+            if ((int)lane < n_nxt) {
+                id_nxt = checked_point(sm.queue[(q_head + lane) & (kQueueCap - 1)]);
+                const float4* p = reinterpret_cast<const float4*>(rec + id_nxt);
+                a_nxt = __ldg(p);
+                if (kBlend) f_nxt = __ldg(p + 1);
+            }
+            q_head += (unsigned)n_nxt;
+        };
+        fill();
+        gather_next();
+        uint32_t* kept = half ? kept1 : kept0;
+        unsigned n_out = 0;
+        while (n_nxt > 0) {
+            n_cur = n_nxt; id_cur = id_nxt; a_cur = a_nxt; f_cur = f_nxt;
+            fill();
+            gather_next();
+            if (kWeights) {
+                if ((int)lane < n_cur) kept[rg.x + n_out + lane] = id_cur;
+                n_out += (unsigned)n_cur;
+            }
+            // ---- lane j: the fragments of staged instance j
+            const int qx = __float2int_rd(a_cur.x - 0.5f) - px0;
+            const int qy = __float2int_rd(a_cur.y - 0.5f) - py0;
+            float al[4], wg[4];
+            int pix[4];
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                const int cx = qx + (c & 1), cy = qy + (c >> 1);
+                const float pcx = (float)(px0 + cx) + 0.5f, pcy = (float)(py0 + cy) + 0.5f;
+                const float dx = fabsf(a_cur.x - pcx), dy = fabsf(a_cur.y - pcy);
+                wg[c] = __saturatef(1.0f - dx) * __saturatef(1.0f - dy);
+                al[c] = a_cur.z * wg[c];
+                const int p = cy * 8 + cx;
+                const bool ok = (int)lane < n_cur && cx >= 0 && cx < 8 && cy >= 0 && cy < 4 && dx < 1.0f && dy < 1.0f &&
+                                !((done_w >> (p & 31)) & 1u);
+                pix[c] = ok ? p : -1;
+                if (ok) atomicOr(sm.mask + p, 1u << lane);
+            }
+            __syncwarp();
+            // ---- per-pixel order: offset of every pixel's list, slot of every fragment
+            const unsigned my_mask = sm.mask[lane];
+            const unsigned cnt = __popc(my_mask);
+            const unsigned off = warp_inclusive_scan(cnt) - cnt;
+            sm.off[lane] = off;
+            __syncwarp();
+            int slot[4];
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                slot[c] = 0;
+                if (pix[c] >= 0) {
+                    slot[c] = (int)(sm.off[pix[c]] + __popc(sm.mask[pix[c]] & lt_mask));
+                    sm.frag_alpha[slot[c]] = al[c];
+                    if (kBlend) sm.frag_feat[slot[c]] = f_cur;
+                    if (kDepth) sm.frag_depth[slot[c]] = a_cur.w;
+                }
+            }
+            __syncwarp();
+            // ---- every lane runs down the list of its own pixel, front to back
+            if (my_mask) sm.mask[lane] = 0u;
+            for (unsigned k = off; k < off + cnt; ++k) {
+                if (done) {
+                    if (kWeights) sm.frag_seen[k] = 0.0f;
+                    continue;
+                }
+                const float a = sm.frag_alpha[k];
+                if (kBlend) {
+                    const float4 f = sm.frag_feat[k];
+                    const float bw = Tr * a;
+                    if (kWeights) sm.frag_seen[k] = Tr;
+                    C0 += bw * f.x; C1 += bw * f.y; C2 += bw * f.z; C3 += bw * f.w;
+                    if (kDepth) Z += bw * sm.frag_depth[k];
+                    Tr *= 1.0f - a;
+                    if (Tr < kTransmittanceEps) done = true;
+                } else {
+                    Tr *= 1.0f - a;
+                    if (T0 * Tr < kTransmittanceEps) done = true;
+                }
+            }
+            __syncwarp();
+            if (kWeights) {
+                // blending weight of every staged instance: its (up to) four fragments in fixed corner order
+                if ((int)lane < n_cur) {
+                    float v[4];
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        const float bw = pix[c] >= 0 ? sm.frag_seen[slot[c]] * al[c] : 0.0f;
+                        v[c] = bw > 0.0f ? bw * wg[c] : 0.0f;
+                    }
+                    const float sum = ((v[0] + v[1]) + v[2]) + v[3];
+                    if (sum > 0.0f) atomicAdd(blending_weights + id_cur, sum);
+                }
+            }
+            done_w = __ballot_sync(kFull, done);
+            __syncwarp();
+            if (done_w == kFull) break;   // every pixel has stopped: the rest of the list has no effect
+        }
+        if (kWeights && lane == 0) n_kept[sidx] = n_out;
+
+        if (PASS == PASS_PRODUCT) {
+            seg_T[sidx * 32 + lane] = Tr;
+            continue;
+        }
+        const int64_t n_px = (int64_t)width * height;
+        const int64_t pi = (int64_t)py * width + px;
+        if (n_seg == 1u) {
+            if (inside) {
+                image[pi] = C0;
+                image[n_px + pi] = C1;
+                image[2 * n_px + pi] = C2;
+                image[3 * n_px + pi] = C3;
+                if (KIND == BLEND_INFER) {
+                    const float A = 1.0f - Tr;
+                    depth_image[pi] = A > 0.0f ? Z / A : 0.0f;
+                    alpha_image[pi] = Tr < kTransmittanceEps ? 1.0f : A;
+                } else {
+                    alpha_image[pi] = Tr < kTransmittanceEps ? 1.0f : 1.0f - Tr;
+                }
+            }
+        } else {
+            // partial colour of this segment; the per-tile combine adds the segments up in order
+            const size_t si = sidx * 32 + lane;
+            seg_C[si] = make_float4(C0, C1, C2, C3);
+            if (PASS == PASS_FIRST) seg_T[si] = Tr;   // the exact state behind segment 0
+            if (KIND == BLEND_INFER) {
+                seg_Z[si] = Z;
+                seg_E[si] = Tr;
+            } else if (seg + 1u == n_seg && inside) {
+                alpha_image[pi] = Tr < kTransmittanceEps ? 1.0f : 1.0f - Tr;
+            }
+        }
+    }
+}
+
+// Per tile half with several segments, between the PRODUCT and REST passes: seg_T of segment s >= 1 becomes
+// the transmittance at its start = (state behind segment 0) * product of the segments 1 .. s-1.
+__global__ void __launch_bounds__(kWarpBlendWarps * 32) warp_blend_prefix_kernel(const uint32_t* __restrict__ list0, const uint32_t* __restrict__ counts,
+                                                                                 const uint2* __restrict__ ranges,
+                                                                                 const uint32_t* __restrict__ tile_first, float* __restrict__ seg_T) {
+    const unsigned lane = lane_id();
+    const unsigned n_parts = __ldg(counts) * 2u;
+    for (unsigned w = blockIdx.x * kWarpBlendWarps + (threadIdx.x >> 5); w < n_parts; w += gridDim.x * kWarpBlendWarps) {
+        const unsigned tile = __ldg(list0 + (w >> 1));
+        const unsigned half = w & 1u;
+        const uint2 r = __ldg(ranges + tile);
+        const unsigned n_seg = warp_segments(r.y - r.x);
+        if (n_seg == 1u) continue;
+        const unsigned first = __ldg(tile_first + tile);
+        float* base = seg_T + ((size_t)first * 2u + half) * 32 + lane;   // segment g of this half: base[g * 64]
+        float run = base[0];
+        for (unsigned g0 = 1; g0 < n_seg; g0 += 8) {
+            float product[8];
+#pragma unroll
+            for (int k = 0; k < 8; ++k) product[k] = g0 + k + 1u < n_seg ? base[(size_t)(g0 + k) * 64] : 1.0f;
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                if (g0 + k < n_seg) base[(size_t)(g0 + k) * 64] = run;
+                run *= product[k];
+            }
+        }
+    }
+}
+
+// Per tile half with several segments, after the REST pass: image = sum of the segment colours in order.
+// For training the running sum before each segment replaces the segment's own colour (the backward pass
+// starts from it).  Inference: expected depth, and the transmittance where the pixel stopped = the end value
+// of the first segment that fell below the threshold.
+template <int KIND>
+__global__ void __launch_bounds__(kWarpBlendWarps * 32) warp_blend_combine_kernel(
+    const uint32_t* __restrict__ list0, const uint32_t* __restrict__ counts, const uint2* __restrict__ ranges,
+    const uint32_t* __restrict__ tile_first, float4* __restrict__ seg_C, const float* __restrict__ seg_Z, const float* __restrict__ seg_E,
+    float* __restrict__ image, float* __restrict__ depth_image, float* __restrict__ alpha_image, int width, int height, int gw) {
+    const unsigned lane = lane_id();
+    const unsigned n_parts = __ldg(counts) * 2u;
+    for (unsigned w = blockIdx.x * kWarpBlendWarps + (threadIdx.x >> 5); w < n_parts; w += gridDim.x * kWarpBlendWarps) {
+        const unsigned tile = __ldg(list0 + (w >> 1));
+        const unsigned half = w & 1u;
+        const uint2 r = __ldg(ranges + tile);
+        const unsigned n_seg = warp_segments(r.y - r.x);
+        if (n_seg == 1u) continue;
+        const unsigned first = __ldg(tile_first + tile);
+        const int tx = (int)(tile % (unsigned)gw), ty = (int)(tile / (unsigned)gw);
+        const int px = tx * 8 + (int)(lane & 7u);
+        const int py = ty * 8 + 4 * (int)half + (int)(lane >> 3);
+        const size_t base = ((size_t)first * 2u + half) * 32 + lane;   // segment g of this half: base + g * 64
+        float4 run = make_float4(0.f, 0.f, 0.f, 0.f);
+        float z = 0.0f, t_final = 1.0f;
+        bool stopped = false;
+        for (unsigned g0 = 0; g0 < n_seg; g0 += 4) {
+            float4 c[4];
+            float zz[4], ee[4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const bool ok = g0 + k < n_seg;
+                const size_t si = base + (size_t)(g0 + k) * 64;
+                c[k] = ok ? seg_C[si] : make_float4(0.f, 0.f, 0.f, 0.f);
+                zz[k] = (KIND == BLEND_INFER && ok) ? seg_Z[si] : 0.0f;
+                ee[k] = (KIND == BLEND_INFER && ok) ? seg_E[si] : 1.0f;
+            }
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const bool ok = g0 + k < n_seg;
+                if (KIND == BLEND_TRAIN && ok) seg_C[base + (size_t)(g0 + k) * 64] = run;
+                run.x += c[k].x; run.y += c[k].y; run.z += c[k].z; run.w += c[k].w;
+                z += zz[k];
+                if (KIND == BLEND_INFER && ok && !stopped) { t_final = ee[k]; stopped = t_final < kTransmittanceEps; }
+            }
+        }
+        if (px < width && py < height) {
+            const int64_t n_px = (int64_t)width * height;
+            const int64_t pi = (int64_t)py * width + px;
+            image[pi] = run.x;
+            image[n_px + pi] = run.y;
+            image[2 * n_px + pi] = run.z;
+            image[3 * n_px + pi] = run.w;
+            if (KIND == BLEND_INFER) {
+                const float A = 1.0f - t_final;
+                depth_image[pi] = A > 0.0f ? z / A : 0.0f;
+                alpha_image[pi] = t_final < kTransmittanceEps ? 1.0f : A;
+            }
+        }
+    }
+}
+
+// Shared memory of one warp of the backward pass.
+struct WarpBackwardSmem {
+    unsigned mask[32];
+    unsigned off[32];
+    float4 pixel_grad[32];                  // image gradient of the half's pixels
+    float frag_alpha[kBatchFragments];      // fragments in per-pixel order
+    float frag_rcp[kBatchFragments];        // 1 / max(1 - alpha, eps)
+    float4 frag_feat[kBatchFragments];
+    float frag_bw[kBatchFragments];         // blending weight the fragment got (0: it was dropped)
+    float frag_dalpha[kBatchFragments];     // dL/dalpha of the fragment
+};
+
+__global__ void __launch_bounds__(kWarpBlendWarps * 32) blend_bilinear_warp_backward_kernel(
+    const uint32_t* __restrict__ list0, const uint2* __restrict__ list1, const uint32_t* __restrict__ counts, unsigned* __restrict__ ticket,
+    const uint2* __restrict__ ranges, const uint32_t* __restrict__ tile_first, const uint32_t* __restrict__ kept0,
+    const uint32_t* __restrict__ kept1, const uint32_t* __restrict__ n_kept, const PointRec* __restrict__ rec,
+    const float* __restrict__ seg_T, const float4* __restrict__ seg_C, const float* __restrict__ grad_image,
+    const float* __restrict__ grad_alpha, const float* __restrict__ image, const float* __restrict__ alpha_image,
+    float4* __restrict__ grad_feat_view, float* __restrict__ grad_opacity, int width, int height, int gw) {
+    constexpr unsigned kFull = 0xffffffffu;
+    __shared__ WarpBackwardSmem s_all[kWarpBlendWarps];
+    const unsigned lane = lane_id();
+    const unsigned lt_mask = (1u << lane) - 1u;
+    WarpBackwardSmem& sm = s_all[threadIdx.x >> 5];
+    sm.mask[lane] = 0u;
+    __syncwarp();
+    const unsigned n_first = __ldg(counts) * 2u;
+    const unsigned n_items = n_first + __ldg(counts + 1) * 2u;
+    const unsigned n_rest = n_items - n_first;
+
+    for (;;) {
+        unsigned item = 0;
+        if (lane == 0) item = atomicAdd(ticket, 1u);
+        item = __shfl_sync(kFull, item, 0);
+        if (item >= n_items) break;
+        // the later segments first: they belong to the longest lists
+        unsigned tile, seg;
+        if (item < n_rest) { const uint2 d = __ldg(list1 + (item >> 1)); tile = d.x; seg = d.y; }
+        else { tile = __ldg(list0 + ((item - n_rest) >> 1)); seg = 0u; }
+        const int half = (int)((item < n_rest ? item : item - n_rest) & 1u);
+        const unsigned first = __ldg(tile_first + tile);
+        const size_t sidx = (size_t)(first + seg) * 2u + half;
+        const unsigned n_list = __ldg(n_kept + sidx);
+        if (n_list == 0u) continue;
+        const uint2 rg_tile = __ldg(ranges + tile);
+        const unsigned n_seg = warp_segments(rg_tile.y - rg_tile.x);
+        const uint32_t* list = (half ? kept1 : kept0) + rg_tile.x + seg * kSegmentLength;
+        const int tx = (int)(tile % (unsigned)gw), ty = (int)(tile / (unsigned)gw);
+        const int px0 = tx * 8, py0 = ty * 8 + 4 * half;
+        const int px = px0 + (int)(lane & 7u), py = py0 + (int)(lane >> 3);
+
+        float4 g = make_float4(0.f, 0.f, 0.f, 0.f), Cfin = g, Crun = g;
+        float K = 0.0f, Tr = 1.0f;
+        bool done = !(px < width && py < height);
+        if (!done) {
+            const int64_t n_px = (int64_t)width * height;
+            const int64_t pi = (int64_t)py * width + px;
+            g = make_float4(__ldg(grad_image + pi), __ldg(grad_image + n_px + pi), __ldg(grad_image + 2 * n_px + pi),
+                            __ldg(grad_image + 3 * n_px + pi));
+            Cfin = make_float4(__ldg(image + pi), __ldg(image + n_px + pi), __ldg(image + 2 * n_px + pi),
+                               __ldg(image + 3 * n_px + pi));
+            K = __ldg(grad_alpha + pi) * (1.0f - __ldg(alpha_image + pi));
+            if (seg > 0u) Tr = seg_T[sidx * 32 + lane];
+            if (n_seg > 1u) Crun = seg_C[sidx * 32 + lane];
+            done = Tr < kTransmittanceEps;
+        }
+        __syncwarp();   // the previous item's readers of pixel_grad are through
+        sm.pixel_grad[lane] = g;
+        unsigned done_w = __ballot_sync(kFull, done);
+
+        // ids two batches ahead, records one batch ahead
+        uint32_t id_cur = 0, id_nxt = 0, id_far = 0;
+        float4 a_cur, f_cur, a_nxt, f_nxt;
+        a_cur = f_cur = a_nxt = f_nxt = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (lane < n_list) id_nxt = checked_point(__ldg(list + lane));
+        if (32u + lane < n_list) id_far = checked_point(__ldg(list + 32u + lane));
+        if (lane < n_list) {
+            const float4* p = reinterpret_cast<const float4*>(rec + id_nxt);
+            a_nxt = __ldg(p);
+            f_nxt = __ldg(p + 1);
+        }
+        for (unsigned base = 0; base < n_list; base += 32u) {
+            const int n_cur = (int)min(32u, n_list - base);
+            id_cur = id_nxt; a_cur = a_nxt; f_cur = f_nxt;
+            id_nxt = id_far;
+            if (base + 32u + lane < n_list) {
+                const float4* p = reinterpret_cast<const float4*>(rec + id_nxt);
+                a_nxt = __ldg(p);
+                f_nxt = __ldg(p + 1);
+            }
+            if (base + 64u + lane < n_list) id_far = checked_point(__ldg(list + base + 64u + lane));
+            // ---- lane j: the fragments of staged instance j
+            const int qx = __float2int_rd(a_cur.x - 0.5f) - px0;
+            const int qy = __float2int_rd(a_cur.y - 0.5f) - py0;
+            float al[4], wg[4];
+            int pix[4];
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                const int cx = qx + (c & 1), cy = qy + (c >> 1);
+                const float pcx = (float)(px0 + cx) + 0.5f, pcy = (float)(py0 + cy) + 0.5f;
+                const float dx = fabsf(a_cur.x - pcx), dy = fabsf(a_cur.y - pcy);
+                wg[c] = __saturatef(1.0f - dx) * __saturatef(1.0f - dy);
+                al[c] = a_cur.z * wg[c];
+                const int p = cy * 8 + cx;
+                const bool ok = (int)lane < n_cur && cx >= 0 && cx < 8 && cy >= 0 && cy < 4 && dx < 1.0f && dy < 1.0f &&
+                                !((done_w >> (p & 31)) & 1u);
+                pix[c] = ok ? p : -1;
+                if (ok) atomicOr(sm.mask + p, 1u << lane);
+            }
+            __syncwarp();
+            const unsigned my_mask = sm.mask[lane];
+            const unsigned cnt = __popc(my_mask);
+            const unsigned off = warp_inclusive_scan(cnt) - cnt;
+            sm.off[lane] = off;
+            __syncwarp();
+            int slot[4];
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                slot[c] = 0;
+                if (pix[c] >= 0) {
+                    slot[c] = (int)(sm.off[pix[c]] + __popc(sm.mask[pix[c]] & lt_mask));
+                    sm.frag_alpha[slot[c]] = al[c];
+                    sm.frag_rcp[slot[c]] = 1.0f / fmaxf(1.0f - al[c], kOneMinusAlphaEps);
+                    sm.frag_feat[slot[c]] = f_cur;
+                }
+            }
+            __syncwarp();
+            if (my_mask) sm.mask[lane] = 0u;
+            for (unsigned k = off; k < off + cnt; ++k) {
+                if (done) {
+                    sm.frag_bw[k] = 0.0f;
+                    sm.frag_dalpha[k] = 0.0f;
+                    continue;
+                }
+                const float a = sm.frag_alpha[k];
+                const float rcp = sm.frag_rcp[k];
+                const float4 f = sm.frag_feat[k];
+                const float bw = Tr * a;
+                Crun.x += bw * f.x; Crun.y += bw * f.y; Crun.z += bw * f.z; Crun.w += bw * f.w;
+                const float from_features = (Tr * f.x + (Crun.x - Cfin.x) * rcp) * g.x +
+                                            (Tr * f.y + (Crun.y - Cfin.y) * rcp) * g.y +
+                                            (Tr * f.z + (Crun.z - Cfin.z) * rcp) * g.z +
+                                            (Tr * f.w + (Crun.w - Cfin.w) * rcp) * g.w;
+                sm.frag_bw[k] = bw;
+                sm.frag_dalpha[k] = from_features + K * rcp;
+                Tr *= 1.0f - a;
+                if (Tr < kTransmittanceEps) done = true;
+            }
+            __syncwarp();
+            // gradients of every staged instance: its (up to) four fragments in fixed corner order, one vector
+            // and one scalar atomic per instance
+            if ((int)lane < n_cur) {
+                float4 sf = make_float4(0.f, 0.f, 0.f, 0.f);
+                float so = 0.0f;
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+                    float o = 0.0f;
+                    if (pix[c] >= 0) {
+                        const float bw = sm.frag_bw[slot[c]];
+                        if (bw > 0.0f) {
+                            const float4 pg = sm.pixel_grad[pix[c]];
+                            v = make_float4(bw * pg.x, bw * pg.y, bw * pg.z, bw * pg.w);
+                        }
+                        o = sm.frag_dalpha[slot[c]] * wg[c];
+                    }
+                    if (c == 0) { sf = v; so = o; }
+                    else { sf.x += v.x; sf.y += v.y; sf.z += v.z; sf.w += v.w; so += o; }
+                }
+                if (sf.x != 0.0f || sf.y != 0.0f || sf.z != 0.0f || sf.w != 0.0f) atomicAdd(grad_feat_view + id_cur, sf);
+                if (so != 0.0f) atomicAdd(grad_opacity + id_cur, so);
+            }
+            done_w = __ballot_sync(kFull, done);
+            __syncwarp();
+            if (done_w == kFull) break;
+        }
+    }
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -1846,7 +2483,6 @@ __global__ void __launch_bounds__(kPreThreads) preprocess_backward_kernel(
 struct PointBlob {
     PointRec* rec;
     uint2* bounds;
-    uint2* bounds_sorted;                 // tile bounds in depth order, written by the last pass of the depth sort
     float4* conic;
     unsigned* block_visible;              // survivors per chunk of kPreThreads points
     unsigned* group_visible;              // per group of 4 chunks; scanned in place
@@ -1869,7 +2505,6 @@ PointBlob carve_point_blob(void* p, int64_t n, int mode) {
     const int64_t nb = ceil_div<int64_t>(n > 0 ? n : 1, kPreThreads);
     b.rec = c.take<PointRec>(n);
     b.bounds = c.take<uint2>(n);
-    b.bounds_sorted = c.take<uint2>(n);
     b.conic = mode == INPC_MODE_GAUSSIAN ? c.take<float4>(n) : nullptr;
     b.block_visible = c.take<unsigned>(nb);
     b.group_visible = c.take<unsigned>(ceil_div<int64_t>(nb, 4));
@@ -1897,7 +2532,12 @@ struct InstanceBlob {
     float* seg_T;
     float4* seg_C;
     float* seg_Z;
+    float* seg_E;         // warp blend, inference: transmittance at the end of every segment
     int64_t max_segments;
+    uint32_t* tile_rank;  // warp blend: non-empty tiles before each tile
+    uint32_t* list0;      // warp blend: the non-empty tiles
+    uint2* list1;         // warp blend: (tile, segment) of every segment behind a tile's first
+    uint32_t* n_kept;     // warp blend: per item, length of the compacted list the forward pass blended
     void* sort_ws;
     size_t total;
 };
@@ -1908,20 +2548,34 @@ int64_t max_segments(int64_t n_instances, int n_tiles, int tile) {
     return (int64_t)n_tiles + ceil_div<int64_t>(n_instances, (int64_t)blend_batch(tile) * kMinBatchesPerSegment);
 }
 
-InstanceBlob carve_instance_blob(void* p, int64_t n_instances, int n_tiles, int tile, int mode, bool with_depth, int c4 = 1) {
+// Which of the two blend organisations a call uses: one warp per tile part with the dead-instance filter
+// (bilinear splats, 8x8 tiles, four view-space channels) or one block per (tile, segment).
+constexpr int kWarpBlendParts = 2;   // work items per (tile, segment): the two 8x4 halves
+bool uses_warp_blend(int mode, int tile, bool rows) { return mode == INPC_MODE_BILINEAR && tile == 8 && !rows; }
+
+InstanceBlob carve_instance_blob(void* p, int64_t n_instances, int n_tiles, int tile, int mode, bool with_depth, int c4 = 1, bool rows = false) {
     InstanceBlob b;
     Carver c(p);
+    const bool warp_blend = uses_warp_blend(mode, tile, rows);
     b.ranges = c.take<uint2>(n_tiles);
     for (int k = 0; k < 2; ++k) b.keys[k] = c.take<uint32_t>(n_instances);
     for (int k = 0; k < 2; ++k) b.ids[k] = c.take<uint32_t>(n_instances);
-    b.max_segments = max_segments(n_instances, n_tiles, tile);
+    // upper bound on the number of (tile, segment) pairs, known from the instance count alone
+    b.max_segments = warp_blend ? (int64_t)n_tiles + ceil_div<int64_t>(n_instances, (int64_t)kSegmentLength) : max_segments(n_instances, n_tiles, tile);
     const size_t px = (size_t)b.max_segments * tile * tile;
-    b.segs = c.take<Segment>(b.max_segments);
+    b.segs = c.take<Segment>(warp_blend ? 0 : b.max_segments);
     b.tile_first = c.take<uint32_t>(n_tiles);
-    b.n_segments = c.take<uint32_t>(4);
+    // [0] segments (block blend) or non-empty tiles (warp blend), [1] later segments (warp blend), [2..5] work tickets of
+    // the warp blend passes FIRST, PRODUCT, REST and of its backward pass
+    b.n_segments = c.take<uint32_t>(8);
     b.seg_T = c.take<float>(px);
     b.seg_C = c.take<float4>(px * (size_t)c4);
     b.seg_Z = c.take<float>(with_depth ? px : 0);
+    b.seg_E = c.take<float>(with_depth && warp_blend ? px : 0);
+    b.tile_rank = c.take<uint32_t>(warp_blend ? (size_t)n_tiles : 0);
+    b.list0 = c.take<uint32_t>(warp_blend ? (size_t)n_tiles : 0);
+    b.list1 = c.take<uint2>(warp_blend ? (size_t)b.max_segments : 0);
+    b.n_kept = c.take<uint32_t>(warp_blend ? (size_t)b.max_segments * kWarpBlendParts : 0);
     c.off = align_up(c.off);
     b.sort_ws = c.base + c.off;
     c.off += sort_workspace_bytes(n_instances);
@@ -1955,6 +2609,12 @@ int check_view(const inpc_view* v, int tile_size, int mode, int64_t n) {
     if (tile_size != 8 && tile_size != 16) { set_error("tile_size must be 8 or 16, got %d", tile_size); return INPC_E_INVALID; }
     if (v->width <= 0 || v->height <= 0 || v->width > 65535 * tile_size || v->height > 65535 * tile_size) {
         set_error("image size %dx%d out of range", v->width, v->height);
+        return INPC_E_INVALID;
+    }
+    // tile indices live in the low kTileKeyBits bits of the instance keys
+    const int64_t tiles = (int64_t)ceil_div(v->width, tile_size) * ceil_div(v->height, tile_size);
+    if (tiles > ((int64_t)1 << kTileKeyBits)) {
+        set_error("image size %dx%d gives %lld tiles of %d pixels, more than the supported 2^%u", v->width, v->height, (long long)tiles, tile_size, kTileKeyBits);
         return INPC_E_INVALID;
     }
     if (n < 0 || n >= ((int64_t)1 << 30)) { set_error("n=%lld out of range [0, 2^30)", (long long)n); return INPC_E_INVALID; }
@@ -1994,6 +2654,8 @@ int run_front(const RasterParams& rp, int64_t n, const float* positions, const v
               inpc_alloc_fn alloc_point, inpc_alloc_fn alloc_instance, void* user, inpc_raster_state* st,
               bool with_depth, PointBlob* pb_out, InstanceBlob* ib_out, cudaStream_t stream, int c4 = 1) {
     const int n_tiles = rp.gw * rp.gh;
+    constexpr bool kRows = VARIANT == VAR_ROWS;
+    const bool warp_blend = uses_warp_blend(MODE, rp.tile, kRows);
     const int64_t nb = ceil_div<int64_t>(n > 0 ? n : 1, kPreThreads);
     const PointBlob sizing = carve_point_blob(nullptr, n, MODE);
     void* pblob = alloc_point(user, sizing.total);
@@ -2058,21 +2720,17 @@ int run_front(const RasterParams& rp, int64_t n, const float* positions, const v
         return INPC_E_CAPACITY;
     }
 
-    const InstanceBlob isz = carve_instance_blob(nullptr, n_instances, n_tiles, rp.tile, MODE, with_depth, c4);
+    const InstanceBlob isz = carve_instance_blob(nullptr, n_instances, n_tiles, rp.tile, MODE, with_depth, c4, kRows);
     void* iblob = alloc_instance(user, isz.total);
     if (!iblob) { set_error("instance allocator returned NULL for %zu bytes", isz.total); return INPC_E_ALLOC; }
-    InstanceBlob ib = carve_instance_blob(iblob, n_instances, n_tiles, rp.tile, MODE, with_depth, c4);
+    InstanceBlob ib = carve_instance_blob(iblob, n_instances, n_tiles, rp.tile, MODE, with_depth, c4, kRows);
     INPC_CUDA_TRY(cudaMemsetAsync(ib.ranges, 0, sizeof(uint2) * (size_t)n_tiles, stream));
 
     int in_alt = 0;
     int rc;
     {
         StageScope scope(STAGE_SORT_DEPTH, stream);
-#if INPC_SORT_CARRIES_BOUNDS
-        rc = sort_pairs(pb.keys[0], pb.keys[1], pb.ids[0], pb.ids[1], n_visible, key_bits, pb.sort_ws, &in_alt, stream, pb.bounds, pb.bounds_sorted);
-#else
         rc = sort_pairs(pb.keys[0], pb.keys[1], pb.ids[0], pb.ids[1], n_visible, key_bits, pb.sort_ws, &in_alt, stream);
-#endif
     }
     if (rc != INPC_OK) return rc;
     const uint32_t* sorted_ids = pb.ids[in_alt];
@@ -2088,11 +2746,10 @@ int run_front(const RasterParams& rp, int64_t n, const float* positions, const v
             INPC_LAUNCH_CHECK("instance_count_kernel");
             scan_u32_kernel<<<1, kScanThreads, 0, stream>>>(pb.inst_block_sums, ibk);
             INPC_LAUNCH_CHECK("scan_u32_kernel");
-            // the depth sort's last pass left the bounds in depth order, unless it had nothing to do
-            if (INPC_SORT_CARRIES_BOUNDS && n_visible > 1 && key_bits > 0)
-                emit_instances_kernel<true><<<(unsigned)ibk, kInstThreads, 0, stream>>>(sorted_ids, pb.bounds_sorted, n_visible, pb.inst_block_sums, rp.gw, ib.keys[0], ib.ids[0]);
+            if (warp_blend)
+                emit_instances_kernel<true><<<(unsigned)ibk, kInstThreads, 0, stream>>>(sorted_ids, pb.bounds, pb.rec, n_visible, pb.inst_block_sums, rp.gw, rp.gh, ib.keys[0], ib.ids[0]);
             else
-                emit_instances_kernel<false><<<(unsigned)ibk, kInstThreads, 0, stream>>>(sorted_ids, pb.bounds, n_visible, pb.inst_block_sums, rp.gw, ib.keys[0], ib.ids[0]);
+                emit_instances_kernel<false><<<(unsigned)ibk, kInstThreads, 0, stream>>>(sorted_ids, pb.bounds, pb.rec, n_visible, pb.inst_block_sums, rp.gw, rp.gh, ib.keys[0], ib.ids[0]);
             INPC_LAUNCH_CHECK("emit_instances_kernel");
         }
         StageScope scope(STAGE_SORT_TILE, stream);
@@ -2102,7 +2759,14 @@ int run_front(const RasterParams& rp, int64_t n, const float* positions, const v
         tile_ranges_kernel<<<(unsigned)ceil_div<int64_t>(n_instances, 256 * 8), 256, 0, stream>>>(ib.keys[t_alt], n_instances, ib.ranges);
         INPC_LAUNCH_CHECK("tile_ranges_kernel");
     }
-    {
+    if (warp_blend) {
+        StageScope scope(STAGE_SORT_TILE, stream);
+        INPC_CUDA_TRY(cudaMemsetAsync(ib.n_segments, 0, 8 * sizeof(uint32_t), stream));   // counts and work tickets
+        warp_items_scan_kernel<<<1, kScanThreads, 0, stream>>>(ib.ranges, n_tiles, ib.tile_first, ib.tile_rank, ib.n_segments);
+        INPC_LAUNCH_CHECK("warp_items_scan_kernel");
+        warp_items_fill_kernel<<<ceil_div(n_tiles, 256), 256, 0, stream>>>(ib.ranges, n_tiles, ib.tile_first, ib.tile_rank, ib.list0, ib.list1);
+        INPC_LAUNCH_CHECK("warp_items_fill_kernel");
+    } else {
         StageScope scope(STAGE_SORT_TILE, stream);
         count_segments_kernel<<<1, kScanThreads, 0, stream>>>(ib.ranges, n_tiles, blend_batch(rp.tile), ib.tile_first, ib.n_segments);
         INPC_LAUNCH_CHECK("count_segments_kernel");
@@ -2142,10 +2806,76 @@ RasterParams make_params(const inpc_view* view, int tile_size, float sigma_world
 // scenes): one per thread is fastest for both tile sizes; deeper batches lose more to mask traffic
 // and same-word atomicOr contention than they gain from fewer barriers.
 template <int T> struct BlendConfig;
-template <> struct BlendConfig<8> { static constexpr int kIpt = INPC_IPT8; };
-template <> struct BlendConfig<16> { static constexpr int kIpt = INPC_IPT16; };
+template <> struct BlendConfig<8> { static constexpr int kIpt = 1; };
+template <> struct BlendConfig<16> { static constexpr int kIpt = 1; };
 
 int blend_batch(int tile) { return tile == 8 ? 64 * BlendConfig<8>::kIpt : 256 * BlendConfig<16>::kIpt; }
+
+// Persistent grid of the warp blend: enough blocks to fill the GPU (the item counts live on the device).
+int warp_blend_grid(unsigned* grid) {
+    int dev = 0, sms = 0;
+    INPC_CUDA_TRY(cudaGetDevice(&dev));
+    static int cached_sms[kMaxDevices] = {0};
+    if (dev >= 0 && dev < kMaxDevices && cached_sms[dev] > 0) sms = cached_sms[dev];
+    else {
+        INPC_CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+        if (dev >= 0 && dev < kMaxDevices) cached_sms[dev] = sms;
+    }
+    *grid = (unsigned)max(1, sms * 4);
+    return INPC_OK;
+}
+
+template <int KIND>
+int launch_bilinear_warp_forward(const RasterParams& rp, const PointBlob& pb, const InstanceBlob& ib, int t_alt, float* image,
+                                 float* depth, float* alpha, float* blending_weights, cudaStream_t stream) {
+    unsigned grid = 1;
+    const int rc = warp_blend_grid(&grid);
+    if (rc != INPC_OK) return rc;
+    const int W = rp.v.width, H = rp.v.height;
+    // tiles without instances are not work items: their pixels are cleared here
+    const size_t n_px = (size_t)W * H;
+    INPC_CUDA_TRY(cudaMemsetAsync(image, 0, sizeof(float) * 4 * n_px, stream));
+    INPC_CUDA_TRY(cudaMemsetAsync(alpha, 0, sizeof(float) * n_px, stream));
+    if (KIND == BLEND_INFER) INPC_CUDA_TRY(cudaMemsetAsync(depth, 0, sizeof(float) * n_px, stream));
+    // the ping-pong buffers the tile sort left unused receive the compacted lists (part 0: ids, part 1: keys)
+    const uint32_t* keys = ib.keys[t_alt];
+    const uint32_t* ids = ib.ids[t_alt];
+    uint32_t* kept0 = ib.ids[1 - t_alt];
+    uint32_t* kept1 = ib.keys[1 - t_alt];
+    const unsigned threads = kWarpBlendWarps * 32;
+    blend_bilinear_warp_forward_kernel<PASS_FIRST, KIND><<<grid, threads, 0, stream>>>(
+        ib.list0, ib.list1, ib.n_segments, ib.n_segments + 2, ib.ranges, ib.tile_first, keys, ids, pb.rec, ib.seg_T, ib.seg_C, ib.seg_Z, ib.seg_E,
+        image, depth, alpha, blending_weights, kept0, kept1, ib.n_kept, W, H, rp.gw);
+    INPC_LAUNCH_CHECK("blend_bilinear_warp_forward_kernel (first segments)");
+    blend_bilinear_warp_forward_kernel<PASS_PRODUCT, KIND><<<grid, threads, 0, stream>>>(
+        ib.list0, ib.list1, ib.n_segments, ib.n_segments + 3, ib.ranges, ib.tile_first, keys, ids, pb.rec, ib.seg_T, ib.seg_C, ib.seg_Z, ib.seg_E,
+        image, depth, alpha, blending_weights, kept0, kept1, ib.n_kept, W, H, rp.gw);
+    INPC_LAUNCH_CHECK("blend_bilinear_warp_forward_kernel (products)");
+    warp_blend_prefix_kernel<<<grid, threads, 0, stream>>>(ib.list0, ib.n_segments, ib.ranges, ib.tile_first, ib.seg_T);
+    INPC_LAUNCH_CHECK("warp_blend_prefix_kernel");
+    blend_bilinear_warp_forward_kernel<PASS_REST, KIND><<<grid, threads, 0, stream>>>(
+        ib.list0, ib.list1, ib.n_segments, ib.n_segments + 4, ib.ranges, ib.tile_first, keys, ids, pb.rec, ib.seg_T, ib.seg_C, ib.seg_Z, ib.seg_E,
+        image, depth, alpha, blending_weights, kept0, kept1, ib.n_kept, W, H, rp.gw);
+    INPC_LAUNCH_CHECK("blend_bilinear_warp_forward_kernel (later segments)");
+    warp_blend_combine_kernel<KIND><<<grid, threads, 0, stream>>>(ib.list0, ib.n_segments, ib.ranges, ib.tile_first, ib.seg_C, ib.seg_Z, ib.seg_E,
+                                                                      image, depth, alpha, W, H, rp.gw);
+    INPC_LAUNCH_CHECK("warp_blend_combine_kernel");
+    return INPC_OK;
+}
+
+int launch_bilinear_warp_backward(const RasterParams& rp, const PointBlob& pb, const InstanceBlob& ib, int t_alt, const float* grad_image,
+                                  const float* grad_alpha, const float* image, const float* alpha, float4* gfv, float* grad_opacities,
+                                  cudaStream_t stream) {
+    unsigned grid = 1;
+    const int rc = warp_blend_grid(&grid);
+    if (rc != INPC_OK) return rc;
+    INPC_CUDA_TRY(cudaMemsetAsync(ib.n_segments + 5, 0, sizeof(uint32_t), stream));   // the work ticket
+    blend_bilinear_warp_backward_kernel<<<grid, kWarpBlendWarps * 32, 0, stream>>>(
+        ib.list0, ib.list1, ib.n_segments, ib.n_segments + 5, ib.ranges, ib.tile_first, ib.ids[1 - t_alt], ib.keys[1 - t_alt], ib.n_kept, pb.rec,
+        ib.seg_T, ib.seg_C, grad_image, grad_alpha, image, alpha, gfv, grad_opacities, rp.v.width, rp.v.height, rp.gw);
+    INPC_LAUNCH_CHECK("blend_bilinear_warp_backward_kernel");
+    return INPC_OK;
+}
 
 template <int T, int KIND>
 int launch_bilinear_forward(const RasterParams& rp, const PointBlob& pb, const InstanceBlob& ib, const uint32_t* ids, float* image,
@@ -2210,10 +2940,11 @@ int launch_blend_forward(int mode, const RasterParams& rp, const PointBlob& pb, 
                          float* image, float* depth, float* alpha, float* blending_weights, float threshold,
                          cudaStream_t stream) {
     const int n_tiles = rp.gw * rp.gh;
-    const uint32_t* ids = ib.ids[tile_result_buffer(n_instances, n_tiles)];
+    const int t_alt = tile_result_buffer(n_instances, n_tiles);
+    const uint32_t* ids = ib.ids[t_alt];
     StageScope scope(STAGE_BLEND_FWD, stream);
     if (mode == INPC_MODE_BILINEAR) {
-        if (rp.tile == 8) return launch_bilinear_forward<8, KIND>(rp, pb, ib, ids, image, depth, alpha, blending_weights, stream);
+        if (rp.tile == 8) return launch_bilinear_warp_forward<KIND>(rp, pb, ib, t_alt, image, depth, alpha, blending_weights, stream);
         return launch_bilinear_forward<16, KIND>(rp, pb, ib, ids, image, depth, alpha, blending_weights, stream);
     }
     if (rp.tile == 8) return launch_gaussian_forward<8, KIND>(rp, pb, ib, ids, image, depth, alpha, blending_weights, threshold, stream);
@@ -2359,7 +3090,7 @@ extern "C" int inpc_rasterize_backward(const inpc_raster_state* state, const inp
     {
         StageScope scope(STAGE_BLEND_BWD, stream);
         if (state->mode == INPC_MODE_BILINEAR) {
-            rc = rp.tile == 8 ? launch_bilinear_backward<8>(rp, pb, ib, ids, grad_image, grad_alpha, image, alpha, gfv, grad_opacities, stream)
+            rc = rp.tile == 8 ? launch_bilinear_warp_backward(rp, pb, ib, tile_result_buffer(state->n_instances, n_tiles), grad_image, grad_alpha, image, alpha, gfv, grad_opacities, stream)
                               : launch_bilinear_backward<16>(rp, pb, ib, ids, grad_image, grad_alpha, image, alpha, gfv, grad_opacities, stream);
             if (rc != INPC_OK) return rc;
         } else {
@@ -2368,8 +3099,8 @@ extern "C" int inpc_rasterize_backward(const inpc_raster_state* state, const inp
                 blend_gaussian_backward_kernel<8><<<grid, 64, 0, stream>>>(ib.segs, ib.n_segments, ids, pb.rec, pb.conic, ib.seg_T, ib.seg_C, grad_image, grad_alpha, image, alpha, gfv, grad_opacities, W, H, rp.gw);
             else
                 blend_gaussian_backward_kernel<16><<<grid, 256, 0, stream>>>(ib.segs, ib.n_segments, ids, pb.rec, pb.conic, ib.seg_T, ib.seg_C, grad_image, grad_alpha, image, alpha, gfv, grad_opacities, W, H, rp.gw);
+            INPC_LAUNCH_CHECK("blend_gaussian_backward_kernel");
         }
-        INPC_LAUNCH_CHECK("blend_backward_kernel");
     }
     StageScope scope(STAGE_PREPROCESS_BWD, stream);
     preprocess_backward_kernel<<<(unsigned)ceil_div<int64_t>(n, kPreThreads), kPreThreads, 0, stream>>>(
@@ -2494,7 +3225,7 @@ extern "C" int inpc_rasterize_rows_backward(const inpc_raster_state* state, cons
     const RasterParams rp = make_params(view, state->tile_size, 0.0f, 3.0f, nullptr);
     const int n_tiles = rp.gw * rp.gh;
     const PointBlob pb = carve_point_blob(state->point_blob, n, state->mode);
-    const InstanceBlob ib = carve_instance_blob(state->instance_blob, state->n_instances, n_tiles, state->tile_size, state->mode, false, channels / 4);
+    const InstanceBlob ib = carve_instance_blob(state->instance_blob, state->n_instances, n_tiles, state->tile_size, state->mode, false, channels / 4, true);
     const uint32_t* ids = ib.ids[tile_result_buffer(state->n_instances, n_tiles)];
     INPC_CUDA_TRY(cudaMemsetAsync(grad_features, 0, sizeof(float) * (size_t)n * channels, stream));
     INPC_CUDA_TRY(cudaMemsetAsync(grad_opacities, 0, sizeof(float) * (size_t)n, stream));
