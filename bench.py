@@ -56,8 +56,9 @@ def parse_args():
     ap.add_argument("--points", type=int, default=N_POINTS)
     ap.add_argument("--tile", type=int, default=8)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-side", action="store_true", help="skip the side workloads (configs 2 and 4, feature rows) at the end of a 1-GPU run")
     ap.add_argument("--streams", type=int, default=4, help="CUDA streams a rank pipelines its views over (1 = one view at a time)")
-    ap.add_argument("--workload", default="config1", choices=["config1", "config2", "config4", "rows16", "rows32"],
+    ap.add_argument("--workload", default="config1", choices=["config1", "config2", "config4", "config4_rows32", "rows16", "rows32"],
                     help="config1 is the headline (default); the others are single-GPU side measurements, one JSON line each")
     return ap.parse_args()
 
@@ -143,9 +144,18 @@ def max_over_ranks(value: float, world: int, device) -> float:
     return float(t.item())
 
 
+def config_dict(args) -> dict:
+    """The workload description both arms print (same keys, same values: the arms differ in `impl` only)."""
+    return {"workload": f"config 1 single-view training step x {args.views} orbit views (config 3 batch), sharded by view",
+            "points_per_view": args.points, "views_per_step": args.views, "leaves": N_LEAVES, "image": [1237, 822],
+            "features": "36 x fp16 SH -> 4 channels", "tile": 8,
+            "l2": "inputs (604 MB of features per view) exceed the 126 MB L2; no flush needed",
+            "allreduce_floats": N_LEAVES + N_APPEARANCE}
+
+
 def build_workload(args, device):
     import torch
-    from inpc_b200 import synthetic as syn
+    import synthetic_workloads as syn
     cfg = syn.config1(n_samples=args.points, n_leaves=N_LEAVES)
     views = syn.config3_views(args.views)
     g = torch.Generator().manual_seed(5)
@@ -164,7 +174,7 @@ def cpu_pipeline_points_per_s(n_points: int, threads: int, n_views: int = 1) -> 
     import torch
     sys.path.insert(0, str(ROOT / "oracle"))
     import oracle as O
-    from inpc_b200 import synthetic as syn
+    import synthetic_workloads as syn
     os.environ["OMP_NUM_THREADS"] = str(threads)
     cfg = syn.config1(n_samples=n_points, n_leaves=N_LEAVES)
     tree = cfg["tree"]
@@ -238,6 +248,23 @@ def run_ours(args):
     stage_views = my_views[:8]
     n_streams = trainer.n_streams
     trainer.n_streams = 1
+    # first the same pass without the stage timers: the workload with ONE view in flight, as the reference's trainer
+    # runs it (one view per optimizer step)
+    trainer.buffers.zero_()
+    for vi in stage_views[:2]:
+        trainer.run_view(wl["views"][vi], gi_dev, ga_dev, view_index=vi)
+    torch.cuda.synchronize()
+    sv_start, sv_stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    sv_clocks = ClockSampler(local) if rank == 0 else None
+    sv_reps = 3
+    sv_start.record()
+    for _ in range(sv_reps):
+        for vi in stage_views:
+            trainer.run_view(wl["views"][vi], gi_dev, ga_dev, view_index=vi)
+    sv_stop.record()
+    torch.cuda.synchronize()
+    sv_ms = sv_start.elapsed_time(sv_stop) / max(len(stage_views) * sv_reps, 1)
+    sv_clock_info = sv_clocks.stop() if sv_clocks else None
     _cabi.profile_read(reset=True)
     _cabi.profile_enable(True)
     trainer.buffers.zero_()
@@ -321,6 +348,13 @@ def run_ours(args):
     barrier(world)
     e2e_s = max_over_ranks(time.perf_counter() - t0, world, device)
 
+    # values every rank count must reproduce: the reduced buffers of the last step (identical views, identical
+    # per-view random streams, so only the order of floating-point sums differs between N = 1, 2, 4, 8)
+    app = trainer.buffers.appearance.double()
+    check = {"leaf_max": float(trainer.buffers.leaf.max_sampled.max().item()),
+             "leaf_max_sum": float(trainer.buffers.leaf.max_sampled.double().sum().item()),
+             "appearance_sum": float(app.sum().item()), "appearance_abs_sum": float(app.abs().sum().item())}
+
     if world > 1:
         import torch.distributed as dist
         gathered = [None] * world
@@ -368,12 +402,8 @@ def run_ours(args):
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
         "ms_per_step": elapsed_ms / args.steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": "f32", "data": "synthetic",
-        "config": {"workload": f"config 1 single-view training step x {args.views} orbit views (config 3 batch), sharded by view",
-                   "points_per_view": args.points, "views_per_step": args.views, "leaves": N_LEAVES, "image": [wl["W"], wl["H"]],
-                   "features": "36 x fp16 SH -> 4 channels", "tile": args.tile, "parallelism": f"view-dp{world}",
-                   "streams_per_rank": args.streams,
-                   "l2": "inputs (604 MB of features per view) exceed the 126 MB L2; no flush needed",
-                   "allreduce_floats": N_LEAVES + N_APPEARANCE},
+        "config": config_dict(args),
+        "parallelism": f"view-dp{world}", "streams_per_rank": args.streams, "tile": args.tile,
         "frames_per_s": args.steps * args.views / (elapsed_ms * 1e-3),
         "ms_per_view": elapsed_ms / args.steps / max(len(my_views), 1),
         "e2e": {"value": e2e_value, "unit": UNIT,
@@ -383,8 +413,21 @@ def run_ours(args):
         "roofline": roofline,
         "stages": per_stage,
         "stage_timing": "CUDA events around each stage, one-stream pass over 8 views directly after the timed region",
+        "single_view": {"value": args.points / (sv_ms * 1e-3) / 1e6, "unit": UNIT, "ms_per_view": sv_ms, "frames_per_s": 1e3 / sv_ms,
+                        "views": len(stage_views) * sv_reps, "clocks": sv_clock_info,
+                        "what": "the same workload with one view in flight (one stream, as the reference's trainer runs it), CUDA events"},
+        "check": check,
         "instances_per_view": mean_i, "visible_per_view": mean_v,
     }
+    if world == 1 and not args.no_side:
+        side = {}
+        for name in ("config2", "config4", "config4_rows32", "rows16", "rows32"):
+            try:
+                torch.cuda.empty_cache()
+                side[name] = side_workload(name, args.tile, warmup=3, reps=6, points=args.points)
+            except Exception as e:   # side numbers never cost the bench line
+                side[name] = {"failed": repr(e)}
+        line["side"] = side
     if world == 1 and not args.no_cpu_baseline:
         try:
             line["cpu_baseline"] = cpu_baseline(args)
@@ -403,11 +446,10 @@ def run_reference(args):
         return                                   # the reference is single-GPU: rank 0 alone runs it
     sys.path.insert(0, str(ROOT / "oracle"))
     import ref_backend as RB
-    config = {"workload": f"config 1 single-view training step x {args.views} orbit views (config 3 batch)",
-              "points_per_view": args.points, "views_per_step": args.views, "leaves": N_LEAVES,
-              "features": "36 x fp16 SH -> 4 channels", "tile": 8, "parallelism": "single GPU (the reference has no multi-GPU path)"}
     base = {"impl": "reference", "metric": METRIC, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps, "warmup": max(args.warmup, 3),
-            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": config}
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": config_dict(args),
+            "parallelism": "single GPU, one view at a time on the legacy default stream (the reference has no multi-GPU path and no streams)",
+            "tile": 8}
     import torch
     if not RB.available() or not torch.cuda.is_available():
         # no compiled reference backend (or no GPU): time the CPU restatement on a bounded sample
@@ -478,68 +520,114 @@ def run_reference(args):
                               "sample": "the reference's own CUDA backend (it has no CPU implementation of this path), "
                                         "compiled unmodified for sm_100a, full workload on one B200"},
                 e2e={"value": total_points / e2e_s / 1e6, "unit": UNIT,
-                     "h2d_bytes_per_step": args.views * (5 * P * 4 + 16 * 4 + 3 * 4), "d2h_bytes_per_step": args.views * 4})
+                     "h2d_bytes_per_step": args.views * (5 * P * 4 + 16 * 4 + 3 * 4), "d2h_bytes_per_step": args.views * 4},
+                single_view={"value": total_points / elapsed / 1e6, "unit": UNIT, "ms_per_view": elapsed / args.steps / args.views * 1e3,
+                             "frames_per_s": args.steps * args.views / elapsed, "views": args.views, "clocks": clock_info,
+                             "what": "the reference always has one view in flight: this is its timed region"})
+    if not args.no_side:
+        side = {}
+        del wl
+        for name in ("config2", "config4", "config4_rows32", "rows16", "rows32"):
+            try:
+                torch.cuda.empty_cache()
+                side[name] = side_workload(name, 8, warmup=3, reps=6, points=args.points, impl="reference")
+            except Exception as e:
+                side[name] = {"failed": repr(e)}
+        base["side"] = side
     print(json.dumps(base))
 
 
 # ---------------------------------------------------------------------------------------------------
-def run_side_workload(args):
-    """Single-GPU side measurements on the other synthetic configurations (device-timed, inputs resident):
-    config2  pre-extracted inference, 2^25 points, 1920x1080            -> frames/s
-    config4  skewed stress case, 2^24 points, 3840x2160, fwd+bwd        -> Mpoints/s
-    rows16 / rows32  config 1 with (N,C) fp32 feature rows, fwd+bwd incl. sampling -> Mpoints/s"""
+SIDE_METRICS = {
+    "config2": ("frames/s", "render_preextracted frames/s at 2^25 points, 1920x1080 (config 2)"),
+    "config4": (UNIT, "fwd+bwd Mpoints/s at 2^24 skewed points, 3840x2160, 36 x fp16 SH -> 4 channels (config 4 in the reference's layout)"),
+    "config4_rows32": (UNIT, "fwd+bwd Mpoints/s at 2^24 skewed points, 3840x2160, 32 fp32 channels (config 4 as stated)"),
+    "rows16": (UNIT, "fwd+bwd Mpoints/s at 2^23 points per view, 1237x822, 16 fp32 channels, incl. sampling"),
+    "rows32": (UNIT, "fwd+bwd Mpoints/s at 2^23 points per view, 1237x822, 32 fp32 channels, incl. sampling"),
+}
+
+
+def side_workload(name: str, tile: int, warmup: int, reps: int, points: int = N_POINTS, impl: str = "ours") -> dict:
+    """One single-GPU side measurement (device-timed with CUDA events, inputs resident in HBM, one call in flight):
+    config2         pre-extracted inference, 2^25 points, 1920x1080                      -> frames/s
+    config4         skewed stress case, 2^24 points, 3840x2160, fwd+bwd, SH layout       -> Mpoints/s
+    config4_rows32  the same with 32 fp32 feature channels                               -> Mpoints/s
+    rows16 / rows32 config 1 with (N,C) fp32 feature rows, fwd+bwd incl. sampling        -> Mpoints/s
+    impl = "reference" runs the reference's own CUDA backend where it can (config 2)."""
     import torch
-    import inpc_b200
-    from inpc_b200 import _cabi, synthetic as syn
-    from inpc_b200.sampling import ProbabilityFieldSampler
-    if int(os.environ.get("RANK", "0")) != 0:
-        return
-    device = torch.device("cuda", 0)
-    torch.cuda.set_device(device)
-    rast = inpc_b200.INPCRasterizer(tile_size=args.tile)
+    import synthetic_workloads as syn
+    unit, metric = SIDE_METRICS[name]
+    device = torch.device("cuda", torch.cuda.current_device())
     g = torch.Generator().manual_seed(5)
-    if args.workload == "config2":
+    if impl == "reference":
+        if name != "config2":
+            why = ("the reference's 16-bit tile key overflows at 3840x2160 (129,600 tiles of 8x8 pixels)" if name.startswith("config4")
+                   else "the reference has no fp32 feature-row layout")
+            return {"metric": metric, "unavailable": why}
+        sys.path.insert(0, str(ROOT / "oracle"))
+        import ref_backend as RB
         c = syn.config2()
-        view, pos, feats, opac = c["view"].to(device), c["positions"].to(device), c["features"].to(device), c["opacities"].to(device)
-        n_points, unit, metric = pos.shape[0], "frames/s", "render_preextracted frames/s at 2^25 points, 1920x1080"
+        view, pos, feats = c["view"].to(device), c["positions"].to(device), c["features"].to(device)
+        opac = c["opacities"].to(device).reshape(-1).contiguous()
+        n_points = pos.shape[0]
 
         def step():
-            rast.render_preextracted(view, 0, pos, feats, opac)
-    elif args.workload == "config4":
-        c = syn.config4()
-        view, pos, feats, opac = c["view"].to(device), c["positions"].to(device), c["features"].to(device), c["opacities"].to(device)
-        H, W = view.camera.height, view.camera.width
-        gi, ga = (torch.randn((4, H, W), generator=g) * 1e-3).to(device), (torch.randn((1, H, W), generator=g) * 1e-3).to(device)
-        n_points, unit, metric = pos.shape[0], UNIT, "fwd+bwd Mpoints/s at 2^24 skewed points, 3840x2160"
-
-        def step():
-            f, o = feats.detach().requires_grad_(True), opac.detach().requires_grad_(True)
-            im, al, _ = rast(view, 0, pos, f, o)
-            torch.autograd.backward([im, al], [gi, ga])
+            RB.render_preextracted(view, 0, pos, feats, opac, None, 1.0, 3.0, sync=False)
     else:
-        channels = 16 if args.workload == "rows16" else 32
-        c = syn.config1(n_samples=args.points, n_leaves=N_LEAVES)
-        view, tree, opac = c["view"].to(device), c["tree"].to(device), c["opacities"].to(device)
-        feats = (torch.randn((args.points, channels), generator=g) * 0.5).to(device)
-        H, W = view.camera.height, view.camera.width
-        gi, ga = (torch.randn((channels, H, W), generator=g) * 1e-3).to(device), (torch.randn((1, H, W), generator=g) * 1e-3).to(device)
-        sampler = ProbabilityFieldSampler(0)
-        n_points, unit, metric = args.points, UNIT, f"fwd+bwd Mpoints/s at 2^23 points per view, 1237x822, {channels} fp32 channels"
+        import inpc_b200
+        from inpc_b200.sampling import ProbabilityFieldSampler
+        rast = inpc_b200.INPCRasterizer(tile_size=tile)
+        if name == "config2":
+            c = syn.config2()
+            view, pos, feats, opac = c["view"].to(device), c["positions"].to(device), c["features"].to(device), c["opacities"].to(device)
+            n_points = pos.shape[0]
 
-        def step():
-            pos, _ = sampler.generate_training_samples(tree.centers, tree.levels, tree.weights, view, args.points, tree.initial_size)
-            f, o = feats.detach().requires_grad_(True), opac.detach().requires_grad_(True)
-            im, al, _ = rast.forward_rows(view, pos, f, o)
-            torch.autograd.backward([im, al], [gi, ga])
+            def step():
+                rast.render_preextracted(view, 0, pos, feats, opac)
+        elif name in ("config4", "config4_rows32"):
+            c = syn.config4()
+            view, pos, opac = c["view"].to(device), c["positions"].to(device), c["opacities"].to(device)
+            H, W = view.camera.height, view.camera.width
+            n_points = pos.shape[0]
+            ga = (torch.randn((1, H, W), generator=g) * 1e-3).to(device)
+            if name == "config4":
+                feats = c["features"].to(device)
+                gi = (torch.randn((4, H, W), generator=g) * 1e-3).to(device)
 
-    for _ in range(max(args.warmup, 3)):
+                def step():
+                    f, o = feats.detach().requires_grad_(True), opac.detach().requires_grad_(True)
+                    im, al, _ = rast(view, 0, pos, f, o)
+                    torch.autograd.backward([im, al], [gi, ga])
+            else:
+                del c
+                feats = (torch.randn((n_points, 32), generator=g) * 0.5).to(device)
+                gi = (torch.randn((32, H, W), generator=g) * 1e-3).to(device)
+
+                def step():
+                    f, o = feats.detach().requires_grad_(True), opac.detach().requires_grad_(True)
+                    im, al, _ = rast.forward_rows(view, pos, f, o)
+                    torch.autograd.backward([im, al], [gi, ga])
+        else:
+            channels = 16 if name == "rows16" else 32
+            c = syn.config1(n_samples=points, n_leaves=N_LEAVES)
+            view, tree, opac = c["view"].to(device), c["tree"].to(device), c["opacities"].to(device)
+            del c
+            feats = (torch.randn((points, channels), generator=g) * 0.5).to(device)
+            H, W = view.camera.height, view.camera.width
+            gi, ga = (torch.randn((channels, H, W), generator=g) * 1e-3).to(device), (torch.randn((1, H, W), generator=g) * 1e-3).to(device)
+            sampler = ProbabilityFieldSampler(0)
+            n_points = points
+
+            def step():
+                pos, _ = sampler.generate_training_samples(tree.centers, tree.levels, tree.weights, view, points, tree.initial_size)
+                f, o = feats.detach().requires_grad_(True), opac.detach().requires_grad_(True)
+                im, al, _ = rast.forward_rows(view, pos, f, o)
+                torch.autograd.backward([im, al], [gi, ga])
+
+    for _ in range(max(warmup, 3)):
         step()
     torch.cuda.synchronize()
-    _cabi.profile_read(reset=True)
-    _cabi.profile_enable(True)
-    launches0 = _cabi.launch_count()
-    clocks = ClockSampler(0)
-    reps = max(args.steps, 1) * 8
+    clocks = ClockSampler(device.index or 0)
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     start.record()
     for _ in range(reps):
@@ -548,22 +636,30 @@ def run_side_workload(args):
     torch.cuda.synchronize()
     ms = start.elapsed_time(stop) / reps
     clock_info = clocks.stop()
-    _cabi.profile_enable(False)
-    stages = {k: {"ms": v[0] / reps} for k, v in _cabi.profile_read(reset=True).items() if v[0] > 0}
     value = 1e3 / ms if unit == "frames/s" else n_points / (ms * 1e-3) / 1e6
-    print(json.dumps({"metric": metric, "value": value, "unit": unit, "n_gpus": 1, "steps": reps, "warmup": max(args.warmup, 3), "ms_per_step": ms,
-                      "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-                      "config": {"workload": args.workload, "points": n_points, "tile": args.tile,
-                                 "l2": "inputs exceed the 126 MB L2; no flush needed"},
-                      "gpu_launches": _cabi.launch_count() - launches0, "clocks": clock_info, "stages": stages}))
+    return {"metric": metric, "value": value, "unit": unit, "ms": ms, "reps": reps, "points": n_points, "clocks": clock_info}
+
+
+def run_side_workload(args):
+    """`--workload X`: one side measurement as a JSON line of its own."""
+    import torch
+    if int(os.environ.get("RANK", "0")) != 0:
+        return
+    torch.cuda.set_device(0)
+    r = side_workload(args.workload, args.tile, warmup=args.warmup, reps=max(args.steps, 1) * 8, points=args.points, impl=args.impl)
+    line = {"metric": r["metric"], "n_gpus": 1, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+            "data": "synthetic", "config": {"workload": args.workload, "tile": args.tile, "l2": "inputs exceed the 126 MB L2; no flush needed"}}
+    if args.impl == "reference":
+        line["impl"] = "reference"
+    line.update({k: v for k, v in r.items() if k != "metric"})
+    if "ms" in r:
+        line.update(steps=r["reps"], warmup=max(args.warmup, 3), ms_per_step=r["ms"])
+    print(json.dumps(line))
 
 
 def main():
     args = parse_args()
     if args.workload != "config1":
-        if args.impl == "reference":
-            print(json.dumps({"impl": "reference", "unavailable": "side workloads are measured for this build only"}))
-            return
         run_side_workload(args)
         return
     if args.impl == "reference":

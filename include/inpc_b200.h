@@ -80,6 +80,21 @@ long long inpc_launch_count(void);
 int inpc_profile_enable(int on);
 int inpc_profile_read(double* stage_ms, long long* stage_calls, int n, int reset);
 
+/* Device-side status of a call.  A few kernels wait on one another or on a copy engine; every such wait is
+ * bounded, and a kernel that gives up stores a flag into the status words of ITS call (words: 0 a
+ * radix-sort tile gave up its look-back | 1 some rejection-sampler slots ran out of attempts
+ * (informational) | 2 a block gave up waiting for its bulk copy | 3 checked build: a gather index was out
+ * of range).  Every entry point that launches such kernels takes a ticket; inpc_last_call_ticket returns
+ * the one the calling host thread took last, inpc_call_status copies the four words of a ticket out
+ * (`words` may be NULL) and returns INPC_E_DEVICE with a message naming the entry point if words 0, 2 or 3
+ * are set, INPC_E_INVALID if the ticket is unknown or older than 1024 calls.  The words live in mapped
+ * host memory: reading them needs no device synchronisation, but they are final only once the call's
+ * stream has been synchronised.  Independently of this, each entry point first looks at the last eight
+ * tickets of its host thread and returns INPC_E_DEVICE if one of them has reported since.
+ * The reference has no counterpart (its only check is the debug macro of utils/utils.h:10-17). */
+long long inpc_last_call_ticket(void);
+int inpc_call_status(long long ticket, unsigned* words);
+
 /* ------------------------------------------------------------------------------------------
  * Rasterizer
  * ---------------------------------------------------------------------------------------- */
@@ -195,11 +210,22 @@ int inpc_sort_pairs(uint32_t* keys, uint32_t* keys_alt, uint32_t* values, uint32
  *   - All calls on a device share the one array, which still holds the previous call's histograms
  *     and flags; each call clears what it reads, on `stream`.  Two calls whose work overlaps on the
  *     GPU (different streams, no ordering) race on it: serialise them.
- *   - A look-back wait that runs out is recorded only inside the array, not reported to the host
- *     (reporting needs pinned memory, which would be an allocation); the wait stays bounded.
+ *   - A look-back wait that runs out is recorded inside the array (reporting through pinned memory would
+ *     be an allocation); the wait stays bounded.  inpc_sort_pairs_static_status synchronises `stream`,
+ *     copies the status words of the last call on the current device out (see inpc_call_status for
+ *     their meaning) and returns INPC_E_DEVICE if the look-back word is set; it allocates nothing either.
  * This entry point has no counterpart in the reference. */
 int inpc_sort_pairs_static(uint32_t* keys, uint32_t* keys_alt, uint32_t* values, uint32_t* values_alt, int64_t n,
                            int end_bit, int* result_in_alt, void* stream);
+int inpc_sort_pairs_static_status(void* stream, unsigned* words);
+
+/* Test hook for the bounded look-back wait: inpc_sort_pairs with tile 0 of every pass leaving before it
+ * publishes its digit counts and a wait limit of 2^10 polls.  The tiles behind it give up within
+ * microseconds, set word 0 of the call's status and finish; every access stays inside the buffers, the
+ * output is simply not sorted.  *ticket receives the call's status ticket.  This hook has no counterpart
+ * in the reference (cub's look-back spins without a limit). */
+int inpc_debug_sort_lookback_timeout(uint32_t* keys, uint32_t* keys_alt, uint32_t* values, uint32_t* values_alt,
+                                     int64_t n, int end_bit, void* workspace, long long* ticket, void* stream);
 
 /* ------------------------------------------------------------------------------------------
  * Probability-field sampler
@@ -220,6 +246,11 @@ void inpc_sampler_destroy(inpc_sampler* s);
 /* Checkpoint / resume of the stream position (the reference's pcg32 state is not checkpointable). */
 uint64_t inpc_sampler_get_counter(const inpc_sampler* s);
 void inpc_sampler_set_counter(inpc_sampler* s, uint64_t counter);
+/* The rejection sampler of inpc_generate_training_samples bounds its attempts per slot (the reference's loop,
+ * sampling/src/sampling_kernels.cu:104-125, is unbounded).  1: some slots of this sampler's last such call
+ * ran out and hold their last candidate, a position outside the view frustum; 0: none did; -1: no longer known
+ * (more than 1024 status-carrying calls since).  Final once the call's stream has been synchronised. */
+int inpc_sampler_exhausted(const inpc_sampler* s);
 
 /* Bytes of device scratch the generate_* calls need for `n_cells` leaves (CDF + scan partials). */
 size_t inpc_sampler_workspace_bytes(int64_t n_cells);

@@ -56,6 +56,11 @@ PROTOTYPES = {
     "inpc_sort_workspace_bytes": (_Z, [_L]),
     "inpc_sort_pairs": (_I, [_P, _P, _P, _P, _L, _I, _P, C.POINTER(C.c_int), _P]),
     "inpc_sort_pairs_static": (_I, [_P, _P, _P, _P, _L, _I, C.POINTER(C.c_int), _P]),
+    "inpc_sort_pairs_static_status": (_I, [_P, C.POINTER(C.c_uint)]),
+    "inpc_debug_sort_lookback_timeout": (_I, [_P, _P, _P, _P, _L, _I, _P, C.POINTER(C.c_longlong), _P]),
+    "inpc_last_call_ticket": (C.c_longlong, []),
+    "inpc_call_status": (_I, [C.c_longlong, C.POINTER(C.c_uint)]),
+    "inpc_sampler_exhausted": (_I, [_P]),
     "inpc_compute_viewpoint_weights": (_I, [_VP, _L, _P, _P, _P, _F, _P, _P]),
     "inpc_sampler_create": (_P, [_L]),
     "inpc_sampler_destroy": (None, [_P]),

@@ -6,6 +6,7 @@
 #include <cstdint>
 #include <cstdio>
 #include <cstdarg>
+#include <mutex>
 #include "../../include/inpc_b200.h"
 
 namespace inpc {
@@ -60,8 +61,14 @@ enum : unsigned {
     STATUS_INDEX_OUT_OF_RANGE = 3, // checked build only: a gather index was outside its array (the access was skipped)
     STATUS_WORDS = 4,
 };
-unsigned* device_status_ptr();            // device pointer to STATUS_WORDS words (allocated on first use)
-unsigned read_and_clear_status(int word);  // host-side read of one word, then reset to 0
+// Takes the next status slot for a call of `entry` (a string literal): returns the device address of its
+// STATUS_WORDS cleared words, or nullptr (error set).  *ticket_out names the slot for read_status.
+unsigned* acquire_status(const char* entry, long long* ticket_out = nullptr);
+int read_status(long long ticket, unsigned* words, const char** entry);
+// INPC_E_DEVICE (with a message naming the entry point) if the last status-carrying call this host thread
+// made has reported a failure since; every entry point that launches work calls it first, so a failure
+// surfaces at the thread's next call at the latest -- or earlier through inpc_call_status.
+int check_previous_calls();
 
 // ---- small utilities ---------------------------------------------------------------------
 template <typename T>
@@ -110,14 +117,20 @@ inline ViewParams to_params(const inpc_view* v) {
 // ---- radix sort (radix_sort.cu) ------------------------------------------------------------
 size_t sort_workspace_bytes(int64_t n);
 int sort_pass_count(int end_bit);   // passes sort_pairs makes; the result is in the alternate buffers iff odd (and n > 1)
+// `status`: device address of the STATUS_WORDS words a tile that gives up its look-back reports to.
 int sort_pairs(uint32_t* keys, uint32_t* keys_alt, uint32_t* values, uint32_t* values_alt, int64_t n,
-               int end_bit, void* workspace, int* result_in_alt, cudaStream_t stream);
+               int end_bit, void* workspace, unsigned* status, int* result_in_alt, cudaStream_t stream);
 
 // More than 48 KB of dynamic shared memory is an opt-in per kernel AND per device: `done` is the
 // caller's per-kernel table of devices already set up.
 constexpr int kMaxDevices = 64;
+// Number of multiprocessors of the current device (looked up once per device; 148 if the query fails).
+int sm_count();
+
 template <typename Kernel>
 int opt_in_dynamic_smem(Kernel kernel, size_t bytes, bool (&done)[kMaxDevices]) {
+    static std::mutex table_mutex;   // one per kernel: host threads may reach the same kernel's table together
+    std::lock_guard<std::mutex> lock(table_mutex);
     int dev = 0;
     INPC_CUDA_TRY(cudaGetDevice(&dev));
     const bool tracked = dev >= 0 && dev < kMaxDevices;

@@ -11,12 +11,7 @@ namespace {
 constexpr int kThreads = 256;
 
 int grid_for(int64_t work_items) {
-    static int sms = 0;
-    if (!sms) {
-        int dev = 0;
-        cudaGetDevice(&dev);
-        if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
-    }
+    const int sms = sm_count();
     const int64_t want = ceil_div<int64_t>(work_items, kThreads);
     const int64_t cap = (int64_t)sms * 8;
     return (int)(want < cap ? (want > 0 ? want : 1) : cap);

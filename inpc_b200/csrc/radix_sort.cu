@@ -100,7 +100,7 @@ __global__ void __launch_bounds__(kThreads) radix_onesweep_pass_kernel(
     const uint32_t* __restrict__ keys_in, const uint32_t* __restrict__ vals_in,
     uint32_t* __restrict__ keys_out, uint32_t* __restrict__ vals_out, int64_t n, int shift, int bits_arg,
     const unsigned* __restrict__ digit_base, volatile unsigned* tile_state, unsigned* ticket,
-    volatile unsigned* status) {
+    volatile unsigned* status, int spin_limit, unsigned mute_tile) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     PassSmem& s = *reinterpret_cast<PassSmem*>(smem_raw);
 
@@ -112,6 +112,9 @@ __global__ void __launch_bounds__(kThreads) radix_onesweep_pass_kernel(
     for (int i = tid; i < kWarps * kRadix; i += kThreads) (&s.warp_hist[0][0])[i] = 0;
     __syncthreads();
     const unsigned tile = s.tile_id;
+    // `mute_tile` (no tile in normal operation) leaves without publishing anything: the tiles behind it then
+    // run into the limit of their look-back wait, which is how the tests exercise that path
+    if (tile == mute_tile) return;
     const int64_t tile_base = (int64_t)tile * kTile;
     const int valid = (int)min((int64_t)kTile, n - tile_base);
 
@@ -211,7 +214,7 @@ __global__ void __launch_bounds__(kThreads) radix_onesweep_pass_kernel(
                     if (finished || gave_up) break;
                     unsigned x = v[k];
                     int spins = 0;
-                    while ((x & kFlagMask) == 0u && spins < kSpinLimit) {   // not published yet: poll this one
+                    while ((x & kFlagMask) == 0u && spins < spin_limit) {   // not published yet: poll this one
                         __nanosleep(20);
                         x = tile_state[(size_t)(j - k) * kRadix + d];
                         ++spins;
@@ -257,9 +260,12 @@ __global__ void __launch_bounds__(kThreads) radix_onesweep_pass_kernel(
         const uint32_t k = s.keys[q];
         const unsigned d = (k >> shift) & digit_mask;
         const unsigned dst = s.global_off[d] + (unsigned)q;
-        keys_out[dst] = k;
-        const uint32_t v = s.values[q];
-        vals_out[dst] = v;
+        // always true in a healthy sort.  After a look-back that gave up, a later pass meets keys whose digits no
+        // longer match the histogram taken up front, and its positions can then run past the end: drop those.
+        if (dst < (unsigned)n) {
+            keys_out[dst] = k;
+            vals_out[dst] = s.values[q];
+        }
     }
 }
 
@@ -296,6 +302,8 @@ struct PassArgs {
     int shift, bits;
     const unsigned* base;
     unsigned *state, *ticket, *status;
+    int spin_limit;        // polls a tile spends on one unpublished predecessor before it gives up
+    unsigned mute_tile;    // tile that never publishes (tests only); 0xFFFFFFFF = none
 };
 
 template <int BITS>
@@ -309,7 +317,7 @@ int launch_onesweep_instance(const PassArgs& a, cudaStream_t stream) {
         if (rc != INPC_OK) return rc;
     }
     radix_onesweep_pass_kernel<BITS><<<(unsigned)a.tiles, kThreads, kSmemBytes, stream>>>(a.kin, a.vin, a.kout, a.vout, a.n, a.shift, a.bits, a.base,
-                                                                                         a.state, a.ticket, a.status);
+                                                                                         a.state, a.ticket, a.status, a.spin_limit, a.mute_tile);
     INPC_LAUNCH_CHECK("radix_onesweep_pass_kernel");
     return INPC_OK;
 }
@@ -348,7 +356,8 @@ static int check_sort_args(const char* who, const uint32_t* keys, const uint32_t
 }
 
 static int sort_pairs_with(const char* who, uint32_t* keys, uint32_t* keys_alt, uint32_t* values, uint32_t* values_alt, int64_t n, int end_bit,
-                           void* workspace, unsigned* status, int* result_in_alt, cudaStream_t stream) {
+                           void* workspace, unsigned* status, int* result_in_alt, cudaStream_t stream, int spin_limit = kSpinLimit,
+                           unsigned mute_tile = 0xFFFFFFFFu) {
     if (result_in_alt) *result_in_alt = 0;
     if (!workspace || !status) { set_error("%s: null workspace", who); return INPC_E_INVALID; }
 
@@ -379,6 +388,7 @@ static int sort_pairs_with(const char* who, uint32_t* keys, uint32_t* keys_alt, 
 
     PassArgs a;
     a.tiles = tiles; a.n = n; a.status = status;
+    a.spin_limit = spin_limit; a.mute_tile = mute_tile;
     a.kin = keys; a.kout = keys_alt; a.vin = values; a.vout = values_alt;
     for (int p = 0; p < pt.n_passes; ++p) {
         a.shift = pt.shift[p]; a.bits = pt.bits[p];
@@ -395,14 +405,12 @@ static int sort_pairs_with(const char* who, uint32_t* keys, uint32_t* keys_alt, 
 }
 
 int sort_pairs(uint32_t* keys, uint32_t* keys_alt, uint32_t* values, uint32_t* values_alt, int64_t n,
-               int end_bit, void* workspace, int* result_in_alt, cudaStream_t stream) {
+               int end_bit, void* workspace, unsigned* status, int* result_in_alt, cudaStream_t stream) {
     if (result_in_alt) *result_in_alt = 0;
     bool nothing = false;
     const int rc = check_sort_args("sort_pairs", keys, keys_alt, values, values_alt, n, end_bit, &nothing);
     if (rc != INPC_OK || nothing) return rc;
     if (!workspace) { set_error("sort_pairs: null workspace"); return INPC_E_INVALID; }
-    unsigned* status = device_status_ptr();
-    if (!status) return INPC_E_CUDA;
     return sort_pairs_with("sort_pairs", keys, keys_alt, values, values_alt, n, end_bit, workspace, status, result_in_alt, stream);
 }
 
@@ -469,6 +477,7 @@ extern "C" int inpc_sort_pairs_static(uint32_t* keys, uint32_t* keys_alt, uint32
     if (rc != INPC_OK) return rc;
     // the status words of this entry point live behind the workspace, inside the same fixed array
     unsigned* status = reinterpret_cast<unsigned*>(static_cast<unsigned char*>(scratch) + kStaticWorkspaceBytes);
+    INPC_CUDA_TRY(cudaMemsetAsync(status, 0, sizeof(unsigned) * STATUS_WORDS, stream));
     return sort_pairs_with("inpc_sort_pairs_static", keys, keys_alt, values, values_alt, n, end_bit, scratch, status, result_in_alt, stream);
 }
 
@@ -476,6 +485,52 @@ extern "C" size_t inpc_sort_workspace_bytes(int64_t n) { return inpc::sort_works
 
 extern "C" int inpc_sort_pairs(uint32_t* keys, uint32_t* keys_alt, uint32_t* values, uint32_t* values_alt,
                                int64_t n, int end_bit, void* workspace, int* result_in_alt, void* stream) {
-    return inpc::sort_pairs(keys, keys_alt, values, values_alt, n, end_bit, workspace, result_in_alt,
-                            static_cast<cudaStream_t>(stream));
+    using namespace inpc;
+    if (result_in_alt) *result_in_alt = 0;
+    bool nothing = false;
+    int rc = check_sort_args("inpc_sort_pairs", keys, keys_alt, values, values_alt, n, end_bit, &nothing);
+    if (rc != INPC_OK || nothing) return rc;
+    if (!workspace) { set_error("inpc_sort_pairs: null workspace"); return INPC_E_INVALID; }
+    rc = check_previous_calls();
+    if (rc != INPC_OK) return rc;
+    unsigned* status = acquire_status("inpc_sort_pairs");
+    if (!status) return INPC_E_CUDA;
+    return sort_pairs(keys, keys_alt, values, values_alt, n, end_bit, workspace, status, result_in_alt, static_cast<cudaStream_t>(stream));
+}
+
+// Test hook: inpc_sort_pairs with tile 0 of every pass leaving before it publishes its digit counts and a
+// look-back limit of 2^10 polls.  The tiles behind it give up within microseconds, report through the call's
+// status words, publish what they have and finish: every access stays inside the buffers (the write-out
+// checks its destination against n), the output is simply not sorted.  Returns the call's status ticket in *ticket.
+extern "C" int inpc_debug_sort_lookback_timeout(uint32_t* keys, uint32_t* keys_alt, uint32_t* values, uint32_t* values_alt,
+                                                int64_t n, int end_bit, void* workspace, long long* ticket, void* stream) {
+    using namespace inpc;
+    bool nothing = false;
+    int rc = check_sort_args("inpc_debug_sort_lookback_timeout", keys, keys_alt, values, values_alt, n, end_bit, &nothing);
+    if (rc != INPC_OK) return rc;
+    if (nothing || !workspace || !ticket) { set_error("inpc_debug_sort_lookback_timeout: needs n > 1, end_bit > 0, a workspace and a ticket pointer"); return INPC_E_INVALID; }
+    unsigned* status = acquire_status("inpc_debug_sort_lookback_timeout", ticket);
+    if (!status) return INPC_E_CUDA;
+    return sort_pairs_with("inpc_debug_sort_lookback_timeout", keys, keys_alt, values, values_alt, n, end_bit, workspace, status, nullptr,
+                           static_cast<cudaStream_t>(stream), 1 << 10, 0u);
+}
+
+// Status words of the last inpc_sort_pairs_static call on the current device, copied out of the fixed array
+// after `stream` has been synchronised (no allocation here either).
+extern "C" int inpc_sort_pairs_static_status(void* stream_, unsigned* words) {
+    using namespace inpc;
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    if (!words) { set_error("inpc_sort_pairs_static_status: null argument"); return INPC_E_INVALID; }
+    void* scratch = nullptr;
+    const int rc = static_scratch_for_current_device(&scratch);
+    if (rc != INPC_OK) return rc;
+    unsigned host[STATUS_WORDS];
+    INPC_CUDA_TRY(cudaMemcpyAsync(host, static_cast<unsigned char*>(scratch) + kStaticWorkspaceBytes, sizeof(host), cudaMemcpyDeviceToHost, stream));
+    INPC_CUDA_TRY(cudaStreamSynchronize(stream));
+    for (int k = 0; k < (int)STATUS_WORDS; ++k) words[k] = host[k];
+    if (host[STATUS_LOOKBACK_TIMEOUT]) {
+        set_error("inpc_sort_pairs_static: a radix-sort tile gave up waiting for a predecessor tile; the results of that call are invalid");
+        return INPC_E_DEVICE;
+    }
+    return INPC_OK;
 }

@@ -79,6 +79,18 @@ __device__ __forceinline__ W2C load_w2c(const float* __restrict__ w2c) {
     return m;
 }
 
+// One row of the world-to-camera transform applied to a point: r.x p.x + r.y p.y + r.z p.z + r.w with the
+// roundings of the reference binary (src/bilinear/kernels.cu:43-49 as nvcc contracts it): the second
+// product is rounded, the first and the third are fused onto it, the translation is added last.  Written
+// with intrinsics so that depth keys and screen positions, which are compared bit for bit, do not depend
+// on the compiler's choice of contraction.
+__device__ __forceinline__ float affine_row(const float* r, float px, float py, float pz) {
+    float t = __fmul_rn(r[1], py);
+    t = __fmaf_rn(r[0], px, t);
+    t = __fmaf_rn(r[2], pz, t);
+    return __fadd_rn(t, r[3]);
+}
+
 // src/bilinear/kernels.cu:41-65 and src/gaussian/kernels.cu:41-90 (training), :145-186 (inference),
 // :243-292 (pre-extracted): depth cull, perspective divide, pixel coordinates, tile bounds.
 template <int MODE, int VARIANT>
@@ -88,14 +100,14 @@ __device__ __forceinline__ Projection project_point(const float px, const float 
     o.visible = false;
     o.x0 = o.x1 = o.y0 = o.y1 = 0;
     o.cx = o.cy = o.cz = 0.0f;
-    const float depth = m.r2[0] * px + m.r2[1] * py + m.r2[2] * pz + m.r2[3];
+    const float depth = affine_row(m.r2, px, py, pz);
     o.depth = depth;
     o.sx = o.sy = 0.0f;
     if (depth < rp.v.near_plane || depth > rp.v.far_plane) return o;
-    const float x = (m.r0[0] * px + m.r0[1] * py + m.r0[2] * pz + m.r0[3]) / depth;
-    const float y = (m.r1[0] * px + m.r1[1] * py + m.r1[2] * pz + m.r1[3]) / depth;
-    const float sx = x * rp.v.fx + rp.v.cx;
-    const float sy = y * rp.v.fy + rp.v.cy;
+    const float x = __fdiv_rn(affine_row(m.r0, px, py, pz), depth);
+    const float y = __fdiv_rn(affine_row(m.r1, px, py, pz), depth);
+    const float sx = __fmaf_rn(x, rp.v.fx, rp.v.cx);
+    const float sy = __fmaf_rn(y, rp.v.fy, rp.v.cy);
     float ex = 0.5f, ey = 0.5f;
     if (MODE == INPC_MODE_GAUSSIAN) {
         float variance_world;
@@ -2591,10 +2603,13 @@ int tile_result_buffer(int64_t n_instances, int n_tiles) {
     return n_instances > 1 ? (sort_pass_count(end_bit) & 1) : 0;
 }
 
+// One event per host thread and device: an event belongs to the device that was current when it was made.
 cudaEvent_t counters_event() {
-    static thread_local cudaEvent_t e = nullptr;
-    if (!e && cudaEventCreateWithFlags(&e, cudaEventDisableTiming) != cudaSuccess) e = nullptr;
-    return e;
+    static thread_local cudaEvent_t events[kMaxDevices] = {nullptr};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return nullptr;
+    if (!events[dev] && cudaEventCreateWithFlags(&events[dev], cudaEventDisableTiming) != cudaSuccess) events[dev] = nullptr;
+    return events[dev];
 }
 
 unsigned long long* pinned_counters() {
@@ -2652,8 +2667,15 @@ int end_index_checks(cudaStream_t stream) {
 template <int MODE, int VARIANT>
 int run_front(const RasterParams& rp, int64_t n, const float* positions, const void* features, const float* opacities,
               inpc_alloc_fn alloc_point, inpc_alloc_fn alloc_instance, void* user, inpc_raster_state* st,
-              bool with_depth, PointBlob* pb_out, InstanceBlob* ib_out, cudaStream_t stream, int c4 = 1) {
+              bool with_depth, PointBlob* pb_out, InstanceBlob* ib_out, cudaStream_t stream, const char* entry, int c4 = 1) {
     const int n_tiles = rp.gw * rp.gh;
+    {
+        // a failure an earlier call of this thread reported from the device surfaces here at the latest
+        const int rc_prev = check_previous_calls();
+        if (rc_prev != INPC_OK) return rc_prev;
+    }
+    unsigned* status = acquire_status(entry);
+    if (!status) return INPC_E_CUDA;
     constexpr bool kRows = VARIANT == VAR_ROWS;
     const bool warp_blend = uses_warp_blend(MODE, rp.tile, kRows);
     const int64_t nb = ceil_div<int64_t>(n > 0 ? n : 1, kPreThreads);
@@ -2689,7 +2711,7 @@ int run_front(const RasterParams& rp, int64_t n, const float* positions, const v
             preprocess_kernel<MODE, VARIANT><<<(unsigned)nb, kPreThreads, 0, stream>>>(
                 positions, static_cast<const __half*>(features), opacities, n, rp, pb.block_visible, pb.group_visible, pb.depth_min, pb.depth_max,
                 pb.rec, pb.bounds,
-                pb.conic, pb.keys[0], pb.ids[0], (reinterpret_cast<uintptr_t>(features) & 15u) == 0, device_status_ptr());
+                pb.conic, pb.keys[0], pb.ids[0], (reinterpret_cast<uintptr_t>(features) & 15u) == 0, status);
             INPC_LAUNCH_CHECK("preprocess_kernel");
         }
         INPC_CUDA_TRY(cudaEventSynchronize(ready));
@@ -2705,14 +2727,6 @@ int run_front(const RasterParams& rp, int64_t n, const float* positions, const v
         if (n_visible > 0) {
             key_base = (uint32_t)host[2];
             key_bits = bit_length((uint32_t)host[3] - key_base);
-        }
-        if (read_and_clear_status(STATUS_LOOKBACK_TIMEOUT)) {
-            set_error("an earlier radix-sort pass gave up waiting for a predecessor tile; results of that call are invalid");
-            return INPC_E_DEVICE;
-        }
-        if (read_and_clear_status(STATUS_BULK_COPY_TIMEOUT)) {
-            set_error("an earlier projection pass gave up waiting for a bulk copy into shared memory; results of that call are invalid");
-            return INPC_E_DEVICE;
         }
     }
     if (n_instances >= ((int64_t)1 << 30)) {
@@ -2730,7 +2744,7 @@ int run_front(const RasterParams& rp, int64_t n, const float* positions, const v
     int rc;
     {
         StageScope scope(STAGE_SORT_DEPTH, stream);
-        rc = sort_pairs(pb.keys[0], pb.keys[1], pb.ids[0], pb.ids[1], n_visible, key_bits, pb.sort_ws, &in_alt, stream);
+        rc = sort_pairs(pb.keys[0], pb.keys[1], pb.ids[0], pb.ids[1], n_visible, key_bits, pb.sort_ws, status, &in_alt, stream);
     }
     if (rc != INPC_OK) return rc;
     const uint32_t* sorted_ids = pb.ids[in_alt];
@@ -2754,7 +2768,7 @@ int run_front(const RasterParams& rp, int64_t n, const float* positions, const v
         }
         StageScope scope(STAGE_SORT_TILE, stream);
         int t_alt = 0;
-        rc = sort_pairs(ib.keys[0], ib.keys[1], ib.ids[0], ib.ids[1], n_instances, bit_length((uint32_t)(n_tiles - 1)), ib.sort_ws, &t_alt, stream);
+        rc = sort_pairs(ib.keys[0], ib.keys[1], ib.ids[0], ib.ids[1], n_instances, bit_length((uint32_t)(n_tiles - 1)), ib.sort_ws, status, &t_alt, stream);
         if (rc != INPC_OK) return rc;
         tile_ranges_kernel<<<(unsigned)ceil_div<int64_t>(n_instances, 256 * 8), 256, 0, stream>>>(ib.keys[t_alt], n_instances, ib.ranges);
         INPC_LAUNCH_CHECK("tile_ranges_kernel");
@@ -2813,15 +2827,7 @@ int blend_batch(int tile) { return tile == 8 ? 64 * BlendConfig<8>::kIpt : 256 *
 
 // Persistent grid of the warp blend: enough blocks to fill the GPU (the item counts live on the device).
 int warp_blend_grid(unsigned* grid) {
-    int dev = 0, sms = 0;
-    INPC_CUDA_TRY(cudaGetDevice(&dev));
-    static int cached_sms[kMaxDevices] = {0};
-    if (dev >= 0 && dev < kMaxDevices && cached_sms[dev] > 0) sms = cached_sms[dev];
-    else {
-        INPC_CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
-        if (dev >= 0 && dev < kMaxDevices) cached_sms[dev] = sms;
-    }
-    *grid = (unsigned)max(1, sms * 4);
+    *grid = (unsigned)max(1, sm_count() * 4);
     return INPC_OK;
 }
 
@@ -3019,7 +3025,7 @@ int rows_forward(int tile_size, const inpc_view* view, int64_t n, const float* p
     PointBlob pb;
     InstanceBlob ib;
     int rc = run_front<INPC_MODE_BILINEAR, VAR_ROWS>(rp, n, positions, nullptr, opacities, alloc_point, alloc_instance, alloc_user, state,
-                                                     KIND == BLEND_INFER, &pb, &ib, stream, channels / 4);
+                                                     KIND == BLEND_INFER, &pb, &ib, stream, KIND == BLEND_INFER ? "inpc_render_rows" : "inpc_rasterize_rows_forward", channels / 4);
     if (rc != INPC_OK) return rc;
     const uint32_t* ids = ib.ids[tile_result_buffer(state->n_instances, rp.gw * rp.gh)];
     {
@@ -3053,9 +3059,9 @@ extern "C" int inpc_rasterize_forward(int mode, int tile_size, const inpc_view* 
     PointBlob pb;
     InstanceBlob ib;
     if (mode == INPC_MODE_BILINEAR)
-        rc = run_front<INPC_MODE_BILINEAR, VAR_TRAIN>(rp, n, positions, features, opacities, alloc_point, alloc_instance, alloc_user, state, false, &pb, &ib, stream);
+        rc = run_front<INPC_MODE_BILINEAR, VAR_TRAIN>(rp, n, positions, features, opacities, alloc_point, alloc_instance, alloc_user, state, false, &pb, &ib, stream, "inpc_rasterize_forward");
     else
-        rc = run_front<INPC_MODE_GAUSSIAN, VAR_TRAIN>(rp, n, positions, features, opacities, alloc_point, alloc_instance, alloc_user, state, false, &pb, &ib, stream);
+        rc = run_front<INPC_MODE_GAUSSIAN, VAR_TRAIN>(rp, n, positions, features, opacities, alloc_point, alloc_instance, alloc_user, state, false, &pb, &ib, stream, "inpc_rasterize_forward");
     if (rc != INPC_OK) return rc;
     rc = launch_blend_forward<BLEND_TRAIN>(mode, rp, pb, ib, state->n_instances, image, nullptr, alpha, blending_weights, kTrainGaussThreshold, stream);
     return rc != INPC_OK ? rc : end_index_checks(stream);
@@ -3125,9 +3131,9 @@ extern "C" int inpc_render(int mode, int tile_size, const inpc_view* view, int64
     PointBlob pb;
     InstanceBlob ib;
     if (mode == INPC_MODE_BILINEAR)
-        rc = run_front<INPC_MODE_BILINEAR, VAR_RAW37>(rp, n, positions, features_raw, nullptr, alloc_point, alloc_instance, alloc_user, &st, true, &pb, &ib, stream);
+        rc = run_front<INPC_MODE_BILINEAR, VAR_RAW37>(rp, n, positions, features_raw, nullptr, alloc_point, alloc_instance, alloc_user, &st, true, &pb, &ib, stream, "inpc_render");
     else
-        rc = run_front<INPC_MODE_GAUSSIAN, VAR_RAW37>(rp, n, positions, features_raw, nullptr, alloc_point, alloc_instance, alloc_user, &st, true, &pb, &ib, stream);
+        rc = run_front<INPC_MODE_GAUSSIAN, VAR_RAW37>(rp, n, positions, features_raw, nullptr, alloc_point, alloc_instance, alloc_user, &st, true, &pb, &ib, stream, "inpc_render");
     if (rc != INPC_OK) return rc;
     // runtime cut-off exp(-cutoff^2/2): src/gaussian/inference.cu:171
     const float threshold = expf(-0.5f * sigma_cutoff * sigma_cutoff);
@@ -3152,9 +3158,9 @@ extern "C" int inpc_render_preextracted(int mode, int tile_size, const inpc_view
     PointBlob pb;
     InstanceBlob ib;
     if (mode == INPC_MODE_BILINEAR)
-        rc = run_front<INPC_MODE_BILINEAR, VAR_PREEXTRACTED>(rp, n, positions, features, opacities, alloc_point, alloc_instance, alloc_user, &st, true, &pb, &ib, stream);
+        rc = run_front<INPC_MODE_BILINEAR, VAR_PREEXTRACTED>(rp, n, positions, features, opacities, alloc_point, alloc_instance, alloc_user, &st, true, &pb, &ib, stream, "inpc_render_preextracted");
     else
-        rc = run_front<INPC_MODE_GAUSSIAN, VAR_PREEXTRACTED>(rp, n, positions, features, opacities, alloc_point, alloc_instance, alloc_user, &st, true, &pb, &ib, stream);
+        rc = run_front<INPC_MODE_GAUSSIAN, VAR_PREEXTRACTED>(rp, n, positions, features, opacities, alloc_point, alloc_instance, alloc_user, &st, true, &pb, &ib, stream, "inpc_render_preextracted");
     if (rc != INPC_OK) return rc;
     const float threshold = expf(-0.5f * sigma_cutoff * sigma_cutoff);
     rc = launch_blend_forward<BLEND_INFER>(mode, rp, pb, ib, st.n_instances, image, depth, alpha, nullptr, threshold, stream);

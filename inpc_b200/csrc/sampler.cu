@@ -90,8 +90,10 @@ constexpr int kCdfChunk = kCdfThreads * kCdfItems;
 constexpr float kFixedOne = 549755813888.0f;   // 2^39
 constexpr double kFixedInv = 1.0 / 549755813888.0;
 
+// Non-finite and non-positive weights count as zero (an infinite one would make the quotient NaN, whose
+// conversion to an integer is undefined).
 __device__ __forceinline__ unsigned long long to_fixed(float w, float w_max) {
-    return w > 0.0f ? (unsigned long long)((w / w_max) * kFixedOne) : 0ull;
+    return (w > 0.0f && w <= 3.402823466e38f) ? (unsigned long long)((w / w_max) * kFixedOne) : 0ull;
 }
 
 // largest weight via atomicMax on the bit pattern (valid for non-negative floats; order-free)
@@ -100,7 +102,10 @@ __global__ void __launch_bounds__(kCdfThreads) cdf_max_kernel(const float* __res
     float m = 0.0f;
 #pragma unroll
     for (int k = 0; k < kCdfItems; ++k)
-        if (base + k < n) m = fmaxf(m, __ldg(w + base + k));
+        if (base + k < n) {
+            const float v = __ldg(w + base + k);
+            if (v <= 3.402823466e38f) m = fmaxf(m, v);   // NaN and +inf do not take part
+        }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_down_sync(0xffffffffu, m, o));
     if (lane_id() == 0 && m > 0.0f) atomicMax(max_bits, __float_as_uint(m));
@@ -582,7 +587,9 @@ int build_cdf(const float* weights, int64_t n_cells, float* cdf, float* sum_out,
 
 int check_cells(const inpc_view* view, int64_t n_cells, const void* a, const void* b, const void* c) {
     if (!view || !view->w2c) { set_error("sampler: view and view.w2c must be non-null"); return INPC_E_INVALID; }
-    if (n_cells <= 0 || n_cells >= ((int64_t)1 << 31)) { set_error("sampler: n_cells=%lld out of range", (long long)n_cells); return INPC_E_INVALID; }
+    // 2^24 leaves is the reference octree's own cap (Modules/ProbabilityField.py:217-257); the 39-bit
+    // fixed-point fractions of the CDF add up in 64 bits without wrapping for up to 2^25 of them
+    if (n_cells <= 0 || n_cells > ((int64_t)1 << 24)) { set_error("sampler: n_cells=%lld out of range [1, 2^24]", (long long)n_cells); return INPC_E_INVALID; }
     if (!a || !b || !c) { set_error("sampler: null leaf array"); return INPC_E_INVALID; }
     return INPC_OK;
 }
@@ -602,15 +609,26 @@ using namespace inpc;
 struct inpc_sampler {
     unsigned long long seed;
     unsigned long long counter;
+    long long training_ticket;   // status slot of the last inpc_generate_training_samples call (0: none)
 };
 
 extern "C" inpc_sampler* inpc_sampler_create(int64_t seed) {
     inpc_sampler* s = new inpc_sampler;
     s->seed = (unsigned long long)seed;
     s->counter = 0;
+    s->training_ticket = 0;
     return s;
 }
 extern "C" void inpc_sampler_destroy(inpc_sampler* s) { delete s; }
+// 1 if some slots of the sampler's last inpc_generate_training_samples call ran out of rejection attempts
+// (they hold their last candidate, a position outside the view frustum), 0 if none did, -1 if that is no longer
+// known (the status slot has been reused).  Meaningful once the call's stream has been synchronised.
+extern "C" int inpc_sampler_exhausted(const inpc_sampler* s) {
+    if (!s || s->training_ticket == 0) return 0;
+    unsigned w[inpc::STATUS_WORDS];
+    if (inpc::read_status(s->training_ticket, w, nullptr) != INPC_OK) return -1;
+    return w[inpc::STATUS_SAMPLER_EXHAUSTED] ? 1 : 0;
+}
 extern "C" uint64_t inpc_sampler_get_counter(const inpc_sampler* s) { return s ? s->counter : 0; }
 extern "C" void inpc_sampler_set_counter(inpc_sampler* s, uint64_t counter) { if (s) s->counter = counter; }
 
@@ -663,7 +681,7 @@ extern "C" int inpc_generate_training_samples(inpc_sampler* s, const inpc_view* 
     INPC_LAUNCH_CHECK("viewpoint_weights_kernel");
     rc = build_cdf(w.vw, n_cells, w.cdf, w.sum, w, stream);
     if (rc != INPC_OK) return rc;
-    unsigned* status = device_status_ptr();
+    unsigned* status = acquire_status("inpc_generate_training_samples", &s->training_ticket);
     if (!status) return INPC_E_CUDA;
     training_samples_kernel<<<(unsigned)ceil_div<int64_t>(n_samples, kThreads), kThreads, 0, stream>>>(
         v, s->seed, s->counter, w.cdf, w.guide, w.guide_bits, w.sum, (unsigned)n_cells, w.leaf_pack, n_samples, positions,
@@ -834,7 +852,13 @@ extern "C" int inpc_morton_order(const float* positions, int64_t n, const float*
                                                                                        1.0f / box_extent, codes[0], order[0]);
     INPC_LAUNCH_CHECK("morton_codes_kernel");
     int in_alt = 0;
-    const int rc = sort_pairs(codes[0], codes[1], order[0], order[1], n, 30, sort_ws, &in_alt, stream);
+    {
+        const int rc_prev = check_previous_calls();
+        if (rc_prev != INPC_OK) return rc_prev;
+    }
+    unsigned* status = acquire_status("inpc_morton_order");
+    if (!status) return INPC_E_CUDA;
+    const int rc = sort_pairs(codes[0], codes[1], order[0], order[1], n, 30, sort_ws, status, &in_alt, stream);
     if (rc != INPC_OK) return rc;
     gather_positions_kernel<<<(unsigned)ceil_div<int64_t>(n, kThreads), kThreads, 0, stream>>>(positions, order[in_alt], n, out);
     INPC_LAUNCH_CHECK("gather_positions_kernel");

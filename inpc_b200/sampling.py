@@ -9,6 +9,7 @@ a resumed run continues the stream (the reference's pcg32 state cannot be checkp
 from __future__ import annotations
 
 import ctypes as C
+import warnings
 
 import torch
 
@@ -95,6 +96,13 @@ class ProbabilityFieldSampler(torch.nn.Module):
         if state and int(state.get("seed", self.seed)) == self.seed:
             self.set_rng_state(int(state["counter"]))
 
+    def last_call_exhausted(self) -> bool | None:
+        """True if some slots of the last `generate_training_samples` call ran out of rejection attempts (they
+        hold their last candidate, a position outside the view frustum), False if none did, None if no longer known.
+        Final once the stream of that call has been synchronised; reading it does not synchronise."""
+        r = int(_cabi.lib().inpc_sampler_exhausted(self._handle))
+        return None if r < 0 else bool(r)
+
     def _workspace(self, n_cells: int, dev: torch.device) -> torch.Tensor:
         nbytes = int(_cabi.lib().inpc_sampler_workspace_bytes(n_cells))
         return torch.empty(nbytes, dtype=torch.uint8, device=dev)
@@ -119,6 +127,10 @@ class ProbabilityFieldSampler(torch.nn.Module):
         _check_view(view)
         centers, levels, weights, n = _leaf_args(centers, levels, weights)
         dev = centers.device
+        if self.last_call_exhausted():
+            # the previous call's flag, read without waiting for anything: by now it is normally final
+            warnings.warn("the previous generate_training_samples call left sample slots unfilled (rejection attempts "
+                          "exhausted): they hold positions outside the view frustum")
         with torch.cuda.device(dev):
             varg = _ViewArg(view, dev)
             positions = torch.empty((n_samples, 3), dtype=torch.float32, device=dev)

@@ -10,7 +10,7 @@ from dataclasses import dataclass
 
 import torch
 
-from .views import View, look_at_view
+from inpc_b200.views import View, look_at_view
 
 INITIAL_SIZE = 2.0   # root cube [-1,1]^3: a leaf of level l has edge 2 / 2**l
 

@@ -22,7 +22,7 @@ sys.path[:0] = [str(ROOT), str(ROOT / "oracle"), str(ROOT / "tests")]
 
 import ref_backend as RB  # noqa: E402
 from helpers import silence_depth_ties, small_scene  # noqa: E402
-from inpc_b200 import synthetic as syn  # noqa: E402
+import synthetic_workloads as syn  # noqa: E402
 
 DEV = "cuda:0"
 

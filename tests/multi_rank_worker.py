@@ -12,7 +12,7 @@ sys.path.insert(0, str(ROOT))
 
 
 def workload(device):
-    from inpc_b200 import synthetic as syn
+    import synthetic_workloads as syn
     tree = syn.adaptive_octree(4096, seed=1, min_level=3, max_level=6).to(device)
     n = 1 << 16
     feats = syn.sh_features(n, 12, "normal", 0.5).to(device)

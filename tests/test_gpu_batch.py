@@ -8,7 +8,7 @@ DEV = "cuda:0"
 
 
 def test_stream_pipelined_batch_equals_sequential_batch():
-    from inpc_b200 import synthetic as syn
+    import synthetic_workloads as syn
     from inpc_b200.batch import ViewShardedTrainer
     tree = syn.adaptive_octree(4096, seed=1, min_level=3, max_level=6).to(DEV)
     n = 1 << 17

@@ -88,7 +88,7 @@ def test_morton_order_is_a_sorted_permutation():
 
 def test_extract_global_end_to_end():
     import inpc_b200
-    from inpc_b200 import synthetic as syn
+    import synthetic_workloads as syn
     from inpc_b200.sampling import extract_global
     tree = syn.uniform_octree(4, seed=0).to(DEV)
     views = [v.to(DEV) for v in syn.orbit_views(3, seed=2, width=160, height=120, focal=140.0)]

@@ -347,7 +347,8 @@ def test_argument_errors_raise():
 def test_full_size_properties():
     """Full benchmark sizes (2^23 points, 1237x822): properties that need no oracle — sorted keys, ranges
     partition the instance list, tile-size independence of the image, run-to-run determinism."""
-    from inpc_b200 import rasterization as R, synthetic as syn
+    from inpc_b200 import rasterization as R
+    import synthetic_workloads as syn
     n = 1 << 23
     view = syn.orbit_view(0.6, 0.25, 3.0, 1237, 822, 960.0).to(DEV)
     g = torch.Generator(device=DEV).manual_seed(18)
@@ -388,7 +389,8 @@ def test_full_size_training_step_matches_reference_backend():
     against the reference's CUDA backend on the same points, both tilings.  Depth ties (about a third of
     the clustered samples share their depth's bit pattern with another one) are silenced first."""
     import inpc_b200
-    from inpc_b200 import rasterization as R, sampling as S, synthetic as syn
+    from inpc_b200 import rasterization as R, sampling as S
+    import synthetic_workloads as syn
     cfg = syn.config1()
     view, tree = cfg["view"].to(DEV), cfg["tree"].to(DEV)
     feats, opac = cfg["features"].to(DEV), cfg["opacities"].to(DEV)

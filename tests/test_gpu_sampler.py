@@ -20,7 +20,7 @@ needs_ref = pytest.mark.skipif(not RB.available(), reason="oracle/_ref/libinpc_r
 
 
 def _scene(adaptive=True):
-    from inpc_b200 import synthetic as syn
+    import synthetic_workloads as syn
     tree = syn.adaptive_octree(20000, seed=7, min_level=3, max_level=7) if adaptive else syn.uniform_octree(4, seed=0)
     view = syn.orbit_view(0.8, -0.3, 2.2, 200, 150, 170.0)      # close enough that part of the tree is outside
     return tree, view
@@ -165,7 +165,7 @@ def test_training_sample_distribution_matches_reference():
     """The reference's rejection sampler is race-ordered (atomic ticket), so only distributions can be
     compared: per-leaf histograms of both samplers against the expected conditional probabilities."""
     import inpc_b200
-    from inpc_b200 import synthetic as syn
+    import synthetic_workloads as syn
     tree = syn.uniform_octree(2, seed=4)
     view = syn.orbit_view(0.3, 0.2, 3.0, 256, 256, 300.0)
     t, v = tree.to(DEV), view.to(DEV)
@@ -186,7 +186,7 @@ def test_training_sample_distribution_matches_reference():
 def test_full_size_sampler_properties():
     """2^18 leaves, 2^23 samples: every sample inside its leaf and inside the frustum, deterministic."""
     import inpc_b200
-    from inpc_b200 import synthetic as syn
+    import synthetic_workloads as syn
     cfg = syn.config1(n_samples=8)                                # attributes are not needed here
     t, v = cfg["tree"].to(DEV), cfg["view"].to(DEV)
     n = 1 << 23

@@ -68,3 +68,41 @@ def test_sort_rejects_bad_arguments():
     assert rc == -1 and b"end_bit" in _cabi.lib().inpc_last_error()
     rc = _cabi.lib().inpc_sort_pairs(None, None, None, None, 10, 32, None, None, None)
     assert rc == -1
+
+
+def test_lookback_wait_runs_out_and_is_reported():
+    """The bounded look-back wait in its failing form: a test hook runs the sort with tile 0 of every pass leaving
+    before it publishes and a wait limit of 2^10 polls.  The tiles behind it must give up (microseconds), report
+    through the status words of that call, finish with every write inside the buffers, and leave the context
+    usable; the next entry point of the same host thread returns INPC_E_DEVICE with the look-back message."""
+    from inpc_b200 import _cabi
+    L = _cabi.lib()
+    n = 100_000                                   # 13 tiles of 8192 pairs
+    g = torch.Generator(device=DEV).manual_seed(3)
+    keys = torch.randint(0, 1 << 31, (n,), generator=g, device=DEV, dtype=torch.int64).to(torch.int32)
+    vals = torch.arange(n, device=DEV, dtype=torch.int32)
+    guard = 4096                                  # canaries around every buffer: nothing may be written outside [0, n)
+    bufs = [torch.full((n + 2 * guard,), -7, dtype=torch.int32, device=DEV) for _ in range(4)]
+    k, ka, v, va = [b[guard:guard + n] for b in bufs]
+    k.copy_(keys); v.copy_(vals)
+    ws = torch.empty(int(L.inpc_sort_workspace_bytes(n)), dtype=torch.uint8, device=DEV)
+    ticket = C.c_longlong(0)
+    stream = torch.cuda.current_stream().cuda_stream
+    _cabi.check(L.inpc_debug_sort_lookback_timeout(k.data_ptr(), ka.data_ptr(), v.data_ptr(), va.data_ptr(), n, 16, ws.data_ptr(),
+                                                   C.byref(ticket), stream))
+    torch.cuda.synchronize()                      # returns: nothing hangs
+    assert ticket.value > 0 and ticket.value == L.inpc_last_call_ticket()
+    words = (C.c_uint * 4)()
+    assert L.inpc_call_status(ticket.value, words) == -4          # INPC_E_DEVICE
+    assert words[0] == 1 and b"predecessor tile" in L.inpc_last_error()
+    for b in bufs:                                # no write left its buffer
+        assert bool((b[:guard] == -7).all()) and bool((b[guard + n:] == -7).all())
+    # the failure also surfaces at this thread's next call, once
+    k2, v2 = keys.clone(), vals.clone()
+    alt = C.c_int(0)
+    rc = L.inpc_sort_pairs(k2.data_ptr(), torch.empty_like(k2).data_ptr(), v2.data_ptr(), torch.empty_like(v2).data_ptr(), n, 16,
+                           ws.data_ptr(), C.byref(alt), stream)
+    assert rc == -4 and b"inpc_debug_sort_lookback_timeout" in L.inpc_last_error()
+    # ... and the library works again afterwards
+    _check(keys.to(torch.int64) & 0xFFFFFFFF, 16)
+    assert L.inpc_call_status(L.inpc_last_call_ticket(), None) == 0

@@ -174,7 +174,7 @@ def test_pcg32_known_answers():
 
 
 def test_training_samples_inside_leaf_and_frustum():
-    from inpc_b200 import synthetic as syn
+    import synthetic_workloads as syn
     cfg = syn.config0()
     tree, view = cfg["tree"], cfg["view"]
     cam = oracle_camera(view)
@@ -199,7 +199,7 @@ def test_training_samples_inside_leaf_and_frustum():
 
 
 def test_training_sample_histogram_matches_weights():
-    from inpc_b200 import synthetic as syn
+    import synthetic_workloads as syn
     tree = syn.uniform_octree(2, seed=4)      # 64 leaves, all well inside the frustum below
     view = look_at_view((0.0, 0.0, 6.0), (0.0, 0.0, 0.0), 256, 256, 500.0, 500.0)
     cam = oracle_camera(view)
