@@ -292,53 +292,33 @@ def run_ours(args):
     pinned_ga = wl["grad_alpha"].pin_memory()
     pinned_views = [(v.w2c.pin_memory(), v.position.pin_memory()) for v in wl["views_host"]]
     loss_host = torch.zeros(args.views, dtype=torch.float32).pin_memory()
-    from inpc_b200.batch import accumulate_view, allreduce_buffers
     from inpc_b200.views import View
-    e2e_streams = [torch.cuda.Stream(device=device) for _ in range(max(args.streams, 1))]
     copy_stream = torch.cuda.Stream(device=device)
-    e2e_parts = [torch.zeros_like(trainer.buffers.appearance) for _ in e2e_streams]
+
+    def host_inputs(vi, stream):
+        # this view's inputs come from pinned host memory on a copy stream of their own, so that the copies run
+        # ahead of, and under, the kernels of the views in flight
+        with torch.cuda.stream(copy_stream):
+            gi = pinned_gi.to(device, non_blocking=True)
+            ga = pinned_ga.to(device, non_blocking=True)
+            w2c, cpos = pinned_views[vi]
+            w2c_d, cpos_d = w2c.to(device, non_blocking=True), cpos.to(device, non_blocking=True)
+            copied = torch.cuda.Event()
+            copied.record(copy_stream)
+        stream.wait_event(copied)
+        for tensor in (gi, ga, w2c_d, cpos_d):
+            tensor.record_stream(stream)
+        return View(wl["views_host"][vi].camera, w2c_d, cpos_d), gi, ga
 
     def e2e_step():
-        main = torch.cuda.current_stream()
-        trainer.buffers.zero_()
-        for part in e2e_parts:
-            part.zero_()
-        for s_ in e2e_streams:
-            s_.wait_stream(main)
-        copy_stream.wait_stream(main)
-        for k, vi in enumerate(my_views):
-            slot = k % len(e2e_streams)
-            # this view's inputs come from pinned host memory on a copy stream of their own, so that the
-            # copies run ahead of, and under, the kernels of the views in flight
-            with torch.cuda.stream(copy_stream):
-                gi = pinned_gi.to(device, non_blocking=True)
-                ga = pinned_ga.to(device, non_blocking=True)
-                w2c, cpos = pinned_views[vi]
-                w2c_d, cpos_d = w2c.to(device, non_blocking=True), cpos.to(device, non_blocking=True)
-                copied = torch.cuda.Event()
-                copied.record(copy_stream)
-            with torch.cuda.stream(e2e_streams[slot]):
-                e2e_streams[slot].wait_event(copied)
-                for tensor in (gi, ga, w2c_d, cpos_d):
-                    tensor.record_stream(e2e_streams[slot])
-                view = View(wl["views_host"][vi].camera, w2c_d, cpos_d)
-                trainer.sampler.set_rng_state(vi)
-                t = wl["tree"]
-                pos, idx = trainer.sampler.generate_training_samples(t.centers, t.levels, t.weights, view, args.points, t.initial_size)
-                feats = wl["features"].detach().requires_grad_(True)
-                opac = wl["opacities"].detach().requires_grad_(True)
-                image, alpha, bw = trainer.rasterizer(view, 0, pos, feats, opac)
-                loss = (image * gi).sum() + (alpha * ga).sum()
-                loss.backward()
-                accumulate_view(trainer.buffers, idx, bw, feats.grad, opac.grad, e2e_parts[slot])
-                loss_host[vi:vi + 1].copy_(loss.detach().reshape(1), non_blocking=True)
-        for s_ in e2e_streams:
-            main.wait_stream(s_)
-        for part in e2e_parts:
-            trainer.buffers.appearance.add_(part)
-        allreduce_buffers(trainer.buffers)
+        copy_stream.wait_stream(torch.cuda.current_stream())
+        out = trainer.run_batch(wl["views"], None, rank, world, inputs=host_inputs)
+        if out is not None:
+            # the step's result read back: the loss of the shard's last view
+            loss = (out[0].detach() * gi_dev).sum() + (out[1].detach() * ga_dev).sum()
+            loss_host[:1].copy_(loss.reshape(1), non_blocking=True)
         torch.cuda.synchronize()
-        return float(loss_host[my_views[-1]].item()) if my_views else 0.0
+        return float(loss_host[0].item())
 
     e2e_step()
     barrier(world)
@@ -407,7 +387,7 @@ def run_ours(args):
         "frames_per_s": args.steps * args.views / (elapsed_ms * 1e-3),
         "ms_per_view": elapsed_ms / args.steps / max(len(my_views), 1),
         "e2e": {"value": e2e_value, "unit": UNIT,
-                "h2d_bytes_per_step": args.views * (5 * P * 4 + 16 * 4 + 3 * 4), "d2h_bytes_per_step": args.views * 4},
+                "h2d_bytes_per_step": args.views * (5 * P * 4 + 16 * 4 + 3 * 4), "d2h_bytes_per_step": 4 * world},
         "gpu_launches": launches,
         "clocks": clock_info,
         "roofline": roofline,

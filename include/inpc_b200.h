@@ -54,14 +54,14 @@ typedef struct inpc_raster_state {
     void* point_blob;     /* per-point scratch from alloc_point */
     void* instance_blob;  /* per-instance + per-tile scratch from alloc_instance */
     int64_t n_points;
-    int64_t n_visible;
-    int64_t n_instances;
+    int64_t n_visible;        /* -1 while the count is still on the device (deferred_counts), see inpc_raster_resolve */
+    int64_t n_instances;      /* likewise */
     int32_t tile_size;
     int32_t mode;
     uint32_t depth_key_base;  /* smallest depth bit pattern among the visible points (sort keys are offsets from it) */
     int32_t depth_key_bits;   /* significant bits of the largest offset */
     int32_t channels;         /* blended channels: 4 for the spherical-harmonics layout, else the feature-row width */
-    int32_t reserved;
+    int32_t deferred_counts;  /* 1: no count was read back; scratch is sized for 4 instances per point */
 } inpc_raster_state;
 
 const char* inpc_last_error(void);
@@ -103,8 +103,11 @@ int inpc_call_status(long long ticket, unsigned* words);
  *   positions (n,3) f32 | features (n,36) f16, coefficient-major channel-minor | opacities (n) f32
  *   image (4,H,W) f32 | alpha (H,W) f32 | blending_weights (n) f32 — all three fully written.
  * tile_size is 8 (the reference's tiling; tile ranges comparable with it) or 16.
- * Reads two counters back to the host once (n_visible, n_instances) to size the instance scratch;
- * this is the only host synchronisation (the reference has two).
+ * Bilinear mode with 8x8 tiles makes no host synchronisation at all: a splat touches at most 2x2 tiles, so the
+ * instance scratch is sized for 4 n instances, the kernels read the two counts from device memory, and
+ * state->n_visible / n_instances stay -1 until inpc_raster_resolve is called.  The other combinations read
+ * the two counters back once to size the instance scratch (the reference does so twice, with blocking copies:
+ * rasterization/src/bilinear/forward.cu:86-89).
  * Replaces inpc::rasterization::{bilinear,gaussian}::forward
  * (rasterization/include/bilinear/forward.h:10-30, gaussian/forward.h:10-30) together with the
  * output zero-fill of forward_wrapper (rasterization/src/rasterization_api.cu:44-46). */
@@ -177,6 +180,12 @@ int inpc_render_rows(int tile_size, const inpc_view* view, int64_t n, const floa
                      const float* features, int channels, const float* opacities, float* image, float* depth,
                      float* alpha, inpc_alloc_fn alloc_point, inpc_alloc_fn alloc_instance, void* alloc_user,
                      void* stream);
+
+/* Fills in state->n_visible, n_instances and depth_key_base of a forward that deferred them: one small
+ * device-to-host copy on `stream` and a synchronisation of that stream.  A no-op for states whose counts were
+ * read back by the forward itself.  The values the reference returns from its blocking copies at
+ * rasterization/src/bilinear/forward.cu:86-89. */
+int inpc_raster_resolve(inpc_raster_state* state, void* stream);
 
 /* Introspection for parity tests: copies one intermediate array of the forward that produced
  * `state` into `dst` (device pointer, caller-sized).  which: 0 sorted visible point ids (n_visible

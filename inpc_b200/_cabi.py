@@ -32,7 +32,7 @@ class RasterState(C.Structure):
     _fields_ = [("point_blob", C.c_void_p), ("instance_blob", C.c_void_p), ("n_points", C.c_int64),
                 ("n_visible", C.c_int64), ("n_instances", C.c_int64), ("tile_size", C.c_int32), ("mode", C.c_int32),
                 ("depth_key_base", C.c_uint32), ("depth_key_bits", C.c_int32), ("channels", C.c_int32),
-                ("reserved", C.c_int32)]
+                ("deferred_counts", C.c_int32)]
 
 
 _P, _I, _L, _F, _Z = C.c_void_p, C.c_int, C.c_int64, C.c_float, C.c_size_t
@@ -53,6 +53,7 @@ PROTOTYPES = {
     "inpc_rasterize_rows_backward": (_I, [_SP, _VP, _P, _P, _P, _P, _P, _P, _P, _P]),
     "inpc_render_rows": (_I, [_I, _VP, _L, _P, _P, _I, _P, _P, _P, _P, ALLOC_FN, ALLOC_FN, _P, _P]),
     "inpc_raster_debug_copy": (_I, [_SP, _VP, _I, _P, _P]),
+    "inpc_raster_resolve": (_I, [_SP, _P]),
     "inpc_sort_workspace_bytes": (_Z, [_L]),
     "inpc_sort_pairs": (_I, [_P, _P, _P, _P, _L, _I, _P, C.POINTER(C.c_int), _P]),
     "inpc_sort_pairs_static": (_I, [_P, _P, _P, _P, _L, _I, C.POINTER(C.c_int), _P]),

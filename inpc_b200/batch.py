@@ -81,19 +81,26 @@ class _HostLeafStatistics:
 
 
 def accumulate_view(buffers: BatchBuffers, leaf_indices: torch.Tensor, blending_weights: torch.Tensor,
-                    grad_features: torch.Tensor, grad_opacities: torch.Tensor, appearance: torch.Tensor | None = None) -> None:
+                    grad_features: torch.Tensor, grad_opacities: torch.Tensor, appearance: torch.Tensor | None = None,
+                    overwrite: bool = False) -> None:
     """Adds one view's contribution to the buffers (device-side, no synchronisation).  The appearance
     stand-in folds the per-point opacity gradient into `n_appearance` slots.  `appearance` redirects
     that sum to a private partial buffer (views running concurrently on several streams must not
-    read-modify-write one buffer; the leaf statistics are updated with atomics and need no such care)."""
+    read-modify-write one buffer; the leaf statistics are updated with atomics and need no such care);
+    `overwrite` stores the view's sum instead of adding it (the first view of a partial buffer: no zero-fill)."""
     buffers.leaf.accumulate(leaf_indices, blending_weights)
     target = buffers.appearance if appearance is None else appearance
     n_app = target.numel()
     per_point = grad_opacities.reshape(-1)
     n = per_point.numel()
     if n % n_app == 0:
-        target.add_(per_point.view(n // n_app, n_app).sum(dim=0))
+        if overwrite:
+            torch.sum(per_point.view(n // n_app, n_app), dim=0, out=target)
+        else:
+            target.add_(per_point.view(n // n_app, n_app).sum(dim=0))
     else:
+        if overwrite:
+            target.zero_()
         slot = torch.arange(n, device=per_point.device) % n_app
         target.index_add_(0, slot, per_point)
 
@@ -136,11 +143,12 @@ class ViewShardedTrainer:
         if self._streams is None:
             dev = self.features.device
             self._streams = [torch.cuda.Stream(device=dev) for _ in range(self.n_streams)]
-            self._appearance_parts = [torch.zeros_like(self.buffers.appearance) for _ in range(self.n_streams)]
+            # one row per stream: the views of a stream add into their own row
+            self._appearance_parts = torch.zeros((self.n_streams, self.buffers.appearance.numel()), dtype=torch.float32, device=dev)
         return self._streams, self._appearance_parts
 
     def run_view(self, view, grad_image: torch.Tensor, grad_alpha: torch.Tensor, view_index: int | None = None,
-                 appearance: torch.Tensor | None = None):
+                 appearance: torch.Tensor | None = None, overwrite: bool = False):
         """One view, forward and backward.  `view_index` pins the random stream to the view, so the
         result does not depend on which rank renders it."""
         t = self.tree
@@ -152,33 +160,60 @@ class ViewShardedTrainer:
         opac = self.opacities.detach().requires_grad_(True)
         image, alpha, blending_weights = self.rasterizer(view, self.mode, positions, feats, opac)
         torch.autograd.backward([image, alpha], [grad_image, grad_alpha])
-        accumulate_view(self.buffers, indices, blending_weights, feats.grad, opac.grad, appearance)
+        accumulate_view(self.buffers, indices, blending_weights, feats.grad, opac.grad, appearance, overwrite)
         return image, alpha, blending_weights, feats.grad, opac.grad
 
-    def run_batch(self, views, grads, rank: int = 0, world_size: int = 1, group=None):
-        """All views of this rank's shard, then the one exchange step.  `grads` is one
-        (grad_image, grad_alpha) pair used for every view, or a list with one pair per view."""
-        self.buffers.zero_()
+    def run_batch(self, views, grads, rank: int = 0, world_size: int = 1, group=None, inputs=None):
+        """All views of this rank's shard and the exchange step.  `grads` is one (grad_image, grad_alpha) pair
+        used for every view, or a list with one pair per view.  `inputs(view_index, stream)`, if given, supplies
+        (view, grad_image, grad_alpha) of a view instead -- e.g. copied from host memory on a stream of the
+        caller's, with `stream` made to wait for the copy.
+
+        Streams: view k of the shard runs on stream k mod n_streams and adds its appearance sum into that
+        stream's row of a partial buffer (the row's first view stores instead of adding: nothing is zero-filled).
+        When a stream has enqueued its last view its row is all-reduced right there, on that stream, under the
+        views the other streams still have in flight; every rank issues exactly n_streams such all-reduces, in
+        stream order.  One fused sum over the rows and the (small) MAX all-reduce of the leaf statistics end
+        the batch."""
+        import torch.distributed as dist
+        distributed = dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1
+        self.buffers.leaf.reset()
         out = None
         mine = partition_views(len(views), rank, world_size)
-        if self.n_streams == 1 or len(mine) < 2:
-            for vi in mine:
-                gi, ga = grads if isinstance(grads[0], torch.Tensor) else grads[vi]
-                out = self.run_view(views[vi], gi, ga, view_index=vi)
+
+        def view_inputs(vi, stream):
+            if inputs is not None:
+                return inputs(vi, stream)
+            gi, ga = grads if isinstance(grads[0], torch.Tensor) else grads[vi]
+            return views[vi], gi, ga
+
+        if self.n_streams == 1:
+            main = torch.cuda.current_stream()
+            if not mine:
+                self.buffers.appearance.zero_()
+            for k, vi in enumerate(mine):
+                view, gi, ga = view_inputs(vi, main)
+                out = self.run_view(view, gi, ga, view_index=vi, appearance=self.buffers.appearance, overwrite=k == 0)
+            if distributed:
+                dist.all_reduce(self.buffers.appearance, op=dist.ReduceOp.SUM, group=group)
         else:
             streams, parts = self._pipeline()
             main = torch.cuda.current_stream()
-            for part in parts:
-                part.zero_()
             for s in streams:
                 s.wait_stream(main)
             for k, vi in enumerate(mine):
-                gi, ga = grads if isinstance(grads[0], torch.Tensor) else grads[vi]
-                with torch.cuda.stream(streams[k % self.n_streams]):
-                    out = self.run_view(views[vi], gi, ga, view_index=vi, appearance=parts[k % self.n_streams])
+                slot = k % self.n_streams
+                with torch.cuda.stream(streams[slot]):
+                    view, gi, ga = view_inputs(vi, streams[slot])
+                    out = self.run_view(view, gi, ga, view_index=vi, appearance=parts[slot], overwrite=k < self.n_streams)
+            for slot, s in enumerate(streams):
+                with torch.cuda.stream(s):
+                    if slot >= len(mine):
+                        parts[slot].zero_()          # a stream without a view this batch
+                    if distributed:
+                        dist.all_reduce(parts[slot], op=dist.ReduceOp.SUM, group=group)
             for s in streams:
                 main.wait_stream(s)
-            for part in parts:
-                self.buffers.appearance.add_(part)
-        allreduce_buffers(self.buffers, group)
+            torch.sum(parts, dim=0, out=self.buffers.appearance)
+        self.buffers.leaf.all_reduce(group)
         return out

@@ -120,6 +120,11 @@ int sort_pass_count(int end_bit);   // passes sort_pairs makes; the result is in
 // `status`: device address of the STATUS_WORDS words a tile that gives up its look-back reports to.
 int sort_pairs(uint32_t* keys, uint32_t* keys_alt, uint32_t* values, uint32_t* values_alt, int64_t n,
                int end_bit, void* workspace, unsigned* status, int* result_in_alt, cudaStream_t stream);
+// The number of pairs is *n_dev (device memory, <= n_max); the workspace is sized for n_max.  The result is in the
+// alternate buffers iff sort_pass_count(end_bit) is odd, whatever the count turns out to be.
+int sort_pairs_device_count(uint32_t* keys, uint32_t* keys_alt, uint32_t* values, uint32_t* values_alt, int64_t n_max,
+                            const unsigned long long* n_dev, int end_bit, void* workspace, unsigned* status, int* result_in_alt,
+                            cudaStream_t stream);
 
 // More than 48 KB of dynamic shared memory is an opt-in per kernel AND per device: `done` is the
 // caller's per-kernel table of devices already set up.

@@ -41,8 +41,11 @@ struct PassTable {
 constexpr int kHistThreads = 512;
 constexpr int kHistItemsPerBlock = kHistThreads * 4 * 8;   // 8 uint4 loads per thread
 
+// `n_dev` (optional): the number of pairs lives on the device (the grid is then sized for an upper bound).
 __global__ void __launch_bounds__(kHistThreads) radix_histogram_kernel(
-    const uint32_t* __restrict__ keys, int64_t n, PassTable pt, unsigned* __restrict__ hist) {
+    const uint32_t* __restrict__ keys, int64_t n_arg, const unsigned long long* __restrict__ n_dev, PassTable pt, unsigned* __restrict__ hist) {
+    const int64_t n = n_dev ? (int64_t)*n_dev : n_arg;
+    if ((int64_t)blockIdx.x * kHistItemsPerBlock >= n) return;
     __shared__ unsigned s_hist[kMaxPasses][kRadix];
     for (int i = threadIdx.x; i < kMaxPasses * kRadix; i += kHistThreads) (&s_hist[0][0])[i] = 0;
     __syncthreads();
@@ -98,8 +101,8 @@ struct PassSmem {
 template <int BITS>
 __global__ void __launch_bounds__(kThreads) radix_onesweep_pass_kernel(
     const uint32_t* __restrict__ keys_in, const uint32_t* __restrict__ vals_in,
-    uint32_t* __restrict__ keys_out, uint32_t* __restrict__ vals_out, int64_t n, int shift, int bits_arg,
-    const unsigned* __restrict__ digit_base, volatile unsigned* tile_state, unsigned* ticket,
+    uint32_t* __restrict__ keys_out, uint32_t* __restrict__ vals_out, int64_t n_arg, const unsigned long long* __restrict__ n_dev,
+    int shift, int bits_arg, const unsigned* __restrict__ digit_base, volatile unsigned* tile_state, unsigned* ticket,
     volatile unsigned* status, int spin_limit, unsigned mute_tile) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     PassSmem& s = *reinterpret_cast<PassSmem*>(smem_raw);
@@ -115,7 +118,9 @@ __global__ void __launch_bounds__(kThreads) radix_onesweep_pass_kernel(
     // `mute_tile` (no tile in normal operation) leaves without publishing anything: the tiles behind it then
     // run into the limit of their look-back wait, which is how the tests exercise that path
     if (tile == mute_tile) return;
+    const int64_t n = n_dev ? (int64_t)*n_dev : n_arg;
     const int64_t tile_base = (int64_t)tile * kTile;
+    if (tile_base >= n) return;   // grid sized for an upper bound of n: nothing here, and no tile waits for this one
     const int valid = (int)min((int64_t)kTile, n - tile_base);
 
     // warp-striped load: warp w owns [w*32*kItems, (w+1)*32*kItems) of the tile, item i of lane l
@@ -299,6 +304,7 @@ struct PassArgs {
     const uint32_t *kin, *vin;
     uint32_t *kout, *vout;
     int64_t n;
+    const unsigned long long* n_dev;
     int shift, bits;
     const unsigned* base;
     unsigned *state, *ticket, *status;
@@ -316,7 +322,7 @@ int launch_onesweep_instance(const PassArgs& a, cudaStream_t stream) {
         const int rc = opt_in_dynamic_smem(radix_onesweep_pass_kernel<BITS>, kSmemBytes, attr_set);
         if (rc != INPC_OK) return rc;
     }
-    radix_onesweep_pass_kernel<BITS><<<(unsigned)a.tiles, kThreads, kSmemBytes, stream>>>(a.kin, a.vin, a.kout, a.vout, a.n, a.shift, a.bits, a.base,
+    radix_onesweep_pass_kernel<BITS><<<(unsigned)a.tiles, kThreads, kSmemBytes, stream>>>(a.kin, a.vin, a.kout, a.vout, a.n, a.n_dev, a.shift, a.bits, a.base,
                                                                                          a.state, a.ticket, a.status, a.spin_limit, a.mute_tile);
     INPC_LAUNCH_CHECK("radix_onesweep_pass_kernel");
     return INPC_OK;
@@ -357,7 +363,7 @@ static int check_sort_args(const char* who, const uint32_t* keys, const uint32_t
 
 static int sort_pairs_with(const char* who, uint32_t* keys, uint32_t* keys_alt, uint32_t* values, uint32_t* values_alt, int64_t n, int end_bit,
                            void* workspace, unsigned* status, int* result_in_alt, cudaStream_t stream, int spin_limit = kSpinLimit,
-                           unsigned mute_tile = 0xFFFFFFFFu) {
+                           unsigned mute_tile = 0xFFFFFFFFu, const unsigned long long* n_dev = nullptr) {
     if (result_in_alt) *result_in_alt = 0;
     if (!workspace || !status) { set_error("%s: null workspace", who); return INPC_E_INVALID; }
 
@@ -381,13 +387,13 @@ static int sort_pairs_with(const char* who, uint32_t* keys, uint32_t* keys_alt, 
     INPC_CUDA_TRY(cudaMemsetAsync(workspace, 0, w.zero_bytes + (size_t)pt.n_passes * tiles * kRadix * sizeof(unsigned), stream));
 
     const int hist_blocks = (int)ceil_div<int64_t>(n, kHistItemsPerBlock);
-    radix_histogram_kernel<<<hist_blocks, kHistThreads, 0, stream>>>(keys, n, pt, w.hist);
+    radix_histogram_kernel<<<hist_blocks, kHistThreads, 0, stream>>>(keys, n, n_dev, pt, w.hist);
     INPC_LAUNCH_CHECK("radix_histogram_kernel");
     radix_scan_histogram_kernel<<<pt.n_passes, kRadix, 0, stream>>>(w.hist, w.base);
     INPC_LAUNCH_CHECK("radix_scan_histogram_kernel");
 
     PassArgs a;
-    a.tiles = tiles; a.n = n; a.status = status;
+    a.tiles = tiles; a.n = n; a.n_dev = n_dev; a.status = status;
     a.spin_limit = spin_limit; a.mute_tile = mute_tile;
     a.kin = keys; a.kout = keys_alt; a.vin = values; a.vout = values_alt;
     for (int p = 0; p < pt.n_passes; ++p) {
@@ -412,6 +418,22 @@ int sort_pairs(uint32_t* keys, uint32_t* keys_alt, uint32_t* values, uint32_t* v
     if (rc != INPC_OK || nothing) return rc;
     if (!workspace) { set_error("sort_pairs: null workspace"); return INPC_E_INVALID; }
     return sort_pairs_with("sort_pairs", keys, keys_alt, values, values_alt, n, end_bit, workspace, status, result_in_alt, stream);
+}
+
+// The same sort with the number of pairs in device memory (*n_dev <= n_max): grids and the look-back state are
+// sized for n_max, the kernels read the count themselves, and the result is always in the alternate buffers iff
+// the number of passes is odd.  No host synchronisation anywhere.
+int sort_pairs_device_count(uint32_t* keys, uint32_t* keys_alt, uint32_t* values, uint32_t* values_alt, int64_t n_max,
+                            const unsigned long long* n_dev, int end_bit, void* workspace, unsigned* status, int* result_in_alt,
+                            cudaStream_t stream) {
+    if (result_in_alt) *result_in_alt = 0;
+    if (n_max <= 0 || end_bit == 0) return INPC_OK;
+    bool nothing = false;
+    const int rc = check_sort_args("sort_pairs", keys, keys_alt, values, values_alt, n_max < 2 ? 2 : n_max, end_bit, &nothing);
+    if (rc != INPC_OK) return rc;
+    if (!workspace || !n_dev) { set_error("sort_pairs: null workspace or count"); return INPC_E_INVALID; }
+    return sort_pairs_with("sort_pairs", keys, keys_alt, values, values_alt, n_max, end_bit, workspace, status, result_in_alt, stream, kSpinLimit,
+                           0xFFFFFFFFu, n_dev);
 }
 
 }  // namespace inpc

@@ -309,6 +309,17 @@ __device__ __forceinline__ float sh_eval_channel(const float* b, const __half* h
            b[6] * __half2float(h[24 + c]) - b[7] * __half2float(h[28 + c]) + b[8] * __half2float(h[32 + c]);
 }
 
+// What the instance emission of the warp blend needs of a bilinear splat, in one word: column of the
+// left pixel of its 2x2 footprint plus one (15 bits), whether it touches two tile columns (1 bit), and the
+// same for rows.  A visible splat's footprint starts at pixel -1 at the earliest, and images of this path
+// are at most kMaxCodedSide pixels wide and high.  4 bytes per point keep the array (33 MB for 2^23
+// points) resident in L2 while the emission gathers from it in depth order.
+constexpr int kMaxCodedSide = 32760;
+__device__ __forceinline__ uint32_t pack_quad(const Projection& pr) {
+    const unsigned qx1 = (unsigned)(__float2int_rd(pr.sx - 0.5f) + 1), qy1 = (unsigned)(__float2int_rd(pr.sy - 0.5f) + 1);
+    return (qx1 & 0x7FFFu) | ((pr.x1 - pr.x0 - 1u) << 15) | ((qy1 & 0x7FFFu) << 16) | ((pr.y1 - pr.y0 - 1u) << 31);
+}
+
 // Pass 2: project again (same arithmetic, same outcome), evaluate SH, write the point record and
 // bounds, and append (depth key, point id) at the slot given by the block offset plus the rank of
 // the point among the block's survivors — index order, hence reproducible.
@@ -318,8 +329,9 @@ __global__ void __launch_bounds__(kPreThreads) preprocess_kernel(
     const float* __restrict__ positions, const __half* __restrict__ features, const float* __restrict__ opacities,
     int64_t n, RasterParams rp, const unsigned* __restrict__ block_visible, const unsigned* __restrict__ group_offset,
     const unsigned* __restrict__ depth_min,
-    const unsigned* __restrict__ depth_max, PointRec* __restrict__ rec, uint2* __restrict__ bounds, float4* __restrict__ conic, uint32_t* __restrict__ depth_keys,
-    uint32_t* __restrict__ point_ids, bool bulk_ok, volatile unsigned* status) {
+    const unsigned* __restrict__ depth_max, PointRec* __restrict__ rec, uint2* __restrict__ bounds, uint32_t* __restrict__ quad,
+    float4* __restrict__ conic, uint32_t* __restrict__ depth_keys,
+    uint32_t* __restrict__ point_ids, bool bulk_ok, int pack_count, volatile unsigned* status) {
     constexpr int kHalves = VARIANT == VAR_RAW37 ? 37 : 36;
     constexpr int kSlabBytes = VARIANT == VAR_ROWS ? 16 : kPreThreads * kHalves * 2;   // multiple of 16 for both layouts
     __shared__ __align__(16) unsigned char s_feat[kSlabBytes];
@@ -386,6 +398,7 @@ __global__ void __launch_bounds__(kPreThreads) preprocess_kernel(
             dst[0] = make_float4(r.sx, r.sy, r.opacity, r.depth);
             dst[1] = make_float4(r.f[0], r.f[1], r.f[2], r.f[3]);
             bounds[i] = make_uint2(pr.x0 | (pr.x1 << 16), pr.y0 | (pr.y1 << 16));
+            if (quad) quad[i] = pack_quad(pr);
             if (MODE == INPC_MODE_GAUSSIAN) conic[i] = make_float4(pr.cx, pr.cy, pr.cz, 0.0f);
         } else {
             bounds[i] = make_uint2(0u, 0u);
@@ -403,7 +416,9 @@ __global__ void __launch_bounds__(kPreThreads) preprocess_kernel(
         // saves the instance pass a gather.
         const unsigned lo = __ldg(depth_min);
         unsigned key = __float_as_uint(pr.depth) - lo;
-        if (MODE == INPC_MODE_BILINEAR && __ldg(depth_max) - lo < (1u << kCountShift))
+        // pack_count: 1 yes, 0 no (the host knows a bound on the offsets), -1 decide from the measured depth range
+        const bool pack = pack_count >= 0 ? pack_count != 0 : __ldg(depth_max) - lo < (1u << kCountShift);
+        if (MODE == INPC_MODE_BILINEAR && pack)
             key |= ((pr.x1 - pr.x0) * (pr.y1 - pr.y0) - 1u) << kCountShift;
         depth_keys[slot] = key;
         point_ids[slot] = (uint32_t)i;
@@ -420,8 +435,10 @@ constexpr int kInstThreads = 1024;   // block sums over 1024 points keep the one
 template <bool PACKED>
 __global__ void __launch_bounds__(kInstThreads / 4) instance_count_kernel(const uint32_t* __restrict__ sorted_keys,
                                                                           const uint32_t* __restrict__ sorted_ids,
-                                                                          const uint2* __restrict__ bounds, int64_t n_visible,
+                                                                          const uint2* __restrict__ bounds, int64_t n_visible_arg,
+                                                                          const unsigned long long* __restrict__ n_visible_dev,
                                                                           unsigned* __restrict__ block_sums) {
+    const int64_t n_visible = n_visible_dev ? (int64_t)*n_visible_dev : n_visible_arg;
     // a block of kInstThreads / 4 threads covers kInstThreads points, four consecutive ones per thread
     // (one 16-byte load when the keys carry the count)
     __shared__ unsigned s_w[kInstThreads / 4 / 32];
@@ -482,16 +499,18 @@ constexpr unsigned kTileKeyBits = 24;
 constexpr uint32_t kTileKeyMask = (1u << kTileKeyBits) - 1u;
 
 // One (tile key, point id) pair per touched tile, row-major over the point's bounds, points in depth
-// order (src/bilinear/kernels.cu:198-220).  CODED (bilinear, 8x8 tiles): bounds and footprint origin are
-// recomputed from the record's screen position with the expressions of the projection pass (same
-// inputs, same operations, hence the same bounds), so that one 8-byte gather serves both.
+// order (src/bilinear/kernels.cu:198-220).  CODED (bilinear, 8x8 tiles): bounds and footprint origin come
+// from the packed word the projection pass left per point (see pack_quad), a 4-byte gather.
 template <bool CODED>
 __global__ void __launch_bounds__(kInstThreads) emit_instances_kernel(const uint32_t* __restrict__ sorted_ids,
-                                                                      const uint2* __restrict__ bounds, const PointRec* __restrict__ rec,
-                                                                      int64_t n_visible, const unsigned* __restrict__ block_base, int gw, int gh,
+                                                                      const uint2* __restrict__ bounds, const uint32_t* __restrict__ quad,
+                                                                      int64_t n_visible_arg, const unsigned long long* __restrict__ n_visible_dev,
+                                                                      const unsigned* __restrict__ block_base, int gw,
                                                                       uint32_t* __restrict__ inst_keys,
                                                                       uint32_t* __restrict__ inst_ids) {
     __shared__ unsigned s_scan[kInstThreads / 32 + 1];
+    const int64_t n_visible = n_visible_dev ? (int64_t)*n_visible_dev : n_visible_arg;
+    if ((int64_t)blockIdx.x * kInstThreads >= n_visible) return;
     const int64_t s = (int64_t)blockIdx.x * kInstThreads + threadIdx.x;
     uint32_t id = 0;
     unsigned x0 = 0, x1 = 0, y0 = 0, y1 = 0;
@@ -499,14 +518,14 @@ __global__ void __launch_bounds__(kInstThreads) emit_instances_kernel(const uint
     if (s < n_visible) {
         id = checked_point(__ldg(sorted_ids + s));
         if (CODED) {
-            const float2 a = __ldg(reinterpret_cast<const float2*>(rec + id));
-            constexpr float itf = 0.125f;
-            x0 = min((unsigned)gw, (unsigned)max(0, __float2int_rd((a.x - 0.5f) * itf)));
-            x1 = min((unsigned)gw, (unsigned)max(0, __float2int_ru((a.x + 0.5f) * itf)));
-            y0 = min((unsigned)gh, (unsigned)max(0, __float2int_rd((a.y - 0.5f) * itf)));
-            y1 = min((unsigned)gh, (unsigned)max(0, __float2int_ru((a.y + 0.5f) * itf)));
-            qx = __float2int_rd(a.x - 0.5f);
-            qy = __float2int_rd(a.y - 0.5f);
+            // the tile bounds follow from the footprint origin: first tile = floor(origin / 8), never below 0
+            const uint32_t q = __ldg(quad + id);
+            qx = (int)(q & 0x7FFFu) - 1;
+            qy = (int)((q >> 16) & 0x7FFFu) - 1;
+            x0 = qx < 0 ? 0u : (unsigned)qx >> 3;
+            y0 = qy < 0 ? 0u : (unsigned)qy >> 3;
+            x1 = x0 + 1u + ((q >> 15) & 1u);
+            y1 = y0 + 1u + (q >> 31);
         } else {
             const uint2 b = __ldg(bounds + id);
             x0 = b.x & 0xffffu; x1 = b.x >> 16; y0 = b.y & 0xffffu; y1 = b.y >> 16;
@@ -530,9 +549,11 @@ __global__ void __launch_bounds__(kInstThreads) emit_instances_kernel(const uint
 }
 
 // Run boundaries of the sorted tile keys -> [first, last+1) per tile (src/bilinear/kernels.cu:222-239).
-__global__ void __launch_bounds__(256) tile_ranges_kernel(const uint32_t* __restrict__ keys, int64_t n_instances,
+__global__ void __launch_bounds__(256) tile_ranges_kernel(const uint32_t* __restrict__ keys, int64_t n_instances_arg,
+                                                          const unsigned long long* __restrict__ n_instances_dev,
                                                           uint2* __restrict__ ranges) {
     constexpr int kPer = 8;
+    const int64_t n_instances = n_instances_dev ? (int64_t)*n_instances_dev : n_instances_arg;
     const int64_t first = ((int64_t)blockIdx.x * 256 + threadIdx.x) * kPer;
     if (first >= n_instances) return;
     uint32_t prev = first > 0 ? __ldg(keys + first - 1) & kTileKeyMask : 0u;
@@ -2495,6 +2516,7 @@ __global__ void __launch_bounds__(kPreThreads) preprocess_backward_kernel(
 struct PointBlob {
     PointRec* rec;
     uint2* bounds;
+    uint32_t* quad;                       // warp blend: packed footprint origin per point (see pack_quad)
     float4* conic;
     unsigned* block_visible;              // survivors per chunk of kPreThreads points
     unsigned* group_visible;              // per group of 4 chunks; scanned in place
@@ -2517,6 +2539,7 @@ PointBlob carve_point_blob(void* p, int64_t n, int mode) {
     const int64_t nb = ceil_div<int64_t>(n > 0 ? n : 1, kPreThreads);
     b.rec = c.take<PointRec>(n);
     b.bounds = c.take<uint2>(n);
+    b.quad = c.take<uint32_t>(mode == INPC_MODE_BILINEAR ? n : 0);
     b.conic = mode == INPC_MODE_GAUSSIAN ? c.take<float4>(n) : nullptr;
     b.block_visible = c.take<unsigned>(nb);
     b.group_visible = c.take<unsigned>(ceil_div<int64_t>(nb, 4));
@@ -2604,6 +2627,17 @@ int tile_result_buffer(int64_t n_instances, int n_tiles) {
 }
 
 // One event per host thread and device: an event belongs to the device that was current when it was made.
+// Instance capacity the blobs of `st` were carved for, and which ping-pong buffer holds the tile-sorted lists.
+int64_t instance_capacity(const inpc_raster_state* st) { return st->deferred_counts ? 4 * st->n_points : st->n_instances; }
+int tile_buffer_of(const inpc_raster_state* st, int n_tiles) {
+    if (st->deferred_counts) return sort_pass_count(bit_length((uint32_t)(n_tiles - 1))) & 1;
+    return tile_result_buffer(st->n_instances, n_tiles);
+}
+int depth_buffer_of(const inpc_raster_state* st) {
+    if (st->deferred_counts) return sort_pass_count(st->depth_key_bits) & 1;
+    return depth_result_buffer(st->n_visible, st->depth_key_bits);
+}
+
 cudaEvent_t counters_event() {
     static thread_local cudaEvent_t events[kMaxDevices] = {nullptr};
     int dev = 0;
@@ -2624,6 +2658,10 @@ int check_view(const inpc_view* v, int tile_size, int mode, int64_t n) {
     if (tile_size != 8 && tile_size != 16) { set_error("tile_size must be 8 or 16, got %d", tile_size); return INPC_E_INVALID; }
     if (v->width <= 0 || v->height <= 0 || v->width > 65535 * tile_size || v->height > 65535 * tile_size) {
         set_error("image size %dx%d out of range", v->width, v->height);
+        return INPC_E_INVALID;
+    }
+    if (mode == INPC_MODE_BILINEAR && tile_size == 8 && (v->width > kMaxCodedSide || v->height > kMaxCodedSide)) {
+        set_error("image size %dx%d exceeds the %d pixels per side of the 8x8-tile bilinear path (use tile_size 16)", v->width, v->height, kMaxCodedSide);
         return INPC_E_INVALID;
     }
     // tile indices live in the low kTileKeyBits bits of the instance keys
@@ -2688,13 +2726,36 @@ int run_front(const RasterParams& rp, int64_t n, const float* positions, const v
         if (rc_check != INPC_OK) return rc_check;
     }
 
+    // Bilinear splats touch at most 2x2 tiles, so the warp-blend path sizes everything behind the visibility pass
+    // for 4 n instances and lets the kernels read the two counts from device memory: no host synchronisation at
+    // all (the reference reads both counts back with blocking copies, src/bilinear/forward.cu:86-89).  The other
+    // paths (gaussian splats have no such bound) read the counts back once.
+    const bool deferred = warp_blend && n > 0 && n < ((int64_t)1 << 28);
     int64_t n_visible = 0, n_instances = 0;
     uint32_t key_base = 0;
     int key_bits = 0;
+    const unsigned long long* n_visible_dev = deferred ? pb.counters : nullptr;
+    const unsigned long long* n_instances_dev = deferred ? pb.counters + 1 : nullptr;
     if (n > 0) {
-        unsigned long long* host = pinned_counters();
-        cudaEvent_t ready = counters_event();
-        if (!host || !ready) return cuda_fail(cudaGetLastError(), "cudaHostAlloc / cudaEventCreate (counters)");
+        unsigned long long* host = nullptr;
+        cudaEvent_t ready = nullptr;
+        int pack_count = -1;
+        if (deferred) {
+            // depth keys are offsets from the smallest visible depth's bit pattern: the near and far planes bound them
+            const float lo = rp.v.near_plane > 0.0f ? rp.v.near_plane : 0.0f, hi = rp.v.far_plane > lo ? rp.v.far_plane : lo;
+            uint32_t lo_bits, hi_bits;
+            memcpy(&lo_bits, &lo, 4);
+            memcpy(&hi_bits, &hi, 4);
+            key_bits = rp.v.near_plane > 0.0f ? bit_length(hi_bits - lo_bits) : 32;
+            if (key_bits == 0) key_bits = 1;
+            pack_count = key_bits <= (int)kCountShift ? 1 : 0;
+            n_visible = n;                // capacities from here on
+            n_instances = 4 * n;
+        } else {
+            host = pinned_counters();
+            ready = counters_event();
+            if (!host || !ready) return cuda_fail(cudaGetLastError(), "cudaHostAlloc / cudaEventCreate (counters)");
+        }
         {
             StageScope scope(STAGE_PREPROCESS, stream);
             INPC_CUDA_TRY(cudaMemsetAsync(pb.depth_min, 0xFF, sizeof(unsigned), stream));
@@ -2705,28 +2766,32 @@ int run_front(const RasterParams& rp, int64_t n, const float* positions, const v
             INPC_LAUNCH_CHECK("visibility_count_kernel");
             scan_block_counts_kernel<<<1, kScanThreads, 0, stream>>>(pb.group_visible, pb.group_instances, groups, pb.depth_min, pb.depth_max, pb.counters);
             INPC_LAUNCH_CHECK("scan_block_counts_kernel");
-            INPC_CUDA_TRY(cudaMemcpyAsync(host, pb.counters, 4 * sizeof(unsigned long long), cudaMemcpyDeviceToHost, stream));
-            INPC_CUDA_TRY(cudaEventRecord(ready, stream));
+            if (!deferred) {
+                INPC_CUDA_TRY(cudaMemcpyAsync(host, pb.counters, 4 * sizeof(unsigned long long), cudaMemcpyDeviceToHost, stream));
+                INPC_CUDA_TRY(cudaEventRecord(ready, stream));
+            }
             // the projection pass needs nothing from the host: it runs while the host waits for the counters
             preprocess_kernel<MODE, VARIANT><<<(unsigned)nb, kPreThreads, 0, stream>>>(
                 positions, static_cast<const __half*>(features), opacities, n, rp, pb.block_visible, pb.group_visible, pb.depth_min, pb.depth_max,
-                pb.rec, pb.bounds,
-                pb.conic, pb.keys[0], pb.ids[0], (reinterpret_cast<uintptr_t>(features) & 15u) == 0, status);
+                pb.rec, pb.bounds, warp_blend ? pb.quad : nullptr,
+                pb.conic, pb.keys[0], pb.ids[0], (reinterpret_cast<uintptr_t>(features) & 15u) == 0, pack_count, status);
             INPC_LAUNCH_CHECK("preprocess_kernel");
         }
-        INPC_CUDA_TRY(cudaEventSynchronize(ready));
-        n_visible = (int64_t)host[0];
-        n_instances = (int64_t)host[1];
-        // counts that cannot be: more survivors than points, or (bilinear: at most 2x2 tiles per splat)
-        // more instances than four per survivor, or instances without survivors
-        if (n_visible > n || (n_visible == 0 && n_instances != 0) || (MODE == INPC_MODE_BILINEAR && n_instances > 4 * n_visible)) {
-            set_error("inconsistent counts from the visibility pass: %lld visible of %lld points, %lld instances", (long long)n_visible,
-                      (long long)n, (long long)n_instances);
-            return INPC_E_DEVICE;
-        }
-        if (n_visible > 0) {
-            key_base = (uint32_t)host[2];
-            key_bits = bit_length((uint32_t)host[3] - key_base);
+        if (!deferred) {
+            INPC_CUDA_TRY(cudaEventSynchronize(ready));
+            n_visible = (int64_t)host[0];
+            n_instances = (int64_t)host[1];
+            // counts that cannot be: more survivors than points, or (bilinear: at most 2x2 tiles per splat)
+            // more instances than four per survivor, or instances without survivors
+            if (n_visible > n || (n_visible == 0 && n_instances != 0) || (MODE == INPC_MODE_BILINEAR && n_instances > 4 * n_visible)) {
+                set_error("inconsistent counts from the visibility pass: %lld visible of %lld points, %lld instances", (long long)n_visible,
+                          (long long)n, (long long)n_instances);
+                return INPC_E_DEVICE;
+            }
+            if (n_visible > 0) {
+                key_base = (uint32_t)host[2];
+                key_bits = bit_length((uint32_t)host[3] - key_base);
+            }
         }
     }
     if (n_instances >= ((int64_t)1 << 30)) {
@@ -2744,7 +2809,8 @@ int run_front(const RasterParams& rp, int64_t n, const float* positions, const v
     int rc;
     {
         StageScope scope(STAGE_SORT_DEPTH, stream);
-        rc = sort_pairs(pb.keys[0], pb.keys[1], pb.ids[0], pb.ids[1], n_visible, key_bits, pb.sort_ws, status, &in_alt, stream);
+        rc = deferred ? sort_pairs_device_count(pb.keys[0], pb.keys[1], pb.ids[0], pb.ids[1], n_visible, n_visible_dev, key_bits, pb.sort_ws, status, &in_alt, stream)
+                      : sort_pairs(pb.keys[0], pb.keys[1], pb.ids[0], pb.ids[1], n_visible, key_bits, pb.sort_ws, status, &in_alt, stream);
     }
     if (rc != INPC_OK) return rc;
     const uint32_t* sorted_ids = pb.ids[in_alt];
@@ -2754,23 +2820,25 @@ int run_front(const RasterParams& rp, int64_t n, const float* positions, const v
             StageScope scope(STAGE_INSTANCES, stream);
             // the count of touched tiles rides in the top key bits when the depth offsets left them free
             if (MODE == INPC_MODE_BILINEAR && key_bits <= (int)kCountShift)
-                instance_count_kernel<true><<<(unsigned)ibk, kInstThreads / 4, 0, stream>>>(pb.keys[in_alt], sorted_ids, pb.bounds, n_visible, pb.inst_block_sums);
+                instance_count_kernel<true><<<(unsigned)ibk, kInstThreads / 4, 0, stream>>>(pb.keys[in_alt], sorted_ids, pb.bounds, n_visible, n_visible_dev, pb.inst_block_sums);
             else
-                instance_count_kernel<false><<<(unsigned)ibk, kInstThreads / 4, 0, stream>>>(pb.keys[in_alt], sorted_ids, pb.bounds, n_visible, pb.inst_block_sums);
+                instance_count_kernel<false><<<(unsigned)ibk, kInstThreads / 4, 0, stream>>>(pb.keys[in_alt], sorted_ids, pb.bounds, n_visible, n_visible_dev, pb.inst_block_sums);
             INPC_LAUNCH_CHECK("instance_count_kernel");
             scan_u32_kernel<<<1, kScanThreads, 0, stream>>>(pb.inst_block_sums, ibk);
             INPC_LAUNCH_CHECK("scan_u32_kernel");
             if (warp_blend)
-                emit_instances_kernel<true><<<(unsigned)ibk, kInstThreads, 0, stream>>>(sorted_ids, pb.bounds, pb.rec, n_visible, pb.inst_block_sums, rp.gw, rp.gh, ib.keys[0], ib.ids[0]);
+                emit_instances_kernel<true><<<(unsigned)ibk, kInstThreads, 0, stream>>>(sorted_ids, pb.bounds, pb.quad, n_visible, n_visible_dev, pb.inst_block_sums, rp.gw, ib.keys[0], ib.ids[0]);
             else
-                emit_instances_kernel<false><<<(unsigned)ibk, kInstThreads, 0, stream>>>(sorted_ids, pb.bounds, pb.rec, n_visible, pb.inst_block_sums, rp.gw, rp.gh, ib.keys[0], ib.ids[0]);
+                emit_instances_kernel<false><<<(unsigned)ibk, kInstThreads, 0, stream>>>(sorted_ids, pb.bounds, nullptr, n_visible, n_visible_dev, pb.inst_block_sums, rp.gw, ib.keys[0], ib.ids[0]);
             INPC_LAUNCH_CHECK("emit_instances_kernel");
         }
         StageScope scope(STAGE_SORT_TILE, stream);
         int t_alt = 0;
-        rc = sort_pairs(ib.keys[0], ib.keys[1], ib.ids[0], ib.ids[1], n_instances, bit_length((uint32_t)(n_tiles - 1)), ib.sort_ws, status, &t_alt, stream);
+        const int tile_bits = bit_length((uint32_t)(n_tiles - 1));
+        rc = deferred ? sort_pairs_device_count(ib.keys[0], ib.keys[1], ib.ids[0], ib.ids[1], n_instances, n_instances_dev, tile_bits, ib.sort_ws, status, &t_alt, stream)
+                      : sort_pairs(ib.keys[0], ib.keys[1], ib.ids[0], ib.ids[1], n_instances, tile_bits, ib.sort_ws, status, &t_alt, stream);
         if (rc != INPC_OK) return rc;
-        tile_ranges_kernel<<<(unsigned)ceil_div<int64_t>(n_instances, 256 * 8), 256, 0, stream>>>(ib.keys[t_alt], n_instances, ib.ranges);
+        tile_ranges_kernel<<<(unsigned)ceil_div<int64_t>(n_instances, 256 * 8), 256, 0, stream>>>(ib.keys[t_alt], n_instances, n_instances_dev, ib.ranges);
         INPC_LAUNCH_CHECK("tile_ranges_kernel");
     }
     if (warp_blend) {
@@ -2790,14 +2858,14 @@ int run_front(const RasterParams& rp, int64_t n, const float* positions, const v
     st->point_blob = pblob;
     st->instance_blob = iblob;
     st->n_points = n;
-    st->n_visible = n_visible;
-    st->n_instances = n_instances;
+    st->n_visible = deferred ? -1 : n_visible;       // -1: still on the device, see inpc_raster_resolve
+    st->n_instances = deferred ? -1 : n_instances;
     st->tile_size = rp.tile;
     st->mode = MODE;
     st->depth_key_base = key_base;
     st->depth_key_bits = key_bits;
     st->channels = VARIANT == VAR_ROWS ? 4 * c4 : 4;
-    st->reserved = 0;
+    st->deferred_counts = deferred ? 1 : 0;
     *pb_out = pb;
     *ib_out = ib;
     return INPC_OK;
@@ -2942,11 +3010,11 @@ int launch_gaussian_forward(const RasterParams& rp, const PointBlob& pb, const I
 }
 
 template <int KIND>
-int launch_blend_forward(int mode, const RasterParams& rp, const PointBlob& pb, const InstanceBlob& ib, int64_t n_instances,
+int launch_blend_forward(int mode, const RasterParams& rp, const PointBlob& pb, const InstanceBlob& ib, const inpc_raster_state* st,
                          float* image, float* depth, float* alpha, float* blending_weights, float threshold,
                          cudaStream_t stream) {
     const int n_tiles = rp.gw * rp.gh;
-    const int t_alt = tile_result_buffer(n_instances, n_tiles);
+    const int t_alt = tile_buffer_of(st, n_tiles);
     const uint32_t* ids = ib.ids[t_alt];
     StageScope scope(STAGE_BLEND_FWD, stream);
     if (mode == INPC_MODE_BILINEAR) {
@@ -3027,7 +3095,7 @@ int rows_forward(int tile_size, const inpc_view* view, int64_t n, const float* p
     int rc = run_front<INPC_MODE_BILINEAR, VAR_ROWS>(rp, n, positions, nullptr, opacities, alloc_point, alloc_instance, alloc_user, state,
                                                      KIND == BLEND_INFER, &pb, &ib, stream, KIND == BLEND_INFER ? "inpc_render_rows" : "inpc_rasterize_rows_forward", channels / 4);
     if (rc != INPC_OK) return rc;
-    const uint32_t* ids = ib.ids[tile_result_buffer(state->n_instances, rp.gw * rp.gh)];
+    const uint32_t* ids = ib.ids[tile_buffer_of(state, rp.gw * rp.gh)];
     {
         StageScope scope(STAGE_BLEND_FWD, stream);
         rc = dispatch_rows(tile_size, channels, [&](auto t, auto c4) {
@@ -3063,7 +3131,7 @@ extern "C" int inpc_rasterize_forward(int mode, int tile_size, const inpc_view* 
     else
         rc = run_front<INPC_MODE_GAUSSIAN, VAR_TRAIN>(rp, n, positions, features, opacities, alloc_point, alloc_instance, alloc_user, state, false, &pb, &ib, stream, "inpc_rasterize_forward");
     if (rc != INPC_OK) return rc;
-    rc = launch_blend_forward<BLEND_TRAIN>(mode, rp, pb, ib, state->n_instances, image, nullptr, alpha, blending_weights, kTrainGaussThreshold, stream);
+    rc = launch_blend_forward<BLEND_TRAIN>(mode, rp, pb, ib, state, image, nullptr, alpha, blending_weights, kTrainGaussThreshold, stream);
     return rc != INPC_OK ? rc : end_index_checks(stream);
 }
 
@@ -3087,8 +3155,8 @@ extern "C" int inpc_rasterize_backward(const inpc_raster_state* state, const inp
     const RasterParams rp = make_params(view, state->tile_size, 0.0f, 3.0f, nullptr);
     const int n_tiles = rp.gw * rp.gh;
     const PointBlob pb = carve_point_blob(state->point_blob, n, state->mode);
-    const InstanceBlob ib = carve_instance_blob(state->instance_blob, state->n_instances, n_tiles, state->tile_size, state->mode, false);
-    const uint32_t* ids = ib.ids[tile_result_buffer(state->n_instances, n_tiles)];
+    const InstanceBlob ib = carve_instance_blob(state->instance_blob, instance_capacity(state), n_tiles, state->tile_size, state->mode, false);
+    const uint32_t* ids = ib.ids[tile_buffer_of(state, n_tiles)];
     INPC_CUDA_TRY(cudaMemsetAsync(grad_features_view, 0, sizeof(float4) * (size_t)n, stream));
     INPC_CUDA_TRY(cudaMemsetAsync(grad_opacities, 0, sizeof(float) * (size_t)n, stream));
     float4* gfv = reinterpret_cast<float4*>(grad_features_view);
@@ -3096,7 +3164,7 @@ extern "C" int inpc_rasterize_backward(const inpc_raster_state* state, const inp
     {
         StageScope scope(STAGE_BLEND_BWD, stream);
         if (state->mode == INPC_MODE_BILINEAR) {
-            rc = rp.tile == 8 ? launch_bilinear_warp_backward(rp, pb, ib, tile_result_buffer(state->n_instances, n_tiles), grad_image, grad_alpha, image, alpha, gfv, grad_opacities, stream)
+            rc = rp.tile == 8 ? launch_bilinear_warp_backward(rp, pb, ib, tile_buffer_of(state, n_tiles), grad_image, grad_alpha, image, alpha, gfv, grad_opacities, stream)
                               : launch_bilinear_backward<16>(rp, pb, ib, ids, grad_image, grad_alpha, image, alpha, gfv, grad_opacities, stream);
             if (rc != INPC_OK) return rc;
         } else {
@@ -3137,7 +3205,7 @@ extern "C" int inpc_render(int mode, int tile_size, const inpc_view* view, int64
     if (rc != INPC_OK) return rc;
     // runtime cut-off exp(-cutoff^2/2): src/gaussian/inference.cu:171
     const float threshold = expf(-0.5f * sigma_cutoff * sigma_cutoff);
-    rc = launch_blend_forward<BLEND_INFER>(mode, rp, pb, ib, st.n_instances, image, depth, alpha, nullptr, threshold, stream);
+    rc = launch_blend_forward<BLEND_INFER>(mode, rp, pb, ib, &st, image, depth, alpha, nullptr, threshold, stream);
     return rc != INPC_OK ? rc : end_index_checks(stream);
 }
 
@@ -3163,7 +3231,7 @@ extern "C" int inpc_render_preextracted(int mode, int tile_size, const inpc_view
         rc = run_front<INPC_MODE_GAUSSIAN, VAR_PREEXTRACTED>(rp, n, positions, features, opacities, alloc_point, alloc_instance, alloc_user, &st, true, &pb, &ib, stream, "inpc_render_preextracted");
     if (rc != INPC_OK) return rc;
     const float threshold = expf(-0.5f * sigma_cutoff * sigma_cutoff);
-    rc = launch_blend_forward<BLEND_INFER>(mode, rp, pb, ib, st.n_instances, image, depth, alpha, nullptr, threshold, stream);
+    rc = launch_blend_forward<BLEND_INFER>(mode, rp, pb, ib, &st, image, depth, alpha, nullptr, threshold, stream);
     return rc != INPC_OK ? rc : end_index_checks(stream);
 }
 
@@ -3231,8 +3299,8 @@ extern "C" int inpc_rasterize_rows_backward(const inpc_raster_state* state, cons
     const RasterParams rp = make_params(view, state->tile_size, 0.0f, 3.0f, nullptr);
     const int n_tiles = rp.gw * rp.gh;
     const PointBlob pb = carve_point_blob(state->point_blob, n, state->mode);
-    const InstanceBlob ib = carve_instance_blob(state->instance_blob, state->n_instances, n_tiles, state->tile_size, state->mode, false, channels / 4, true);
-    const uint32_t* ids = ib.ids[tile_result_buffer(state->n_instances, n_tiles)];
+    const InstanceBlob ib = carve_instance_blob(state->instance_blob, instance_capacity(state), n_tiles, state->tile_size, state->mode, false, channels / 4, true);
+    const uint32_t* ids = ib.ids[tile_buffer_of(state, n_tiles)];
     INPC_CUDA_TRY(cudaMemsetAsync(grad_features, 0, sizeof(float) * (size_t)n * channels, stream));
     INPC_CUDA_TRY(cudaMemsetAsync(grad_opacities, 0, sizeof(float) * (size_t)n, stream));
     rc = begin_index_checks(n, stream);
@@ -3245,6 +3313,26 @@ extern "C" int inpc_rasterize_rows_backward(const inpc_raster_state* state, cons
         });
     }
     return rc != INPC_OK ? rc : end_index_checks(stream);
+}
+
+extern "C" int inpc_raster_resolve(inpc_raster_state* state, void* stream_) {
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    if (!state) { set_error("inpc_raster_resolve: null state"); return INPC_E_INVALID; }
+    if (!state->deferred_counts || state->n_points == 0) return INPC_OK;
+    if (!state->point_blob) { set_error("inpc_raster_resolve: state without a point blob"); return INPC_E_INVALID; }
+    const PointBlob pb = carve_point_blob(state->point_blob, state->n_points, state->mode);
+    unsigned long long host[4];
+    INPC_CUDA_TRY(cudaMemcpyAsync(host, pb.counters, sizeof(host), cudaMemcpyDeviceToHost, stream));
+    INPC_CUDA_TRY(cudaStreamSynchronize(stream));
+    state->n_visible = (int64_t)host[0];
+    state->n_instances = (int64_t)host[1];
+    state->depth_key_base = state->n_visible > 0 ? (uint32_t)host[2] : 0u;
+    if (state->n_visible > state->n_points || state->n_instances > 4 * state->n_visible) {
+        set_error("inconsistent counts from the visibility pass: %lld visible of %lld points, %lld instances", (long long)state->n_visible,
+                  (long long)state->n_points, (long long)state->n_instances);
+        return INPC_E_DEVICE;
+    }
+    return INPC_OK;
 }
 
 namespace inpc_debug {
@@ -3279,9 +3367,10 @@ extern "C" int inpc_raster_debug_copy(const inpc_raster_state* state, const inpc
     const int gw = ceil_div(view->width, state->tile_size), gh = ceil_div(view->height, state->tile_size);
     const int n_tiles = gw * gh;
     const PointBlob pb = carve_point_blob(state->point_blob, state->n_points, state->mode);
-    const InstanceBlob ib = carve_instance_blob(state->instance_blob, state->n_instances, n_tiles, state->tile_size, state->mode, false);
-    const int d = depth_result_buffer(state->n_visible, state->depth_key_bits);
-    const int ti = tile_result_buffer(state->n_instances, n_tiles);
+    if (state->n_visible < 0 || state->n_instances < 0) { set_error("inpc_raster_debug_copy: the counts of this state are still on the device; call inpc_raster_resolve first"); return INPC_E_INVALID; }
+    const InstanceBlob ib = carve_instance_blob(state->instance_blob, instance_capacity(state), n_tiles, state->tile_size, state->mode, false);
+    const int d = depth_buffer_of(state);
+    const int ti = tile_buffer_of(state, n_tiles);
     switch (which) {
         case 0: INPC_CUDA_TRY(cudaMemcpyAsync(dst, pb.ids[d], 4 * (size_t)state->n_visible, cudaMemcpyDeviceToDevice, stream)); break;
         case 1:   // the sort works on offsets from the smallest depth key: add the base back

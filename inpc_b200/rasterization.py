@@ -126,9 +126,16 @@ def _check(status: int, blobs: _Blobs | None = None) -> None:
     _cabi.check(status)
 
 
+def resolve_counts(state) -> None:
+    """Fills in `n_visible` / `n_instances` of a state whose forward left them on the device (one small copy and a
+    synchronisation of the current stream)."""
+    _check(_cabi.lib().inpc_raster_resolve(C.byref(state), _stream()))
+
+
 def forward_with_state(positions: torch.Tensor, features: torch.Tensor, opacities: torch.Tensor,
-                       rasterizer_settings: RasterizerSettings, tile_size: int = DEFAULT_TILE_SIZE):
-    """Training forward without autograd; also returns the C state and the scratch blobs."""
+                       rasterizer_settings: RasterizerSettings, tile_size: int = DEFAULT_TILE_SIZE, resolve: bool = True):
+    """Training forward without autograd; also returns the C state and the scratch blobs.  `resolve` fetches the
+    visible / instance counts (a host synchronisation the autograd path does without)."""
     positions = _cuda_f32(positions, "positions")
     features = _cuda_f16(features, "features")
     opacities = _cuda_f32(opacities, "opacities")
@@ -152,6 +159,8 @@ def forward_with_state(positions: torch.Tensor, features: torch.Tensor, opacitie
             s.mode.value, int(tile_size), C.byref(view.c), n, _ptr(positions), _ptr(features), _ptr(opacities),
             _ptr(image), _ptr(alpha), _ptr(blending_weights), blobs.cb_point, blobs.cb_instance, None,
             C.byref(state), _stream()), blobs)
+        if resolve:
+            resolve_counts(state)
     return image, alpha, blending_weights, state, blobs, (positions, opacities)
 
 
@@ -160,7 +169,7 @@ class _Rasterize(torch.autograd.Function):
     def forward(ctx: Any, positions: torch.Tensor, features: torch.Tensor, opacities: torch.Tensor,
                 rasterizer_settings: RasterizerSettings, tile_size: int = DEFAULT_TILE_SIZE):
         image, alpha, blending_weights, state, blobs, (positions, opacities) = forward_with_state(
-            positions, features, opacities, rasterizer_settings, tile_size)
+            positions, features, opacities, rasterizer_settings, tile_size, resolve=False)
         ctx.save_for_backward(image, alpha, positions, opacities, blobs.point, blobs.instance)
         ctx.rasterizer_settings = rasterizer_settings
         ctx.raster_state = state
