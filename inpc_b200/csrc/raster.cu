@@ -1194,7 +1194,7 @@ constexpr size_t backward_smem_bytes() {
 // and its order are those of a plain front-to-back loop per pixel.
 //
 // (3) Segments.  Front-to-back compositing is associative: (C, T) o (C', T') = (C + T C', T T').  A
-// tile's list is cut into segments of kSegmentLength instances and every (tile half, segment) is one
+// tile's list is cut into a first segment of kFirstSegment instances and later ones of kLaterSegment, and every (tile half, segment) is one
 // item, so a tile with 100x the average load does not set the critical path.  Pass FIRST blends
 // segment 0 of every tile exactly; the pixels that dense clusters hit stop there.  Pass PRODUCT
 // computes, for the later segments, the per-pixel product of (1 - alpha) over the segment, starting
@@ -1215,7 +1215,11 @@ constexpr size_t backward_smem_bytes() {
 constexpr int kWarpBlendWarps = 8;        // warps per block; every warp works on items of its own
 constexpr int kQueueCap = 256;            // ring of candidate point ids per warp: >= 31 left over + 128 of one filter step
 constexpr int kFilterKeys = 4;            // keys per lane and filter step
-constexpr unsigned kSegmentLength = 1024;   // instances per segment (512, 2048 and 4096 measured within 5 % of it)
+// Measured on B200 (2^23 clustered samples, 1237x822; forward / backward stage in microseconds): uniform segments of
+// 256: 815 / 539, 512: 597 / 401, 1024: 494 / 339, 2048: 464 / 325, 4096: 507 / 354 (the first pass is bound by its
+// longest item), 8192: 566 / 376; first 512 + later 2048: 478 / 300, first 1024 + later 4096: 471 / 308.
+constexpr unsigned kFirstSegment = 1024;    // instances in a tile's first segment
+constexpr unsigned kLaterSegment = 4096;    // ... and in every later one
 constexpr int kBatchFragments = 128;      // 32 instances x 4 fragments
 enum { PASS_FIRST = 0, PASS_PRODUCT = 1, PASS_REST = 2 };
 
@@ -1228,7 +1232,9 @@ __device__ __forceinline__ unsigned long long key_pixels(unsigned code) {
     return cy == 0u ? two >> 8 : two << (8u * (cy - 1u));                // rows cy - 1 and cy, clipped likewise
 }
 
-__device__ __forceinline__ unsigned warp_segments(unsigned len) { return max(1u, ceil_div(len, kSegmentLength)); }
+__device__ __forceinline__ unsigned warp_segments(unsigned len) {
+    return len <= kFirstSegment ? 1u : 1u + ceil_div(len - kFirstSegment, kLaterSegment);
+}
 
 // Work lists of the warp blend, step 1 (one block): tile_first[t] = number of segments of the tiles before t
 // (empty tiles have none), tile_rank[t] = number of non-empty tiles before t, counts[0] = non-empty tiles,
@@ -1272,20 +1278,42 @@ __global__ void __launch_bounds__(kScanThreads) warp_items_scan_kernel(const uin
     if (threadIdx.x == 0) { counts[0] = run_tiles; counts[1] = run_seg - run_tiles; }
 }
 
-// Step 2 (one thread per tile): list0 = the non-empty tiles (their segment 0), list1 = (tile, segment) of every
-// later segment.
-__global__ void __launch_bounds__(256) warp_items_fill_kernel(const uint2* __restrict__ ranges, int n_tiles,
-                                                             const uint32_t* __restrict__ tile_first, const uint32_t* __restrict__ tile_rank,
-                                                             uint32_t* __restrict__ list0, uint2* __restrict__ list1) {
+// Everything a warp needs to know about a (tile, segment), in one 32-byte record: the blend kernels read it with
+// two 16-byte loads, one item ahead of the one they work on, instead of chasing tile -> range -> first segment.
+struct __align__(16) WarpItem {
+    uint32_t tile, seg;       // which tile, which of its segments
+    uint32_t begin, end;      // instance range of the segment
+    uint32_t first, n_seg;    // slot of the tile's segment 0 in the per-segment arrays; segments of the tile
+    uint32_t pad0, pad1;
+};
+
+__device__ __forceinline__ WarpItem load_item(const WarpItem* p) {
+    const uint4 a = __ldg(reinterpret_cast<const uint4*>(p)), b = __ldg(reinterpret_cast<const uint4*>(p) + 1);
+    WarpItem w;
+    w.tile = a.x; w.seg = a.y; w.begin = a.z; w.end = a.w; w.first = b.x; w.n_seg = b.y; w.pad0 = 0; w.pad1 = 0;
+    return w;
+}
+
+// Step 2 (one thread per tile): items0 = segment 0 of the non-empty tiles, items1 = every later segment, tile by tile.
+__global__ void __launch_bounds__(256) warp_items_fill_kernel(const uint2* __restrict__ ranges, int n_tiles, const uint32_t* __restrict__ tile_first,
+                                                             const uint32_t* __restrict__ tile_rank, WarpItem* __restrict__ items0,
+                                                             WarpItem* __restrict__ items1) {
     const int t = blockIdx.x * 256 + threadIdx.x;
     if (t >= n_tiles) return;
     const uint2 r = __ldg(ranges + t);
     if (r.y <= r.x) return;
-    const unsigned ns = warp_segments(r.y - r.x);
-    const unsigned rank = tile_rank[t], first = tile_first[t];
-    list0[rank] = (uint32_t)t;
-    // later segments: position = segments before this tile minus tiles before it
-    for (unsigned s = 1; s < ns; ++s) list1[first - rank + s - 1u] = make_uint2((uint32_t)t, s);
+    WarpItem w;
+    w.tile = (uint32_t)t; w.first = tile_first[t]; w.n_seg = warp_segments(r.y - r.x); w.pad0 = 0; w.pad1 = 0;
+    const unsigned rank = tile_rank[t];
+    for (unsigned s = 0; s < w.n_seg; ++s) {
+        w.seg = s;
+        w.begin = s == 0 ? r.x : r.x + kFirstSegment + (s - 1u) * kLaterSegment;
+        w.end = min(r.y, w.begin + (s == 0 ? kFirstSegment : kLaterSegment));
+        // later segments: position = segments before this tile minus tiles before it
+        WarpItem* dst = s == 0 ? items0 + rank : items1 + (w.first - rank + s - 1u);
+        reinterpret_cast<uint4*>(dst)[0] = make_uint4(w.tile, w.seg, w.begin, w.end);
+        reinterpret_cast<uint4*>(dst)[1] = make_uint4(w.first, w.n_seg, 0u, 0u);
+    }
 }
 
 // Shared memory of one warp of the forward passes.
@@ -1302,14 +1330,13 @@ struct WarpForwardSmem {
 
 template <int PASS, int KIND>
 __global__ void __launch_bounds__(kWarpBlendWarps * 32) blend_bilinear_warp_forward_kernel(
-    const uint32_t* __restrict__ list0, const uint2* __restrict__ list1, const uint32_t* __restrict__ counts, unsigned* __restrict__ ticket,
-    const uint2* __restrict__ ranges, const uint32_t* __restrict__ tile_first, const uint32_t* __restrict__ inst_keys,
+    const WarpItem* __restrict__ items, const uint32_t* __restrict__ counts, unsigned* __restrict__ ticket, const uint32_t* __restrict__ inst_keys,
     const uint32_t* __restrict__ inst_ids, const PointRec* __restrict__ rec, float* __restrict__ seg_T, float4* __restrict__ seg_C,
     float* __restrict__ seg_Z, float* __restrict__ seg_E, float* __restrict__ image, float* __restrict__ depth_image,
-    float* __restrict__ alpha_image, float* __restrict__ blending_weights, uint32_t* __restrict__ kept0, uint32_t* __restrict__ kept1,
+    float* __restrict__ alpha_image, float* __restrict__ blending_weights, uint32_t* kept0, uint32_t* kept1,
     uint32_t* __restrict__ n_kept, int width, int height, int gw) {
     constexpr unsigned kFull = 0xffffffffu;
-    constexpr bool kBlend = PASS != PASS_PRODUCT;               // colours, weights, lists; PRODUCT only multiplies
+    constexpr bool kBlend = PASS != PASS_PRODUCT;               // colours and weights; PRODUCT only multiplies
     constexpr bool kWeights = kBlend && KIND == BLEND_TRAIN;
     constexpr bool kDepth = kBlend && KIND == BLEND_INFER;
     using Smem = WarpForwardSmem<kBlend, kWeights, kDepth>;
@@ -1322,25 +1349,20 @@ __global__ void __launch_bounds__(kWarpBlendWarps * 32) blend_bilinear_warp_forw
     sm.mask[lane] = 0u;   // the masks start at zero and every batch leaves them at zero again
     __syncthreads();
     const unsigned n_items = __ldg(counts + (PASS == PASS_FIRST ? 0 : 1)) * 2u;
-
+    // Items are handed out one at a time through a ticket counter: consecutive items cost about the same (neighbouring
+    // tiles, or consecutive segments of one tile), so a warp that reserved items ahead would sit on work that idle warps
+    // could take (measured: holding two tickets ahead to prefetch the records made every pass 10-70 % slower).
     for (;;) {
         unsigned item = 0;
         if (lane == 0) item = atomicAdd(ticket, 1u);
         item = __shfl_sync(kFull, item, 0);
         if (item >= n_items) break;
-        unsigned tile, seg;
-        if (PASS == PASS_FIRST) { tile = __ldg(list0 + (item >> 1)); seg = 0u; }
-        else { const uint2 d = __ldg(list1 + (item >> 1)); tile = d.x; seg = d.y; }
+        const WarpItem it = load_item(items + (item >> 1));
+        const unsigned tile = it.tile, seg = it.seg, n_seg = it.n_seg, first = it.first;
         const int half = (int)(item & 1u);
-        const uint2 rg_tile = __ldg(ranges + tile);
-        const unsigned n_seg = warp_segments(rg_tile.y - rg_tile.x);
-        if (PASS == PASS_PRODUCT && seg + 1u == n_seg) continue;   // the last segment's product is never needed
-        const unsigned first = __ldg(tile_first + tile);
         const size_t sidx = (size_t)(first + seg) * 2u + half;      // this item's slot in the per-segment arrays
         const size_t sidx0 = (size_t)first * 2u + half;             // segment 0 of the same tile half
-        uint2 rg;
-        rg.x = rg_tile.x + seg * kSegmentLength;
-        rg.y = min(rg_tile.y, rg.x + kSegmentLength);
+        const uint2 rg = make_uint2(it.begin, it.end);
         const int tx = (int)(tile % (unsigned)gw), ty = (int)(tile / (unsigned)gw);
         const int px0 = tx * 8, py0 = ty * 8 + 4 * half;            // first pixel of this half
         const int px = px0 + (int)(lane & 7u), py = py0 + (int)(lane >> 3);
@@ -1360,13 +1382,14 @@ __global__ void __launch_bounds__(kWarpBlendWarps * 32) blend_bilinear_warp_forw
         }
         unsigned done_w = __ballot_sync(kFull, done);   // bit l = pixel of lane l has stopped (warp-uniform)
 
-        // ---- filter: keys are loaded one step ahead of their use
+        uint32_t* kept = half ? kept1 : kept0;
+        // ---- where the instances come from.  FIRST and PRODUCT filter the item's keys (loaded one step ahead of
+        // their use); REST blends the list PRODUCT compacted for this item (a superset of what is still alive at
+        // the true transmittance, see above), ids two batches ahead like the backward pass.
         unsigned pos = rg.x;           // next key to load
-        unsigned step_pos = rg.x;      // first key of the loaded step
         bool loaded = false;
         uint32_t kq[kFilterKeys], iq[kFilterKeys];
         auto load_step = [&]() {
-            step_pos = pos;
 #pragma unroll
             for (int k = 0; k < kFilterKeys; ++k) {
                 const unsigned idx = pos + 32u * k + lane;
@@ -1377,9 +1400,9 @@ __global__ void __launch_bounds__(kWarpBlendWarps * 32) blend_bilinear_warp_forw
             pos = min(pos + 32u * kFilterKeys, rg.y);
             loaded = true;
         };
-        if (pos < rg.y) load_step();
         unsigned q_head = 0, q_tail = 0;
         auto fill = [&]() {
+            if (PASS == PASS_REST) return;
             while (q_tail - q_head < 32u && loaded) {
                 uint32_t ck[kFilterKeys], ci[kFilterKeys];
 #pragma unroll
@@ -1398,13 +1421,25 @@ __global__ void __launch_bounds__(kWarpBlendWarps * 32) blend_bilinear_warp_forw
             __syncwarp();
         };
         int n_cur = 0, n_nxt = 0;
-        uint32_t id_cur = 0, id_nxt = 0;
+        uint32_t id_cur = 0, id_nxt = 0, id_far = 0;
         float4 a_cur, f_cur, a_nxt, f_nxt;
         a_cur = f_cur = a_nxt = f_nxt = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (PASS == PASS_REST) {
+            q_tail = n_kept[sidx];     // length of PRODUCT's list; the list itself starts at kept[rg.x]
+            if (lane < q_tail) id_far = kept[rg.x + lane];
+        } else if (pos < rg.y) {
+            load_step();
+        }
         auto gather_next = [&]() {
             n_nxt = (int)min(32u, q_tail - q_head);
+            if (PASS == PASS_REST) {
+                id_nxt = id_far;
+                if (q_head + 32u + lane < q_tail) id_far = kept[rg.x + q_head + 32u + lane];
+            } else if ((int)lane < n_nxt) {
+                id_nxt = sm.queue[(q_head + lane) & (kQueueCap - 1)];
+            }
             if ((int)lane < n_nxt) {
-                id_nxt = checked_point(sm.queue[(q_head + lane) & (kQueueCap - 1)]);
+                id_nxt = checked_point(id_nxt);
                 const float4* p = reinterpret_cast<const float4*>(rec + id_nxt);
                 a_nxt = __ldg(p);
                 if (kBlend) f_nxt = __ldg(p + 1);
@@ -1413,13 +1448,13 @@ __global__ void __launch_bounds__(kWarpBlendWarps * 32) blend_bilinear_warp_forw
         };
         fill();
         gather_next();
-        uint32_t* kept = half ? kept1 : kept0;
         unsigned n_out = 0;
         while (n_nxt > 0) {
             n_cur = n_nxt; id_cur = id_nxt; a_cur = a_nxt; f_cur = f_nxt;
             fill();
             gather_next();
-            if (kWeights) {
+            if (PASS != PASS_REST) {
+                // the list this pass blended: FIRST's goes to the backward pass, PRODUCT's to REST
                 if ((int)lane < n_cur) kept[rg.x + n_out + lane] = id_cur;
                 n_out += (unsigned)n_cur;
             }
@@ -1440,6 +1475,14 @@ __global__ void __launch_bounds__(kWarpBlendWarps * 32) blend_bilinear_warp_forw
                                 !((done_w >> (p & 31)) & 1u);
                 pix[c] = ok ? p : -1;
                 if (ok) atomicOr(sm.mask + p, 1u << lane);
+            }
+            if (PASS == PASS_REST && kWeights) {
+                // what is still alive at the true transmittance goes on to the backward pass; written in place, behind
+                // the part of PRODUCT's list that has been read already
+                const bool live = (pix[0] & pix[1] & pix[2] & pix[3]) >= 0;
+                const unsigned b = __ballot_sync(kFull, live);
+                if (live) kept[rg.x + n_out + __popc(b & lt_mask)] = id_cur;
+                n_out += __popc(b);
             }
             __syncwarp();
             // ---- per-pixel order: offset of every pixel's list, slot of every fragment
@@ -1462,23 +1505,39 @@ __global__ void __launch_bounds__(kWarpBlendWarps * 32) blend_bilinear_warp_forw
             __syncwarp();
             // ---- every lane runs down the list of its own pixel, front to back
             if (my_mask) sm.mask[lane] = 0u;
-            for (unsigned k = off; k < off + cnt; ++k) {
-                if (done) {
-                    if (kWeights) sm.frag_seen[k] = 0.0f;
-                    continue;
+            // The chain from one fragment to the next is one multiply (the transmittance); everything else of a step
+            // hangs off it.  The steps are therefore written without branches -- a stopped pixel selects its old
+            // values -- and in chunks whose loads are issued together, so that consecutive steps overlap in the
+            // pipeline instead of each waiting for its own shared-memory loads.
+            constexpr int kChunk = 4;
+            for (unsigned k0 = off; k0 < off + cnt; k0 += kChunk) {
+                float a[kChunk];
+                float4 f[kChunk];
+                float zd[kChunk];
+#pragma unroll
+                for (int u = 0; u < kChunk; ++u) {
+                    const unsigned k = min(k0 + u, off + cnt - 1u);   // the tail repeats the last slot: masked out below
+                    a[u] = sm.frag_alpha[k];
+                    if (kBlend) f[u] = sm.frag_feat[k];
+                    if (kDepth) zd[u] = sm.frag_depth[k];
                 }
-                const float a = sm.frag_alpha[k];
-                if (kBlend) {
-                    const float4 f = sm.frag_feat[k];
-                    const float bw = Tr * a;
-                    if (kWeights) sm.frag_seen[k] = Tr;
-                    C0 += bw * f.x; C1 += bw * f.y; C2 += bw * f.z; C3 += bw * f.w;
-                    if (kDepth) Z += bw * sm.frag_depth[k];
-                    Tr *= 1.0f - a;
-                    if (Tr < kTransmittanceEps) done = true;
-                } else {
-                    Tr *= 1.0f - a;
-                    if (T0 * Tr < kTransmittanceEps) done = true;
+#pragma unroll
+                for (int u = 0; u < kChunk; ++u) {
+                    const bool live = !done && k0 + u < off + cnt;
+                    if (kBlend) {
+                        const float bw = Tr * a[u];
+                        if (kWeights && k0 + u < off + cnt) sm.frag_seen[k0 + u] = live ? Tr : 0.0f;
+                        C0 = live ? C0 + bw * f[u].x : C0;
+                        C1 = live ? C1 + bw * f[u].y : C1;
+                        C2 = live ? C2 + bw * f[u].z : C2;
+                        C3 = live ? C3 + bw * f[u].w : C3;
+                        if (kDepth) Z = live ? Z + bw * zd[u] : Z;
+                        Tr = live ? Tr * (1.0f - a[u]) : Tr;
+                        done = done || Tr < kTransmittanceEps;
+                    } else {
+                        Tr = live ? Tr * (1.0f - a[u]) : Tr;
+                        done = done || T0 * Tr < kTransmittanceEps;
+                    }
                 }
             }
             __syncwarp();
@@ -1499,10 +1558,10 @@ __global__ void __launch_bounds__(kWarpBlendWarps * 32) blend_bilinear_warp_forw
             __syncwarp();
             if (done_w == kFull) break;   // every pixel has stopped: the rest of the list has no effect
         }
-        if (kWeights && lane == 0) n_kept[sidx] = n_out;
+        if ((PASS != PASS_REST || kWeights) && lane == 0) n_kept[sidx] = n_out;
 
         if (PASS == PASS_PRODUCT) {
-            seg_T[sidx * 32 + lane] = Tr;
+            seg_T[sidx * 32 + lane] = Tr;          // this segment's product (Tr started at 1)
             continue;
         }
         const int64_t n_px = (int64_t)width * height;
@@ -1538,18 +1597,16 @@ __global__ void __launch_bounds__(kWarpBlendWarps * 32) blend_bilinear_warp_forw
 
 // Per tile half with several segments, between the PRODUCT and REST passes: seg_T of segment s >= 1 becomes
 // the transmittance at its start = (state behind segment 0) * product of the segments 1 .. s-1.
-__global__ void __launch_bounds__(kWarpBlendWarps * 32) warp_blend_prefix_kernel(const uint32_t* __restrict__ list0, const uint32_t* __restrict__ counts,
-                                                                                 const uint2* __restrict__ ranges,
-                                                                                 const uint32_t* __restrict__ tile_first, float* __restrict__ seg_T) {
+__global__ void __launch_bounds__(kWarpBlendWarps * 32) warp_blend_prefix_kernel(const WarpItem* __restrict__ items0, const uint32_t* __restrict__ counts,
+                                                                                 float* __restrict__ seg_T) {
     const unsigned lane = lane_id();
     const unsigned n_parts = __ldg(counts) * 2u;
     for (unsigned w = blockIdx.x * kWarpBlendWarps + (threadIdx.x >> 5); w < n_parts; w += gridDim.x * kWarpBlendWarps) {
-        const unsigned tile = __ldg(list0 + (w >> 1));
+        const WarpItem it = load_item(items0 + (w >> 1));
         const unsigned half = w & 1u;
-        const uint2 r = __ldg(ranges + tile);
-        const unsigned n_seg = warp_segments(r.y - r.x);
+        const unsigned n_seg = it.n_seg;
         if (n_seg == 1u) continue;
-        const unsigned first = __ldg(tile_first + tile);
+        const unsigned first = it.first;
         float* base = seg_T + ((size_t)first * 2u + half) * 32 + lane;   // segment g of this half: base[g * 64]
         float run = base[0];
         for (unsigned g0 = 1; g0 < n_seg; g0 += 8) {
@@ -1571,18 +1628,16 @@ __global__ void __launch_bounds__(kWarpBlendWarps * 32) warp_blend_prefix_kernel
 // of the first segment that fell below the threshold.
 template <int KIND>
 __global__ void __launch_bounds__(kWarpBlendWarps * 32) warp_blend_combine_kernel(
-    const uint32_t* __restrict__ list0, const uint32_t* __restrict__ counts, const uint2* __restrict__ ranges,
-    const uint32_t* __restrict__ tile_first, float4* __restrict__ seg_C, const float* __restrict__ seg_Z, const float* __restrict__ seg_E,
+    const WarpItem* __restrict__ items0, const uint32_t* __restrict__ counts, float4* __restrict__ seg_C, const float* __restrict__ seg_Z,
+    const float* __restrict__ seg_E,
     float* __restrict__ image, float* __restrict__ depth_image, float* __restrict__ alpha_image, int width, int height, int gw) {
     const unsigned lane = lane_id();
     const unsigned n_parts = __ldg(counts) * 2u;
     for (unsigned w = blockIdx.x * kWarpBlendWarps + (threadIdx.x >> 5); w < n_parts; w += gridDim.x * kWarpBlendWarps) {
-        const unsigned tile = __ldg(list0 + (w >> 1));
+        const WarpItem it = load_item(items0 + (w >> 1));
         const unsigned half = w & 1u;
-        const uint2 r = __ldg(ranges + tile);
-        const unsigned n_seg = warp_segments(r.y - r.x);
+        const unsigned tile = it.tile, n_seg = it.n_seg, first = it.first;
         if (n_seg == 1u) continue;
-        const unsigned first = __ldg(tile_first + tile);
         const int tx = (int)(tile % (unsigned)gw), ty = (int)(tile / (unsigned)gw);
         const int px = tx * 8 + (int)(lane & 7u);
         const int py = ty * 8 + 4 * (int)half + (int)(lane >> 3);
@@ -1639,8 +1694,8 @@ struct WarpBackwardSmem {
 };
 
 __global__ void __launch_bounds__(kWarpBlendWarps * 32) blend_bilinear_warp_backward_kernel(
-    const uint32_t* __restrict__ list0, const uint2* __restrict__ list1, const uint32_t* __restrict__ counts, unsigned* __restrict__ ticket,
-    const uint2* __restrict__ ranges, const uint32_t* __restrict__ tile_first, const uint32_t* __restrict__ kept0,
+    const WarpItem* __restrict__ items0, const WarpItem* __restrict__ items1, const uint32_t* __restrict__ counts,
+    unsigned* __restrict__ ticket, const uint32_t* __restrict__ kept0,
     const uint32_t* __restrict__ kept1, const uint32_t* __restrict__ n_kept, const PointRec* __restrict__ rec,
     const float* __restrict__ seg_T, const float4* __restrict__ seg_C, const float* __restrict__ grad_image,
     const float* __restrict__ grad_alpha, const float* __restrict__ image, const float* __restrict__ alpha_image,
@@ -1656,23 +1711,19 @@ __global__ void __launch_bounds__(kWarpBlendWarps * 32) blend_bilinear_warp_back
     const unsigned n_items = n_first + __ldg(counts + 1) * 2u;
     const unsigned n_rest = n_items - n_first;
 
+    // items one at a time through a ticket counter, the later segments first (they belong to the longest lists)
     for (;;) {
         unsigned item = 0;
         if (lane == 0) item = atomicAdd(ticket, 1u);
         item = __shfl_sync(kFull, item, 0);
         if (item >= n_items) break;
-        // the later segments first: they belong to the longest lists
-        unsigned tile, seg;
-        if (item < n_rest) { const uint2 d = __ldg(list1 + (item >> 1)); tile = d.x; seg = d.y; }
-        else { tile = __ldg(list0 + ((item - n_rest) >> 1)); seg = 0u; }
+        const WarpItem it = load_item(item < n_rest ? items1 + (item >> 1) : items0 + ((item - n_rest) >> 1));
         const int half = (int)((item < n_rest ? item : item - n_rest) & 1u);
-        const unsigned first = __ldg(tile_first + tile);
-        const size_t sidx = (size_t)(first + seg) * 2u + half;
-        const unsigned n_list = __ldg(n_kept + sidx);
+        const unsigned n_list = __ldg(n_kept + (size_t)(it.first + it.seg) * 2u + half);
+        const unsigned tile = it.tile, seg = it.seg, n_seg = it.n_seg;
+        const size_t sidx = (size_t)(it.first + seg) * 2u + half;
         if (n_list == 0u) continue;
-        const uint2 rg_tile = __ldg(ranges + tile);
-        const unsigned n_seg = warp_segments(rg_tile.y - rg_tile.x);
-        const uint32_t* list = (half ? kept1 : kept0) + rg_tile.x + seg * kSegmentLength;
+        const uint32_t* list = (half ? kept1 : kept0) + it.begin;
         const int tx = (int)(tile % (unsigned)gw), ty = (int)(tile / (unsigned)gw);
         const int px0 = tx * 8, py0 = ty * 8 + 4 * half;
         const int px = px0 + (int)(lane & 7u), py = py0 + (int)(lane >> 3);
@@ -1754,25 +1805,36 @@ __global__ void __launch_bounds__(kWarpBlendWarps * 32) blend_bilinear_warp_back
             }
             __syncwarp();
             if (my_mask) sm.mask[lane] = 0u;
-            for (unsigned k = off; k < off + cnt; ++k) {
-                if (done) {
-                    sm.frag_bw[k] = 0.0f;
-                    sm.frag_dalpha[k] = 0.0f;
-                    continue;
+            // branch-free steps in chunks whose loads are issued together (see the forward pass)
+            constexpr int kChunk = 2;
+            for (unsigned k0 = off; k0 < off + cnt; k0 += kChunk) {
+                float a[kChunk], rcp[kChunk];
+                float4 f[kChunk];
+#pragma unroll
+                for (int u = 0; u < kChunk; ++u) {
+                    const unsigned k = min(k0 + u, off + cnt - 1u);
+                    a[u] = sm.frag_alpha[k];
+                    rcp[u] = sm.frag_rcp[k];
+                    f[u] = sm.frag_feat[k];
                 }
-                const float a = sm.frag_alpha[k];
-                const float rcp = sm.frag_rcp[k];
-                const float4 f = sm.frag_feat[k];
-                const float bw = Tr * a;
-                Crun.x += bw * f.x; Crun.y += bw * f.y; Crun.z += bw * f.z; Crun.w += bw * f.w;
-                const float from_features = (Tr * f.x + (Crun.x - Cfin.x) * rcp) * g.x +
-                                            (Tr * f.y + (Crun.y - Cfin.y) * rcp) * g.y +
-                                            (Tr * f.z + (Crun.z - Cfin.z) * rcp) * g.z +
-                                            (Tr * f.w + (Crun.w - Cfin.w) * rcp) * g.w;
-                sm.frag_bw[k] = bw;
-                sm.frag_dalpha[k] = from_features + K * rcp;
-                Tr *= 1.0f - a;
-                if (Tr < kTransmittanceEps) done = true;
+#pragma unroll
+                for (int u = 0; u < kChunk; ++u) {
+                    const bool in_list = k0 + u < off + cnt;
+                    const bool live = !done && in_list;
+                    const float bw = Tr * a[u];
+                    const float4 cr = make_float4(Crun.x + bw * f[u].x, Crun.y + bw * f[u].y, Crun.z + bw * f[u].z, Crun.w + bw * f[u].w);
+                    const float from_features = (Tr * f[u].x + (cr.x - Cfin.x) * rcp[u]) * g.x +
+                                                (Tr * f[u].y + (cr.y - Cfin.y) * rcp[u]) * g.y +
+                                                (Tr * f[u].z + (cr.z - Cfin.z) * rcp[u]) * g.z +
+                                                (Tr * f[u].w + (cr.w - Cfin.w) * rcp[u]) * g.w;
+                    if (in_list) {
+                        sm.frag_bw[k0 + u] = live ? bw : 0.0f;
+                        sm.frag_dalpha[k0 + u] = live ? from_features + K * rcp[u] : 0.0f;
+                    }
+                    Crun = live ? cr : Crun;
+                    Tr = live ? Tr * (1.0f - a[u]) : Tr;
+                    done = done || Tr < kTransmittanceEps;
+                }
             }
             __syncwarp();
             // gradients of every staged instance: its (up to) four fragments in fixed corner order, one vector
@@ -2570,8 +2632,8 @@ struct InstanceBlob {
     float* seg_E;         // warp blend, inference: transmittance at the end of every segment
     int64_t max_segments;
     uint32_t* tile_rank;  // warp blend: non-empty tiles before each tile
-    uint32_t* list0;      // warp blend: the non-empty tiles
-    uint2* list1;         // warp blend: (tile, segment) of every segment behind a tile's first
+    WarpItem* items0;     // warp blend: segment 0 of the non-empty tiles
+    WarpItem* items1;     // warp blend: every segment behind a tile's first
     uint32_t* n_kept;     // warp blend: per item, length of the compacted list the forward pass blended
     void* sort_ws;
     size_t total;
@@ -2596,7 +2658,7 @@ InstanceBlob carve_instance_blob(void* p, int64_t n_instances, int n_tiles, int 
     for (int k = 0; k < 2; ++k) b.keys[k] = c.take<uint32_t>(n_instances);
     for (int k = 0; k < 2; ++k) b.ids[k] = c.take<uint32_t>(n_instances);
     // upper bound on the number of (tile, segment) pairs, known from the instance count alone
-    b.max_segments = warp_blend ? (int64_t)n_tiles + ceil_div<int64_t>(n_instances, (int64_t)kSegmentLength) : max_segments(n_instances, n_tiles, tile);
+    b.max_segments = warp_blend ? (int64_t)n_tiles + ceil_div<int64_t>(n_instances, (int64_t)kLaterSegment) : max_segments(n_instances, n_tiles, tile);
     const size_t px = (size_t)b.max_segments * tile * tile;
     b.segs = c.take<Segment>(warp_blend ? 0 : b.max_segments);
     b.tile_first = c.take<uint32_t>(n_tiles);
@@ -2608,8 +2670,8 @@ InstanceBlob carve_instance_blob(void* p, int64_t n_instances, int n_tiles, int 
     b.seg_Z = c.take<float>(with_depth ? px : 0);
     b.seg_E = c.take<float>(with_depth && warp_blend ? px : 0);
     b.tile_rank = c.take<uint32_t>(warp_blend ? (size_t)n_tiles : 0);
-    b.list0 = c.take<uint32_t>(warp_blend ? (size_t)n_tiles : 0);
-    b.list1 = c.take<uint2>(warp_blend ? (size_t)b.max_segments : 0);
+    b.items0 = c.take<WarpItem>(warp_blend ? (size_t)n_tiles : 0);
+    b.items1 = c.take<WarpItem>(warp_blend ? (size_t)b.max_segments : 0);
     b.n_kept = c.take<uint32_t>(warp_blend ? (size_t)b.max_segments * kWarpBlendParts : 0);
     c.off = align_up(c.off);
     b.sort_ws = c.base + c.off;
@@ -2843,10 +2905,10 @@ int run_front(const RasterParams& rp, int64_t n, const float* positions, const v
     }
     if (warp_blend) {
         StageScope scope(STAGE_SORT_TILE, stream);
-        INPC_CUDA_TRY(cudaMemsetAsync(ib.n_segments, 0, 8 * sizeof(uint32_t), stream));   // counts and work tickets
+        INPC_CUDA_TRY(cudaMemsetAsync(ib.n_segments, 0, 8 * sizeof(uint32_t), stream));
         warp_items_scan_kernel<<<1, kScanThreads, 0, stream>>>(ib.ranges, n_tiles, ib.tile_first, ib.tile_rank, ib.n_segments);
         INPC_LAUNCH_CHECK("warp_items_scan_kernel");
-        warp_items_fill_kernel<<<ceil_div(n_tiles, 256), 256, 0, stream>>>(ib.ranges, n_tiles, ib.tile_first, ib.tile_rank, ib.list0, ib.list1);
+        warp_items_fill_kernel<<<ceil_div(n_tiles, 256), 256, 0, stream>>>(ib.ranges, n_tiles, ib.tile_first, ib.tile_rank, ib.items0, ib.items1);
         INPC_LAUNCH_CHECK("warp_items_fill_kernel");
     } else {
         StageScope scope(STAGE_SORT_TILE, stream);
@@ -2918,20 +2980,20 @@ int launch_bilinear_warp_forward(const RasterParams& rp, const PointBlob& pb, co
     uint32_t* kept1 = ib.keys[1 - t_alt];
     const unsigned threads = kWarpBlendWarps * 32;
     blend_bilinear_warp_forward_kernel<PASS_FIRST, KIND><<<grid, threads, 0, stream>>>(
-        ib.list0, ib.list1, ib.n_segments, ib.n_segments + 2, ib.ranges, ib.tile_first, keys, ids, pb.rec, ib.seg_T, ib.seg_C, ib.seg_Z, ib.seg_E,
+        ib.items0, ib.n_segments, ib.n_segments + 2, keys, ids, pb.rec, ib.seg_T, ib.seg_C, ib.seg_Z, ib.seg_E,
         image, depth, alpha, blending_weights, kept0, kept1, ib.n_kept, W, H, rp.gw);
     INPC_LAUNCH_CHECK("blend_bilinear_warp_forward_kernel (first segments)");
     blend_bilinear_warp_forward_kernel<PASS_PRODUCT, KIND><<<grid, threads, 0, stream>>>(
-        ib.list0, ib.list1, ib.n_segments, ib.n_segments + 3, ib.ranges, ib.tile_first, keys, ids, pb.rec, ib.seg_T, ib.seg_C, ib.seg_Z, ib.seg_E,
+        ib.items1, ib.n_segments, ib.n_segments + 3, keys, ids, pb.rec, ib.seg_T, ib.seg_C, ib.seg_Z, ib.seg_E,
         image, depth, alpha, blending_weights, kept0, kept1, ib.n_kept, W, H, rp.gw);
     INPC_LAUNCH_CHECK("blend_bilinear_warp_forward_kernel (products)");
-    warp_blend_prefix_kernel<<<grid, threads, 0, stream>>>(ib.list0, ib.n_segments, ib.ranges, ib.tile_first, ib.seg_T);
+    warp_blend_prefix_kernel<<<grid, threads, 0, stream>>>(ib.items0, ib.n_segments, ib.seg_T);
     INPC_LAUNCH_CHECK("warp_blend_prefix_kernel");
     blend_bilinear_warp_forward_kernel<PASS_REST, KIND><<<grid, threads, 0, stream>>>(
-        ib.list0, ib.list1, ib.n_segments, ib.n_segments + 4, ib.ranges, ib.tile_first, keys, ids, pb.rec, ib.seg_T, ib.seg_C, ib.seg_Z, ib.seg_E,
+        ib.items1, ib.n_segments, ib.n_segments + 4, keys, ids, pb.rec, ib.seg_T, ib.seg_C, ib.seg_Z, ib.seg_E,
         image, depth, alpha, blending_weights, kept0, kept1, ib.n_kept, W, H, rp.gw);
     INPC_LAUNCH_CHECK("blend_bilinear_warp_forward_kernel (later segments)");
-    warp_blend_combine_kernel<KIND><<<grid, threads, 0, stream>>>(ib.list0, ib.n_segments, ib.ranges, ib.tile_first, ib.seg_C, ib.seg_Z, ib.seg_E,
+    warp_blend_combine_kernel<KIND><<<grid, threads, 0, stream>>>(ib.items0, ib.n_segments, ib.seg_C, ib.seg_Z, ib.seg_E,
                                                                       image, depth, alpha, W, H, rp.gw);
     INPC_LAUNCH_CHECK("warp_blend_combine_kernel");
     return INPC_OK;
@@ -2945,7 +3007,7 @@ int launch_bilinear_warp_backward(const RasterParams& rp, const PointBlob& pb, c
     if (rc != INPC_OK) return rc;
     INPC_CUDA_TRY(cudaMemsetAsync(ib.n_segments + 5, 0, sizeof(uint32_t), stream));   // the work ticket
     blend_bilinear_warp_backward_kernel<<<grid, kWarpBlendWarps * 32, 0, stream>>>(
-        ib.list0, ib.list1, ib.n_segments, ib.n_segments + 5, ib.ranges, ib.tile_first, ib.ids[1 - t_alt], ib.keys[1 - t_alt], ib.n_kept, pb.rec,
+        ib.items0, ib.items1, ib.n_segments, ib.n_segments + 5, ib.ids[1 - t_alt], ib.keys[1 - t_alt], ib.n_kept, pb.rec,
         ib.seg_T, ib.seg_C, grad_image, grad_alpha, image, alpha, gfv, grad_opacities, rp.v.width, rp.v.height, rp.gw);
     INPC_LAUNCH_CHECK("blend_bilinear_warp_backward_kernel");
     return INPC_OK;
