@@ -120,7 +120,12 @@ int inpc_rasterize_forward(int mode, int tile_size, const inpc_view* view, int64
 /* Training backward for the forward that produced `state`.
  *   grad_image (4,H,W), grad_alpha (H,W), image, alpha: as returned by / upstream of forward
  *   grad_features (n,36) f16 and grad_opacities (n) f32 — fully written (zero rows for culled points)
- *   grad_features_view (n,4) f32 — caller scratch for the per-point view-space gradient
+ *   grad_features_view (n,33) f32, 32-byte aligned — caller scratch: per point four 32-byte slot records
+ *     (4 feature + 1 opacity gradient sums) plus one mask word.  A splat's pixels lie in at most four (tile, half-tile) parts; every part stores
+ *     its sums into the slot that is its own by construction and the per-point pass adds the written slots in
+ *     fixed order, so bilinear gradients on 8x8 tiles involve no floating-point atomics and are bit-identical
+ *     from run to run (the reference adds five float atomics per fragment, bilinear/kernels.cu:392-415).  The
+ *     other paths use the first (n,4) floats as an atomic accumulation buffer.
  * Replaces inpc::rasterization::{bilinear,gaussian}::backward
  * (rasterization/include/bilinear/backward.h:8-26) together with the three zero-fills of
  * backward_wrapper (rasterization/src/rasterization_api.cu:138-140). */

@@ -1699,7 +1699,7 @@ __global__ void __launch_bounds__(kWarpBlendWarps * 32) blend_bilinear_warp_back
     const uint32_t* __restrict__ kept1, const uint32_t* __restrict__ n_kept, const PointRec* __restrict__ rec,
     const float* __restrict__ seg_T, const float4* __restrict__ seg_C, const float* __restrict__ grad_image,
     const float* __restrict__ grad_alpha, const float* __restrict__ image, const float* __restrict__ alpha_image,
-    float4* __restrict__ grad_feat_view, float* __restrict__ grad_opacity, int width, int height, int gw) {
+    float4* __restrict__ slot_grad, unsigned* __restrict__ slot_mask, int width, int height, int gw) {
     constexpr unsigned kFull = 0xffffffffu;
     __shared__ WarpBackwardSmem s_all[kWarpBlendWarps];
     const unsigned lane = lane_id();
@@ -1837,8 +1837,7 @@ __global__ void __launch_bounds__(kWarpBlendWarps * 32) blend_bilinear_warp_back
                 }
             }
             __syncwarp();
-            // gradients of every staged instance: its (up to) four fragments in fixed corner order, one vector
-            // and one scalar atomic per instance
+            // gradients of every staged instance: its (up to) four fragments in fixed corner order
             if ((int)lane < n_cur) {
                 float4 sf = make_float4(0.f, 0.f, 0.f, 0.f);
                 float so = 0.0f;
@@ -1857,8 +1856,20 @@ __global__ void __launch_bounds__(kWarpBlendWarps * 32) blend_bilinear_warp_back
                     if (c == 0) { sf = v; so = o; }
                     else { sf.x += v.x; sf.y += v.y; sf.z += v.z; sf.w += v.w; so += o; }
                 }
-                if (sf.x != 0.0f || sf.y != 0.0f || sf.z != 0.0f || sf.w != 0.0f) atomicAdd(grad_feat_view + id_cur, sf);
-                if (so != 0.0f) atomicAdd(grad_opacity + id_cur, so);
+                // A splat's 2x2 pixels lie in at most two tile columns and two (tile row, half) groups, and which of
+                // them this item is follows from where the footprint starts: it holds the left column unless the
+                // footprint starts left of it, and the upper row unless it starts above it.  So every (point, slot)
+                // has exactly one writer in the whole launch: the sums go there with plain stores, a bit marks the
+                // slot as written, and the per-point pass adds the slots in fixed order -- no floating-point
+                // atomics, the same gradient bits on every run.
+                if (sf.x != 0.0f || sf.y != 0.0f || sf.z != 0.0f || sf.w != 0.0f || so != 0.0f) {
+                    const unsigned slot_of_point = (qx < 0 ? 1u : 0u) + (qy < 0 ? 2u : 0u);
+                    // one aligned 32-byte record per slot: a whole memory sector, written without reading it first
+                    float4* e = slot_grad + ((size_t)id_cur * 4u + slot_of_point) * 2u;
+                    e[0] = sf;
+                    e[1] = make_float4(so, 0.0f, 0.0f, 0.0f);
+                    atomicOr(slot_mask + id_cur, 1u << slot_of_point);
+                }
             }
             done_w = __ballot_sync(kFull, done);
             __syncwarp();
@@ -2527,9 +2538,17 @@ __global__ void __launch_bounds__(T * T) blend_gaussian_backward_kernel(
 // through a shared-memory slab so the stores are coalesced 16-byte vectors.
 // src/bilinear/kernels.cu:86-104 + include/sh_utils.cuh:44-62; the zero rows replace the
 // torch::zeros of src/rasterization_api.cu:139.
+// SLOTS (warp blend): the view-space gradient of a point is the sum of its (up to four) written slots in slot order,
+// see blend_bilinear_warp_backward_kernel; the opacity gradient is formed here too and written for every point.
+struct GradientSlots {
+    const float4* grad;      // [4 n][2]: {feature gradient}, {opacity gradient, -, -, -}
+    const unsigned* mask;    // [n] bit s: slot s was written
+};
+template <bool SLOTS>
 __global__ void __launch_bounds__(kPreThreads) preprocess_backward_kernel(
     const float* __restrict__ positions, const float* __restrict__ cam, const uint2* __restrict__ bounds,
-    const float4* __restrict__ grad_feat_view, __half* __restrict__ grad_features, int64_t n, bool bulk_ok) {
+    const float4* __restrict__ grad_feat_view, GradientSlots slots, float* __restrict__ grad_opacities,
+    __half* __restrict__ grad_features, int64_t n, bool bulk_ok) {
     __shared__ __align__(16) __half s_out[kPreThreads * 36];
     const int64_t block_first = (int64_t)blockIdx.x * kPreThreads;
     const int in_block = (int)min((int64_t)kPreThreads, n - block_first);
@@ -2541,7 +2560,22 @@ __global__ void __launch_bounds__(kPreThreads) preprocess_backward_kernel(
         float b[9];
         sh_basis(__ldg(positions + 3 * i), __ldg(positions + 3 * i + 1), __ldg(positions + 3 * i + 2), cam, b);
         b[1] = -b[1]; b[3] = -b[3]; b[5] = -b[5]; b[7] = -b[7];
-        const float4 gv = __ldg(grad_feat_view + i);
+        float4 gv = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (SLOTS) {
+            float go = 0.0f;
+            const unsigned m = __ldg(slots.mask + i);
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                if ((m >> q) & 1u) {
+                    const float4 v = __ldg(slots.grad + (i * 4 + q) * 2);
+                    gv.x += v.x; gv.y += v.y; gv.z += v.z; gv.w += v.w;
+                    go += __ldg(slots.grad + (i * 4 + q) * 2 + 1).x;
+                }
+            }
+            grad_opacities[i] = go;
+        } else {
+            gv = __ldg(grad_feat_view + i);
+        }
 #pragma unroll
         for (int k = 0; k < 9; ++k) {
             const __half2 xy = __float22half2_rn(make_float2(b[k] * gv.x, b[k] * gv.y));
@@ -2552,6 +2586,7 @@ __global__ void __launch_bounds__(kPreThreads) preprocess_backward_kernel(
     } else {
 #pragma unroll
         for (int k = 0; k < 18; ++k) *reinterpret_cast<unsigned*>(o + 2 * k) = 0u;
+        if (SLOTS && i < n) grad_opacities[i] = 0.0f;
     }
     unsigned char* dst = reinterpret_cast<unsigned char*>(grad_features) + block_first * 72;
     const int bytes = in_block * 72;
@@ -3000,15 +3035,15 @@ int launch_bilinear_warp_forward(const RasterParams& rp, const PointBlob& pb, co
 }
 
 int launch_bilinear_warp_backward(const RasterParams& rp, const PointBlob& pb, const InstanceBlob& ib, int t_alt, const float* grad_image,
-                                  const float* grad_alpha, const float* image, const float* alpha, float4* gfv, float* grad_opacities,
-                                  cudaStream_t stream) {
+                                  const float* grad_alpha, const float* image, const float* alpha, float4* slot_grad,
+                                  unsigned* slot_mask, cudaStream_t stream) {
     unsigned grid = 1;
     const int rc = warp_blend_grid(&grid);
     if (rc != INPC_OK) return rc;
     INPC_CUDA_TRY(cudaMemsetAsync(ib.n_segments + 5, 0, sizeof(uint32_t), stream));   // the work ticket
     blend_bilinear_warp_backward_kernel<<<grid, kWarpBlendWarps * 32, 0, stream>>>(
         ib.items0, ib.items1, ib.n_segments, ib.n_segments + 5, ib.ids[1 - t_alt], ib.keys[1 - t_alt], ib.n_kept, pb.rec,
-        ib.seg_T, ib.seg_C, grad_image, grad_alpha, image, alpha, gfv, grad_opacities, rp.v.width, rp.v.height, rp.gw);
+        ib.seg_T, ib.seg_C, grad_image, grad_alpha, image, alpha, slot_grad, slot_mask, rp.v.width, rp.v.height, rp.gw);
     INPC_LAUNCH_CHECK("blend_bilinear_warp_backward_kernel");
     return INPC_OK;
 }
@@ -3219,14 +3254,27 @@ extern "C" int inpc_rasterize_backward(const inpc_raster_state* state, const inp
     const PointBlob pb = carve_point_blob(state->point_blob, n, state->mode);
     const InstanceBlob ib = carve_instance_blob(state->instance_blob, instance_capacity(state), n_tiles, state->tile_size, state->mode, false);
     const uint32_t* ids = ib.ids[tile_buffer_of(state, n_tiles)];
-    INPC_CUDA_TRY(cudaMemsetAsync(grad_features_view, 0, sizeof(float4) * (size_t)n, stream));
-    INPC_CUDA_TRY(cudaMemsetAsync(grad_opacities, 0, sizeof(float) * (size_t)n, stream));
     float4* gfv = reinterpret_cast<float4*>(grad_features_view);
     const int W = rp.v.width, H = rp.v.height;
+    // the caller's scratch holds 33 floats per point: four 32-byte slot records and one mask word for the warp blend
+    // or, for the other paths, the (n,4) accumulation buffer of their atomics
+    const bool slots = uses_warp_blend(state->mode, state->tile_size, false);
+    if (slots && (reinterpret_cast<uintptr_t>(grad_features_view) & 31u)) {
+        set_error("inpc_rasterize_backward: grad_features_view must be 32-byte aligned");
+        return INPC_E_INVALID;
+    }
+    float4* slot_grad = gfv;
+    unsigned* slot_mask = reinterpret_cast<unsigned*>(grad_features_view + 32 * (size_t)n);
+    if (slots) {
+        INPC_CUDA_TRY(cudaMemsetAsync(slot_mask, 0, sizeof(unsigned) * (size_t)n, stream));
+    } else {
+        INPC_CUDA_TRY(cudaMemsetAsync(grad_features_view, 0, sizeof(float4) * (size_t)n, stream));
+        INPC_CUDA_TRY(cudaMemsetAsync(grad_opacities, 0, sizeof(float) * (size_t)n, stream));
+    }
     {
         StageScope scope(STAGE_BLEND_BWD, stream);
         if (state->mode == INPC_MODE_BILINEAR) {
-            rc = rp.tile == 8 ? launch_bilinear_warp_backward(rp, pb, ib, tile_buffer_of(state, n_tiles), grad_image, grad_alpha, image, alpha, gfv, grad_opacities, stream)
+            rc = rp.tile == 8 ? launch_bilinear_warp_backward(rp, pb, ib, tile_buffer_of(state, n_tiles), grad_image, grad_alpha, image, alpha, slot_grad, slot_mask, stream)
                               : launch_bilinear_backward<16>(rp, pb, ib, ids, grad_image, grad_alpha, image, alpha, gfv, grad_opacities, stream);
             if (rc != INPC_OK) return rc;
         } else {
@@ -3239,8 +3287,14 @@ extern "C" int inpc_rasterize_backward(const inpc_raster_state* state, const inp
         }
     }
     StageScope scope(STAGE_PREPROCESS_BWD, stream);
-    preprocess_backward_kernel<<<(unsigned)ceil_div<int64_t>(n, kPreThreads), kPreThreads, 0, stream>>>(
-        positions, view->cam_position, pb.bounds, gfv, static_cast<__half*>(grad_features), n, (reinterpret_cast<uintptr_t>(grad_features) & 15u) == 0);
+    const GradientSlots gs{slot_grad, slot_mask};
+    const bool bulk_ok = (reinterpret_cast<uintptr_t>(grad_features) & 15u) == 0;
+    if (slots)
+        preprocess_backward_kernel<true><<<(unsigned)ceil_div<int64_t>(n, kPreThreads), kPreThreads, 0, stream>>>(
+            positions, view->cam_position, pb.bounds, gfv, gs, grad_opacities, static_cast<__half*>(grad_features), n, bulk_ok);
+    else
+        preprocess_backward_kernel<false><<<(unsigned)ceil_div<int64_t>(n, kPreThreads), kPreThreads, 0, stream>>>(
+            positions, view->cam_position, pb.bounds, gfv, gs, grad_opacities, static_cast<__half*>(grad_features), n, bulk_ok);
     INPC_LAUNCH_CHECK("preprocess_backward_kernel");
     return end_index_checks(stream);
 }

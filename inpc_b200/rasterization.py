@@ -190,7 +190,7 @@ class _Rasterize(torch.autograd.Function):
         grad_alpha = torch.zeros_like(alpha) if grad_alpha is None else _cuda_f32(grad_alpha, "grad_alpha")
         with torch.cuda.device(dev):
             view = _ViewArg(s, dev)
-            grad_features_view = torch.empty((n, 4), dtype=torch.float32, device=dev)
+            grad_features_view = torch.empty((n, 33), dtype=torch.float32, device=dev)   # per-point gradient slots
             grad_features = torch.empty((n, 36), dtype=torch.float16, device=dev)
             grad_opacities = torch.empty((n, 1), dtype=torch.float32, device=dev)
             _check(_cabi.lib().inpc_rasterize_backward(

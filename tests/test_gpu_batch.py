@@ -34,3 +34,33 @@ def test_stream_pipelined_batch_equals_sequential_batch():
     torch.testing.assert_close(results[1][1], results[3][1], rtol=1e-4, atol=1e-8)
     for a, b in zip(results[1][2][:2], results[3][2][:2]):        # last view's image and alpha
         assert torch.equal(a, b)
+    # gradients are accumulated without floating-point atomics (every (point, part) slot has one writer, the slots are
+    # added in fixed order): bit-identical whatever the scheduling
+    assert torch.equal(results[1][2][3], results[3][2][3]) and torch.equal(results[1][2][4], results[3][2][4])
+
+
+def test_gradients_are_bit_identical_from_run_to_run():
+    """Two backward passes over the same forward inputs give the same bits: grad_features and grad_opacities of the
+    bilinear 8x8 path are sums over per-point slots in fixed order, not over atomics in arrival order (the reference
+    adds five float atomics per fragment, bilinear/kernels.cu:392-415, and is not reproducible)."""
+    import inpc_b200
+    import synthetic_workloads as syn
+    cfg = syn.config1(n_samples=1 << 21, n_leaves=1 << 16)
+    view, tree = cfg["view"].to(DEV), cfg["tree"].to(DEV)
+    feats, opac = cfg["features"].to(DEV), cfg["opacities"].to(DEV)
+    pos, _ = inpc_b200.ProbabilityFieldSampler(0).generate_training_samples(tree.centers, tree.levels, tree.weights, view, 1 << 21,
+                                                                             tree.initial_size)
+    H, W = view.camera.height, view.camera.width
+    g = torch.Generator().manual_seed(5)
+    gi = (torch.randn((4, H, W), generator=g) * 1e-3).to(DEV)
+    ga = (torch.randn((1, H, W), generator=g) * 1e-3).to(DEV)
+    grads = []
+    for _ in range(3):
+        f = feats.detach().requires_grad_(True)
+        o = opac.detach().requires_grad_(True)
+        im, al, _ = inpc_b200.INPCRasterizer(tile_size=8)(view, 0, pos, f, o)
+        torch.autograd.backward([im, al], [gi, ga])
+        grads.append((f.grad.clone(), o.grad.clone()))
+    assert float(grads[0][1].abs().sum()) > 0
+    for gf, go in grads[1:]:
+        assert torch.equal(gf, grads[0][0]) and torch.equal(go, grads[0][1])
