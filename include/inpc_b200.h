@@ -145,6 +145,18 @@ int inpc_render(int mode, int tile_size, const inpc_view* view, int64_t n, const
                 float* depth, float* alpha, inpc_alloc_fn alloc_point, inpc_alloc_fn alloc_instance,
                 void* alloc_user, void* stream);
 
+/* Batched inference over several sample sets of one view (bilinear splats, 8x8 tiles): set j = positions[j] (n_points[j],3)
+ * f32 and features_raw[j] (n_points[j],37) f16, drawn into images[j] (4,H,W), depths[j] (H,W), alphas[j] (H,W) of the three
+ * contiguous output arrays -- bit for bit what n_sets calls of inpc_render give, from ONE launch sequence: the sets are
+ * culled and projected together, sorted together (a set's tiles are rows of a stacked tile grid, so the set index rides in
+ * the tile key) and blended together.  n_sets <= 8; no host synchronisation.  Replaces the loop over
+ * rasterizer.render of the reference's multisampled and ring-buffer inference (Renderer.py:99-125, :139-166,
+ * utils.py:145-174). */
+int inpc_render_multi(int tile_size, const inpc_view* view, int n_sets, const int64_t* n_points,
+                      const float* const* positions, const void* const* features_raw, float* images, float* depths,
+                      float* alphas, inpc_alloc_fn alloc_point, inpc_alloc_fn alloc_instance, void* alloc_user,
+                      void* stream);
+
 /* Inference from a pre-extracted point cloud; `scales` (n) f32 may be NULL (gaussian mode then uses
  * sigma_world for every point).
  * Replaces inpc::rasterization::{bilinear,gaussian}::inference_preextracted

@@ -48,6 +48,7 @@ PROTOTYPES = {
     "inpc_rasterize_forward": (_I, [_I, _I, _VP, _L, _P, _P, _P, _P, _P, _P, ALLOC_FN, ALLOC_FN, _P, _SP, _P]),
     "inpc_rasterize_backward": (_I, [_SP, _VP, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P]),
     "inpc_render": (_I, [_I, _I, _VP, _L, _P, _P, _F, _F, _P, _P, _P, ALLOC_FN, ALLOC_FN, _P, _P]),
+    "inpc_render_multi": (_I, [_I, _VP, _I, C.POINTER(_L), C.POINTER(_P), C.POINTER(_P), _P, _P, _P, ALLOC_FN, ALLOC_FN, _P, _P]),
     "inpc_render_preextracted": (_I, [_I, _I, _VP, _L, _P, _P, _P, _P, _F, _F, _P, _P, _P, ALLOC_FN, ALLOC_FN, _P, _P]),
     "inpc_rasterize_rows_forward": (_I, [_I, _VP, _L, _P, _P, _I, _P, _P, _P, _P, ALLOC_FN, ALLOC_FN, _P, _SP, _P]),
     "inpc_rasterize_rows_backward": (_I, [_SP, _VP, _P, _P, _P, _P, _P, _P, _P, _P]),

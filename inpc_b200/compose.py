@@ -155,12 +155,13 @@ def _side_streams(device: torch.device, n: int) -> list:
 @torch.no_grad()
 def render_multisampled(rasterizer, view, mode: int, sample_sets, background: torch.Tensor | None = None,
                         sigma_world_scale: float = 1.0, sigma_cutoff: float = 3.0,
-                        average_with_premultiplied_alpha: bool = True, n_streams: int = 1):
+                        average_with_premultiplied_alpha: bool = True, n_streams: int = 1, batched: bool = False):
     """Inference over several sample sets of one view (Renderer.py:99-125 and :139-166): every set
     `(positions, features_raw)` is rasterised with `rasterizer.render`, the results are averaged and
     composed over `background`.  `sample_sets` is a list of pairs or a filled `MultisamplingRingBuffer`.
     With `n_streams > 1` the sets are rasterised concurrently on that many CUDA streams (they are
-    independent; the accumulation order, and hence the result, stays that of the list).
+    independent; the accumulation order, and hence the result, stays that of the list).  `batched` (bilinear splats,
+    8x8 tiles, at most 8 sets) renders all sets with one `render_multi` call instead: same bits, one launch sequence.
     Returns (feature_image, depth, alpha, alpha_sum)."""
     if isinstance(sample_sets, MultisamplingRingBuffer):
         ring = sample_sets
@@ -168,6 +169,12 @@ def render_multisampled(rasterizer, view, mode: int, sample_sets, background: to
     else:
         sets = list(sample_sets)
     acc = MultisampleAccumulator(len(sets), average_with_premultiplied_alpha)
+    if batched and mode == 0 and 2 <= len(sets) <= 8 and getattr(rasterizer, "tile_size", 0) == 8:
+        # one launch sequence for all sets (culled, sorted and blended together), then the same accumulation, set by set
+        images, depths, alphas = rasterizer.render_multi(view, sets)
+        for j in range(len(sets)):
+            acc.add(images[j], depths[j], alphas[j])
+        return acc.resolve(background)
     if n_streams <= 1 or len(sets) < 2:
         for positions, features_raw in sets:
             acc.add(*rasterizer.render(view, mode, positions, features_raw, sigma_world_scale, sigma_cutoff))

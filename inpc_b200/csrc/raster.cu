@@ -56,10 +56,30 @@ struct RasterParams {
     ViewParams v;
     int tile;       // tile edge in pixels (8 or 16)
     float inv_tile; // its reciprocal: the edge is a power of two, so x * inv_tile == x / tile bit for bit
-    int gw, gh;     // tile grid
+    int gw, gh;     // tile grid of one image
+    int n_sets;     // images drawn by the call (1 except for batched multi-set inference): the grid has n_sets * gh rows
     float sigma_world, sigma_cutoff;
     const float* scales;   // optional per-point sigma (gaussian, pre-extracted)
 };
+
+// Input points of a call: one array triple, or (batched multi-set inference) up to kMaxSets of them laid end to end in
+// a virtual index space in which every set starts at a multiple of 1024, so that a block of the two input passes never
+// straddles two sets.  Set j is drawn into its own image: its tiles are rows [j * gh, (j + 1) * gh) of a stacked grid.
+constexpr int kMaxSets = 8;
+constexpr int64_t kSetAlign = 1024;
+struct PointSets {
+    int count;
+    int64_t start[kMaxSets + 1];      // virtual index of every set's first point; start[count] = virtual total
+    int64_t size[kMaxSets];
+    const float* positions[kMaxSets];
+    const void* features[kMaxSets];
+    const float* opacities[kMaxSets];
+};
+__device__ __forceinline__ int set_of_block(const PointSets& ps, int64_t block_first) {
+    int j = 0;
+    while (j + 1 < ps.count && block_first >= ps.start[j + 1]) ++j;
+    return j;
+}
 
 struct Projection {
     bool visible;
@@ -93,9 +113,10 @@ __device__ __forceinline__ float affine_row(const float* r, float px, float py, 
 
 // src/bilinear/kernels.cu:41-65 and src/gaussian/kernels.cu:41-90 (training), :145-186 (inference),
 // :243-292 (pre-extracted): depth cull, perspective divide, pixel coordinates, tile bounds.
+// `scales_index`: index into rp.scales; `set`: which image of the stacked tile grid the point is drawn into.
 template <int MODE, int VARIANT>
 __device__ __forceinline__ Projection project_point(const float px, const float py, const float pz, const W2C& m,
-                                                    const RasterParams& rp, const int64_t i) {
+                                                    const RasterParams& rp, const int64_t i, const int set = 0) {
     Projection o;
     o.visible = false;
     o.x0 = o.x1 = o.y0 = o.y1 = 0;
@@ -152,6 +173,8 @@ __device__ __forceinline__ Projection project_point(const float px, const float 
     o.sx = sx;
     o.sy = sy;
     o.visible = (o.x1 - o.x0) * (o.y1 - o.y0) != 0u;
+    o.y0 += (unsigned)set * gh;   // rows of this set's image in the stacked grid (screen coordinates stay the set's own)
+    o.y1 += (unsigned)set * gh;
     return o;
 }
 
@@ -162,9 +185,14 @@ constexpr unsigned kCountShift = 30;   // bilinear: (tiles touched - 1) in key b
 // (point, tile) instances they create.
 template <int MODE, int VARIANT>
 __global__ void __launch_bounds__(kPreThreads) visibility_count_kernel(
-    const float* __restrict__ positions, int64_t n, RasterParams rp, unsigned* __restrict__ block_visible,
+    PointSets ps, RasterParams rp, unsigned* __restrict__ block_visible,
     unsigned* __restrict__ group_visible, unsigned long long* __restrict__ group_instances, unsigned* __restrict__ depth_min,
     unsigned* __restrict__ depth_max) {
+    // this block's set; indices below are local to it
+    const int set = set_of_block(ps, (int64_t)blockIdx.x * kPreThreads * 4);
+    const float* __restrict__ positions = ps.positions[set];
+    const int64_t n = ps.size[set];
+    const int64_t n_virtual = ps.start[ps.count];
     // Every thread takes 4 consecutive points (three 16-byte loads when the array is aligned), so a
     // block covers 4 chunks of kPreThreads points; counts are kept per chunk because the projection
     // pass works on chunks of kPreThreads points.
@@ -174,7 +202,7 @@ __global__ void __launch_bounds__(kPreThreads) visibility_count_kernel(
     __shared__ unsigned long long s_i[kPreThreads / 32];
     __shared__ unsigned s_lo[kPreThreads / 32], s_hi[kPreThreads / 32];
     const W2C m = load_w2c(rp.v.w2c);
-    const int64_t first = ((int64_t)blockIdx.x * kPreThreads + threadIdx.x) * kPerThread;
+    const int64_t first = ((int64_t)blockIdx.x * kPreThreads + threadIdx.x) * kPerThread - ps.start[set];   // local to the set
     float p[3 * kPerThread];
     if (first + kPerThread <= n && (reinterpret_cast<uintptr_t>(positions) & 15u) == 0) {
         const float4* src = reinterpret_cast<const float4*>(positions + 3 * first);
@@ -192,7 +220,7 @@ __global__ void __launch_bounds__(kPreThreads) visibility_count_kernel(
 #pragma unroll
     for (int k = 0; k < kPerThread; ++k) {
         if (first + k < n) {
-            const Projection pr = project_point<MODE, VARIANT>(p[3 * k], p[3 * k + 1], p[3 * k + 2], m, rp, first + k);
+            const Projection pr = project_point<MODE, VARIANT>(p[3 * k], p[3 * k + 1], p[3 * k + 2], m, rp, first + k, set);
             if (pr.visible) {
                 v += 1u;
                 c += (pr.x1 - pr.x0) * (pr.y1 - pr.y0);
@@ -215,7 +243,7 @@ __global__ void __launch_bounds__(kPreThreads) visibility_count_kernel(
     if (threadIdx.x < kPerThread) {
         // chunk `threadIdx.x` of this block
         const int64_t chunk = (int64_t)blockIdx.x * kPerThread + threadIdx.x;
-        if (chunk * kPreThreads < n) {
+        if (chunk * kPreThreads < n_virtual) {   // chunks of the padding behind a set count zero survivors
             unsigned tv = 0;
             unsigned long long ti = 0;
 #pragma unroll
@@ -309,15 +337,19 @@ __device__ __forceinline__ float sh_eval_channel(const float* b, const __half* h
            b[6] * __half2float(h[24 + c]) - b[7] * __half2float(h[28 + c]) + b[8] * __half2float(h[32 + c]);
 }
 
-// What the instance emission of the warp blend needs of a bilinear splat, in one word: column of the
-// left pixel of its 2x2 footprint plus one (15 bits), whether it touches two tile columns (1 bit), and the
-// same for rows.  A visible splat's footprint starts at pixel -1 at the earliest, and images of this path
-// are at most kMaxCodedSide pixels wide and high.  4 bytes per point keep the array (33 MB for 2^23
-// points) resident in L2 while the emission gathers from it in depth order.
-constexpr int kMaxCodedSide = 32760;
-__device__ __forceinline__ uint32_t pack_quad(const Projection& pr) {
-    const unsigned qx1 = (unsigned)(__float2int_rd(pr.sx - 0.5f) + 1), qy1 = (unsigned)(__float2int_rd(pr.sy - 0.5f) + 1);
-    return (qx1 & 0x7FFFu) | ((pr.x1 - pr.x0 - 1u) << 15) | ((qy1 & 0x7FFFu) << 16) | ((pr.y1 - pr.y0 - 1u) << 31);
+// What the instance emission of the warp blend needs of a bilinear splat, in one word.  Columns: pixel column of the
+// left pixel of its 2x2 footprint plus one (15 bits; a visible splat's footprint starts at pixel -1 at the earliest),
+// whether it touches two tile columns (1 bit).  Rows: the first tile row it touches in the stacked grid (11 bits), the
+// row of its upper pixel relative to that tile plus one (4 bits, 0..8), whether it touches two tile rows (1 bit).
+// Rows are kept relative to the tile because the first row of an image other than the first is not row 0 of the
+// grid.  4 bytes per point keep the array (33 MB for 2^23 points) resident in L2 while the emission gathers from
+// it in depth order.
+constexpr int kMaxCodedSide = 32760;       // widest image of this path, in pixels
+constexpr int kMaxCodedTileRows = 2047;    // most tile rows of the (stacked) grid
+__device__ __forceinline__ uint32_t pack_quad(const Projection& pr, int tile_rows_before) {
+    const unsigned qx1 = (unsigned)(__float2int_rd(pr.sx - 0.5f) + 1);
+    const unsigned ry1 = (unsigned)(__float2int_rd(pr.sy - 0.5f) - ((int)pr.y0 - tile_rows_before) * 8 + 1);
+    return (qx1 & 0x7FFFu) | ((pr.x1 - pr.x0 - 1u) << 15) | ((pr.y0 & 0x7FFu) << 16) | ((ry1 & 0xFu) << 27) | ((pr.y1 - pr.y0 - 1u) << 31);
 }
 
 // Pass 2: project again (same arithmetic, same outcome), evaluate SH, write the point record and
@@ -326,24 +358,32 @@ __device__ __forceinline__ uint32_t pack_quad(const Projection& pr) {
 // src/bilinear/kernels.cu:11-84, :106-184; src/gaussian/kernels.cu:11-111, :113-217, :219-324.
 template <int MODE, int VARIANT>
 __global__ void __launch_bounds__(kPreThreads) preprocess_kernel(
-    const float* __restrict__ positions, const __half* __restrict__ features, const float* __restrict__ opacities,
-    int64_t n, RasterParams rp, const unsigned* __restrict__ block_visible, const unsigned* __restrict__ group_offset,
+    PointSets ps, RasterParams rp, const unsigned* __restrict__ block_visible, const unsigned* __restrict__ group_offset,
     const unsigned* __restrict__ depth_min,
     const unsigned* __restrict__ depth_max, PointRec* __restrict__ rec, uint2* __restrict__ bounds, uint32_t* __restrict__ quad,
     float4* __restrict__ conic, uint32_t* __restrict__ depth_keys,
-    uint32_t* __restrict__ point_ids, bool bulk_ok, int pack_count, volatile unsigned* status) {
+    uint32_t* __restrict__ point_ids, int pack_count, volatile unsigned* status) {
     constexpr int kHalves = VARIANT == VAR_RAW37 ? 37 : 36;
     constexpr int kSlabBytes = VARIANT == VAR_ROWS ? 16 : kPreThreads * kHalves * 2;   // multiple of 16 for both layouts
     __shared__ __align__(16) unsigned char s_feat[kSlabBytes];
     __shared__ unsigned s_scan[kPreThreads / 32 + 1];
 
-    const int64_t block_first = (int64_t)blockIdx.x * kPreThreads;
-    const int in_block = (int)min((int64_t)kPreThreads, n - block_first);
+    // this block's set: the input arrays are indexed by the point's position in its set (i), everything this pass
+    // writes by its position in the virtual index space of the call (iv); the two coincide for a single set
+    const int64_t block_first_v = (int64_t)blockIdx.x * kPreThreads;
+    const int set = set_of_block(ps, block_first_v);
+    const float* __restrict__ positions = ps.positions[set];
+    const __half* __restrict__ features = static_cast<const __half*>(ps.features[set]);
+    const float* __restrict__ opacities = ps.opacities[set];
+    const int64_t n = ps.size[set];
+    const bool bulk_ok = (reinterpret_cast<uintptr_t>(features) & 15u) == 0;
+    const int64_t block_first = block_first_v - ps.start[set];
+    const int in_block = (int)max((int64_t)0, min((int64_t)kPreThreads, n - block_first));
     __shared__ __align__(8) unsigned long long s_bar;
     // The block's feature slab is contiguous in global memory.  When base and size allow (multiples of
     // 16 bytes) one bulk asynchronous copy brings it in while the threads project their points;
     // otherwise (odd tail block, unaligned caller view) 16-byte loads through registers do.
-    const bool bulk = VARIANT != VAR_ROWS && bulk_ok && ((in_block * kHalves * 2) & 15) == 0;
+    const bool bulk = VARIANT != VAR_ROWS && bulk_ok && in_block > 0 && ((in_block * kHalves * 2) & 15) == 0;
     if (bulk) {
         if (threadIdx.x == 0) mbarrier_init(&s_bar, 1);
         __syncthreads();
@@ -363,22 +403,24 @@ __global__ void __launch_bounds__(kPreThreads) preprocess_kernel(
     }
     const W2C m = load_w2c(rp.v.w2c);
     const int64_t i = block_first + threadIdx.x;
+    const int64_t iv = block_first_v + threadIdx.x;
     Projection pr;
     pr.visible = false;
     float px = 0, py = 0, pz = 0;
     if (i < n) {
         px = __ldg(positions + 3 * i); py = __ldg(positions + 3 * i + 1); pz = __ldg(positions + 3 * i + 2);
-        pr = project_point<MODE, VARIANT>(px, py, pz, m, rp, i);
+        pr = project_point<MODE, VARIANT>(px, py, pz, m, rp, i, set);
     }
     bool slab_ready = true;
     if (bulk) slab_ready = mbarrier_wait_bounded(&s_bar, 0u);
     if (!slab_ready && status) status[STATUS_BULK_COPY_TIMEOUT] = 1u;
     __syncthreads();
+    if (i >= n && iv < ps.start[ps.count]) bounds[iv] = make_uint2(0u, 0u);   // padding behind a set
     if (i < n && slab_ready) {
         if (pr.visible && VARIANT == VAR_ROWS) {
             // feature rows are gathered by the blend itself: the record carries the geometry only
-            *reinterpret_cast<float4*>(rec + i) = make_float4(pr.sx, pr.sy, __ldg(opacities + i), pr.depth);
-            bounds[i] = make_uint2(pr.x0 | (pr.x1 << 16), pr.y0 | (pr.y1 << 16));
+            *reinterpret_cast<float4*>(rec + iv) = make_float4(pr.sx, pr.sy, __ldg(opacities + i), pr.depth);
+            bounds[iv] = make_uint2(pr.x0 | (pr.x1 << 16), pr.y0 | (pr.y1 << 16));
         } else if (pr.visible) {
             const __half* h = reinterpret_cast<const __half*>(s_feat) + threadIdx.x * kHalves;
             float b[9];
@@ -394,14 +436,14 @@ __global__ void __launch_bounds__(kPreThreads) preprocess_kernel(
             }
 #pragma unroll
             for (int c = 0; c < 4; ++c) r.f[c] = sh_eval_channel(b, h, c);
-            float4* dst = reinterpret_cast<float4*>(rec + i);
+            float4* dst = reinterpret_cast<float4*>(rec + iv);
             dst[0] = make_float4(r.sx, r.sy, r.opacity, r.depth);
             dst[1] = make_float4(r.f[0], r.f[1], r.f[2], r.f[3]);
-            bounds[i] = make_uint2(pr.x0 | (pr.x1 << 16), pr.y0 | (pr.y1 << 16));
-            if (quad) quad[i] = pack_quad(pr);
-            if (MODE == INPC_MODE_GAUSSIAN) conic[i] = make_float4(pr.cx, pr.cy, pr.cz, 0.0f);
+            bounds[iv] = make_uint2(pr.x0 | (pr.x1 << 16), pr.y0 | (pr.y1 << 16));
+            if (quad) quad[iv] = pack_quad(pr, set * rp.gh);
+            if (MODE == INPC_MODE_GAUSSIAN) conic[iv] = make_float4(pr.cx, pr.cy, pr.cz, 0.0f);
         } else {
-            bounds[i] = make_uint2(0u, 0u);
+            bounds[iv] = make_uint2(0u, 0u);
         }
     }
     unsigned total;
@@ -421,7 +463,7 @@ __global__ void __launch_bounds__(kPreThreads) preprocess_kernel(
         if (MODE == INPC_MODE_BILINEAR && pack)
             key |= ((pr.x1 - pr.x0) * (pr.y1 - pr.y0) - 1u) << kCountShift;
         depth_keys[slot] = key;
-        point_ids[slot] = (uint32_t)i;
+        point_ids[slot] = (uint32_t)iv;
     }
 }
 
@@ -521,9 +563,9 @@ __global__ void __launch_bounds__(kInstThreads) emit_instances_kernel(const uint
             // the tile bounds follow from the footprint origin: first tile = floor(origin / 8), never below 0
             const uint32_t q = __ldg(quad + id);
             qx = (int)(q & 0x7FFFu) - 1;
-            qy = (int)((q >> 16) & 0x7FFFu) - 1;
             x0 = qx < 0 ? 0u : (unsigned)qx >> 3;
-            y0 = qy < 0 ? 0u : (unsigned)qy >> 3;
+            y0 = (q >> 16) & 0x7FFu;
+            qy = (int)y0 * 8 + (int)((q >> 27) & 0xFu) - 1;   // row of the upper pixel in the stacked grid (or one above its image)
             x1 = x0 + 1u + ((q >> 15) & 1u);
             y1 = y0 + 1u + (q >> 31);
         } else {
@@ -1334,7 +1376,7 @@ __global__ void __launch_bounds__(kWarpBlendWarps * 32) blend_bilinear_warp_forw
     const uint32_t* __restrict__ inst_ids, const PointRec* __restrict__ rec, float* __restrict__ seg_T, float4* __restrict__ seg_C,
     float* __restrict__ seg_Z, float* __restrict__ seg_E, float* __restrict__ image, float* __restrict__ depth_image,
     float* __restrict__ alpha_image, float* __restrict__ blending_weights, uint32_t* kept0, uint32_t* kept1,
-    uint32_t* __restrict__ n_kept, int width, int height, int gw) {
+    uint32_t* __restrict__ n_kept, int width, int height, int gw, int gh) {
     constexpr unsigned kFull = 0xffffffffu;
     constexpr bool kBlend = PASS != PASS_PRODUCT;               // colours and weights; PRODUCT only multiplies
     constexpr bool kWeights = kBlend && KIND == BLEND_TRAIN;
@@ -1363,7 +1405,9 @@ __global__ void __launch_bounds__(kWarpBlendWarps * 32) blend_bilinear_warp_forw
         const size_t sidx = (size_t)(first + seg) * 2u + half;      // this item's slot in the per-segment arrays
         const size_t sidx0 = (size_t)first * 2u + half;             // segment 0 of the same tile half
         const uint2 rg = make_uint2(it.begin, it.end);
-        const int tx = (int)(tile % (unsigned)gw), ty = (int)(tile / (unsigned)gw);
+        // rows [j gh, (j + 1) gh) of the tile grid are image j of the call (one image except for batched inference)
+        const int tx = (int)(tile % (unsigned)gw), ty_all = (int)(tile / (unsigned)gw);
+        const int set = ty_all / gh, ty = ty_all - set * gh;
         const int px0 = tx * 8, py0 = ty * 8 + 4 * half;            // first pixel of this half
         const int px = px0 + (int)(lane & 7u), py = py0 + (int)(lane >> 3);
         const bool inside = px < width && py < height;
@@ -1566,18 +1610,20 @@ __global__ void __launch_bounds__(kWarpBlendWarps * 32) blend_bilinear_warp_forw
         }
         const int64_t n_px = (int64_t)width * height;
         const int64_t pi = (int64_t)py * width + px;
+        float* image_s = image + (int64_t)set * 4 * n_px;
+        float* alpha_s = alpha_image + (int64_t)set * n_px;
         if (n_seg == 1u) {
             if (inside) {
-                image[pi] = C0;
-                image[n_px + pi] = C1;
-                image[2 * n_px + pi] = C2;
-                image[3 * n_px + pi] = C3;
+                image_s[pi] = C0;
+                image_s[n_px + pi] = C1;
+                image_s[2 * n_px + pi] = C2;
+                image_s[3 * n_px + pi] = C3;
                 if (KIND == BLEND_INFER) {
                     const float A = 1.0f - Tr;
-                    depth_image[pi] = A > 0.0f ? Z / A : 0.0f;
-                    alpha_image[pi] = Tr < kTransmittanceEps ? 1.0f : A;
+                    depth_image[(int64_t)set * n_px + pi] = A > 0.0f ? Z / A : 0.0f;
+                    alpha_s[pi] = Tr < kTransmittanceEps ? 1.0f : A;
                 } else {
-                    alpha_image[pi] = Tr < kTransmittanceEps ? 1.0f : 1.0f - Tr;
+                    alpha_s[pi] = Tr < kTransmittanceEps ? 1.0f : 1.0f - Tr;
                 }
             }
         } else {
@@ -1589,7 +1635,7 @@ __global__ void __launch_bounds__(kWarpBlendWarps * 32) blend_bilinear_warp_forw
                 seg_Z[si] = Z;
                 seg_E[si] = Tr;
             } else if (seg + 1u == n_seg && inside) {
-                alpha_image[pi] = Tr < kTransmittanceEps ? 1.0f : 1.0f - Tr;
+                alpha_s[pi] = Tr < kTransmittanceEps ? 1.0f : 1.0f - Tr;
             }
         }
     }
@@ -1630,7 +1676,7 @@ template <int KIND>
 __global__ void __launch_bounds__(kWarpBlendWarps * 32) warp_blend_combine_kernel(
     const WarpItem* __restrict__ items0, const uint32_t* __restrict__ counts, float4* __restrict__ seg_C, const float* __restrict__ seg_Z,
     const float* __restrict__ seg_E,
-    float* __restrict__ image, float* __restrict__ depth_image, float* __restrict__ alpha_image, int width, int height, int gw) {
+    float* __restrict__ image, float* __restrict__ depth_image, float* __restrict__ alpha_image, int width, int height, int gw, int gh) {
     const unsigned lane = lane_id();
     const unsigned n_parts = __ldg(counts) * 2u;
     for (unsigned w = blockIdx.x * kWarpBlendWarps + (threadIdx.x >> 5); w < n_parts; w += gridDim.x * kWarpBlendWarps) {
@@ -1638,7 +1684,8 @@ __global__ void __launch_bounds__(kWarpBlendWarps * 32) warp_blend_combine_kerne
         const unsigned half = w & 1u;
         const unsigned tile = it.tile, n_seg = it.n_seg, first = it.first;
         if (n_seg == 1u) continue;
-        const int tx = (int)(tile % (unsigned)gw), ty = (int)(tile / (unsigned)gw);
+        const int tx = (int)(tile % (unsigned)gw), ty_all = (int)(tile / (unsigned)gw);
+        const int set = ty_all / gh, ty = ty_all - set * gh;
         const int px = tx * 8 + (int)(lane & 7u);
         const int py = ty * 8 + 4 * (int)half + (int)(lane >> 3);
         const size_t base = ((size_t)first * 2u + half) * 32 + lane;   // segment g of this half: base + g * 64
@@ -1668,14 +1715,15 @@ __global__ void __launch_bounds__(kWarpBlendWarps * 32) warp_blend_combine_kerne
         if (px < width && py < height) {
             const int64_t n_px = (int64_t)width * height;
             const int64_t pi = (int64_t)py * width + px;
-            image[pi] = run.x;
-            image[n_px + pi] = run.y;
-            image[2 * n_px + pi] = run.z;
-            image[3 * n_px + pi] = run.w;
+            float* image_s = image + (int64_t)set * 4 * n_px;
+            image_s[pi] = run.x;
+            image_s[n_px + pi] = run.y;
+            image_s[2 * n_px + pi] = run.z;
+            image_s[3 * n_px + pi] = run.w;
             if (KIND == BLEND_INFER) {
                 const float A = 1.0f - t_final;
-                depth_image[pi] = A > 0.0f ? z / A : 0.0f;
-                alpha_image[pi] = t_final < kTransmittanceEps ? 1.0f : A;
+                depth_image[(int64_t)set * n_px + pi] = A > 0.0f ? z / A : 0.0f;
+                alpha_image[(int64_t)set * n_px + pi] = t_final < kTransmittanceEps ? 1.0f : A;
             }
         }
     }
@@ -2757,8 +2805,9 @@ int check_view(const inpc_view* v, int tile_size, int mode, int64_t n) {
         set_error("image size %dx%d out of range", v->width, v->height);
         return INPC_E_INVALID;
     }
-    if (mode == INPC_MODE_BILINEAR && tile_size == 8 && (v->width > kMaxCodedSide || v->height > kMaxCodedSide)) {
-        set_error("image size %dx%d exceeds the %d pixels per side of the 8x8-tile bilinear path (use tile_size 16)", v->width, v->height, kMaxCodedSide);
+    if (mode == INPC_MODE_BILINEAR && tile_size == 8 && (v->width > kMaxCodedSide || ceil_div(v->height, 8) > kMaxCodedTileRows)) {
+        set_error("image size %dx%d exceeds the %d x %d pixels of the 8x8-tile bilinear path (use tile_size 16)", v->width, v->height, kMaxCodedSide,
+                  kMaxCodedTileRows * 8);
         return INPC_E_INVALID;
     }
     // tile indices live in the low kTileKeyBits bits of the instance keys
@@ -2802,8 +2851,19 @@ int end_index_checks(cudaStream_t stream) {
 template <int MODE, int VARIANT>
 int run_front(const RasterParams& rp, int64_t n, const float* positions, const void* features, const float* opacities,
               inpc_alloc_fn alloc_point, inpc_alloc_fn alloc_instance, void* user, inpc_raster_state* st,
-              bool with_depth, PointBlob* pb_out, InstanceBlob* ib_out, cudaStream_t stream, const char* entry, int c4 = 1) {
-    const int n_tiles = rp.gw * rp.gh;
+              bool with_depth, PointBlob* pb_out, InstanceBlob* ib_out, cudaStream_t stream, const char* entry, int c4 = 1,
+              const PointSets* sets = nullptr) {
+    // `sets`: the input of a batched multi-set call (then n is the virtual total and the three pointers are unused)
+    const int n_tiles = rp.gw * rp.gh * rp.n_sets;
+    PointSets ps;
+    if (sets) {
+        ps = *sets;
+    } else {
+        ps.count = 1;
+        ps.start[0] = 0; ps.start[1] = n;
+        ps.size[0] = n;
+        ps.positions[0] = positions; ps.features[0] = features; ps.opacities[0] = opacities;
+    }
     {
         // a failure an earlier call of this thread reported from the device surfaces here at the latest
         const int rc_prev = check_previous_calls();
@@ -2858,7 +2918,7 @@ int run_front(const RasterParams& rp, int64_t n, const float* positions, const v
             INPC_CUDA_TRY(cudaMemsetAsync(pb.depth_min, 0xFF, sizeof(unsigned), stream));
             INPC_CUDA_TRY(cudaMemsetAsync(pb.depth_max, 0, sizeof(unsigned), stream));
             const int64_t groups = ceil_div<int64_t>(nb, 4);
-            visibility_count_kernel<MODE, VARIANT><<<(unsigned)groups, kPreThreads, 0, stream>>>(positions, n, rp, pb.block_visible, pb.group_visible,
+            visibility_count_kernel<MODE, VARIANT><<<(unsigned)groups, kPreThreads, 0, stream>>>(ps, rp, pb.block_visible, pb.group_visible,
                                                                                              pb.group_instances, pb.depth_min, pb.depth_max);
             INPC_LAUNCH_CHECK("visibility_count_kernel");
             scan_block_counts_kernel<<<1, kScanThreads, 0, stream>>>(pb.group_visible, pb.group_instances, groups, pb.depth_min, pb.depth_max, pb.counters);
@@ -2869,9 +2929,9 @@ int run_front(const RasterParams& rp, int64_t n, const float* positions, const v
             }
             // the projection pass needs nothing from the host: it runs while the host waits for the counters
             preprocess_kernel<MODE, VARIANT><<<(unsigned)nb, kPreThreads, 0, stream>>>(
-                positions, static_cast<const __half*>(features), opacities, n, rp, pb.block_visible, pb.group_visible, pb.depth_min, pb.depth_max,
+                ps, rp, pb.block_visible, pb.group_visible, pb.depth_min, pb.depth_max,
                 pb.rec, pb.bounds, warp_blend ? pb.quad : nullptr,
-                pb.conic, pb.keys[0], pb.ids[0], (reinterpret_cast<uintptr_t>(features) & 15u) == 0, pack_count, status);
+                pb.conic, pb.keys[0], pb.ids[0], pack_count, status);
             INPC_LAUNCH_CHECK("preprocess_kernel");
         }
         if (!deferred) {
@@ -2975,6 +3035,7 @@ RasterParams make_params(const inpc_view* view, int tile_size, float sigma_world
     rp.inv_tile = 1.0f / (float)tile_size;
     rp.gw = ceil_div(view->width, tile_size);
     rp.gh = ceil_div(view->height, tile_size);
+    rp.n_sets = 1;
     rp.sigma_world = sigma_world;
     rp.sigma_cutoff = sigma_cutoff;
     rp.scales = scales;
@@ -3004,7 +3065,7 @@ int launch_bilinear_warp_forward(const RasterParams& rp, const PointBlob& pb, co
     if (rc != INPC_OK) return rc;
     const int W = rp.v.width, H = rp.v.height;
     // tiles without instances are not work items: their pixels are cleared here
-    const size_t n_px = (size_t)W * H;
+    const size_t n_px = (size_t)W * H * rp.n_sets;
     INPC_CUDA_TRY(cudaMemsetAsync(image, 0, sizeof(float) * 4 * n_px, stream));
     INPC_CUDA_TRY(cudaMemsetAsync(alpha, 0, sizeof(float) * n_px, stream));
     if (KIND == BLEND_INFER) INPC_CUDA_TRY(cudaMemsetAsync(depth, 0, sizeof(float) * n_px, stream));
@@ -3016,20 +3077,20 @@ int launch_bilinear_warp_forward(const RasterParams& rp, const PointBlob& pb, co
     const unsigned threads = kWarpBlendWarps * 32;
     blend_bilinear_warp_forward_kernel<PASS_FIRST, KIND><<<grid, threads, 0, stream>>>(
         ib.items0, ib.n_segments, ib.n_segments + 2, keys, ids, pb.rec, ib.seg_T, ib.seg_C, ib.seg_Z, ib.seg_E,
-        image, depth, alpha, blending_weights, kept0, kept1, ib.n_kept, W, H, rp.gw);
+        image, depth, alpha, blending_weights, kept0, kept1, ib.n_kept, W, H, rp.gw, rp.gh);
     INPC_LAUNCH_CHECK("blend_bilinear_warp_forward_kernel (first segments)");
     blend_bilinear_warp_forward_kernel<PASS_PRODUCT, KIND><<<grid, threads, 0, stream>>>(
         ib.items1, ib.n_segments, ib.n_segments + 3, keys, ids, pb.rec, ib.seg_T, ib.seg_C, ib.seg_Z, ib.seg_E,
-        image, depth, alpha, blending_weights, kept0, kept1, ib.n_kept, W, H, rp.gw);
+        image, depth, alpha, blending_weights, kept0, kept1, ib.n_kept, W, H, rp.gw, rp.gh);
     INPC_LAUNCH_CHECK("blend_bilinear_warp_forward_kernel (products)");
     warp_blend_prefix_kernel<<<grid, threads, 0, stream>>>(ib.items0, ib.n_segments, ib.seg_T);
     INPC_LAUNCH_CHECK("warp_blend_prefix_kernel");
     blend_bilinear_warp_forward_kernel<PASS_REST, KIND><<<grid, threads, 0, stream>>>(
         ib.items1, ib.n_segments, ib.n_segments + 4, keys, ids, pb.rec, ib.seg_T, ib.seg_C, ib.seg_Z, ib.seg_E,
-        image, depth, alpha, blending_weights, kept0, kept1, ib.n_kept, W, H, rp.gw);
+        image, depth, alpha, blending_weights, kept0, kept1, ib.n_kept, W, H, rp.gw, rp.gh);
     INPC_LAUNCH_CHECK("blend_bilinear_warp_forward_kernel (later segments)");
     warp_blend_combine_kernel<KIND><<<grid, threads, 0, stream>>>(ib.items0, ib.n_segments, ib.seg_C, ib.seg_Z, ib.seg_E,
-                                                                      image, depth, alpha, W, H, rp.gw);
+                                                                      image, depth, alpha, W, H, rp.gw, rp.gh);
     INPC_LAUNCH_CHECK("warp_blend_combine_kernel");
     return INPC_OK;
 }
@@ -3052,7 +3113,7 @@ template <int T, int KIND>
 int launch_bilinear_forward(const RasterParams& rp, const PointBlob& pb, const InstanceBlob& ib, const uint32_t* ids, float* image,
                             float* depth, float* alpha, float* blending_weights, cudaStream_t stream) {
     constexpr int IPT = BlendConfig<T>::kIpt;
-    const int n_tiles = rp.gw * rp.gh;
+    const int n_tiles = rp.gw * rp.gh * rp.n_sets;
     const int W = rp.v.width, H = rp.v.height;
     const unsigned grid = (unsigned)ib.max_segments;
     blend_bilinear_transmittance_kernel<T, IPT><<<grid, T * T, 0, stream>>>(ib.segs, ib.n_segments, ids, pb.rec, ib.seg_T, W, H, rp.gw);
@@ -3089,7 +3150,7 @@ int launch_bilinear_backward(const RasterParams& rp, const PointBlob& pb, const 
 template <int T, int KIND>
 int launch_gaussian_forward(const RasterParams& rp, const PointBlob& pb, const InstanceBlob& ib, const uint32_t* ids, float* image,
                             float* depth, float* alpha, float* blending_weights, float threshold, cudaStream_t stream) {
-    const int n_tiles = rp.gw * rp.gh;
+    const int n_tiles = rp.gw * rp.gh * rp.n_sets;
     const int W = rp.v.width, H = rp.v.height;
     const unsigned grid = (unsigned)ib.max_segments;
     const float neg_log_threshold = -logf(threshold);
@@ -3110,7 +3171,7 @@ template <int KIND>
 int launch_blend_forward(int mode, const RasterParams& rp, const PointBlob& pb, const InstanceBlob& ib, const inpc_raster_state* st,
                          float* image, float* depth, float* alpha, float* blending_weights, float threshold,
                          cudaStream_t stream) {
-    const int n_tiles = rp.gw * rp.gh;
+    const int n_tiles = rp.gw * rp.gh * rp.n_sets;
     const int t_alt = tile_buffer_of(st, n_tiles);
     const uint32_t* ids = ib.ids[t_alt];
     StageScope scope(STAGE_BLEND_FWD, stream);
@@ -3131,7 +3192,7 @@ int launch_rows_forward(const RasterParams& rp, const PointBlob& pb, const Insta
         const int rc_attr = opt_in_dynamic_smem(blend_rows_forward_kernel<T, C4, KIND>, smem, attr_set);
         if (rc_attr != INPC_OK) return rc_attr;
     }
-    const int n_tiles = rp.gw * rp.gh;
+    const int n_tiles = rp.gw * rp.gh * rp.n_sets;
     const int W = rp.v.width, H = rp.v.height;
     const unsigned grid = (unsigned)ib.max_segments;
     blend_bilinear_transmittance_kernel<T, 1><<<grid, T * T, 0, stream>>>(ib.segs, ib.n_segments, ids, pb.rec, ib.seg_T, W, H, rp.gw);
@@ -3250,7 +3311,7 @@ extern "C" int inpc_rasterize_backward(const inpc_raster_state* state, const inp
     rc = begin_index_checks(n, stream);
     if (rc != INPC_OK) return rc;
     const RasterParams rp = make_params(view, state->tile_size, 0.0f, 3.0f, nullptr);
-    const int n_tiles = rp.gw * rp.gh;
+    const int n_tiles = rp.gw * rp.gh * rp.n_sets;
     const PointBlob pb = carve_point_blob(state->point_blob, n, state->mode);
     const InstanceBlob ib = carve_instance_blob(state->instance_blob, instance_capacity(state), n_tiles, state->tile_size, state->mode, false);
     const uint32_t* ids = ib.ids[tile_buffer_of(state, n_tiles)];
@@ -3351,6 +3412,49 @@ extern "C" int inpc_render_preextracted(int mode, int tile_size, const inpc_view
     return rc != INPC_OK ? rc : end_index_checks(stream);
 }
 
+extern "C" int inpc_render_multi(int tile_size, const inpc_view* view, int n_sets, const int64_t* n_points, const float* const* positions,
+                                 const void* const* features_raw, float* images, float* depths, float* alphas,
+                                 inpc_alloc_fn alloc_point, inpc_alloc_fn alloc_instance, void* alloc_user, void* stream_) {
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    if (n_sets < 1 || n_sets > kMaxSets) { set_error("inpc_render_multi: n_sets=%d outside [1, %d]", n_sets, kMaxSets); return INPC_E_INVALID; }
+    if (!n_points || !positions || !features_raw || !alloc_point || !alloc_instance || !images || !depths || !alphas) {
+        set_error("inpc_render_multi: null argument");
+        return INPC_E_INVALID;
+    }
+    if (tile_size != 8) { set_error("inpc_render_multi: bilinear splats on 8x8 tiles only (tile_size %d)", tile_size); return INPC_E_INVALID; }
+    PointSets ps;
+    ps.count = n_sets;
+    int64_t cursor = 0;
+    for (int j = 0; j < n_sets; ++j) {
+        if (n_points[j] < 0 || (n_points[j] > 0 && (!positions[j] || !features_raw[j]))) { set_error("inpc_render_multi: bad set %d", j); return INPC_E_INVALID; }
+        ps.start[j] = cursor;
+        ps.size[j] = n_points[j];
+        ps.positions[j] = positions[j];
+        ps.features[j] = features_raw[j];
+        ps.opacities[j] = nullptr;
+        cursor = (cursor + n_points[j] + kSetAlign - 1) / kSetAlign * kSetAlign;   // every set starts a block of the input passes
+    }
+    ps.start[n_sets] = cursor;
+    const int64_t n_virtual = cursor;
+    int rc = check_view(view, tile_size, INPC_MODE_BILINEAR, n_virtual);
+    if (rc != INPC_OK) return rc;
+    RasterParams rp = make_params(view, tile_size, 0.0f, 3.0f, nullptr);
+    rp.n_sets = n_sets;
+    // the stacked grid has to fit what a single image may use: tile indices in 24 bits, tile rows in 11
+    if ((int64_t)rp.gw * rp.gh * n_sets > ((int64_t)1 << kTileKeyBits) || (int64_t)rp.gh * n_sets > kMaxCodedTileRows) {
+        set_error("inpc_render_multi: %d images of %dx%d exceed the stacked tile grid", n_sets, view->width, view->height);
+        return INPC_E_INVALID;
+    }
+    inpc_raster_state st;
+    PointBlob pb;
+    InstanceBlob ib;
+    rc = run_front<INPC_MODE_BILINEAR, VAR_RAW37>(rp, n_virtual, nullptr, nullptr, nullptr, alloc_point, alloc_instance, alloc_user, &st, true, &pb, &ib,
+                                                  stream, "inpc_render_multi", 1, &ps);
+    if (rc != INPC_OK) return rc;
+    rc = launch_blend_forward<BLEND_INFER>(INPC_MODE_BILINEAR, rp, pb, ib, &st, images, depths, alphas, nullptr, 0.0f, stream);
+    return rc != INPC_OK ? rc : end_index_checks(stream);
+}
+
 namespace {
 int check_rows(const inpc_view* view, int tile_size, int64_t n, int channels) {
     const int rc = check_view(view, tile_size, INPC_MODE_BILINEAR, n);
@@ -3413,7 +3517,7 @@ extern "C" int inpc_rasterize_rows_backward(const inpc_raster_state* state, cons
     }
     if (n == 0) return INPC_OK;
     const RasterParams rp = make_params(view, state->tile_size, 0.0f, 3.0f, nullptr);
-    const int n_tiles = rp.gw * rp.gh;
+    const int n_tiles = rp.gw * rp.gh * rp.n_sets;
     const PointBlob pb = carve_point_blob(state->point_blob, n, state->mode);
     const InstanceBlob ib = carve_instance_blob(state->instance_blob, instance_capacity(state), n_tiles, state->tile_size, state->mode, false, channels / 4, true);
     const uint32_t* ids = ib.ids[tile_buffer_of(state, n_tiles)];

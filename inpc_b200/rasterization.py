@@ -327,6 +327,38 @@ class INPCRasterizer(torch.nn.Module):
         return image, depth, alpha
 
     @torch.no_grad()
+    def render_multi(self, view, sample_sets):
+        """Bilinear inference over several sample sets `(positions (N_j,3) f32, features_raw (N_j,37) f16)` of one view
+        in ONE launch sequence: returns images (k,4,H,W), depths (k,1,H,W), alphas (k,1,H,W), set by set bit for bit what
+        `render` gives.  Needs 8x8 tiles and at most 8 sets."""
+        if self.tile_size != 8:
+            raise ValueError("render_multi needs tile_size 8")
+        s = self.extract_settings(view, 0)
+        sets = [(self._render_common(p), _cuda_f16(f, "features_raw")) for p, f in sample_sets]
+        k = len(sets)
+        if not 1 <= k <= 8:
+            raise ValueError(f"render_multi takes 1 to 8 sample sets, got {k}")
+        for p, f in sets:
+            if f.shape != (p.shape[0], 37):
+                raise ValueError(f"features_raw must be (N,37), got {tuple(f.shape)}")
+        dev = sets[0][0].device
+        with torch.cuda.device(dev):
+            varg = _ViewArg(s, dev)
+            images = torch.empty((k, 4, s.height, s.width), dtype=torch.float32, device=dev)
+            depths = torch.empty((k, 1, s.height, s.width), dtype=torch.float32, device=dev)
+            alphas = torch.empty((k, 1, s.height, s.width), dtype=torch.float32, device=dev)
+            n_points = (C.c_int64 * k)(*[p.shape[0] for p, _ in sets])
+            pos_ptrs = (C.c_void_p * k)(*[p.data_ptr() if p.numel() else 0 for p, _ in sets])
+            feat_ptrs = (C.c_void_p * k)(*[f.data_ptr() if f.numel() else 0 for _, f in sets])
+            blobs = _Blobs(dev)
+            _check(_cabi.lib().inpc_render_multi(self.tile_size, C.byref(varg.c), k, n_points, pos_ptrs, feat_ptrs, _ptr(images),
+                                                 _ptr(depths), _ptr(alphas), blobs.cb_point, blobs.cb_instance, None, _stream()), blobs)
+            for b in (blobs.point, blobs.instance):
+                if b is not None:
+                    b.record_stream(torch.cuda.current_stream())
+        return images, depths, alphas
+
+    @torch.no_grad()
     def render_preextracted(self, view, mode: int, positions: torch.Tensor, features: torch.Tensor,
                             opacities: torch.Tensor, scales: torch.Tensor | None = None,
                             sigma_world_scale: float = 1.0, sigma_cutoff: float = 3.0):

@@ -126,3 +126,34 @@ def test_ring_buffer_and_multisampled_render():
         ring.read_idx = 0
         f2, d2, a2, s2 = render_multisampled(rast, v, 0, ring, bg, 1.0, 3.0, premult, n_streams=3)
         assert torch.equal(f2, f) and torch.equal(d2, d) and torch.equal(a2, a) and torch.equal(s2, s)
+        # ... and neither does rendering all sets with ONE batched call (one cull / sort / blend sequence for all of them)
+        ring.read_idx = 0
+        f3, d3, a3, s3 = render_multisampled(rast, v, 0, ring, bg, 1.0, 3.0, premult, batched=True)
+        assert torch.equal(f3, f) and torch.equal(d3, d) and torch.equal(a3, a) and torch.equal(s3, s)
+
+
+def test_batched_multi_set_render_equals_per_set_render():
+    """inpc_render_multi against inpc_render, set by set and bit for bit: sets of different sizes (none a multiple of
+    the internal alignment, one empty), clustered points whose tile lists span several segments, an image whose
+    height is not a multiple of the tile edge, so that the rows of one set's tile grid end inside a tile."""
+    import inpc_b200
+    from inpc_b200.views import look_at_view
+    view = look_at_view((0.3, 0.2, 2.8), (0.0, 0.0, 0.0), 333, 205, 260.0, 250.0).to(DEV)
+    gen = torch.Generator().manual_seed(21)
+    sizes = [70_001, 0, 33_333, 120_777, 1]
+    sets = []
+    for n in sizes:
+        cluster = torch.randn((n, 3), generator=gen) * torch.tensor([0.05, 0.05, 0.4])
+        spread = (torch.rand((n, 3), generator=gen) * 2 - 1) * 1.3
+        pos = torch.where(torch.rand((n, 1), generator=gen) < 0.7, cluster, spread).contiguous()
+        raw = torch.cat([torch.randn((n, 1), generator=gen) * 2 - 2, torch.randn((n, 36), generator=gen) * 0.5], dim=1).to(torch.float16)
+        sets.append((pos.to(DEV), raw.contiguous().to(DEV)))
+    rast = inpc_b200.INPCRasterizer(tile_size=8)
+    images, depths, alphas = rast.render_multi(view, sets)
+    assert images.shape == (len(sizes), 4, 205, 333)
+    for j, (pos, raw) in enumerate(sets):
+        img, dep, alp = rast.render(view, 0, pos, raw, 1.0, 3.0)
+        assert torch.equal(images[j], img) and torch.equal(depths[j], dep) and torch.equal(alphas[j], alp), f"set {j}"
+    assert float(alphas[0].max()) == 1.0 and float(alphas[1].abs().max()) == 0.0      # saturated pixels; the empty set is blank
+    with pytest.raises(ValueError):
+        rast.render_multi(view, sets * 2)                                              # more than 8 sets
