@@ -58,7 +58,7 @@ def parse_args():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-side", action="store_true", help="skip the side workloads (configs 2 and 4, feature rows) at the end of a 1-GPU run")
     ap.add_argument("--streams", type=int, default=4, help="CUDA streams a rank pipelines its views over (1 = one view at a time)")
-    ap.add_argument("--workload", default="config1", choices=["config1", "config2", "config4", "config4_rows32", "rows16", "rows32"],
+    ap.add_argument("--workload", default="config1", choices=["config1", "config2", "config4", "config4_rows32", "rows16", "rows32", "multisample4", "multisample4_batched"],
                     help="config1 is the headline (default); the others are single-GPU side measurements, one JSON line each")
     return ap.parse_args()
 
@@ -401,7 +401,7 @@ def run_ours(args):
     }
     if world == 1 and not args.no_side:
         side = {}
-        for name in ("config2", "config4", "config4_rows32", "rows16", "rows32"):
+        for name in ("config2", "config4", "config4_rows32", "rows16", "rows32", "multisample4", "multisample4_batched"):
             try:
                 torch.cuda.empty_cache()
                 side[name] = side_workload(name, args.tile, warmup=3, reps=6, points=args.points)
@@ -507,7 +507,7 @@ def run_reference(args):
     if not args.no_side:
         side = {}
         del wl
-        for name in ("config2", "config4", "config4_rows32", "rows16", "rows32"):
+        for name in ("config2", "config4", "config4_rows32", "rows16", "rows32", "multisample4", "multisample4_batched"):
             try:
                 torch.cuda.empty_cache()
                 side[name] = side_workload(name, 8, warmup=3, reps=6, points=args.points, impl="reference")
@@ -520,6 +520,8 @@ def run_reference(args):
 # ---------------------------------------------------------------------------------------------------
 SIDE_METRICS = {
     "config2": ("frames/s", "render_preextracted frames/s at 2^25 points, 1920x1080 (config 2)"),
+    "multisample4": ("frames/s", "multisampled inference frames/s, 4 sets of 2^23 expected samples of config 1, one stream per set"),
+    "multisample4_batched": ("frames/s", "multisampled inference frames/s, 4 sets of 2^23 expected samples of config 1, two batched renders of two sets on two streams"),
     "config4": (UNIT, "fwd+bwd Mpoints/s at 2^24 skewed points, 3840x2160, 36 x fp16 SH -> 4 channels (config 4 in the reference's layout)"),
     "config4_rows32": (UNIT, "fwd+bwd Mpoints/s at 2^24 skewed points, 3840x2160, 32 fp32 channels (config 4 as stated)"),
     "rows16": (UNIT, "fwd+bwd Mpoints/s at 2^23 points per view, 1237x822, 16 fp32 channels, incl. sampling"),
@@ -533,6 +535,8 @@ def side_workload(name: str, tile: int, warmup: int, reps: int, points: int = N_
     config4         skewed stress case, 2^24 points, 3840x2160, fwd+bwd, SH layout       -> Mpoints/s
     config4_rows32  the same with 32 fp32 feature channels                               -> Mpoints/s
     rows16 / rows32 config 1 with (N,C) fp32 feature rows, fwd+bwd incl. sampling        -> Mpoints/s
+    multisample4 / multisample4_batched   inference over 4 sample sets of config 1's octree (raw 37-half features,
+                    accumulate + background compose): one render per set on 4 streams / two batched renders on 2 streams -> frames/s
     impl = "reference" runs the reference's own CUDA backend where it can (config 2)."""
     import torch
     import synthetic_workloads as syn
@@ -542,6 +546,7 @@ def side_workload(name: str, tile: int, warmup: int, reps: int, points: int = N_
     if impl == "reference":
         if name != "config2":
             why = ("the reference's 16-bit tile key overflows at 3840x2160 (129,600 tiles of 8x8 pixels)" if name.startswith("config4")
+                   else "not wired up for the reference arm" if name.startswith("multisample")
                    else "the reference has no fp32 feature-row layout")
             return {"metric": metric, "unavailable": why}
         sys.path.insert(0, str(ROOT / "oracle"))
@@ -564,6 +569,23 @@ def side_workload(name: str, tile: int, warmup: int, reps: int, points: int = N_
 
             def step():
                 rast.render_preextracted(view, 0, pos, feats, opac)
+        elif name in ("multisample4", "multisample4_batched"):
+            from inpc_b200.compose import render_multisampled
+            c = syn.config1(n_samples=points, n_leaves=N_LEAVES)
+            view, tree = c["view"].to(device), c["tree"].to(device)
+            del c
+            sampler = ProbabilityFieldSampler(0)
+            gd = torch.Generator(device=device).manual_seed(3)
+            sets = []
+            for _ in range(4):
+                pos = sampler.generate_expected_samples(tree.centers, tree.levels, tree.weights, view, points, 1, tree.initial_size)
+                sets.append((pos, (torch.randn((pos.shape[0], 37), generator=gd, device=device) * 0.5).to(torch.float16)))
+            n_points = sum(p.shape[0] for p, _ in sets)
+            bg = torch.zeros((4, view.camera.height, view.camera.width), device=device)
+            batched = name.endswith("batched")
+
+            def step():
+                render_multisampled(rast, view, 0, sets, bg, n_streams=2 if batched else 4, batched=batched)
         elif name in ("config4", "config4_rows32"):
             c = syn.config4()
             view, pos, opac = c["view"].to(device), c["positions"].to(device), c["opacities"].to(device)

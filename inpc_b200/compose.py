@@ -161,7 +161,8 @@ def render_multisampled(rasterizer, view, mode: int, sample_sets, background: to
     composed over `background`.  `sample_sets` is a list of pairs or a filled `MultisamplingRingBuffer`.
     With `n_streams > 1` the sets are rasterised concurrently on that many CUDA streams (they are
     independent; the accumulation order, and hence the result, stays that of the list).  `batched` (bilinear splats,
-    8x8 tiles, at most 8 sets) renders all sets with one `render_multi` call instead: same bits, one launch sequence.
+    8x8 tiles, at most 8 sets) renders all sets with one `render_multi` call instead: same bits, one launch sequence;
+    with `n_streams > 1` as well, the sets are split into that many groups (of two sets at least), one batched call each.
     Returns (feature_image, depth, alpha, alpha_sum)."""
     if isinstance(sample_sets, MultisamplingRingBuffer):
         ring = sample_sets
@@ -170,10 +171,28 @@ def render_multisampled(rasterizer, view, mode: int, sample_sets, background: to
         sets = list(sample_sets)
     acc = MultisampleAccumulator(len(sets), average_with_premultiplied_alpha)
     if batched and mode == 0 and 2 <= len(sets) <= 8 and getattr(rasterizer, "tile_size", 0) == 8:
-        # one launch sequence for all sets (culled, sorted and blended together), then the same accumulation, set by set
-        images, depths, alphas = rasterizer.render_multi(view, sets)
-        for j in range(len(sets)):
-            acc.add(images[j], depths[j], alphas[j])
+        # one launch sequence per group of sets (culled, sorted and blended together), then the same accumulation, set by set
+        n_groups = max(1, min(n_streams, len(sets) // 2))
+        if n_groups == 1:
+            images, depths, alphas = rasterizer.render_multi(view, sets)
+            for j in range(len(sets)):
+                acc.add(images[j], depths[j], alphas[j])
+            return acc.resolve(background)
+        main = torch.cuda.current_stream()
+        streams = _side_streams(sets[0][0].device, n_groups)
+        bounds = [len(sets) * g // n_groups for g in range(n_groups + 1)]
+        rendered = []
+        for g, s in enumerate(streams):
+            s.wait_stream(main)
+            with torch.cuda.stream(s):
+                rendered.append(rasterizer.render_multi(view, sets[bounds[g]:bounds[g + 1]]))
+        for s in streams:
+            main.wait_stream(s)
+        for images, depths, alphas in rendered:
+            for t in (images, depths, alphas):
+                t.record_stream(main)
+            for j in range(images.shape[0]):
+                acc.add(images[j], depths[j], alphas[j])
         return acc.resolve(background)
     if n_streams <= 1 or len(sets) < 2:
         for positions, features_raw in sets:

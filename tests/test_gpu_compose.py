@@ -157,3 +157,10 @@ def test_batched_multi_set_render_equals_per_set_render():
     assert float(alphas[0].max()) == 1.0 and float(alphas[1].abs().max()) == 0.0      # saturated pixels; the empty set is blank
     with pytest.raises(ValueError):
         rast.render_multi(view, sets * 2)                                              # more than 8 sets
+    # the composed frame: per set, batched, and batched in two groups on two streams
+    from inpc_b200.compose import render_multisampled
+    bg = torch.randn((4, 205, 333), generator=gen).to(DEV)
+    one_by_one = render_multisampled(rast, view, 0, sets, bg)
+    for kw in (dict(batched=True), dict(batched=True, n_streams=2)):
+        frame = render_multisampled(rast, view, 0, sets, bg, **kw)
+        assert all(torch.equal(x, y) for x, y in zip(frame, one_by_one)), kw
