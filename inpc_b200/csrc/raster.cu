@@ -1257,9 +1257,12 @@ constexpr size_t backward_smem_bytes() {
 constexpr int kWarpBlendWarps = 8;        // warps per block; every warp works on items of its own
 constexpr int kQueueCap = 256;            // ring of candidate point ids per warp: >= 31 left over + 128 of one filter step
 constexpr int kFilterKeys = 4;            // keys per lane and filter step
-// Measured on B200 (2^23 clustered samples, 1237x822; forward / backward stage in microseconds): uniform segments of
-// 256: 815 / 539, 512: 597 / 401, 1024: 494 / 339, 2048: 464 / 325, 4096: 507 / 354 (the first pass is bound by its
-// longest item), 8192: 566 / 376; first 512 + later 2048: 478 / 300, first 1024 + later 4096: 471 / 308.
+// Measured on B200 (2^23 clustered samples, 1237x822; forward / backward stage in microseconds), first + later segment:
+// 1024 + 4096: 422 / 276, 1024 + 2048: 439 / 268, 512 + 4096: 437 / 297, 512 + 2048: 458 / 274, 1024 + 1024: 488 / 291,
+// 512 + 1024: 518 / 283, 256 + 2048: 469 / 283.  Per-item timestamps of the same run: every pass is full (about 3000 of
+// the 3552 resident warps busy) for its first half and then drains for as long again while the longest items finish at
+// 1.0 - 1.4 us per batch; shorter segments shorten that tail but add more work (more lists to filter, more states to
+// carry) than they save.
 constexpr unsigned kFirstSegment = 1024;    // instances in a tile's first segment
 constexpr unsigned kLaterSegment = 4096;    // ... and in every later one
 constexpr int kBatchFragments = 128;      // 32 instances x 4 fragments
@@ -1358,35 +1361,59 @@ __global__ void __launch_bounds__(256) warp_items_fill_kernel(const uint2* __res
     }
 }
 
+// Asynchronous copies (global -> shared, 16 bytes, not through registers) and their completion groups.
+__device__ __forceinline__ void async_copy_16(void* smem_dst, const void* gmem_src) {
+    const unsigned d = (unsigned)__cvta_generic_to_shared(smem_dst);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(gmem_src) : "memory");
+}
+__device__ __forceinline__ void async_copy_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void async_copy_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+// A warp walks its list one batch of 32 instances at a time, and a batch cannot start before its 32 records have
+// arrived from DRAM (gathers, a microsecond or two under load).  Measured with one batch in flight: 2 - 3 us per
+// batch whatever the load on the SM, i.e. the items with the longest lists -- which set the duration of a pass --
+// ran at the speed of one memory round trip per batch.  So the records of the next kGatherDepth - 1 batches are
+// kept in flight, copied asynchronously into a ring in shared memory.
+constexpr int kGatherDepth = 4;   // power of two
+constexpr int kIdsAhead = 3;      // later segments: batches whose point ids are loaded ahead of their gather
+
 // Shared memory of one warp of the forward passes.
-template <bool BLEND, bool WEIGHTS, bool DEPTH>
-struct WarpForwardSmem {
+template <bool BLEND, bool WEIGHTS>
+struct __align__(16) WarpForwardSmem {
+    float4 ring_a[kGatherDepth][32];                 // records of the batches in flight: position, alpha, depth ...
+    float4 ring_f[BLEND ? kGatherDepth : 1][32];     // ... and features
+    float2 frag[kBatchFragments];                    // fragments in per-pixel order: alpha, lane of the staged instance
+    float frag_seen[WEIGHTS ? kBatchFragments : 1];  // transmittance the fragment met (0: it was dropped)
+    uint32_t ring_id[kGatherDepth][32];              // point ids of the batches in flight (0xFFFFFFFF: no instance)
     unsigned mask[32];                               // per pixel: staged instances with a fragment there
     unsigned off[32];                                // per pixel: first slot of its fragment list
-    float frag_alpha[kBatchFragments];               // fragments in per-pixel order
-    float4 frag_feat[BLEND ? kBatchFragments : 1];
-    float frag_depth[DEPTH ? kBatchFragments : 1];
-    float frag_seen[WEIGHTS ? kBatchFragments : 1];  // transmittance the fragment met (0: it was dropped)
     uint32_t queue[kQueueCap];
 };
 
 template <int PASS, int KIND>
-__global__ void __launch_bounds__(kWarpBlendWarps * 32) blend_bilinear_warp_forward_kernel(
+constexpr size_t warp_forward_smem_bytes() {
+    return 256 * sizeof(unsigned long long) + kWarpBlendWarps * sizeof(WarpForwardSmem<PASS != PASS_PRODUCT, PASS != PASS_PRODUCT && KIND == BLEND_TRAIN>);
+}
+
+template <int PASS, int KIND>
+__global__ void __launch_bounds__(kWarpBlendWarps * 32, 3) blend_bilinear_warp_forward_kernel(
     const WarpItem* __restrict__ items, const uint32_t* __restrict__ counts, unsigned* __restrict__ ticket, const uint32_t* __restrict__ inst_keys,
     const uint32_t* __restrict__ inst_ids, const PointRec* __restrict__ rec, float* __restrict__ seg_T, float4* __restrict__ seg_C,
     float* __restrict__ seg_Z, float* __restrict__ seg_E, float* __restrict__ image, float* __restrict__ depth_image,
     float* __restrict__ alpha_image, float* __restrict__ blending_weights, uint32_t* kept0, uint32_t* kept1,
     uint32_t* __restrict__ n_kept, int width, int height, int gw, int gh) {
     constexpr unsigned kFull = 0xffffffffu;
+    constexpr unsigned kNoInstance = 0xffffffffu;
     constexpr bool kBlend = PASS != PASS_PRODUCT;               // colours and weights; PRODUCT only multiplies
     constexpr bool kWeights = kBlend && KIND == BLEND_TRAIN;
     constexpr bool kDepth = kBlend && KIND == BLEND_INFER;
-    using Smem = WarpForwardSmem<kBlend, kWeights, kDepth>;
-    __shared__ Smem s_all[kWarpBlendWarps];
-    __shared__ unsigned long long s_reach[256];     // key code -> pixels reached
+    using Smem = WarpForwardSmem<kBlend, kWeights>;
+    extern __shared__ __align__(16) unsigned char blend_smem[];
+    unsigned long long* s_reach = reinterpret_cast<unsigned long long*>(blend_smem);     // key code -> pixels reached
+    Smem& sm = reinterpret_cast<Smem*>(blend_smem + 256 * sizeof(unsigned long long))[threadIdx.x >> 5];
     const unsigned lane = lane_id();
     const unsigned lt_mask = (1u << lane) - 1u;
-    Smem& sm = s_all[threadIdx.x >> 5];
     s_reach[threadIdx.x] = key_pixels(threadIdx.x);
     sm.mask[lane] = 0u;   // the masks start at zero and every batch leaves them at zero again
     __syncthreads();
@@ -1427,180 +1454,192 @@ __global__ void __launch_bounds__(kWarpBlendWarps * 32) blend_bilinear_warp_forw
         unsigned done_w = __ballot_sync(kFull, done);   // bit l = pixel of lane l has stopped (warp-uniform)
 
         uint32_t* kept = half ? kept1 : kept0;
-        // ---- where the instances come from.  FIRST and PRODUCT filter the item's keys (loaded one step ahead of
-        // their use); REST blends the list PRODUCT compacted for this item (a superset of what is still alive at
-        // the true transmittance, see above), ids two batches ahead like the backward pass.
-        unsigned pos = rg.x;           // next key to load
-        bool loaded = false;
-        uint32_t kq[kFilterKeys], iq[kFilterKeys];
-        auto load_step = [&]() {
-#pragma unroll
-            for (int k = 0; k < kFilterKeys; ++k) {
-                const unsigned idx = pos + 32u * k + lane;
-                const bool ok = idx < rg.y;
-                kq[k] = ok ? __ldg(inst_keys + idx) : 0xFFFFFFFFu;   // code 0xFF reaches nothing
-                iq[k] = ok ? __ldg(inst_ids + idx) : 0u;
-            }
-            pos = min(pos + 32u * kFilterKeys, rg.y);
-            loaded = true;
-        };
-        unsigned q_head = 0, q_tail = 0;
-        auto fill = [&]() {
-            if (PASS == PASS_REST) return;
-            while (q_tail - q_head < 32u && loaded) {
-                uint32_t ck[kFilterKeys], ci[kFilterKeys];
-#pragma unroll
-                for (int k = 0; k < kFilterKeys; ++k) { ck[k] = kq[k]; ci[k] = iq[k]; }
-                loaded = false;
-                if (pos < rg.y) load_step();
+        unsigned n_out = 0;
+        if (done_w != kFull) {   // else: nothing in this list can have an effect, and it is not even read
+            // ---- where the instances come from.  FIRST and PRODUCT filter the item's keys (loaded one step ahead of
+            // their use); REST blends the list PRODUCT compacted for this item (a superset of what is still alive at
+            // the true transmittance, see above), its ids loaded kIdsAhead batches ahead of their gather.
+            unsigned pos = rg.x;           // next key to load
+            bool loaded = false;
+            uint32_t kq[kFilterKeys], iq[kFilterKeys];
+            auto load_step = [&]() {
 #pragma unroll
                 for (int k = 0; k < kFilterKeys; ++k) {
-                    const unsigned long long reach = s_reach[ck[k] >> kTileKeyBits];
-                    const bool keep = ((unsigned)(reach >> (32 * half)) & ~done_w) != 0u;
-                    const unsigned b = __ballot_sync(kFull, keep);
-                    if (keep) sm.queue[(q_tail + __popc(b & lt_mask)) & (kQueueCap - 1)] = ci[k];
-                    q_tail += __popc(b);
+                    const unsigned idx = pos + 32u * k + lane;
+                    const bool ok = idx < rg.y;
+                    kq[k] = ok ? __ldg(inst_keys + idx) : 0xFFFFFFFFu;   // code 0xFF reaches nothing
+                    iq[k] = ok ? __ldg(inst_ids + idx) : 0u;
                 }
-            }
-            __syncwarp();
-        };
-        int n_cur = 0, n_nxt = 0;
-        uint32_t id_cur = 0, id_nxt = 0, id_far = 0;
-        float4 a_cur, f_cur, a_nxt, f_nxt;
-        a_cur = f_cur = a_nxt = f_nxt = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (PASS == PASS_REST) {
-            q_tail = n_kept[sidx];     // length of PRODUCT's list; the list itself starts at kept[rg.x]
-            if (lane < q_tail) id_far = kept[rg.x + lane];
-        } else if (pos < rg.y) {
-            load_step();
-        }
-        auto gather_next = [&]() {
-            n_nxt = (int)min(32u, q_tail - q_head);
+                pos = min(pos + 32u * kFilterKeys, rg.y);
+                loaded = true;
+            };
+            unsigned q_head = 0, q_tail = 0;   // candidates [q_head, q_tail) wait for their gather
+            // (measured: a second filter step of keys in flight gains 10 % in the PRODUCT pass and loses as much in FIRST)
+            auto fill = [&]() {
+                while (PASS != PASS_REST && q_tail - q_head < 32u && loaded) {
+                    uint32_t ck[kFilterKeys], ci[kFilterKeys];
+#pragma unroll
+                    for (int k = 0; k < kFilterKeys; ++k) { ck[k] = kq[k]; ci[k] = iq[k]; }
+                    loaded = false;
+                    if (pos < rg.y) load_step();
+#pragma unroll
+                    for (int k = 0; k < kFilterKeys; ++k) {
+                        const unsigned long long reach = s_reach[ck[k] >> kTileKeyBits];
+                        const bool keep = ((unsigned)(reach >> (32 * half)) & ~done_w) != 0u;
+                        const unsigned b = __ballot_sync(kFull, keep);
+                        if (keep) sm.queue[(q_tail + __popc(b & lt_mask)) & (kQueueCap - 1)] = ci[k];
+                        q_tail += __popc(b);
+                    }
+                }
+                __syncwarp();
+            };
+            uint32_t idf[kIdsAhead];
             if (PASS == PASS_REST) {
-                id_nxt = id_far;
-                if (q_head + 32u + lane < q_tail) id_far = kept[rg.x + q_head + 32u + lane];
-            } else if ((int)lane < n_nxt) {
-                id_nxt = sm.queue[(q_head + lane) & (kQueueCap - 1)];
+                q_tail = n_kept[sidx];     // length of PRODUCT's list; the list itself starts at kept[rg.x]
+#pragma unroll
+                for (int k = 0; k < kIdsAhead; ++k) idf[k] = 32u * k + lane < q_tail ? kept[rg.x + 32u * k + lane] : 0u;
+            } else if (pos < rg.y) {
+                load_step();
             }
-            if ((int)lane < n_nxt) {
-                id_nxt = checked_point(id_nxt);
-                const float4* p = reinterpret_cast<const float4*>(rec + id_nxt);
-                a_nxt = __ldg(p);
-                if (kBlend) f_nxt = __ldg(p + 1);
-            }
-            q_head += (unsigned)n_nxt;
-        };
-        fill();
-        gather_next();
-        unsigned n_out = 0;
-        while (n_nxt > 0) {
-            n_cur = n_nxt; id_cur = id_nxt; a_cur = a_nxt; f_cur = f_nxt;
+            // the next (up to) 32 candidates become a batch: their records start to travel into `stage` of the ring
+            auto gather = [&](unsigned stage) {
+                const unsigned n = min(32u, q_tail - q_head);
+                uint32_t id = kNoInstance;
+                if (lane < n) {
+                    id = checked_point(PASS == PASS_REST ? idf[0] : sm.queue[(q_head + lane) & (kQueueCap - 1)]);
+                    const float4* p = reinterpret_cast<const float4*>(rec + id);
+                    async_copy_16(&sm.ring_a[stage][lane], p);
+                    if (kBlend) async_copy_16(&sm.ring_f[stage][lane], p + 1);
+                }
+                sm.ring_id[stage][lane] = id;
+                async_copy_commit();   // one group per batch, empty or not: the waits below count groups
+                if (PASS == PASS_REST) {
+#pragma unroll
+                    for (int k = 0; k + 1 < kIdsAhead; ++k) idf[k] = idf[k + 1];
+                    const unsigned nxt = q_head + 32u * kIdsAhead + lane;
+                    idf[kIdsAhead - 1] = nxt < q_tail ? kept[rg.x + nxt] : 0u;
+                }
+                q_head += n;
+            };
             fill();
-            gather_next();
-            if (PASS != PASS_REST) {
-                // the list this pass blended: FIRST's goes to the backward pass, PRODUCT's to REST
-                if ((int)lane < n_cur) kept[rg.x + n_out + lane] = id_cur;
-                n_out += (unsigned)n_cur;
-            }
-            // ---- lane j: the fragments of staged instance j
-            const int qx = __float2int_rd(a_cur.x - 0.5f) - px0;
-            const int qy = __float2int_rd(a_cur.y - 0.5f) - py0;
-            float al[4], wg[4];
-            int pix[4];
 #pragma unroll
-            for (int c = 0; c < 4; ++c) {
-                const int cx = qx + (c & 1), cy = qy + (c >> 1);
-                const float pcx = (float)(px0 + cx) + 0.5f, pcy = (float)(py0 + cy) + 0.5f;
-                const float dx = fabsf(a_cur.x - pcx), dy = fabsf(a_cur.y - pcy);
-                wg[c] = __saturatef(1.0f - dx) * __saturatef(1.0f - dy);
-                al[c] = a_cur.z * wg[c];
-                const int p = cy * 8 + cx;
-                const bool ok = (int)lane < n_cur && cx >= 0 && cx < 8 && cy >= 0 && cy < 4 && dx < 1.0f && dy < 1.0f &&
-                                !((done_w >> (p & 31)) & 1u);
-                pix[c] = ok ? p : -1;
-                if (ok) atomicOr(sm.mask + p, 1u << lane);
+            for (int st = 0; st + 1 < kGatherDepth; ++st) {
+                gather((unsigned)st);
+                fill();
             }
-            if (PASS == PASS_REST && kWeights) {
-                // what is still alive at the true transmittance goes on to the backward pass; written in place, behind
-                // the part of PRODUCT's list that has been read already
-                const bool live = (pix[0] & pix[1] & pix[2] & pix[3]) >= 0;
-                const unsigned b = __ballot_sync(kFull, live);
-                if (live) kept[rg.x + n_out + __popc(b & lt_mask)] = id_cur;
-                n_out += __popc(b);
-            }
-            __syncwarp();
-            // ---- per-pixel order: offset of every pixel's list, slot of every fragment
-            const unsigned my_mask = sm.mask[lane];
-            const unsigned cnt = __popc(my_mask);
-            const unsigned off = warp_inclusive_scan(cnt) - cnt;
-            sm.off[lane] = off;
-            __syncwarp();
-            int slot[4];
+            for (unsigned batch = 0;; ++batch) {
+                gather((batch + kGatherDepth - 1) & (kGatherDepth - 1));
+                async_copy_wait<kGatherDepth - 1>();   // all but the newest kGatherDepth - 1 groups: this batch has arrived
+                const unsigned stage = batch & (kGatherDepth - 1);
+                const uint32_t id_cur = sm.ring_id[stage][lane];
+                const bool staged = id_cur != kNoInstance;
+                if (__ballot_sync(kFull, staged) == 0u) break;   // batches are filled in order: nothing is left
+                const float4 a_cur = sm.ring_a[stage][lane];
+                fill();
+                // ---- lane j: the fragments of staged instance j
+                const int qx = __float2int_rd(a_cur.x - 0.5f) - px0;
+                const int qy = __float2int_rd(a_cur.y - 0.5f) - py0;
+                float al[4], wg[4];
+                int pix[4];
 #pragma unroll
-            for (int c = 0; c < 4; ++c) {
-                slot[c] = 0;
-                if (pix[c] >= 0) {
-                    slot[c] = (int)(sm.off[pix[c]] + __popc(sm.mask[pix[c]] & lt_mask));
-                    sm.frag_alpha[slot[c]] = al[c];
-                    if (kBlend) sm.frag_feat[slot[c]] = f_cur;
-                    if (kDepth) sm.frag_depth[slot[c]] = a_cur.w;
+                for (int c = 0; c < 4; ++c) {
+                    const int cx = qx + (c & 1), cy = qy + (c >> 1);
+                    const float pcx = (float)(px0 + cx) + 0.5f, pcy = (float)(py0 + cy) + 0.5f;
+                    const float dx = fabsf(a_cur.x - pcx), dy = fabsf(a_cur.y - pcy);
+                    wg[c] = __saturatef(1.0f - dx) * __saturatef(1.0f - dy);
+                    al[c] = a_cur.z * wg[c];
+                    const int p = cy * 8 + cx;
+                    const bool ok = staged && cx >= 0 && cx < 8 && cy >= 0 && cy < 4 && dx < 1.0f && dy < 1.0f &&
+                                    !((done_w >> (p & 31)) & 1u);
+                    pix[c] = ok ? p : -1;
+                    if (ok) atomicOr(sm.mask + p, 1u << lane);
                 }
-            }
-            __syncwarp();
-            // ---- every lane runs down the list of its own pixel, front to back
-            if (my_mask) sm.mask[lane] = 0u;
-            // The chain from one fragment to the next is one multiply (the transmittance); everything else of a step
-            // hangs off it.  The steps are therefore written without branches -- a stopped pixel selects its old
-            // values -- and in chunks whose loads are issued together, so that consecutive steps overlap in the
-            // pipeline instead of each waiting for its own shared-memory loads.
-            constexpr int kChunk = 4;
-            for (unsigned k0 = off; k0 < off + cnt; k0 += kChunk) {
-                float a[kChunk];
-                float4 f[kChunk];
-                float zd[kChunk];
-#pragma unroll
-                for (int u = 0; u < kChunk; ++u) {
-                    const unsigned k = min(k0 + u, off + cnt - 1u);   // the tail repeats the last slot: masked out below
-                    a[u] = sm.frag_alpha[k];
-                    if (kBlend) f[u] = sm.frag_feat[k];
-                    if (kDepth) zd[u] = sm.frag_depth[k];
+                if (PASS != PASS_REST || kWeights) {
+                    // What reaches a pixel that has not stopped goes into the list of this item: FIRST's list is the
+                    // backward pass's, PRODUCT's is blended by REST, REST's (what is still alive at the true
+                    // transmittance; written in place, behind the part of PRODUCT's list already read) the backward
+                    // pass's again.  The filter runs several batches ahead of the blend, so some of what it let
+                    // through is dead by now and is dropped here.
+                    const bool live = (pix[0] & pix[1] & pix[2] & pix[3]) >= 0;
+                    const unsigned b = __ballot_sync(kFull, live);
+                    if (live) kept[rg.x + n_out + __popc(b & lt_mask)] = id_cur;
+                    n_out += __popc(b);
                 }
+                __syncwarp();
+                // ---- per-pixel order: offset of every pixel's list, slot of every fragment
+                const unsigned my_mask = sm.mask[lane];
+                const unsigned cnt = __popc(my_mask);
+                const unsigned off = warp_inclusive_scan(cnt) - cnt;
+                sm.off[lane] = off;
+                __syncwarp();
+                int slot[4];
 #pragma unroll
-                for (int u = 0; u < kChunk; ++u) {
-                    const bool live = !done && k0 + u < off + cnt;
-                    if (kBlend) {
-                        const float bw = Tr * a[u];
-                        if (kWeights && k0 + u < off + cnt) sm.frag_seen[k0 + u] = live ? Tr : 0.0f;
-                        C0 = live ? C0 + bw * f[u].x : C0;
-                        C1 = live ? C1 + bw * f[u].y : C1;
-                        C2 = live ? C2 + bw * f[u].z : C2;
-                        C3 = live ? C3 + bw * f[u].w : C3;
-                        if (kDepth) Z = live ? Z + bw * zd[u] : Z;
-                        Tr = live ? Tr * (1.0f - a[u]) : Tr;
-                        done = done || Tr < kTransmittanceEps;
-                    } else {
-                        Tr = live ? Tr * (1.0f - a[u]) : Tr;
-                        done = done || T0 * Tr < kTransmittanceEps;
+                for (int c = 0; c < 4; ++c) {
+                    slot[c] = 0;
+                    if (pix[c] >= 0) {
+                        slot[c] = (int)(sm.off[pix[c]] + __popc(sm.mask[pix[c]] & lt_mask));
+                        sm.frag[slot[c]] = make_float2(al[c], __uint_as_float(lane));
                     }
                 }
-            }
-            __syncwarp();
-            if (kWeights) {
-                // blending weight of every staged instance: its (up to) four fragments in fixed corner order
-                if ((int)lane < n_cur) {
-                    float v[4];
+                __syncwarp();
+                // ---- every lane runs down the list of its own pixel, front to back
+                if (my_mask) sm.mask[lane] = 0u;
+                // The chain from one fragment to the next is one multiply (the transmittance); everything else of a step
+                // hangs off it.  The steps are therefore written without branches -- a stopped pixel selects its old
+                // values -- and in chunks whose loads are issued together, so that consecutive steps overlap in the
+                // pipeline instead of each waiting for its own shared-memory loads.
+                constexpr int kChunk = 4;
+                for (unsigned k0 = off; k0 < off + cnt; k0 += kChunk) {
+                    float a[kChunk];
+                    float4 f[kChunk];
+                    float zd[kChunk];
 #pragma unroll
-                    for (int c = 0; c < 4; ++c) {
-                        const float bw = pix[c] >= 0 ? sm.frag_seen[slot[c]] * al[c] : 0.0f;
-                        v[c] = bw > 0.0f ? bw * wg[c] : 0.0f;
+                    for (int u = 0; u < kChunk; ++u) {
+                        const unsigned k = min(k0 + u, off + cnt - 1u);   // the tail repeats the last slot: masked out below
+                        const float2 e = sm.frag[k];
+                        a[u] = e.x;
+                        if (kBlend) f[u] = sm.ring_f[stage][__float_as_uint(e.y)];
+                        if (kDepth) zd[u] = sm.ring_a[stage][__float_as_uint(e.y)].w;
                     }
-                    const float sum = ((v[0] + v[1]) + v[2]) + v[3];
-                    if (sum > 0.0f) atomicAdd(blending_weights + id_cur, sum);
+#pragma unroll
+                    for (int u = 0; u < kChunk; ++u) {
+                        const bool live = !done && k0 + u < off + cnt;
+                        if (kBlend) {
+                            const float bw = Tr * a[u];
+                            if (kWeights && k0 + u < off + cnt) sm.frag_seen[k0 + u] = live ? Tr : 0.0f;
+                            C0 = live ? C0 + bw * f[u].x : C0;
+                            C1 = live ? C1 + bw * f[u].y : C1;
+                            C2 = live ? C2 + bw * f[u].z : C2;
+                            C3 = live ? C3 + bw * f[u].w : C3;
+                            if (kDepth) Z = live ? Z + bw * zd[u] : Z;
+                            Tr = live ? Tr * (1.0f - a[u]) : Tr;
+                            done = done || Tr < kTransmittanceEps;
+                        } else {
+                            Tr = live ? Tr * (1.0f - a[u]) : Tr;
+                            done = done || T0 * Tr < kTransmittanceEps;
+                        }
+                    }
                 }
+                __syncwarp();
+                if (kWeights) {
+                    // blending weight of every staged instance: its (up to) four fragments in fixed corner order
+                    if (staged) {
+                        float v[4];
+#pragma unroll
+                        for (int c = 0; c < 4; ++c) {
+                            const float bw = pix[c] >= 0 ? sm.frag_seen[slot[c]] * al[c] : 0.0f;
+                            v[c] = bw > 0.0f ? bw * wg[c] : 0.0f;
+                        }
+                        const float sum = ((v[0] + v[1]) + v[2]) + v[3];
+                        if (sum > 0.0f) atomicAdd(blending_weights + id_cur, sum);
+                    }
+                }
+                done_w = __ballot_sync(kFull, done);
+                __syncwarp();
+                if (done_w == kFull) break;   // every pixel has stopped: the rest of the list has no effect
             }
-            done_w = __ballot_sync(kFull, done);
+            async_copy_wait<0>();   // whatever is still travelling lands before the next item reuses the ring
             __syncwarp();
-            if (done_w == kFull) break;   // every pixel has stopped: the rest of the list has no effect
         }
         if ((PASS != PASS_REST || kWeights) && lane == 0) n_kept[sidx] = n_out;
 
@@ -1730,18 +1769,21 @@ __global__ void __launch_bounds__(kWarpBlendWarps * 32) warp_blend_combine_kerne
 }
 
 // Shared memory of one warp of the backward pass.
-struct WarpBackwardSmem {
-    unsigned mask[32];
-    unsigned off[32];
+struct __align__(16) WarpBackwardSmem {
+    float4 ring_a[kGatherDepth][32];        // records of the batches in flight (see the forward pass): position, alpha ...
+    float4 ring_f[kGatherDepth][32];        // ... and features
     float4 pixel_grad[32];                  // image gradient of the half's pixels
-    float frag_alpha[kBatchFragments];      // fragments in per-pixel order
-    float frag_rcp[kBatchFragments];        // 1 / max(1 - alpha, eps)
-    float4 frag_feat[kBatchFragments];
+    float2 frag[kBatchFragments];           // fragments in per-pixel order: alpha, 1 / max(1 - alpha, eps)
+    uint32_t frag_src[kBatchFragments];     // lane of the staged instance the fragment belongs to
     float frag_bw[kBatchFragments];         // blending weight the fragment got (0: it was dropped)
     float frag_dalpha[kBatchFragments];     // dL/dalpha of the fragment
+    uint32_t ring_id[kGatherDepth][32];     // point ids of the batches in flight (0xFFFFFFFF: no instance)
+    unsigned mask[32];
+    unsigned off[32];
 };
+constexpr size_t kWarpBackwardSmemBytes = kWarpBlendWarps * sizeof(WarpBackwardSmem);
 
-__global__ void __launch_bounds__(kWarpBlendWarps * 32) blend_bilinear_warp_backward_kernel(
+__global__ void __launch_bounds__(kWarpBlendWarps * 32, 3) blend_bilinear_warp_backward_kernel(
     const WarpItem* __restrict__ items0, const WarpItem* __restrict__ items1, const uint32_t* __restrict__ counts,
     unsigned* __restrict__ ticket, const uint32_t* __restrict__ kept0,
     const uint32_t* __restrict__ kept1, const uint32_t* __restrict__ n_kept, const PointRec* __restrict__ rec,
@@ -1749,10 +1791,11 @@ __global__ void __launch_bounds__(kWarpBlendWarps * 32) blend_bilinear_warp_back
     const float* __restrict__ grad_alpha, const float* __restrict__ image, const float* __restrict__ alpha_image,
     float4* __restrict__ slot_grad, unsigned* __restrict__ slot_mask, int width, int height, int gw) {
     constexpr unsigned kFull = 0xffffffffu;
-    __shared__ WarpBackwardSmem s_all[kWarpBlendWarps];
+    constexpr unsigned kNoInstance = 0xffffffffu;
+    extern __shared__ __align__(16) unsigned char blend_smem[];
     const unsigned lane = lane_id();
     const unsigned lt_mask = (1u << lane) - 1u;
-    WarpBackwardSmem& sm = s_all[threadIdx.x >> 5];
+    WarpBackwardSmem& sm = reinterpret_cast<WarpBackwardSmem*>(blend_smem)[threadIdx.x >> 5];
     sm.mask[lane] = 0u;
     __syncwarp();
     const unsigned n_first = __ldg(counts) * 2u;
@@ -1795,27 +1838,38 @@ __global__ void __launch_bounds__(kWarpBlendWarps * 32) blend_bilinear_warp_back
         sm.pixel_grad[lane] = g;
         unsigned done_w = __ballot_sync(kFull, done);
 
-        // ids two batches ahead, records one batch ahead
-        uint32_t id_cur = 0, id_nxt = 0, id_far = 0;
-        float4 a_cur, f_cur, a_nxt, f_nxt;
-        a_cur = f_cur = a_nxt = f_nxt = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (lane < n_list) id_nxt = checked_point(__ldg(list + lane));
-        if (32u + lane < n_list) id_far = checked_point(__ldg(list + 32u + lane));
-        if (lane < n_list) {
-            const float4* p = reinterpret_cast<const float4*>(rec + id_nxt);
-            a_nxt = __ldg(p);
-            f_nxt = __ldg(p + 1);
-        }
-        for (unsigned base = 0; base < n_list; base += 32u) {
-            const int n_cur = (int)min(32u, n_list - base);
-            id_cur = id_nxt; a_cur = a_nxt; f_cur = f_nxt;
-            id_nxt = id_far;
-            if (base + 32u + lane < n_list) {
-                const float4* p = reinterpret_cast<const float4*>(rec + id_nxt);
-                a_nxt = __ldg(p);
-                f_nxt = __ldg(p + 1);
+        // ids kIdsAhead batches ahead of their gather, records kGatherDepth - 1 batches ahead of their use
+        uint32_t idf[kIdsAhead];
+#pragma unroll
+        for (int k = 0; k < kIdsAhead; ++k) idf[k] = 32u * k + lane < n_list ? __ldg(list + 32u * k + lane) : 0u;
+        unsigned issued = 0;   // instances whose gather has started
+        auto gather = [&](unsigned stage) {
+            const unsigned n = min(32u, n_list - issued);
+            uint32_t id = kNoInstance;
+            if (lane < n) {
+                id = checked_point(idf[0]);
+                const float4* p = reinterpret_cast<const float4*>(rec + id);
+                async_copy_16(&sm.ring_a[stage][lane], p);
+                async_copy_16(&sm.ring_f[stage][lane], p + 1);
             }
-            if (base + 64u + lane < n_list) id_far = checked_point(__ldg(list + base + 64u + lane));
+            sm.ring_id[stage][lane] = id;
+            async_copy_commit();   // one group per batch, empty or not
+#pragma unroll
+            for (int k = 0; k + 1 < kIdsAhead; ++k) idf[k] = idf[k + 1];
+            const unsigned nxt = issued + 32u * kIdsAhead + lane;
+            idf[kIdsAhead - 1] = nxt < n_list ? __ldg(list + nxt) : 0u;
+            issued += n;
+        };
+#pragma unroll
+        for (int st = 0; st + 1 < kGatherDepth; ++st) gather((unsigned)st);
+        for (unsigned batch = 0;; ++batch) {
+            gather((batch + kGatherDepth - 1) & (kGatherDepth - 1));
+            async_copy_wait<kGatherDepth - 1>();
+            const unsigned stage = batch & (kGatherDepth - 1);
+            const uint32_t id_cur = sm.ring_id[stage][lane];
+            const bool staged = id_cur != kNoInstance;
+            if (__ballot_sync(kFull, staged) == 0u) break;
+            const float4 a_cur = sm.ring_a[stage][lane];
             // ---- lane j: the fragments of staged instance j
             const int qx = __float2int_rd(a_cur.x - 0.5f) - px0;
             const int qy = __float2int_rd(a_cur.y - 0.5f) - py0;
@@ -1829,7 +1883,7 @@ __global__ void __launch_bounds__(kWarpBlendWarps * 32) blend_bilinear_warp_back
                 wg[c] = __saturatef(1.0f - dx) * __saturatef(1.0f - dy);
                 al[c] = a_cur.z * wg[c];
                 const int p = cy * 8 + cx;
-                const bool ok = (int)lane < n_cur && cx >= 0 && cx < 8 && cy >= 0 && cy < 4 && dx < 1.0f && dy < 1.0f &&
+                const bool ok = staged && cx >= 0 && cx < 8 && cy >= 0 && cy < 4 && dx < 1.0f && dy < 1.0f &&
                                 !((done_w >> (p & 31)) & 1u);
                 pix[c] = ok ? p : -1;
                 if (ok) atomicOr(sm.mask + p, 1u << lane);
@@ -1846,9 +1900,8 @@ __global__ void __launch_bounds__(kWarpBlendWarps * 32) blend_bilinear_warp_back
                 slot[c] = 0;
                 if (pix[c] >= 0) {
                     slot[c] = (int)(sm.off[pix[c]] + __popc(sm.mask[pix[c]] & lt_mask));
-                    sm.frag_alpha[slot[c]] = al[c];
-                    sm.frag_rcp[slot[c]] = 1.0f / fmaxf(1.0f - al[c], kOneMinusAlphaEps);
-                    sm.frag_feat[slot[c]] = f_cur;
+                    sm.frag[slot[c]] = make_float2(al[c], 1.0f / fmaxf(1.0f - al[c], kOneMinusAlphaEps));
+                    sm.frag_src[slot[c]] = lane;
                 }
             }
             __syncwarp();
@@ -1861,9 +1914,10 @@ __global__ void __launch_bounds__(kWarpBlendWarps * 32) blend_bilinear_warp_back
 #pragma unroll
                 for (int u = 0; u < kChunk; ++u) {
                     const unsigned k = min(k0 + u, off + cnt - 1u);
-                    a[u] = sm.frag_alpha[k];
-                    rcp[u] = sm.frag_rcp[k];
-                    f[u] = sm.frag_feat[k];
+                    const float2 e = sm.frag[k];
+                    a[u] = e.x;
+                    rcp[u] = e.y;
+                    f[u] = sm.ring_f[stage][sm.frag_src[k]];
                 }
 #pragma unroll
                 for (int u = 0; u < kChunk; ++u) {
@@ -1886,7 +1940,7 @@ __global__ void __launch_bounds__(kWarpBlendWarps * 32) blend_bilinear_warp_back
             }
             __syncwarp();
             // gradients of every staged instance: its (up to) four fragments in fixed corner order
-            if ((int)lane < n_cur) {
+            if (staged) {
                 float4 sf = make_float4(0.f, 0.f, 0.f, 0.f);
                 float so = 0.0f;
 #pragma unroll
@@ -1923,6 +1977,8 @@ __global__ void __launch_bounds__(kWarpBlendWarps * 32) blend_bilinear_warp_back
             __syncwarp();
             if (done_w == kFull) break;
         }
+        async_copy_wait<0>();   // whatever is still travelling lands before the next item reuses the ring
+        __syncwarp();
     }
 }
 
@@ -3057,6 +3113,31 @@ int warp_blend_grid(unsigned* grid) {
     return INPC_OK;
 }
 
+struct ForwardPassArgs {
+    const uint32_t *keys, *ids;
+    const PointRec* rec;
+    float* seg_T;
+    float4* seg_C;
+    float *seg_Z, *seg_E, *image, *depth, *alpha, *blending_weights;
+    uint32_t *kept0, *kept1, *n_kept;
+    int W, H, gw, gh;
+};
+
+// One pass of the warp blend's forward: its shared memory (the per-warp rings) is above the 48 KB a kernel gets unasked.
+template <int PASS, int KIND>
+int launch_warp_forward_pass(unsigned grid, const WarpItem* items, const uint32_t* counts, unsigned* ticket, const ForwardPassArgs& a,
+                             cudaStream_t stream) {
+    static bool attr_set[kMaxDevices] = {false};
+    constexpr size_t smem = warp_forward_smem_bytes<PASS, KIND>();
+    const int rc = opt_in_dynamic_smem(blend_bilinear_warp_forward_kernel<PASS, KIND>, smem, attr_set);
+    if (rc != INPC_OK) return rc;
+    blend_bilinear_warp_forward_kernel<PASS, KIND><<<grid, kWarpBlendWarps * 32, smem, stream>>>(
+        items, counts, ticket, a.keys, a.ids, a.rec, a.seg_T, a.seg_C, a.seg_Z, a.seg_E, a.image, a.depth, a.alpha, a.blending_weights,
+        a.kept0, a.kept1, a.n_kept, a.W, a.H, a.gw, a.gh);
+    INPC_LAUNCH_CHECK("blend_bilinear_warp_forward_kernel");
+    return INPC_OK;
+}
+
 template <int KIND>
 int launch_bilinear_warp_forward(const RasterParams& rp, const PointBlob& pb, const InstanceBlob& ib, int t_alt, float* image,
                                  float* depth, float* alpha, float* blending_weights, cudaStream_t stream) {
@@ -3075,20 +3156,16 @@ int launch_bilinear_warp_forward(const RasterParams& rp, const PointBlob& pb, co
     uint32_t* kept0 = ib.ids[1 - t_alt];
     uint32_t* kept1 = ib.keys[1 - t_alt];
     const unsigned threads = kWarpBlendWarps * 32;
-    blend_bilinear_warp_forward_kernel<PASS_FIRST, KIND><<<grid, threads, 0, stream>>>(
-        ib.items0, ib.n_segments, ib.n_segments + 2, keys, ids, pb.rec, ib.seg_T, ib.seg_C, ib.seg_Z, ib.seg_E,
-        image, depth, alpha, blending_weights, kept0, kept1, ib.n_kept, W, H, rp.gw, rp.gh);
-    INPC_LAUNCH_CHECK("blend_bilinear_warp_forward_kernel (first segments)");
-    blend_bilinear_warp_forward_kernel<PASS_PRODUCT, KIND><<<grid, threads, 0, stream>>>(
-        ib.items1, ib.n_segments, ib.n_segments + 3, keys, ids, pb.rec, ib.seg_T, ib.seg_C, ib.seg_Z, ib.seg_E,
-        image, depth, alpha, blending_weights, kept0, kept1, ib.n_kept, W, H, rp.gw, rp.gh);
-    INPC_LAUNCH_CHECK("blend_bilinear_warp_forward_kernel (products)");
+    const ForwardPassArgs a{keys, ids, pb.rec, ib.seg_T, ib.seg_C, ib.seg_Z, ib.seg_E, image, depth, alpha, blending_weights,
+                            kept0, kept1, ib.n_kept, W, H, rp.gw, rp.gh};
+    int rc_pass = launch_warp_forward_pass<PASS_FIRST, KIND>(grid, ib.items0, ib.n_segments, ib.n_segments + 2, a, stream);
+    if (rc_pass != INPC_OK) return rc_pass;
+    rc_pass = launch_warp_forward_pass<PASS_PRODUCT, KIND>(grid, ib.items1, ib.n_segments, ib.n_segments + 3, a, stream);
+    if (rc_pass != INPC_OK) return rc_pass;
     warp_blend_prefix_kernel<<<grid, threads, 0, stream>>>(ib.items0, ib.n_segments, ib.seg_T);
     INPC_LAUNCH_CHECK("warp_blend_prefix_kernel");
-    blend_bilinear_warp_forward_kernel<PASS_REST, KIND><<<grid, threads, 0, stream>>>(
-        ib.items1, ib.n_segments, ib.n_segments + 4, keys, ids, pb.rec, ib.seg_T, ib.seg_C, ib.seg_Z, ib.seg_E,
-        image, depth, alpha, blending_weights, kept0, kept1, ib.n_kept, W, H, rp.gw, rp.gh);
-    INPC_LAUNCH_CHECK("blend_bilinear_warp_forward_kernel (later segments)");
+    rc_pass = launch_warp_forward_pass<PASS_REST, KIND>(grid, ib.items1, ib.n_segments, ib.n_segments + 4, a, stream);
+    if (rc_pass != INPC_OK) return rc_pass;
     warp_blend_combine_kernel<KIND><<<grid, threads, 0, stream>>>(ib.items0, ib.n_segments, ib.seg_C, ib.seg_Z, ib.seg_E,
                                                                       image, depth, alpha, W, H, rp.gw, rp.gh);
     INPC_LAUNCH_CHECK("warp_blend_combine_kernel");
@@ -3102,7 +3179,10 @@ int launch_bilinear_warp_backward(const RasterParams& rp, const PointBlob& pb, c
     const int rc = warp_blend_grid(&grid);
     if (rc != INPC_OK) return rc;
     INPC_CUDA_TRY(cudaMemsetAsync(ib.n_segments + 5, 0, sizeof(uint32_t), stream));   // the work ticket
-    blend_bilinear_warp_backward_kernel<<<grid, kWarpBlendWarps * 32, 0, stream>>>(
+    static bool attr_set[kMaxDevices] = {false};
+    const int rc_attr = opt_in_dynamic_smem(blend_bilinear_warp_backward_kernel, kWarpBackwardSmemBytes, attr_set);
+    if (rc_attr != INPC_OK) return rc_attr;
+    blend_bilinear_warp_backward_kernel<<<grid, kWarpBlendWarps * 32, kWarpBackwardSmemBytes, stream>>>(
         ib.items0, ib.items1, ib.n_segments, ib.n_segments + 5, ib.ids[1 - t_alt], ib.keys[1 - t_alt], ib.n_kept, pb.rec,
         ib.seg_T, ib.seg_C, grad_image, grad_alpha, image, alpha, slot_grad, slot_mask, rp.v.width, rp.v.height, rp.gw);
     INPC_LAUNCH_CHECK("blend_bilinear_warp_backward_kernel");
@@ -3613,3 +3693,4 @@ extern "C" int inpc_raster_debug_copy(const inpc_raster_state* state, const inpc
     }
     return INPC_OK;
 }
+
