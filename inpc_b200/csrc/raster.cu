@@ -594,16 +594,24 @@ __global__ void __launch_bounds__(kInstThreads) emit_instances_kernel(const uint
 __global__ void __launch_bounds__(256) tile_ranges_kernel(const uint32_t* __restrict__ keys, int64_t n_instances_arg,
                                                           const unsigned long long* __restrict__ n_instances_dev,
                                                           uint2* __restrict__ ranges) {
-    constexpr int kPer = 8;
+    constexpr int kPer = 8;   // two 16-byte loads per thread (the key array is 256-byte aligned)
     const int64_t n_instances = n_instances_dev ? (int64_t)*n_instances_dev : n_instances_arg;
     const int64_t first = ((int64_t)blockIdx.x * 256 + threadIdx.x) * kPer;
     if (first >= n_instances) return;
     uint32_t prev = first > 0 ? __ldg(keys + first - 1) & kTileKeyMask : 0u;
+    uint32_t k8[kPer];
+    if (first + kPer <= n_instances) {
+        const uint4 a = __ldg(reinterpret_cast<const uint4*>(keys + first)), b = __ldg(reinterpret_cast<const uint4*>(keys + first) + 1);
+        k8[0] = a.x; k8[1] = a.y; k8[2] = a.z; k8[3] = a.w; k8[4] = b.x; k8[5] = b.y; k8[6] = b.z; k8[7] = b.w;
+    } else {
+#pragma unroll
+        for (int k = 0; k < kPer; ++k) k8[k] = first + k < n_instances ? __ldg(keys + first + k) : 0u;
+    }
 #pragma unroll
     for (int k = 0; k < kPer; ++k) {
         const int64_t i = first + k;
         if (i >= n_instances) break;
-        const uint32_t key = __ldg(keys + i) & kTileKeyMask;
+        const uint32_t key = k8[k] & kTileKeyMask;
         if (i == 0) ranges[key].x = 0u;
         else if (key != prev) { ranges[prev].y = (unsigned)i; ranges[key].x = (unsigned)i; }
         if (i == n_instances - 1) ranges[key].y = (unsigned)n_instances;
@@ -1287,7 +1295,7 @@ __device__ __forceinline__ unsigned warp_segments(unsigned len) {
 __global__ void __launch_bounds__(kScanThreads) warp_items_scan_kernel(const uint2* __restrict__ ranges, int n_tiles,
                                                                       uint32_t* __restrict__ tile_first, uint32_t* __restrict__ tile_rank,
                                                                       uint32_t* __restrict__ counts) {
-    constexpr int kItems = 4;
+    constexpr int kItems = 16;   // 2^14 tiles per round: one round for images up to 1024 x 1024
     __shared__ unsigned s_scan[kScanThreads / 32 + 1];
     unsigned run_seg = 0, run_tiles = 0;
     for (int base = 0; base < n_tiles; base += kScanThreads * kItems) {
@@ -1295,14 +1303,15 @@ __global__ void __launch_bounds__(kScanThreads) warp_items_scan_kernel(const uin
         unsigned ns[kItems];
         unsigned sum_seg = 0, sum_tiles = 0;
 #pragma unroll
-        for (int k = 0; k < kItems; ++k) {
-            ns[k] = 0u;
-            if (t0 + k < n_tiles) {
-                const uint2 r = __ldg(ranges + t0 + k);
-                ns[k] = r.y > r.x ? warp_segments(r.y - r.x) : 0u;
-            }
-            sum_seg += ns[k];
-            sum_tiles += ns[k] ? 1u : 0u;
+        for (int k = 0; k < kItems; k += 2) {
+            // two ranges per 16-byte load (t0 is even, the array 256-byte aligned)
+            uint4 r = make_uint4(0u, 0u, 0u, 0u);
+            if (t0 + k + 1 < n_tiles) r = __ldg(reinterpret_cast<const uint4*>(ranges + t0 + k));
+            else if (t0 + k < n_tiles) { const uint2 r0 = __ldg(ranges + t0 + k); r.x = r0.x; r.y = r0.y; }
+            ns[k] = r.y > r.x ? warp_segments(r.y - r.x) : 0u;
+            ns[k + 1] = r.w > r.z ? warp_segments(r.w - r.z) : 0u;
+            sum_seg += ns[k] + ns[k + 1];
+            sum_tiles += (ns[k] ? 1u : 0u) + (ns[k + 1] ? 1u : 0u);
         }
         // both scans in one: segments in the low 20 bits would overflow, so two calls
         unsigned total_seg, total_tiles;
