@@ -1782,10 +1782,10 @@ struct __align__(16) WarpBackwardSmem {
     float4 ring_a[kGatherDepth][32];        // records of the batches in flight (see the forward pass): position, alpha ...
     float4 ring_f[kGatherDepth][32];        // ... and features
     float4 pixel_grad[32];                  // image gradient of the half's pixels
-    float2 frag[kBatchFragments];           // fragments in per-pixel order: alpha, 1 / max(1 - alpha, eps)
-    uint32_t frag_src[kBatchFragments];     // lane of the staged instance the fragment belongs to
-    float frag_bw[kBatchFragments];         // blending weight the fragment got (0: it was dropped)
-    float frag_dalpha[kBatchFragments];     // dL/dalpha of the fragment
+    float4 frag_diff[kBatchFragments];      // per fragment: colour accumulated up to and including it, minus the final colour
+    float2 frag[kBatchFragments];           // fragments in per-pixel order: alpha, lane of the staged instance
+    float frag_seen[kBatchFragments];       // transmittance the fragment met (negative: it was dropped)
+    float pixel_k[32];                      // grad_alpha * (1 - alpha) of the half's pixels
     uint32_t ring_id[kGatherDepth][32];     // point ids of the batches in flight (0xFFFFFFFF: no instance)
     unsigned mask[32];
     unsigned off[32];
@@ -1845,6 +1845,7 @@ __global__ void __launch_bounds__(kWarpBlendWarps * 32, 3) blend_bilinear_warp_b
         }
         __syncwarp();   // the previous item's readers of pixel_grad are through
         sm.pixel_grad[lane] = g;
+        sm.pixel_k[lane] = K;
         unsigned done_w = __ballot_sync(kFull, done);
 
         // ids kIdsAhead batches ahead of their gather, records kGatherDepth - 1 batches ahead of their use
@@ -1909,24 +1910,25 @@ __global__ void __launch_bounds__(kWarpBlendWarps * 32, 3) blend_bilinear_warp_b
                 slot[c] = 0;
                 if (pix[c] >= 0) {
                     slot[c] = (int)(sm.off[pix[c]] + __popc(sm.mask[pix[c]] & lt_mask));
-                    sm.frag[slot[c]] = make_float2(al[c], 1.0f / fmaxf(1.0f - al[c], kOneMinusAlphaEps));
-                    sm.frag_src[slot[c]] = lane;
+                    sm.frag[slot[c]] = make_float2(al[c], __uint_as_float(lane));
                 }
             }
             __syncwarp();
             if (my_mask) sm.mask[lane] = 0u;
-            // branch-free steps in chunks whose loads are issued together (see the forward pass)
-            constexpr int kChunk = 2;
+            // The serial part, per pixel: only what one fragment hands to the next (transmittance, running colour) is
+            // computed here, where the lanes with short lists idle; each fragment's state is left in shared memory
+            // and the gradient arithmetic follows below, per instance, with every staged lane busy.  Branch-free
+            // steps in chunks whose loads are issued together (see the forward pass).
+            constexpr int kChunk = 4;
             for (unsigned k0 = off; k0 < off + cnt; k0 += kChunk) {
-                float a[kChunk], rcp[kChunk];
+                float a[kChunk];
                 float4 f[kChunk];
 #pragma unroll
                 for (int u = 0; u < kChunk; ++u) {
                     const unsigned k = min(k0 + u, off + cnt - 1u);
                     const float2 e = sm.frag[k];
                     a[u] = e.x;
-                    rcp[u] = e.y;
-                    f[u] = sm.ring_f[stage][sm.frag_src[k]];
+                    f[u] = sm.ring_f[stage][__float_as_uint(e.y)];
                 }
 #pragma unroll
                 for (int u = 0; u < kChunk; ++u) {
@@ -1934,13 +1936,9 @@ __global__ void __launch_bounds__(kWarpBlendWarps * 32, 3) blend_bilinear_warp_b
                     const bool live = !done && in_list;
                     const float bw = Tr * a[u];
                     const float4 cr = make_float4(Crun.x + bw * f[u].x, Crun.y + bw * f[u].y, Crun.z + bw * f[u].z, Crun.w + bw * f[u].w);
-                    const float from_features = (Tr * f[u].x + (cr.x - Cfin.x) * rcp[u]) * g.x +
-                                                (Tr * f[u].y + (cr.y - Cfin.y) * rcp[u]) * g.y +
-                                                (Tr * f[u].z + (cr.z - Cfin.z) * rcp[u]) * g.z +
-                                                (Tr * f[u].w + (cr.w - Cfin.w) * rcp[u]) * g.w;
                     if (in_list) {
-                        sm.frag_bw[k0 + u] = live ? bw : 0.0f;
-                        sm.frag_dalpha[k0 + u] = live ? from_features + K * rcp[u] : 0.0f;
+                        sm.frag_seen[k0 + u] = live ? Tr : -1.0f;
+                        sm.frag_diff[k0 + u] = make_float4(cr.x - Cfin.x, cr.y - Cfin.y, cr.z - Cfin.z, cr.w - Cfin.w);
                     }
                     Crun = live ? cr : Crun;
                     Tr = live ? Tr * (1.0f - a[u]) : Tr;
@@ -1950,6 +1948,7 @@ __global__ void __launch_bounds__(kWarpBlendWarps * 32, 3) blend_bilinear_warp_b
             __syncwarp();
             // gradients of every staged instance: its (up to) four fragments in fixed corner order
             if (staged) {
+                const float4 fo = sm.ring_f[stage][lane];
                 float4 sf = make_float4(0.f, 0.f, 0.f, 0.f);
                 float so = 0.0f;
 #pragma unroll
@@ -1957,12 +1956,17 @@ __global__ void __launch_bounds__(kWarpBlendWarps * 32, 3) blend_bilinear_warp_b
                     float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
                     float o = 0.0f;
                     if (pix[c] >= 0) {
-                        const float bw = sm.frag_bw[slot[c]];
-                        if (bw > 0.0f) {
+                        const float seen = sm.frag_seen[slot[c]];
+                        if (seen >= 0.0f) {
+                            const float4 d = sm.frag_diff[slot[c]];
                             const float4 pg = sm.pixel_grad[pix[c]];
-                            v = make_float4(bw * pg.x, bw * pg.y, bw * pg.z, bw * pg.w);
+                            const float rcp = 1.0f / fmaxf(1.0f - al[c], kOneMinusAlphaEps);
+                            const float bw = seen * al[c];
+                            const float from_features = (seen * fo.x + d.x * rcp) * pg.x + (seen * fo.y + d.y * rcp) * pg.y +
+                                                        (seen * fo.z + d.z * rcp) * pg.z + (seen * fo.w + d.w * rcp) * pg.w;
+                            o = (from_features + sm.pixel_k[pix[c]] * rcp) * wg[c];
+                            if (bw > 0.0f) v = make_float4(bw * pg.x, bw * pg.y, bw * pg.z, bw * pg.w);
                         }
-                        o = sm.frag_dalpha[slot[c]] * wg[c];
                     }
                     if (c == 0) { sf = v; so = o; }
                     else { sf.x += v.x; sf.y += v.y; sf.z += v.z; sf.w += v.w; so += o; }
