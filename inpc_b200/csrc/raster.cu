@@ -1373,28 +1373,33 @@ __global__ void __launch_bounds__(256) warp_items_fill_kernel(const uint2* __res
 // Asynchronous copies (global -> shared, 16 bytes, not through registers) and their completion groups.
 __device__ __forceinline__ void async_copy_16(void* smem_dst, const void* gmem_src) {
     const unsigned d = (unsigned)__cvta_generic_to_shared(smem_dst);
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(gmem_src) : "memory");
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 16;" ::"r"(d), "l"(gmem_src) : "memory");
 }
 __device__ __forceinline__ void async_copy_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N>
 __device__ __forceinline__ void async_copy_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
 // A warp walks its list one batch of 32 instances at a time, and a batch cannot start before its 32 records have
-// arrived from DRAM (gathers, a microsecond or two under load).  Measured with one batch in flight: 2 - 3 us per
-// batch whatever the load on the SM, i.e. the items with the longest lists -- which set the duration of a pass --
-// ran at the speed of one memory round trip per batch.  So the records of the next kGatherDepth - 1 batches are
-// kept in flight, copied asynchronously into a ring in shared memory.
-constexpr int kGatherDepth = 4;   // power of two
+// arrived (gathers from DRAM or, for the other half of the tile and for neighbouring tiles, from L1: hence the
+// L1-caching form of the copy -- the form that bypasses L1 made the blend of a dense 2^25-point scene 30 % slower).
+// The records of the next batch travel while the current one is blended, copied asynchronously into a two-stage ring
+// in shared memory rather than through registers, and the per-pixel loops read a fragment's features from that
+// ring instead of from a copy per fragment.  Measured with four stages (three batches in flight): the same
+// single-view time, but 6 % less throughput with four views in flight on four streams (4985 against 5315
+// Mpoints/s), since the larger rings leave room for fewer blocks of other views' kernels on an SM.
+constexpr int kGatherDepthFilter = 2;     // stages of the ring, a power of two: first segments and products,
+constexpr int kGatherDepthRest = 2;       // later segments,
+constexpr int kGatherDepthBackward = 2;   // backward pass
 constexpr int kIdsAhead = 3;      // later segments: batches whose point ids are loaded ahead of their gather
 
 // Shared memory of one warp of the forward passes.
-template <bool BLEND, bool WEIGHTS>
+template <bool BLEND, bool WEIGHTS, int DEPTH>
 struct __align__(16) WarpForwardSmem {
-    float4 ring_a[kGatherDepth][32];                 // records of the batches in flight: position, alpha, depth ...
-    float4 ring_f[BLEND ? kGatherDepth : 1][32];     // ... and features
+    float4 ring_a[DEPTH][32];                        // records of the batches in flight: position, alpha, depth ...
+    float4 ring_f[BLEND ? DEPTH : 1][32];            // ... and features
     float2 frag[kBatchFragments];                    // fragments in per-pixel order: alpha, lane of the staged instance
     float frag_seen[WEIGHTS ? kBatchFragments : 1];  // transmittance the fragment met (0: it was dropped)
-    uint32_t ring_id[kGatherDepth][32];              // point ids of the batches in flight (0xFFFFFFFF: no instance)
+    uint32_t ring_id[DEPTH][32];                     // point ids of the batches in flight (0xFFFFFFFF: no instance)
     unsigned mask[32];                               // per pixel: staged instances with a fragment there
     unsigned off[32];                                // per pixel: first slot of its fragment list
     uint32_t queue[kQueueCap];
@@ -1402,7 +1407,9 @@ struct __align__(16) WarpForwardSmem {
 
 template <int PASS, int KIND>
 constexpr size_t warp_forward_smem_bytes() {
-    return 256 * sizeof(unsigned long long) + kWarpBlendWarps * sizeof(WarpForwardSmem<PASS != PASS_PRODUCT, PASS != PASS_PRODUCT && KIND == BLEND_TRAIN>);
+    return 256 * sizeof(unsigned long long) +
+           kWarpBlendWarps * sizeof(WarpForwardSmem<PASS != PASS_PRODUCT, PASS != PASS_PRODUCT && KIND == BLEND_TRAIN,
+                                                    PASS == PASS_REST ? kGatherDepthRest : kGatherDepthFilter>);
 }
 
 template <int PASS, int KIND>
@@ -1417,7 +1424,8 @@ __global__ void __launch_bounds__(kWarpBlendWarps * 32, 3) blend_bilinear_warp_f
     constexpr bool kBlend = PASS != PASS_PRODUCT;               // colours and weights; PRODUCT only multiplies
     constexpr bool kWeights = kBlend && KIND == BLEND_TRAIN;
     constexpr bool kDepth = kBlend && KIND == BLEND_INFER;
-    using Smem = WarpForwardSmem<kBlend, kWeights>;
+    constexpr int kGatherDepth = PASS == PASS_REST ? kGatherDepthRest : kGatherDepthFilter;
+    using Smem = WarpForwardSmem<kBlend, kWeights, kGatherDepth>;
     extern __shared__ __align__(16) unsigned char blend_smem[];
     unsigned long long* s_reach = reinterpret_cast<unsigned long long*>(blend_smem);     // key code -> pixels reached
     Smem& sm = reinterpret_cast<Smem*>(blend_smem + 256 * sizeof(unsigned long long))[threadIdx.x >> 5];
@@ -1779,14 +1787,14 @@ __global__ void __launch_bounds__(kWarpBlendWarps * 32) warp_blend_combine_kerne
 
 // Shared memory of one warp of the backward pass.
 struct __align__(16) WarpBackwardSmem {
-    float4 ring_a[kGatherDepth][32];        // records of the batches in flight (see the forward pass): position, alpha ...
-    float4 ring_f[kGatherDepth][32];        // ... and features
+    float4 ring_a[kGatherDepthBackward][32];   // records of the batches in flight (see the forward pass): position, alpha ...
+    float4 ring_f[kGatherDepthBackward][32];   // ... and features
     float4 pixel_grad[32];                  // image gradient of the half's pixels
     float4 frag_diff[kBatchFragments];      // per fragment: colour accumulated up to and including it, minus the final colour
     float2 frag[kBatchFragments];           // fragments in per-pixel order: alpha, lane of the staged instance
     float frag_seen[kBatchFragments];       // transmittance the fragment met (negative: it was dropped)
     float pixel_k[32];                      // grad_alpha * (1 - alpha) of the half's pixels
-    uint32_t ring_id[kGatherDepth][32];     // point ids of the batches in flight (0xFFFFFFFF: no instance)
+    uint32_t ring_id[kGatherDepthBackward][32];   // point ids of the batches in flight (0xFFFFFFFF: no instance)
     unsigned mask[32];
     unsigned off[32];
 };
@@ -1801,6 +1809,7 @@ __global__ void __launch_bounds__(kWarpBlendWarps * 32, 3) blend_bilinear_warp_b
     float4* __restrict__ slot_grad, unsigned* __restrict__ slot_mask, int width, int height, int gw) {
     constexpr unsigned kFull = 0xffffffffu;
     constexpr unsigned kNoInstance = 0xffffffffu;
+    constexpr int kGatherDepth = kGatherDepthBackward;
     extern __shared__ __align__(16) unsigned char blend_smem[];
     const unsigned lane = lane_id();
     const unsigned lt_mask = (1u << lane) - 1u;
