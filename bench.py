@@ -298,17 +298,20 @@ def run_ours(args):
     def host_inputs(vi, stream):
         # this view's inputs come from pinned host memory on a copy stream of their own, so that the copies run
         # ahead of, and under, the kernels of the views in flight
+        # (the camera first: sampling and the forward pass wait for it alone, the backward pass for the gradients)
         with torch.cuda.stream(copy_stream):
-            gi = pinned_gi.to(device, non_blocking=True)
-            ga = pinned_ga.to(device, non_blocking=True)
             w2c, cpos = pinned_views[vi]
             w2c_d, cpos_d = w2c.to(device, non_blocking=True), cpos.to(device, non_blocking=True)
-            copied = torch.cuda.Event()
-            copied.record(copy_stream)
-        stream.wait_event(copied)
+            camera_copied = torch.cuda.Event()
+            camera_copied.record(copy_stream)
+            gi = pinned_gi.to(device, non_blocking=True)
+            ga = pinned_ga.to(device, non_blocking=True)
+            grads_copied = torch.cuda.Event()
+            grads_copied.record(copy_stream)
+        stream.wait_event(camera_copied)
         for tensor in (gi, ga, w2c_d, cpos_d):
             tensor.record_stream(stream)
-        return View(wl["views_host"][vi].camera, w2c_d, cpos_d), gi, ga
+        return View(wl["views_host"][vi].camera, w2c_d, cpos_d), gi, ga, grads_copied
 
     def e2e_step():
         copy_stream.wait_stream(torch.cuda.current_stream())

@@ -148,9 +148,10 @@ class ViewShardedTrainer:
         return self._streams, self._appearance_parts
 
     def run_view(self, view, grad_image: torch.Tensor, grad_alpha: torch.Tensor, view_index: int | None = None,
-                 appearance: torch.Tensor | None = None, overwrite: bool = False):
+                 appearance: torch.Tensor | None = None, overwrite: bool = False, grads_ready=None):
         """One view, forward and backward.  `view_index` pins the random stream to the view, so the
-        result does not depend on which rank renders it."""
+        result does not depend on which rank renders it.  `grads_ready` (a CUDA event) is waited for between the
+        forward and the backward pass: upstream gradients that are still being copied do not hold up the forward."""
         t = self.tree
         if view_index is not None:
             self.sampler.set_rng_state(view_index)
@@ -159,6 +160,8 @@ class ViewShardedTrainer:
         feats = self.features.detach().requires_grad_(True)
         opac = self.opacities.detach().requires_grad_(True)
         image, alpha, blending_weights = self.rasterizer(view, self.mode, positions, feats, opac)
+        if grads_ready is not None:
+            torch.cuda.current_stream().wait_event(grads_ready)
         torch.autograd.backward([image, alpha], [grad_image, grad_alpha])
         accumulate_view(self.buffers, indices, blending_weights, feats.grad, opac.grad, appearance, overwrite)
         return image, alpha, blending_weights, feats.grad, opac.grad
@@ -167,7 +170,8 @@ class ViewShardedTrainer:
         """All views of this rank's shard and the exchange step.  `grads` is one (grad_image, grad_alpha) pair
         used for every view, or a list with one pair per view.  `inputs(view_index, stream)`, if given, supplies
         (view, grad_image, grad_alpha) of a view instead -- e.g. copied from host memory on a stream of the
-        caller's, with `stream` made to wait for the copy.
+        caller's, with `stream` made to wait for the copy -- or (view, grad_image, grad_alpha, grads_ready) with a
+        CUDA event that marks the gradients' arrival and is waited for only before the backward pass.
 
         Streams: view k of the shard runs on stream k mod n_streams and adds its appearance sum into that
         stream's row of a partial buffer (the row's first view stores instead of adding: nothing is zero-filled).
@@ -183,17 +187,18 @@ class ViewShardedTrainer:
 
         def view_inputs(vi, stream):
             if inputs is not None:
-                return inputs(vi, stream)
+                got = inputs(vi, stream)
+                return got if len(got) == 4 else (*got, None)
             gi, ga = grads if isinstance(grads[0], torch.Tensor) else grads[vi]
-            return views[vi], gi, ga
+            return views[vi], gi, ga, None
 
         if self.n_streams == 1:
             main = torch.cuda.current_stream()
             if not mine:
                 self.buffers.appearance.zero_()
             for k, vi in enumerate(mine):
-                view, gi, ga = view_inputs(vi, main)
-                out = self.run_view(view, gi, ga, view_index=vi, appearance=self.buffers.appearance, overwrite=k == 0)
+                view, gi, ga, ready = view_inputs(vi, main)
+                out = self.run_view(view, gi, ga, view_index=vi, appearance=self.buffers.appearance, overwrite=k == 0, grads_ready=ready)
             if distributed:
                 dist.all_reduce(self.buffers.appearance, op=dist.ReduceOp.SUM, group=group)
         else:
@@ -204,8 +209,8 @@ class ViewShardedTrainer:
             for k, vi in enumerate(mine):
                 slot = k % self.n_streams
                 with torch.cuda.stream(streams[slot]):
-                    view, gi, ga = view_inputs(vi, streams[slot])
-                    out = self.run_view(view, gi, ga, view_index=vi, appearance=parts[slot], overwrite=k < self.n_streams)
+                    view, gi, ga, ready = view_inputs(vi, streams[slot])
+                    out = self.run_view(view, gi, ga, view_index=vi, appearance=parts[slot], overwrite=k < self.n_streams, grads_ready=ready)
             for slot, s in enumerate(streams):
                 with torch.cuda.stream(s):
                     if slot >= len(mine):
