@@ -543,6 +543,8 @@ constexpr uint32_t kTileKeyMask = (1u << kTileKeyBits) - 1u;
 // One (tile key, point id) pair per touched tile, row-major over the point's bounds, points in depth
 // order (src/bilinear/kernels.cu:198-220).  CODED (bilinear, 8x8 tiles): bounds and footprint origin come
 // from the packed word the projection pass left per point (see pack_quad), a 4-byte gather.
+// (Four consecutive points per thread, with the four gathers in flight together, measured the same 0.12 ms for 2^23
+// points: the kernel is bound by the throughput of the random 4-byte gathers, one 32-byte sector each, not by latency.)
 template <bool CODED>
 __global__ void __launch_bounds__(kInstThreads) emit_instances_kernel(const uint32_t* __restrict__ sorted_ids,
                                                                       const uint2* __restrict__ bounds, const uint32_t* __restrict__ quad,
