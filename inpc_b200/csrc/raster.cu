@@ -1573,7 +1573,7 @@ __global__ void __launch_bounds__(kWarpBlendWarps * 32, 3) blend_bilinear_warp_f
                     pix[c] = ok ? p : -1;
                     if (ok) atomicOr(sm.mask + p, 1u << lane);
                 }
-                if (PASS != PASS_REST || kWeights) {
+                if (PASS == PASS_PRODUCT || kWeights) {   // inference keeps no lists for a backward pass
                     // What reaches a pixel that has not stopped goes into the list of this item: FIRST's list is the
                     // backward pass's, PRODUCT's is blended by REST, REST's (what is still alive at the true
                     // transmittance; written in place, behind the part of PRODUCT's list already read) the backward
@@ -1660,7 +1660,7 @@ __global__ void __launch_bounds__(kWarpBlendWarps * 32, 3) blend_bilinear_warp_f
             async_copy_wait<0>();   // whatever is still travelling lands before the next item reuses the ring
             __syncwarp();
         }
-        if ((PASS != PASS_REST || kWeights) && lane == 0) n_kept[sidx] = n_out;
+        if ((PASS == PASS_PRODUCT || kWeights) && lane == 0) n_kept[sidx] = n_out;
 
         if (PASS == PASS_PRODUCT) {
             seg_T[sidx * 32 + lane] = Tr;          // this segment's product (Tr started at 1)
