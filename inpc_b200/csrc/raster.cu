@@ -1435,6 +1435,7 @@ __global__ void __launch_bounds__(kWarpBlendWarps * 32, 3) blend_bilinear_warp_f
     const unsigned lt_mask = (1u << lane) - 1u;
     s_reach[threadIdx.x] = key_pixels(threadIdx.x);
     sm.mask[lane] = 0u;   // the masks start at zero and every batch leaves them at zero again
+    sm.off[lane] = 0u;    // (the product pass uses both arrays as per-pixel accumulators)
     __syncthreads();
     const unsigned n_items = __ldg(counts + (PASS == PASS_FIRST ? 0 : 1)) * 2u;
     // Items are handed out one at a time through a ticket counter: consecutive items cost about the same (neighbouring
@@ -1458,14 +1459,17 @@ __global__ void __launch_bounds__(kWarpBlendWarps * 32, 3) blend_bilinear_warp_f
         const int px = px0 + (int)(lane & 7u), py = py0 + (int)(lane >> 3);
         const bool inside = px < width && py < height;
 
-        float Tr = 1.0f, T0 = 1.0f, Z = 0.0f, C0 = 0.0f, C1 = 0.0f, C2 = 0.0f, C3 = 0.0f;
+        float Tr = 1.0f, Z = 0.0f, C0 = 0.0f, C1 = 0.0f, C2 = 0.0f, C3 = 0.0f;
+        double log_sum = 0.0, log_stop = 0.0;   // PRODUCT: -log2 of the product so far, and where the pixel counts as stopped
         bool done = !inside;
         if (PASS == PASS_PRODUCT) {
             // the state segment 0 left: a pixel that has stopped there stays stopped; for the others the
             // product is taken until T0 * product falls below the threshold (the true transmittance at
-            // that point is smaller still, so everything behind is dead whatever the product says)
-            T0 = seg_T[sidx0 * 32 + lane];
+            // that point is smaller still, so everything behind is dead whatever the product says).  The margin
+            // keeps a pixel open when the sum's rounding could be what carries it over the line.
+            const float T0 = seg_T[sidx0 * 32 + lane];
             done = done || T0 < kTransmittanceEps;
+            log_stop = done ? 0.0 : log2((double)T0 / (double)kTransmittanceEps) + 1e-4;
         } else if (PASS == PASS_REST) {
             Tr = seg_T[sidx * 32 + lane];
             done = done || Tr < kTransmittanceEps;
@@ -1571,7 +1575,18 @@ __global__ void __launch_bounds__(kWarpBlendWarps * 32, 3) blend_bilinear_warp_f
                     const bool ok = staged && cx >= 0 && cx < 8 && cy >= 0 && cy < 4 && dx < 1.0f && dy < 1.0f &&
                                     !((done_w >> (p & 31)) & 1u);
                     pix[c] = ok ? p : -1;
-                    if (ok) atomicOr(sm.mask + p, 1u << lane);
+                    if (PASS != PASS_PRODUCT) {
+                        if (ok) atomicOr(sm.mask + p, 1u << lane);
+                    } else if (ok) {
+                        // A product does not care about order.  Its factors are added up as -log2(1 - alpha) in fixed
+                        // point (integer part and 24 fractional bits in two words per pixel): integer atomics commute, so
+                        // the sum is the same on every run, and none of the per-pixel ordering below is needed.
+                        const float x = 1.0f - al[c];
+                        const float t = x > 0.0f ? fminf(-log2f(x), 64.0f) : 64.0f;   // 2^-64: far below the threshold
+                        const float ti = floorf(t);
+                        atomicAdd(sm.mask + p, __float2uint_rn((t - ti) * 16777216.0f));
+                        if (ti > 0.0f) atomicAdd(sm.off + p, (unsigned)ti);
+                    }
                 }
                 if (PASS == PASS_PRODUCT || kWeights) {   // inference keeps no lists for a backward pass
                     // What reaches a pixel that has not stopped goes into the list of this item: FIRST's list is the
@@ -1585,6 +1600,19 @@ __global__ void __launch_bounds__(kWarpBlendWarps * 32, 3) blend_bilinear_warp_f
                     n_out += __popc(b);
                 }
                 __syncwarp();
+                if (PASS == PASS_PRODUCT) {
+                    const unsigned frac = sm.mask[lane], whole = sm.off[lane];
+                    if (frac | whole) {
+                        sm.mask[lane] = 0u;
+                        sm.off[lane] = 0u;
+                        log_sum += (double)whole + (double)frac * (1.0 / 16777216.0);
+                    }
+                    done = done || log_sum > log_stop;
+                    done_w = __ballot_sync(kFull, done);
+                    __syncwarp();
+                    if (done_w == kFull) break;   // every pixel has stopped: the rest of the list has no effect
+                    continue;
+                }
                 // ---- per-pixel order: offset of every pixel's list, slot of every fragment
                 const unsigned my_mask = sm.mask[lane];
                 const unsigned cnt = __popc(my_mask);
@@ -1633,9 +1661,6 @@ __global__ void __launch_bounds__(kWarpBlendWarps * 32, 3) blend_bilinear_warp_f
                             if (kDepth) Z = live ? Z + bw * zd[u] : Z;
                             Tr = live ? Tr * (1.0f - a[u]) : Tr;
                             done = done || Tr < kTransmittanceEps;
-                        } else {
-                            Tr = live ? Tr * (1.0f - a[u]) : Tr;
-                            done = done || T0 * Tr < kTransmittanceEps;
                         }
                     }
                 }
@@ -1663,7 +1688,7 @@ __global__ void __launch_bounds__(kWarpBlendWarps * 32, 3) blend_bilinear_warp_f
         if ((PASS == PASS_PRODUCT || kWeights) && lane == 0) n_kept[sidx] = n_out;
 
         if (PASS == PASS_PRODUCT) {
-            seg_T[sidx * 32 + lane] = Tr;          // this segment's product (Tr started at 1)
+            seg_T[sidx * 32 + lane] = (float)exp2(-log_sum);   // this segment's product
             continue;
         }
         const int64_t n_px = (int64_t)width * height;
