@@ -42,9 +42,9 @@ N_LEAVES = 1 << 18
 N_APPEARANCE = 1 << 22
 # DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) per (point, tile) instance of the kernels of a
 # stage, from an ncu capture of the warp blend kernels on the small case of this workload (2^22 points,
-# 5,274,412 instances, 8x8 tiles: forward passes 451.7 MB, backward 331.7 MB); the traffic of these kernels grows in
+# 5,274,412 instances, 8x8 tiles: forward passes 453.9 MB, backward 328.1 MB); the traffic of these kernels grows in
 # proportion to the instances.
-TRAFFIC_BYTES_PER_INSTANCE = {"blend_fwd": 451.7e6 / 5274412, "blend_bwd": 331.7e6 / 5274412}
+TRAFFIC_BYTES_PER_INSTANCE = {"blend_fwd": 453.9e6 / 5274412, "blend_bwd": 328.1e6 / 5274412}
 
 
 def parse_args():
