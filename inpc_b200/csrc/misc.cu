@@ -145,18 +145,35 @@ constexpr unsigned kMinFlip = 0x7FFFFFFFu;
 
 __global__ void __launch_bounds__(kThreads) leaf_stats_kernel(const long long* __restrict__ indices, const float* __restrict__ weights,
                                                               int64_t n, int64_t n_leaves, uint2* __restrict__ stats) {
+    // four samples per thread and round, their loads issued together: the kernel is bound by the latency of the
+    // random reads of `stats`, not by bandwidth
+    constexpr int kPer = 4;
     const int64_t stride = (int64_t)gridDim.x * kThreads;
-    for (int64_t i = (int64_t)blockIdx.x * kThreads + threadIdx.x; i < n; i += stride) {
-        const long long leaf = __ldg(indices + i);
-        if (leaf < 0 || leaf >= n_leaves) continue;
-        const unsigned bits = __float_as_uint(fmaxf(__ldg(weights + i), 0.0f));
-        const unsigned flipped = kMinFlip - bits;
+    for (int64_t i0 = (int64_t)blockIdx.x * kThreads + threadIdx.x; i0 < n; i0 += stride * kPer) {
+        long long leaf[kPer];
+        unsigned bits[kPer];
+        uint2 cur[kPer];
+#pragma unroll
+        for (int k = 0; k < kPer; ++k) {
+            const int64_t i = i0 + k * stride;
+            leaf[k] = i < n ? __ldg(indices + i) : -1;
+            bits[k] = i < n ? __float_as_uint(fmaxf(__ldg(weights + i), 0.0f)) : 0u;
+        }
+#pragma unroll
+        for (int k = 0; k < kPer; ++k) {
+            if (leaf[k] < 0 || leaf[k] >= n_leaves) leaf[k] = -1;
+            cur[k] = leaf[k] >= 0 ? __ldcg(stats + leaf[k]) : make_uint2(0xFFFFFFFFu, 0xFFFFFFFFu);
+        }
         // Both halves only grow, so a value that does not beat what a plain (possibly stale) read
         // returns cannot beat the current one either: most samples of a leaf that has already seen a
         // few skip both atomics.
-        const uint2 cur = __ldcg(stats + leaf);
-        if (bits > cur.x) atomicMax(&stats[leaf].x, bits);
-        if (flipped > cur.y) atomicMax(&stats[leaf].y, flipped);
+#pragma unroll
+        for (int k = 0; k < kPer; ++k) {
+            if (leaf[k] < 0) continue;
+            const unsigned flipped = kMinFlip - bits[k];
+            if (bits[k] > cur[k].x) atomicMax(&stats[leaf[k]].x, bits[k]);
+            if (flipped > cur[k].y) atomicMax(&stats[leaf[k]].y, flipped);
+        }
     }
 }
 
