@@ -1291,43 +1291,62 @@ __device__ __forceinline__ unsigned warp_segments(unsigned len) {
     return len <= kFirstSegment ? 1u : 1u + ceil_div(len - kFirstSegment, kLaterSegment);
 }
 
-// Work lists of the warp blend, step 1 (one block): tile_first[t] = number of segments of the tiles before t
-// (empty tiles have none), tile_rank[t] = number of non-empty tiles before t, counts[0] = non-empty tiles,
-// counts[1] = segments behind a tile's first.
-__global__ void __launch_bounds__(kScanThreads) warp_items_scan_kernel(const uint2* __restrict__ ranges, int n_tiles,
-                                                                      uint32_t* __restrict__ tile_first, uint32_t* __restrict__ tile_rank,
-                                                                      uint32_t* __restrict__ counts) {
-    constexpr int kItems = 16;   // 2^14 tiles per round: one round for images up to 1024 x 1024
+// Work lists of the warp blend.  Step 1 (one block per 1024 tiles): segments and non-empty tiles of the block's tiles.
+// Step 2 (one block): exclusive scan of those block sums; counts[0] = non-empty tiles, counts[1] = segments behind a
+// tile's first.  Step 3 (same blocks as step 1): every tile's position from its block's base and a scan inside the
+// block, and its items.  (One block scanning all tiles took 177 us for the 129,600 tiles of a 3840x2160 image.)
+constexpr int kItemThreads = 256;
+constexpr int kItemTilesPerThread = 4;
+constexpr int kItemTilesPerBlock = kItemThreads * kItemTilesPerThread;
+
+__device__ __forceinline__ void load_tile_segments(const uint2* __restrict__ ranges, int n_tiles, int t0, unsigned (&ns)[kItemTilesPerThread],
+                                                   uint2 (&rg)[kItemTilesPerThread]) {
+#pragma unroll
+    for (int k = 0; k < kItemTilesPerThread; k += 2) {
+        // two ranges per 16-byte load (t0 is even, the array 256-byte aligned)
+        uint4 r = make_uint4(0u, 0u, 0u, 0u);
+        if (t0 + k + 1 < n_tiles) r = __ldg(reinterpret_cast<const uint4*>(ranges + t0 + k));
+        else if (t0 + k < n_tiles) { const uint2 r0 = __ldg(ranges + t0 + k); r.x = r0.x; r.y = r0.y; }
+        rg[k] = make_uint2(r.x, r.y);
+        rg[k + 1] = make_uint2(r.z, r.w);
+        ns[k] = r.y > r.x ? warp_segments(r.y - r.x) : 0u;
+        ns[k + 1] = r.w > r.z ? warp_segments(r.w - r.z) : 0u;
+    }
+}
+
+__global__ void __launch_bounds__(kItemThreads) warp_items_count_kernel(const uint2* __restrict__ ranges, int n_tiles, uint2* __restrict__ block_sums) {
+    __shared__ unsigned s_seg[kItemThreads / 32], s_tiles[kItemThreads / 32];
+    unsigned ns[kItemTilesPerThread];
+    uint2 rg[kItemTilesPerThread];
+    load_tile_segments(ranges, n_tiles, blockIdx.x * kItemTilesPerBlock + threadIdx.x * kItemTilesPerThread, ns, rg);
+    unsigned seg = 0, tiles = 0;
+#pragma unroll
+    for (int k = 0; k < kItemTilesPerThread; ++k) { seg += ns[k]; tiles += ns[k] ? 1u : 0u; }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        seg += __shfl_down_sync(0xffffffffu, seg, o);
+        tiles += __shfl_down_sync(0xffffffffu, tiles, o);
+    }
+    if (lane_id() == 0) { s_seg[threadIdx.x >> 5] = seg; s_tiles[threadIdx.x >> 5] = tiles; }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        unsigned a = 0, c = 0;
+#pragma unroll
+        for (int w = 0; w < kItemThreads / 32; ++w) { a += s_seg[w]; c += s_tiles[w]; }
+        block_sums[blockIdx.x] = make_uint2(a, c);
+    }
+}
+
+__global__ void __launch_bounds__(kScanThreads) warp_items_scan_kernel(uint2* __restrict__ block_sums, int n_blocks, uint32_t* __restrict__ counts) {
     __shared__ unsigned s_scan[kScanThreads / 32 + 1];
     unsigned run_seg = 0, run_tiles = 0;
-    for (int base = 0; base < n_tiles; base += kScanThreads * kItems) {
-        const int t0 = base + threadIdx.x * kItems;
-        unsigned ns[kItems];
-        unsigned sum_seg = 0, sum_tiles = 0;
-#pragma unroll
-        for (int k = 0; k < kItems; k += 2) {
-            // two ranges per 16-byte load (t0 is even, the array 256-byte aligned)
-            uint4 r = make_uint4(0u, 0u, 0u, 0u);
-            if (t0 + k + 1 < n_tiles) r = __ldg(reinterpret_cast<const uint4*>(ranges + t0 + k));
-            else if (t0 + k < n_tiles) { const uint2 r0 = __ldg(ranges + t0 + k); r.x = r0.x; r.y = r0.y; }
-            ns[k] = r.y > r.x ? warp_segments(r.y - r.x) : 0u;
-            ns[k + 1] = r.w > r.z ? warp_segments(r.w - r.z) : 0u;
-            sum_seg += ns[k] + ns[k + 1];
-            sum_tiles += (ns[k] ? 1u : 0u) + (ns[k + 1] ? 1u : 0u);
-        }
-        // both scans in one: segments in the low 20 bits would overflow, so two calls
+    for (int base = 0; base < n_blocks; base += kScanThreads) {
+        const int j = base + threadIdx.x;
+        const uint2 v = j < n_blocks ? block_sums[j] : make_uint2(0u, 0u);
         unsigned total_seg, total_tiles;
-        unsigned ex_seg = run_seg + block_exclusive_scan(sum_seg, s_scan, &total_seg);
-        unsigned ex_tiles = run_tiles + block_exclusive_scan(sum_tiles, s_scan, &total_tiles);
-#pragma unroll
-        for (int k = 0; k < kItems; ++k) {
-            if (t0 + k < n_tiles) {
-                tile_first[t0 + k] = ex_seg;
-                tile_rank[t0 + k] = ex_tiles;
-                ex_seg += ns[k];
-                ex_tiles += ns[k] ? 1u : 0u;
-            }
-        }
+        const unsigned ex_seg = run_seg + block_exclusive_scan(v.x, s_scan, &total_seg);
+        const unsigned ex_tiles = run_tiles + block_exclusive_scan(v.y, s_scan, &total_tiles);
+        if (j < n_blocks) block_sums[j] = make_uint2(ex_seg, ex_tiles);
         run_seg += total_seg;
         run_tiles += total_tiles;
     }
@@ -1350,25 +1369,36 @@ __device__ __forceinline__ WarpItem load_item(const WarpItem* p) {
     return w;
 }
 
-// Step 2 (one thread per tile): items0 = segment 0 of the non-empty tiles, items1 = every later segment, tile by tile.
-__global__ void __launch_bounds__(256) warp_items_fill_kernel(const uint2* __restrict__ ranges, int n_tiles, const uint32_t* __restrict__ tile_first,
-                                                             const uint32_t* __restrict__ tile_rank, WarpItem* __restrict__ items0,
-                                                             WarpItem* __restrict__ items1) {
-    const int t = blockIdx.x * 256 + threadIdx.x;
-    if (t >= n_tiles) return;
-    const uint2 r = __ldg(ranges + t);
-    if (r.y <= r.x) return;
-    WarpItem w;
-    w.tile = (uint32_t)t; w.first = tile_first[t]; w.n_seg = warp_segments(r.y - r.x); w.pad0 = 0; w.pad1 = 0;
-    const unsigned rank = tile_rank[t];
-    for (unsigned s = 0; s < w.n_seg; ++s) {
-        w.seg = s;
-        w.begin = s == 0 ? r.x : r.x + kFirstSegment + (s - 1u) * kLaterSegment;
-        w.end = min(r.y, w.begin + (s == 0 ? kFirstSegment : kLaterSegment));
-        // later segments: position = segments before this tile minus tiles before it
-        WarpItem* dst = s == 0 ? items0 + rank : items1 + (w.first - rank + s - 1u);
-        reinterpret_cast<uint4*>(dst)[0] = make_uint4(w.tile, w.seg, w.begin, w.end);
-        reinterpret_cast<uint4*>(dst)[1] = make_uint4(w.first, w.n_seg, 0u, 0u);
+// Step 3: items0 = segment 0 of the non-empty tiles, items1 = every later segment, tile by tile.
+__global__ void __launch_bounds__(kItemThreads) warp_items_fill_kernel(const uint2* __restrict__ ranges, int n_tiles,
+                                                                      const uint2* __restrict__ block_base, WarpItem* __restrict__ items0,
+                                                                      WarpItem* __restrict__ items1) {
+    __shared__ unsigned s_scan[kItemThreads / 32 + 1];
+    unsigned ns[kItemTilesPerThread];
+    uint2 rg[kItemTilesPerThread];
+    const int t0 = blockIdx.x * kItemTilesPerBlock + threadIdx.x * kItemTilesPerThread;
+    load_tile_segments(ranges, n_tiles, t0, ns, rg);
+    unsigned seg = 0, tiles = 0;
+#pragma unroll
+    for (int k = 0; k < kItemTilesPerThread; ++k) { seg += ns[k]; tiles += ns[k] ? 1u : 0u; }
+    const uint2 base = __ldg(block_base + blockIdx.x);
+    unsigned total;
+    unsigned first = base.x + block_exclusive_scan(seg, s_scan, &total);     // segments of the tiles before this one
+    unsigned rank = base.y + block_exclusive_scan(tiles, s_scan, &total);    // non-empty tiles before this one
+#pragma unroll
+    for (int k = 0; k < kItemTilesPerThread; ++k) {
+        if (ns[k] == 0u) continue;
+        const uint2 r = rg[k];
+        for (unsigned sg = 0; sg < ns[k]; ++sg) {
+            const unsigned begin = sg == 0 ? r.x : r.x + kFirstSegment + (sg - 1u) * kLaterSegment;
+            const unsigned end = min(r.y, begin + (sg == 0 ? kFirstSegment : kLaterSegment));
+            // later segments: position = segments before this tile minus tiles before it
+            WarpItem* dst = sg == 0 ? items0 + rank : items1 + (first - rank + sg - 1u);
+            reinterpret_cast<uint4*>(dst)[0] = make_uint4((uint32_t)(t0 + k), sg, begin, end);
+            reinterpret_cast<uint4*>(dst)[1] = make_uint4(first, ns[k], 0u, 0u);
+        }
+        first += ns[k];
+        rank += 1u;
     }
 }
 
@@ -1415,7 +1445,7 @@ constexpr size_t warp_forward_smem_bytes() {
 }
 
 template <int PASS, int KIND>
-__global__ void __launch_bounds__(kWarpBlendWarps * 32, 3) blend_bilinear_warp_forward_kernel(
+__global__ void __launch_bounds__(kWarpBlendWarps * 32, PASS == PASS_PRODUCT ? 4 : 3) blend_bilinear_warp_forward_kernel(
     const WarpItem* __restrict__ items, const uint32_t* __restrict__ counts, unsigned* __restrict__ ticket, const uint32_t* __restrict__ inst_keys,
     const uint32_t* __restrict__ inst_ids, const PointRec* __restrict__ rec, float* __restrict__ seg_T, float4* __restrict__ seg_C,
     float* __restrict__ seg_Z, float* __restrict__ seg_E, float* __restrict__ image, float* __restrict__ depth_image,
@@ -1441,11 +1471,21 @@ __global__ void __launch_bounds__(kWarpBlendWarps * 32, 3) blend_bilinear_warp_f
     // Items are handed out one at a time through a ticket counter: consecutive items cost about the same (neighbouring
     // tiles, or consecutive segments of one tile), so a warp that reserved items ahead would sit on work that idle warps
     // could take (measured: holding two tickets ahead to prefetch the records made every pass 10-70 % slower).
+    // ... unless there are very many of them: a single counter hands out one ticket every 2.7 ns at best (measured:
+    // 259,200 items of a 3840x2160 image took 700 us whatever the occupancy), so with many small items a warp takes
+    // several consecutive ones per visit.
+    const unsigned per_visit = max(1u, min(8u, n_items / (gridDim.x * kWarpBlendWarps * 16u)));
+    unsigned next_item = 0, visit_end = 0;
     for (;;) {
-        unsigned item = 0;
-        if (lane == 0) item = atomicAdd(ticket, 1u);
-        item = __shfl_sync(kFull, item, 0);
-        if (item >= n_items) break;
+        if (next_item == visit_end) {
+            unsigned first_item = 0;
+            if (lane == 0) first_item = atomicAdd(ticket, per_visit);
+            first_item = __shfl_sync(kFull, first_item, 0);
+            if (first_item >= n_items) break;
+            next_item = first_item;
+            visit_end = min(first_item + per_visit, n_items);
+        }
+        const unsigned item = next_item++;
         const WarpItem it = load_item(items + (item >> 1));
         const unsigned tile = it.tile, seg = it.seg, n_seg = it.n_seg, first = it.first;
         const int half = (int)(item & 1u);
@@ -1848,11 +1888,19 @@ __global__ void __launch_bounds__(kWarpBlendWarps * 32, 3) blend_bilinear_warp_b
     const unsigned n_rest = n_items - n_first;
 
     // items one at a time through a ticket counter, the later segments first (they belong to the longest lists)
+    // (several consecutive ones per visit when there are very many, see the forward pass)
+    const unsigned per_visit = max(1u, min(8u, n_items / (gridDim.x * kWarpBlendWarps * 16u)));
+    unsigned next_item = 0, visit_end = 0;
     for (;;) {
-        unsigned item = 0;
-        if (lane == 0) item = atomicAdd(ticket, 1u);
-        item = __shfl_sync(kFull, item, 0);
-        if (item >= n_items) break;
+        if (next_item == visit_end) {
+            unsigned first_item = 0;
+            if (lane == 0) first_item = atomicAdd(ticket, per_visit);
+            first_item = __shfl_sync(kFull, first_item, 0);
+            if (first_item >= n_items) break;
+            next_item = first_item;
+            visit_end = min(first_item + per_visit, n_items);
+        }
+        const unsigned item = next_item++;
         const WarpItem it = load_item(item < n_rest ? items1 + (item >> 1) : items0 + ((item - n_rest) >> 1));
         const int half = (int)((item < n_rest ? item : item - n_rest) & 1u);
         const unsigned n_list = __ldg(n_kept + (size_t)(it.first + it.seg) * 2u + half);
@@ -2819,7 +2867,7 @@ struct InstanceBlob {
     float* seg_Z;
     float* seg_E;         // warp blend, inference: transmittance at the end of every segment
     int64_t max_segments;
-    uint32_t* tile_rank;  // warp blend: non-empty tiles before each tile
+    uint32_t* tile_rank;  // warp blend: per block of 1024 tiles, the segments and the non-empty tiles before it
     WarpItem* items0;     // warp blend: segment 0 of the non-empty tiles
     WarpItem* items1;     // warp blend: every segment behind a tile's first
     uint32_t* n_kept;     // warp blend: per item, length of the compacted list the forward pass blended
@@ -2857,7 +2905,7 @@ InstanceBlob carve_instance_blob(void* p, int64_t n_instances, int n_tiles, int 
     b.seg_C = c.take<float4>(px * (size_t)c4);
     b.seg_Z = c.take<float>(with_depth ? px : 0);
     b.seg_E = c.take<float>(with_depth && warp_blend ? px : 0);
-    b.tile_rank = c.take<uint32_t>(warp_blend ? (size_t)n_tiles : 0);
+    b.tile_rank = c.take<uint32_t>(warp_blend ? (size_t)n_tiles + 8 : 0);   // warp blend: (segments, tiles) per block of 1024 tiles
     b.items0 = c.take<WarpItem>(warp_blend ? (size_t)n_tiles : 0);
     b.items1 = c.take<WarpItem>(warp_blend ? (size_t)b.max_segments : 0);
     b.n_kept = c.take<uint32_t>(warp_blend ? (size_t)b.max_segments * kWarpBlendParts : 0);
@@ -3106,9 +3154,13 @@ int run_front(const RasterParams& rp, int64_t n, const float* positions, const v
     if (warp_blend) {
         StageScope scope(STAGE_SORT_TILE, stream);
         INPC_CUDA_TRY(cudaMemsetAsync(ib.n_segments, 0, 8 * sizeof(uint32_t), stream));
-        warp_items_scan_kernel<<<1, kScanThreads, 0, stream>>>(ib.ranges, n_tiles, ib.tile_first, ib.tile_rank, ib.n_segments);
+        const int item_blocks = ceil_div(n_tiles, kItemTilesPerBlock);
+        uint2* item_sums = reinterpret_cast<uint2*>(ib.tile_rank);
+        warp_items_count_kernel<<<item_blocks, kItemThreads, 0, stream>>>(ib.ranges, n_tiles, item_sums);
+        INPC_LAUNCH_CHECK("warp_items_count_kernel");
+        warp_items_scan_kernel<<<1, kScanThreads, 0, stream>>>(item_sums, item_blocks, ib.n_segments);
         INPC_LAUNCH_CHECK("warp_items_scan_kernel");
-        warp_items_fill_kernel<<<ceil_div(n_tiles, 256), 256, 0, stream>>>(ib.ranges, n_tiles, ib.tile_first, ib.tile_rank, ib.items0, ib.items1);
+        warp_items_fill_kernel<<<item_blocks, kItemThreads, 0, stream>>>(ib.ranges, n_tiles, item_sums, ib.items0, ib.items1);
         INPC_LAUNCH_CHECK("warp_items_fill_kernel");
     } else {
         StageScope scope(STAGE_SORT_TILE, stream);
