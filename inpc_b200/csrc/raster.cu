@@ -1474,7 +1474,7 @@ __global__ void __launch_bounds__(kWarpBlendWarps * 32, PASS == PASS_PRODUCT ? 4
     // ... unless there are very many of them: a single counter hands out one ticket every 2.7 ns at best (measured:
     // 259,200 items of a 3840x2160 image took 700 us whatever the occupancy), so with many small items a warp takes
     // several consecutive ones per visit.
-    const unsigned per_visit = max(1u, min(8u, n_items / (gridDim.x * kWarpBlendWarps * 16u)));
+    const unsigned per_visit = max(1u, min(8u, n_items / (gridDim.x * kWarpBlendWarps * 8u)));
     unsigned next_item = 0, visit_end = 0;
     for (;;) {
         if (next_item == visit_end) {
@@ -1889,7 +1889,7 @@ __global__ void __launch_bounds__(kWarpBlendWarps * 32, 3) blend_bilinear_warp_b
 
     // items one at a time through a ticket counter, the later segments first (they belong to the longest lists)
     // (several consecutive ones per visit when there are very many, see the forward pass)
-    const unsigned per_visit = max(1u, min(8u, n_items / (gridDim.x * kWarpBlendWarps * 16u)));
+    const unsigned per_visit = max(1u, min(8u, n_items / (gridDim.x * kWarpBlendWarps * 8u)));
     unsigned next_item = 0, visit_end = 0;
     for (;;) {
         if (next_item == visit_end) {
