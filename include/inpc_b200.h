@@ -58,7 +58,7 @@ typedef struct inpc_raster_state {
     int64_t n_instances;      /* likewise */
     int32_t tile_size;
     int32_t mode;
-    uint32_t depth_key_base;  /* smallest depth bit pattern among the visible points (sort keys are offsets from it) */
+    uint32_t depth_key_base;  /* depth bit pattern the sort keys are offsets from: the smallest visible one, or the near plane's when the counts are deferred */
     int32_t depth_key_bits;   /* significant bits of the largest offset */
     int32_t channels;         /* blended channels: 4 for the spherical-harmonics layout, else the feature-row width */
     int32_t deferred_counts;  /* 1: no count was read back; scratch is sized for 4 instances per point */

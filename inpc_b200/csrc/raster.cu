@@ -260,7 +260,8 @@ __global__ void __launch_bounds__(kPreThreads) visibility_count_kernel(
         // totals of this group of 4 chunks: the one-block scan runs over groups, four times fewer entries
         group_visible[blockIdx.x] = tv;
         group_instances[blockIdx.x] = ti;
-        if (tlo <= thi) { atomicMin(depth_min, tlo); atomicMax(depth_max, thi); }
+        // (callers that know a bound on the depths beforehand pass no pointers; measured: no difference in time)
+        if (depth_min && tlo <= thi) { atomicMin(depth_min, tlo); atomicMax(depth_max, thi); }
     }
 }
 
@@ -270,9 +271,10 @@ constexpr int kScanThreads = 1024;
 __global__ void __launch_bounds__(kScanThreads) scan_block_counts_kernel(unsigned* __restrict__ block_visible,
                                                                          const unsigned long long* __restrict__ block_instances,
                                                                          int64_t n_blocks,
-                                                                         const unsigned* __restrict__ depth_min,
-                                                                         const unsigned* __restrict__ depth_max,
-                                                                         unsigned long long* __restrict__ counters) {
+                                                                         unsigned* __restrict__ depth_min,
+                                                                         unsigned* __restrict__ depth_max,
+                                                                         unsigned long long* __restrict__ counters, int fixed_range,
+                                                                         unsigned fixed_lo, unsigned fixed_hi) {
     constexpr int kItems = 8;
     __shared__ unsigned s_scan[kScanThreads / 32 + 1];
     __shared__ unsigned long long s_inst[kScanThreads / 32];
@@ -306,6 +308,8 @@ __global__ void __launch_bounds__(kScanThreads) scan_block_counts_kernel(unsigne
         for (int w = 0; w < kScanThreads / 32; ++w) t += s_inst[w];
         counters[0] = running;
         counters[1] = t;
+        // the range of depth bit patterns the keys are offsets into: measured by the count pass, or given by the caller
+        if (fixed_range) { *depth_min = fixed_lo; *depth_max = fixed_hi; }
         counters[2] = *depth_min;
         counters[3] = *depth_max;
     }
@@ -3050,14 +3054,16 @@ int run_front(const RasterParams& rp, int64_t n, const float* positions, const v
         unsigned long long* host = nullptr;
         cudaEvent_t ready = nullptr;
         int pack_count = -1;
+        uint32_t lo_bits = 0u, hi_bits = 0u;
         if (deferred) {
-            // depth keys are offsets from the smallest visible depth's bit pattern: the near and far planes bound them
+            // depth keys are offsets from the near plane's bit pattern, bounded by the far plane's: nothing is measured
             const float lo = rp.v.near_plane > 0.0f ? rp.v.near_plane : 0.0f, hi = rp.v.far_plane > lo ? rp.v.far_plane : lo;
-            uint32_t lo_bits, hi_bits;
             memcpy(&lo_bits, &lo, 4);
             memcpy(&hi_bits, &hi, 4);
+            if (!(rp.v.near_plane > 0.0f)) { lo_bits = 0u; hi_bits = 0xFFFFFFFFu; }
             key_bits = rp.v.near_plane > 0.0f ? bit_length(hi_bits - lo_bits) : 32;
             if (key_bits == 0) key_bits = 1;
+            key_base = lo_bits;
             pack_count = key_bits <= (int)kCountShift ? 1 : 0;
             n_visible = n;                // capacities from here on
             n_instances = 4 * n;
@@ -3072,9 +3078,11 @@ int run_front(const RasterParams& rp, int64_t n, const float* positions, const v
             INPC_CUDA_TRY(cudaMemsetAsync(pb.depth_max, 0, sizeof(unsigned), stream));
             const int64_t groups = ceil_div<int64_t>(nb, 4);
             visibility_count_kernel<MODE, VARIANT><<<(unsigned)groups, kPreThreads, 0, stream>>>(ps, rp, pb.block_visible, pb.group_visible,
-                                                                                             pb.group_instances, pb.depth_min, pb.depth_max);
+                                                                                             pb.group_instances, deferred ? nullptr : pb.depth_min,
+                                                                                             deferred ? nullptr : pb.depth_max);
             INPC_LAUNCH_CHECK("visibility_count_kernel");
-            scan_block_counts_kernel<<<1, kScanThreads, 0, stream>>>(pb.group_visible, pb.group_instances, groups, pb.depth_min, pb.depth_max, pb.counters);
+            scan_block_counts_kernel<<<1, kScanThreads, 0, stream>>>(pb.group_visible, pb.group_instances, groups, pb.depth_min, pb.depth_max, pb.counters,
+                                                                     deferred ? 1 : 0, lo_bits, hi_bits);
             INPC_LAUNCH_CHECK("scan_block_counts_kernel");
             if (!deferred) {
                 INPC_CUDA_TRY(cudaMemcpyAsync(host, pb.counters, 4 * sizeof(unsigned long long), cudaMemcpyDeviceToHost, stream));
