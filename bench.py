@@ -564,20 +564,43 @@ def side_workload(name: str, tile: int, warmup: int, reps: int, points: int = N_
     device = torch.device("cuda", torch.cuda.current_device())
     g = torch.Generator().manual_seed(5)
     if impl == "reference":
-        if name != "config2":
+        if name not in ("config2", "multisample4"):
             why = ("the reference's 16-bit tile key overflows at 3840x2160 (129,600 tiles of 8x8 pixels)" if name.startswith("config4")
-                   else "not wired up for the reference arm" if name.startswith("multisample")
+                   else "the reference has no batched multi-set render" if name.startswith("multisample")
                    else "the reference has no fp32 feature-row layout")
             return {"metric": metric, "unavailable": why}
         sys.path.insert(0, str(ROOT / "oracle"))
         import ref_backend as RB
-        c = syn.config2()
-        view, pos, feats = c["view"].to(device), c["positions"].to(device), c["features"].to(device)
-        opac = c["opacities"].to(device).reshape(-1).contiguous()
-        n_points = pos.shape[0]
+        if name == "config2":
+            c = syn.config2()
+            view, pos, feats = c["view"].to(device), c["positions"].to(device), c["features"].to(device)
+            opac = c["opacities"].to(device).reshape(-1).contiguous()
+            n_points = pos.shape[0]
 
-        def step():
-            RB.render_preextracted(view, 0, pos, feats, opac, None, 1.0, 3.0, sync=False)
+            def step():
+                RB.render_preextracted(view, 0, pos, feats, opac, None, 1.0, 3.0, sync=False)
+        else:
+            # the reference's own loop (Renderer.py:99-125): one render per set on the default stream, then accumulate
+            # and compose; the sets are the ones this library's sampler draws for the other arm
+            from inpc_b200.compose import MultisampleAccumulator
+            from inpc_b200.sampling import ProbabilityFieldSampler
+            c = syn.config1(n_samples=points, n_leaves=N_LEAVES)
+            view, tree = c["view"].to(device), c["tree"].to(device)
+            del c
+            sampler = ProbabilityFieldSampler(0)
+            gd = torch.Generator(device=device).manual_seed(3)
+            sets = []
+            for _ in range(4):
+                pos = sampler.generate_expected_samples(tree.centers, tree.levels, tree.weights, view, points, 1, tree.initial_size)
+                sets.append((pos, (torch.randn((pos.shape[0], 37), generator=gd, device=device) * 0.5).to(torch.float16)))
+            n_points = sum(p.shape[0] for p, _ in sets)
+            bg = torch.zeros((4, view.camera.height, view.camera.width), device=device)
+
+            def step():
+                acc = MultisampleAccumulator(len(sets), True)
+                for p, raw in sets:
+                    acc.add(*RB.render(view, 0, p, raw, 1.0, 3.0))
+                acc.resolve(bg)
     else:
         import inpc_b200
         from inpc_b200.sampling import ProbabilityFieldSampler
