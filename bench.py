@@ -341,14 +341,18 @@ def run_ours(args):
     torch.cuda.synchronize()
     barrier(world)
     t0 = time.perf_counter()
+    e2e_marks = [t0]
     for k in range(args.steps):
         e2e_enqueue(k)
         if k > 0:
             e2e_collect(k - 1)
+            e2e_marks.append(time.perf_counter())   # step k - 1 has delivered its result
     e2e_collect(args.steps - 1)
     torch.cuda.synchronize()
+    e2e_marks.append(time.perf_counter())
     barrier(world)
     e2e_s = max_over_ranks(time.perf_counter() - t0, world, device)
+    e2e_step_ms = [round((b - a) * 1e3, 2) for a, b in zip(e2e_marks[:-1], e2e_marks[1:])]
 
     # values every rank count must reproduce: the reduced buffers of the last step (identical views, identical
     # per-view random streams, so only the order of floating-point sums differs between N = 1, 2, 4, 8)
@@ -410,7 +414,8 @@ def run_ours(args):
         "ms_per_view": elapsed_ms / args.steps / max(len(my_views), 1),
         "e2e": {"value": e2e_value, "unit": UNIT,
                 "h2d_bytes_per_step": args.views * (5 * P * 4 + 16 * 4 + 3 * 4), "d2h_bytes_per_step": 4 * world,
-                "readback": "loss of every step copied to pinned memory behind the step and waited for one step later"},
+                "readback": "loss of every step copied to pinned memory behind the step and waited for one step later",
+                "step_ms": e2e_step_ms},
         "gpu_launches": launches,
         "clocks": clock_info,
         "roofline": roofline,
